@@ -1,0 +1,27 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    from oracle_lib import OracleOnly
+    return OracleOnly()
+
+
+@pytest.fixture(scope="session")
+def ref():
+    from oracle_lib import Ref
+    if not Ref.available():
+        pytest.skip("oracle/_ref/libgai_ref.so not built (reference sources not mounted)")
+    return Ref()
