@@ -1,0 +1,259 @@
+// Linear layers over fp32 / fp16 / packed weights, the materialising dequantiser
+// and the small layout ops that sit beside them.
+//
+// y[M,N] = x[M,K] . W^T with W row-major [N,K] (reference: cpu::linear_forward,
+// core/math_cpu.cpp:117-134; ops::linear_forward_q4, core/ops.cpp:360-401; CUDA
+// side cuda/kernels.cu:482-633).
+//
+// Decode shapes (M <= 8) are HBM-bound weight streaming: one warp per output row,
+// each lane dequantises 32-weight units in registers and the row sum is a warp
+// shuffle reduction; every token of the tile reuses the registers.  Larger M walks
+// the same kernel over token tiles of 8 (weights then come from L2).
+#include "linear.cuh"
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------
+// dequantize_quant: packed -> fp16, bit-exact with ops::quant_materialize on CPU.
+// ---------------------------------------------------------------------------
+template <int KIND>
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ src,
+                                                      uint16_t* __restrict__ dst, int64_t n) {
+    const int64_t groups = (n + 7) / 8;
+    for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < groups;
+         g += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i0 = g * 8;
+        if (i0 + 8 <= n) {
+            uint32_t out[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t lo = float_to_half_bits(q_value<KIND>(src, i0 + 2 * j));
+                const uint32_t hi = float_to_half_bits(q_value<KIND>(src, i0 + 2 * j + 1));
+                out[j] = lo | (hi << 16);
+            }
+            *reinterpret_cast<uint4*>(dst + i0) = make_uint4(out[0], out[1], out[2], out[3]);
+        } else {
+            for (int64_t i = i0; i < n; ++i) dst[i] = float_to_half_bits(q_value<KIND>(src, i));
+        }
+    }
+}
+
+int dequantize(const uint8_t* src, uint16_t* dst, int64_t n, int kind) {
+    B200_REQUIRE(src && dst && n > 0, "dequantize_quant: bad arguments");
+    B200_REQUIRE(kind >= 0 && kind <= 3, "dequantize_quant: unknown kind %d", kind);
+    B200_REQUIRE((reinterpret_cast<uintptr_t>(dst) & 15) == 0, "dequantize_quant: dst must be 16-byte aligned");
+    const int64_t groups = (n + 7) / 8;
+    const int grid = (int)std::min<int64_t>(ceil_div64(groups, 256), (int64_t)num_sms() * 32);
+    switch (kind) {
+        case 0: dequant_kernel<0><<<grid, 256, 0, stream()>>>(src, dst, n); break;
+        case 1: dequant_kernel<1><<<grid, 256, 0, stream()>>>(src, dst, n); break;
+        case 2: dequant_kernel<2><<<grid, 256, 0, stream()>>>(src, dst, n); break;
+        default: dequant_kernel<3><<<grid, 256, 0, stream()>>>(src, dst, n); break;
+    }
+    B200_LAUNCH_CHECK("dequant_kernel");
+    return B200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Row-streaming GEMV (M <= MT tokens per pass).
+// ---------------------------------------------------------------------------
+template <int KIND, int MT>
+__global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(GemvArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * GEMV_WARPS + warp;
+    if (n >= a.N) return;
+    float acc[MT];
+    gemv_row<KIND, MT>(a.x, a.w, n, a.M, a.K, lane, acc);
+    if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+            if (m < a.M) a.y[(int64_t)m * a.N + n] = acc[m];
+    }
+}
+
+// Slow but general: K not a multiple of 32 (fp32 / fp16 weights only).
+template <int KIND>
+__global__ void __launch_bounds__(128) gemv_ragged_kernel(GemvArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 4 + warp;
+    if (n >= a.N) return;
+    for (int m = 0; m < a.M; ++m) {
+        float acc = 0.0f;
+        for (int k = lane; k < a.K; k += 32) {
+            const float wv = KIND == KIND_F32
+                                 ? reinterpret_cast<const float*>(a.w)[(int64_t)n * a.K + k]
+                                 : half_bits_to_float(reinterpret_cast<const uint16_t*>(a.w)[(int64_t)n * a.K + k]);
+            acc += a.x[(int64_t)m * a.K + k] * wv;
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) a.y[(int64_t)m * a.N + n] = acc;
+    }
+}
+
+template <int KIND>
+static int launch_gemv_kind(const GemvArgs& a) {
+    const int grid = ceil_div(a.N, GEMV_WARPS);
+    if (a.M == 1) gemv_kernel<KIND, 1><<<grid, GEMV_THREADS, 0, stream()>>>(a);
+    else if (a.M == 2) gemv_kernel<KIND, 2><<<grid, GEMV_THREADS, 0, stream()>>>(a);
+    else if (a.M <= 4) gemv_kernel<KIND, 4><<<grid, GEMV_THREADS, 0, stream()>>>(a);
+    else gemv_kernel<KIND, 8><<<grid, GEMV_THREADS, 0, stream()>>>(a);
+    B200_LAUNCH_CHECK("gemv_kernel");
+    return B200_OK;
+}
+
+// kind: KIND_F32 / KIND_F16 / 0..3.  Any M; tokens are processed 8 at a time.
+int linear(const float* x, const void* w, int kind, float* y, int M, int K, int N) {
+    if (M <= 0 || N <= 0) return B200_OK;   // the reference returns silently too
+    B200_REQUIRE(x && w && y, "linear: null pointer");
+    B200_REQUIRE(K > 0, "linear: K must be positive");
+    if (kind >= 0 && kind <= 3) {
+        B200_REQUIRE(K % q_block_elems(kind) == 0, "linear_forward_q4: K must be a multiple of %d",
+                     q_block_elems(kind));
+    } else {
+        B200_REQUIRE(kind == KIND_F32 || kind == KIND_F16, "linear: unknown weight kind %d", kind);
+    }
+    if (K % 32 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0 ||
+        (kind == KIND_F16 && (reinterpret_cast<uintptr_t>(w) & 15) != 0) ||
+        (kind == KIND_F32 && (reinterpret_cast<uintptr_t>(w) & 15) != 0)) {
+        B200_REQUIRE(kind == KIND_F32 || kind == KIND_F16,
+                     "linear_forward_q4: x must be 16-byte aligned");
+        GemvArgs a{x, reinterpret_cast<const uint8_t*>(w), y, M, K, N};
+        if (kind == KIND_F32) gemv_ragged_kernel<KIND_F32><<<ceil_div(N, 4), 128, 0, stream()>>>(a);
+        else gemv_ragged_kernel<KIND_F16><<<ceil_div(N, 4), 128, 0, stream()>>>(a);
+        B200_LAUNCH_CHECK("gemv_ragged_kernel");
+        return B200_OK;
+    }
+    for (int m0 = 0; m0 < M; m0 += 8) {
+        GemvArgs a{x + (int64_t)m0 * K, reinterpret_cast<const uint8_t*>(w), y + (int64_t)m0 * N,
+                   std::min(8, M - m0), K, N};
+        int rc;
+        switch (kind) {
+            case 0: rc = launch_gemv_kind<0>(a); break;
+            case 1: rc = launch_gemv_kind<1>(a); break;
+            case 2: rc = launch_gemv_kind<2>(a); break;
+            case 3: rc = launch_gemv_kind<3>(a); break;
+            case KIND_F16: rc = launch_gemv_kind<KIND_F16>(a); break;
+            default: rc = launch_gemv_kind<KIND_F32>(a); break;
+        }
+        if (rc) return rc;
+    }
+    return B200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// split_qkv, converts (cuda/kernels.cu:104,451 and k_split_qkv)
+// ---------------------------------------------------------------------------
+__global__ void split_qkv_kernel(const float* __restrict__ qkv, float* __restrict__ q,
+                                 float* __restrict__ k, float* __restrict__ v, int64_t n, int qd,
+                                 int kvd) {
+    const int w = qd + 2 * kvd;
+    const int64_t total = n * w;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / w;
+        const int c = (int)(i - r * w);
+        const float val = qkv[i];
+        if (c < qd) q[r * qd + c] = val;
+        else if (c < qd + kvd) k[r * kvd + (c - qd)] = val;
+        else v[r * kvd + (c - qd - kvd)] = val;
+    }
+}
+
+__global__ void f32_to_f16_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        dst[i] = float_to_half_bits(src[i]);
+}
+__global__ void f16_to_f32_kernel(const uint16_t* __restrict__ src, float* __restrict__ dst, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        dst[i] = half_bits_to_float(src[i]);
+}
+
+static inline int flat_grid(int64_t n) {
+    return (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div64(n, 256), (int64_t)num_sms() * 16));
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_linear_forward(const float* x, const float* w, float* y, int M, int K, int N) {
+    return linear(x, w, KIND_F32, y, M, K, N);
+}
+int b200_linear_forward_f32(const float* x, const float* w, float* y, int M, int K, int N) {
+    return linear(x, w, KIND_F32, y, M, K, N);
+}
+int b200_linear_forward_fp16(const float* x, const uint16_t* w, float* y, int M, int K, int N) {
+    return linear(x, w, KIND_F16, y, M, K, N);
+}
+int b200_linear_forward_q4(const float* x, const uint16_t* w, float* y, int M, int K, int N, int kind) {
+    if (M <= 0 || N <= 0) return B200_OK;
+    B200_REQUIRE(kind >= 0 && kind <= 3, "linear_forward_q4: unknown kind %d", kind);
+    return linear(x, w, kind, y, M, K, N);
+}
+int b200_gemm(int trans_a, int trans_b, int M, int N, int K, float alpha, const float* A, int lda,
+              const float* B, int ldb, float beta, float* C, int ldc) {
+    if (M <= 0 || N <= 0) return B200_OK;
+    if (trans_a || !trans_b || alpha != 1.0f || beta != 0.0f || lda != K || ldb != K || ldc != N)
+        return fail(B200_EUNSUPPORTED,
+                    "gemm: only C = A . B^T (alpha 1, beta 0, packed leading dimensions) is provided "
+                    "by the inference backend");
+    return linear(A, B, KIND_F32, C, M, K, N);
+}
+int b200_dequantize_quant(const uint16_t* src, uint16_t* dst, int64_t n, int kind) {
+    return dequantize(reinterpret_cast<const uint8_t*>(src), dst, n, kind);
+}
+
+// 16 reusable fp16 scratch slots for materialised weights (cuda/kernels.cu:516-541).
+static void* g_qslot[16];
+static size_t g_qslot_bytes[16];
+int b200_quant_scratch(int slot, int64_t n, uint16_t** out) {
+    B200_REQUIRE(out && n > 0, "quant_scratch: bad arguments");
+    if (slot < 0 || slot >= 16) slot = 0;
+    const size_t need = (size_t)n * 2;
+    if (g_qslot_bytes[slot] < need) {
+        if (g_qslot[slot]) B200_CUDA(cudaFree(g_qslot[slot]));
+        g_qslot[slot] = nullptr;
+        g_qslot_bytes[slot] = 0;
+        const size_t rounded = (need + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
+        B200_CUDA(cudaMalloc(&g_qslot[slot], rounded));
+        g_qslot_bytes[slot] = rounded;
+    }
+    *out = static_cast<uint16_t*>(g_qslot[slot]);
+    return B200_OK;
+}
+int b200_free_quant_scratch(void) {
+    for (int i = 0; i < 16; ++i) {
+        if (g_qslot[i]) cudaFree(g_qslot[i]);
+        g_qslot[i] = nullptr;
+        g_qslot_bytes[i] = 0;
+    }
+    return B200_OK;
+}
+
+int b200_split_qkv(const float* qkv, float* q, float* k, float* v, int64_t n, int qd, int kvd) {
+    if (n <= 0) return B200_OK;
+    B200_REQUIRE(qkv && q && k && v && qd > 0 && kvd > 0, "split_qkv: bad arguments");
+    split_qkv_kernel<<<flat_grid(n * (qd + 2 * kvd)), 256, 0, stream()>>>(qkv, q, k, v, n, qd, kvd);
+    B200_LAUNCH_CHECK("split_qkv_kernel");
+    return B200_OK;
+}
+int b200_convert_f32_to_f16(const float* src, uint16_t* dst, int64_t n) {
+    if (n <= 0) return B200_OK;
+    B200_REQUIRE(src && dst, "convert_f32_to_f16: null pointer");
+    f32_to_f16_kernel<<<flat_grid(n), 256, 0, stream()>>>(src, dst, n);
+    B200_LAUNCH_CHECK("f32_to_f16_kernel");
+    return B200_OK;
+}
+int b200_convert_f16_to_f32(const uint16_t* src, float* dst, int64_t n) {
+    if (n <= 0) return B200_OK;
+    B200_REQUIRE(src && dst, "convert_f16_to_f32: null pointer");
+    f16_to_f32_kernel<<<flat_grid(n), 256, 0, stream()>>>(src, dst, n);
+    B200_LAUNCH_CHECK("f16_to_f32_kernel");
+    return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,470 @@
+// Mixture-of-experts layer: router (softmax + top-K), deterministic expert
+// permutation, routed SwiGLU experts + shared expert, weighted combine.
+//
+// Reference arithmetic: cpu::moe_forward_bias, core/moe_cpu.cpp:198-288 (router
+// dot order :76-83, softmax core/math_cpu.cpp:546-558, top-K :85-98); kernels
+// replaced: cuda/moe.cu:170-333 (route), :623-651 (grouping), :731-958 (layer).
+//
+// Routing is reproduced bit for bit: the router logit of (token, expert) is the
+// fp32 chain s += ((a0*b0 + a1*b1) + a2*b2) + a3*b3 over groups of four in k order
+// with unfused multiplies and adds; the softmax sums in expert order; selection is
+// strict '>' in ascending expert order (lowest index wins ties).  Expert outputs
+// are combined per token in k order (no atomics), so results are run-to-run
+// bit-stable.
+#include "linear.cuh"
+
+namespace b200 {
+
+constexpr int MOE_MAX_NE = 256;
+constexpr int MOE_MAX_K = 16;
+
+// ---------------------------------------------------------------------------
+// Router: one block per token.
+//   phase A  all threads: group sums g[i][e] = ((a0b0+a1b1)+a2b2)+a3b3 -> smem
+//   phase B  thread e: the serial chain over the groups (and the scalar tail)
+//   then     softmax in expert order, K rounds of warp arg-max, renormalise
+// Shared memory: x[d] + g[chunk_groups][ne + 1] floats.
+// ---------------------------------------------------------------------------
+constexpr int ROUTE_THREADS = 256;
+
+__global__ void __launch_bounds__(ROUTE_THREADS)
+moe_route_kernel(const float* __restrict__ x, const float* __restrict__ router_w,
+                 const float* __restrict__ router_bias, float* __restrict__ probs_out,
+                 int32_t* __restrict__ idx_out, float* __restrict__ w_out, int d, int ne, int K,
+                 int chunk_groups) {
+    extern __shared__ float sm[];
+    float* sx = sm;                          // [d]
+    float* sg = sm + ((d + 3) & ~3);         // [chunk_groups][ne + 1] (padded: conflict-free both ways)
+    __shared__ float s_logit[MOE_MAX_NE];    // logits -> exp -> probs
+    __shared__ float s_sel[MOE_MAX_NE];
+    __shared__ int s_idx[MOE_MAX_K];
+    __shared__ float s_inv;
+    const int64_t t = blockIdx.x;
+    const float* xt = x + t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) sx[i] = xt[i];
+    const int groups = d >> 2;
+    float chain = 0.0f;                      // thread e's running sum
+    for (int g0 = 0; g0 < groups; g0 += chunk_groups) {
+        const int ng = min(chunk_groups, groups - g0);
+        __syncthreads();
+        // phase A: item = (e, gi) with gi fastest so a thread's loads walk a weight row
+        for (int item = threadIdx.x; item < ng * ne; item += blockDim.x) {
+            const int e = item / ng, gi = item - e * ng;
+            const int k = (g0 + gi) << 2;
+            const float4 b = *reinterpret_cast<const float4*>(router_w + (int64_t)e * d + k);
+            const float4 a = *reinterpret_cast<const float4*>(sx + k);
+            float g = __fadd_rn(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y));
+            g = __fadd_rn(g, __fmul_rn(a.z, b.z));
+            g = __fadd_rn(g, __fmul_rn(a.w, b.w));
+            sg[gi * (ne + 1) + e] = g;
+        }
+        __syncthreads();
+        // phase B
+        if (threadIdx.x < ne) {
+            const int e = threadIdx.x;
+#pragma unroll 8
+            for (int gi = 0; gi < ng; ++gi) chain = __fadd_rn(chain, sg[gi * (ne + 1) + e]);
+        }
+    }
+    if (threadIdx.x < ne) {
+        const int e = threadIdx.x;
+        for (int k = groups << 2; k < d; ++k)
+            chain = __fadd_rn(chain, __fmul_rn(sx[k], router_w[(int64_t)e * d + k]));
+        s_logit[e] = chain;
+    }
+    __syncthreads();
+    // softmax: max (order-free), exp, then the sum in expert order by one thread
+    if (threadIdx.x < 32) {
+        float mx = s_logit[0];
+        for (int e = threadIdx.x; e < ne; e += 32) mx = fmaxf(mx, s_logit[e]);
+        mx = warp_max(mx);
+        // exp in double, rounded to float: matches the CPU libm's correctly rounded expf
+        for (int e = threadIdx.x; e < ne; e += 32)
+            s_logit[e] = (float)exp((double)__fsub_rn(s_logit[e], mx));
+        __syncwarp();
+        if (threadIdx.x == 0) {
+            float sum = 0.0f;
+            for (int e = 0; e < ne; ++e) sum = __fadd_rn(sum, s_logit[e]);
+            s_inv = (sum > 1e-12f) ? __fdiv_rn(1.0f, sum) : 0.0f;
+        }
+        __syncwarp();
+        const float inv = s_inv;
+        for (int e = threadIdx.x; e < ne; e += 32) {
+            const float p = __fmul_rn(s_logit[e], inv);
+            s_logit[e] = p;
+            s_sel[e] = router_bias ? __fadd_rn(p, router_bias[e]) : p;
+        }
+        __syncwarp();
+        // K rounds of arg-max: value descending, index ascending; candidates must
+        // exceed -1e30 (the reference's initial best value); none left -> expert 0.
+        for (int k = 0; k < K; ++k) {
+            float bv = -1e30f;
+            int bi = -1;
+            for (int e = threadIdx.x; e < ne; e += 32) {
+                bool taken = false;
+                for (int j = 0; j < k; ++j) taken |= (s_idx[j] == e);
+                const float v = s_sel[e];
+                if (!taken && v > bv) { bv = v; bi = e; }   // ascending e: strict '>' keeps the lowest
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+            }
+            if (threadIdx.x == 0) s_idx[k] = bi < 0 ? 0 : bi;
+            __syncwarp();
+        }
+        if (threadIdx.x == 0) {
+            float tw[MOE_MAX_K];
+            float sum_w = 0.0f;
+            for (int k = 0; k < K; ++k) { tw[k] = s_logit[s_idx[k]]; sum_w = __fadd_rn(sum_w, tw[k]); }
+            if (sum_w > 1e-8f) {
+                const float inv_w = __fdiv_rn(1.0f, sum_w);
+                for (int k = 0; k < K; ++k) tw[k] = __fmul_rn(tw[k], inv_w);
+            } else {
+                const float uni = __fdiv_rn(1.0f, (float)K);
+                for (int k = 0; k < K; ++k) tw[k] = uni;
+            }
+            for (int k = 0; k < K; ++k) {
+                idx_out[t * K + k] = s_idx[k];
+                w_out[t * K + k] = tw[k];
+            }
+        }
+        if (probs_out)
+            for (int e = threadIdx.x; e < ne; e += 32) probs_out[t * ne + e] = s_logit[e];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Expert permutation: stable counting sort of slots s = t*K + k by expert.
+// Three kernels, no atomics on ordering: per-block histograms, a scan over
+// (expert, block), then a fill where each warp ranks its 32 slots with
+// __match_any_sync and warps are ordered through shared-memory prefix sums.
+// ---------------------------------------------------------------------------
+constexpr int PERM_THREADS = 256;
+constexpr int PERM_ITERS = 16;                             // slots per block = 256 * 16
+constexpr int PERM_CHUNK = PERM_THREADS * PERM_ITERS;
+
+__global__ void __launch_bounds__(PERM_THREADS)
+perm_count_kernel(const int32_t* __restrict__ idx, int64_t NK, int ne, int32_t* __restrict__ block_counts) {
+    __shared__ int cnt[MOE_MAX_NE];
+    for (int e = threadIdx.x; e < ne; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    const int64_t base = (int64_t)blockIdx.x * PERM_CHUNK;
+    for (int it = 0; it < PERM_ITERS; ++it) {
+        const int64_t s = base + it * PERM_THREADS + threadIdx.x;
+        if (s < NK) atomicAdd(&cnt[idx[s]], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < ne; e += blockDim.x) block_counts[(int64_t)blockIdx.x * ne + e] = cnt[e];
+}
+
+// One block; thread e walks the blocks of expert e.  block_counts becomes the
+// first output position of (block, expert); offsets[ne+1] the expert boundaries.
+__global__ void perm_scan_kernel(int32_t* __restrict__ block_counts, int nblocks, int ne,
+                                 int32_t* __restrict__ offsets) {
+    __shared__ int total[MOE_MAX_NE + 1];
+    const int e = threadIdx.x;
+    if (e < ne) {
+        int run = 0;
+        for (int b = 0; b < nblocks; ++b) {
+            const int c = block_counts[(int64_t)b * ne + e];
+            block_counts[(int64_t)b * ne + e] = run;
+            run += c;
+        }
+        total[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int i = 0; i < ne; ++i) { const int c = total[i]; total[i] = run; run += c; }
+        total[ne] = run;
+    }
+    __syncthreads();
+    if (e <= ne) offsets[e] = total[e];
+    if (e < ne) {
+        const int off = total[e];
+        for (int b = 0; b < nblocks; ++b) block_counts[(int64_t)b * ne + e] += off;
+    }
+}
+
+__global__ void __launch_bounds__(PERM_THREADS)
+perm_fill_kernel(const int32_t* __restrict__ idx, int64_t NK, int ne, const int32_t* __restrict__ block_base,
+                 int32_t* __restrict__ grouped) {
+    constexpr int NW = PERM_THREADS / 32;
+    __shared__ int cursor[MOE_MAX_NE];
+    __shared__ int wcnt[NW][MOE_MAX_NE];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = threadIdx.x; e < ne; e += blockDim.x) cursor[e] = block_base[(int64_t)blockIdx.x * ne + e];
+    const int64_t base = (int64_t)blockIdx.x * PERM_CHUNK;
+    for (int it = 0; it < PERM_ITERS; ++it) {
+        for (int i = threadIdx.x; i < NW * ne; i += blockDim.x) (&wcnt[0][0])[(i / ne) * MOE_MAX_NE + (i % ne)] = 0;
+        __syncthreads();
+        const int64_t s = base + it * PERM_THREADS + threadIdx.x;
+        const bool live = s < NK;
+        const int e = live ? idx[s] : -1 - lane;              // dead lanes match nobody
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        if (live && rank == 0) wcnt[warp][e] = __popc(peers);
+        __syncthreads();
+        if (live) {
+            int pos = cursor[e] + rank;
+            for (int w = 0; w < warp; ++w) pos += wcnt[w][e];
+            grouped[pos] = (int32_t)s;
+        }
+        __syncthreads();
+        for (int ee = threadIdx.x; ee < ne; ee += blockDim.x) {
+            int add = 0;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) add += wcnt[w][ee];
+            cursor[ee] += add;
+        }
+        __syncthreads();
+    }
+}
+
+int moe_permutation(const int32_t* idx, int64_t NK, int ne, int32_t* grouped, int32_t* offsets) {
+    B200_REQUIRE(idx && grouped && offsets, "moe_permutation: null pointer");
+    B200_REQUIRE(ne > 0 && ne <= MOE_MAX_NE, "moe_permutation: ne out of range");
+    B200_REQUIRE(NK >= 0 && NK < ((int64_t)1 << 31), "moe_permutation: slot count out of range");
+    const int nblocks = (int)std::max<int64_t>(1, ceil_div64(NK, PERM_CHUNK));
+    void* wsp;
+    int rc = workspace(WS_PERM).ensure((size_t)nblocks * ne * sizeof(int32_t) + 256, &wsp);
+    if (rc) return rc;
+    int32_t* bc = static_cast<int32_t*>(wsp);
+    perm_count_kernel<<<nblocks, PERM_THREADS, 0, stream()>>>(idx, NK, ne, bc);
+    B200_LAUNCH_CHECK("perm_count_kernel");
+    perm_scan_kernel<<<1, 320, 0, stream()>>>(bc, nblocks, ne, offsets);
+    B200_LAUNCH_CHECK("perm_scan_kernel");
+    perm_fill_kernel<<<nblocks, PERM_THREADS, 0, stream()>>>(idx, NK, ne, bc, grouped);
+    B200_LAUNCH_CHECK("perm_fill_kernel");
+    return B200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Experts, token-major (small N): every (token, k) slot and every token's shared
+// expert is an independent job.
+//   kernel 1  act[job][i] = silu(gate_e[i].x_t) * up_e[i].x_t        (one warp per i)
+//   kernel 2  out[t][j]   = shared_down[j].act_sh + sum_k w_k down_{e_k}[j].act_k
+// ---------------------------------------------------------------------------
+struct MoeArgs {
+    const float* x;
+    const uint8_t *gates, *ups, *downs, *sh_g, *sh_u, *sh_d;
+    const int32_t* idx;     // [N,K]
+    const float* w;         // [N,K]
+    float* act;             // [N*K, E]
+    float* sh_act;          // [N, SH]
+    float *s_gate, *s_up;   // optional [N*K, E]
+    float* out;             // [N, d]
+    int N, d, E, ne, K, SH;
+};
+
+template <int KIND>
+__global__ void __launch_bounds__(GEMV_THREADS) moe_gate_up_kernel(MoeArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i = blockIdx.x * GEMV_WARPS + warp;
+    const int job = blockIdx.y;
+    const int routed = a.N * a.K;
+    float g[1], u[1];
+    if (job < routed) {
+        if (i >= a.E) return;
+        const int t = job / a.K, e = a.idx[job];
+        const float* xt = a.x + (int64_t)t * a.d;
+        gemv_row<KIND, 1>(xt, a.gates, (int64_t)e * a.E + i, 1, a.d, lane, g);
+        gemv_row<KIND, 1>(xt, a.ups, (int64_t)e * a.E + i, 1, a.d, lane, u);
+        if (lane == 0) {
+            const int64_t o = (int64_t)job * a.E + i;
+            a.act[o] = silu_acc(g[0]) * u[0];
+            if (a.s_gate) a.s_gate[o] = g[0];
+            if (a.s_up) a.s_up[o] = u[0];
+        }
+    } else {
+        if (i >= a.SH) return;
+        const int t = job - routed;
+        const float* xt = a.x + (int64_t)t * a.d;
+        gemv_row<KIND, 1>(xt, a.sh_g, i, 1, a.d, lane, g);
+        gemv_row<KIND, 1>(xt, a.sh_u, i, 1, a.d, lane, u);
+        if (lane == 0) a.sh_act[(int64_t)t * a.SH + i] = silu_acc(g[0]) * u[0];
+    }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(GEMV_THREADS) moe_down_combine_kernel(MoeArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = blockIdx.x * GEMV_WARPS + warp;
+    const int t = blockIdx.y;
+    if (j >= a.d) return;
+    float r[1];
+    float acc = 0.0f;
+    if (a.sh_d) {
+        gemv_row<KIND, 1>(a.sh_act + (int64_t)t * a.SH, a.sh_d, j, 1, a.SH, lane, r);
+        acc = r[0];
+    }
+    for (int k = 0; k < a.K; ++k) {
+        const int slot = t * a.K + k;
+        const int e = a.idx[slot];
+        gemv_row<KIND, 1>(a.act + (int64_t)slot * a.E, a.downs, (int64_t)e * a.d + j, 1, a.E, lane, r);
+        acc = __fadd_rn(acc, __fmul_rn(a.w[slot], r[0]));
+    }
+    if (lane == 0) a.out[(int64_t)t * a.d + j] = acc;
+}
+
+template <int KIND>
+static int launch_experts(const MoeArgs& a) {
+    const bool shared = a.sh_g != nullptr;
+    const int jobs = a.N * a.K + (shared ? a.N : 0);
+    const int rows = std::max(a.E, shared ? a.SH : 0);
+    moe_gate_up_kernel<KIND><<<dim3(ceil_div(rows, GEMV_WARPS), jobs), GEMV_THREADS, 0, stream()>>>(a);
+    B200_LAUNCH_CHECK("moe_gate_up_kernel");
+    moe_down_combine_kernel<KIND><<<dim3(ceil_div(a.d, GEMV_WARPS), a.N), GEMV_THREADS, 0, stream()>>>(a);
+    B200_LAUNCH_CHECK("moe_down_combine_kernel");
+    return B200_OK;
+}
+
+int moe_route(const float* x, const float* router_w, const float* router_bias, float* probs,
+              int32_t* idx, float* w, int64_t N, int d, int ne, int K) {
+    // shared memory: x + as many group rows as fit in ~96 KB
+    const int groups = d >> 2;
+    const size_t x_bytes = (size_t)((d + 3) & ~3) * 4;
+    int chunk = (int)std::min<size_t>((size_t)std::max(groups, 1), (96 * 1024 - x_bytes) / ((size_t)(ne + 1) * 4));
+    B200_REQUIRE(chunk >= 1, "moe: hidden size too large for the router kernel");
+    const size_t smem = x_bytes + (size_t)chunk * (ne + 1) * 4;
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        B200_CUDA(cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        configured = 100 * 1024;
+    }
+    moe_route_kernel<<<(unsigned)N, ROUTE_THREADS, smem, stream()>>>(x, router_w, router_bias, probs, idx, w, d, ne,
+                                                                     K, chunk);
+    B200_LAUNCH_CHECK("moe_route_kernel");
+    return B200_OK;
+}
+
+// kind: template tag.  Weight pointers are raw bytes in that kind.
+int moe_forward(const float* x, const float* router_w, const float* router_bias, const void* gates,
+                const void* ups, const void* downs, const void* sh_g, const void* sh_u, const void* sh_d,
+                float* out, float* probs_cache, int32_t* idx_cache, float* w_cache, float* s_gate,
+                float* s_up, float* s_act, int64_t N, int d, int E, int ne, int K, int SH, int kind) {
+    if (N <= 0) return B200_OK;
+    B200_REQUIRE(K >= 1 && K <= MOE_MAX_K, "moe_forward: K must be in [1,%d]", MOE_MAX_K);
+    B200_REQUIRE(ne > 0 && ne <= MOE_MAX_NE && K <= ne, "moe_forward: ne out of range");
+    B200_REQUIRE(d > 0 && E > 0, "moe_forward: bad dims");
+    B200_REQUIRE(x && router_w && gates && ups && downs && out, "moe_forward: null pointer");
+    B200_REQUIRE(d % 32 == 0 && E % 32 == 0, "moe_forward: d and E must be multiples of 32");
+    B200_REQUIRE((reinterpret_cast<uintptr_t>(router_w) & 15) == 0 && d % 4 == 0, "moe_forward: router_w alignment");
+    const bool shared = sh_g && sh_u && sh_d;
+    if (shared) B200_REQUIRE(SH > 0 && SH % 32 == 0, "moe_forward: SH must be a positive multiple of 32");
+    if (kind >= 0 && kind <= 3)
+        B200_REQUIRE(d % q_block_elems(kind) == 0 && E % q_block_elems(kind) == 0 &&
+                         (!shared || SH % q_block_elems(kind) == 0),
+                     "moe_forward: d, E and SH must be multiples of the quantisation block");
+    B200_REQUIRE(N * K < ((int64_t)1 << 31), "moe_forward: N too large");
+
+    // workspace: idx | w | act | sh_act
+    const size_t NK = (size_t)N * K;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
+    const size_t o_idx = take(NK * 4), o_w = take(NK * 4);
+    const size_t o_act = s_act ? 0 : take(NK * E * 4);
+    const size_t o_sh = shared ? take((size_t)N * SH * 4) : 0;
+    void* wsp;
+    int rc = workspace(WS_MOE).ensure(off + 256, &wsp);
+    if (rc) return rc;
+    char* base = static_cast<char*>(wsp);
+    int32_t* idx = idx_cache ? idx_cache : reinterpret_cast<int32_t*>(base + o_idx);
+    float* w = w_cache ? w_cache : reinterpret_cast<float*>(base + o_w);
+
+    rc = moe_route(x, router_w, router_bias, probs_cache, idx, w, N, d, ne, K);
+    if (rc) return rc;
+
+    MoeArgs a;
+    a.x = x;
+    a.gates = static_cast<const uint8_t*>(gates);
+    a.ups = static_cast<const uint8_t*>(ups);
+    a.downs = static_cast<const uint8_t*>(downs);
+    a.sh_g = shared ? static_cast<const uint8_t*>(sh_g) : nullptr;
+    a.sh_u = shared ? static_cast<const uint8_t*>(sh_u) : nullptr;
+    a.sh_d = shared ? static_cast<const uint8_t*>(sh_d) : nullptr;
+    a.idx = idx;
+    a.w = w;
+    a.act = s_act ? s_act : reinterpret_cast<float*>(base + o_act);
+    a.sh_act = shared ? reinterpret_cast<float*>(base + o_sh) : nullptr;
+    a.s_gate = s_gate;
+    a.s_up = s_up;
+    a.out = out;
+    a.N = (int)N; a.d = d; a.E = E; a.ne = ne; a.K = K; a.SH = shared ? SH : 0;
+    // grid.y carries the jobs: walk the tokens in chunks that keep it under 65535
+    const int chunk_tokens = std::max(1, 65535 / (K + 1));
+    for (int64_t t0 = 0; t0 < N; t0 += chunk_tokens) {
+        MoeArgs c = a;
+        c.N = (int)std::min<int64_t>(chunk_tokens, N - t0);
+        c.x = a.x + t0 * d;
+        c.idx = a.idx + t0 * K;
+        c.w = a.w + t0 * K;
+        c.act = a.act + t0 * K * E;
+        if (a.sh_act) c.sh_act = a.sh_act + t0 * SH;
+        if (a.s_gate) c.s_gate = a.s_gate + t0 * K * E;
+        if (a.s_up) c.s_up = a.s_up + t0 * K * E;
+        c.out = a.out + t0 * d;
+        switch (kind) {
+            case 0: rc = launch_experts<0>(c); break;
+            case 1: rc = launch_experts<1>(c); break;
+            case 2: rc = launch_experts<2>(c); break;
+            case 3: rc = launch_experts<3>(c); break;
+            case KIND_F16: rc = launch_experts<KIND_F16>(c); break;
+            default: rc = launch_experts<KIND_F32>(c); break;
+        }
+        if (rc) return rc;
+    }
+    return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_moe_forward(const float* x, const float* router_w, const float* gates, const float* ups,
+                     const float* downs, const float* sh_g, const float* sh_u, const float* sh_d,
+                     float* out, float* probs_cache, int32_t* idx_cache, float* w_cache,
+                     float* s_gate, float* s_up, float* s_act,
+                     int64_t N, int d, int E, int ne, int K, int SH) {
+    return moe_forward(x, router_w, nullptr, gates, ups, downs, sh_g, sh_u, sh_d, out, probs_cache, idx_cache,
+                       w_cache, s_gate, s_up, s_act, N, d, E, ne, K, SH, KIND_F32);
+}
+int b200_moe_forward_bias(const float* x, const float* router_w, const float* router_bias,
+                          const float* gates, const float* ups, const float* downs,
+                          const float* sh_g, const float* sh_u, const float* sh_d,
+                          float* out, float* probs_cache, int32_t* idx_cache, float* w_cache,
+                          float* s_gate, float* s_up, float* s_act,
+                          int64_t N, int d, int E, int ne, int K, int SH) {
+    return moe_forward(x, router_w, router_bias, gates, ups, downs, sh_g, sh_u, sh_d, out, probs_cache, idx_cache,
+                       w_cache, s_gate, s_up, s_act, N, d, E, ne, K, SH, KIND_F32);
+}
+int b200_moe_forward_half(const float* x, const float* router_w, const uint16_t* gates,
+                          const uint16_t* ups, const uint16_t* downs, const uint16_t* sh_g,
+                          const uint16_t* sh_u, const uint16_t* sh_d, float* out,
+                          float* probs_cache, int32_t* idx_cache, float* w_cache,
+                          float* s_gate, float* s_up, float* s_act,
+                          int64_t N, int d, int E, int ne, int K, int SH, int qkind) {
+    B200_REQUIRE(qkind >= -1 && qkind <= 3, "moe_forward_half: unknown qkind %d", qkind);
+    return moe_forward(x, router_w, nullptr, gates, ups, downs, sh_g, sh_u, sh_d, out, probs_cache, idx_cache,
+                       w_cache, s_gate, s_up, s_act, N, d, E, ne, K, SH, tag_of_qkind(qkind));
+}
+int b200_moe_forward_bias_half(const float* x, const float* router_w, const float* router_bias,
+                               const uint16_t* gates, const uint16_t* ups, const uint16_t* downs,
+                               const uint16_t* sh_g, const uint16_t* sh_u, const uint16_t* sh_d,
+                               float* out, float* probs_cache, int32_t* idx_cache, float* w_cache,
+                               float* s_gate, float* s_up, float* s_act,
+                               int64_t N, int d, int E, int ne, int K, int SH, int qkind) {
+    B200_REQUIRE(qkind >= -1 && qkind <= 3, "moe_forward_bias_half: unknown qkind %d", qkind);
+    return moe_forward(x, router_w, router_bias, gates, ups, downs, sh_g, sh_u, sh_d, out, probs_cache, idx_cache,
+                       w_cache, s_gate, s_up, s_act, N, d, E, ne, K, SH, tag_of_qkind(qkind));
+}
+int b200_moe_permutation(const int32_t* idx, int64_t NK, int ne, int32_t* grouped, int32_t* offsets) {
+    return moe_permutation(idx, NK, ne, grouped, offsets);
+}
+
+}  // extern "C"

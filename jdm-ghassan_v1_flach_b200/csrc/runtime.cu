@@ -1,0 +1,175 @@
+// Process-wide state of the library: last error, current stream, cached
+// workspaces, device utilities (the gai::cuda::* functions of the reference,
+// cuda/cuda_utils.cu) and the recorded-only toggles.
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "common.cuh"
+
+namespace b200 {
+
+static thread_local char g_err[512] = "";
+static cudaStream_t g_stream = nullptr;   // legacy default stream, as in the reference
+static Workspace g_ws[WS_COUNT];
+static int g_sms = 0;
+static bool g_fp16_gemm = false, g_bf16_gemm = false;
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_status(cudaError_t e, const char* what) {
+    snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
+    return e == cudaErrorMemoryAllocation ? B200_ENOMEM : B200_ECUDA;
+}
+
+cudaStream_t stream() { return g_stream; }
+
+int num_sms() {
+    if (g_sms == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            g_sms = n;
+        else
+            g_sms = 148;
+    }
+    return g_sms;
+}
+
+int Workspace::ensure(size_t need, void** out) {
+    if (need > bytes) {
+        if (ptr) {
+            B200_CUDA(cudaFree(ptr));
+            ptr = nullptr;
+            bytes = 0;
+        }
+        const size_t mb = (size_t)1 << 20;
+        const size_t rounded = (need + mb - 1) / mb * mb;
+        B200_CUDA(cudaMalloc(&ptr, rounded));
+        bytes = rounded;
+    }
+    *out = ptr;
+    return B200_OK;
+}
+
+void Workspace::release() {
+    if (ptr) cudaFree(ptr);
+    ptr = nullptr;
+    bytes = 0;
+}
+
+Workspace& workspace(int which) { return g_ws[which]; }
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+const char* b200_last_error(void) { return g_err; }
+int b200_version(void) { return 100; }
+
+int b200_device_count(int* count) {
+    B200_REQUIRE(count, "device_count: null pointer");
+    B200_CUDA(cudaGetDeviceCount(count));
+    return B200_OK;
+}
+int b200_malloc_device(void** ptr, size_t nbytes) {
+    B200_REQUIRE(ptr, "malloc_device: null pointer");
+    *ptr = nullptr;
+    if (nbytes == 0) return B200_OK;
+    B200_CUDA(cudaMalloc(ptr, nbytes));
+    return B200_OK;
+}
+int b200_free_device(void* ptr) {
+    if (ptr) B200_CUDA(cudaFree(ptr));
+    return B200_OK;
+}
+int b200_memset_zero(void* ptr, size_t nbytes) {
+    if (!ptr || nbytes == 0) return B200_OK;
+    B200_CUDA(cudaMemsetAsync(ptr, 0, nbytes, stream()));
+    return B200_OK;
+}
+int b200_is_device_memory(const void* ptr, int* yes) {
+    B200_REQUIRE(yes, "is_device_memory: null pointer");
+    cudaPointerAttributes at;
+    const cudaError_t e = cudaPointerGetAttributes(&at, ptr);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        *yes = 0;
+        return B200_OK;
+    }
+    *yes = (at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged) ? 1 : 0;
+    return B200_OK;
+}
+int b200_copy(void* dst, int dst_is_device, const void* src, int src_is_device, size_t nbytes) {
+    if (nbytes == 0) return B200_OK;
+    B200_REQUIRE(dst && src, "copy: null pointer");
+    const cudaMemcpyKind kind = dst_is_device ? (src_is_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice)
+                                              : (src_is_device ? cudaMemcpyDeviceToHost : cudaMemcpyHostToHost);
+    // Ordered on the library's stream, then completed before returning, like the
+    // reference's blocking cudaMemcpy on stream 0.
+    B200_CUDA(cudaMemcpyAsync(dst, src, nbytes, kind, stream()));
+    if (kind != cudaMemcpyDeviceToDevice) B200_CUDA(cudaStreamSynchronize(stream()));
+    return B200_OK;
+}
+int b200_synchronize(void) {
+    B200_CUDA(cudaDeviceSynchronize());
+    return B200_OK;
+}
+int b200_free_bytes_live(size_t* bytes) {
+    B200_REQUIRE(bytes, "free_bytes_live: null pointer");
+    size_t total = 0;
+    B200_CUDA(cudaMemGetInfo(bytes, &total));
+    return B200_OK;
+}
+int b200_set_stream(void* s) {
+    g_stream = static_cast<cudaStream_t>(s);
+    return B200_OK;
+}
+
+int b200_set_fp16_gemm(int on) { g_fp16_gemm = on != 0; return B200_OK; }
+int b200_fp16_gemm_enabled(void) { return g_fp16_gemm ? 1 : 0; }
+int b200_set_bf16_gemm(int on) { g_bf16_gemm = on != 0; return B200_OK; }
+int b200_bf16_gemm_enabled(void) { return g_bf16_gemm ? 1 : 0; }
+int b200_set_moe_jitter(float j) {
+    if (j != 0.0f)
+        return fail(B200_EUNSUPPORTED, "set_moe_jitter: router noise is a training feature; the "
+                                       "inference backend only accepts 0");
+    return B200_OK;
+}
+int b200_set_moe_jitter_seed(uint64_t) { return B200_OK; }
+
+int b200_free_workspace(void) { workspace(WS_LINEAR).release(); workspace(WS_ATTN).release(); return B200_OK; }
+int b200_moe_free_workspace(void) { workspace(WS_MOE).release(); return B200_OK; }
+int b200_mamba_free_workspace(void) { workspace(WS_MAMBA).release(); return B200_OK; }
+int b200_free_sampling_workspace(void) { workspace(WS_SAMPLE).release(); return B200_OK; }
+int b200_free_workspaces(void) {
+    for (int i = 0; i < WS_COUNT; ++i) workspace(i).release();
+    return b200_free_quant_scratch();
+}
+int b200_reserve_workspaces(size_t gemm_bytes, size_t moe_bytes) {
+    void* p;
+    if (gemm_bytes) { int rc = workspace(WS_LINEAR).ensure(gemm_bytes, &p); if (rc) return rc; }
+    if (moe_bytes) { int rc = workspace(WS_MOE).ensure(moe_bytes, &p); if (rc) return rc; }
+    return B200_OK;
+}
+int b200_moe_reserve_workspace(size_t bytes) {
+    void* p;
+    return bytes ? workspace(WS_MOE).ensure(bytes, &p) : B200_OK;
+}
+size_t b200_pool_bytes(void) { return workspace(WS_LINEAR).bytes + workspace(WS_ATTN).bytes + workspace(WS_MAMBA).bytes; }
+size_t b200_moe_pool_bytes(void) { return workspace(WS_MOE).bytes; }
+
+int b200_training_op_unsupported(const char* name) {
+    return fail(B200_EUNSUPPORTED, "%s: training op not provided by the B200 inference backend",
+                name ? name : "?");
+}
+
+}  // extern "C"

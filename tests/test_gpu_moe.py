@@ -1,0 +1,186 @@
+"""GPU parity: MoE routing (bit-exact), expert permutation (bit-exact), layer output."""
+import numpy as np
+import pytest
+import torch
+
+from cases import moe_case
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(c, N, d, E, ne, K, SH, wkind, caches=True, scratch=False):
+    from gpu_util import dev, empty, host, ops
+    out = empty((N, d))
+    probs = empty((N, ne)) if caches else None
+    idx = empty((N, K), torch.int32) if caches else None
+    w = empty((N, K)) if caches else None
+    sg = empty((N, K, E)) if scratch else None
+    su = empty((N, K, E)) if scratch else None
+    sa = empty((N, K, E)) if scratch else None
+    args = [dev(c[k]) for k in ("gates", "ups", "downs", "sh_g", "sh_u", "sh_d")]
+    if wkind == -2:
+        ops.moe_forward_bias(dev(c["x"]), dev(c["router_w"]), dev(c["router_bias"]), *args, out, probs, idx, w,
+                             sg, su, sa, N, d, E, ne, K, SH)
+    else:
+        ops.moe_forward_bias_half(dev(c["x"]), dev(c["router_w"]), dev(c["router_bias"]), *args, out, probs, idx,
+                                  w, sg, su, sa, N, d, E, ne, K, SH, wkind)
+    res = dict(out=host(out))
+    if caches:
+        res.update(probs=host(probs), idx=host(idx), w=host(w))
+    if scratch:
+        res.update(sg=host(sg), su=host(su), sa=host(sa))
+    return res
+
+
+def _ulp_close(a, b, maxulp=4):
+    """Router probabilities / mixture weights.  Logits follow the reference's fp32 chain
+    bit for bit; exp() is evaluated in double and rounded, which differs from the host
+    libm's expf by one ulp for a fraction of a percent of arguments, and the softmax
+    sum can carry that ulp into every probability of the row."""
+    np.testing.assert_array_max_ulp(a, b, maxulp=maxulp)
+
+
+def _oracle(oracle, c, d, E, ne, K, SH, wkind):
+    return oracle.moe_forward(c["x"], c["router_w"], c["router_bias"], c["gates"], c["ups"], c["downs"],
+                              c["sh_g"], c["sh_u"], c["sh_d"], d, E, ne, K, SH, wkind)
+
+
+@pytest.mark.parametrize("wkind", [-2, -1, 0, 1, 2, 3])
+@pytest.mark.parametrize("N", [1, 5, 64])
+def test_layer_small(oracle, wkind, N):
+    from gpu_util import SUM_ORDER
+    d, E, ne, K, SH = 256, 256, 16, 2, 512
+    c = moe_case(oracle, 10 * N + wkind + 3, N, d, E, ne, K, SH, wkind)
+    got = _run(c, N, d, E, ne, K, SH, wkind)
+    out, probs, idx, w = _oracle(oracle, c, d, E, ne, K, SH, wkind)
+    assert np.array_equal(got["idx"], idx)                                # top-k indices bit-exact
+    _ulp_close(got["probs"], probs)
+    _ulp_close(got["w"], w)
+    np.testing.assert_allclose(got["out"], out, **SUM_ORDER)
+
+
+@pytest.mark.parametrize("N", [1, 64, 512])
+def test_layer_config3_shape(oracle, N):
+    """hidden 1536, 64 experts, top-6, ffn 512, shared 1024, Q4_K, skewed router bias."""
+    from gpu_util import SUM_ORDER
+    d, E, ne, K, SH = 1536, 512, 64, 6, 1024
+    c = moe_case(oracle, 300 + N, N, d, E, ne, K, SH, 3)
+    got = _run(c, N, d, E, ne, K, SH, 3)
+    out, probs, idx, w = _oracle(oracle, c, d, E, ne, K, SH, 3)
+    assert np.array_equal(got["idx"], idx)
+    _ulp_close(got["w"], w)
+    np.testing.assert_allclose(got["out"], out, **SUM_ORDER)
+
+
+def test_routing_bit_exact_many_tokens(oracle):
+    """4096 tokens at the config-3 router shape: every top-k index identical, probabilities
+    and weights within a few ulp."""
+    from gpu_util import dev, empty, host, ops
+    d, ne, K = 1536, 64, 6
+    r = np.random.default_rng(42)
+    x = r.standard_normal((4096, d)).astype(np.float32)
+    rw = (r.standard_normal((ne, d)) / np.sqrt(d)).astype(np.float32)
+    bias = (r.standard_normal(ne) * 0.5 / ne).astype(np.float32)
+    probs, idx, w = oracle.moe_route(x, rw, bias, ne, K)
+    # drive the router alone through a layer whose experts are tiny
+    E = 32
+    z = np.zeros((ne * E, d), np.float32)
+    zd = np.zeros((ne * d, E), np.float32)
+    out, dp, di, dw = empty((4096, d)), empty((4096, ne)), empty((4096, K), torch.int32), empty((4096, K))
+    ops.moe_forward_bias(dev(x), dev(rw), dev(bias), dev(z), dev(z), dev(zd), None, None, None, out, dp, di, dw,
+                         None, None, None, 4096, d, E, ne, K, 0)
+    assert np.array_equal(host(di), idx)
+    _ulp_close(host(dp), probs)
+    _ulp_close(host(dw), w)
+    # the logits themselves are bit-identical (same fp32 chain); only exp differs
+    exact = (host(dp).view(np.uint32) == probs.view(np.uint32)).mean()
+    assert exact > 0.98, f"only {exact:.4f} of the probabilities are bit-identical"
+    assert not host(out).any()
+
+
+def test_routing_ties_and_degenerate(oracle):
+    """Identical router rows give exact ties (lowest index wins); huge negative bias and
+    underflowing probabilities exercise the uniform-weight fallback."""
+    from gpu_util import dev, empty, host, ops
+    d, ne, K, E = 64, 8, 3, 32
+    r = np.random.default_rng(9)
+    x = r.standard_normal((6, d)).astype(np.float32)
+    rw = np.tile(r.standard_normal((1, d)).astype(np.float32), (ne, 1))     # all experts tie
+    rw[5] *= 1.5
+    bias = np.zeros(ne, np.float32)
+    x[4] *= 1e4            # softmax saturates: one prob 1, the rest underflow to 0
+    z, zd = np.zeros((ne * E, d), np.float32), np.zeros((ne * d, E), np.float32)
+    for b in (bias, None, np.full(ne, -2e30, np.float32)):
+        probs, idx, w = oracle.moe_route(x, rw, b, ne, K)
+        out, di, dw = empty((6, d)), empty((6, K), torch.int32), empty((6, K))
+        ops.moe_forward_bias(dev(x), dev(rw), dev(b), dev(z), dev(z), dev(zd), None, None, None, out, None, di,
+                             dw, None, None, None, 6, d, E, ne, K, 0)
+        assert np.array_equal(host(di), idx)
+        _ulp_close(host(dw), w)
+
+
+def test_wide_config5_limits(oracle):
+    """72 experts, top-10: beyond the reference's ne <= 64 / K <= 8 arrays."""
+    from gpu_util import SUM_ORDER
+    d, E, ne, K, SH = 256, 256, 72, 10, 256
+    c = moe_case(oracle, 55, 7, d, E, ne, K, SH, 3)
+    got = _run(c, 7, d, E, ne, K, SH, 3)
+    out, probs, idx, w = _oracle(oracle, c, d, E, ne, K, SH, 3)
+    assert np.array_equal(got["idx"], idx)
+    np.testing.assert_allclose(got["out"], out, **SUM_ORDER)
+
+
+def test_no_shared_k1_and_scratch_outputs(oracle):
+    from gpu_util import SUM_ORDER, dev, host
+    d, E, ne, K = 128, 64, 4, 1
+    c = moe_case(oracle, 66, 9, d, E, ne, K, 0, -2)
+    got = _run(c, 9, d, E, ne, K, 0, -2, caches=False, scratch=True)
+    out, probs, idx, w = _oracle(oracle, c, d, E, ne, K, 0, -2)
+    np.testing.assert_allclose(got["out"], out, **SUM_ORDER)
+    # s_gate / s_up / s_act hold the selected experts' pre-activations and activations
+    x = c["x"]
+    for t in range(9):
+        e = idx[t, 0]
+        g = c["gates"].reshape(ne, E, d)[e] @ x[t]
+        u = c["ups"].reshape(ne, E, d)[e] @ x[t]
+        np.testing.assert_allclose(got["sg"][t, 0], g, rtol=1e-4, atol=1e-5)
+        np.testing.assert_allclose(got["su"][t, 0], u, rtol=1e-4, atol=1e-5)
+        np.testing.assert_allclose(got["sa"][t, 0], oracle.swiglu(g, u), rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("NK,ne", [(1, 4), (6, 64), (4096 * 6, 64), (100003, 72), (64 * 4096 * 6, 64)])
+def test_permutation_bit_exact(oracle, NK, ne):
+    """Stable counting sort by expert; the largest case is batch-64 x 4096-token prefill."""
+    from gpu_util import dev, empty, host, ops
+    r = np.random.default_rng(NK % 1000 + ne)
+    p = r.dirichlet(np.full(ne, 0.3))                 # skewed loads, some experts (nearly) empty
+    idx = r.choice(ne, size=NK, p=p).astype(np.int32)
+    grouped, offsets = empty(NK, torch.int32), empty(ne + 1, torch.int32)
+    ops.moe_permutation(dev(idx), NK, ne, grouped, offsets)
+    g, o = host(grouped), host(offsets)
+    if NK <= 200000:
+        wg, wo = oracle.moe_permutation(idx, ne)
+        assert np.array_equal(o, wo) and np.array_equal(g, wg)
+    # size-independent properties
+    assert o[0] == 0 and o[-1] == NK and np.array_equal(np.diff(o), np.bincount(idx, minlength=ne))
+    assert np.array_equal(np.sort(g), np.arange(NK))
+    ge = idx[g]
+    assert (np.diff(ge) >= 0).all()
+    same = np.diff(ge) == 0
+    assert (np.diff(g)[same] > 0).all()               # ascending slot id inside an expert
+
+
+def test_argument_errors(oracle):
+    from gpu_util import B200Error, empty, ops
+    t = empty(1 << 16)
+    with pytest.raises(B200Error, match="K must be in"):
+        ops.moe_forward_bias(t, t, None, t, t, t, None, None, None, t, None, None, None, None, None, None,
+                             1, 64, 32, 8, 0, 0)
+    with pytest.raises(B200Error, match="ne out of range"):
+        ops.moe_forward_bias(t, t, None, t, t, t, None, None, None, t, None, None, None, None, None, None,
+                             1, 64, 32, 300, 2, 0)
+    with pytest.raises(B200Error, match="unknown qkind"):
+        ops.moe_forward_bias_half(t, t, None, t, t, t, None, None, None, t, None, None, None, None, None, None,
+                                  1, 64, 32, 8, 2, 0, 5)
+    ops.moe_forward_bias(t, t, None, t, t, t, None, None, None, t, None, None, None, None, None, None,
+                         0, 64, 32, 8, 2, 0)          # N == 0 returns silently
