@@ -1,0 +1,498 @@
+#!/usr/bin/env python
+"""Decode-throughput benchmark of the quantized hybrid-layer forward step.
+
+Workload (N = 1): the Granite-4.0-H-Tiny-shaped model - hidden 1536, vocab 100352,
+40 layers (36 Mamba-2: 48 heads x 64, d_state 128, conv 4; 4 GQA at layers
+9/19/29/39: 12 q / 4 kv heads, head_dim 128, no RoPE), MoE with 64 experts, top-6,
+expert ffn 512, shared expert 1024 - with random-init N(0, 0.02) weights quantised
+to Q4_K on the device, batch 1, greedy decode after a `--ctx`-token prompt.
+One step = one decoded token per sequence.
+
+    value         tok/s with the token ids resident on the device (the step is one
+                  CUDA graph; CUDA events on the launching stream)
+    e2e           tok/s through b200_decoder_step_host: host token id in, host
+                  arg-max out, a stream synchronise per token
+    roofline      achieved HBM GB/s of the whole step and of its dominant kernel
+                  against the measured copy bandwidth
+    cpu_baseline  the reference engine's CPU ops (oracle/_ref) or the oracle port on
+                  this box's host cores, on a bounded sample of the same token
+
+`--impl reference` prints the CPU arm alone.  Under torchrun (N > 1) every rank runs
+an independent replica of the model (only the MoE layer shards in this workload and
+expert parallelism is a separate mode), value is the sum over ranks.
+"""
+import argparse
+import ctypes as C
+import importlib
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+PKG = "jdm-ghassan_v1_flach_b200"
+
+H_TINY = dict(vocab=100352, hidden=1536, n_layers=40,
+              layer_types=[1 if l in (9, 19, 29, 39) else 0 for l in range(40)],
+              n_heads=12, n_kv=4, head_dim=128, rope_type=-1, rope_theta=1e4,
+              mamba_heads=48, mamba_d_head=64, mamba_d_state=128, mamba_d_conv=4,
+              n_experts=64, top_k=6, expert_dim=512, shared_dim=1024, qkind=3,
+              rms_eps=1e-5, embedding_multiplier=12.0, residual_multiplier=0.22,
+              attn_scale=0.0078125, logits_scaling=6.0)
+
+T_IDS = dict(embed=0, final_norm=1, lm_head=2, inv_freq=3, attn_norm=10, ffn_norm=11,
+             w_in=20, conv_w=21, conv_b=22, dt_bias=23, a_log=24, D=25, norm_w=26, w_out=27,
+             wq=30, wk=31, wv=32, wo=33, router=40, router_bias=41, gate=42, up=43, down=44,
+             sh_gate=45, sh_up=46, sh_down=47)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# model construction on the device
+# ---------------------------------------------------------------------------
+class DeviceModel:
+    """Random-init weights generated and quantised on the GPU, bound to a b200_decoder."""
+
+    def __init__(self, cfg, batch, max_ctx, seed=0, kv_page=64):
+        import torch
+        self.torch = torch
+        self.lib = importlib.import_module(PKG).lib()
+        self.cfg, self.batch = cfg, batch
+        self.gen = torch.Generator(device="cuda").manual_seed(seed)
+        self.tensors = {}
+        c = cfg
+        self.handle = C.c_void_p()
+        types = np.array(c["layer_types"], np.int32)
+        self.lib.b200_decoder_create(C.byref(self.handle), batch, c["vocab"], c["hidden"], c["n_layers"],
+                                     types.ctypes.data, c["n_heads"], c["n_kv"], c["head_dim"], c["rope_type"],
+                                     c["mamba_heads"], c["mamba_d_head"], c["mamba_d_state"], c["mamba_d_conv"],
+                                     c["n_experts"], c["top_k"], c["expert_dim"], c["shared_dim"], max_ctx, kv_page,
+                                     c["qkind"], c["rms_eps"], c["embedding_multiplier"], c["residual_multiplier"],
+                                     c["attn_scale"], c["logits_scaling"])
+        d, q = c["hidden"], c["qkind"]
+        hd = c["head_dim"]
+        qd, kvd = c["n_heads"] * hd, c["n_kv"] * hd
+        ne, E, SH = c["n_experts"], c["expert_dim"], c["shared_dim"]
+        d_inner = c["mamba_heads"] * c["mamba_d_head"]
+        conv_dim = d_inner + 2 * c["mamba_d_state"]
+        proj = d_inner + conv_dim + c["mamba_heads"]
+        emb = (self.randn(c["vocab"] * d) * 0.02).half()
+        self.put(-1, "embed", emb)
+        self.lib.b200_decoder_set_tensor(self.handle, -1, T_IDS["lm_head"], emb)     # tied
+        self.put(-1, "final_norm", 1 + 0.1 * self.randn(d))
+        if c["rope_type"] >= 0:
+            inv = 1.0 / c["rope_theta"] ** (torch.arange(hd // 2, device="cuda") * 2.0 / hd)
+            self.put(-1, "inv_freq", inv.float())
+        for l, t in enumerate(c["layer_types"]):
+            self.put(l, "attn_norm", 1 + 0.1 * self.randn(d))
+            self.put(l, "ffn_norm", 1 + 0.1 * self.randn(d))
+            if t == 0:
+                nh = c["mamba_heads"]
+                self.put(l, "w_in", self.packed(proj * d))
+                self.put(l, "conv_w", self.randn(conv_dim * c["mamba_d_conv"]) * 0.1)
+                self.put(l, "conv_b", self.randn(conv_dim) * 0.1)
+                u = torch.rand(nh, device="cuda", generator=self.gen) * (1e-1 - 1e-3) + 1e-3
+                self.put(l, "dt_bias", torch.log(torch.expm1(u)))
+                a = torch.rand(nh, device="cuda", generator=self.gen) * np.log(16.0)
+                self.put(l, "a_log", a)
+                self.put(l, "D", self.randn(nh))
+                self.put(l, "norm_w", 1 + 0.1 * self.randn(d_inner))
+                self.put(l, "w_out", self.packed(d * d_inner))
+            else:
+                self.put(l, "wq", self.packed(qd * d))
+                self.put(l, "wk", self.packed(kvd * d))
+                self.put(l, "wv", self.packed(kvd * d))
+                self.put(l, "wo", self.packed(d * qd))
+            self.put(l, "router", self.randn(ne * d) / np.sqrt(d))
+            self.put(l, "router_bias", self.randn(ne) * 0.5 / ne)
+            self.put(l, "gate", self.packed(ne * E * d))
+            self.put(l, "up", self.packed(ne * E * d))
+            self.put(l, "down", self.packed(ne * d * E))
+            self.put(l, "sh_gate", self.packed(SH * d))
+            self.put(l, "sh_up", self.packed(SH * d))
+            self.put(l, "sh_down", self.packed(d * SH))
+        torch.cuda.synchronize()
+
+    def randn(self, n):
+        return self.torch.randn(n, device="cuda", generator=self.gen, dtype=self.torch.float32)
+
+    def packed(self, n, std=0.02):
+        """N(0, std) weights in the model's storage: packed blocks, or fp16 when qkind is -1."""
+        torch = self.torch
+        q = self.cfg["qkind"]
+        w = self.randn(n) * std
+        if q < 0:
+            return w.half()
+        be, bb = (256, 144) if q == 3 else (32, {0: 18, 1: 20, 2: 34}[q])
+        out = torch.empty(n // be * bb, dtype=torch.uint8, device="cuda")
+        self.lib.b200_quantize(w, out, n, q)
+        return out
+
+    def put(self, layer, name, t):
+        t = t.contiguous()
+        self.tensors[(layer, name)] = t
+        self.lib.b200_decoder_set_tensor(self.handle, layer, T_IDS[name], t)
+
+    def configure(self, fused, graph):
+        self.lib.b200_decoder_configure(self.handle, int(fused), int(graph))
+
+    def step_dev(self, tok_dev):
+        self.lib.b200_decoder_step(self.handle, tok_dev, tok_dev)       # in place: next token feeds the next step
+
+    def step_host(self, tok_np, out_np):
+        self.lib.b200_decoder_step_host(self.handle, tok_np.ctypes.data, out_np.ctypes.data)
+
+    def step_bytes(self):
+        b = C.c_double()
+        self.lib.b200_decoder_step_bytes(self.handle, C.byref(b))
+        return b.value
+
+    def launches(self):
+        n = C.c_int()
+        self.lib.b200_decoder_launches_per_step(self.handle, C.byref(n))
+        return n.value
+
+    def close(self):
+        self.lib.b200_decoder_destroy(self.handle)
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi samples of this rank's GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        res = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.proc:
+            return res
+        self.proc.terminate()          # the exact child started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [s.strip() for s in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx.append(float(parts[1]))
+                except ValueError:
+                    continue
+                for nm, v in zip(names, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nm)
+        os.unlink(self.path)
+        if sm:
+            res = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        return res
+
+
+# ---------------------------------------------------------------------------
+# CPU arm
+# ---------------------------------------------------------------------------
+def cpu_decode_token_seconds(cfg, ctx, reps=1, seed=0):
+    """Seconds per decoded token of the CPU path, from a bounded sample: one Mamba-2
+    layer, one attention layer, one MoE layer and the lm_head of a single token are
+    timed and scaled by the layer counts.  Uses the reference engine's own CPU ops
+    (oracle/_ref) on fp16-materialised weights - what its CPU inference path feeds them
+    after ops::quant_materialize - when that library exists, else the oracle port."""
+    from oracle_lib import OracleOnly, Ref
+    ora = OracleOnly()
+    use_ref = Ref.available()
+    cpu = Ref() if use_ref else ora
+    r = np.random.default_rng(seed)
+    d = cfg["hidden"]
+    q = cfg["qkind"] if cfg["qkind"] >= 0 else 3
+    wkind = -1 if use_ref else q
+
+    def weight(rows, cols):
+        w = (r.standard_normal(rows * cols) * 0.02).astype(np.float32)
+        packed = ora.quantize(w, q)
+        return ora.dequantize(packed, rows * cols, q) if use_ref else packed     # fp16 bits or packed
+
+    x = r.standard_normal((1, d)).astype(np.float32)
+    times = {}
+    # Mamba-2 layer, one token
+    nh, dh, ds, k = cfg["mamba_heads"], cfg["mamba_d_head"], cfg["mamba_d_state"], cfg["mamba_d_conv"]
+    d_inner = nh * dh
+    conv_dim = d_inner + 2 * ds
+    proj = d_inner + conv_dim + nh
+    margs = (x.reshape(1, 1, d), weight(proj, d), (r.standard_normal((conv_dim, k)) * 0.1).astype(np.float32),
+             np.zeros(conv_dim, np.float32), np.zeros(nh, np.float32), np.zeros(nh, np.float32),
+             np.ones(nh, np.float32), np.ones(d_inner, np.float32), weight(d, d_inner),
+             np.zeros((1, nh, dh, ds), np.float32), 1, 1, d, d_inner, conv_dim, nh, dh, ds, k, 1e-5)
+
+    def best(fn):
+        out = []
+        for _ in range(max(1, reps)):
+            t = time.perf_counter()
+            fn()
+            out.append(time.perf_counter() - t)
+        return min(out)
+
+    times["mamba"] = best(lambda: cpu.mamba2_forward(*margs, wkind))
+    # attention layer: 4 projections + decode attention over ctx cached tokens
+    H, KV, hd = cfg["n_heads"], cfg["n_kv"], cfg["head_dim"]
+    wq, wk, wv, wo = weight(H * hd, d), weight(KV * hd, d), weight(KV * hd, d), weight(d, H * hd)
+    kc = r.integers(0, 0x3C00, (ctx, KV * hd)).astype(np.uint16)
+    vc = r.integers(0, 0x3C00, (ctx, KV * hd)).astype(np.uint16)
+
+    def attn_layer():
+        qv = cpu.linear(x, wq, wkind, 1, d, H * hd)
+        cpu.linear(x, wk, wkind, 1, d, KV * hd)
+        cpu.linear(x, wv, wkind, 1, d, KV * hd)
+        a = cpu.attention_decode_ring(qv.reshape(H, hd), kc, vc, 1, H, KV, hd, 0, 0, ctx, ctx, 0.1, 0)
+        cpu.linear(a.reshape(1, -1), wo, wkind, 1, H * hd, d)
+
+    times["attention"] = best(attn_layer)
+    # MoE layer
+    ne, E, K, SH = cfg["n_experts"], cfg["expert_dim"], cfg["top_k"], cfg["shared_dim"]
+    moe = (x, (r.standard_normal((ne, d)) / np.sqrt(d)).astype(np.float32),
+           (r.standard_normal(ne) * 0.5 / ne).astype(np.float32), weight(ne * E, d), weight(ne * E, d),
+           weight(ne * d, E), weight(SH, d), weight(SH, d), weight(d, SH), d, E, ne, K, SH, wkind)
+    times["moe"] = best(lambda: cpu.moe_forward(*moe))
+    # lm_head (fp16) on a slice of the vocabulary, scaled
+    vs = min(cfg["vocab"], 16384)
+    head = r.integers(0, 0x3000, (vs, d)).astype(np.uint16)
+    times["lm_head"] = best(lambda: cpu.linear(x, head, -1, 1, d, vs)) * cfg["vocab"] / vs
+    n_mamba = sum(1 for t_ in cfg["layer_types"] if t_ == 0)
+    n_attn = cfg["n_layers"] - n_mamba
+    total = n_mamba * times["mamba"] + n_attn * times["attention"] + cfg["n_layers"] * times["moe"] + times["lm_head"]
+    info = {"kind": "reference" if use_ref else "port", "cores": cpu.num_threads(),
+            "sample": ("1 Mamba-2 layer + 1 attention layer (ctx %d) + 1 MoE layer + lm_head of one decode token, "
+                       "each timed %d time(s) (best kept) and scaled by the layer counts; %s" %
+                       (ctx, max(1, reps), "reference CPU ops on fp16-materialised Q4_K values" if use_ref
+                        else "oracle port on packed Q4_K")),
+            "seconds": {k_: round(v, 4) for k_, v in times.items()}}
+    return total, info
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    cfg = H_TINY
+    # every "step" is the same bounded sample; repeat it at most three times
+    secs, info = cpu_decode_token_seconds(cfg, args.ctx, reps=min(max(1, args.steps), 3))
+    val = args.batch / secs
+    line = {"impl": "reference", "metric": "decode tok/s", "value": val, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(cfg, args),
+            "cpu_baseline": dict(info, value=val, unit="tok/s"),
+            "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(cfg, args):
+    return {"workload": "Granite-4.0-H-Tiny-shaped model, random-init Q4_K, greedy decode, batch %d, ctx %d" %
+                        (args.batch, args.ctx),
+            "batch": args.batch, "ctx": args.ctx, "l2": "inputs larger than L2 (>1 GB of weights and state per step)",
+            "parallelism": "replicas" if args.gpus > 1 else "single"}
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def time_kernel_gbs(fn, bytes_per_launch, iters=20):
+    """Average duration of one launch with CUDA events on the default stream."""
+    import torch
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    return bytes_per_launch / (ms * 1e-3) / 1e9, ms
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--ctx", type=int, default=4096, help="tokens in the KV cache / state before the timed steps")
+    ap.add_argument("--fused", type=int, default=0)
+    ap.add_argument("--graph", type=int, default=1)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--small", action="store_true", help="4-layer model (development only; not a bench number)")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    cfg = dict(H_TINY)
+    if args.small:
+        cfg.update(n_layers=4, layer_types=[0, 1, 0, 0], vocab=8192)
+    B = args.batch
+    W = max(3, args.warmup)
+    total_ctx = args.ctx + W + 2 * args.steps + 8
+    model = DeviceModel(cfg, B, total_ctx, seed=rank)
+    lib = model.lib
+    model.configure(args.fused, args.graph)
+
+    # prompt: ctx uniform token ids per sequence, fed through the decoder one token at a time
+    g = torch.Generator(device="cuda").manual_seed(1 + rank)
+    prompt = torch.randint(0, cfg["vocab"], (args.ctx, B), device="cuda", generator=g, dtype=torch.int32)
+    tok = torch.empty(B, dtype=torch.int32, device="cuda")
+    for t in range(args.ctx):
+        tok.copy_(prompt[t])
+        model.step_dev(tok)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing -------------------------------------------------
+    for _ in range(W):
+        model.step_dev(tok)
+    barrier()
+    launches_before = lib.b200_kernel_launches()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        model.step_dev(tok)
+    e1.record()
+    barrier()
+    ms_dev = e0.elapsed_time(e1)
+    step_bytes = model.step_bytes()
+    launches_per_step = model.launches()
+
+    # ---- end to end through host buffers -----------------------------------------
+    tok_h = tok.cpu().numpy().copy()
+    out_h = np.empty(B, np.int32)
+    for _ in range(3):
+        model.step_host(tok_h, out_h)
+        tok_h[:] = out_h
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        model.step_host(tok_h, out_h)
+        tok_h[:] = out_h
+    torch.cuda.synchronize()
+    sec_e2e = time.perf_counter() - t0
+    clocks = sampler.stop()
+
+    times = torch.tensor([ms_dev, sec_e2e * 1e3], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_dev, ms_e2e = float(times[0]), float(times[1])
+
+    # ---- dominant kernel: the lm_head GEMV (fp16 [vocab, hidden], the largest single read)
+    peak, peak_src = peaks()
+    V, d = cfg["vocab"], cfg["hidden"]
+    xb = torch.randn(B, d, device="cuda")
+    logits = torch.empty(B, V, device="cuda")
+    head = model.tensors[(-1, "embed")]
+    head_bytes = V * d * 2
+    head_gbs, head_ms = time_kernel_gbs(lambda: lib.b200_linear_forward_fp16(xb, head, logits, B, d, V), head_bytes)
+    # and the Q4_K projection kernel on one layer's in_proj (alternating layers so L2 holds nothing)
+    mamba_layers = [l for l, t in enumerate(cfg["layer_types"]) if t == 0]
+    proj_n = 2 * cfg["mamba_heads"] * cfg["mamba_d_head"] + 2 * cfg["mamba_d_state"] + cfg["mamba_heads"]
+    yproj = torch.empty(B, proj_n, device="cuda")
+    state = {"i": 0}
+
+    def q4k_call():
+        l = mamba_layers[state["i"] % len(mamba_layers)]
+        state["i"] += 1
+        lib.b200_linear_forward_q4(xb, model.tensors[(l, "w_in")], yproj, B, d, proj_n, cfg["qkind"])
+
+    q4k_bytes = proj_n * d // 256 * 144
+    q4k_gbs, q4k_ms = time_kernel_gbs(q4k_call, q4k_bytes, iters=len(mamba_layers) * 2)
+
+    if rank == 0:
+        tok_s = B * args.steps * world / (ms_dev * 1e-3)
+        e2e_tok_s = B * args.steps * world / (ms_e2e * 1e-3)
+        step_gbs = step_bytes / (ms_dev / args.steps * 1e-3) / 1e9
+        line = {
+            "metric": "decode tok/s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": W, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(cfg, args),
+            "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": head_gbs, "peak": peak, "unit": "GB/s",
+                         "frac": head_gbs / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "gemv_kernel<fp16> (lm_head [%d,%d])" % (V, d), "ms_per_launch": head_ms,
+                         "algorithmic_bytes_per_launch": head_bytes},
+            "roofline_q4k_gemv": {"bound": "hbm", "achieved": q4k_gbs, "peak": peak, "unit": "GB/s",
+                                  "frac": q4k_gbs / peak, "kernel": "gemv_kernel<Q4_K> (in_proj [%d,%d])" % (proj_n, d),
+                                  "ms_per_launch": q4k_ms, "algorithmic_bytes_per_launch": q4k_bytes},
+            "roofline_step": {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s",
+                              "frac": step_gbs / peak, "algorithmic_bytes_per_step": step_bytes,
+                              "launches_per_step": launches_per_step, "fused": args.fused, "graph": args.graph},
+        }
+        if not args.no_cpu and world == 1:
+            secs, info = cpu_decode_token_seconds(cfg, args.ctx)
+            line["cpu_baseline"] = dict(info, value=B / secs, unit="tok/s")
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line))
+    model.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

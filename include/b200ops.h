@@ -36,6 +36,8 @@ extern "C" {
 
 const char* b200_last_error(void);
 int b200_version(void);
+/* Kernels this library has enqueued so far in this process (a graph replay is not counted). */
+uint64_t b200_kernel_launches(void);
 
 /* ---- device utilities: gai::cuda::*, cuda/cuda_utils.h:14-33 ------------------ */
 int b200_device_count(int* count);                       /* probe(), :14 */

@@ -1,0 +1,93 @@
+/* b200step - whole-token decode step over the op library.
+ *
+ * The reference engine drives one token through the model with one op call at a
+ * time (Generator::decode_step_logits, inference/generator.cpp:221-443, and
+ * Generator::decode_mamba_layer, :456-617), copies the token id to the device and
+ * the arg-max back per token, and keeps per-sequence state in Generator
+ * (MambaState, generator.h:126-134; KVCache, inference/kv_cache.h:11-138).  A
+ * b200_decoder holds the same state for `batch` independent sequences and
+ * enqueues the same op sequence without any host synchronisation, so the whole
+ * step can be replayed as one CUDA graph.
+ *
+ * Weights stay caller-owned device memory (like the reference's Model tensors):
+ * the decoder only records the pointers given to b200_decoder_set_tensor.
+ */
+#ifndef B200STEP_H
+#define B200STEP_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Tensor ids for b200_decoder_set_tensor.  Layer tensors take the layer index,
+ * model tensors take layer = -1.  Storage follows the reference's policy
+ * (Model::storage_dtype_for, model/model.cpp:959-986): norms, conv, dt_bias,
+ * A_log, D, router and router bias are fp32; embeddings / lm_head fp16; every
+ * other matrix is packed in the decoder's qkind (or fp16 when qkind is -1). */
+enum {
+    B200_T_EMBED = 0,        /* [vocab, hidden] fp16 */
+    B200_T_FINAL_NORM = 1,   /* [hidden] fp32 */
+    B200_T_LM_HEAD = 2,      /* [vocab, hidden] fp16 */
+    B200_T_ROPE_INV_FREQ = 3,/* [head_dim/2] fp32 (only when rope_type >= 0) */
+    B200_T_ATTN_NORM = 10,   /* [hidden] fp32: the norm before the mixer */
+    B200_T_FFN_NORM = 11,    /* [hidden] fp32: the norm before the MoE */
+    B200_T_MAMBA_IN = 20, B200_T_MAMBA_CONV_W = 21, B200_T_MAMBA_CONV_B = 22,
+    B200_T_MAMBA_DT_BIAS = 23, B200_T_MAMBA_A_LOG = 24, B200_T_MAMBA_D = 25,
+    B200_T_MAMBA_NORM = 26, B200_T_MAMBA_OUT = 27,
+    B200_T_WQ = 30, B200_T_WK = 31, B200_T_WV = 32, B200_T_WO = 33,
+    B200_T_ROUTER = 40, B200_T_ROUTER_BIAS = 41, B200_T_MOE_GATE = 42, B200_T_MOE_UP = 43,
+    B200_T_MOE_DOWN = 44, B200_T_SH_GATE = 45, B200_T_SH_UP = 46, B200_T_SH_DOWN = 47
+};
+
+typedef struct b200_decoder b200_decoder;
+
+/* layer_types[n_layers]: 0 = Mamba-2 layer, 1 = attention layer (ModelConfig::
+ * layer_types, model/model.h).  rope_type: -1 none (NoPE), 0 interleaved, 1 neox.
+ * attn_scale <= 0 selects 1/sqrt(head_dim).  max_ctx is the per-sequence KV
+ * capacity (rounded up to whole pages of kv_page tokens). */
+int b200_decoder_create(b200_decoder** out, int batch, int vocab, int hidden, int n_layers,
+                        const int32_t* layer_types_host,
+                        int n_heads, int n_kv_heads, int head_dim, int rope_type,
+                        int mamba_heads, int mamba_d_head, int mamba_d_state, int mamba_d_conv,
+                        int n_experts, int top_k, int expert_dim, int shared_dim,
+                        int max_ctx, int kv_page, int qkind, float rms_eps,
+                        float embedding_multiplier, float residual_multiplier, float attn_scale,
+                        float logits_scaling);
+int b200_decoder_destroy(b200_decoder* dec);
+int b200_decoder_set_tensor(b200_decoder* dec, int layer, int tensor_id, const void* device_ptr);
+/* Zero every sequence's Mamba state, conv window and KV length. */
+int b200_decoder_reset(b200_decoder* dec);
+/* fused = 0: one library op per reference op call, in the reference's order.
+ * fused = 1: cross-op fusions (norm into the following projection's prologue,
+ * residual add into the epilogue).  use_graph = 1 captures the step once and
+ * replays it. */
+int b200_decoder_configure(b200_decoder* dec, int fused, int use_graph);
+/* One token per sequence.  tokens_dev [batch] int32 in; next_dev [batch] int32 out
+ * (greedy arg-max of the logits); both device pointers; no host synchronisation. */
+int b200_decoder_step(b200_decoder* dec, const int32_t* tokens_dev, int32_t* next_dev);
+/* Same through host buffers: H2D of the token ids, the step, D2H of the picks,
+ * then a stream synchronise (what Generator::decode_step + ops::argmax_token do). */
+int b200_decoder_step_host(b200_decoder* dec, const int32_t* tokens_host, int32_t* next_host);
+/* Device pointer to the logits of the last step, [batch, vocab] fp32. */
+int b200_decoder_logits(b200_decoder* dec, const float** logits_dev);
+/* Tokens in each sequence's KV cache / state so far (all sequences advance together). */
+int b200_decoder_position(b200_decoder* dec, int* position);
+/* Kernel launches enqueued by one step in the current configuration. */
+int b200_decoder_launches_per_step(b200_decoder* dec, int* launches);
+/* Algorithmic bytes one step touches: every weight read once (K routed experts +
+ * shared per token), Mamba state read+written, KV read for the current length. */
+int b200_decoder_step_bytes(b200_decoder* dec, double* bytes);
+
+/* ---- quantisers on the device (reference host code: quant::quantize_q8_0 /
+ * q4_0 / q4_1, quantization/quantize.cpp:20-246; kind 3 = Q4_K, this library's own
+ * single-pass quantiser).  n must be a multiple of the block size (32 or 256).
+ * Bit-identical to the CPU functions for finite inputs. */
+int b200_quantize(const float* src, void* dst, int64_t n, int kind);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200STEP_H */

@@ -50,7 +50,7 @@ def parse_header(path):
     text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
     text = re.sub(r"//[^\n]*", " ", text)
     protos = {}
-    for m in re.finditer(r"\b(int|size_t|const\s+char\s*\*)\s*(b200_\w+)\s*\(([^)]*)\)\s*;", text):
+    for m in re.finditer(r"\b(int|size_t|uint64_t|const\s+char\s*\*)\s*(b200_\w+)\s*\(([^)]*)\)\s*;", text):
         ret, name, args = m.group(1), m.group(2), m.group(3)
         args = args.strip()
         if args in ("", "void"):
@@ -89,7 +89,7 @@ class Library:
         for name, (ret, argtypes) in self.protos.items():
             fn = getattr(self.cdll, name)          # AttributeError = symbol not exported
             fn.argtypes = argtypes
-            fn.restype = {"int": C.c_int, "size_t": C.c_size_t}.get(ret, C.c_char_p)
+            fn.restype = {"int": C.c_int, "size_t": C.c_size_t, "uint64_t": C.c_uint64}.get(ret, C.c_char_p)
 
     def last_error(self):
         return self.cdll.b200_last_error().decode(errors="replace")

@@ -17,6 +17,7 @@ namespace b200 {
 int fail(int code, const char* fmt, ...);      // records the message, returns code
 int cuda_status(cudaError_t e, const char* what);
 cudaStream_t stream();
+extern unsigned long long g_kernel_launches;   // kernels enqueued by this library so far
 
 #define B200_REQUIRE(cond, ...)                                 \
     do {                                                        \
@@ -34,6 +35,7 @@ cudaStream_t stream();
     do {                                                                  \
         cudaError_t e__ = cudaGetLastError();                             \
         if (e__ != cudaSuccess) return b200::cuda_status(e__, name);      \
+        ++b200::g_kernel_launches;                                        \
     } while (0)
 
 // ---- workspaces -----------------------------------------------------------

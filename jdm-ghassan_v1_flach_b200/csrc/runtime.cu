@@ -13,6 +13,7 @@ static thread_local char g_err[512] = "";
 static cudaStream_t g_stream = nullptr;   // legacy default stream, as in the reference
 static Workspace g_ws[WS_COUNT];
 static int g_sms = 0;
+unsigned long long g_kernel_launches = 0;
 static bool g_fp16_gemm = false, g_bf16_gemm = false;
 
 int fail(int code, const char* fmt, ...) {
@@ -74,6 +75,7 @@ extern "C" {
 
 const char* b200_last_error(void) { return g_err; }
 int b200_version(void) { return 100; }
+uint64_t b200_kernel_launches(void) { return g_kernel_launches; }
 
 int b200_device_count(int* count) {
     B200_REQUIRE(count, "device_count: null pointer");

@@ -1,0 +1,493 @@
+// Whole-token decode step: the op sequence of Generator::decode_step_logits
+// (inference/generator.cpp:221-443) and Generator::decode_mamba_layer (:456-617)
+// for `batch` independent sequences, with per-sequence state (Mamba conv window and
+// ssm state, paged fp16 KV cache) owned by the decoder, token ids and arg-max
+// picks kept on the device, and no host synchronisation - so one step is a fixed
+// list of kernels that is captured once into a CUDA graph and replayed.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "common.cuh"
+#include "../../include/b200step.h"
+
+namespace b200 {
+
+// pos[b] = len[b]; len[b] += 1 : the position the new token is written at, and the
+// number of cached tokens attention then sees.
+__global__ void step_begin_kernel(int32_t* __restrict__ len, int32_t* __restrict__ pos, int batch) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < batch) { pos[b] = len[b]; len[b] += 1; }
+}
+
+// Store this token's K and V rows as fp16 into each sequence's page
+// (the reference converts into its ring slot: generator.cpp:354-357).
+__global__ void kv_append_kernel(const float* __restrict__ k, const float* __restrict__ v,
+                                 uint16_t* __restrict__ k_pages, uint16_t* __restrict__ v_pages,
+                                 const int32_t* __restrict__ page_table, const int32_t* __restrict__ pos,
+                                 int max_pages, int page, int kvd) {
+    const int b = blockIdx.y;
+    const int p = pos[b];
+    const int64_t row = (int64_t)page_table[(int64_t)b * max_pages + p / page] * page + p % page;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < kvd; c += gridDim.x * blockDim.x) {
+        k_pages[row * kvd + c] = float_to_half_bits(k[(int64_t)b * kvd + c]);
+        v_pages[row * kvd + c] = float_to_half_bits(v[(int64_t)b * kvd + c]);
+    }
+}
+
+// out = a + s * b  (the reference's scale_inplace + add_inplace pair, generator.cpp:262-264)
+__global__ void residual_kernel(float* __restrict__ x, const float* __restrict__ y, float s, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        x[i] = x[i] + y[i] * s;
+}
+
+// Row-wise greedy pick: largest finite logit, ties to the lowest id
+// (core/math_cpu.cpp:709-722).  One block per sequence.
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float* __restrict__ logits, int V,
+                                                           int32_t* __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* row = logits + (int64_t)blockIdx.x * V;
+    float bv = 0.0f;
+    int bi = -1;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = row[i];
+        if (isfinite(v) && (bi < 0 || v > bv)) { bv = v; bi = i; }   // ascending i per thread
+    }
+    auto take = [&](float ov, int oi) {
+        if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) take(__shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) { sv[wid] = bv; si[wid] = bi; }
+    __syncthreads();
+    if (wid == 0) {
+        bv = sv[lane];
+        bi = si[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) take(__shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+        if (lane == 0) {
+            if (bi < 0) {   // nothing finite: the reference's serial fallback
+                bi = 0;
+                for (int i = 1; i < V; ++i) if (row[i] > row[bi]) bi = i;
+            }
+            out[blockIdx.x] = bi;
+        }
+    }
+}
+
+struct LayerW {
+    const float *attn_norm = nullptr, *ffn_norm = nullptr;
+    const void *mamba_in = nullptr, *mamba_out = nullptr;
+    const float *conv_w = nullptr, *conv_b = nullptr, *dt_bias = nullptr, *a_log = nullptr, *D = nullptr, *mamba_norm = nullptr;
+    const void *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr;
+    const float *router = nullptr, *router_bias = nullptr;
+    const void *gate = nullptr, *up = nullptr, *down = nullptr, *sh_gate = nullptr, *sh_up = nullptr, *sh_down = nullptr;
+    // state
+    float *conv_state = nullptr, *ssm_state = nullptr;       // Mamba layers
+    uint16_t *k_pages = nullptr, *v_pages = nullptr;         // attention layers
+};
+
+}  // namespace b200
+
+using namespace b200;
+
+struct b200_decoder {
+    int batch, vocab, d, n_layers;
+    std::vector<int> types;
+    int H, KV, hd, rope_type;
+    int mh, mdh, mds, mk, d_inner, conv_dim;
+    int ne, K, E, SH;
+    int max_ctx, page, max_pages, qkind;
+    float eps, emb_mult, res_mult, attn_scale, logits_scaling;
+    const uint16_t *embed = nullptr, *lm_head = nullptr;
+    const float *final_norm = nullptr, *inv_freq = nullptr;
+    std::vector<LayerW> L;
+    // buffers
+    std::vector<void*> owned;
+    float *x = nullptr, *xb = nullptr, *proj = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *logits = nullptr;
+    int32_t *tok = nullptr, *next = nullptr, *len = nullptr, *pos = nullptr, *page_table = nullptr;
+    int position = 0;
+    int fused = 0, use_graph = 0;
+    cudaGraphExec_t graph = nullptr;
+    const int32_t* graph_tok = nullptr;
+    int32_t* graph_next = nullptr;
+    cudaStream_t own_stream = nullptr;
+    int launches = 0;
+    int32_t *h_tok = nullptr, *h_next = nullptr;   // pinned staging for the host entry point
+};
+
+static int dev_alloc(b200_decoder* dec, void** p, size_t bytes) {
+    B200_CUDA(cudaMalloc(p, bytes ? bytes : 4));
+    B200_CUDA(cudaMemset(*p, 0, bytes ? bytes : 4));
+    dec->owned.push_back(*p);
+    return B200_OK;
+}
+
+static void drop_graph(b200_decoder* dec) {
+    if (dec->graph) cudaGraphExecDestroy(dec->graph);
+    dec->graph = nullptr;
+}
+
+// The op sequence of one token, enqueued on the library's current stream.
+static int enqueue_step(b200_decoder* dec, const int32_t* tokens, int32_t* next) {
+    const int B = dec->batch, d = dec->d;
+    cudaStream_t st = stream();
+    int rc;
+#define STEP(call)              \
+    do {                        \
+        rc = (call);            \
+        if (rc) return rc;      \
+    } while (0)
+    step_begin_kernel<<<ceil_div(B, 128), 128, 0, st>>>(dec->len, dec->pos, B);
+    B200_LAUNCH_CHECK("step_begin_kernel");
+    STEP(b200_embedding_forward_half(tokens, dec->embed, dec->x, B, d, dec->vocab));
+    if (dec->emb_mult != 1.0f) STEP(b200_scale_inplace(dec->x, dec->emb_mult, (int64_t)B * d));
+    const int res_grid = std::min(ceil_div(B * d, 256), num_sms() * 8);
+    for (int l = 0; l < dec->n_layers; ++l) {
+        LayerW& w = dec->L[l];
+        STEP(b200_rmsnorm_forward(dec->x, w.attn_norm, dec->xb, nullptr, B, d, dec->eps));
+        if (dec->types[l] == 0) {
+            STEP(b200_mamba2_step_batched(dec->xb, static_cast<const uint16_t*>(w.mamba_in), w.conv_w, w.conv_b,
+                                          w.dt_bias, w.a_log, w.D, w.mamba_norm,
+                                          static_cast<const uint16_t*>(w.mamba_out), w.conv_state, w.ssm_state,
+                                          dec->proj, B, d, dec->d_inner, dec->conv_dim, dec->mh, dec->mdh, dec->mds,
+                                          dec->mk, dec->eps, dec->qkind));
+        } else {
+            const int qd = dec->H * dec->hd, kvd = dec->KV * dec->hd;
+            if (dec->qkind >= 0) {
+                STEP(b200_linear_forward_q4(dec->xb, static_cast<const uint16_t*>(w.wq), dec->q, B, d, qd, dec->qkind));
+                STEP(b200_linear_forward_q4(dec->xb, static_cast<const uint16_t*>(w.wk), dec->k, B, d, kvd, dec->qkind));
+                STEP(b200_linear_forward_q4(dec->xb, static_cast<const uint16_t*>(w.wv), dec->v, B, d, kvd, dec->qkind));
+            } else {
+                STEP(b200_linear_forward_fp16(dec->xb, static_cast<const uint16_t*>(w.wq), dec->q, B, d, qd));
+                STEP(b200_linear_forward_fp16(dec->xb, static_cast<const uint16_t*>(w.wk), dec->k, B, d, kvd));
+                STEP(b200_linear_forward_fp16(dec->xb, static_cast<const uint16_t*>(w.wv), dec->v, B, d, kvd));
+            }
+            if (dec->rope_type >= 0)
+                STEP(b200_rope_forward_cached(dec->q, dec->k, dec->pos, dec->inv_freq, B, dec->H, dec->KV, dec->hd,
+                                              dec->rope_type));
+            kv_append_kernel<<<dim3(ceil_div(kvd, 256), B), 256, 0, st>>>(dec->k, dec->v, w.k_pages, w.v_pages,
+                                                                         dec->page_table, dec->pos, dec->max_pages,
+                                                                         dec->page, kvd);
+            B200_LAUNCH_CHECK("kv_append_kernel");
+            STEP(b200_attention_decode_paged_fp16(dec->q, w.k_pages, w.v_pages, dec->page_table, dec->len, dec->attn,
+                                                  B, dec->max_pages, dec->page, dec->H, dec->KV, dec->hd,
+                                                  dec->attn_scale));
+            if (dec->qkind >= 0)
+                STEP(b200_linear_forward_q4(dec->attn, static_cast<const uint16_t*>(w.wo), dec->proj, B, qd, d, dec->qkind));
+            else
+                STEP(b200_linear_forward_fp16(dec->attn, static_cast<const uint16_t*>(w.wo), dec->proj, B, qd, d));
+        }
+        residual_kernel<<<res_grid, 256, 0, st>>>(dec->x, dec->proj, dec->res_mult, (int64_t)B * d);
+        B200_LAUNCH_CHECK("residual_kernel");
+        STEP(b200_rmsnorm_forward(dec->x, w.ffn_norm, dec->xb, nullptr, B, d, dec->eps));
+        STEP(b200_moe_forward_bias_half(dec->xb, w.router, w.router_bias, static_cast<const uint16_t*>(w.gate),
+                                        static_cast<const uint16_t*>(w.up), static_cast<const uint16_t*>(w.down),
+                                        static_cast<const uint16_t*>(w.sh_gate), static_cast<const uint16_t*>(w.sh_up),
+                                        static_cast<const uint16_t*>(w.sh_down), dec->proj, nullptr, nullptr, nullptr,
+                                        nullptr, nullptr, nullptr, B, d, dec->E, dec->ne, dec->K, dec->SH, dec->qkind));
+        residual_kernel<<<res_grid, 256, 0, st>>>(dec->x, dec->proj, dec->res_mult, (int64_t)B * d);
+        B200_LAUNCH_CHECK("residual_kernel");
+    }
+    STEP(b200_rmsnorm_forward(dec->x, dec->final_norm, dec->xb, nullptr, B, d, dec->eps));
+    STEP(b200_linear_forward_fp16(dec->xb, dec->lm_head, dec->logits, B, d, dec->vocab));
+    if (dec->logits_scaling != 1.0f)
+        STEP(b200_scale_inplace(dec->logits, 1.0f / dec->logits_scaling, (int64_t)B * dec->vocab));
+    argmax_rows_kernel<<<B, 1024, 0, st>>>(dec->logits, dec->vocab, next);
+    B200_LAUNCH_CHECK("argmax_rows_kernel");
+#undef STEP
+    return B200_OK;
+}
+
+static int check_ready(const b200_decoder* dec) {
+    B200_REQUIRE(dec, "decoder: null handle");
+    B200_REQUIRE(dec->embed && dec->lm_head && dec->final_norm, "decoder: embeddings / lm_head / final norm not set");
+    B200_REQUIRE(dec->rope_type < 0 || dec->inv_freq, "decoder: RoPE frequency table not set");
+    for (int l = 0; l < dec->n_layers; ++l) {
+        const LayerW& w = dec->L[l];
+        B200_REQUIRE(w.attn_norm && w.ffn_norm && w.router && w.gate && w.up && w.down, "decoder: layer %d: norm or MoE tensors not set", l);
+        if (dec->types[l] == 0)
+            B200_REQUIRE(w.mamba_in && w.mamba_out && w.conv_w && w.dt_bias && w.a_log && w.D && w.mamba_norm,
+                         "decoder: layer %d: Mamba tensors not set", l);
+        else
+            B200_REQUIRE(w.wq && w.wk && w.wv && w.wo, "decoder: layer %d: attention tensors not set", l);
+    }
+    return B200_OK;
+}
+
+extern "C" {
+
+int b200_decoder_create(b200_decoder** out, int batch, int vocab, int hidden, int n_layers,
+                        const int32_t* layer_types_host, int n_heads, int n_kv_heads, int head_dim, int rope_type,
+                        int mamba_heads, int mamba_d_head, int mamba_d_state, int mamba_d_conv, int n_experts,
+                        int top_k, int expert_dim, int shared_dim, int max_ctx, int kv_page, int qkind,
+                        float rms_eps, float embedding_multiplier, float residual_multiplier, float attn_scale,
+                        float logits_scaling) {
+    B200_REQUIRE(out && layer_types_host, "decoder_create: null pointer");
+    B200_REQUIRE(batch > 0 && vocab > 0 && hidden > 0 && n_layers > 0, "decoder_create: bad model dims");
+    B200_REQUIRE(qkind >= -1 && qkind <= 3, "decoder_create: unknown qkind %d", qkind);
+    B200_REQUIRE(max_ctx > 0 && kv_page > 0, "decoder_create: bad KV geometry");
+    B200_REQUIRE(logits_scaling != 0.0f, "decoder_create: logits_scaling must be non-zero");
+    b200_decoder* dec = new b200_decoder();
+    dec->batch = batch; dec->vocab = vocab; dec->d = hidden; dec->n_layers = n_layers;
+    dec->types.assign(layer_types_host, layer_types_host + n_layers);
+    dec->H = n_heads; dec->KV = n_kv_heads; dec->hd = head_dim; dec->rope_type = rope_type;
+    dec->mh = mamba_heads; dec->mdh = mamba_d_head; dec->mds = mamba_d_state; dec->mk = mamba_d_conv;
+    dec->d_inner = mamba_heads * mamba_d_head;
+    dec->conv_dim = dec->d_inner + 2 * mamba_d_state;
+    dec->ne = n_experts; dec->K = top_k; dec->E = expert_dim; dec->SH = shared_dim;
+    dec->page = kv_page;
+    dec->max_pages = ceil_div(max_ctx, kv_page);
+    dec->max_ctx = dec->max_pages * kv_page;
+    dec->qkind = qkind;
+    dec->eps = rms_eps; dec->emb_mult = embedding_multiplier; dec->res_mult = residual_multiplier;
+    dec->attn_scale = attn_scale > 0.0f ? attn_scale : 1.0f / sqrtf((float)head_dim);
+    dec->logits_scaling = logits_scaling;
+    dec->L.resize(n_layers);
+    *out = dec;
+    const int B = batch, d = hidden, qd = n_heads * head_dim, kvd = n_kv_heads * head_dim;
+    int rc = 0;
+    auto A = [&](void** p, size_t bytes) { if (!rc) rc = dev_alloc(dec, p, bytes); };
+    A((void**)&dec->x, (size_t)B * d * 4);
+    A((void**)&dec->xb, (size_t)B * d * 4);
+    A((void**)&dec->proj, (size_t)B * d * 4);
+    A((void**)&dec->q, (size_t)B * std::max(qd, 1) * 4);
+    A((void**)&dec->k, (size_t)B * std::max(kvd, 1) * 4);
+    A((void**)&dec->v, (size_t)B * std::max(kvd, 1) * 4);
+    A((void**)&dec->attn, (size_t)B * std::max(qd, 1) * 4);
+    A((void**)&dec->logits, (size_t)B * vocab * 4);
+    A((void**)&dec->tok, (size_t)B * 4);
+    A((void**)&dec->next, (size_t)B * 4);
+    A((void**)&dec->len, (size_t)B * 4);
+    A((void**)&dec->pos, (size_t)B * 4);
+    A((void**)&dec->page_table, (size_t)B * dec->max_pages * 4);
+    for (int l = 0; l < n_layers && !rc; ++l) {
+        LayerW& w = dec->L[l];
+        if (dec->types[l] == 0) {
+            A((void**)&w.conv_state, (size_t)B * dec->conv_dim * std::max(dec->mk - 1, 1) * 4);
+            A((void**)&w.ssm_state, (size_t)B * dec->d_inner * dec->mds * 4);
+        } else {
+            const size_t bytes = (size_t)B * dec->max_pages * kv_page * kvd * 2;
+            A((void**)&w.k_pages, bytes);
+            A((void**)&w.v_pages, bytes);
+        }
+    }
+    if (!rc) {
+        // sequence b owns pages [b*max_pages, (b+1)*max_pages): identity page table
+        std::vector<int32_t> pt((size_t)B * dec->max_pages);
+        for (size_t i = 0; i < pt.size(); ++i) pt[i] = (int32_t)i;
+        cudaError_t e = cudaMemcpy(dec->page_table, pt.data(), pt.size() * 4, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) rc = cuda_status(e, "decoder_create: page table upload");
+    }
+    if (!rc) {
+        cudaError_t e = cudaMallocHost((void**)&dec->h_tok, (size_t)B * 4);
+        if (e == cudaSuccess) e = cudaMallocHost((void**)&dec->h_next, (size_t)B * 4);
+        if (e != cudaSuccess) rc = cuda_status(e, "decoder_create: pinned staging");
+    }
+    if (rc) {
+        b200_decoder_destroy(dec);
+        *out = nullptr;
+    }
+    return rc;
+}
+
+int b200_decoder_destroy(b200_decoder* dec) {
+    if (!dec) return B200_OK;
+    drop_graph(dec);
+    if (dec->own_stream) cudaStreamDestroy(dec->own_stream);
+    for (void* p : dec->owned) cudaFree(p);
+    if (dec->h_tok) cudaFreeHost(dec->h_tok);
+    if (dec->h_next) cudaFreeHost(dec->h_next);
+    delete dec;
+    return B200_OK;
+}
+
+int b200_decoder_set_tensor(b200_decoder* dec, int layer, int id, const void* p) {
+    B200_REQUIRE(dec, "decoder_set_tensor: null handle");
+    drop_graph(dec);
+    if (layer < 0) {
+        switch (id) {
+            case B200_T_EMBED: dec->embed = static_cast<const uint16_t*>(p); return B200_OK;
+            case B200_T_FINAL_NORM: dec->final_norm = static_cast<const float*>(p); return B200_OK;
+            case B200_T_LM_HEAD: dec->lm_head = static_cast<const uint16_t*>(p); return B200_OK;
+            case B200_T_ROPE_INV_FREQ: dec->inv_freq = static_cast<const float*>(p); return B200_OK;
+            default: return fail(B200_EINVAL, "decoder_set_tensor: %d is not a model-level tensor", id);
+        }
+    }
+    B200_REQUIRE(layer < dec->n_layers, "decoder_set_tensor: layer %d out of range", layer);
+    LayerW& w = dec->L[layer];
+    const float* f = static_cast<const float*>(p);
+    switch (id) {
+        case B200_T_ATTN_NORM: w.attn_norm = f; break;
+        case B200_T_FFN_NORM: w.ffn_norm = f; break;
+        case B200_T_MAMBA_IN: w.mamba_in = p; break;
+        case B200_T_MAMBA_CONV_W: w.conv_w = f; break;
+        case B200_T_MAMBA_CONV_B: w.conv_b = f; break;
+        case B200_T_MAMBA_DT_BIAS: w.dt_bias = f; break;
+        case B200_T_MAMBA_A_LOG: w.a_log = f; break;
+        case B200_T_MAMBA_D: w.D = f; break;
+        case B200_T_MAMBA_NORM: w.mamba_norm = f; break;
+        case B200_T_MAMBA_OUT: w.mamba_out = p; break;
+        case B200_T_WQ: w.wq = p; break;
+        case B200_T_WK: w.wk = p; break;
+        case B200_T_WV: w.wv = p; break;
+        case B200_T_WO: w.wo = p; break;
+        case B200_T_ROUTER: w.router = f; break;
+        case B200_T_ROUTER_BIAS: w.router_bias = f; break;
+        case B200_T_MOE_GATE: w.gate = p; break;
+        case B200_T_MOE_UP: w.up = p; break;
+        case B200_T_MOE_DOWN: w.down = p; break;
+        case B200_T_SH_GATE: w.sh_gate = p; break;
+        case B200_T_SH_UP: w.sh_up = p; break;
+        case B200_T_SH_DOWN: w.sh_down = p; break;
+        default: return fail(B200_EINVAL, "decoder_set_tensor: unknown tensor id %d", id);
+    }
+    return B200_OK;
+}
+
+int b200_decoder_reset(b200_decoder* dec) {
+    B200_REQUIRE(dec, "decoder_reset: null handle");
+    cudaStream_t st = stream();
+    const int B = dec->batch;
+    B200_CUDA(cudaMemsetAsync(dec->len, 0, (size_t)B * 4, st));
+    for (int l = 0; l < dec->n_layers; ++l) {
+        LayerW& w = dec->L[l];
+        if (dec->types[l] == 0) {
+            B200_CUDA(cudaMemsetAsync(w.conv_state, 0, (size_t)B * dec->conv_dim * std::max(dec->mk - 1, 1) * 4, st));
+            B200_CUDA(cudaMemsetAsync(w.ssm_state, 0, (size_t)B * dec->d_inner * dec->mds * 4, st));
+        }
+    }
+    dec->position = 0;
+    return B200_OK;
+}
+
+int b200_decoder_configure(b200_decoder* dec, int fused, int use_graph) {
+    B200_REQUIRE(dec, "decoder_configure: null handle");
+    drop_graph(dec);
+    dec->fused = fused ? 1 : 0;
+    dec->use_graph = use_graph ? 1 : 0;
+    dec->launches = 0;
+    return B200_OK;
+}
+
+int b200_decoder_step(b200_decoder* dec, const int32_t* tokens_dev, int32_t* next_dev) {
+    int rc = check_ready(dec);
+    if (rc) return rc;
+    B200_REQUIRE(tokens_dev && next_dev, "decoder_step: null pointer");
+    B200_REQUIRE(dec->position < dec->max_ctx, "decoder_step: context full (%d tokens)", dec->max_ctx);
+    if (!dec->use_graph) {
+        const unsigned long long before = g_kernel_launches;
+        rc = enqueue_step(dec, tokens_dev, next_dev);
+        dec->launches = (int)(g_kernel_launches - before);
+        if (rc) return rc;
+        dec->position += 1;
+        return B200_OK;
+    }
+    if (!dec->graph || dec->graph_tok != tokens_dev || dec->graph_next != next_dev) {
+        drop_graph(dec);
+        // Workspaces grow with cudaMalloc, which cannot run inside a capture.  The
+        // first step of a configuration therefore runs eagerly (sizing every
+        // workspace); the capture happens on the second.
+        if (dec->launches == 0) {
+            const unsigned long long before = g_kernel_launches;
+            rc = enqueue_step(dec, tokens_dev, next_dev);
+            dec->launches = (int)(g_kernel_launches - before);
+            if (rc) return rc;
+            dec->position += 1;
+            return B200_OK;
+        }
+        if (!dec->own_stream) B200_CUDA(cudaStreamCreateWithFlags(&dec->own_stream, cudaStreamNonBlocking));
+        cudaStream_t prev = stream();
+        b200_set_stream(dec->own_stream);
+        cudaGraph_t g = nullptr;
+        cudaError_t e = cudaStreamBeginCapture(dec->own_stream, cudaStreamCaptureModeThreadLocal);
+        if (e == cudaSuccess) {
+            const unsigned long long before = g_kernel_launches;
+            rc = enqueue_step(dec, tokens_dev, next_dev);
+            dec->launches = (int)(g_kernel_launches - before);
+            e = cudaStreamEndCapture(dec->own_stream, &g);
+        }
+        b200_set_stream(prev);
+        if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+        if (e != cudaSuccess) return cuda_status(e, "decoder_step: stream capture");
+        e = cudaGraphInstantiate(&dec->graph, g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) return cuda_status(e, "decoder_step: cudaGraphInstantiate");
+        dec->graph_tok = tokens_dev;
+        dec->graph_next = next_dev;
+    }
+    B200_CUDA(cudaGraphLaunch(dec->graph, stream()));
+    dec->position += 1;
+    return B200_OK;
+}
+
+int b200_decoder_step_host(b200_decoder* dec, const int32_t* tokens_host, int32_t* next_host) {
+    B200_REQUIRE(dec && tokens_host && next_host, "decoder_step_host: null pointer");
+    const size_t bytes = (size_t)dec->batch * 4;
+    memcpy(dec->h_tok, tokens_host, bytes);
+    B200_CUDA(cudaMemcpyAsync(dec->tok, dec->h_tok, bytes, cudaMemcpyHostToDevice, stream()));
+    int rc = b200_decoder_step(dec, dec->tok, dec->next);
+    if (rc) return rc;
+    B200_CUDA(cudaMemcpyAsync(dec->h_next, dec->next, bytes, cudaMemcpyDeviceToHost, stream()));
+    B200_CUDA(cudaStreamSynchronize(stream()));
+    memcpy(next_host, dec->h_next, bytes);
+    return B200_OK;
+}
+
+int b200_decoder_logits(b200_decoder* dec, const float** logits_dev) {
+    B200_REQUIRE(dec && logits_dev, "decoder_logits: null pointer");
+    *logits_dev = dec->logits;
+    return B200_OK;
+}
+int b200_decoder_position(b200_decoder* dec, int* position) {
+    B200_REQUIRE(dec && position, "decoder_position: null pointer");
+    *position = dec->position;
+    return B200_OK;
+}
+int b200_decoder_launches_per_step(b200_decoder* dec, int* launches) {
+    B200_REQUIRE(dec && launches, "decoder_launches_per_step: null pointer");
+    *launches = dec->launches;
+    return B200_OK;
+}
+
+static double packed_bytes(int qkind, double rows, double cols) {
+    if (qkind < 0) return rows * cols * 2.0;
+    const double be = qkind == 3 ? 256.0 : 32.0;
+    const double bb = qkind == 0 ? 18.0 : qkind == 1 ? 20.0 : qkind == 2 ? 34.0 : 144.0;
+    return rows * cols / be * bb;
+}
+
+int b200_decoder_step_bytes(b200_decoder* dec, double* bytes) {
+    B200_REQUIRE(dec && bytes, "decoder_step_bytes: null pointer");
+    const double B = dec->batch, d = dec->d;
+    const int q = dec->qkind;
+    double total = d * 2.0 * B;                              // embedding rows
+    total += (double)dec->vocab * d * 2.0;                   // lm_head
+    total += d * 4.0;                                        // final norm
+    const double tokens_in_cache = dec->position + 1;
+    // experts touched by a step: at most all of them, at most batch*K
+    const double routed = std::min((double)dec->ne, B * dec->K);
+    for (int l = 0; l < dec->n_layers; ++l) {
+        total += 2.0 * d * 4.0;                              // two norms
+        if (dec->types[l] == 0) {
+            const double proj = dec->d_inner + dec->conv_dim + dec->mh;
+            total += packed_bytes(q, proj, d) + packed_bytes(q, d, dec->d_inner);
+            total += (double)dec->conv_dim * (dec->mk + 1) * 4.0 + dec->mh * 12.0 + dec->d_inner * 4.0;
+            total += B * 2.0 * ((double)dec->d_inner * dec->mds * 4.0 + (double)dec->conv_dim * (dec->mk - 1) * 4.0);
+        } else {
+            const double qd = (double)dec->H * dec->hd, kvd = (double)dec->KV * dec->hd;
+            total += packed_bytes(q, qd + 2 * kvd, d) + packed_bytes(q, d, qd);
+            total += B * tokens_in_cache * 2.0 * kvd * 2.0;  // K and V rows, fp16
+        }
+        total += (double)dec->ne * d * 4.0 + dec->ne * 4.0;  // router + bias
+        total += routed * 3.0 * packed_bytes(q, dec->E, d);
+        if (dec->SH > 0) total += 3.0 * packed_bytes(q, dec->SH, d);
+    }
+    *bytes = total;
+    return B200_OK;
+}
+
+}  // extern "C"

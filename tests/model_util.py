@@ -1,0 +1,209 @@
+"""Random-init hybrid models (Mamba-2 + GQA + MoE) for the model-level tests, the
+Python restatement of the reference's per-token op sequence over the CPU oracle,
+and the loader that hands the same bytes to the CUDA decoder.
+
+Weight storage follows Model::storage_dtype_for (model/model.cpp:959-986): norms,
+conv, dt_bias, A_log, D, router and router bias fp32; embeddings / lm_head fp16
+(tied); every other matrix packed in the model's qkind.
+"""
+import ctypes as C
+
+import numpy as np
+
+from cases import mamba_params, store_weight
+
+# config 1 of the benchmark description, scaled to a test-sized vocabulary
+CONFIG_1 = dict(vocab=32768, hidden=768, n_layers=8, layer_types=[0, 0, 0, 1, 0, 0, 0, 1],
+                n_heads=12, n_kv=4, head_dim=64, rope_type=1, rope_theta=1e4,
+                mamba_heads=24, mamba_d_head=64, mamba_d_state=64, mamba_d_conv=4,
+                n_experts=16, top_k=2, expert_dim=512, shared_dim=1024, qkind=2,
+                rms_eps=1e-5, embedding_multiplier=1.0, residual_multiplier=1.0,
+                attn_scale=0.0, logits_scaling=1.0)
+
+TINY = dict(vocab=512, hidden=256, n_layers=4, layer_types=[0, 1, 0, 1],
+            n_heads=4, n_kv=2, head_dim=64, rope_type=1, rope_theta=1e4,
+            mamba_heads=8, mamba_d_head=64, mamba_d_state=128, mamba_d_conv=4,
+            n_experts=8, top_k=2, expert_dim=256, shared_dim=256, qkind=3,
+            rms_eps=1e-5, embedding_multiplier=12.0, residual_multiplier=0.22,
+            attn_scale=0.0078125, logits_scaling=6.0)
+
+
+def make_model(oracle, cfg, seed=0, w_std=0.02):
+    r = np.random.default_rng(seed)
+    d, q = cfg["hidden"], cfg["qkind"]
+    m = {"cfg": cfg, "layers": []}
+    emb = (r.standard_normal((cfg["vocab"], d)) * w_std).astype(np.float32)
+    m["embed"] = oracle.f32_to_f16(emb)                      # tied with lm_head
+    m["final_norm"] = (1 + 0.1 * r.standard_normal(d)).astype(np.float32)
+    hd = cfg["head_dim"]
+    m["inv_freq"] = (1.0 / cfg["rope_theta"] ** (np.arange(hd // 2) * 2.0 / hd)).astype(np.float32)
+    qd, kvd = cfg["n_heads"] * hd, cfg["n_kv"] * hd
+    ne, E, SH = cfg["n_experts"], cfg["expert_dim"], cfg["shared_dim"]
+    for t in cfg["layer_types"]:
+        L = {"type": t,
+             "attn_norm": (1 + 0.1 * r.standard_normal(d)).astype(np.float32),
+             "ffn_norm": (1 + 0.1 * r.standard_normal(d)).astype(np.float32)}
+        if t == 0:
+            L.update(mamba_params(oracle, r, d, cfg["mamba_heads"], cfg["mamba_d_head"], cfg["mamba_d_state"],
+                                  cfg["mamba_d_conv"], q, w_std))
+        else:
+            L["wq"] = store_weight(oracle, r.standard_normal((qd, d)) * w_std, q)
+            L["wk"] = store_weight(oracle, r.standard_normal((kvd, d)) * w_std, q)
+            L["wv"] = store_weight(oracle, r.standard_normal((kvd, d)) * w_std, q)
+            L["wo"] = store_weight(oracle, r.standard_normal((d, qd)) * w_std, q)
+        L["router"] = (r.standard_normal((ne, d)) / np.sqrt(d)).astype(np.float32)
+        L["router_bias"] = (r.standard_normal(ne) * 0.5 / ne).astype(np.float32)
+        L["gate"] = store_weight(oracle, r.standard_normal((ne * E, d)) * w_std, q)
+        L["up"] = store_weight(oracle, r.standard_normal((ne * E, d)) * w_std, q)
+        L["down"] = store_weight(oracle, r.standard_normal((ne * d, E)) * w_std, q)
+        L["sh_gate"] = store_weight(oracle, r.standard_normal((SH, d)) * w_std, q)
+        L["sh_up"] = store_weight(oracle, r.standard_normal((SH, d)) * w_std, q)
+        L["sh_down"] = store_weight(oracle, r.standard_normal((d, SH)) * w_std, q)
+        m["layers"].append(L)
+    return m
+
+
+class OracleDecoder:
+    """One sequence, one token at a time, in the op order of
+    Generator::decode_step_logits (inference/generator.cpp:221-443) with the CPU
+    oracle standing in for every op.  The KV cache is the reference's fp16 ring with
+    no pinned prefix and ring_start 0 (a contiguous cache)."""
+
+    def __init__(self, oracle, model, max_ctx):
+        self.o, self.m, self.cfg = oracle, model, model["cfg"]
+        c = self.cfg
+        self.max_ctx = max_ctx
+        self.conv_dim = c["mamba_heads"] * c["mamba_d_head"] + 2 * c["mamba_d_state"]
+        self.reset()
+
+    def reset(self):
+        c = self.cfg
+        kvd = c["n_kv"] * c["head_dim"]
+        self.pos = 0
+        self.state = []
+        for t in c["layer_types"]:
+            if t == 0:
+                self.state.append(dict(
+                    conv=np.zeros((self.conv_dim, c["mamba_d_conv"] - 1), np.float32),
+                    ssm=np.zeros((c["mamba_heads"] * c["mamba_d_head"], c["mamba_d_state"]), np.float32)))
+            else:
+                self.state.append(dict(k=np.zeros((self.max_ctx, kvd), np.uint16),
+                                       v=np.zeros((self.max_ctx, kvd), np.uint16)))
+
+    def step(self, token):
+        o, c, m = self.o, self.cfg, self.m
+        d, q = c["hidden"], c["qkind"]
+        hd, H, KV = c["head_dim"], c["n_heads"], c["n_kv"]
+        scale = c["attn_scale"] if c["attn_scale"] > 0 else 1.0 / np.sqrt(np.float32(hd))
+        x = o.embedding(np.array([token], np.int32), m["embed"], True, d, c["vocab"])[0]
+        if c["embedding_multiplier"] != 1.0:
+            x = x * np.float32(c["embedding_multiplier"])
+        for L, st in zip(m["layers"], self.state):
+            xb = o.rmsnorm(x[None], L["attn_norm"], c["rms_eps"])[0]
+            if L["type"] == 0:
+                y, st["conv"], st["ssm"] = o.mamba2_step(
+                    xb, L["w_in"], L["conv_w"], L["conv_b"], L["dt_bias"], L["a_log"], L["D"], L["norm_w"],
+                    L["w_out"], st["conv"], st["ssm"], d, L["d_inner"], L["conv_dim"], c["mamba_heads"],
+                    c["mamba_d_head"], c["mamba_d_state"], c["mamba_d_conv"], c["rms_eps"], q)
+            else:
+                qv = o.linear(xb[None], L["wq"], q, 1, d, H * hd)
+                kv = o.linear(xb[None], L["wk"], q, 1, d, KV * hd)
+                vv = o.linear(xb[None], L["wv"], q, 1, d, KV * hd)
+                if c["rope_type"] >= 0:
+                    qv, kv = o.rope_cached(qv.reshape(1, H, hd), kv.reshape(1, KV, hd),
+                                           np.array([self.pos], np.int32), m["inv_freq"], H, KV, hd, c["rope_type"])
+                st["k"][self.pos] = o.f32_to_f16(kv.reshape(-1))
+                st["v"][self.pos] = o.f32_to_f16(vv.reshape(-1))
+                a = o.attention_decode_ring(qv.reshape(H, hd), st["k"], st["v"], 1, H, KV, hd, 0, 0, self.pos + 1,
+                                            self.max_ctx, float(scale), 0)
+                y = o.linear(a.reshape(1, -1), L["wo"], q, 1, H * hd, d)[0]
+            x = x + y * np.float32(c["residual_multiplier"])
+            xb = o.rmsnorm(x[None], L["ffn_norm"], c["rms_eps"])
+            y, _, _, _ = o.moe_forward(xb, L["router"], L["router_bias"], L["gate"], L["up"], L["down"], L["sh_gate"],
+                                       L["sh_up"], L["sh_down"], d, c["expert_dim"], c["n_experts"], c["top_k"],
+                                       c["shared_dim"], q)
+            x = x + y[0] * np.float32(c["residual_multiplier"])
+        xb = o.rmsnorm(x[None], m["final_norm"], c["rms_eps"])
+        logits = o.linear(xb, m["embed"], -1, 1, d, c["vocab"])[0]
+        if c["logits_scaling"] != 1.0:
+            logits = logits * np.float32(1.0 / np.float32(c["logits_scaling"]))
+        self.pos += 1
+        return logits
+
+
+# tensor ids of include/b200step.h
+T = dict(embed=0, final_norm=1, lm_head=2, inv_freq=3, attn_norm=10, ffn_norm=11,
+         w_in=20, conv_w=21, conv_b=22, dt_bias=23, a_log=24, D=25, norm_w=26, w_out=27,
+         wq=30, wk=31, wv=32, wo=33, router=40, router_bias=41, gate=42, up=43, down=44,
+         sh_gate=45, sh_up=46, sh_down=47)
+
+
+class CudaDecoder:
+    """b200_decoder over device copies of a make_model() model."""
+
+    def __init__(self, model, batch, max_ctx, kv_page=64):
+        from gpu_util import dev, pkg
+        self.lib = pkg.lib()
+        c = model["cfg"]
+        self.cfg, self.batch = c, batch
+        self.handle = C.c_void_p()
+        types = np.array(c["layer_types"], np.int32)
+        self.lib.b200_decoder_create(C.byref(self.handle), batch, c["vocab"], c["hidden"], c["n_layers"],
+                                     types.ctypes.data, c["n_heads"], c["n_kv"], c["head_dim"], c["rope_type"],
+                                     c["mamba_heads"], c["mamba_d_head"], c["mamba_d_state"], c["mamba_d_conv"],
+                                     c["n_experts"], c["top_k"], c["expert_dim"], c["shared_dim"], max_ctx, kv_page,
+                                     c["qkind"], c["rms_eps"], c["embedding_multiplier"], c["residual_multiplier"],
+                                     c["attn_scale"], c["logits_scaling"])
+        self.keep = []
+
+        def put(layer, name, arr):
+            t = dev(arr)
+            self.keep.append(t)
+            self.lib.b200_decoder_set_tensor(self.handle, layer, T[name], t)
+            return t
+
+        e = put(-1, "embed", model["embed"])
+        self.lib.b200_decoder_set_tensor(self.handle, -1, T["lm_head"], e)
+        put(-1, "final_norm", model["final_norm"])
+        put(-1, "inv_freq", model["inv_freq"])
+        for i, L in enumerate(model["layers"]):
+            for name in T:
+                if name in L and isinstance(L[name], np.ndarray):
+                    put(i, name, L[name])
+
+    def configure(self, fused, graph):
+        self.lib.b200_decoder_configure(self.handle, int(fused), int(graph))
+
+    def reset(self):
+        self.lib.b200_decoder_reset(self.handle)
+
+    def step_host(self, tokens):
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        nxt = np.empty(self.batch, np.int32)
+        self.lib.b200_decoder_step_host(self.handle, tokens.ctypes.data, nxt.ctypes.data)
+        return nxt
+
+    def logits(self):
+        import torch
+        p = C.c_void_p()
+        self.lib.b200_decoder_logits(self.handle, C.byref(p))
+        n = self.batch * self.cfg["vocab"]
+        buf = torch.empty(n, dtype=torch.float32, device="cuda")
+        self.lib.b200_copy(buf, 1, p.value, 1, n * 4)
+        torch.cuda.synchronize()
+        return buf.cpu().numpy().reshape(self.batch, self.cfg["vocab"])
+
+    def launches(self):
+        n = C.c_int()
+        self.lib.b200_decoder_launches_per_step(self.handle, C.byref(n))
+        return n.value
+
+    def step_bytes(self):
+        b = C.c_double()
+        self.lib.b200_decoder_step_bytes(self.handle, C.byref(b))
+        return b.value
+
+    def close(self):
+        if self.handle:
+            self.lib.b200_decoder_destroy(self.handle)
+            self.handle = None

@@ -1,0 +1,104 @@
+"""GPU parity at model level: the CUDA decoder against the oracle walking the
+reference's per-token op sequence, teacher-forced."""
+import numpy as np
+import pytest
+
+from model_util import CONFIG_1, TINY, CudaDecoder, OracleDecoder, make_model
+
+pytestmark = pytest.mark.gpu
+
+
+def _teacher_forced(oracle, cfg, steps, graph, fused, seed=0):
+    """Feed the same seeded token stream to both sides (greedy continuation of the
+    oracle after a random prompt), compare logits and arg-max every step."""
+    model = make_model(oracle, cfg, seed)
+    ora = OracleDecoder(oracle, model, max_ctx=steps + 1)
+    dec = CudaDecoder(model, batch=1, max_ctx=steps + 1)
+    dec.configure(fused, graph)
+    r = np.random.default_rng(seed + 1)
+    prompt = r.integers(0, cfg["vocab"], steps // 2)
+    tok = int(prompt[0])
+    agree, margins, worst = 0, [], 0.0
+    for s in range(steps):
+        want = ora.step(tok)
+        got_next = int(dec.step_host([tok])[0])
+        got = dec.logits()[0]
+        err = np.abs(got - want)
+        worst = max(worst, float(err.max()))
+        # stated tolerance for logits vs the reference CPU path
+        assert np.all(err <= 2e-2 + 1e-2 * np.abs(want)), f"step {s}: max abs err {err.max()}"
+        top2 = np.sort(want)[-2:]
+        margins.append(float(top2[1] - top2[0]))
+        want_next = oracle.argmax(want)
+        agree += int(got_next == want_next)
+        assert got_next == int(np.argmax(got)) or got[got_next] == got.max()
+        tok = int(prompt[s + 1]) if s + 1 < len(prompt) else want_next       # teacher forcing
+    dec.close()
+    return agree / steps, worst, margins
+
+
+@pytest.mark.parametrize("graph", [0, 1])
+def test_tiny_model_teacher_forced(oracle, graph):
+    rate, worst, _ = _teacher_forced(oracle, TINY, steps=24, graph=graph, fused=0)
+    assert rate >= 0.99, f"greedy agreement {rate:.3f}"
+    assert worst < 2e-3            # fp32 paths: far inside the stated tolerance
+
+
+def test_config1_teacher_forced(oracle):
+    """Config-1 shape (hidden 768, 8 layers, Q8_0) with a reduced vocabulary so the scalar
+    oracle finishes in seconds."""
+    cfg = dict(CONFIG_1, vocab=4096)
+    rate, worst, margins = _teacher_forced(oracle, cfg, steps=32, graph=1, fused=0)
+    assert rate >= 0.99, f"greedy agreement {rate:.3f} (min top-2 margin {min(margins):.2e})"
+    assert worst < 2e-3
+
+
+def test_batch_rows_are_independent(oracle):
+    """batch 3 with different tokens per row == three batch-1 oracle runs."""
+    model = make_model(oracle, TINY, 3)
+    dec = CudaDecoder(model, batch=3, max_ctx=16)
+    oras = [OracleDecoder(oracle, model, max_ctx=16) for _ in range(3)]
+    r = np.random.default_rng(4)
+    for s in range(6):
+        toks = r.integers(0, TINY["vocab"], 3)
+        dec.step_host(toks)
+        got = dec.logits()
+        for b in range(3):
+            want = oras[b].step(int(toks[b]))
+            np.testing.assert_allclose(got[b], want, rtol=1e-3, atol=1e-4)
+    dec.close()
+
+
+def test_reset_and_replay_is_bit_stable(oracle):
+    model = make_model(oracle, TINY, 5)
+    dec = CudaDecoder(model, batch=2, max_ctx=16)
+    dec.configure(0, 1)
+    toks = np.array([[1, 2], [3, 4], [5, 6], [7, 8]])
+    runs = []
+    for _ in range(2):
+        dec.reset()
+        out = []
+        for t in toks:
+            dec.step_host(t)
+            out.append(dec.logits().copy())
+        runs.append(np.stack(out))
+    assert np.array_equal(runs[0].view(np.uint32), runs[1].view(np.uint32))
+    assert dec.launches() > 0 and dec.step_bytes() > 0
+    dec.close()
+
+
+def test_errors(oracle):
+    from gpu_util import B200Error, pkg
+    import ctypes as C
+    lib = pkg.lib()
+    h = C.c_void_p()
+    types = np.zeros(2, np.int32)
+    with pytest.raises(B200Error, match="unknown qkind"):
+        lib.b200_decoder_create(C.byref(h), 1, 64, 64, 2, types.ctypes.data, 2, 1, 32, -1, 2, 32, 16, 4, 4, 2, 32, 32,
+                                8, 4, 9, 1e-5, 1.0, 1.0, 0.0, 1.0)
+    lib.b200_decoder_create(C.byref(h), 1, 64, 64, 2, types.ctypes.data, 2, 1, 32, -1, 2, 32, 16, 4, 4, 2, 32, 32,
+                            8, 4, 2, 1e-5, 1.0, 1.0, 0.0, 1.0)
+    tok = np.zeros(1, np.int32)
+    with pytest.raises(B200Error, match="not set"):
+        lib.b200_decoder_step_host(h, tok.ctypes.data, tok.ctypes.data)
+    lib.b200_decoder_destroy(h)
