@@ -1,0 +1,47 @@
+// Host interface of the fused decode-step kernels (see fused.cu, moe_fused.cu).
+#pragma once
+
+#include "stream.cuh"
+
+namespace b200 {
+
+struct MambaDims {
+    int d, d_inner, conv_dim, n_heads, d_head, d_state, k, proj;
+    float eps;
+};
+
+enum { PRO_NONE = 0, PRO_RMS = 1 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_INPROJ = 2 };
+
+// One streamed matrix-vector product y[M,N] = f(x)[M,K] . W^T for M <= 8 tokens.
+struct SgArgs {
+    const uint8_t* w = nullptr;     // [N,K] in the kernel's weight kind
+    int N = 0, K = 0, M = 0;
+    const float* x = nullptr;       // [M, x_stride]
+    int x_stride = 0;
+    const float* norm_w = nullptr;  // PRO_RMS: x <- x * inv_rms(x) * norm_w
+    float eps = 0.0f;
+    const float* in_scale = nullptr;// optional per-token scalar applied to the dot products
+    float out_scale = 1.0f;         // EPI_STORE: y = acc * out_scale
+    float* y = nullptr;             // EPI_STORE output, rows y_stride apart
+    int y_stride = 0;
+    float* resid = nullptr;         // EPI_RESIDUAL: resid += res_mult * acc (rows y_stride apart)
+    float res_mult = 1.0f;
+    // EPI_INPROJ (Mamba in_proj): gate | conv step | dt
+    MambaDims p = {};
+    const float *conv_w = nullptr, *conv_b = nullptr;
+    float *conv_state = nullptr, *gate = nullptr, *bc = nullptr, *dt_raw = nullptr;
+    // filled by stream_gemv()
+    int rows_per_tile = 0, num_tiles = 0, stage_bytes = 0;
+    int64_t row_bytes = 0;
+    int* status = nullptr;
+};
+
+int stream_gemv(SgArgs a, int kind, int pro, int epi);
+
+int mamba_scan_norm(const float* bc, const float* dt_raw, const float* gate, const float* dt_bias,
+                    const float* a_log, const float* D, const float* norm_w, float* ssm_state, float* u_out,
+                    double* partials, unsigned* counter, float* inv_out, int batch, const MambaDims& p);
+int mamba_scan_norm_blocks(const MambaDims& p);
+
+}  // namespace b200

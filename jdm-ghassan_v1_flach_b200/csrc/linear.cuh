@@ -62,6 +62,32 @@ __device__ __forceinline__ void load_unit_plain(const uint8_t* row, int u, float
     }
 }
 
+// Same through generic loads (the row may live in shared memory).
+template <int KIND>
+__device__ __forceinline__ void load_unit_plain_generic(const uint8_t* row, int u, float (&w)[32]) {
+    if (KIND == KIND_F16) {
+        const uint4* p = reinterpret_cast<const uint4*>(row) + (int64_t)u * 4;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 v = p[i];
+            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&words[j]));
+                w[8 * i + 2 * j] = f.x;
+                w[8 * i + 2 * j + 1] = f.y;
+            }
+        }
+    } else {
+        const float4* p = reinterpret_cast<const float4*>(row) + (int64_t)u * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float4 v = p[i];
+            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+    }
+}
+
 // Dot products of weight row n with M (<= MT) activation rows.  Lanes split the
 // row's 32-weight units; on return every lane holds the full sums.  Packed weights
 // are rounded through fp16 exactly like the reference's CPU inference path

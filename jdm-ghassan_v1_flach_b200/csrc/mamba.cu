@@ -15,14 +15,9 @@
 // State updates and the convolution use explicit unfused multiply/add in the
 // reference's operand order, so given identical inputs the carried state is
 // bit-identical to the CPU path; only dot-product summation order differs.
-#include "linear.cuh"
+#include "fused.cuh"
 
 namespace b200 {
-
-struct MambaDims {
-    int d, d_inner, conv_dim, n_heads, d_head, d_state, k, proj;
-    float eps;
-};
 
 // ---------------------------------------------------------------------------
 // Decode: in_proj GEMV whose epilogue performs the convolution step.

@@ -9,7 +9,7 @@
 #include <cstring>
 #include <vector>
 
-#include "common.cuh"
+#include "fused.cuh"
 #include "../../include/b200step.h"
 
 namespace b200 {
@@ -117,6 +117,10 @@ struct b200_decoder {
     cudaStream_t own_stream = nullptr;
     int launches = 0;
     int32_t *h_tok = nullptr, *h_next = nullptr;   // pinned staging for the host entry point
+    // fused mode scratch
+    float *f_gate = nullptr, *f_bc = nullptr, *f_dt = nullptr, *f_u = nullptr, *f_inv = nullptr;
+    double* f_partials = nullptr;
+    unsigned* f_counter = nullptr;
 };
 
 static int dev_alloc(b200_decoder* dec, void** p, size_t bytes) {
@@ -202,6 +206,94 @@ static int enqueue_step(b200_decoder* dec, const int32_t* tokens, int32_t* next)
     return B200_OK;
 }
 
+// Fused variant (batch <= 8): the RMSNorm before each projection runs as that
+// projection's prologue, the residual add as the epilogue of the layer's last
+// projection, the Mamba conv step inside in_proj's epilogue and the gated norm is
+// folded into the state update + out_proj.  Kernels are chained with programmatic
+// dependent launch so each one streams its weights while its predecessor drains.
+static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t* next) {
+    const int B = dec->batch, d = dec->d;
+    cudaStream_t st = stream();
+    const int kind = tag_of_qkind(dec->qkind);
+    int rc;
+#define STEP(call)              \
+    do {                        \
+        rc = (call);            \
+        if (rc) return rc;      \
+    } while (0)
+    step_begin_kernel<<<ceil_div(B, 128), 128, 0, st>>>(dec->len, dec->pos, B);
+    B200_LAUNCH_CHECK("step_begin_kernel");
+    STEP(b200_embedding_forward_half(tokens, dec->embed, dec->x, B, d, dec->vocab));
+    if (dec->emb_mult != 1.0f) STEP(b200_scale_inplace(dec->x, dec->emb_mult, (int64_t)B * d));
+    const int res_grid = std::min(ceil_div(B * d, 256), num_sms() * 8);
+    MambaDims p;
+    p.d = d; p.d_inner = dec->d_inner; p.conv_dim = dec->conv_dim; p.n_heads = dec->mh; p.d_head = dec->mdh;
+    p.d_state = dec->mds; p.k = dec->mk; p.eps = dec->eps; p.proj = dec->d_inner + dec->conv_dim + dec->mh;
+    auto base = [&](const void* w, int N, int K, const float* x, int xs) {
+        SgArgs a;
+        a.w = static_cast<const uint8_t*>(w); a.N = N; a.K = K; a.M = B; a.x = x; a.x_stride = xs; a.eps = dec->eps;
+        return a;
+    };
+    for (int l = 0; l < dec->n_layers; ++l) {
+        LayerW& w = dec->L[l];
+        if (dec->types[l] == 0) {
+            SgArgs a = base(w.mamba_in, p.proj, d, dec->x, d);
+            a.norm_w = w.attn_norm; a.p = p; a.conv_w = w.conv_w; a.conv_b = w.conv_b; a.conv_state = w.conv_state;
+            a.gate = dec->f_gate; a.bc = dec->f_bc; a.dt_raw = dec->f_dt;
+            STEP(stream_gemv(a, kind, PRO_RMS, EPI_INPROJ));
+            STEP(mamba_scan_norm(dec->f_bc, dec->f_dt, dec->f_gate, w.dt_bias, w.a_log, w.D, w.mamba_norm, w.ssm_state,
+                                 dec->f_u, dec->f_partials, dec->f_counter, dec->f_inv, B, p));
+            SgArgs c = base(w.mamba_out, d, dec->d_inner, dec->f_u, dec->d_inner);
+            c.in_scale = dec->f_inv; c.resid = dec->x; c.y_stride = d; c.res_mult = dec->res_mult;
+            STEP(stream_gemv(c, kind, PRO_NONE, EPI_RESIDUAL));
+        } else {
+            const int qd = dec->H * dec->hd, kvd = dec->KV * dec->hd;
+            SgArgs aq = base(w.wq, qd, d, dec->x, d);
+            aq.norm_w = w.attn_norm; aq.y = dec->q; aq.y_stride = qd;
+            STEP(stream_gemv(aq, kind, PRO_RMS, EPI_STORE));
+            SgArgs ak = base(w.wk, kvd, d, dec->x, d);
+            ak.norm_w = w.attn_norm; ak.y = dec->k; ak.y_stride = kvd;
+            STEP(stream_gemv(ak, kind, PRO_RMS, EPI_STORE));
+            SgArgs av = base(w.wv, kvd, d, dec->x, d);
+            av.norm_w = w.attn_norm; av.y = dec->v; av.y_stride = kvd;
+            STEP(stream_gemv(av, kind, PRO_RMS, EPI_STORE));
+            if (dec->rope_type >= 0)
+                STEP(b200_rope_forward_cached(dec->q, dec->k, dec->pos, dec->inv_freq, B, dec->H, dec->KV, dec->hd,
+                                              dec->rope_type));
+            kv_append_kernel<<<dim3(ceil_div(kvd, 256), B), 256, 0, st>>>(dec->k, dec->v, w.k_pages, w.v_pages,
+                                                                         dec->page_table, dec->pos, dec->max_pages,
+                                                                         dec->page, kvd);
+            B200_LAUNCH_CHECK("kv_append_kernel");
+            STEP(b200_attention_decode_paged_fp16(dec->q, w.k_pages, w.v_pages, dec->page_table, dec->len, dec->attn,
+                                                  B, dec->max_pages, dec->page, dec->H, dec->KV, dec->hd,
+                                                  dec->attn_scale));
+            SgArgs ao = base(w.wo, d, qd, dec->attn, qd);
+            ao.resid = dec->x; ao.y_stride = d; ao.res_mult = dec->res_mult;
+            STEP(stream_gemv(ao, kind, PRO_NONE, EPI_RESIDUAL));
+        }
+        STEP(b200_rmsnorm_forward(dec->x, w.ffn_norm, dec->xb, nullptr, B, d, dec->eps));
+        STEP(b200_moe_forward_bias_half(dec->xb, w.router, w.router_bias, static_cast<const uint16_t*>(w.gate),
+                                        static_cast<const uint16_t*>(w.up), static_cast<const uint16_t*>(w.down),
+                                        static_cast<const uint16_t*>(w.sh_gate), static_cast<const uint16_t*>(w.sh_up),
+                                        static_cast<const uint16_t*>(w.sh_down), dec->proj, nullptr, nullptr, nullptr,
+                                        nullptr, nullptr, nullptr, B, d, dec->E, dec->ne, dec->K, dec->SH, dec->qkind));
+        residual_kernel<<<res_grid, 256, 0, st>>>(dec->x, dec->proj, dec->res_mult, (int64_t)B * d);
+        B200_LAUNCH_CHECK("residual_kernel");
+    }
+    SgArgs h = base(dec->lm_head, dec->vocab, d, dec->x, d);
+    h.norm_w = dec->final_norm; h.y = dec->logits; h.y_stride = dec->vocab; h.out_scale = 1.0f / dec->logits_scaling;
+    STEP(stream_gemv(h, KIND_F16, PRO_RMS, EPI_STORE));
+    argmax_rows_kernel<<<B, 1024, 0, st>>>(dec->logits, dec->vocab, next);
+    B200_LAUNCH_CHECK("argmax_rows_kernel");
+#undef STEP
+    return B200_OK;
+}
+
+static int enqueue(b200_decoder* dec, const int32_t* tokens, int32_t* next) {
+    if (dec->fused && dec->batch <= 8) return enqueue_step_fused(dec, tokens, next);
+    return enqueue_step(dec, tokens, next);
+}
+
 static int check_ready(const b200_decoder* dec) {
     B200_REQUIRE(dec, "decoder: null handle");
     B200_REQUIRE(dec->embed && dec->lm_head && dec->final_norm, "decoder: embeddings / lm_head / final norm not set");
@@ -264,6 +356,17 @@ int b200_decoder_create(b200_decoder** out, int batch, int vocab, int hidden, in
     A((void**)&dec->len, (size_t)B * 4);
     A((void**)&dec->pos, (size_t)B * 4);
     A((void**)&dec->page_table, (size_t)B * dec->max_pages * 4);
+    {
+        MambaDims p{};
+        p.n_heads = mamba_heads; p.d_head = mamba_d_head;
+        A((void**)&dec->f_gate, (size_t)B * dec->d_inner * 4);
+        A((void**)&dec->f_bc, (size_t)B * dec->conv_dim * 4);
+        A((void**)&dec->f_dt, (size_t)B * std::max(mamba_heads, 4) * 4);
+        A((void**)&dec->f_u, (size_t)B * dec->d_inner * 4);
+        A((void**)&dec->f_inv, (size_t)B * 4);
+        A((void**)&dec->f_partials, (size_t)B * std::max(1, mamba_scan_norm_blocks(p)) * 8);
+        A((void**)&dec->f_counter, (size_t)B * 4);
+    }
     for (int l = 0; l < n_layers && !rc; ++l) {
         LayerW& w = dec->L[l];
         if (dec->types[l] == 0) {
@@ -380,7 +483,7 @@ int b200_decoder_step(b200_decoder* dec, const int32_t* tokens_dev, int32_t* nex
     B200_REQUIRE(dec->position < dec->max_ctx, "decoder_step: context full (%d tokens)", dec->max_ctx);
     if (!dec->use_graph) {
         const unsigned long long before = g_kernel_launches;
-        rc = enqueue_step(dec, tokens_dev, next_dev);
+        rc = enqueue(dec, tokens_dev, next_dev);
         dec->launches = (int)(g_kernel_launches - before);
         if (rc) return rc;
         dec->position += 1;
@@ -393,7 +496,7 @@ int b200_decoder_step(b200_decoder* dec, const int32_t* tokens_dev, int32_t* nex
         // workspace); the capture happens on the second.
         if (dec->launches == 0) {
             const unsigned long long before = g_kernel_launches;
-            rc = enqueue_step(dec, tokens_dev, next_dev);
+            rc = enqueue(dec, tokens_dev, next_dev);
             dec->launches = (int)(g_kernel_launches - before);
             if (rc) return rc;
             dec->position += 1;
@@ -406,7 +509,7 @@ int b200_decoder_step(b200_decoder* dec, const int32_t* tokens_dev, int32_t* nex
         cudaError_t e = cudaStreamBeginCapture(dec->own_stream, cudaStreamCaptureModeThreadLocal);
         if (e == cudaSuccess) {
             const unsigned long long before = g_kernel_launches;
-            rc = enqueue_step(dec, tokens_dev, next_dev);
+            rc = enqueue(dec, tokens_dev, next_dev);
             dec->launches = (int)(g_kernel_launches - before);
             e = cudaStreamEndCapture(dec->own_stream, &g);
         }

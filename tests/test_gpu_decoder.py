@@ -44,6 +44,21 @@ def test_tiny_model_teacher_forced(oracle, graph):
     assert worst < 2e-3            # fp32 paths: far inside the stated tolerance
 
 
+@pytest.mark.parametrize("graph", [0, 1])
+def test_tiny_model_fused_teacher_forced(oracle, graph):
+    """Cross-op fused kernels (norm prologue, conv / residual epilogues, streamed weights)."""
+    rate, worst, _ = _teacher_forced(oracle, TINY, steps=24, graph=graph, fused=1)
+    assert rate >= 0.99, f"greedy agreement {rate:.3f}"
+    assert worst < 2e-3
+
+
+def test_config1_fused_teacher_forced(oracle):
+    cfg = dict(CONFIG_1, vocab=4096)
+    rate, worst, margins = _teacher_forced(oracle, cfg, steps=32, graph=1, fused=1)
+    assert rate >= 0.99, f"greedy agreement {rate:.3f} (min top-2 margin {min(margins):.2e})"
+    assert worst < 2e-3
+
+
 def test_config1_teacher_forced(oracle):
     """Config-1 shape (hidden 768, 8 layers, Q8_0) with a reduced vocabulary so the scalar
     oracle finishes in seconds."""
