@@ -1,4 +1,4 @@
-// Host interface of the fused decode-step kernels (see fused.cu, moe_fused.cu).
+// Host interface of the fused decode-step kernels (fused.cu).
 #pragma once
 
 #include "stream.cuh"
@@ -21,7 +21,9 @@ struct SgArgs {
     int x_stride = 0;
     const float* norm_w = nullptr;  // PRO_RMS: x <- x * inv_rms(x) * norm_w
     float eps = 0.0f;
-    const float* in_scale = nullptr;// optional per-token scalar applied to the dot products
+    // optional per-token scalar on the dot products: 1/sqrt(sum(partials)/in_dim + eps)
+    const double* in_partials = nullptr;
+    int n_partials = 0, in_dim = 1;
     float out_scale = 1.0f;         // EPI_STORE: y = acc * out_scale
     float* y = nullptr;             // EPI_STORE output, rows y_stride apart
     int y_stride = 0;
@@ -32,16 +34,39 @@ struct SgArgs {
     const float *conv_w = nullptr, *conv_b = nullptr;
     float *conv_state = nullptr, *gate = nullptr, *bc = nullptr, *dt_raw = nullptr;
     // filled by stream_gemv()
-    int rows_per_tile = 0, num_tiles = 0, stage_bytes = 0;
+    int rows_per_tile = 0, num_tiles = 0, stage_bytes = 0, n_stages = 0;
     int64_t row_bytes = 0;
     int* status = nullptr;
 };
 
 int stream_gemv(SgArgs a, int kind, int pro, int epi);
 
+// Decode state update; partials: [batch, mamba_scan_norm_blocks()] doubles.
 int mamba_scan_norm(const float* bc, const float* dt_raw, const float* gate, const float* dt_bias,
                     const float* a_log, const float* D, const float* norm_w, float* ssm_state, float* u_out,
-                    double* partials, unsigned* counter, float* inv_out, int batch, const MambaDims& p);
+                    double* partials, int batch, const MambaDims& p);
 int mamba_scan_norm_blocks(const MambaDims& p);
+
+// MoE layer on M <= 8 tokens: resid += res_mult * moe(rmsnorm(x) * norm_w).
+struct MoeFusedArgs {
+    const float* x = nullptr;        // [M, d] pre-norm residual stream
+    const float* norm_w = nullptr;
+    float eps = 0.0f;
+    const float *router_w = nullptr, *router_bias = nullptr;
+    const uint8_t *gates = nullptr, *ups = nullptr, *downs = nullptr, *sh_g = nullptr, *sh_u = nullptr, *sh_d = nullptr;
+    float* logits = nullptr;         // [M, ne] scratch
+    int32_t* idx = nullptr;          // [M, K]
+    float* w = nullptr;              // [M, K]
+    float* probs_out = nullptr;      // optional [M, ne]
+    float* act = nullptr;            // [M, K, E] scratch
+    float* sh_act = nullptr;         // [M, SH] scratch
+    float* resid = nullptr;          // [M, d], updated in place
+    float res_mult = 1.0f;
+    int M = 0, d = 0, E = 0, ne = 0, K = 0, SH = 0;
+    // filled per phase
+    int rows_per_tile = 0, stage_bytes = 0, n_stages = 0;
+    int* status = nullptr;
+};
+int moe_fused(MoeFusedArgs a, int kind);
 
 }  // namespace b200

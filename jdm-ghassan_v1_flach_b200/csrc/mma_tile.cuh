@@ -1,0 +1,161 @@
+// Tensor-core dot products of a 16-row weight tile (in shared memory) with up to 8
+// activation vectors: the decode-time GEMV mapped onto mma.sync m16n8k16 (weights =
+// A, the tokens = the 8 columns of B) so that dequantisation costs about one
+// instruction per two weights instead of five per weight.
+//
+// Numerics.  A holds exact values (Q4_K: the integer nibble, or 16x the nibble for
+// the high half, produced with the 0x6400 exponent trick and an exact fp16 subtract;
+// fp16 weights as stored).  Each activation is split x = hi + lo into two fp16 values
+// (22 significant bits) and both parts are multiplied, accumulation is fp32, and
+// the Q4_K sub-block scale and minimum are applied in fp32 afterwards:
+//     y += (d*sc) * sum(q*x) - (dmin*m) * sum(x)        per 32-weight sub-block.
+// The result differs from the fp32 scalar path only by summation order and by the
+// 2^-11 rounding the reference's CPU path applies to each dequantised weight.
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include "quant.cuh"
+
+namespace b200 {
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Activations for the MMA path: per token two fp16 arrays (hi, lo parts) of K values
+// and K/32 fp32 sub-block sums.  Token rows are XH_PAD halves longer than K so that
+// two tokens' 64-byte segments fall into different bank halves.  Row `zero_row` is
+// all zeros and stands in for absent tokens.
+constexpr int XH_PAD = 32;
+struct XHalf {
+    const __half* hi;     // [(tokens+1)][K + XH_PAD]
+    const __half* lo;
+    const float* sumx;    // [(tokens+1)][K/32]
+    int stride;           // K + XH_PAD
+    int nsub;             // K / 32
+    int zero_row;
+};
+__host__ __device__ inline size_t xhalf_bytes(int K, int tokens) {
+    return (size_t)(tokens + 1) * ((size_t)(K + XH_PAD) * 2 * 2 + (size_t)(K / 32) * 4);
+}
+
+// Position of activation k inside its token row.  Q4_K: within every aligned run of 8
+// the order is 0,2,1,3,4,6,5,7 so that one 16-byte load yields the four B registers
+// of the two MMAs that consume one 32-bit word of nibbles.
+template <int KIND>
+__device__ __forceinline__ int xh_index(int k) {
+    if (KIND == 3) {
+        const int r = k & 7;
+        const int p = (r & 4) | ((r & 1) << 1) | ((r >> 1) & 1);
+        return (k & ~7) | p;
+    }
+    return k;
+}
+
+__device__ __forceinline__ uint32_t nib_lo(uint32_t w) {   // nibbles at bits 0-3 and 16-19 -> half2 (q, q)
+    const uint32_t t = (w & 0x000F000Fu) | 0x64006400u;
+    const __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&t), __half2half2(__ushort_as_half(0x6400)));
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t nib_hi(uint32_t w) {   // nibbles at bits 4-7 and 20-23 -> half2 (16q, 16q)
+    const uint32_t t = (w & 0x00F000F0u) | 0x64006400u;
+    const __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&t), __half2half2(__ushort_as_half(0x6400)));
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Q4_K: partial sums over this warp's share of K (64-weight groups g = part,
+// part + nparts, ...) for the 16 rows at `tile` (row stride rb bytes).  acc: the m16n8
+// accumulator fragment (rows lane/4 and lane/4+8, columns = tokens 2*(lane%4), +1).
+__device__ __forceinline__ void tile_dot_q4k(const uint8_t* tile, int rb, int K, const XHalf& xh, int M, int part,
+                                             int nparts, int lane, float (&acc)[4]) {
+    const int gid = lane >> 2, tig = lane & 3;
+    const int tok = gid < M ? gid : xh.zero_row;
+    const __half* xh_row = xh.hi + (size_t)tok * xh.stride;
+    const __half* xl_row = xh.lo + (size_t)tok * xh.stride;
+    const int c0 = 2 * tig, c1 = 2 * tig + 1;
+    const float* sx0 = xh.sumx + (size_t)(c0 < M ? c0 : xh.zero_row) * xh.nsub;
+    const float* sx1 = xh.sumx + (size_t)(c1 < M ? c1 : xh.zero_row) * xh.nsub;
+    const int groups = K >> 6;
+    for (int g = part; g < groups; g += nparts) {
+        const int sb = g >> 2, j = g & 3;
+        // this lane's (row, sub-block) scale pair; shared with the warp by shuffles
+        float P, Q;
+        {
+            const int row = lane & 15, hi = lane >> 4;
+            const uint8_t* hdr = tile + (size_t)row * rb + sb * 144;
+            const uint4 h4 = *reinterpret_cast<const uint4*>(hdr);
+            const uint8_t* hb = reinterpret_cast<const uint8_t*>(&h4);
+            int s, m;
+            q4k_scale_min(2 * j + hi, hb + 4, s, m);
+            const float d = half_bits_to_float((uint16_t)(h4.x & 0xFFFF));
+            const float dmin = half_bits_to_float((uint16_t)(h4.x >> 16));
+            P = d * (float)s * (hi ? 0.0625f : 1.0f);
+            Q = dmin * (float)m;
+        }
+        const float P_lo_a = __shfl_sync(0xffffffffu, P, gid), P_lo_b = __shfl_sync(0xffffffffu, P, gid + 8);
+        const float P_hi_a = __shfl_sync(0xffffffffu, P, 16 + gid), P_hi_b = __shfl_sync(0xffffffffu, P, 24 + gid);
+        const float Q_lo_a = __shfl_sync(0xffffffffu, Q, gid), Q_lo_b = __shfl_sync(0xffffffffu, Q, gid + 8);
+        const float Q_hi_a = __shfl_sync(0xffffffffu, Q, 16 + gid), Q_hi_b = __shfl_sync(0xffffffffu, Q, 24 + gid);
+        const uint8_t* wbase = tile + sb * 144 + 16 + 32 * j + 8 * tig;
+        const uint2 wa = *reinterpret_cast<const uint2*>(wbase + (size_t)gid * rb);
+        const uint2 wb = *reinterpret_cast<const uint2*>(wbase + (size_t)(gid + 8) * rb);
+        const int k0 = sb * 256 + j * 64 + 8 * tig;
+        const uint4 bh_lo = *reinterpret_cast<const uint4*>(xh_row + k0);
+        const uint4 bl_lo = *reinterpret_cast<const uint4*>(xl_row + k0);
+        const uint4 bh_hi = *reinterpret_cast<const uint4*>(xh_row + k0 + 32);
+        const uint4 bl_hi = *reinterpret_cast<const uint4*>(xl_row + k0 + 32);
+        float cl[4] = {0.f, 0.f, 0.f, 0.f}, ch[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const uint32_t a0 = nib_lo(wa.x), a1 = nib_lo(wb.x), a2 = nib_lo(wa.x >> 8), a3 = nib_lo(wb.x >> 8);
+            mma_16816(cl, a0, a1, a2, a3, bh_lo.x, bh_lo.y);
+            mma_16816(cl, a0, a1, a2, a3, bl_lo.x, bl_lo.y);
+            const uint32_t e0 = nib_hi(wa.x), e1 = nib_hi(wb.x), e2 = nib_hi(wa.x >> 8), e3 = nib_hi(wb.x >> 8);
+            mma_16816(ch, e0, e1, e2, e3, bh_hi.x, bh_hi.y);
+            mma_16816(ch, e0, e1, e2, e3, bl_hi.x, bl_hi.y);
+        }
+        {
+            const uint32_t a0 = nib_lo(wa.y), a1 = nib_lo(wb.y), a2 = nib_lo(wa.y >> 8), a3 = nib_lo(wb.y >> 8);
+            mma_16816(cl, a0, a1, a2, a3, bh_lo.z, bh_lo.w);
+            mma_16816(cl, a0, a1, a2, a3, bl_lo.z, bl_lo.w);
+            const uint32_t e0 = nib_hi(wa.y), e1 = nib_hi(wb.y), e2 = nib_hi(wa.y >> 8), e3 = nib_hi(wb.y >> 8);
+            mma_16816(ch, e0, e1, e2, e3, bh_hi.z, bh_hi.w);
+            mma_16816(ch, e0, e1, e2, e3, bl_hi.z, bl_hi.w);
+        }
+        const int sub = sb * 8 + 2 * j;
+        const float s0l = sx0[sub], s1l = sx1[sub], s0h = sx0[sub + 1], s1h = sx1[sub + 1];
+        acc[0] += P_lo_a * cl[0] - Q_lo_a * s0l + P_hi_a * ch[0] - Q_hi_a * s0h;
+        acc[1] += P_lo_a * cl[1] - Q_lo_a * s1l + P_hi_a * ch[1] - Q_hi_a * s1h;
+        acc[2] += P_lo_b * cl[2] - Q_lo_b * s0l + P_hi_b * ch[2] - Q_hi_b * s0h;
+        acc[3] += P_lo_b * cl[3] - Q_lo_b * s1l + P_hi_b * ch[3] - Q_hi_b * s1h;
+    }
+}
+
+// fp16 weights: 32-wide k chunks c = part, part + nparts, ...
+__device__ __forceinline__ void tile_dot_f16(const uint8_t* tile, int rb, int K, const XHalf& xh, int M, int part,
+                                             int nparts, int lane, float (&acc)[4]) {
+    const int gid = lane >> 2, tig = lane & 3;
+    const int tok = gid < M ? gid : xh.zero_row;
+    const __half* xh_row = xh.hi + (size_t)tok * xh.stride;
+    const __half* xl_row = xh.lo + (size_t)tok * xh.stride;
+    const int chunks = K >> 5;
+    for (int c = part; c < chunks; c += nparts) {
+        const int k0 = 32 * c + 8 * tig;
+        const uint4 ra = *reinterpret_cast<const uint4*>(tile + (size_t)gid * rb + (size_t)k0 * 2);
+        const uint4 rb8 = *reinterpret_cast<const uint4*>(tile + (size_t)(gid + 8) * rb + (size_t)k0 * 2);
+        const uint4 bh = *reinterpret_cast<const uint4*>(xh_row + k0);
+        const uint4 bl = *reinterpret_cast<const uint4*>(xl_row + k0);
+        mma_16816(acc, ra.x, rb8.x, ra.y, rb8.y, bh.x, bh.y);
+        mma_16816(acc, ra.x, rb8.x, ra.y, rb8.y, bl.x, bl.y);
+        mma_16816(acc, ra.z, rb8.z, ra.w, rb8.w, bh.z, bh.w);
+        mma_16816(acc, ra.z, rb8.z, ra.w, rb8.w, bl.z, bl.w);
+    }
+}
+#endif
+
+}  // namespace b200

@@ -118,9 +118,11 @@ struct b200_decoder {
     int launches = 0;
     int32_t *h_tok = nullptr, *h_next = nullptr;   // pinned staging for the host entry point
     // fused mode scratch
-    float *f_gate = nullptr, *f_bc = nullptr, *f_dt = nullptr, *f_u = nullptr, *f_inv = nullptr;
+    float *f_gate = nullptr, *f_bc = nullptr, *f_dt = nullptr, *f_u = nullptr;
     double* f_partials = nullptr;
-    unsigned* f_counter = nullptr;
+    int f_blocks = 0;
+    float *f_logits = nullptr, *f_w = nullptr, *f_act = nullptr, *f_shact = nullptr;
+    int32_t* f_idx = nullptr;
 };
 
 static int dev_alloc(b200_decoder* dec, void** p, size_t bytes) {
@@ -242,9 +244,10 @@ static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t*
             a.gate = dec->f_gate; a.bc = dec->f_bc; a.dt_raw = dec->f_dt;
             STEP(stream_gemv(a, kind, PRO_RMS, EPI_INPROJ));
             STEP(mamba_scan_norm(dec->f_bc, dec->f_dt, dec->f_gate, w.dt_bias, w.a_log, w.D, w.mamba_norm, w.ssm_state,
-                                 dec->f_u, dec->f_partials, dec->f_counter, dec->f_inv, B, p));
+                                 dec->f_u, dec->f_partials, B, p));
             SgArgs c = base(w.mamba_out, d, dec->d_inner, dec->f_u, dec->d_inner);
-            c.in_scale = dec->f_inv; c.resid = dec->x; c.y_stride = d; c.res_mult = dec->res_mult;
+            c.in_partials = dec->f_partials; c.n_partials = dec->f_blocks; c.in_dim = dec->d_inner;
+            c.resid = dec->x; c.y_stride = d; c.res_mult = dec->res_mult;
             STEP(stream_gemv(c, kind, PRO_NONE, EPI_RESIDUAL));
         } else {
             const int qd = dec->H * dec->hd, kvd = dec->KV * dec->hd;
@@ -271,14 +274,16 @@ static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t*
             ao.resid = dec->x; ao.y_stride = d; ao.res_mult = dec->res_mult;
             STEP(stream_gemv(ao, kind, PRO_NONE, EPI_RESIDUAL));
         }
-        STEP(b200_rmsnorm_forward(dec->x, w.ffn_norm, dec->xb, nullptr, B, d, dec->eps));
-        STEP(b200_moe_forward_bias_half(dec->xb, w.router, w.router_bias, static_cast<const uint16_t*>(w.gate),
-                                        static_cast<const uint16_t*>(w.up), static_cast<const uint16_t*>(w.down),
-                                        static_cast<const uint16_t*>(w.sh_gate), static_cast<const uint16_t*>(w.sh_up),
-                                        static_cast<const uint16_t*>(w.sh_down), dec->proj, nullptr, nullptr, nullptr,
-                                        nullptr, nullptr, nullptr, B, d, dec->E, dec->ne, dec->K, dec->SH, dec->qkind));
-        residual_kernel<<<res_grid, 256, 0, st>>>(dec->x, dec->proj, dec->res_mult, (int64_t)B * d);
-        B200_LAUNCH_CHECK("residual_kernel");
+        MoeFusedArgs mo;
+        mo.x = dec->x; mo.norm_w = w.ffn_norm; mo.eps = dec->eps; mo.router_w = w.router; mo.router_bias = w.router_bias;
+        mo.gates = static_cast<const uint8_t*>(w.gate); mo.ups = static_cast<const uint8_t*>(w.up);
+        mo.downs = static_cast<const uint8_t*>(w.down); mo.sh_g = static_cast<const uint8_t*>(w.sh_gate);
+        mo.sh_u = static_cast<const uint8_t*>(w.sh_up); mo.sh_d = static_cast<const uint8_t*>(w.sh_down);
+        mo.logits = dec->f_logits; mo.idx = dec->f_idx; mo.w = dec->f_w; mo.act = dec->f_act; mo.sh_act = dec->f_shact;
+        mo.resid = dec->x; mo.res_mult = dec->res_mult;
+        mo.M = B; mo.d = d; mo.E = dec->E; mo.ne = dec->ne; mo.K = dec->K;
+        mo.SH = (w.sh_gate && w.sh_up && w.sh_down) ? dec->SH : 0;
+        STEP(moe_fused(mo, kind));
     }
     SgArgs h = base(dec->lm_head, dec->vocab, d, dec->x, d);
     h.norm_w = dec->final_norm; h.y = dec->logits; h.y_stride = dec->vocab; h.out_scale = 1.0f / dec->logits_scaling;
@@ -363,9 +368,13 @@ int b200_decoder_create(b200_decoder** out, int batch, int vocab, int hidden, in
         A((void**)&dec->f_bc, (size_t)B * dec->conv_dim * 4);
         A((void**)&dec->f_dt, (size_t)B * std::max(mamba_heads, 4) * 4);
         A((void**)&dec->f_u, (size_t)B * dec->d_inner * 4);
-        A((void**)&dec->f_inv, (size_t)B * 4);
+        dec->f_blocks = std::max(1, mamba_scan_norm_blocks(p));
+        A((void**)&dec->f_logits, (size_t)B * std::max(n_experts, 1) * 4);
+        A((void**)&dec->f_idx, (size_t)B * std::max(top_k, 1) * 4);
+        A((void**)&dec->f_w, (size_t)B * std::max(top_k, 1) * 4);
+        A((void**)&dec->f_act, (size_t)B * std::max(top_k * expert_dim, 1) * 4);
+        A((void**)&dec->f_shact, (size_t)B * std::max(shared_dim, 1) * 4);
         A((void**)&dec->f_partials, (size_t)B * std::max(1, mamba_scan_norm_blocks(p)) * 8);
-        A((void**)&dec->f_counter, (size_t)B * 4);
     }
     for (int l = 0; l < n_layers && !rc; ++l) {
         LayerW& w = dec->L[l];
