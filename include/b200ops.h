@@ -41,6 +41,11 @@ uint64_t b200_kernel_launches(void);
 
 /* ---- device utilities: gai::cuda::*, cuda/cuda_utils.h:14-33 ------------------ */
 int b200_device_count(int* count);                       /* probe(), :14 */
+/* What probe() fills into gai::DeviceInfo (core/device.h): the current device
+ * (LOCAL_RANK selects it on first use, as cuda/cuda_utils.cu:46-55 does). */
+int b200_device_info(int* index, char* name, int name_cap, int* cc_major, int* cc_minor,
+                     size_t* total_mem, size_t* free_mem);
+int b200_shutdown(void);                                 /* shutdown(), :31: frees every cached workspace */
 int b200_malloc_device(void** ptr, size_t nbytes);       /* malloc_device, :16 */
 int b200_free_device(void* ptr);                         /* free_device, :17 */
 int b200_memset_zero(void* ptr, size_t nbytes);          /* memset_zero, :18 */

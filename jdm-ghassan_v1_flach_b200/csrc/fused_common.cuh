@@ -1,0 +1,337 @@
+// Device-side machinery shared by the fused decode-step kernels: the TMA ring, the
+// staging of activations in shared memory, the per-tile dot products (tensor-core
+// path for Q4_K and fp16 weights, scalar path for the 32-element formats and fp32)
+// and the launch helpers.
+//
+// Kernel shape: SG_CONSUMERS consumer warps + one producer warp.  The producer
+// streams weight tiles (<= 16 rows, contiguous bytes) into a ring of stages; the
+// consumers compute the tile's dot products into a small shared buffer
+// red[buf][part][pass][row][token]; after one consumer barrier the threads
+// (row, token) add the parts and run the epilogue.  `pass` lets one tile carry two
+// matrices (gate and up rows of the same expert).
+#pragma once
+
+#include "fused.cuh"
+#include "mma_tile.cuh"
+
+namespace b200 {
+
+constexpr int SG_CONSUMERS = 8;                    // consumer warps
+constexpr int SG_CTHREADS = SG_CONSUMERS * 32;
+constexpr int SG_THREADS = SG_CTHREADS + 32;       // + one producer warp
+constexpr int SG_MAX_STAGES = 4;
+constexpr int SMEM_BUDGET = 113 * 1024;            // per CTA: two kernels' CTAs fit one SM, so a
+                                                   // dependent kernel can start streaming early
+constexpr int SMEM_BUDGET_FULL = 200 * 1024;       // fallback for wide rows: one CTA per SM
+constexpr int TILE_ROWS = 16;                      // rows of a tile on the tensor-core path (max elsewhere)
+constexpr int RED_TOK = 8;                         // token columns
+constexpr int RED_PASS = TILE_ROWS * RED_TOK;      // floats of one (part, pass)
+constexpr int RED_PASSES = 2;
+constexpr int RED_BUF = SG_CONSUMERS * RED_PASSES * RED_PASS;   // floats of one buffer
+constexpr int RED_FLOATS = 2 * RED_BUF;                         // double-buffered by tile parity
+constexpr int BAR_BYTES = 2 * SG_MAX_STAGES * 8 + 2 * SG_CONSUMERS * 8;   // mbarriers + reduction scratch
+
+template <int KIND>
+struct UsesMma {
+    static constexpr bool value = (KIND == 3 || KIND == KIND_F16);
+};
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(SG_CTHREADS) : "memory"); }
+
+// Sum over the consumer threads; result in every consumer thread.  red: >= SG_CONSUMERS doubles.
+__device__ __forceinline__ double consumer_sum_d(double v, double* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    v = warp_sum_d(v);
+    consumer_sync();
+    if (lane == 0) red[wid] = v;
+    consumer_sync();
+    double t = 0.0;
+#pragma unroll
+    for (int w = 0; w < SG_CONSUMERS; ++w) t += red[w];
+    return t;
+}
+
+// ---- the shared-memory ring ---------------------------------------------------
+struct Ring {
+    uint8_t* stages;
+    uint64_t *full, *empty;
+    int stage_bytes, n_stages;
+    int* status;
+    __device__ __forceinline__ void init() {
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < n_stages; ++s) {
+                mbar_init(&full[s], 1);
+                mbar_init(&empty[s], SG_CONSUMERS);
+            }
+            mbar_fence_init();
+        }
+        __syncthreads();
+    }
+    __device__ __forceinline__ uint8_t* stage(int i) const { return stages + (size_t)(i % n_stages) * stage_bytes; }
+    // producer side
+    __device__ __forceinline__ bool acquire(int i) {
+        return i < n_stages || mbar_wait(&empty[i % n_stages], ((i / n_stages) - 1) & 1, status);
+    }
+    __device__ __forceinline__ void expect(int i, uint32_t bytes) { mbar_expect_tx(&full[i % n_stages], bytes); }
+    __device__ __forceinline__ void copy(int i, int offset, const void* src, uint32_t bytes) {
+        tma_load_1d(stage(i) + offset, src, bytes, &full[i % n_stages]);
+    }
+    // never leave with copies of this CTA still in flight
+    __device__ __forceinline__ void drain(int issued) {
+        for (int i = max(0, issued - n_stages); i < issued; ++i)
+            if (!mbar_wait(&full[i % n_stages], (i / n_stages) & 1, status)) break;
+    }
+    // consumer side
+    __device__ __forceinline__ bool wait_full(int i) { return mbar_wait(&full[i % n_stages], (i / n_stages) & 1, status); }
+    __device__ __forceinline__ void release(int i) {
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) mbar_arrive(&empty[i % n_stages]);
+    }
+};
+
+// ---- activations in shared memory ----------------------------------------------
+// Scalar path: fp32, unit-major (stream.cuh).  Tensor-core path: fp16 hi/lo parts
+// and sub-block sums (mma_tile.cuh), plus an optional fp32 copy in natural order
+// (needed while normalising and by the exact-order router).
+struct XAct {
+    float* xs = nullptr;       // scalar path: [tokens][xs_tok]
+    int xs_tok = 0;
+    __half *hi = nullptr, *lo = nullptr;   // tensor-core path
+    float* sumx = nullptr;
+    float* f32 = nullptr;      // [tokens][K] natural order, may be null
+    int K = 0, tokens = 0;
+    __device__ __forceinline__ XHalf half() const {
+        XHalf h;
+        h.hi = hi; h.lo = lo; h.sumx = sumx; h.stride = K + XH_PAD; h.nsub = K >> 5; h.zero_row = tokens;
+        return h;
+    }
+};
+
+template <int KIND>
+__host__ __device__ inline size_t xact_bytes(int K, int tokens, bool want_f32) {
+    if (UsesMma<KIND>::value) return xhalf_bytes(K, tokens) + 16 + (want_f32 ? (size_t)tokens * K * 4 : 0);
+    return (size_t)tokens * xs_floats(K) * 4;
+}
+
+// Carve an XAct out of shared memory at p (16-byte aligned); returns the end.
+template <int KIND>
+__device__ __forceinline__ uint8_t* xact_carve(XAct& xa, uint8_t* p, int K, int tokens, bool want_f32) {
+    xa.K = K;
+    xa.tokens = tokens;
+    if (UsesMma<KIND>::value) {
+        const size_t row = (size_t)(K + XH_PAD);
+        xa.hi = reinterpret_cast<__half*>(p);
+        xa.lo = xa.hi + (size_t)(tokens + 1) * row;
+        xa.sumx = reinterpret_cast<float*>(xa.lo + (size_t)(tokens + 1) * row);
+        p = reinterpret_cast<uint8_t*>(xa.sumx + (size_t)(tokens + 1) * (K >> 5));
+        p = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 15) & ~(uintptr_t)15);
+        if (want_f32) {
+            xa.f32 = reinterpret_cast<float*>(p);
+            p += (size_t)tokens * K * 4;
+        }
+    } else {
+        xa.xs = reinterpret_cast<float*>(p);
+        xa.xs_tok = xs_floats(K);
+        p += (size_t)tokens * xa.xs_tok * 4;
+    }
+    return p;
+}
+
+// Zero row of the tensor-core layout (stands in for tokens beyond M).
+template <int KIND>
+__device__ __forceinline__ void xact_zero_row(const XAct& xa) {
+    if (UsesMma<KIND>::value) {
+        const size_t row = (size_t)(xa.K + XH_PAD);
+        for (int k = threadIdx.x; k < xa.K + XH_PAD; k += SG_CTHREADS) {
+            xa.hi[(size_t)xa.tokens * row + k] = __ushort_as_half(0);
+            xa.lo[(size_t)xa.tokens * row + k] = __ushort_as_half(0);
+        }
+        for (int s = threadIdx.x; s < (xa.K >> 5); s += SG_CTHREADS) xa.sumx[(size_t)xa.tokens * (xa.K >> 5) + s] = 0.0f;
+    }
+}
+
+__device__ __forceinline__ void split_half(float v, __half& h, __half& l) {
+    v = fminf(fmaxf(v, -60000.0f), 60000.0f);
+    h = __float2half_rn(v);
+    l = __float2half_rn(v - __half2float(h));
+}
+
+// Two sums over the consumer threads at once; red: >= 2 * SG_CONSUMERS doubles.
+__device__ __forceinline__ void consumer_sum_d2(double& a, double& b, double* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    a = warp_sum_d(a);
+    b = warp_sum_d(b);
+    consumer_sync();
+    if (lane == 0) { red[wid] = a; red[SG_CONSUMERS + wid] = b; }
+    consumer_sync();
+    a = 0.0;
+    b = 0.0;
+#pragma unroll
+    for (int w = 0; w < SG_CONSUMERS; ++w) { a += red[w]; b += red[SG_CONSUMERS + w]; }
+}
+
+// Token m's activations from global memory (K floats at x, K <= 256 * XV_MAX) into
+// shared memory.  Each thread keeps its K/256 values in registers, so global memory
+// is read once and one barrier (three with a reduction) separates load from use.
+// RMS: v = x * inv_rms * norm_w in the reference's operand order
+// (core/math_cpu.cpp:299-316; inv from a double sum of squares); nw_s is norm_w
+// already in shared memory.  `extra` is summed over the consumer threads in the same
+// reduction and returned (used for the gated-norm partial sums).  On the tensor-core
+// path the 32 consecutive k of a sub-block sit in one warp, so the sub-block sums
+// are warp shuffles.  Consumer threads only; ends with a consumer barrier.
+constexpr int XV_MAX = 32;
+template <int KIND, bool RMS, bool EXTRA>
+__device__ __forceinline__ double stage_x(const float* __restrict__ x, const float* nw_s, const XAct& xa, int m,
+                                          float eps, double* red, double extra) {
+    const int K = xa.K;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nv = (K + SG_CTHREADS - 1) / SG_CTHREADS;
+    float v[XV_MAX];
+    double ss = 0.0;
+#pragma unroll
+    for (int j = 0; j < XV_MAX; ++j) {
+        if (j < nv) {
+            const int k = j * SG_CTHREADS + threadIdx.x;
+            v[j] = k < K ? x[k] : 0.0f;
+            if (RMS) ss += (double)v[j] * v[j];
+        }
+    }
+    float inv = 1.0f;
+    if (RMS || EXTRA) {
+        consumer_sum_d2(ss, extra, red);
+        if (RMS) {
+            const double inv_d = 1.0 / sqrt(ss / (double)K + (double)eps);
+            inv = isfinite(inv_d) ? (float)inv_d : 0.0f;
+        }
+    }
+    float* xs = UsesMma<KIND>::value ? nullptr : xa.xs + (size_t)m * xa.xs_tok;
+    const size_t row = (size_t)(K + XH_PAD);
+    __half* hi = UsesMma<KIND>::value ? xa.hi + (size_t)m * row : nullptr;
+    __half* lo = UsesMma<KIND>::value ? xa.lo + (size_t)m * row : nullptr;
+    float* f32 = (UsesMma<KIND>::value && xa.f32) ? xa.f32 + (size_t)m * K : nullptr;
+    float* sx = UsesMma<KIND>::value ? xa.sumx + (size_t)m * (K >> 5) : nullptr;
+#pragma unroll
+    for (int j = 0; j < XV_MAX; ++j) {
+        if (j < nv) {
+            const int k = j * SG_CTHREADS + threadIdx.x;
+            const bool ok = k < K;                      // uniform per warp: K is a multiple of 32
+            float val = v[j];
+            if (RMS && ok) val = val * inv * nw_s[k];
+            if (UsesMma<KIND>::value) {
+                __half h, l;
+                split_half(val, h, l);
+                if (ok) {
+                    const int i = xh_index<KIND>(k);
+                    hi[i] = h;
+                    lo[i] = l;
+                    if (f32) f32[k] = val;
+                }
+                const float t = warp_sum(ok ? __half2float(h) + __half2float(l) : 0.0f);
+                if (ok && lane == 0) sx[(j * SG_CTHREADS + warp * 32) >> 5] = t;
+            } else if (ok) {
+                xs[xs_index<KIND>(k)] = val;
+            }
+        }
+    }
+    consumer_sync();
+    return extra;
+}
+
+// Dot products of a tile's rows with the staged activations of M tokens into
+// red_pass[part][row][token] (part stride RED_PASSES * RED_PASS floats).
+template <int KIND, int MT>
+__device__ __forceinline__ void tile_compute(const uint8_t* tile, int64_t rb, int rows, int K, const XAct& xa,
+                                             int tok0, int M, float* red_pass, int warp, int lane) {
+    if (UsesMma<KIND>::value) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        XHalf xh = xa.half();
+        xh.hi += (size_t)tok0 * xh.stride;
+        xh.lo += (size_t)tok0 * xh.stride;
+        xh.sumx += (size_t)tok0 * xh.nsub;
+        xh.zero_row -= tok0;
+        if (KIND == 3) tile_dot_q4k(tile, (int)rb, K, xh, M, warp, SG_CONSUMERS, lane, acc);
+        else tile_dot_f16(tile, (int)rb, K, xh, M, warp, SG_CONSUMERS, lane, acc);
+        float* o = red_pass + (size_t)warp * RED_PASSES * RED_PASS;
+        const int gid = lane >> 2, c = 2 * (lane & 3);
+        o[gid * RED_TOK + c] = acc[0];
+        o[gid * RED_TOK + c + 1] = acc[1];
+        o[(gid + 8) * RED_TOK + c] = acc[2];
+        o[(gid + 8) * RED_TOK + c + 1] = acc[3];
+    } else {
+        for (int r = warp; r < rows; r += SG_CONSUMERS) {
+            float acc[MT];
+            row_dot_xs<KIND, MT>(tile + (int64_t)r * rb, xa.xs + (size_t)tok0 * xa.xs_tok, xa.xs_tok, M, K, lane, acc);
+            if (lane < MT && lane < M) {
+                float v = 0.0f;
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+                    if (m == lane) v = acc[m];
+                red_pass[r * RED_TOK + lane] = v;
+            }
+        }
+    }
+}
+
+// Sum of the parts for element (row, token) of one pass.
+template <int KIND>
+__device__ __forceinline__ float red_value(const float* red_pass, int row, int tok) {
+    if (!UsesMma<KIND>::value) return red_pass[row * RED_TOK + tok];
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < SG_CONSUMERS; ++w) v += red_pass[(size_t)w * RED_PASSES * RED_PASS + row * RED_TOK + tok];
+    return v;
+}
+#endif
+
+// ---- host helpers ---------------------------------------------------------------
+template <typename Kern, typename Args>
+static int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, const Args& a) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
+    ++g_kernel_launches;
+    return B200_OK;
+}
+
+template <typename Kern>
+static int allow_smem(Kern kern) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET_FULL));
+    return B200_OK;
+}
+
+// Rows per tile.  Tensor-core kinds: always TILE_ROWS.  Others: about 8 KB, at most
+// TILE_ROWS, a multiple of what keeps every tile (and sub-tile of `align_row_bytes`
+// rows) 16-byte aligned.  Returns -1 when no such count exists.
+static inline int pick_rows(int kind, int64_t bytes_per_row, int64_t align_a, int64_t align_b, int max_rows) {
+    if (kind == 3 || kind == KIND_F16) return TILE_ROWS;
+    int R = (int)std::max<int64_t>(1, 8192 / std::max<int64_t>(1, bytes_per_row));
+    R = std::min(std::min(R, TILE_ROWS), std::max(1, max_rows));
+    for (int r = R; r >= 1; --r)
+        if ((r * align_a) % 16 == 0 && (r * align_b) % 16 == 0) return r;
+    for (int r = R + 1; r <= TILE_ROWS; ++r)
+        if ((r * align_a) % 16 == 0 && (r * align_b) % 16 == 0) return r;
+    return -1;
+}
+
+// Stages of the ring: as many as fit the half-SM budget; when that leaves fewer than
+// three (wide rows), the whole-SM budget is used instead.
+static inline int pick_stages_in(size_t stage_bytes, size_t other_bytes, size_t budget) {
+    int s = SG_MAX_STAGES;
+    while (s > 1 && s * stage_bytes + other_bytes > budget) --s;
+    return (s * stage_bytes + other_bytes <= budget) ? s : 0;
+}
+static inline int pick_stages(size_t stage_bytes, size_t other_bytes) {
+    const int s = pick_stages_in(stage_bytes, other_bytes, SMEM_BUDGET);
+    return s >= 3 ? s : std::max(s, pick_stages_in(stage_bytes, other_bytes, SMEM_BUDGET_FULL));
+}
+
+}  // namespace b200

@@ -82,6 +82,32 @@ int b200_device_count(int* count) {
     B200_CUDA(cudaGetDeviceCount(count));
     return B200_OK;
 }
+int b200_device_info(int* index, char* name, int name_cap, int* cc_major, int* cc_minor,
+                     size_t* total_mem, size_t* free_mem) {
+    static bool selected = false;
+    if (!selected) {
+        // one process per GPU: LOCAL_RANK picks the device, like the reference's probe
+        const char* lr = getenv("LOCAL_RANK");
+        int count = 0;
+        B200_CUDA(cudaGetDeviceCount(&count));
+        if (lr && count > 0) B200_CUDA(cudaSetDevice(atoi(lr) % count));
+        selected = true;
+    }
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    cudaDeviceProp prop;
+    B200_CUDA(cudaGetDeviceProperties(&prop, dev));
+    if (index) *index = dev;
+    if (name && name_cap > 0) snprintf(name, (size_t)name_cap, "%s", prop.name);
+    if (cc_major) *cc_major = prop.major;
+    if (cc_minor) *cc_minor = prop.minor;
+    size_t fr = 0, tot = 0;
+    B200_CUDA(cudaMemGetInfo(&fr, &tot));
+    if (total_mem) *total_mem = tot;
+    if (free_mem) *free_mem = fr;
+    return B200_OK;
+}
+int b200_shutdown(void) { return b200_free_workspaces(); }
 int b200_malloc_device(void** ptr, size_t nbytes) {
     B200_REQUIRE(ptr, "malloc_device: null pointer");
     *ptr = nullptr;

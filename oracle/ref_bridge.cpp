@@ -213,3 +213,119 @@ REF_API int ref_attention_decode_ring(const float* q, const void* kc, const void
                                        pinned, cur_len, cache_max, scale, scratch.data(), window);
     });
 }
+
+// ---------------------------------------------------------------------------
+// Model level: the reference's own Model + Generator, unmodified, on the CPU device
+// (libgai_ref.so) or - when this file is linked into libgai_b200.so with the
+// reference compiled for GAI_CUDA and the B200 shim standing in for its CUDA
+// backend - on the CUDA device.  Generator::decode_step_logits is private; the test
+// bridge reaches it by including the header with private opened up.
+// ---------------------------------------------------------------------------
+#define private public
+#include "inference/generator.h"
+#undef private
+#include "core/quant.h"
+#include "model/model.h"
+#include "tokenizer/tokenizer.h"
+
+#include <memory>
+
+namespace {
+struct RefSession {
+    ModelConfig cfg;
+    std::unique_ptr<Model> model;
+    Tokenizer tok;
+    std::unique_ptr<Generator> gen;
+};
+}  // namespace
+
+// icfg: vocab, hidden, n_layers, n_heads, n_kv, head_dim, rope_type(-1 none),
+//       mamba_heads, mamba_d_head, mamba_d_state, mamba_d_conv, n_experts, top_k,
+//       expert_dim, shared_dim, max_ctx
+// fcfg: rope_theta, rms_eps, embedding_multiplier, residual_multiplier,
+//       attention_multiplier, logits_scaling
+// device: 0 CPU, 1 CUDA; quant_kind: -1 fp32 weights, 0..2 packed (fp16 embeddings)
+REF_API void* ref_model_create(const int* icfg, const float* fcfg, const int* layer_types, int device,
+                               int quant_kind) {
+    RefSession* s = new RefSession();
+    try {
+        ModelConfig& c = s->cfg;
+        c.arch = ModelConfig::ArchGranite;
+        c.vocab_size = icfg[0]; c.hidden_size = icfg[1]; c.num_layers = icfg[2];
+        c.num_heads = icfg[3]; c.num_kv_heads = icfg[4]; c.head_dim_override = icfg[5];
+        c.position_embedding = icfg[6] < 0 ? 1 : 0;
+        c.rope_type = icfg[6] < 0 ? 1 : icfg[6];
+        c.mamba_n_heads = icfg[7]; c.mamba_d_head = icfg[8]; c.mamba_d_state = icfg[9]; c.mamba_d_conv = icfg[10];
+        c.mamba_n_groups = 1;
+        c.mamba_expand = (icfg[7] * icfg[8]) / icfg[1];
+        c.use_moe = true; c.num_experts = icfg[11]; c.moe_top_k = icfg[12]; c.moe_expert_dim = icfg[13];
+        c.moe_shared = icfg[14] > 0; c.shared_expert_intermediate_size = icfg[14];
+        c.max_seq_len = icfg[15];
+        c.tie_embeddings = true;
+        c.rope_theta = fcfg[0]; c.rms_eps = fcfg[1]; c.embedding_multiplier = fcfg[2];
+        c.residual_multiplier = fcfg[3]; c.attention_multiplier = fcfg[4]; c.logits_scaling = fcfg[5];
+        c.layer_types.assign(layer_types, layer_types + c.num_layers);
+        c.validate();
+        s->model.reset(new Model(c, device ? Device::CUDA : Device::CPU, false, quant_kind));
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        delete s;
+        return nullptr;
+    }
+    return s;
+}
+
+REF_API void ref_model_destroy(void* h) { delete static_cast<RefSession*>(h); }
+
+REF_API int ref_model_param_count(void* h) {
+    return static_cast<int>(static_cast<RefSession*>(h)->model->parameters().size());
+}
+
+// name, element count and storage dtype code (DType) of parameter i
+REF_API int ref_model_param_info(void* h, int i, char* name, int cap, i64* numel, int* dtype) {
+    return guarded([&] {
+        Parameter* p = static_cast<RefSession*>(h)->model->parameters().at(static_cast<size_t>(i));
+        std::snprintf(name, static_cast<size_t>(cap), "%s", p->name.c_str());
+        *numel = p->w.numel();
+        *dtype = static_cast<int>(p->w.dtype());
+    });
+}
+
+// Fill a parameter from fp32 host data the way load-time quantisation does
+// (format/gguf_codec.cpp:1495-1500): packed tensors through quant::quantize, fp16
+// tensors through copy_from_f32, fp32 tensors verbatim.
+REF_API int ref_model_set_param(void* h, const char* name, const float* data, i64 n) {
+    return guarded([&] {
+        RefSession* s = static_cast<RefSession*>(h);
+        Parameter* p = s->model->find_parameter(name);
+        GAI_CHECK(p != nullptr, std::string("no such parameter: ") + name);
+        GAI_CHECK(p->w.numel() == n, std::string("element count mismatch for ") + name);
+        Tensor src(p->shape, DType::F32, Device::CPU);
+        std::memcpy(src.data_ptr(), data, sizeof(float) * static_cast<size_t>(n));
+        if (is_quant(p->w)) p->w.copy_from(quant::quantize(src, p->w.dtype()));
+        else if (p->w.dtype() == DType::F16) p->w.copy_from_f32(src);
+        else p->w.copy_from(src);
+    });
+}
+
+REF_API int ref_generator_create(void* h, int max_ctx) {
+    return guarded([&] {
+        RefSession* s = static_cast<RefSession*>(h);
+        s->model->rebuild_rope_cache();
+        s->gen.reset(new Generator(*s->model, s->tok, max_ctx));
+        s->gen->reset();
+    });
+}
+
+REF_API int ref_generator_reset(void* h) {
+    return guarded([&] { static_cast<RefSession*>(h)->gen->reset(); });
+}
+
+// One token through Generator::decode_step (logits copied to the host).
+REF_API int ref_decode_step(void* h, int token, int position, float* logits_out) {
+    return guarded([&] {
+        RefSession* s = static_cast<RefSession*>(h);
+        const float* lp = s->gen->decode_step(token, position);
+        std::memcpy(logits_out, lp, sizeof(float) * static_cast<size_t>(s->cfg.vocab_size));
+    });
+}

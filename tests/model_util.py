@@ -207,3 +207,149 @@ class CudaDecoder:
         if self.handle:
             self.lib.b200_decoder_destroy(self.handle)
             self.handle = None
+
+
+# ---------------------------------------------------------------------------
+# The same model through the reference engine's own Model + Generator
+# ---------------------------------------------------------------------------
+def ref_param_shapes(cfg):
+    """Parameter names and shapes as the reference's Model allocates them
+    (model/model.cpp:1087-1160)."""
+    d, V = cfg["hidden"], cfg["vocab"]
+    hd = cfg["head_dim"]
+    qd, kvd = cfg["n_heads"] * hd, cfg["n_kv"] * hd
+    ne, E, SH = cfg["n_experts"], cfg["expert_dim"], cfg["shared_dim"]
+    d_inner = cfg["mamba_heads"] * cfg["mamba_d_head"]
+    conv_dim = d_inner + 2 * cfg["mamba_d_state"]
+    proj = d_inner + conv_dim + cfg["mamba_heads"]
+    shapes = {"tok_embeddings": (V, d), "final_norm": (d,)}
+    for i, t in enumerate(cfg["layer_types"]):
+        p = f"layers.{i}."
+        shapes[p + "attn_norm"] = (d,)
+        shapes[p + "ffn_norm"] = (d,)
+        if t == 0:
+            shapes[p + "mamba.in_proj"] = (proj, d)
+            shapes[p + "mamba.conv1d.weight"] = (conv_dim, cfg["mamba_d_conv"])
+            shapes[p + "mamba.conv1d.bias"] = (conv_dim,)
+            shapes[p + "mamba.dt_bias"] = (cfg["mamba_heads"],)
+            shapes[p + "mamba.A_log"] = (cfg["mamba_heads"],)
+            shapes[p + "mamba.D"] = (cfg["mamba_heads"],)
+            shapes[p + "mamba.norm.weight"] = (d_inner,)
+            shapes[p + "mamba.out_proj"] = (d, d_inner)
+        else:
+            shapes[p + "wq"] = (qd, d)
+            shapes[p + "wk"] = (kvd, d)
+            shapes[p + "wv"] = (kvd, d)
+            shapes[p + "wo"] = (d, qd)
+        shapes[p + "moe_router"] = (ne, d)
+        shapes[p + "moe_gate"] = (ne * E, d)
+        shapes[p + "moe_up"] = (ne * E, d)
+        shapes[p + "moe_down"] = (ne * d, E)
+        shapes[p + "moe_sh_gate"] = (SH, d)
+        shapes[p + "moe_sh_up"] = (SH, d)
+        shapes[p + "moe_sh_down"] = (d, SH)
+    return shapes
+
+
+def random_f32_params(cfg, seed=0, w_std=0.02):
+    """fp32 source weights keyed by the reference's parameter names."""
+    r = np.random.default_rng(seed)
+    out = {}
+    for name, shape in ref_param_shapes(cfg).items():
+        n = int(np.prod(shape))
+        leaf = name.split(".")[-1] if not name.endswith("norm.weight") else "norm.weight"
+        if "norm" in name and "conv" not in name:
+            a = 1 + 0.1 * r.standard_normal(n)
+        elif leaf == "A_log":
+            a = r.uniform(np.log(1.0), np.log(16.0), n)
+        elif leaf == "dt_bias":
+            a = np.log(np.expm1(r.uniform(1e-3, 1e-1, n)))
+        elif leaf == "D":
+            a = r.standard_normal(n)
+        elif "conv1d" in name:
+            a = r.standard_normal(n) * 0.1
+        elif leaf == "moe_router":
+            a = r.standard_normal(n) / np.sqrt(cfg["hidden"])
+        else:
+            a = r.standard_normal(n) * w_std
+        out[name] = a.astype(np.float32).reshape(shape)
+    return out
+
+
+def model_from_f32(oracle, cfg, params):
+    """The stored-form model (as make_model returns) from fp32 source weights, with
+    the reference's storage policy: packed matrices, fp16 embeddings, fp32 the rest."""
+    q = cfg["qkind"]
+    hd = cfg["head_dim"]
+    m = {"cfg": cfg, "layers": [], "embed": oracle.f32_to_f16(params["tok_embeddings"]),
+         "final_norm": params["final_norm"],
+         "inv_freq": (1.0 / cfg["rope_theta"] ** (np.arange(hd // 2) * 2.0 / hd)).astype(np.float32)}
+    d_inner = cfg["mamba_heads"] * cfg["mamba_d_head"]
+    conv_dim = d_inner + 2 * cfg["mamba_d_state"]
+    for i, t in enumerate(cfg["layer_types"]):
+        p = f"layers.{i}."
+        L = {"type": t, "attn_norm": params[p + "attn_norm"], "ffn_norm": params[p + "ffn_norm"]}
+        if t == 0:
+            L.update(w_in=store_weight(oracle, params[p + "mamba.in_proj"], q),
+                     conv_w=params[p + "mamba.conv1d.weight"], conv_b=params[p + "mamba.conv1d.bias"],
+                     dt_bias=params[p + "mamba.dt_bias"], a_log=params[p + "mamba.A_log"], D=params[p + "mamba.D"],
+                     norm_w=params[p + "mamba.norm.weight"], w_out=store_weight(oracle, params[p + "mamba.out_proj"], q),
+                     d_inner=d_inner, conv_dim=conv_dim)
+        else:
+            for k in ("wq", "wk", "wv", "wo"):
+                L[k] = store_weight(oracle, params[p + k], q)
+        L["router"] = params[p + "moe_router"]
+        L["router_bias"] = None
+        for mine, theirs in (("gate", "moe_gate"), ("up", "moe_up"), ("down", "moe_down"), ("sh_gate", "moe_sh_gate"),
+                             ("sh_up", "moe_sh_up"), ("sh_down", "moe_sh_down")):
+            L[mine] = store_weight(oracle, params[p + theirs], q)
+        m["layers"].append(L)
+    return m
+
+
+class RefGenerator:
+    """The reference's Model + Generator behind oracle/_ref (lib: 'ref' = its CPU
+    device, 'b200' = its CUDA device with this repository's backend linked in)."""
+
+    def __init__(self, cfg, params, max_ctx, lib="ref"):
+        import os
+        from oracle_lib import ROOT
+        path = os.path.join(ROOT, "oracle", "_ref", "libgai_ref.so" if lib == "ref" else "libgai_b200.so")
+        self.lib = C.CDLL(path)
+        self.lib.ref_model_create.restype = C.c_void_p
+        self.lib.ref_last_error.restype = C.c_char_p
+        self.cfg = cfg
+        icfg = np.array([cfg["vocab"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["n_kv"], cfg["head_dim"],
+                         cfg["rope_type"], cfg["mamba_heads"], cfg["mamba_d_head"], cfg["mamba_d_state"],
+                         cfg["mamba_d_conv"], cfg["n_experts"], cfg["top_k"], cfg["expert_dim"], cfg["shared_dim"],
+                         max(max_ctx, 64)], np.int32)
+        fcfg = np.array([cfg["rope_theta"], cfg["rms_eps"], cfg["embedding_multiplier"], cfg["residual_multiplier"],
+                         cfg["attn_scale"], cfg["logits_scaling"]], np.float32)
+        types = np.array(cfg["layer_types"], np.int32)
+        self.h = self.lib.ref_model_create(icfg.ctypes.data_as(C.c_void_p), fcfg.ctypes.data_as(C.c_void_p),
+                                           types.ctypes.data_as(C.c_void_p), 0 if lib == "ref" else 1,
+                                           cfg["qkind"])
+        if not self.h:
+            raise RuntimeError("ref_model_create: " + self.lib.ref_last_error().decode())
+        self.h = C.c_void_p(self.h)
+        for name, a in params.items():
+            a = np.ascontiguousarray(a, np.float32)
+            self._ck(self.lib.ref_model_set_param(self.h, name.encode(), a.ctypes.data_as(C.c_void_p),
+                                                  C.c_int64(a.size)), name)
+        self._ck(self.lib.ref_generator_create(self.h, max_ctx), "generator")
+        self.pos = 0
+
+    def _ck(self, rc, what):
+        if rc != 0:
+            raise RuntimeError(f"{what}: " + self.lib.ref_last_error().decode())
+
+    def step(self, token):
+        out = np.empty(self.cfg["vocab"], np.float32)
+        self._ck(self.lib.ref_decode_step(self.h, int(token), self.pos, out.ctypes.data_as(C.c_void_p)), "decode_step")
+        self.pos += 1
+        return out
+
+    def close(self):
+        if self.h:
+            self.lib.ref_model_destroy(self.h)
+            self.h = None
