@@ -101,6 +101,7 @@ struct XAct {
     float* sumx = nullptr;
     float* f32 = nullptr;      // [tokens][K] natural order, may be null
     int K = 0, tokens = 0;
+    unsigned long long* tr = nullptr;
     __device__ __forceinline__ XHalf half() const {
         XHalf h;
         h.hi = hi; h.lo = lo; h.sumx = sumx; h.stride = K + XH_PAD; h.nsub = K >> 5; h.zero_row = tokens;
@@ -171,7 +172,7 @@ __device__ __forceinline__ void consumer_sum_d2(double& a, double& b, double* re
     for (int w = 0; w < SG_CONSUMERS; ++w) { a += red[w]; b += red[SG_CONSUMERS + w]; }
 }
 
-// Token m's activations from global memory (K floats at x, K <= 256 * XV_MAX) into
+// Token m's activations from global memory (K floats at x) into
 // shared memory.  Each thread keeps its K/256 values in registers, so global memory
 // is read once and one barrier (three with a reduction) separates load from use.
 // RMS: v = x * inv_rms * norm_w in the reference's operand order
@@ -180,58 +181,90 @@ __device__ __forceinline__ void consumer_sum_d2(double& a, double& b, double* re
 // reduction and returned (used for the gated-norm partial sums).  On the tensor-core
 // path the 32 consecutive k of a sub-block sit in one warp, so the sub-block sums
 // are warp shuffles.  Consumer threads only; ends with a consumer barrier.
-constexpr int XV_MAX = 32;
+constexpr int XV_REG = 8;
 template <int KIND, bool RMS, bool EXTRA>
 __device__ __forceinline__ double stage_x(const float* __restrict__ x, const float* nw_s, const XAct& xa, int m,
                                           float eps, double* red, double extra) {
     const int K = xa.K;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nv = (K + SG_CTHREADS - 1) / SG_CTHREADS;
-    float v[XV_MAX];
-    double ss = 0.0;
-#pragma unroll
-    for (int j = 0; j < XV_MAX; ++j) {
-        if (j < nv) {
-            const int k = j * SG_CTHREADS + threadIdx.x;
-            v[j] = k < K ? x[k] : 0.0f;
-            if (RMS) ss += (double)v[j] * v[j];
-        }
-    }
-    float inv = 1.0f;
-    if (RMS || EXTRA) {
-        consumer_sum_d2(ss, extra, red);
-        if (RMS) {
-            const double inv_d = 1.0 / sqrt(ss / (double)K + (double)eps);
-            inv = isfinite(inv_d) ? (float)inv_d : 0.0f;
-        }
-    }
     float* xs = UsesMma<KIND>::value ? nullptr : xa.xs + (size_t)m * xa.xs_tok;
     const size_t row = (size_t)(K + XH_PAD);
     __half* hi = UsesMma<KIND>::value ? xa.hi + (size_t)m * row : nullptr;
     __half* lo = UsesMma<KIND>::value ? xa.lo + (size_t)m * row : nullptr;
     float* f32 = (UsesMma<KIND>::value && xa.f32) ? xa.f32 + (size_t)m * K : nullptr;
     float* sx = UsesMma<KIND>::value ? xa.sumx + (size_t)m * (K >> 5) : nullptr;
-#pragma unroll
-    for (int j = 0; j < XV_MAX; ++j) {
-        if (j < nv) {
-            const int k = j * SG_CTHREADS + threadIdx.x;
-            const bool ok = k < K;                      // uniform per warp: K is a multiple of 32
-            float val = v[j];
-            if (RMS && ok) val = val * inv * nw_s[k];
-            if (UsesMma<KIND>::value) {
-                __half h, l;
-                split_half(val, h, l);
-                if (ok) {
-                    const int i = xh_index<KIND>(k);
-                    hi[i] = h;
-                    lo[i] = l;
-                    if (f32) f32[k] = val;
-                }
-                const float t = warp_sum(ok ? __half2float(h) + __half2float(l) : 0.0f);
-                if (ok && lane == 0) sx[(j * SG_CTHREADS + warp * 32) >> 5] = t;
-            } else if (ok) {
-                xs[xs_index<KIND>(k)] = val;
+    // final value of activation k (k's validity is uniform per warp: K % 32 == 0)
+    auto emit = [&](int j, float val) {
+        const int k = j * SG_CTHREADS + threadIdx.x;
+        const bool ok = k < K;
+        if (UsesMma<KIND>::value) {
+            __half h, l;
+            split_half(val, h, l);
+            if (ok) {
+                const int i = xh_index<KIND>(k);
+                hi[i] = h;
+                lo[i] = l;
+                if (f32) f32[k] = val;
             }
+            const float t = warp_sum(ok ? __half2float(h) + __half2float(l) : 0.0f);
+            if (ok && lane == 0) sx[(j * SG_CTHREADS + warp * 32) >> 5] = t;
+        } else if (ok) {
+            xs[xs_index<KIND>(k)] = val;
+        }
+    };
+    if (!RMS) {
+        if (EXTRA) {
+            double z = 0.0;
+            consumer_sum_d2(extra, z, red);
+        }
+#pragma unroll 4
+        for (int j = 0; j < nv; ++j) {
+            const int k = j * SG_CTHREADS + threadIdx.x;
+            emit(j, k < K ? x[k] : 0.0f);
+        }
+        consumer_sync();
+        return extra;
+    }
+    double ss = 0.0;
+    if (nv <= XV_REG) {
+        // the common case (K <= 2048): the token stays in registers across the reduction
+        float v[XV_REG];
+#pragma unroll
+        for (int j = 0; j < XV_REG; ++j) {
+            const int k = j * SG_CTHREADS + threadIdx.x;
+            v[j] = (j < nv && k < K) ? x[k] : 0.0f;
+            ss += (double)v[j] * v[j];
+        }
+        if (xa.tr) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); xa.tr[5] = t_; }
+        consumer_sum_d2(ss, extra, red);
+        const double inv_d = 1.0 / sqrt(ss / (double)K + (double)eps);
+        const float inv = isfinite(inv_d) ? (float)inv_d : 0.0f;
+        if (xa.tr) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); xa.tr[6] = t_; }
+#pragma unroll
+        for (int j = 0; j < XV_REG; ++j) {
+            if (j < nv) {
+                const int k = j * SG_CTHREADS + threadIdx.x;
+                emit(j, k < K ? v[j] * inv * nw_s[k] : 0.0f);
+            }
+        }
+    } else {
+        // wide rows: raw values parked in shared memory between the two passes
+        float* stash = UsesMma<KIND>::value ? f32 : xs;
+        for (int j = 0; j < nv; ++j) {
+            const int k = j * SG_CTHREADS + threadIdx.x;
+            if (k < K) {
+                const float val = x[k];
+                stash[UsesMma<KIND>::value ? k : xs_index<KIND>(k)] = val;
+                ss += (double)val * val;
+            }
+        }
+        consumer_sum_d2(ss, extra, red);
+        const double inv_d = 1.0 / sqrt(ss / (double)K + (double)eps);
+        const float inv = isfinite(inv_d) ? (float)inv_d : 0.0f;
+        for (int j = 0; j < nv; ++j) {
+            const int k = j * SG_CTHREADS + threadIdx.x;
+            emit(j, k < K ? stash[UsesMma<KIND>::value ? k : xs_index<KIND>(k)] * inv * nw_s[k] : 0.0f);
         }
     }
     consumer_sync();

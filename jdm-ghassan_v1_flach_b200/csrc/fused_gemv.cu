@@ -51,7 +51,7 @@ int stream_status_check(const char* who) {
 // streamed GEMV: y[M,N] = f(x)[M,K] . W^T, M <= 8
 // ===========================================================================
 template <int KIND, int MT, int PRO, int EPI>
-__global__ void __launch_bounds__(SG_THREADS) stream_gemv_kernel(SgArgs a) {
+__global__ void __launch_bounds__(SG_THREADS, 2) stream_gemv_kernel(SgArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     Ring ring;
     ring.stages = smem;
@@ -102,6 +102,7 @@ __global__ void __launch_bounds__(SG_THREADS) stream_gemv_kernel(SgArgs a) {
     TRACE(2);
     pdl_wait();
     TRACE(3);
+    if (tr) xa.tr = a.trace;
     // element (row, token) this thread finishes
     const int e_row = threadIdx.x >> 3, e_m = threadIdx.x & 7;
     float in_scale = 1.0f;
@@ -147,12 +148,10 @@ __global__ void __launch_bounds__(SG_THREADS) stream_gemv_kernel(SgArgs a) {
             }
         }
         if (!ring.wait_full(i)) break;
-        if (i == 0) TRACE(5);
         float* red_pass = red + (size_t)(i & 1) * RED_BUF;
         tile_compute<KIND, MT>(ring.stage(i), a.row_bytes, rows, a.K, xa, 0, a.M, red_pass, warp, lane);
         ring.release(i);
         consumer_sync();
-        if (i == 0) TRACE(6);
         if (owner) {
             float v = red_value<KIND>(red_pass, e_row, e_m) * in_scale;
             const int m = e_m;

@@ -104,7 +104,7 @@ __device__ __forceinline__ void route_finish_warp(const float* __restrict__ logi
 // tiles [0, n_router): ROUTER_ROWS fp32 router rows; then shared tiles: R rows of
 // sh_gate (pass 0) followed by the same R rows of sh_up (pass 1).
 template <int KIND, int MT>
-__global__ void __launch_bounds__(SG_THREADS) moe_phase1_kernel(MoeFusedArgs a) {
+__global__ void __launch_bounds__(SG_THREADS, 2) moe_phase1_kernel(MoeFusedArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     Ring ring;
     ring.stages = smem;
@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(SG_THREADS) moe_phase1_kernel(MoeFusedArgs a) 
 // (idx, w) - every CTA computes the same values, CTA x == 0 publishes them - then
 // streams tiles (k, row tile) of expert idx[k]: R gate rows then R up rows.
 template <int KIND>
-__global__ void __launch_bounds__(SG_THREADS) moe_phase2_kernel(MoeFusedArgs a) {
+__global__ void __launch_bounds__(SG_THREADS, 2) moe_phase2_kernel(MoeFusedArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     Ring ring;
     ring.stages = smem;
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(SG_THREADS) moe_phase2_kernel(MoeFusedArgs a) 
 // each k, by R rows of down[idx[k]] (K = E).  The routed activations are staged as K
 // "tokens" of one activation block so every slot has its own vector.
 template <int KIND>
-__global__ void __launch_bounds__(SG_THREADS) moe_phase3_kernel(MoeFusedArgs a) {
+__global__ void __launch_bounds__(SG_THREADS, 2) moe_phase3_kernel(MoeFusedArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     Ring ring;
     ring.stages = smem;

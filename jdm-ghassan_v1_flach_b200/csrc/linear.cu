@@ -9,7 +9,7 @@
 // each lane dequantises 32-weight units in registers and the row sum is a warp
 // shuffle reduction; every token of the tile reuses the registers.  Larger M walks
 // the same kernel over token tiles of 8 (weights then come from L2).
-#include "linear.cuh"
+#include "fused.cuh"
 
 namespace b200 {
 
@@ -122,6 +122,22 @@ int linear(const float* x, const void* w, int kind, float* y, int M, int K, int 
         else gemv_ragged_kernel<KIND_F16><<<ceil_div(N, 4), 128, 0, stream()>>>(a);
         B200_LAUNCH_CHECK("gemv_ragged_kernel");
         return B200_OK;
+    }
+    // Preferred path: the TMA-streamed kernel (tensor-core dot for Q4_K / fp16 weights),
+    // eight tokens per pass.  Shapes it cannot tile fall through to the plain kernel.
+    if ((reinterpret_cast<uintptr_t>(w) & 15) == 0 && (kind != 3 || K % 256 == 0)) {
+        bool streamed = true;
+        for (int m0 = 0; m0 < M && streamed; m0 += 8) {
+            SgArgs s;
+            s.w = reinterpret_cast<const uint8_t*>(w);
+            s.N = N; s.K = K; s.M = std::min(8, M - m0);
+            s.x = x + (int64_t)m0 * K; s.x_stride = K;
+            s.y = y + (int64_t)m0 * N; s.y_stride = N;
+            const int rc = stream_gemv(s, kind, PRO_NONE, EPI_STORE);
+            if (rc == B200_EUNSUPPORTED && m0 == 0) streamed = false;
+            else if (rc) return rc;
+        }
+        if (streamed) return B200_OK;
     }
     for (int m0 = 0; m0 < M; m0 += 8) {
         GemvArgs a{x + (int64_t)m0 * K, reinterpret_cast<const uint8_t*>(w), y + (int64_t)m0 * N,

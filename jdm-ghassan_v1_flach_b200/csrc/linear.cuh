@@ -90,8 +90,9 @@ __device__ __forceinline__ void load_unit_plain_generic(const uint8_t* row, int 
 
 // Dot products of weight row n with M (<= MT) activation rows.  Lanes split the
 // row's 32-weight units; on return every lane holds the full sums.  Packed weights
-// are rounded through fp16 exactly like the reference's CPU inference path
-// (core/ops.cpp:392), so only the summation order differs from it.
+// enter with their exact dequantised fp32 value, as in the reference's fused CUDA
+// kernel (cuda/kernels.cu:549-598); its CPU path rounds each value through fp16
+// first (core/ops.cpp:392), a 2^-12 relative perturbation per weight.
 // Requires K % 32 == 0 and x 16-byte aligned.
 template <int KIND, int MT>
 __device__ __forceinline__ void gemv_row(const float* __restrict__ x, const uint8_t* __restrict__ w,
@@ -104,7 +105,7 @@ __device__ __forceinline__ void gemv_row(const float* __restrict__ x, const uint
         float wv[32];
         int k_lo, k_hi;
         if constexpr (KIND <= 3) {
-            load_unit<KIND, true>(row, u, wv);
+            load_unit<KIND, false>(row, u, wv);
             unit_k<KIND>(u, k_lo, k_hi);
         } else {
             load_unit_plain<KIND>(row, u, wv);

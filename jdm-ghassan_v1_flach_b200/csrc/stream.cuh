@@ -94,7 +94,7 @@ __device__ __forceinline__ void row_dot_xs(const uint8_t* row, const float* xs, 
     const int U = K >> 5;
     for (int u = lane; u < U; u += 32) {
         float wv[32];
-        if constexpr (KIND <= 3) load_unit<KIND, true>(row, u, wv);
+        if constexpr (KIND <= 3) load_unit<KIND, false>(row, u, wv);
         else load_unit_plain_generic<KIND>(row, u, wv);
         const float* xu = xs + u * XU_STRIDE;
 #pragma unroll

@@ -169,6 +169,18 @@ static inline float dequant_one(const u8* packed, int kind, i64 i) {
     return (float)((const i8*)(blk + 2))[j] * d;
 }
 
+// The weight value a linear layer multiplies with.  Default: rounded through fp16,
+// as the reference's CPU inference path does (core/ops.cpp:335,392).  With rounding
+// switched off it is the exact dequantised value, which is what the reference's
+// fused CUDA kernel (cuda/kernels.cu:549-598) and this repository's kernels use;
+// the two differ by a 2^-12 relative perturbation per weight.
+static bool g_round_weights = true;
+ORA_API void ora_set_weight_rounding(int on) { g_round_weights = on != 0; }
+static inline float weight_value(const u8* packed, int kind, i64 i) {
+    const float v = dequant_one(packed, kind, i);
+    return g_round_weights ? f16_bits_to_f32(f32_to_f16_bits(v)) : v;
+}
+
 // Packed -> fp16, the form the reference's CPU inference path consumes
 // (ops::quant_materialize, core/ops.cpp:304-338).
 ORA_API void ora_dequantize(const void* packed, u16* dst, i64 n, int kind) {
@@ -347,12 +359,37 @@ ORA_API int ora_linear_q4(const float* x, const void* w, float* y, int M, int K,
     for (int n = 0; n < N; ++n) {
         std::vector<float> row((size_t)K);
         const u8* wr = p + (i64)n * row_bytes;
-        for (int k = 0; k < K; ++k) row[k] = f16_bits_to_f32(f32_to_f16_bits(dequant_one(wr, kind, k)));
+        for (int k = 0; k < K; ++k) row[k] = weight_value(wr, kind, k);
         for (int m = 0; m < M; ++m) {
             const float* xa = x + (size_t)m * K;
             float acc = 0.0f;
             for (int k = 0; k < K; ++k) acc += xa[k] * row[k];
             y[(size_t)m * N + n] = acc;
+        }
+    }
+    return 0;
+}
+
+// The same product without the fp16 rounding of each dequantised weight: what the
+// reference's fused CUDA kernel computes (q4_val keeps fp32, cuda/kernels.cu:549-598).
+// The tensor-core kernels are held to this variant tightly and to the rounded CPU
+// variant above within the stated activation tolerance.
+ORA_API int ora_linear_q4_exact(const float* x, const void* w, float* y, int M, int K, int N, int kind) {
+    if (M <= 0 || N <= 0) return 0;
+    const int be = kind_block_elems(kind);
+    if (K % be != 0) return -1;
+    const u8* p = (const u8*)w;
+    const i64 row_bytes = (i64)(K / be) * kind_block_bytes(kind);
+#pragma omp parallel for schedule(static) if ((i64)N * K > 65536)
+    for (int n = 0; n < N; ++n) {
+        std::vector<double> row((size_t)K);
+        const u8* wr = p + (i64)n * row_bytes;
+        for (int k = 0; k < K; ++k) row[k] = (double)dequant_one(wr, kind, k);
+        for (int m = 0; m < M; ++m) {
+            const float* xa = x + (size_t)m * K;
+            double acc = 0.0;
+            for (int k = 0; k < K; ++k) acc += (double)xa[k] * row[k];
+            y[(size_t)m * N + n] = (float)acc;
         }
     }
     return 0;
@@ -403,7 +440,7 @@ static void weight_rows_to_f32(const void* w, int wkind, i64 row0, int rows, int
         for (int r = 0; r < rows; ++r) {
             const u8* wr = p + (row0 + r) * row_bytes;
             for (int k = 0; k < K; ++k)
-                dst[(size_t)r * K + k] = f16_bits_to_f32(f32_to_f16_bits(dequant_one(wr, wkind, k)));
+                dst[(size_t)r * K + k] = weight_value(wr, wkind, k);
         }
     }
 }

@@ -125,6 +125,19 @@ class Oracle(_Base):
         self._call("linear_any", _p(x), _p(w), wkind, _p(y), M, K, N)
         return y
 
+    def set_weight_rounding(self, on):
+        """True (default): linear layers use fp16-rounded dequantised weights like the
+        reference's CPU path; False: the exact dequantised values like its CUDA path."""
+        self.lib.ora_set_weight_rounding(int(bool(on)))
+
+    def linear_exact(self, x, w, kind, M, K, N):
+        """Packed weights without the fp16 rounding of each weight, double accumulation."""
+        x = _f32(x)
+        w = _wt(w, kind)
+        y = np.empty((M, N), np.float32)
+        self._call("linear_q4_exact", _p(x), _p(w), _p(y), M, K, N, kind)
+        return y
+
     # --- small ops ---------------------------------------------------------
     def embedding(self, ids, table, half, dim, vocab):
         ids = _i32(ids)
