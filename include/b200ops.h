@@ -175,6 +175,24 @@ int b200_attention_decode_ring_fp16(const float* q, const uint16_t* kc, const ui
 int b200_attention_decode_paged_fp16(const float* q, const uint16_t* k_pages, const uint16_t* v_pages,
                                      const int32_t* page_table, const int32_t* seq_lens, float* out,
                                      int batch, int max_pages, int page, int H, int KV, int hd, float scale);
+/* No counterpart in the reference.  b200_attention_decode_ring_fp16 for hosts that
+ * must not allocate device memory on the decode path (an application that gave the
+ * whole GPU to its own pool, a thread that cannot afford the device-wide
+ * synchronisation of cudaMalloc/cudaFree, a process in which another thread is
+ * capturing a stream).  The split-KV partial results go to a 1 MiB array built into
+ * the library (resident on every GPU that loads it until the process exits) instead
+ * of the growing workspace; the call performs no cudaMalloc / cudaFree and uses no
+ * allocating library routine.  Limits: H * (hd + 2) <= 262144 floats, otherwise
+ * B200_EINVAL with a message naming the allocating entry point.  The first call on
+ * each device resolves the array's device address (make it before any stream
+ * capture).  All calls share the one array, which keeps the previous call's partial
+ * results (nothing in it has to start at zero: every record read is written first by
+ * the same call); two calls whose kernels overlap on the GPU - different streams,
+ * no ordering - race on it.  Same arguments as the ring fp16 entry point without
+ * `scratch`. */
+int b200_attention_decode_ring_fp16_noalloc(const float* q, const uint16_t* kc, const uint16_t* vc, float* out,
+                                            int H, int KV, int hd, int ring_start, int pinned_prefix,
+                                            int cur_len, int cache_max, float scale, int window);
 
 /* ---- sampling tail: cuda_ops.h:289-293 ------------------------------------------ */
 int b200_topk_select(const float* logits, int V, int K, float* out_vals, int32_t* out_ids);  /* :289; outputs on device */

@@ -389,3 +389,91 @@ int b200_attention_forward_ex(const float* q, const float* k, const float* v, fl
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// Some hosts of this library cannot tolerate a cudaMalloc on the decode path: a
+// serving loop that has handed the whole device to its own pool allocator, a
+// latency-critical thread where the implicit device synchronisation of cudaMalloc /
+// cudaFree is unacceptable, or code running while another thread captures a stream.
+// The regular entry points keep their split-KV partial results in a workspace that
+// grows with cudaMalloc on demand; this variant keeps them in a fixed array that is
+// part of the library image instead, so it never allocates and never frees.
+//
+// The array lives in device memory of every GPU that loads the library, from load
+// to exit (NOALLOC_FLOATS * 4 bytes = 1 MiB).  Its name is only a host-side handle;
+// the device address is looked up once per device with cudaGetSymbolAddress and that
+// pointer is what the kernels receive.
+// ---------------------------------------------------------------------------
+namespace b200 {
+constexpr int NOALLOC_FLOATS = 256 * 1024;
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static __device__ __align__(256) float g_noalloc_partials[NOALLOC_FLOATS];
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES];   // device address of the array, per device
+}  // namespace b200
+
+extern "C" int b200_attention_decode_ring_fp16_noalloc(const float* q, const uint16_t* kc, const uint16_t* vc,
+                                                       float* out, int H, int KV, int hd, int ring_start,
+                                                       int pinned_prefix, int cur_len, int cache_max,
+                                                       float scale, int window) {
+    const char* who = "attention_decode_ring_fp16_noalloc";
+    // same argument checks as the allocating entry point
+    B200_REQUIRE(H > 0 && KV > 0 && hd > 0, "%s: empty shape", who);
+    B200_REQUIRE(H % KV == 0, "%s: H must be a multiple of KV", who);
+    B200_REQUIRE(cur_len >= 0 && cache_max >= 0 && cur_len <= cache_max, "%s: length exceeds cache capacity", who);
+    B200_REQUIRE(pinned_prefix >= 0 && pinned_prefix <= cur_len, "%s: pinned prefix out of range", who);
+    const int ring_cap = cache_max - pinned_prefix;
+    if (cur_len > pinned_prefix) {
+        B200_REQUIRE(ring_cap > 0, "%s: ring has no rolling slots", who);
+        B200_REQUIRE(ring_start >= 0 && ring_start < ring_cap, "%s: ring start out of range", who);
+    }
+    B200_REQUIRE(q && kc && vc && out, "%s: null pointer", who);
+    int rc = check_hd(who, hd);
+    if (rc) return rc;
+    // The fixed scratch bounds the problem: at least one split of (hd + 2) floats per head.
+    B200_REQUIRE((int64_t)H * (hd + 2) <= NOALLOC_FLOATS,
+                 "%s: H * (head_dim + 2) = %lld floats exceeds the built-in scratch of %d floats; use "
+                 "attention_decode_ring_fp16 for this shape", who, (long long)H * (hd + 2), NOALLOC_FLOATS);
+
+    // One-time set-up per device, with that device current: resolve the array's device
+    // address.  This first call should happen outside any stream capture.
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, "%s: device index %d not supported", who, dev);
+    if (!g_noalloc_ptr[dev]) {
+        float* p = nullptr;
+        B200_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_partials));
+        g_noalloc_ptr[dev] = p;
+    }
+
+    DecodeArgs a{};
+    a.q = q; a.kc = kc; a.vc = vc;
+    a.H = H; a.KV = KV; a.hd = hd; a.group = H / KV;
+    a.cur_len = cur_len;
+    a.j0 = (window > 0 && cur_len > window) ? cur_len - window : 0;
+    a.ring_start = ring_start; a.pinned = pinned_prefix; a.ring_cap = ring_cap > 0 ? ring_cap : 1;
+    a.scale = scale;
+    const int span = std::max(cur_len - a.j0, 1);
+    // Splits as in the allocating path, then capped to what the array holds.  Every
+    // (head, split) record the merge kernel reads is written by the split kernel first,
+    // so nothing in the array needs clearing between calls.
+    const int gblocks = ceil_div(a.group, ATT_GMAX);
+    const int want = std::max(1, (4 * num_sms()) / std::max(1, a.KV * gblocks));
+    const int cap = (int)(NOALLOC_FLOATS / ((int64_t)H * (hd + 2)));
+    a.splits = std::max(1, std::min(std::min(want, cap), ceil_div(span, 32)));
+    a.chunk = std::max(1, ceil_div(span, a.splits));
+    a.splits = std::max(1, ceil_div(span, a.chunk));
+    a.part = g_noalloc_ptr[dev];
+    const dim3 grid(a.splits, a.KV * gblocks, 1);
+    switch (hd / 32) {
+        case 1: attn_decode_split_kernel<1, true, false><<<grid, ATT_WARPS * 32, 0, stream()>>>(a); break;
+        case 2: attn_decode_split_kernel<2, true, false><<<grid, ATT_WARPS * 32, 0, stream()>>>(a); break;
+        case 4: attn_decode_split_kernel<4, true, false><<<grid, ATT_WARPS * 32, 0, stream()>>>(a); break;
+        default: attn_decode_split_kernel<8, true, false><<<grid, ATT_WARPS * 32, 0, stream()>>>(a); break;
+    }
+    B200_LAUNCH_CHECK("attn_decode_split_kernel");
+    attn_decode_merge_kernel<<<dim3(a.H, 1), std::min(a.hd, 256), 0, stream()>>>(a.part, out, a.H, a.hd, a.splits);
+    B200_LAUNCH_CHECK("attn_decode_merge_kernel");
+    return B200_OK;
+}
