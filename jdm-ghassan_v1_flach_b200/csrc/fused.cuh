@@ -1,4 +1,4 @@
-// Host interface of the fused decode-step kernels (fused.cu).
+// Host interface of the fused decode-step kernels (fused_gemv.cu, fused_moe.cu).
 #pragma once
 
 #include "stream.cuh"
@@ -37,7 +37,6 @@ struct SgArgs {
     int rows_per_tile = 0, num_tiles = 0, stage_bytes = 0, n_stages = 0;
     int64_t row_bytes = 0;
     int* status = nullptr;
-    unsigned long long* trace = nullptr;
 };
 
 int stream_gemv(SgArgs a, int kind, int pro, int epi);

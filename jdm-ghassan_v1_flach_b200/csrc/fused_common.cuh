@@ -101,7 +101,6 @@ struct XAct {
     float* sumx = nullptr;
     float* f32 = nullptr;      // [tokens][K] natural order, may be null
     int K = 0, tokens = 0;
-    unsigned long long* tr = nullptr;
     __device__ __forceinline__ XHalf half() const {
         XHalf h;
         h.hi = hi; h.lo = lo; h.sumx = sumx; h.stride = K + XH_PAD; h.nsub = K >> 5; h.zero_row = tokens;
@@ -236,11 +235,9 @@ __device__ __forceinline__ double stage_x(const float* __restrict__ x, const flo
             v[j] = (j < nv && k < K) ? x[k] : 0.0f;
             ss += (double)v[j] * v[j];
         }
-        if (xa.tr) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); xa.tr[5] = t_; }
         consumer_sum_d2(ss, extra, red);
         const double inv_d = 1.0 / sqrt(ss / (double)K + (double)eps);
         const float inv = isfinite(inv_d) ? (float)inv_d : 0.0f;
-        if (xa.tr) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); xa.tr[6] = t_; }
 #pragma unroll
         for (int j = 0; j < XV_REG; ++j) {
             if (j < nv) {

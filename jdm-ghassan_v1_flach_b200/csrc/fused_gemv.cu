@@ -20,22 +20,6 @@ int* stream_status_ptr() {
     }
     return g_status_dev;
 }
-static unsigned long long* g_trace_dev = nullptr;
-static int g_trace_n = 0;
-unsigned long long* trace_slot() {
-    static int on = -1;
-    if (on < 0) on = getenv("B200_TRACE") ? 1 : 0;
-    if (!on) return nullptr;
-    if (!g_trace_dev) { cudaMalloc(&g_trace_dev, 4096 * 8 * 8); cudaMemset(g_trace_dev, 0, 4096 * 8 * 8); }
-    unsigned long long* p = g_trace_dev + (size_t)(g_trace_n % 4096) * 8;
-    ++g_trace_n;
-    return p;
-}
-extern "C" int b200_debug_trace_read(unsigned long long* host, int* n) {
-    *n = g_trace_n < 4096 ? g_trace_n : 4096;
-    if (g_trace_dev) cudaMemcpy(host, g_trace_dev, 4096 * 8 * 8, cudaMemcpyDeviceToHost);
-    return 0;
-}
 int stream_status_check(const char* who) {
     if (!g_status_dev) return B200_OK;
     int h = 0;
@@ -70,11 +54,7 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemv_kernel(SgArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int first = blockIdx.x, step = gridDim.x;
     const int n_my = first < a.num_tiles ? (a.num_tiles - first + step - 1) / step : 0;
-    const bool tr = a.trace && blockIdx.x == 0 && threadIdx.x == 0;
-#define TRACE(i) do { if (tr) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.trace[i] = t_; } } while (0)
-    TRACE(0);
     ring.init();
-    TRACE(1);
     if (threadIdx.x == 0) pdl_launch_dependents();
 
     if (warp == SG_CONSUMERS) {
@@ -99,10 +79,7 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemv_kernel(SgArgs a) {
     if (PRO == PRO_RMS)
         for (int k = threadIdx.x; k < a.K; k += SG_CTHREADS) nw_s[k] = a.norm_w[k];
     xact_zero_row<KIND>(xa);
-    TRACE(2);
     pdl_wait();
-    TRACE(3);
-    if (tr) xa.tr = a.trace;
     // element (row, token) this thread finishes
     const int e_row = threadIdx.x >> 3, e_m = threadIdx.x & 7;
     float in_scale = 1.0f;
@@ -120,7 +97,6 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemv_kernel(SgArgs a) {
         }
     }
 
-    TRACE(4);
     for (int i = 0; i < n_my; ++i) {
         const int tile = first + i * step;
         const int rows = min(a.rows_per_tile, a.N - tile * a.rows_per_tile);
@@ -200,8 +176,6 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemv_kernel(SgArgs a) {
             }
         }
     }
-    TRACE(7);
-#undef TRACE
 }
 
 // ===========================================================================
@@ -323,7 +297,6 @@ int stream_gemv(SgArgs a, int kind, int pro, int epi) {
     a.num_tiles = ceil_div(a.N, R);
     a.stage_bytes = (int)((R * a.row_bytes + 127) / 128 * 128);
     a.status = stream_status_ptr();
-    a.trace = trace_slot();
     B200_REQUIRE(a.status, "stream_gemv: status word allocation failed");
     B200_REQUIRE((reinterpret_cast<uintptr_t>(a.w) & 15) == 0, "stream_gemv: weights must be 16-byte aligned");
     const int grid = std::min(a.num_tiles, num_sms());

@@ -1,0 +1,75 @@
+"""Generates the golden fixtures of this directory from the reference engine's own
+compiled CPU code (oracle/_ref/libgai_ref.so, built by `make -C oracle` where the
+reference sources are mounted).  Run from the repository root:
+
+    python tests/golden/make_golden.py
+
+ops.npz    per case of tests/golden_ops.py: "<case>/in/<name>" (the inputs) and
+           "<case>/out/<name>" (what the reference's CPU objects returned).
+model.npz  a two-layer hybrid model (Mamba-2 layer + GQA layer, MoE after each) in
+           its stored form (Q8_0 matrices, fp16 embeddings), a token sequence, and the
+           logits the reference's Model + Generator produced for each token on its
+           CPU device from the same fp32 source weights.
+
+The fixtures are read by tests/test_golden.py; nothing at test time needs the
+reference sources.
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+
+from golden_ops import all_cases                                     # noqa: E402
+from model_util import RefGenerator, model_from_f32, random_f32_params   # noqa: E402
+from oracle_lib import OracleOnly, Ref                               # noqa: E402
+
+GOLDEN_MODEL = dict(vocab=96, hidden=64, n_layers=2, layer_types=[0, 1],
+                    n_heads=2, n_kv=1, head_dim=32, rope_type=1, rope_theta=1e4,
+                    mamba_heads=2, mamba_d_head=32, mamba_d_state=32, mamba_d_conv=4,
+                    n_experts=4, top_k=2, expert_dim=32, shared_dim=32, qkind=2,
+                    rms_eps=1e-5, embedding_multiplier=12.0, residual_multiplier=0.22,
+                    attn_scale=0.0078125, logits_scaling=6.0)
+GOLDEN_TOKENS = [5, 17, 0, 95, 42, 42, 7, 63, 1, 30]
+MODEL_ARRAYS = ("embed", "final_norm", "inv_freq")
+
+
+def make_ops(oracle, ref):
+    out = {}
+    for case in all_cases(oracle):
+        for k, v in case["inputs"].items():
+            out[f"{case['name']}/in/{k}"] = np.asarray(v)
+        for k, v in case["cpu"](ref, case["inputs"]).items():
+            out[f"{case['name']}/out/{k}"] = np.asarray(v)
+    return out
+
+
+def make_model(oracle):
+    cfg = GOLDEN_MODEL
+    params = random_f32_params(cfg, seed=11)
+    gen = RefGenerator(cfg, params, max_ctx=16)
+    logits = np.stack([gen.step(t) for t in GOLDEN_TOKENS])
+    gen.close()
+    m = model_from_f32(oracle, cfg, params)
+    out = {"tokens": np.array(GOLDEN_TOKENS, np.int32), "logits": logits}
+    for k in MODEL_ARRAYS:
+        out[k] = m[k]
+    for i, L in enumerate(m["layers"]):
+        for k, v in L.items():
+            if isinstance(v, np.ndarray):
+                out[f"layer{i}/{k}"] = v
+    return out
+
+
+def main():
+    oracle, ref = OracleOnly(), Ref()
+    np.savez_compressed(os.path.join(HERE, "ops.npz"), **make_ops(oracle, ref))
+    np.savez_compressed(os.path.join(HERE, "model.npz"), **make_model(oracle))
+    for f in ("ops.npz", "model.npz"):
+        print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
+
+
+if __name__ == "__main__":
+    main()
