@@ -38,6 +38,11 @@ const char* b200_last_error(void);
 int b200_version(void);
 /* Kernels this library has enqueued so far in this process (a graph replay is not counted). */
 uint64_t b200_kernel_launches(void);
+/* Waits inside the TMA / tensor-core kernels are bounded: a kernel whose wait runs out
+ * raises a device status word, skips its stores and returns.  This call synchronises the
+ * device, reads the word back, clears it, and returns B200_OK or B200_ECUDA.  (The
+ * reference has no such waits; b200_synchronize and b200_decoder_step_host check too.) */
+int b200_stream_status(void);
 
 /* ---- device utilities: gai::cuda::*, cuda/cuda_utils.h:14-33 ------------------ */
 int b200_device_count(int* count);                       /* probe(), :14 */

@@ -62,8 +62,10 @@ int b200_decoder_set_tensor(b200_decoder* dec, int layer, int tensor_id, const v
 int b200_decoder_reset(b200_decoder* dec);
 /* fused = 0: one library op per reference op call, in the reference's order.
  * fused = 1: cross-op fusions (norm into the following projection's prologue,
- * residual add into the epilogue).  use_graph = 1 captures the step once and
- * replays it. */
+ * residual add into the epilogue); returns B200_EUNSUPPORTED, leaving the mode
+ * unchanged, when a matrix of the model cannot be cut into 16-byte-aligned row
+ * tiles (the per-op mode has no such limit).  use_graph = 1 captures the step
+ * once and replays it. */
 int b200_decoder_configure(b200_decoder* dec, int fused, int use_graph);
 /* One token per sequence.  tokens_dev [batch] int32 in; next_dev [batch] int32 out
  * (greedy arg-max of the logits); both device pointers; no host synchronisation. */

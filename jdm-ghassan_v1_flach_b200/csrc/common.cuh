@@ -54,6 +54,11 @@ static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 int num_sms();
 
+// Status word of the kernels with bounded waits (0 = ok).  Device pointer, allocated
+// on first use; the check reads it back (synchronising copy) and clears it.
+int* stream_status_ptr();
+int stream_status_check(const char* who);
+
 // ---- device helpers -------------------------------------------------------
 #ifdef __CUDACC__
 __device__ __forceinline__ float warp_sum(float v) {

@@ -37,6 +37,7 @@ struct SgArgs {
     int rows_per_tile = 0, num_tiles = 0, stage_bytes = 0, n_stages = 0;
     int64_t row_bytes = 0;
     int* status = nullptr;
+    bool dry = false;               // validate shapes and tiling, launch nothing
 };
 
 int stream_gemv(SgArgs a, int kind, int pro, int epi);
@@ -66,6 +67,7 @@ struct MoeFusedArgs {
     // filled per phase
     int rows_per_tile = 0, stage_bytes = 0, n_stages = 0;
     int* status = nullptr;
+    bool dry = false;               // validate shapes and tiling, launch nothing
 };
 int moe_fused(MoeFusedArgs a, int kind);
 

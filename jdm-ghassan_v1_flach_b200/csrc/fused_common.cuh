@@ -317,6 +317,7 @@ __device__ __forceinline__ float red_value(const float* red_pass, int row, int t
 // ---- host helpers ---------------------------------------------------------------
 template <typename Kern, typename Args>
 static int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, const Args& a) {
+    if (a.dry) return B200_OK;          // shape check only: everything up to the launch has passed
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -350,6 +351,13 @@ static inline int pick_rows(int kind, int64_t bytes_per_row, int64_t align_a, in
     for (int r = R + 1; r <= TILE_ROWS; ++r)
         if ((r * align_a) % 16 == 0 && (r * align_b) % 16 == 0) return r;
     return -1;
+}
+
+// A bulk copy moves a multiple of 16 bytes: the last, shorter tile of `total_rows`
+// rows must keep that property too (for each of the row sizes a tile carries).
+static inline bool tail_tile_ok(int total_rows, int R, int64_t bytes_a, int64_t bytes_b = 0) {
+    const int tail = total_rows % R;
+    return (tail * bytes_a) % 16 == 0 && (tail * bytes_b) % 16 == 0;
 }
 
 // Stages of the ring: as many as fit the half-SM budget; when that leaves fewer than

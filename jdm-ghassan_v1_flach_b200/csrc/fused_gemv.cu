@@ -292,7 +292,8 @@ int stream_gemv(SgArgs a, int kind, int pro, int epi) {
     a.row_bytes = row_bytes_of(kind, a.K);
     const int R = pick_rows(kind, a.row_bytes, a.row_bytes, a.row_bytes, a.N);
     if (R < 1) return fail(B200_EUNSUPPORTED, "stream_gemv: row size %lld cannot be tiled to 16 bytes", (long long)a.row_bytes);
-    B200_REQUIRE((R * a.row_bytes) % 16 == 0, "stream_gemv: row size %lld is not 16-byte tileable", (long long)a.row_bytes);
+    if ((R * a.row_bytes) % 16 != 0 || !tail_tile_ok(a.N, R, a.row_bytes))
+        return fail(B200_EUNSUPPORTED, "stream_gemv: %d rows of %lld bytes cannot be tiled to 16 bytes", a.N, (long long)a.row_bytes);
     a.rows_per_tile = R;
     a.num_tiles = ceil_div(a.N, R);
     a.stage_bytes = (int)((R * a.row_bytes + 127) / 128 * 128);
@@ -338,3 +339,9 @@ int mamba_scan_norm(const float* bc, const float* dt_raw, const float* gate, con
 }
 
 }  // namespace b200
+
+extern "C" int b200_stream_status(void) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return b200::cuda_status(e, "stream_status: synchronize");
+    return b200::stream_status_check("stream_status");
+}

@@ -416,7 +416,7 @@ static int moe_fused_kind(MoeFusedArgs a) {
     {
         MoeFusedArgs p1 = a;
         const int R = pick_rows(KIND, 2 * rb_d, rb_d, rb_d, std::max(a.SH, 1));
-        if (R < 1) return fail(B200_EUNSUPPORTED, "moe_fused: row size cannot be tiled to 16 bytes");
+        if (R < 1 || !tail_tile_ok(a.SH, R, rb_d)) return fail(B200_EUNSUPPORTED, "moe_fused: row size cannot be tiled to 16 bytes");
         p1.rows_per_tile = R;
         const size_t stage = std::max<size_t>((size_t)ROUTER_ROWS * a.d * 4, (size_t)2 * R * rb_d);
         p1.stage_bytes = (int)((stage + 127) / 128 * 128);
@@ -442,7 +442,7 @@ static int moe_fused_kind(MoeFusedArgs a) {
     {
         MoeFusedArgs p2 = a;
         const int R = pick_rows(KIND, 2 * rb_d, rb_d, rb_d, a.E);
-        if (R < 1) return fail(B200_EUNSUPPORTED, "moe_fused: row size cannot be tiled to 16 bytes");
+        if (R < 1 || !tail_tile_ok(a.E, R, rb_d)) return fail(B200_EUNSUPPORTED, "moe_fused: row size cannot be tiled to 16 bytes");
         p2.rows_per_tile = R;
         p2.stage_bytes = (int)(((size_t)2 * R * rb_d + 127) / 128 * 128);
         const size_t other = xact_bytes<KIND>(a.d, 1, true) + (size_t)a.d * 4 + (size_t)2 * a.ne * 4 + 128 + 16 + fixed;
@@ -461,7 +461,7 @@ static int moe_fused_kind(MoeFusedArgs a) {
         MoeFusedArgs p3 = a;
         const int64_t per_row = rb_sh + (int64_t)a.K * rb_e;
         const int R = pick_rows(KIND, per_row, rb_e, rb_sh > 0 ? rb_sh : rb_e, a.d);
-        if (R < 1 || (R * rb_e) % 16 != 0 || (R * rb_sh) % 16 != 0)
+        if (R < 1 || (R * rb_e) % 16 != 0 || (R * rb_sh) % 16 != 0 || !tail_tile_ok(a.d, R, rb_e, rb_sh))
             return fail(B200_EUNSUPPORTED, "moe_fused: row size cannot be tiled to 16 bytes");
         p3.rows_per_tile = R;
         p3.stage_bytes = (int)(((size_t)R * per_row + 127) / 128 * 128);

@@ -1,0 +1,29 @@
+// Host interface of the tensor-core GEMM (gemm_umma.cu).
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+enum { GEMM_EPI_STORE = 0, GEMM_EPI_SWIGLU = 1 };
+
+// From this many activation rows on, linear layers over fp16 or packed weights run
+// on the tensor cores (activations rounded to fp16, as the reference's cuBLAS path
+// does); below it they stream the weights once through the GEMV kernels in fp32.
+constexpr int GEMM_MIN_ROWS = 32;
+
+// dst[r, :] = fp16(src[(row_map ? row_map[r] / div : r), :]); K % 8 == 0.
+int pack_rows_f16(const float* src, const int32_t* row_map, int div, __half* dst, int64_t rows, int K);
+
+// C = A . B^T on tcgen05.  A [a_rows, K] fp16, B (and B2) [b_rows, K] fp16, fp32
+// accumulation.  Rows of A form `groups` consecutive ranges given by the device
+// array offsets[groups + 1] (null: one group of all M rows); range g uses rows
+// [g*N, (g+1)*N) of B.
+//   GEMM_EPI_STORE   c[row, n]   = scale * acc                      (fp32, ld = ldc)
+//   GEMM_EPI_SWIGLU  c16[row, n] = silu(A.B^T) * (A.B2^T)           (fp16, ld = ldc)
+int umma_gemm(int epi, const __half* A, int64_t a_rows, const __half* B, const __half* B2, int64_t b_rows,
+              const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc, float scale);
+
+}  // namespace b200

@@ -10,6 +10,7 @@
 // shuffle reduction; every token of the tile reuses the registers.  Larger M walks
 // the same kernel over token tiles of 8 (weights then come from L2).
 #include "fused.cuh"
+#include "gemm.cuh"
 
 namespace b200 {
 
@@ -122,6 +123,28 @@ int linear(const float* x, const void* w, int kind, float* y, int M, int K, int 
         else gemv_ragged_kernel<KIND_F16><<<ceil_div(N, 4), 128, 0, stream()>>>(a);
         B200_LAUNCH_CHECK("gemv_ragged_kernel");
         return B200_OK;
+    }
+    // Many tokens over fp16 or packed weights: tensor-core GEMM on fp16 copies of the
+    // activations and (for packed kinds) of the weights.  fp32 weights stay on the
+    // exact fp32 path.
+    if (M >= GEMM_MIN_ROWS && kind != KIND_F32 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && N % 4 == 0 &&
+        (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
+        const size_t a_bytes = ((size_t)M * K * 2 + 255) & ~(size_t)255;
+        const size_t b_bytes = kind == KIND_F16 ? 0 : (size_t)N * K * 2;
+        void* ws;
+        int rc = workspace(WS_LINEAR).ensure(a_bytes + b_bytes + 256, &ws);
+        if (rc) return rc;
+        __half* a16 = static_cast<__half*>(ws);
+        rc = pack_rows_f16(x, nullptr, 1, a16, M, K);
+        if (rc) return rc;
+        const __half* b16 = static_cast<const __half*>(w);
+        if (kind != KIND_F16) {
+            uint16_t* scratch = reinterpret_cast<uint16_t*>(static_cast<char*>(ws) + a_bytes);
+            rc = dequantize(static_cast<const uint8_t*>(w), scratch, (int64_t)N * K, kind);
+            if (rc) return rc;
+            b16 = reinterpret_cast<const __half*>(scratch);
+        }
+        return umma_gemm(GEMM_EPI_STORE, a16, M, b16, nullptr, N, nullptr, 1, M, N, K, y, nullptr, N, 1.0f);
     }
     // Preferred path: the TMA-streamed kernel (tensor-core dot for Q4_K / fp16 weights),
     // eight tokens per pass.  Shapes it cannot tile fall through to the plain kernel.

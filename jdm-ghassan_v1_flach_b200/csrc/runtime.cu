@@ -149,7 +149,7 @@ int b200_copy(void* dst, int dst_is_device, const void* src, int src_is_device, 
 }
 int b200_synchronize(void) {
     B200_CUDA(cudaDeviceSynchronize());
-    return B200_OK;
+    return b200::stream_status_check("synchronize");    // surfaces a bounded wait that ran out
 }
 int b200_free_bytes_live(size_t* bytes) {
     B200_REQUIRE(bytes, "free_bytes_live: null pointer");

@@ -213,7 +213,8 @@ static int enqueue_step(b200_decoder* dec, const int32_t* tokens, int32_t* next)
 // projection, the Mamba conv step inside in_proj's epilogue and the gated norm is
 // folded into the state update + out_proj.  Kernels are chained with programmatic
 // dependent launch so each one streams its weights while its predecessor drains.
-static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t* next) {
+// dry = true walks the same calls but only validates shapes and tiling (no launch).
+static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t* next, bool dry = false) {
     const int B = dec->batch, d = dec->d;
     cudaStream_t st = stream();
     const int kind = tag_of_qkind(dec->qkind);
@@ -223,10 +224,12 @@ static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t*
         rc = (call);            \
         if (rc) return rc;      \
     } while (0)
-    step_begin_kernel<<<ceil_div(B, 128), 128, 0, st>>>(dec->len, dec->pos, B);
-    B200_LAUNCH_CHECK("step_begin_kernel");
-    STEP(b200_embedding_forward_half(tokens, dec->embed, dec->x, B, d, dec->vocab));
-    if (dec->emb_mult != 1.0f) STEP(b200_scale_inplace(dec->x, dec->emb_mult, (int64_t)B * d));
+    if (!dry) {
+        step_begin_kernel<<<ceil_div(B, 128), 128, 0, st>>>(dec->len, dec->pos, B);
+        B200_LAUNCH_CHECK("step_begin_kernel");
+        STEP(b200_embedding_forward_half(tokens, dec->embed, dec->x, B, d, dec->vocab));
+        if (dec->emb_mult != 1.0f) STEP(b200_scale_inplace(dec->x, dec->emb_mult, (int64_t)B * d));
+    }
     const int res_grid = std::min(ceil_div(B * d, 256), num_sms() * 8);
     MambaDims p;
     p.d = d; p.d_inner = dec->d_inner; p.conv_dim = dec->conv_dim; p.n_heads = dec->mh; p.d_head = dec->mdh;
@@ -234,6 +237,7 @@ static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t*
     auto base = [&](const void* w, int N, int K, const float* x, int xs) {
         SgArgs a;
         a.w = static_cast<const uint8_t*>(w); a.N = N; a.K = K; a.M = B; a.x = x; a.x_stride = xs; a.eps = dec->eps;
+        a.dry = dry;
         return a;
     };
     for (int l = 0; l < dec->n_layers; ++l) {
@@ -243,8 +247,9 @@ static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t*
             a.norm_w = w.attn_norm; a.p = p; a.conv_w = w.conv_w; a.conv_b = w.conv_b; a.conv_state = w.conv_state;
             a.gate = dec->f_gate; a.bc = dec->f_bc; a.dt_raw = dec->f_dt;
             STEP(stream_gemv(a, kind, PRO_RMS, EPI_INPROJ));
-            STEP(mamba_scan_norm(dec->f_bc, dec->f_dt, dec->f_gate, w.dt_bias, w.a_log, w.D, w.mamba_norm, w.ssm_state,
-                                 dec->f_u, dec->f_partials, B, p));
+            if (!dry)
+                STEP(mamba_scan_norm(dec->f_bc, dec->f_dt, dec->f_gate, w.dt_bias, w.a_log, w.D, w.mamba_norm,
+                                     w.ssm_state, dec->f_u, dec->f_partials, B, p));
             SgArgs c = base(w.mamba_out, d, dec->d_inner, dec->f_u, dec->d_inner);
             c.in_partials = dec->f_partials; c.n_partials = dec->f_blocks; c.in_dim = dec->d_inner;
             c.resid = dec->x; c.y_stride = d; c.res_mult = dec->res_mult;
@@ -260,16 +265,18 @@ static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t*
             SgArgs av = base(w.wv, kvd, d, dec->x, d);
             av.norm_w = w.attn_norm; av.y = dec->v; av.y_stride = kvd;
             STEP(stream_gemv(av, kind, PRO_RMS, EPI_STORE));
-            if (dec->rope_type >= 0)
-                STEP(b200_rope_forward_cached(dec->q, dec->k, dec->pos, dec->inv_freq, B, dec->H, dec->KV, dec->hd,
-                                              dec->rope_type));
-            kv_append_kernel<<<dim3(ceil_div(kvd, 256), B), 256, 0, st>>>(dec->k, dec->v, w.k_pages, w.v_pages,
-                                                                         dec->page_table, dec->pos, dec->max_pages,
-                                                                         dec->page, kvd);
-            B200_LAUNCH_CHECK("kv_append_kernel");
-            STEP(b200_attention_decode_paged_fp16(dec->q, w.k_pages, w.v_pages, dec->page_table, dec->len, dec->attn,
-                                                  B, dec->max_pages, dec->page, dec->H, dec->KV, dec->hd,
-                                                  dec->attn_scale));
+            if (!dry) {
+                if (dec->rope_type >= 0)
+                    STEP(b200_rope_forward_cached(dec->q, dec->k, dec->pos, dec->inv_freq, B, dec->H, dec->KV, dec->hd,
+                                                  dec->rope_type));
+                kv_append_kernel<<<dim3(ceil_div(kvd, 256), B), 256, 0, st>>>(dec->k, dec->v, w.k_pages, w.v_pages,
+                                                                             dec->page_table, dec->pos,
+                                                                             dec->max_pages, dec->page, kvd);
+                B200_LAUNCH_CHECK("kv_append_kernel");
+                STEP(b200_attention_decode_paged_fp16(dec->q, w.k_pages, w.v_pages, dec->page_table, dec->len,
+                                                      dec->attn, B, dec->max_pages, dec->page, dec->H, dec->KV,
+                                                      dec->hd, dec->attn_scale));
+            }
             SgArgs ao = base(w.wo, d, qd, dec->attn, qd);
             ao.resid = dec->x; ao.y_stride = d; ao.res_mult = dec->res_mult;
             STEP(stream_gemv(ao, kind, PRO_NONE, EPI_RESIDUAL));
@@ -282,12 +289,14 @@ static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t*
         mo.logits = dec->f_logits; mo.idx = dec->f_idx; mo.w = dec->f_w; mo.act = dec->f_act; mo.sh_act = dec->f_shact;
         mo.resid = dec->x; mo.res_mult = dec->res_mult;
         mo.M = B; mo.d = d; mo.E = dec->E; mo.ne = dec->ne; mo.K = dec->K;
-        mo.SH = (w.sh_gate && w.sh_up && w.sh_down) ? dec->SH : 0;
+        mo.SH = (dry || (w.sh_gate && w.sh_up && w.sh_down)) ? dec->SH : 0;
+        mo.dry = dry;
         STEP(moe_fused(mo, kind));
     }
     SgArgs h = base(dec->lm_head, dec->vocab, d, dec->x, d);
     h.norm_w = dec->final_norm; h.y = dec->logits; h.y_stride = dec->vocab; h.out_scale = 1.0f / dec->logits_scaling;
     STEP(stream_gemv(h, KIND_F16, PRO_RMS, EPI_STORE));
+    if (dry) return B200_OK;
     argmax_rows_kernel<<<B, 1024, 0, st>>>(dec->logits, dec->vocab, next);
     B200_LAUNCH_CHECK("argmax_rows_kernel");
 #undef STEP
@@ -396,7 +405,8 @@ int b200_decoder_create(b200_decoder** out, int batch, int vocab, int hidden, in
     }
     if (!rc) {
         cudaError_t e = cudaMallocHost((void**)&dec->h_tok, (size_t)B * 4);
-        if (e == cudaSuccess) e = cudaMallocHost((void**)&dec->h_next, (size_t)B * 4);
+        // one extra word after the tokens receives the kernels' status word
+        if (e == cudaSuccess) e = cudaMallocHost((void**)&dec->h_next, (size_t)(B + 1) * 4);
         if (e != cudaSuccess) rc = cuda_status(e, "decoder_create: pinned staging");
     }
     if (rc) {
@@ -479,6 +489,12 @@ int b200_decoder_reset(b200_decoder* dec) {
 int b200_decoder_configure(b200_decoder* dec, int fused, int use_graph) {
     B200_REQUIRE(dec, "decoder_configure: null handle");
     drop_graph(dec);
+    if (fused && dec->batch <= 8) {
+        // every matrix of the model must fit the streaming kernels' tiling: say so now,
+        // not in the middle of a step
+        const int rc = enqueue_step_fused(dec, nullptr, nullptr, true);
+        if (rc) return rc;
+    }
     dec->fused = fused ? 1 : 0;
     dec->use_graph = use_graph ? 1 : 0;
     dec->launches = 0;
@@ -544,8 +560,13 @@ int b200_decoder_step_host(b200_decoder* dec, const int32_t* tokens_host, int32_
     int rc = b200_decoder_step(dec, dec->tok, dec->next);
     if (rc) return rc;
     B200_CUDA(cudaMemcpyAsync(dec->h_next, dec->next, bytes, cudaMemcpyDeviceToHost, stream()));
+    int* status_dev = stream_status_ptr();
+    dec->h_next[dec->batch] = 0;
+    if (status_dev)
+        B200_CUDA(cudaMemcpyAsync(dec->h_next + dec->batch, status_dev, 4, cudaMemcpyDeviceToHost, stream()));
     B200_CUDA(cudaStreamSynchronize(stream()));
     memcpy(next_host, dec->h_next, bytes);
+    if (dec->h_next[dec->batch] != 0) return stream_status_check("decoder_step_host");
     return B200_OK;
 }
 

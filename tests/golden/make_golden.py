@@ -28,7 +28,7 @@ from oracle_lib import OracleOnly, Ref                               # noqa: E40
 
 GOLDEN_MODEL = dict(vocab=96, hidden=64, n_layers=2, layer_types=[0, 1],
                     n_heads=2, n_kv=1, head_dim=32, rope_type=1, rope_theta=1e4,
-                    mamba_heads=2, mamba_d_head=32, mamba_d_state=32, mamba_d_conv=4,
+                    mamba_heads=4, mamba_d_head=16, mamba_d_state=32, mamba_d_conv=4,
                     n_experts=4, top_k=2, expert_dim=32, shared_dim=32, qkind=2,
                     rms_eps=1e-5, embedding_multiplier=12.0, residual_multiplier=0.22,
                     attn_scale=0.0078125, logits_scaling=6.0)

@@ -266,7 +266,7 @@ def _mamba_case(oracle, wkind):
 # ---------------------------------------------------------------------------
 def _attention_cases():
     r = _rng(170)
-    B, T, H, KV, hd = 2, 9, 4, 2, 16
+    B, T, H, KV, hd = 2, 9, 4, 2, 32
     q = r.standard_normal((B, T, H, hd)).astype(np.float32)
     k = r.standard_normal((B, T, KV, hd)).astype(np.float32)
     v = r.standard_normal((B, T, KV, hd)).astype(np.float32)
@@ -334,7 +334,7 @@ def all_cases(oracle):
     cases.append(_sampling_case())
     cases += [_moe_case(oracle, -2, 8, 2, 64, 150), _moe_case(oracle, -1, 8, 2, 64, 151),
               _moe_case(oracle, 2, 8, 2, 64, 152), _moe_case(oracle, 0, 8, 2, 64, 153),
-              _moe_case(oracle, -1, 64, 8, 0, 154, d=32, E=16)]
+              _moe_case(oracle, -1, 64, 8, 0, 154, d=32, E=32)]
     cases += [_mamba_case(oracle, wk) for wk in (-2, -1, 2, 1)]
     cases += _attention_cases()
     return cases

@@ -1,0 +1,61 @@
+"""GPU parity: the tensor-core (tcgen05) path of the linear layers for many tokens.
+
+Two checks per shape: against the same product computed in fp32 from the
+fp16-rounded operands (what the kernel is meant to compute: tight, summation-order
+tolerance), and against the CPU oracle on the unrounded activations (the stated
+activation bound)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+FP16_OPERANDS = dict(rtol=2e-3, atol=2e-3)
+
+
+def _fp16_product(x, w16_bits):
+    xh = torch.from_numpy(x).cuda().half().float()
+    wh = torch.from_numpy(w16_bits.view(np.float16).astype(np.float32)).cuda()
+    return (xh.double() @ wh.double().T).float().cpu().numpy()
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 64, 128), (32, 64, 8), (128, 128, 128), (129, 192, 132), (300, 1536, 200),
+                                   (64, 1536, 6448), (1000, 3072, 1536)])
+def test_linear_fp16_many_tokens(oracle, M, K, N):
+    from gpu_util import ACTIVATION, SUM_ORDER, dev, empty, host, ops
+    r = np.random.default_rng(M + K + N)
+    x = r.standard_normal((M, K)).astype(np.float32)
+    w = oracle.f32_to_f16((r.standard_normal((N, K)) * 0.02).astype(np.float32))
+    y = empty((M, N))
+    ops.linear_forward_fp16(dev(x), dev(w), y, M, K, N)
+    got = host(y)
+    np.testing.assert_allclose(got, _fp16_product(x, w), **SUM_ORDER)
+    if M * N * K <= 1 << 27:
+        np.testing.assert_allclose(got, oracle.linear(x, w, -1, M, K, N), **FP16_OPERANDS)
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+@pytest.mark.parametrize("M,K,N", [(64, 1536, 6448), (257, 512, 1536)])
+def test_linear_packed_many_tokens(oracle, kind, M, K, N):
+    from gpu_util import ACTIVATION, SUM_ORDER, dev, empty, host, ops
+    r = np.random.default_rng(10 * kind + M)
+    x = r.standard_normal((M, K)).astype(np.float32)
+    w = oracle.quantize((r.standard_normal(N * K) * 0.02).astype(np.float32), kind)
+    y = empty((M, N))
+    ops.linear_forward_q4(dev(x), dev(w), y, M, K, N, kind)
+    got = host(y)
+    w16 = oracle.dequantize(w, N * K, kind).reshape(N, K)          # the fp16-rounded weights
+    np.testing.assert_allclose(got, _fp16_product(x, w16), **SUM_ORDER)
+    oracle.set_weight_rounding(True)
+    try:
+        rows = slice(0, min(M, 16))
+        want = oracle.linear(x[rows], w, kind, rows.stop, K, N)
+    finally:
+        oracle.set_weight_rounding(False)
+    np.testing.assert_allclose(got[rows], want, **FP16_OPERANDS)
+
+
+def test_status_word_is_clean_after_gemms():
+    """No bounded wait inside the kernels ran out during the tests above."""
+    from gpu_util import pkg
+    assert pkg.lib().raw("b200_stream_status") == 0
