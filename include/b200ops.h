@@ -137,6 +137,34 @@ int b200_moe_forward_bias_half(const float* x, const float* router_w, const floa
  * grouped [N*K] int32, offsets [ne+1] int32, both device pointers. */
 int b200_moe_permutation(const int32_t* idx, int64_t NK, int ne, int32_t* grouped, int32_t* offsets);
 
+/* Extensions for expert parallelism (the reference runs the MoE layer on one device
+ * only): the layer cut at its two exchange points.  The caller - one process per GPU -
+ * moves rows16 to the ranks that own the experts and y back, with any transport
+ * (jdm-ghassan_v1_flach_b200/ep.py uses NCCL all-to-all through torch.distributed).
+ * All pointers are device pointers; qkind -1 = fp16 experts, 0..3 packed (then d, E and
+ * SH must be multiples of 256).
+ *
+ * route          probs [N,ne] (optional), idx [N,K], w [N,K]: the router alone, bit for
+ *                bit the routing of b200_moe_forward_bias.
+ * dispatch_pack  rows16 [N*K, d] fp16: the token row of every slot t*K+k, slots stably
+ *                sorted by expert (so rows bound for one rank are contiguous);
+ *                inv [N*K]: position of slot s in that order; offsets [ne+1].
+ * experts_rows   y [R, d] fp32 = down_e(silu(gate_e r) * up_e r) for R received rows cut
+ *                into `groups` consecutive blocks by offsets [groups+1]; block g uses
+ *                local expert group_map[g] (null: g) of the n_local experts stored in
+ *                gates/ups [n_local*E, d] and downs [n_local*d, E].
+ * shared_combine out [N, d] = shared_expert(x) + sum_k w[t,k] * y[inv[t*K+k]] (k order);
+ *                sh_* may be null (no shared expert). */
+int b200_moe_route(const float* x, const float* router_w, const float* router_bias, float* probs, int32_t* idx,
+                   float* w, int64_t N, int d, int ne, int K);
+int b200_moe_dispatch_pack(const float* x, const int32_t* idx, int64_t N, int d, int ne, int K, uint16_t* rows16,
+                           int32_t* inv, int32_t* offsets);
+int b200_moe_experts_rows(const uint16_t* rows16, const int32_t* offsets, const int32_t* group_map, int groups,
+                          int64_t R, const void* gates, const void* ups, const void* downs, int n_local, float* y,
+                          int d, int E, int qkind);
+int b200_moe_shared_combine(const float* x, const void* sh_g, const void* sh_u, const void* sh_d, const float* y,
+                            const int32_t* inv, const float* w, float* out, int64_t N, int d, int K, int SH, int qkind);
+
 /* ---- Mamba-2: cuda_ops.h:142-189 ------------------------------------------------ */
 int b200_mamba2_forward(const float* x, const float* w_in, const float* conv_w, const float* conv_b,
                         const float* dt_bias, const float* a_log, const float* D, const float* norm_w,

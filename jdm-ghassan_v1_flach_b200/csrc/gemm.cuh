@@ -20,10 +20,17 @@ int pack_rows_f16(const float* src, const int32_t* row_map, int div, __half* dst
 // C = A . B^T on tcgen05.  A [a_rows, K] fp16, B (and B2) [b_rows, K] fp16, fp32
 // accumulation.  Rows of A form `groups` consecutive ranges given by the device
 // array offsets[groups + 1] (null: one group of all M rows); range g uses rows
-// [g*N, (g+1)*N) of B.
+// [g*N, (g+1)*N) of B - or block group_map[g] when that device array is given.
 //   GEMM_EPI_STORE   c[row, n]   = scale * acc                      (fp32, ld = ldc)
 //   GEMM_EPI_SWIGLU  c16[row, n] = silu(A.B^T) * (A.B2^T)           (fp16, ld = ldc)
 int umma_gemm(int epi, const __half* A, int64_t a_rows, const __half* B, const __half* B2, int64_t b_rows,
-              const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc, float scale);
+              const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc, float scale,
+              const int32_t* group_map = nullptr);
+
+// The same with B (and B2) in packed form, `kind` 0..3, dequantised inside the kernel
+// (values rounded to fp16).  K % 256 == 0.
+int umma_gemm_q(int epi, int kind, const __half* A, int64_t a_rows, const void* B, const void* B2, int64_t b_rows,
+                const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc,
+                float scale, const int32_t* group_map = nullptr);
 
 }  // namespace b200

@@ -40,6 +40,7 @@ constexpr int GM_STAGE_A = GM_TILE_M * GM_TILE_K * 2;
 struct alignas(64) GemmArgs {
     CUtensorMap map_a, map_b, map_b2;   // b2: the "up" matrix of the SwiGLU form
     const int32_t* offsets;             // device [groups + 1], or null: one group [0, M)
+    const int32_t* group_map;           // device [groups]: which N-row block of B a group uses; null = its own index
     int M, groups, N, K;
     float* c;                           // STORE: fp32 [M, ldc]
     __half* c16;                        // SWIGLU: fp16 [M, ldc]  silu(A.B^T) * (A.B2^T)
@@ -57,6 +58,77 @@ struct GemmShape {
     static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
+// Epilogue of one 128 x 128 tile, run by the four warps whose index modulo 4 selects
+// the 32 accumulator rows (tensor-memory lanes) a warp may read.  Waits (bounded) for
+// the accumulator; a failed wait anywhere in the CTA leaves the status word set and
+// the stores are skipped (decided per warp: tcgen05.ld is a warp-wide instruction).
+template <int EPI>
+__device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tmem, uint64_t* accum, int warp, int lane,
+                                              int row0, int row_end, int n0) {
+    const int q = warp & 3;
+    const int row = row0 + q * 32 + lane;
+    bool ok = mbar_wait(accum, 0, a.status);
+    tc_fence_after();
+    ok = __all_sync(0xffffffffu, ok && *reinterpret_cast<volatile int*>(a.status) == 0);
+    if (!ok) return;
+    const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+    for (int c0 = 0; c0 < GM_TILE_N; c0 += 32) {
+        float v[32];
+        tmem_ld32(tbase + c0, v);
+        if (EPI == GEMM_EPI_SWIGLU) {
+            float u[32];
+            tmem_ld32(tbase + GM_TILE_N + c0, u);
+            if (row < row_end) {
+                __half* dst = a.c16 + (int64_t)row * a.ldc + n0 + c0;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    if (n0 + c0 + i + 1 < a.N) {
+                        *reinterpret_cast<__half2*>(dst + i) =
+                            __floats2half2_rn(silu_acc(v[i]) * u[i], silu_acc(v[i + 1]) * u[i + 1]);
+                    } else if (n0 + c0 + i < a.N) {
+                        dst[i] = __float2half_rn(silu_acc(v[i]) * u[i]);
+                    }
+                }
+            }
+        } else if (row < row_end) {
+            float* dst = a.c + (int64_t)row * a.ldc + n0 + c0;
+            if (n0 + c0 + 32 <= a.N && (a.ldc & 3) == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4*>(dst + i) =
+                        make_float4(v[i] * a.scale, v[i + 1] * a.scale, v[i + 2] * a.scale, v[i + 3] * a.scale);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (n0 + c0 + i < a.N) dst[i] = v[i] * a.scale;
+            }
+        }
+    }
+}
+
+// Which tile blockIdx.y is: (group, first row, row limit); false when past the last tile.
+__device__ __forceinline__ bool gemm_find_tile(const GemmArgs& a, int& group, int& row0, int& row_end) {
+    int slot = blockIdx.y;
+    group = 0; row0 = 0; row_end = a.M;
+    if (!a.offsets) {
+        row0 = slot * GM_TILE_M;
+        return row0 < a.M;
+    }
+    int lo = a.offsets[0];
+    for (int g = 0; g < a.groups; ++g) {
+        const int hi = a.offsets[g + 1];
+        const int tiles = (hi - lo + GM_TILE_M - 1) / GM_TILE_M;
+        if (slot < tiles) {
+            group = g; row0 = lo + slot * GM_TILE_M; row_end = hi;
+            return true;
+        }
+        slot -= tiles;
+        lo = hi;
+    }
+    return false;
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_constant__ GemmArgs a) {
     using S = GemmShape<EPI>;
@@ -68,31 +140,10 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // ---- which tile: (group, first row, row limit) -------------------------------
-    int group = 0, row0 = 0, row_end = a.M;
-    {
-        int slot = blockIdx.y;
-        if (a.offsets) {
-            bool found = false;
-            int lo = a.offsets[0];
-            for (int g = 0; g < a.groups; ++g) {
-                const int hi = a.offsets[g + 1];
-                const int tiles = (hi - lo + GM_TILE_M - 1) / GM_TILE_M;
-                if (slot < tiles) {
-                    group = g; row0 = lo + slot * GM_TILE_M; row_end = hi; found = true;
-                    break;
-                }
-                slot -= tiles;
-                lo = hi;
-            }
-            if (!found) return;                       // uniform for the whole CTA
-        } else {
-            row0 = slot * GM_TILE_M;
-            if (row0 >= a.M) return;
-        }
-    }
+    int group, row0, row_end;
+    if (!gemm_find_tile(a, group, row0, row_end)) return;     // uniform for the whole CTA
     const int n0 = blockIdx.x * GM_TILE_N;            // first output column inside the group
-    const int brow0 = group * a.N + n0;               // first row of B
+    const int brow0 = (a.group_map ? a.group_map[group] : group) * a.N + n0;   // first row of B
     const int KB = (a.K + GM_TILE_K - 1) / GM_TILE_K;
 
     if (threadIdx.x == 0) {
@@ -152,49 +203,230 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
             umma_commit(accum);                       // accumulator complete (or as far as we got)
         }
     } else {
-        const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
-        const int row = row0 + q * 32 + lane;
-        bool ok = mbar_wait(accum, 0, a.status);
-        tc_fence_after();
-        // a failed wait anywhere in the CTA leaves the status word set: skip the stores
-        // (decided per warp: tcgen05.ld is a warp-wide instruction)
-        ok = __all_sync(0xffffffffu, ok && *reinterpret_cast<volatile int*>(a.status) == 0);
-        if (ok) {
-            const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-            for (int c0 = 0; c0 < GM_TILE_N; c0 += 32) {
-                float v[32];
-                tmem_ld32(tbase + c0, v);
-                if (EPI == GEMM_EPI_SWIGLU) {
-                    float u[32];
-                    tmem_ld32(tbase + GM_TILE_N + c0, u);
-                    if (row < row_end) {
-                        __half* dst = a.c16 + (int64_t)row * a.ldc + n0 + c0;
+        gemm_epilogue<EPI>(a, tmem, accum, warp, lane, row0, row_end, n0);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, S::UN);
+}
+
+// ===========================================================================
+// Packed weights: dequantise inside the GEMM
+// ===========================================================================
+// Same tiling, but B arrives in its packed form: per 256 weights of K (8 blocks of
+// the 32-weight kinds, one Q4_K super-block) a row contributes a fixed number of
+// bytes (144 / 160 / 272 / 144), which one 2-D TMA box brings in for all rows of the
+// tile.  Eight warps expand it, 64 weights of K per row and step, to fp16 - the
+// value the reference's CPU path multiplies with, its dequantised weight rounded to
+// fp16 (core/ops.cpp:313-336, :392), to within one fp16 ulp - and store the result in
+// the swizzled K-major layout the MMA reads.  HBM sees the packed bytes only.
+//
+//   warp 0      TMA: A tile per 64 of K, packed B per 256 of K
+//   warps 2..9  packed B (shared) -> fp16 B tile (shared, 2 buffers); 2..5 then run the epilogue
+//   warp 1      MMA when an A stage and a B tile are both ready
+template <int KIND>
+struct PackedShape {
+    static constexpr int SBB = 8 * (KIND == 3 ? 18 : q_block_bytes(KIND));   // bytes per row per 256 of K
+};
+
+template <int EPI, int KIND>
+struct GemmQShape {
+    static constexpr int UN = GemmShape<EPI>::UN;
+    static constexpr int SBB = PackedShape<KIND>::SBB;
+    static constexpr int B16 = UN * GM_TILE_K * 2;                  // one fp16 B tile
+    static constexpr int PACKED = UN * SBB;                         // one packed stage
+    static constexpr int SA = 4, SB = 2;
+    static constexpr int FIXED = SA * GM_STAGE_A + SB * B16 + 1024 + 256;
+    // packed stages: as many as fit (up to 4) - with few rows of A the kernel is a pure
+    // weight stream and needs tens of KB in flight per SM to keep HBM busy
+    static constexpr int ROOM = (227 * 1024 - FIXED) / PACKED;
+    static constexpr int SP = ROOM >= 4 ? 4 : (ROOM >= 1 ? ROOM : 1);
+    static constexpr int SMEM = FIXED + SP * PACKED;
+};
+
+// Half-precision expansion of packed weights, two values per instruction.  A byte
+// b OR-ed into the mantissa of 0x6400 is the fp16 number 1024 + b, so small integers
+// become fp16 without a conversion instruction; __byte_perm interleaves two payload
+// bytes with two 0x64 bytes into one half2.
+__device__ __forceinline__ __half2 magic_pair(uint32_t bytes, uint32_t sel) {
+    const uint32_t v = __byte_perm(bytes, 0x64646464u, sel);
+    return *reinterpret_cast<const __half2*>(&v);
+}
+constexpr uint32_t SEL_01 = 0x5140, SEL_23 = 0x5342;   // (byte0, byte1) / (byte2, byte3) of the first operand
+
+// 32 of the 64 weights of K block j of a row (segment of 256 weights at `seg`):
+// hh = 0 the first 32 of the block, hh = 1 the last 32.  Written as four 16-byte
+// chunks of row r of the swizzled fp16 tile.  Arithmetic in fp16 FMAs:
+//   Q4_0  (q - 8) * d,  Q8_0  q * d       exact (one rounding of an exact product)
+//   Q4_1  q * d + m                        one rounding
+//   Q4_K  (q * sc) * d - fp16(m * dmin)    q * sc exact; the min term rounded first
+// against fp16(fp32 value) of the materialising dequantiser: equal for Q4_0 / Q8_0,
+// within one fp16 ulp otherwise.
+template <int KIND>
+__device__ __forceinline__ void dequant_half_block(const uint8_t* seg, int j, int hh, uint8_t* tile, int r) {
+    uint8_t* rowp = tile + (size_t)(r >> 3) * 1024 + (size_t)(r & 7) * 128;
+    const int sw = r & 7;
+    __half2 out[16];
+    if (KIND == 3) {
+        const uint4 hdr = *reinterpret_cast<const uint4*>(seg);
+        int s, m;
+        q4k_scale_min(2 * j + hh, reinterpret_cast<const uint8_t*>(&hdr) + 4, s, m);
+        const __half d = __ushort_as_half((unsigned short)(hdr.x & 0xFFFF));
+        const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
+        const __half2 sc2 = __half2half2(__int2half_rn(s));
+        const __half2 nsc = __half2half2(__int2half_rn(-1024 * s));          // exact: |1024 * s| <= 64512
+        const __half2 d2 = __half2half2(d);
+        const __half2 nm = __half2half2(__float2half_rn(-__fmul_rn(dmin, (float)m)));
+        const uint4 q0 = *reinterpret_cast<const uint4*>(seg + 16 + 32 * j);
+        const uint4 q1 = *reinterpret_cast<const uint4*>(seg + 32 + 32 * j);
+        const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            if (n0 + c0 + i + 1 < a.N) {
-                                *reinterpret_cast<__half2*>(dst + i) =
-                                    __floats2half2_rn(silu_acc(v[i]) * u[i], silu_acc(v[i + 1]) * u[i + 1]);
-                            } else if (n0 + c0 + i < a.N) {
-                                dst[i] = __float2half_rn(silu_acc(v[i]) * u[i]);
-                            }
-                        }
-                    }
-                } else if (row < row_end) {
-                    float* dst = a.c + (int64_t)row * a.ldc + n0 + c0;
-                    if (n0 + c0 + 32 <= a.N && (a.ldc & 3) == 0) {
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t x = (words[i] >> (4 * hh)) & 0x0F0F0F0Fu;
+            const __half2 a = __hfma2(magic_pair(x, SEL_01), sc2, nsc);      // q * sc, exact
+            const __half2 b = __hfma2(magic_pair(x, SEL_23), sc2, nsc);
+            out[2 * i] = __hfma2(a, d2, nm);
+            out[2 * i + 1] = __hfma2(b, d2, nm);
+        }
+    } else if (KIND == 2) {
+        const uint16_t* blk = reinterpret_cast<const uint16_t*>(seg + (2 * j + hh) * 34);
+        const __half2 d2 = __half2half2(__ushort_as_half(blk[0]));
+        const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6480));   // 1152 = 1024 + 128
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4)
-                            *reinterpret_cast<float4*>(dst + i) =
-                                make_float4(v[i] * a.scale, v[i + 1] * a.scale, v[i + 2] * a.scale, v[i + 3] * a.scale);
-                    } else {
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t x = (uint32_t)blk[1 + i] ^ 0x8080u;              // int8 + 128 as unsigned bytes
+            out[i] = __hmul2(__hsub2(magic_pair(x, SEL_01), bias), d2);
+        }
+    } else {
+        const int bb = KIND == 0 ? 18 : 20;
+        const uint16_t* blk = reinterpret_cast<const uint16_t*>(seg + (2 * j + hh) * bb);
+        const __half2 d2 = __half2half2(__ushort_as_half(blk[0]));
+        const __half2 m2 = KIND == 1 ? __half2half2(__ushort_as_half(blk[1])) : __half2half2(__ushort_as_half(0));
+        const uint16_t* qs = blk + (KIND == 0 ? 1 : 2);
+        const __half2 off = __half2half2(__ushort_as_half((unsigned short)(KIND == 0 ? 0x6408 : 0x6400)));  // 1032 / 1024
+        // byte i: low nibble = weight i, high nibble = weight 16 + i
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (n0 + c0 + i < a.N) dst[i] = v[i] * a.scale;
-                    }
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t p = qs[i];
+            const __half2 lo = __hsub2(magic_pair(p & 0x0F0Fu, SEL_01), off);
+            const __half2 hi = __hsub2(magic_pair((p >> 4) & 0x0F0Fu, SEL_01), off);
+            out[i] = KIND == 0 ? __hmul2(lo, d2) : __hfma2(lo, d2, m2);
+            out[8 + i] = KIND == 0 ? __hmul2(hi, d2) : __hfma2(hi, d2, m2);
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<uint4*>(rowp + (((4 * hh + c) ^ sw) << 4)) = *reinterpret_cast<const uint4*>(&out[4 * c]);
+}
+
+constexpr int GQ_EXPAND_WARPS = 8;
+constexpr int GQ_THREADS = 64 + GQ_EXPAND_WARPS * 32;
+
+template <int EPI, int KIND>
+__global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid_constant__ GemmArgs a) {
+    using S = GemmQShape<EPI, KIND>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sm_a = smem;
+    uint8_t* sm_b = sm_a + S::SA * GM_STAGE_A;
+    uint8_t* sm_p = sm_b + S::SB * S::B16;
+    uint64_t* a_full = reinterpret_cast<uint64_t*>(sm_p + S::SP * S::PACKED);
+    uint64_t* a_empty = a_full + S::SA;
+    uint64_t* b_full = a_empty + S::SA;
+    uint64_t* b_empty = b_full + S::SB;
+    uint64_t* p_full = b_empty + S::SB;
+    uint64_t* p_empty = p_full + 4;
+    uint64_t* accum = p_empty + 4;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    int group, row0, row_end;
+    if (!gemm_find_tile(a, group, row0, row_end)) return;
+    const int n0 = blockIdx.x * GM_TILE_N;
+    const int brow0 = (a.group_map ? a.group_map[group] : group) * a.N + n0;
+    const int KB = a.K / GM_TILE_K;                   // K % 256 == 0 (host)
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::SA; ++s) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
+        for (int s = 0; s < S::SB; ++s) { mbar_init(&b_full[s], GQ_EXPAND_WARPS); mbar_init(&b_empty[s], 1); }
+        for (int s = 0; s < S::SP; ++s) { mbar_init(&p_full[s], 1); mbar_init(&p_empty[s], GQ_EXPAND_WARPS); }
+        mbar_init(accum, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, S::UN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int kb = 0; kb < KB && ok; ++kb) {
+                if ((kb & 3) == 0) {
+                    const int sb = kb >> 2, p = sb % S::SP;
+                    if (sb >= S::SP) ok = mbar_wait(&p_empty[p], ((sb / S::SP) - 1) & 1, a.status);
+                    if (!ok) break;
+                    uint8_t* dst = sm_p + (size_t)p * S::PACKED;
+                    mbar_expect_tx(&p_full[p], S::PACKED);
+                    tma_load_2d(dst, &a.map_b, sb * (S::SBB / 4), brow0, &p_full[p]);
+                    if (EPI == GEMM_EPI_SWIGLU)
+                        tma_load_2d(dst + GM_TILE_N * S::SBB, &a.map_b2, sb * (S::SBB / 4), brow0, &p_full[p]);
                 }
+                const int s = kb % S::SA;
+                if (kb >= S::SA) ok = mbar_wait(&a_empty[s], ((kb / S::SA) - 1) & 1, a.status);
+                if (!ok) break;
+                mbar_expect_tx(&a_full[s], GM_STAGE_A);
+                tma_load_2d(sm_a + (size_t)s * GM_STAGE_A, &a.map_a, kb * GM_TILE_K, row0, &a_full[s]);
             }
         }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_f16(GM_TILE_M, S::UN);
+            for (int kb = 0; kb < KB; ++kb) {
+                const int s = kb % S::SA, b = kb % S::SB;
+                if (!mbar_wait(&a_full[s], (kb / S::SA) & 1, a.status)) break;
+                if (!mbar_wait(&b_full[b], (kb / S::SB) & 1, a.status)) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(sm_a + (size_t)s * GM_STAGE_A);
+                const uint32_t b_addr = smem_u32(sm_b + (size_t)b * S::B16);
+#pragma unroll
+                for (int k = 0; k < GM_TILE_K / 16; ++k)
+                    umma_f16(tmem, umma_smem_desc(a_addr + k * 32), umma_smem_desc(b_addr + k * 32), idesc,
+                             kb > 0 || k > 0);
+                umma_commit(&a_empty[s]);
+                umma_commit(&b_empty[b]);
+            }
+            umma_commit(accum);
+        }
+    } else {
+        // eight expanding warps: thread -> (B row, which 32 of the block's 64 weights)
+        const int t = threadIdx.x - 64, row_t = t & 127, hh = t >> 7;
+        bool ok = true;
+        for (int kb = 0; kb < KB && ok; ++kb) {
+            const int sb = kb >> 2, j = kb & 3, p = sb % S::SP, b = kb % S::SB;
+            if (j == 0) ok = mbar_wait(&p_full[p], (sb / S::SP) & 1, a.status);
+            if (ok && kb >= S::SB) ok = mbar_wait(&b_empty[b], ((kb / S::SB) - 1) & 1, a.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const uint8_t* packed = sm_p + (size_t)p * S::PACKED;
+            uint8_t* tile = sm_b + (size_t)b * S::B16;
+#pragma unroll
+            for (int rr = 0; rr < S::UN / 128; ++rr) {
+                const int r = row_t + rr * 128;
+                dequant_half_block<KIND>(packed + (size_t)r * S::SBB, j, hh, tile, r);
+            }
+            fence_proxy_async();                      // generic-proxy stores -> visible to the MMA
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&b_full[b]);
+                if (j == 3) mbar_arrive(&p_empty[p]);
+            }
+        }
+        if (warp < 6) gemm_epilogue<EPI>(a, tmem, accum, warp, lane, row0, row_end, n0);
     }
     tc_fence_before();
     __syncthreads();
@@ -284,6 +516,92 @@ int make_tile_map(CUtensorMap* out, const void* base, int64_t rows, int64_t K, i
     return B200_OK;
 }
 
+// Tensor map over packed rows viewed as 32-bit words: boxes of (box_bytes / 4) words
+// x GM_TILE_N rows, no swizzle.
+static int make_packed_map(CUtensorMap* out, const void* base, int64_t rows, int64_t row_bytes, int box_bytes) {
+    B200_REQUIRE(base && rows > 0 && row_bytes % 16 == 0 && box_bytes % 16 == 0, "packed map: rows must be 16-byte multiples");
+    B200_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "packed map: base must be 16-byte aligned");
+    typedef std::tuple<const void*, int64_t, int64_t, int> Key;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    const Key key(base, rows, row_bytes, box_bytes);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return B200_OK;
+    }
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(B200_ECUDA, "packed map: the driver does not export cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 4), (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)(box_bytes / 4), (cuuint32_t)GM_TILE_N};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200_ECUDA, "packed map: cuTensorMapEncodeTiled failed with %d", (int)r);
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *out;
+    return B200_OK;
+}
+
+template <int EPI, int KIND>
+static int launch_gemm_q(const GemmArgs& a) {
+    using S = GemmQShape<EPI, KIND>;
+    auto kern = umma_gemm_q_kernel<EPI, KIND>;
+    static bool configured = false;
+    if (!configured) {
+        B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM));
+        configured = true;
+    }
+    const int m_slots = (a.M + GM_TILE_M - 1) / GM_TILE_M + (a.offsets ? a.groups : 0);
+    B200_REQUIRE(m_slots <= 65535, "umma_gemm_q: too many row tiles (%d)", m_slots);
+    dim3 grid((a.N + GM_TILE_N - 1) / GM_TILE_N, m_slots);
+    kern<<<grid, GQ_THREADS, S::SMEM, stream()>>>(a);
+    B200_LAUNCH_CHECK("umma_gemm_q_kernel");
+    return B200_OK;
+}
+
+// As umma_gemm(), with B (and B2) packed in `kind` (0..3), [b_rows, K]; K % 256 == 0.
+int umma_gemm_q(int epi, int kind, const __half* A, int64_t a_rows, const void* B, const void* B2, int64_t b_rows,
+                const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc,
+                float scale, const int32_t* group_map) {
+    if (M <= 0 || N <= 0) return B200_OK;
+    B200_REQUIRE(kind >= 0 && kind <= 3, "umma_gemm_q: unknown kind %d", kind);
+    B200_REQUIRE(A && B && K > 0 && K % 256 == 0, "umma_gemm_q: K must be a positive multiple of 256");
+    B200_REQUIRE(groups >= 1 && (offsets || groups == 1), "umma_gemm_q: groups need a device offsets array");
+    B200_REQUIRE((group_map || b_rows >= (int64_t)groups * N) && a_rows >= M, "umma_gemm_q: operand shapes do not cover the groups");
+    GemmArgs a;
+    int rc = make_tile_map(&a.map_a, A, a_rows, K, GM_TILE_M);
+    if (rc) return rc;
+    const int64_t row_bytes = q_row_bytes(kind, K);
+    const int sbb = 8 * (kind == 3 ? 18 : q_block_bytes(kind));
+    rc = make_packed_map(&a.map_b, B, b_rows, row_bytes, sbb);
+    if (rc) return rc;
+    a.map_b2 = a.map_b;
+    if (epi == GEMM_EPI_SWIGLU) {
+        B200_REQUIRE(B2 && c16 && ldc % 2 == 0, "umma_gemm_q: the SwiGLU form needs the second matrix and an fp16 output");
+        rc = make_packed_map(&a.map_b2, B2, b_rows, row_bytes, sbb);
+        if (rc) return rc;
+    } else {
+        B200_REQUIRE(c, "umma_gemm_q: null output");
+    }
+    a.offsets = offsets; a.group_map = group_map; a.M = M; a.groups = groups; a.N = N; a.K = K;
+    a.c = c; a.c16 = c16; a.ldc = ldc; a.scale = scale;
+    a.status = stream_status_ptr();
+    B200_REQUIRE(a.status, "umma_gemm_q: status word allocation failed");
+#define GQ(KIND_)                                                                        \
+    return epi == GEMM_EPI_SWIGLU ? launch_gemm_q<GEMM_EPI_SWIGLU, KIND_>(a) : launch_gemm_q<GEMM_EPI_STORE, KIND_>(a);
+    switch (kind) {
+        case 0: GQ(0)
+        case 1: GQ(1)
+        case 2: GQ(2)
+        default: GQ(3)
+    }
+#undef GQ
+}
+
 template <int EPI>
 static int launch_gemm(const GemmArgs& a) {
     using S = GemmShape<EPI>;
@@ -304,11 +622,12 @@ static int launch_gemm(const GemmArgs& a) {
 // A [a_rows, K] fp16; B (and B2) [b_rows, K] fp16 with b_rows = groups * N.
 // offsets: device [groups + 1] or null (then groups must be 1 and all M rows form it).
 int umma_gemm(int epi, const __half* A, int64_t a_rows, const __half* B, const __half* B2, int64_t b_rows,
-              const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc, float scale) {
+              const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc, float scale,
+              const int32_t* group_map) {
     if (M <= 0 || N <= 0) return B200_OK;
     B200_REQUIRE(A && B && K > 0 && K % 8 == 0, "umma_gemm: K must be a positive multiple of 8");
     B200_REQUIRE(groups >= 1 && (offsets || groups == 1), "umma_gemm: groups need a device offsets array");
-    B200_REQUIRE(b_rows >= (int64_t)groups * N && a_rows >= M, "umma_gemm: operand shapes do not cover the groups");
+    B200_REQUIRE((group_map || b_rows >= (int64_t)groups * N) && a_rows >= M, "umma_gemm: operand shapes do not cover the groups");
     GemmArgs a;
     int rc = make_tile_map(&a.map_a, A, a_rows, K, GM_TILE_M);
     if (rc) return rc;
@@ -322,7 +641,7 @@ int umma_gemm(int epi, const __half* A, int64_t a_rows, const __half* B, const _
     } else {
         B200_REQUIRE(c, "umma_gemm: null output");
     }
-    a.offsets = offsets; a.M = M; a.groups = groups; a.N = N; a.K = K;
+    a.offsets = offsets; a.group_map = group_map; a.M = M; a.groups = groups; a.N = N; a.K = K;
     a.c = c; a.c16 = c16; a.ldc = ldc; a.scale = scale;
     a.status = stream_status_ptr();
     B200_REQUIRE(a.status, "umma_gemm: status word allocation failed");

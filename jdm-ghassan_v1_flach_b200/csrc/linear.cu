@@ -130,13 +130,16 @@ int linear(const float* x, const void* w, int kind, float* y, int M, int K, int 
     if (M >= GEMM_MIN_ROWS && kind != KIND_F32 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && N % 4 == 0 &&
         (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
         const size_t a_bytes = ((size_t)M * K * 2 + 255) & ~(size_t)255;
-        const size_t b_bytes = kind == KIND_F16 ? 0 : (size_t)N * K * 2;
+        const bool in_kernel = kind != KIND_F16 && K % 256 == 0;     // packed weights dequantised by the GEMM itself
+        const size_t b_bytes = (kind == KIND_F16 || in_kernel) ? 0 : (size_t)N * K * 2;
         void* ws;
         int rc = workspace(WS_LINEAR).ensure(a_bytes + b_bytes + 256, &ws);
         if (rc) return rc;
         __half* a16 = static_cast<__half*>(ws);
         rc = pack_rows_f16(x, nullptr, 1, a16, M, K);
         if (rc) return rc;
+        if (in_kernel)
+            return umma_gemm_q(GEMM_EPI_STORE, kind, a16, M, w, nullptr, N, nullptr, 1, M, N, K, y, nullptr, N, 1.0f);
         const __half* b16 = static_cast<const __half*>(w);
         if (kind != KIND_F16) {
             uint16_t* scratch = reinterpret_cast<uint16_t*>(static_cast<char*>(ws) + a_bytes);

@@ -16,6 +16,7 @@
 // reference's operand order, so given identical inputs the carried state is
 // bit-identical to the CPU path; only dot-product summation order differs.
 #include "fused.cuh"
+#include "gemm.cuh"
 
 namespace b200 {
 
@@ -76,6 +77,7 @@ mamba_step_scan_kernel(const float* __restrict__ bc, const float* __restrict__ d
                        const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                        const float* __restrict__ Dv, float* __restrict__ ssm_state,  // [M, rows, d_state]
                        float* __restrict__ y,                                          // [M, d_inner]
+                       int dt_stride,                                                  // floats between dt_raw rows
                        MambaDims p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rows = p.n_heads * p.d_head;
@@ -83,7 +85,7 @@ mamba_step_scan_kernel(const float* __restrict__ bc, const float* __restrict__ d
     const int m = blockIdx.y;
     if (row >= rows) return;
     const int h = row / p.d_head;
-    const float u = dt_raw[(int64_t)m * p.n_heads + h] + dt_bias[h];
+    const float u = dt_raw[(int64_t)m * dt_stride + h] + dt_bias[h];
     const float dt = (u > 20.0f) ? u : log1pf(expf(u));
     const float A = -expf(a_log[h]);
     const float dA = expf(__fmul_rn(A, dt));
@@ -100,6 +102,33 @@ mamba_step_scan_kernel(const float* __restrict__ bc, const float* __restrict__ d
     }
     acc = warp_sum(acc);
     if (lane == 0) y[(int64_t)m * p.d_inner + row] = acc + Dv[h] * xv;
+}
+
+// ---------------------------------------------------------------------------
+// Decode, many sequences: the convolution step on rows of an already computed
+// projection [M, proj] (gate | bc | dt).  One thread per (sequence, channel); same
+// arithmetic as the epilogue of mamba_inproj_conv_kernel.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+mamba_conv_step_kernel(const float* __restrict__ proj, const float* __restrict__ conv_w,
+                       const float* __restrict__ conv_b, float* __restrict__ conv_state, float* __restrict__ bc,
+                       int M, MambaDims p) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)M * p.conv_dim) return;
+    const int m = (int)(i / p.conv_dim), c = (int)(i - (int64_t)m * p.conv_dim);
+    const float raw = proj[(int64_t)m * p.proj + p.d_inner + c];
+    const int win = p.k - 1;
+    float* st = conv_state + ((int64_t)m * p.conv_dim + c) * win;
+    const float* wc = conv_w + (int64_t)c * p.k;
+    float a = conv_b ? conv_b[c] : 0.0f;
+    for (int j = 0; j < win; ++j) {
+        const float v = st[j];
+        a = __fadd_rn(a, __fmul_rn(wc[j], v));
+        if (j > 0) st[j - 1] = v;
+    }
+    a = __fadd_rn(a, __fmul_rn(wc[win], raw));
+    if (win > 0) st[win - 1] = raw;
+    bc[i] = silu_acc(a);
 }
 
 // ---------------------------------------------------------------------------
@@ -307,6 +336,30 @@ int mamba2_step(const float* x, const void* w_in, const float* conv_w, const flo
     float* dt_raw = bc + (size_t)batch * p.conv_dim;
     float* y = dt_raw + (((size_t)batch * p.n_heads + 3) & ~(size_t)3);
     const int win = p.k - 1;
+    const int rows = p.n_heads * p.d_head;
+    if (batch >= GEMM_MIN_ROWS && kind != KIND_F32) {
+        // many sequences: both projections as tensor-core GEMMs, the conv step on its own
+        void* wsp2;
+        rc = workspace(WS_MAMBA).ensure((per + p.proj) * batch * sizeof(float) + 512, &wsp2);
+        if (rc) return rc;
+        gate = static_cast<float*>(wsp2);
+        bc = gate + (size_t)batch * p.d_inner;
+        dt_raw = bc + (size_t)batch * p.conv_dim;
+        y = dt_raw + (((size_t)batch * p.n_heads + 3) & ~(size_t)3);
+        float* proj = y + (size_t)batch * p.d_inner;
+        rc = linear(x, w_in, kind, proj, batch, p.d, p.proj);
+        if (rc) return rc;
+        const int64_t items = (int64_t)batch * p.conv_dim;
+        mamba_conv_step_kernel<<<(unsigned)ceil_div64(items, 256), 256, 0, stream()>>>(proj, conv_w, conv_b, conv_state,
+                                                                                       bc, batch, p);
+        B200_LAUNCH_CHECK("mamba_conv_step_kernel");
+        mamba_step_scan_kernel<<<dim3(ceil_div(rows, SCAN_WARPS), batch), SCAN_WARPS * 32, 0, stream()>>>(
+            bc, proj + p.d_inner + p.conv_dim, dt_bias, a_log, D, ssm_state, y, p.proj, p);
+        B200_LAUNCH_CHECK("mamba_step_scan_kernel");
+        mamba_gated_norm_kernel<<<batch, 256, 0, stream()>>>(y, proj, p.proj, norm_w, y, p.d_inner, p.eps);
+        B200_LAUNCH_CHECK("mamba_gated_norm_kernel");
+        return linear(y, w_out, kind, out, batch, p.d_inner, p.d);
+    }
     for (int m0 = 0; m0 < batch; m0 += 8) {
         const int M = std::min(8, batch - m0);
         const float* xm = x + (int64_t)m0 * p.d;
@@ -325,9 +378,8 @@ int mamba2_step(const float* x, const void* w_in, const float* conv_w, const flo
         }
         if (rc) return rc;
     }
-    const int rows = p.n_heads * p.d_head;
     mamba_step_scan_kernel<<<dim3(ceil_div(rows, SCAN_WARPS), batch), SCAN_WARPS * 32, 0, stream()>>>(
-        bc, dt_raw, dt_bias, a_log, D, ssm_state, y, p);
+        bc, dt_raw, dt_bias, a_log, D, ssm_state, y, p.n_heads, p);
     B200_LAUNCH_CHECK("mamba_step_scan_kernel");
     mamba_gated_norm_kernel<<<batch, 256, 0, stream()>>>(y, gate, p.d_inner, norm_w, y, p.d_inner, p.eps);
     B200_LAUNCH_CHECK("mamba_gated_norm_kernel");

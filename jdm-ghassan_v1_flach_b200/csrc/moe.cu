@@ -11,9 +11,17 @@
 // strict '>' in ascending expert order (lowest index wins ties).  Expert outputs
 // are combined per token in k order (no atomics), so results are run-to-run
 // bit-stable.
+#include "gemm.cuh"
 #include "linear.cuh"
+#include "route.cuh"
 
 namespace b200 {
+
+// moe_grouped.cu
+int moe_forward_grouped(const float* x, const float* router_w, const float* router_bias, const void* gates,
+                        const void* ups, const void* downs, const void* sh_g, const void* sh_u, const void* sh_d,
+                        float* out, float* probs_cache, int32_t* idx_cache, float* w_cache, int64_t N, int d, int E,
+                        int ne, int K, int SH, int kind);
 
 constexpr int MOE_MAX_NE = 256;
 constexpr int MOE_MAX_K = 16;
@@ -322,8 +330,108 @@ static int launch_experts(const MoeArgs& a) {
     return B200_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Router for many tokens.  The logit of (token, expert) keeps the reference's
+// sequential fp32 chain over groups of four, but the chains of a 32-token x
+// 64-expert tile advance together: activations and router rows are staged in
+// shared memory 64 columns at a time and every thread carries TPT x EPT chains in
+// registers (4 x 2 for prompts; 1 x 1 for a batch of decode tokens, so that the few
+// chains spread over many SMs).  A second kernel finishes each token with one warp.
+// ---------------------------------------------------------------------------
+constexpr int RT_K = 64, RT_LD = RT_K + 4;
+
+template <int TPT, int EPT>
+__global__ void __launch_bounds__(256)
+route_logits_kernel(const float* __restrict__ x, const float* __restrict__ router_w, float* __restrict__ logits,
+                    int64_t N, int d, int ne) {
+    constexpr int RT_TOK = 8 * TPT, RT_EXP = 32 * EPT;
+    __shared__ __align__(16) float xs[RT_TOK][RT_LD];
+    __shared__ __align__(16) float ws[RT_EXP][RT_LD];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t t0 = (int64_t)blockIdx.x * RT_TOK;
+    const int e0 = blockIdx.y * RT_EXP;
+    float acc[TPT][EPT] = {};
+    for (int k0 = 0; k0 < d; k0 += RT_K) {
+        const int kc = min(RT_K, d - k0);              // a multiple of 4
+        __syncthreads();
+        for (int i = threadIdx.x; i < (RT_TOK + RT_EXP) * (RT_K / 4); i += 256) {
+            const int row = i / (RT_K / 4), c4 = (i % (RT_K / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c4 < kc) {
+                if (row < RT_TOK) {
+                    if (t0 + row < N) v = *reinterpret_cast<const float4*>(x + (t0 + row) * d + k0 + c4);
+                } else if (e0 + row - RT_TOK < ne) {
+                    v = *reinterpret_cast<const float4*>(router_w + (int64_t)(e0 + row - RT_TOK) * d + k0 + c4);
+                }
+            }
+            float* dst = row < RT_TOK ? &xs[row][c4] : &ws[row - RT_TOK][c4];
+            *reinterpret_cast<float4*>(dst) = v;
+        }
+        __syncthreads();
+        for (int g = 0; g < kc; g += 4) {
+            float4 a[TPT], b[EPT];
+#pragma unroll
+            for (int i = 0; i < TPT; ++i) a[i] = *reinterpret_cast<const float4*>(&xs[TPT * ty + i][g]);
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) b[j] = *reinterpret_cast<const float4*>(&ws[tx + 32 * j][g]);
+#pragma unroll
+            for (int i = 0; i < TPT; ++i)
+#pragma unroll
+                for (int j = 0; j < EPT; ++j) {
+                    float s = __fadd_rn(__fmul_rn(a[i].x, b[j].x), __fmul_rn(a[i].y, b[j].y));
+                    s = __fadd_rn(s, __fmul_rn(a[i].z, b[j].z));
+                    s = __fadd_rn(s, __fmul_rn(a[i].w, b[j].w));
+                    acc[i][j] = __fadd_rn(acc[i][j], s);
+                }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TPT; ++i)
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            const int64_t t = t0 + TPT * ty + i;
+            const int e = e0 + tx + 32 * j;
+            if (t < N && e < ne) logits[t * ne + e] = acc[i][j];
+        }
+}
+
+constexpr int RF_WARPS = 8;
+__global__ void __launch_bounds__(RF_WARPS * 32)
+route_finish_kernel(const float* __restrict__ logits, const float* __restrict__ router_bias, float* __restrict__ probs_out,
+                    int32_t* __restrict__ idx_out, float* __restrict__ w_out, int64_t N, int ne, int K) {
+    __shared__ float s_p[RF_WARPS][MOE_MAX_NE], s_sel[RF_WARPS][MOE_MAX_NE], s_w[RF_WARPS][MOE_MAX_K];
+    __shared__ int s_idx[RF_WARPS][MOE_MAX_K];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * RF_WARPS + warp;
+    if (t >= N) return;
+    route_finish_warp(logits + t * ne, router_bias, ne, K, s_p[warp], s_sel[warp], s_idx[warp], s_w[warp],
+                      probs_out ? probs_out + t * ne : nullptr, lane);
+    if (lane < K) {
+        idx_out[t * K + lane] = s_idx[warp][lane];
+        w_out[t * K + lane] = s_w[warp][lane];
+    }
+}
+
 int moe_route(const float* x, const float* router_w, const float* router_bias, float* probs,
               int32_t* idx, float* w, int64_t N, int d, int ne, int K) {
+    if (N >= 16 && d % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        void* wsp;
+        int rc = workspace(WS_ROUTE).ensure((size_t)N * ne * 4 + 256, &wsp);
+        if (rc) return rc;
+        float* logits = static_cast<float*>(wsp);
+        if (N <= 1024) {
+            const dim3 grid((unsigned)ceil_div64(N, 8), ceil_div(ne, 32));
+            route_logits_kernel<1, 1><<<grid, 256, 0, stream()>>>(x, router_w, logits, N, d, ne);
+        } else {
+            const dim3 grid((unsigned)ceil_div64(N, 32), ceil_div(ne, 64));
+            route_logits_kernel<4, 2><<<grid, 256, 0, stream()>>>(x, router_w, logits, N, d, ne);
+        }
+        B200_LAUNCH_CHECK("route_logits_kernel");
+        route_finish_kernel<<<(unsigned)ceil_div64(N, RF_WARPS), RF_WARPS * 32, 0, stream()>>>(logits, router_bias, probs,
+                                                                                                  idx, w, N, ne, K);
+        B200_LAUNCH_CHECK("route_finish_kernel");
+        return B200_OK;
+    }
     // shared memory: x + as many group rows as fit in ~96 KB
     const int groups = d >> 2;
     const size_t x_bytes = (size_t)((d + 3) & ~3) * 4;
@@ -360,6 +468,15 @@ int moe_forward(const float* x, const float* router_w, const float* router_bias,
                          (!shared || SH % q_block_elems(kind) == 0),
                      "moe_forward: d, E and SH must be multiples of the quantisation block");
     B200_REQUIRE(N * K < ((int64_t)1 << 31), "moe_forward: N too large");
+
+    // Many tokens over fp16 / packed experts: expert-grouped tensor-core GEMMs.  The
+    // optional fp32 scratch outputs only exist on the token-major path.
+    auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (N >= GEMM_MIN_ROWS && kind != KIND_F32 && !s_gate && !s_up && !s_act && aligned16(x) && aligned16(out) &&
+        aligned16(gates) && aligned16(ups) && aligned16(downs) &&
+        (!shared || (aligned16(sh_g) && aligned16(sh_u) && aligned16(sh_d))))
+        return moe_forward_grouped(x, router_w, router_bias, gates, ups, downs, sh_g, sh_u, sh_d, out, probs_cache,
+                                   idx_cache, w_cache, N, d, E, ne, K, shared ? SH : 0, kind);
 
     // workspace: idx | w | act | sh_act
     const size_t NK = (size_t)N * K;

@@ -49,3 +49,26 @@ def sync():
 SUM_ORDER = dict(rtol=2e-4, atol=2e-5)
 # The stated bound for activations/logits vs the reference CPU path:
 ACTIVATION = dict(rtol=1e-2, atol=2e-2)
+# From this many activation rows on, linears over fp16 / packed weights run as
+# tensor-core GEMMs on fp16 copies of the activations, as the reference's cuBLAS path
+# does (cuda/kernels.cu:600-633); csrc/gemm.cuh holds the same constant.
+GEMM_MIN_ROWS = 32
+
+
+def fp16_close(got, want, frac=4e-3):
+    """Results of the tensor-core path against an fp32 computation: operands were
+    rounded to fp16 (2^-11 relative each), so the error is bounded relative to the
+    scale of the output, not element by element."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    assert got.shape == want.shape
+    scale = float(np.abs(want).max())
+    err = float(np.abs(got - want).max())
+    assert np.isfinite(got).all() and err <= frac * scale + 1e-6, f"max error {err:.3e} vs scale {scale:.3e}"
+
+
+def close(got, want, rows, tol):
+    """tol (an assert_allclose dict) below GEMM_MIN_ROWS rows, fp16_close from there on."""
+    if rows >= GEMM_MIN_ROWS:
+        fp16_close(got, want)
+    else:
+        np.testing.assert_allclose(got, want, **tol)

@@ -1,0 +1,103 @@
+"""GPU parity: the expert-parallel building blocks of the C ABI.
+
+One GPU is enough: world_size 1 runs jdm-ghassan_v1_flach_b200/ep.py end to end on the
+device, and G virtual ranks are emulated in one process by carrying the rows between
+the per-rank steps with tensor copies where the ranks would use all-to-all - the
+device code (routing of a slice, packing, experts on (source, expert) blocks through
+the group map, combine) is exactly what a rank runs."""
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+from cases import moe_case
+
+pytestmark = pytest.mark.gpu
+
+ep = importlib.import_module("jdm-ghassan_v1_flach_b200.ep")
+
+
+def _dev_case(oracle, seed, T, d, E, ne, K, SH, wkind):
+    from gpu_util import dev
+    c = moe_case(oracle, seed, T, d, E, ne, K, SH, wkind)
+    return c, {k: dev(v) for k, v in c.items()}
+
+
+def _single_gpu_layer(dc, T, d, E, ne, K, SH, wkind):
+    from gpu_util import empty, host, ops
+    out, idx = empty((T, d)), empty((T, K), torch.int32)
+    ops.moe_forward_bias_half(dc["x"], dc["router_w"], dc["router_bias"], dc["gates"], dc["ups"], dc["downs"], dc["sh_g"],
+                              dc["sh_u"], dc["sh_d"], out, None, idx, None, None, None, None, T, d, E, ne, K, SH, wkind)
+    return host(out), host(idx)
+
+
+@pytest.mark.parametrize("wkind,d,E,SH", [(3, 256, 256, 512), (-1, 128, 64, 64), (2, 256, 256, 256)])
+def test_world_size_one_equals_the_layer(oracle, wkind, d, E, SH):
+    from gpu_util import host
+    T, ne, K = 96, 16, 2
+    c, dc = _dev_case(oracle, 7, T, d, E, ne, K, SH, wkind)
+    layer = ep.ExpertParallelMoE(d, E, ne, K, SH, wkind, dc["router_w"], dc["router_bias"], dc["gates"], dc["ups"],
+                                 dc["downs"], (dc["sh_g"], dc["sh_u"], dc["sh_d"]))
+    out, idx = layer.forward(dc["x"])
+    want, want_idx = _single_gpu_layer(dc, T, d, E, ne, K, SH, wkind)
+    assert np.array_equal(host(idx), want_idx)
+    # same kernels, same order of additions: identical bits
+    assert np.array_equal(host(out).view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("G", [2, 4, 8])
+def test_virtual_ranks_equal_the_layer(oracle, G):
+    """Config-3 shape (hidden 1536, 64 experts, top-6, Q4_K) on 200 tokens, G ranks emulated."""
+    from gpu_util import fp16_close, host
+    T, d, E, ne, K, SH, wkind = 200, 1536, 512, 64, 6, 1024, 3
+    c, dc = _dev_case(oracle, 11, T, d, E, ne, K, SH, wkind)
+    be = ep.CudaBackend()
+    nl = ne // G
+    shards = [tuple(ep.shard_experts(dc[k], ne, r, G) for k in ("gates", "ups", "downs")) for r in range(G)]
+    # phase 1 on every rank: route + pack its slice
+    st = []
+    for r in range(G):
+        lo, hi = ep.token_slice(T, r, G)
+        xs = dc["x"][lo:hi].contiguous()
+        idx, w = be.route(xs, dc["router_w"], dc["router_bias"], ne, K)
+        rows, inv, offsets = be.dispatch_pack(xs, idx, ne)
+        counts = (offsets[1:] - offsets[:-1]).view(G, nl)
+        st.append(dict(xs=xs, idx=idx, w=w, rows=rows, inv=inv, offsets=offsets, counts=counts))
+    # "all-to-all": destination q receives from every source r its block of rows
+    outs = [None] * G
+    y_back = [[None] * G for _ in range(G)]          # [source][dest] results travelling home
+    for q in range(G):
+        blocks, cnts = [], []
+        for r in range(G):
+            o = st[r]["offsets"]
+            lo, hi = int(o[q * nl]), int(o[(q + 1) * nl])
+            blocks.append(st[r]["rows"][lo:hi])
+            cnts.append(st[r]["counts"][q])
+        got = torch.cat(blocks, 0)
+        recv_counts = torch.cat(cnts).to(torch.int32)
+        goff = torch.zeros(G * nl + 1, dtype=torch.int32, device="cuda")
+        goff[1:] = torch.cumsum(recv_counts, 0)
+        gmap = torch.arange(nl, dtype=torch.int32, device="cuda").repeat(G)
+        y = be.experts_rows(got, goff, gmap, *shards[q], nl, d, E, wkind)
+        pos = 0
+        for r in range(G):
+            n = int(cnts[r].sum())
+            y_back[r][q] = y[pos:pos + n]
+            pos += n
+    sh = (dc["sh_g"], dc["sh_u"], dc["sh_d"])
+    for r in range(G):
+        y = torch.cat(y_back[r], 0)
+        outs[r] = be.shared_combine(st[r]["xs"], sh, y, st[r]["inv"], st[r]["w"], K, SH, wkind)
+    out = host(torch.cat(outs, 0))
+    idx = host(torch.cat([s["idx"] for s in st], 0))
+    want, want_idx = _single_gpu_layer(dc, T, d, E, ne, K, SH, wkind)
+    assert np.array_equal(idx, want_idx)                          # routing identical to the 1-GPU run
+    # every row is the same dot products in the same order, whichever tile it sat in
+    assert np.array_equal(out.view(np.uint32), want.view(np.uint32))
+    # and the layer itself against the CPU oracle on a sample of tokens
+    sample = np.array([0, 1, 99, 100, 199])
+    sub = dict(c, x=np.ascontiguousarray(c["x"][sample]))
+    ref, _, _, _ = oracle.moe_forward(sub["x"], c["router_w"], c["router_bias"], c["gates"], c["ups"], c["downs"],
+                                      c["sh_g"], c["sh_u"], c["sh_d"], d, E, ne, K, SH, wkind)
+    fp16_close(out[sample], ref)

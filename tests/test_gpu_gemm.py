@@ -35,9 +35,13 @@ def test_linear_fp16_many_tokens(oracle, M, K, N):
 
 
 @pytest.mark.parametrize("kind", [0, 1, 2, 3])
-@pytest.mark.parametrize("M,K,N", [(64, 1536, 6448), (257, 512, 1536)])
+@pytest.mark.parametrize("M,K,N", [(64, 1536, 6448), (257, 512, 1536), (40, 160, 72), (300, 256, 128)])
 def test_linear_packed_many_tokens(oracle, kind, M, K, N):
-    from gpu_util import ACTIVATION, SUM_ORDER, dev, empty, host, ops
+    """K a multiple of 256: weights dequantised inside the GEMM; otherwise (160 for the
+    32-weight kinds) through an fp16 copy."""
+    if kind == 3 and K % 256:
+        pytest.skip("Q4_K rows are multiples of 256 weights")
+    from gpu_util import ACTIVATION, SUM_ORDER, dev, empty, fp16_close, host, ops
     r = np.random.default_rng(10 * kind + M)
     x = r.standard_normal((M, K)).astype(np.float32)
     w = oracle.quantize((r.standard_normal(N * K) * 0.02).astype(np.float32), kind)
@@ -45,7 +49,12 @@ def test_linear_packed_many_tokens(oracle, kind, M, K, N):
     ops.linear_forward_q4(dev(x), dev(w), y, M, K, N, kind)
     got = host(y)
     w16 = oracle.dequantize(w, N * K, kind).reshape(N, K)          # the fp16-rounded weights
-    np.testing.assert_allclose(got, _fp16_product(x, w16), **SUM_ORDER)
+    if kind in (0, 2) or K % 256:
+        # the in-kernel expansion is exact for Q4_0 / Q8_0; the fp16-copy path always is
+        np.testing.assert_allclose(got, _fp16_product(x, w16), **SUM_ORDER)
+    else:
+        # Q4_1 / Q4_K inside the GEMM: fp16 FMAs, within one fp16 ulp of the rounded value
+        fp16_close(got, _fp16_product(x, w16), frac=1e-3)
     oracle.set_weight_rounding(True)
     try:
         rows = slice(0, min(M, 16))

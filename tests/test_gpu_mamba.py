@@ -65,7 +65,7 @@ def test_step_model_shapes(oracle, shape):
 @pytest.mark.parametrize("batch", [2, 8, 11, 64])
 def test_step_batched(oracle, batch):
     """batch independent sequences == batch single-sequence oracle steps."""
-    from gpu_util import SUM_ORDER, dev, empty, host, ops
+    from gpu_util import SUM_ORDER, close, dev, empty, host, ops
     c = mamba_case(oracle, 200 + batch, B=batch, T=1, d=256, n_heads=4, d_head=64, d_state=128, k=4, wkind=3)
     (x, w_in, conv_w, conv_b, dt_bias, a_log, D, norm_w, w_out, state,
      _, _, d, d_inner, conv_dim, n_heads, d_head, d_state, k, eps) = c["args"]
@@ -78,15 +78,15 @@ def test_step_batched(oracle, batch):
     for b in range(batch):
         want, wcs, wss = oracle.mamba2_step(x[b, 0], w_in, conv_w, conv_b, dt_bias, a_log, D, norm_w, w_out,
                                             cs[b], ss[b], d, d_inner, conv_dim, n_heads, d_head, d_state, k, eps, 3)
-        np.testing.assert_allclose(host(out)[b], want, **SUM_ORDER)
-        np.testing.assert_allclose(host(dss)[b], wss, **STATE_TOL)
-        np.testing.assert_allclose(host(dcs)[b], wcs, **SUM_ORDER)
+        close(host(out)[b], want, batch, SUM_ORDER)
+        close(host(dss)[b], wss, batch, STATE_TOL)
+        close(host(dcs)[b], wcs, batch, SUM_ORDER)
 
 
 @pytest.mark.parametrize("B,T", [(1, 1), (2, 7), (1, 33), (3, 64), (1, 300)])
 @pytest.mark.parametrize("wkind", [-2, 2, 3])
 def test_forward_sequence(oracle, B, T, wkind):
-    from gpu_util import SUM_ORDER, dev, empty, host, ops
+    from gpu_util import SUM_ORDER, close, dev, empty, host, ops
     c = mamba_case(oracle, B * 1000 + T + wkind, B=B, T=T, d=256, n_heads=4, d_head=64, d_state=128, k=4, wkind=wkind)
     a = c["args"]
     want, want_state = oracle.mamba2_forward(*a, wkind)
@@ -96,8 +96,9 @@ def test_forward_sequence(oracle, B, T, wkind):
         ops.mamba2_forward(dev(a[0]), *pw, dstate, out, *a[10:])
     else:
         ops.mamba2_forward_half(dev(a[0]), *pw, dstate, out, *a[10:], wkind)
-    np.testing.assert_allclose(host(out), want, rtol=5e-4, atol=5e-5)
-    np.testing.assert_allclose(host(dstate), want_state, rtol=5e-4, atol=5e-6)
+    rows = B * T if wkind != -2 else 1          # fp32 weights never take the tensor-core path
+    close(host(out), want, rows, dict(rtol=5e-4, atol=5e-5))
+    close(host(dstate), want_state, rows, dict(rtol=5e-4, atol=5e-6))
 
 
 def test_forward_small_state_general_path(oracle):

@@ -40,6 +40,18 @@ def _ulp_close(a, b, maxulp=4):
     np.testing.assert_array_max_ulp(a, b, maxulp=maxulp)
 
 
+def _close(got, want, N, wkind):
+    """From 32 tokens on, fp16 / packed experts run as tensor-core GEMMs on fp16 copies
+    of the activations (and of the dequantised weights): compared relative to the
+    output scale.  Fewer tokens and fp32 experts stay in fp32: summation-order bound."""
+    from gpu_util import SUM_ORDER
+    if N >= 32 and wkind != -2:
+        scale = float(np.abs(want).max())
+        assert float(np.abs(got - want).max()) <= 4e-3 * scale, (float(np.abs(got - want).max()), scale)
+    else:
+        np.testing.assert_allclose(got, want, **SUM_ORDER)
+
+
 def _oracle(oracle, c, d, E, ne, K, SH, wkind):
     return oracle.moe_forward(c["x"], c["router_w"], c["router_bias"], c["gates"], c["ups"], c["downs"],
                               c["sh_g"], c["sh_u"], c["sh_d"], d, E, ne, K, SH, wkind)
@@ -56,20 +68,38 @@ def test_layer_small(oracle, wkind, N):
     assert np.array_equal(got["idx"], idx)                                # top-k indices bit-exact
     _ulp_close(got["probs"], probs)
     _ulp_close(got["w"], w)
-    np.testing.assert_allclose(got["out"], out, **SUM_ORDER)
+    _close(got["out"], out, N, wkind)
 
 
 @pytest.mark.parametrize("N", [1, 64, 512])
 def test_layer_config3_shape(oracle, N):
     """hidden 1536, 64 experts, top-6, ffn 512, shared 1024, Q4_K, skewed router bias."""
-    from gpu_util import SUM_ORDER
     d, E, ne, K, SH = 1536, 512, 64, 6, 1024
     c = moe_case(oracle, 300 + N, N, d, E, ne, K, SH, 3)
     got = _run(c, N, d, E, ne, K, SH, 3)
     out, probs, idx, w = _oracle(oracle, c, d, E, ne, K, SH, 3)
     assert np.array_equal(got["idx"], idx)
     _ulp_close(got["w"], w)
-    np.testing.assert_allclose(got["out"], out, **SUM_ORDER)
+    _close(got["out"], out, N, 3)
+
+
+def test_layer_config3_4096_tokens(oracle):
+    """The prefill-sized case: routing checked on every token, outputs on a sample of
+    tokens (a token's output depends on no other token), and run-to-run bit stability."""
+    d, E, ne, K, SH = 1536, 512, 64, 6, 1024
+    N = 4096
+    c = moe_case(oracle, 4096, N, d, E, ne, K, SH, 3)
+    got = _run(c, N, d, E, ne, K, SH, 3)
+    again = _run(c, N, d, E, ne, K, SH, 3)
+    assert np.array_equal(got["out"].view(np.uint32), again["out"].view(np.uint32))
+    probs, idx, w = oracle.moe_route(c["x"], c["router_w"], c["router_bias"], ne, K)
+    assert np.array_equal(got["idx"], idx)
+    _ulp_close(got["w"], w)
+    sample = np.array([0, 1, 127, 128, 2047, 4000, 4095])
+    sub = dict(c, x=np.ascontiguousarray(c["x"][sample]))
+    out, _, sidx, _ = _oracle(oracle, sub, d, E, ne, K, SH, 3)
+    assert np.array_equal(sidx, idx[sample])
+    _close(got["out"][sample], out, N, 3)
 
 
 def test_routing_bit_exact_many_tokens(oracle):
