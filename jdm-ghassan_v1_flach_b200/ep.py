@@ -46,7 +46,7 @@ class CudaBackend:
     def dispatch_pack(self, x, idx, ne):
         n, d = x.shape
         K = idx.shape[1]
-        rows = torch.empty((n * K, d), dtype=torch.int16, device=x.device)     # fp16 bits
+        rows = torch.empty((n * K, d), dtype=torch.float16, device=x.device)
         inv = torch.empty(n * K, dtype=torch.int32, device=x.device)
         offsets = torch.zeros(ne + 1, dtype=torch.int32, device=x.device)
         if n:
