@@ -403,6 +403,42 @@ def moe_layer_bench(lib, rank, world, tokens=4096, iters=10):
             "shape": "hidden 1536, 64 experts, top-6, ffn 512, shared 1024, Q4_K"}
 
 
+def gemm_only_bench():
+    """The many-token kernels alone: fp16 and Q4_K linears of the in_proj shape at 4096 rows,
+    and the MoE layer at 512 and 4096 tokens.  One JSON line; ~1 GB on the device."""
+    import torch
+    lib = importlib.import_module(PKG).lib()
+    M, K, N = 4096, 1536, 6448
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(M, K, device="cuda", generator=g)
+    w16 = (torch.randn(N, K, device="cuda", generator=g) * 0.02).half()
+    wq = torch.empty(N * K // 256 * 144, dtype=torch.uint8, device="cuda")
+    lib.b200_quantize(w16.float().reshape(-1).contiguous(), wq, N * K, 3)
+    y = torch.empty(M, N, device="cuda")
+    flops = 2.0 * M * K * N
+
+    def timed(fn, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    ms16 = timed(lambda: lib.b200_linear_forward_fp16(x, w16, y, M, K, N))
+    msq = timed(lambda: lib.b200_linear_forward_q4(x, wq, y, M, K, N, 3))
+    out = {"linear_fp16": {"M": M, "K": K, "N": N, "ms": ms16, "tflops": flops / ms16 / 1e9},
+           "linear_q4k": {"M": M, "K": K, "N": N, "ms": msq, "tflops": flops / msq / 1e9},
+           "moe_512": moe_layer_bench(lib, 0, 1, tokens=512), "moe_4096": moe_layer_bench(lib, 0, 1, tokens=4096)}
+    if lib.raw("b200_stream_status") != 0:
+        raise RuntimeError(lib.last_error())
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -415,7 +451,12 @@ def main():
     ap.add_argument("--graph", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--small", action="store_true", help="4-layer model (development only; not a bench number)")
+    ap.add_argument("--only", default="", choices=["", "gemm"],
+                    help="gemm: time the tensor-core linears and the MoE layer alone (small; also the profiling case)")
     args = ap.parse_args()
+    if args.only == "gemm":
+        gemm_only_bench()
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
