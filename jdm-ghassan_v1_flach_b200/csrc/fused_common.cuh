@@ -171,32 +171,103 @@ __device__ __forceinline__ void consumer_sum_d2(double& a, double& b, double* re
     for (int w = 0; w < SG_CONSUMERS; ++w) { a += red[w]; b += red[SG_CONSUMERS + w]; }
 }
 
-// Token m's activations from global memory (K floats at x) into
-// shared memory.  Each thread keeps its K/256 values in registers, so global memory
-// is read once and one barrier (three with a reduction) separates load from use.
+// Token m's activations from global memory (K floats at x) into shared memory.
+// A thread owns runs of four consecutive k (one 128-bit load each) and keeps them in
+// registers across the reduction, so global memory is read once, every load is in
+// flight before the first is used, and one barrier (three with a reduction)
+// separates load from use.  Eight neighbouring lanes hold one 32-wide sub-block, so
+// the sub-block sums of the tensor-core path take three shuffles.
 // RMS: v = x * inv_rms * norm_w in the reference's operand order
 // (core/math_cpu.cpp:299-316; inv from a double sum of squares); nw_s is norm_w
 // already in shared memory.  `extra` is summed over the consumer threads in the same
-// reduction and returned (used for the gated-norm partial sums).  On the tensor-core
-// path the 32 consecutive k of a sub-block sit in one warp, so the sub-block sums
-// are warp shuffles.  Consumer threads only; ends with a consumer barrier.
-constexpr int XV_REG = 8;
+// reduction and returned (used for the gated-norm partial sums).  Consumer threads
+// only; ends with a consumer barrier.  K % 32 == 0.
+constexpr int XQ_REG = 4;                          // runs per thread held in registers: K <= 4096
 template <int KIND, bool RMS, bool EXTRA>
 __device__ __forceinline__ double stage_x(const float* __restrict__ x, const float* nw_s, const XAct& xa, int m,
                                           float eps, double* red, double extra) {
     const int K = xa.K;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nv = (K + SG_CTHREADS - 1) / SG_CTHREADS;
     float* xs = UsesMma<KIND>::value ? nullptr : xa.xs + (size_t)m * xa.xs_tok;
     const size_t row = (size_t)(K + XH_PAD);
     __half* hi = UsesMma<KIND>::value ? xa.hi + (size_t)m * row : nullptr;
     __half* lo = UsesMma<KIND>::value ? xa.lo + (size_t)m * row : nullptr;
     float* f32 = (UsesMma<KIND>::value && xa.f32) ? xa.f32 + (size_t)m * K : nullptr;
     float* sx = UsesMma<KIND>::value ? xa.sumx + (size_t)m * (K >> 5) : nullptr;
-    // final value of activation k (k's validity is uniform per warp: K % 32 == 0)
+    const int nq = K >> 2;                                          // runs of four
+    const int nrun = (nq + SG_CTHREADS - 1) / SG_CTHREADS;
+    if (nrun <= XQ_REG && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        // final values of run q (k = 4q .. 4q+3); every lane of the warp calls this
+        auto emit4 = [&](int q, bool ok, float4 v) {
+            const int k = q << 2;
+            if (UsesMma<KIND>::value) {
+                __half h[4], l[4];
+                split_half(v.x, h[0], l[0]);
+                split_half(v.y, h[1], l[1]);
+                split_half(v.z, h[2], l[2]);
+                split_half(v.w, h[3], l[3]);
+                float t = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) t += __half2float(h[e]) + __half2float(l[e]);
+                if (!ok) t = 0.0f;
+                t += __shfl_xor_sync(0xffffffffu, t, 1);
+                t += __shfl_xor_sync(0xffffffffu, t, 2);
+                t += __shfl_xor_sync(0xffffffffu, t, 4);
+                if (ok) {
+                    // Q4_K keeps every aligned run of 8 in the order 0,2,1,3,4,6,5,7 (xh_index)
+                    const int a1 = KIND == 3 ? 2 : 1, a2 = KIND == 3 ? 1 : 2;
+                    const __half2 h01 = __halves2half2(h[0], h[a1]), h23 = __halves2half2(h[a2], h[3]);
+                    const __half2 l01 = __halves2half2(l[0], l[a1]), l23 = __halves2half2(l[a2], l[3]);
+                    *reinterpret_cast<uint2*>(hi + k) =
+                        make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+                    *reinterpret_cast<uint2*>(lo + k) =
+                        make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+                    if (f32) *reinterpret_cast<float4*>(f32 + k) = v;
+                    if ((lane & 7) == 0) sx[k >> 5] = t;
+                }
+            } else if (ok) {
+                *reinterpret_cast<float4*>(xs + xs_index<KIND>(k)) = v;
+            }
+        };
+        float4 v[XQ_REG];
+        double ss = 0.0;
+#pragma unroll
+        for (int j = 0; j < XQ_REG; ++j) {
+            const int q = j * SG_CTHREADS + threadIdx.x;
+            v[j] = (j < nrun && q < nq) ? *reinterpret_cast<const float4*>(x + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (RMS) ss += (double)v[j].x * v[j].x + (double)v[j].y * v[j].y + (double)v[j].z * v[j].z + (double)v[j].w * v[j].w;
+        }
+        float inv = 1.0f;
+        if (RMS) {
+            consumer_sum_d2(ss, extra, red);
+            const double inv_d = 1.0 / sqrt(ss / (double)K + (double)eps);
+            inv = isfinite(inv_d) ? (float)inv_d : 0.0f;
+        } else if (EXTRA) {
+            double z = 0.0;
+            consumer_sum_d2(extra, z, red);
+        }
+#pragma unroll
+        for (int j = 0; j < XQ_REG; ++j) {
+            if (j < nrun) {
+                const int q = j * SG_CTHREADS + threadIdx.x;
+                const bool ok = q < nq;
+                float4 o = v[j];
+                if (RMS && ok) {
+                    const float4 w4 = *reinterpret_cast<const float4*>(nw_s + 4 * q);
+                    o = make_float4(o.x * inv * w4.x, o.y * inv * w4.y, o.z * inv * w4.z, o.w * inv * w4.w);
+                }
+                emit4(q, ok, o);
+            }
+        }
+        consumer_sync();
+        return extra;
+    }
+    // wide or unaligned rows: one value per thread and pass, raw values parked in shared
+    // memory between the two passes of the normalisation
+    const int nv = (K + SG_CTHREADS - 1) / SG_CTHREADS;
     auto emit = [&](int j, float val) {
         const int k = j * SG_CTHREADS + threadIdx.x;
-        const bool ok = k < K;
+        const bool ok = k < K;                       // uniform per warp: K % 32 == 0
         if (UsesMma<KIND>::value) {
             __half h, l;
             split_half(val, h, l);
@@ -226,43 +297,21 @@ __device__ __forceinline__ double stage_x(const float* __restrict__ x, const flo
         return extra;
     }
     double ss = 0.0;
-    if (nv <= XV_REG) {
-        // the common case (K <= 2048): the token stays in registers across the reduction
-        float v[XV_REG];
-#pragma unroll
-        for (int j = 0; j < XV_REG; ++j) {
-            const int k = j * SG_CTHREADS + threadIdx.x;
-            v[j] = (j < nv && k < K) ? x[k] : 0.0f;
-            ss += (double)v[j] * v[j];
+    float* stash = UsesMma<KIND>::value ? f32 : xs;
+    for (int j = 0; j < nv; ++j) {
+        const int k = j * SG_CTHREADS + threadIdx.x;
+        if (k < K) {
+            const float val = x[k];
+            stash[UsesMma<KIND>::value ? k : xs_index<KIND>(k)] = val;
+            ss += (double)val * val;
         }
-        consumer_sum_d2(ss, extra, red);
-        const double inv_d = 1.0 / sqrt(ss / (double)K + (double)eps);
-        const float inv = isfinite(inv_d) ? (float)inv_d : 0.0f;
-#pragma unroll
-        for (int j = 0; j < XV_REG; ++j) {
-            if (j < nv) {
-                const int k = j * SG_CTHREADS + threadIdx.x;
-                emit(j, k < K ? v[j] * inv * nw_s[k] : 0.0f);
-            }
-        }
-    } else {
-        // wide rows: raw values parked in shared memory between the two passes
-        float* stash = UsesMma<KIND>::value ? f32 : xs;
-        for (int j = 0; j < nv; ++j) {
-            const int k = j * SG_CTHREADS + threadIdx.x;
-            if (k < K) {
-                const float val = x[k];
-                stash[UsesMma<KIND>::value ? k : xs_index<KIND>(k)] = val;
-                ss += (double)val * val;
-            }
-        }
-        consumer_sum_d2(ss, extra, red);
-        const double inv_d = 1.0 / sqrt(ss / (double)K + (double)eps);
-        const float inv = isfinite(inv_d) ? (float)inv_d : 0.0f;
-        for (int j = 0; j < nv; ++j) {
-            const int k = j * SG_CTHREADS + threadIdx.x;
-            emit(j, k < K ? stash[UsesMma<KIND>::value ? k : xs_index<KIND>(k)] * inv * nw_s[k] : 0.0f);
-        }
+    }
+    consumer_sum_d2(ss, extra, red);
+    const double inv_d = 1.0 / sqrt(ss / (double)K + (double)eps);
+    const float inv = isfinite(inv_d) ? (float)inv_d : 0.0f;
+    for (int j = 0; j < nv; ++j) {
+        const int k = j * SG_CTHREADS + threadIdx.x;
+        emit(j, k < K ? stash[UsesMma<KIND>::value ? k : xs_index<KIND>(k)] * inv * nw_s[k] : 0.0f);
     }
     consumer_sync();
     return extra;
