@@ -67,6 +67,7 @@ struct MoeFusedArgs {
     // filled per phase
     int rows_per_tile = 0, stage_bytes = 0, n_stages = 0;
     int* status = nullptr;
+    int* route_counter = nullptr;   // router tiles finished so far in this layer (returns to 0)
     bool dry = false;               // validate shapes and tiling, launch nothing
 };
 int moe_fused(MoeFusedArgs a, int kind);

@@ -317,6 +317,66 @@ __device__ __forceinline__ double stage_x(const float* __restrict__ x, const flo
     return extra;
 }
 
+// `cnt` vectors of K floats (src + r * src_stride) into token rows 0..cnt-1 of xa in
+// one pass: all loads in flight together, one barrier.  No normalisation.  Falls back
+// to one stage_x per vector when the runs do not fit the registers.
+template <int KIND>
+__device__ __forceinline__ void stage_rows(const float* __restrict__ src, int64_t src_stride, const XAct& xa, int cnt,
+                                           double* red) {
+    const int K = xa.K, nq = K >> 2, total = cnt * nq;
+    const int nrun = (total + SG_CTHREADS - 1) / SG_CTHREADS;
+    if (nrun > XQ_REG || (reinterpret_cast<uintptr_t>(src) & 15) != 0 || (src_stride & 3) != 0) {
+        for (int r = 0; r < cnt; ++r) stage_x<KIND, false, false>(src + r * src_stride, nullptr, xa, r, 0.0f, red, 0.0);
+        return;
+    }
+    const int lane = threadIdx.x & 31;
+    const size_t row = (size_t)(K + XH_PAD);
+    float4 v[XQ_REG];
+#pragma unroll
+    for (int j = 0; j < XQ_REG; ++j) {
+        const int i = j * SG_CTHREADS + threadIdx.x;
+        const int r = i / nq, q = i - r * nq;
+        v[j] = (j < nrun && i < total) ? *reinterpret_cast<const float4*>(src + r * src_stride + 4 * q)
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < XQ_REG; ++j) {
+        if (j < nrun) {
+            const int i = j * SG_CTHREADS + threadIdx.x;
+            const bool ok = i < total;
+            const int r = ok ? i / nq : 0, q = ok ? i - r * nq : 0, k = q << 2;
+            if (UsesMma<KIND>::value) {
+                __half h[4], l[4];
+                split_half(v[j].x, h[0], l[0]);
+                split_half(v[j].y, h[1], l[1]);
+                split_half(v[j].z, h[2], l[2]);
+                split_half(v[j].w, h[3], l[3]);
+                float t = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) t += __half2float(h[e]) + __half2float(l[e]);
+                if (!ok) t = 0.0f;
+                t += __shfl_xor_sync(0xffffffffu, t, 1);
+                t += __shfl_xor_sync(0xffffffffu, t, 2);
+                t += __shfl_xor_sync(0xffffffffu, t, 4);
+                if (ok) {
+                    const int a1 = KIND == 3 ? 2 : 1, a2 = KIND == 3 ? 1 : 2;
+                    const __half2 h01 = __halves2half2(h[0], h[a1]), h23 = __halves2half2(h[a2], h[3]);
+                    const __half2 l01 = __halves2half2(l[0], l[a1]), l23 = __halves2half2(l[a2], l[3]);
+                    *reinterpret_cast<uint2*>(xa.hi + r * row + k) =
+                        make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+                    *reinterpret_cast<uint2*>(xa.lo + r * row + k) =
+                        make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+                    if (xa.f32) *reinterpret_cast<float4*>(xa.f32 + (size_t)r * K + k) = v[j];
+                    if ((lane & 7) == 0) xa.sumx[(size_t)r * (K >> 5) + (k >> 5)] = t;
+                }
+            } else if (ok) {
+                *reinterpret_cast<float4*>(xa.xs + (size_t)r * xa.xs_tok + xs_index<KIND>(k)) = v[j];
+            }
+        }
+    }
+    consumer_sync();
+}
+
 // Dot products of a tile's rows with the staged activations of M tokens into
 // red_pass[part][row][token] (part stride RED_PASSES * RED_PASS floats).
 template <int KIND, int MT>

@@ -1,8 +1,9 @@
 // Fused decode-step kernels, part 2: the MoE layer for a few tokens in three
 // streamed kernels -
 //   phase 1  router logits in the reference's exact fp32 order + the shared
-//            expert's gate/up (SwiGLU activation)
-//   phase 2  softmax / top-K / mixture weights, then the routed experts' gate/up
+//            expert's gate/up (SwiGLU activation); the CTA that finishes the last
+//            router tile does softmax / top-K / mixture weights
+//   phase 2  the routed experts' gate/up
 //   phase 3  all down projections, weighted combine, residual add
 // Arithmetic followed: cpu::moe_forward_bias, core/moe_cpu.cpp:198-288.
 #include "fused_common.cuh"
@@ -60,6 +61,12 @@ __global__ void __launch_bounds__(SG_THREADS, 2) moe_phase1_kernel(MoeFusedArgs 
     p += (size_t)a.d * 4;
     float* gs = reinterpret_cast<float*>(p);                        // [SG_CONSUMERS][d/4]
     p += (size_t)SG_CONSUMERS * (a.d >> 2) * 4;
+    float* r_p = reinterpret_cast<float*>(p);           // routing scratch: [ne] [ne] [16] [16]
+    float* r_sel = r_p + a.ne;
+    float* r_w = r_sel + a.ne;
+    int* r_idx = reinterpret_cast<int*>(r_w + 16);
+    p = reinterpret_cast<uint8_t*>(r_idx + 16);
+    p = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 15) & ~(uintptr_t)15);
     float* red = reinterpret_cast<float*>(p);
     p += (size_t)RED_FLOATS * 4;
     ring.full = reinterpret_cast<uint64_t*>(p);
@@ -119,9 +126,34 @@ __global__ void __launch_bounds__(SG_THREADS, 2) moe_phase1_kernel(MoeFusedArgs 
                     const float lg = router_logit<KIND>(wrow, xa, m, gs + warp * (a.d >> 2), a.d, lane);
                     if (lane == 0) a.logits[(int64_t)m * a.ne + e] = lg;
                 }
+                if (lane == 0) __threadfence();
             }
             ring.release(i);
             consumer_sync();       // keeps the tile parity of the reduction buffers in step
+            // The CTA that completes the last router tile turns the logits into (idx, w):
+            // nobody waits - each tile counts itself in, and whoever counts last finds every
+            // logit published (fence before the count, fence after it).
+            if (warp == 0) {
+                int last = 0;
+                if (lane == 0) {
+                    __threadfence();
+                    last = atomicAdd(a.route_counter, 1) == n_router - 1;
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+                    for (int m = 0; m < a.M; ++m) {
+                        route_finish_warp(a.logits + (int64_t)m * a.ne, a.router_bias, a.ne, a.K, r_p, r_sel, r_idx, r_w,
+                                          a.probs_out ? a.probs_out + (int64_t)m * a.ne : nullptr, lane);
+                        if (lane < a.K) {
+                            a.idx[(int64_t)m * a.K + lane] = r_idx[lane];
+                            a.w[(int64_t)m * a.K + lane] = r_w[lane];
+                        }
+                        __syncwarp();
+                    }
+                    if (lane == 0) *a.route_counter = 0;       // ready for the next layer
+                }
+            }
         } else {
             const int r0 = (tile - n_router) * a.rows_per_tile;
             const int rows = min(a.rows_per_tile, a.SH - r0);
@@ -140,9 +172,9 @@ __global__ void __launch_bounds__(SG_THREADS, 2) moe_phase1_kernel(MoeFusedArgs 
 }
 
 // ---- phase 2 -------------------------------------------------------------------
-// grid (ctas, M): blockIdx.y is the token.  The producer warp turns the logits into
-// (idx, w) - every CTA computes the same values, CTA x == 0 publishes them - then
-// streams tiles (k, row tile) of expert idx[k]: R gate rows then R up rows.
+// grid (ctas, M): blockIdx.y is the token.  The producer warp reads the experts
+// phase 1 chose and streams tiles (k, row tile) of expert idx[k]: R gate rows then R
+// up rows.
 template <int KIND>
 __global__ void __launch_bounds__(SG_THREADS, 2) moe_phase2_kernel(MoeFusedArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -155,10 +187,7 @@ __global__ void __launch_bounds__(SG_THREADS, 2) moe_phase2_kernel(MoeFusedArgs 
     uint8_t* p = xact_carve<KIND>(xa, smem + (size_t)a.n_stages * a.stage_bytes, a.d, 1, true);
     float* nw_s = reinterpret_cast<float*>(p);
     p += (size_t)a.d * 4;
-    float* s_p = reinterpret_cast<float*>(p);          // [ne]
-    float* s_sel = s_p + a.ne;                          // [ne]
-    float* s_w = s_sel + a.ne;                          // [16]
-    int* s_idx = reinterpret_cast<int*>(s_w + 16);      // [16]
+    int* s_idx = reinterpret_cast<int*>(p);             // [16]
     p = reinterpret_cast<uint8_t*>(s_idx + 16);
     p = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 15) & ~(uintptr_t)15);
     float* red = reinterpret_cast<float*>(p);
@@ -179,12 +208,8 @@ __global__ void __launch_bounds__(SG_THREADS, 2) moe_phase2_kernel(MoeFusedArgs 
 
     if (warp == SG_CONSUMERS) {
         pdl_wait();
-        route_finish_warp(a.logits + (int64_t)m * a.ne, a.router_bias, a.ne, a.K, s_p, s_sel, s_idx, s_w,
-                          (blockIdx.x == 0 && a.probs_out) ? a.probs_out + (int64_t)m * a.ne : nullptr, lane);
-        if (blockIdx.x == 0 && lane < a.K) {
-            a.idx[(int64_t)m * a.K + lane] = s_idx[lane];
-            a.w[(int64_t)m * a.K + lane] = s_w[lane];
-        }
+        if (lane < a.K) s_idx[lane] = a.idx[(int64_t)m * a.K + lane];     // chosen by phase 1
+        __syncwarp();
         if (lane == 0) {
             int issued = 0;
             for (int i = 0; i < n_my; ++i) {
@@ -285,7 +310,7 @@ __global__ void __launch_bounds__(SG_THREADS, 2) moe_phase3_kernel(MoeFusedArgs 
     pdl_wait();
     if (threadIdx.x < a.K) s_w[threadIdx.x] = a.w[(int64_t)m * a.K + threadIdx.x];
     if (a.SH > 0) stage_x<KIND, false, false>(a.sh_act + (int64_t)m * a.SH, nullptr, xsh, 0, 0.0f, red_d, 0.0);
-    for (int k = 0; k < a.K; ++k) stage_x<KIND, false, false>(a.act + ((int64_t)m * a.K + k) * a.E, nullptr, xe, k, 0.0f, red_d, 0.0);
+    stage_rows<KIND>(a.act + (int64_t)m * a.K * a.E, a.E, xe, a.K, red_d);
     const int e_row = threadIdx.x >> 3, e_m = threadIdx.x & 7;
     for (int i = 0; i < n_my; ++i) {
         const int r0 = (first + i * step) * a.rows_per_tile;
@@ -363,7 +388,8 @@ static int moe_fused_kind(MoeFusedArgs a) {
         p1.rows_per_tile = R;
         const size_t stage = std::max<size_t>((size_t)ROUTER_ROWS * a.d * 4, (size_t)2 * R * rb_d);
         p1.stage_bytes = (int)((stage + 127) / 128 * 128);
-        const size_t other = xact_bytes<KIND>(a.d, mt, true) + (size_t)a.d * 4 + (size_t)SG_CONSUMERS * (a.d / 4) * 4 + fixed;
+        const size_t other = xact_bytes<KIND>(a.d, mt, true) + (size_t)a.d * 4 + (size_t)SG_CONSUMERS * (a.d / 4) * 4 +
+                             (size_t)2 * a.ne * 4 + 128 + 16 + fixed;
         p1.n_stages = pick_stages(p1.stage_bytes, other);
         if (p1.n_stages < 2) return fail(B200_EUNSUPPORTED, "moe_fused: hidden size %d does not fit the shared-memory staging", a.d);
         const int tiles = ceil_div(a.ne, ROUTER_ROWS) + (a.SH > 0 ? ceil_div(a.SH, R) : 0);
@@ -388,7 +414,7 @@ static int moe_fused_kind(MoeFusedArgs a) {
         if (R < 1 || !tail_tile_ok(a.E, R, rb_d)) return fail(B200_EUNSUPPORTED, "moe_fused: row size cannot be tiled to 16 bytes");
         p2.rows_per_tile = R;
         p2.stage_bytes = (int)(((size_t)2 * R * rb_d + 127) / 128 * 128);
-        const size_t other = xact_bytes<KIND>(a.d, 1, true) + (size_t)a.d * 4 + (size_t)2 * a.ne * 4 + 128 + 16 + fixed;
+        const size_t other = xact_bytes<KIND>(a.d, 1, true) + (size_t)a.d * 4 + 64 + 16 + fixed;
         p2.n_stages = pick_stages(p2.stage_bytes, other);
         if (p2.n_stages < 2) return fail(B200_EUNSUPPORTED, "moe_fused: hidden size %d does not fit the shared-memory staging", a.d);
         const int tiles = a.K * ceil_div(a.E, R);
@@ -429,6 +455,7 @@ int moe_fused(MoeFusedArgs a, int kind) {
     if (kind == 3) B200_REQUIRE(a.d % 256 == 0 && a.E % 256 == 0 && a.SH % 256 == 0, "moe_fused: Q4_K needs multiples of 256");
     B200_REQUIRE((reinterpret_cast<uintptr_t>(a.router_w) & 15) == 0, "moe_fused: router_w must be 16-byte aligned");
     a.status = stream_status_ptr();
+    a.route_counter = a.status ? a.status + 8 : nullptr;      // a word of the same zero-initialised block
     B200_REQUIRE(a.status, "moe_fused: status word allocation failed");
     switch (kind) {
         case 0: return moe_fused_kind<0>(a);

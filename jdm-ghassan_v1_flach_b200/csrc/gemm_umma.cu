@@ -13,15 +13,19 @@
 // Grouped form: the rows of A are partitioned into `groups` consecutive ranges
 // (offsets[g] .. offsets[g+1], device memory) and range g multiplies rows
 // [g*N, (g+1)*N) of B - the expert-sorted token rows of the MoE layer.  The tile
-// list is the concatenation of every group's 128-row tiles; a CTA finds its own by
+// list is the concatenation of every group's 128-row tiles; a CTA finds a tile by
 // walking the offsets, so no host synchronisation is needed to size the grid.
 //
-// One CTA = one 128 x 128 output tile, 192 threads:
+// Persistent kernel: one CTA per SM walks the 128 x 128 output tiles t = blockIdx.x,
+// + gridDim.x, ...  The operand ring runs on across tile boundaries and there are
+// two accumulators in tensor memory, so the epilogue of one tile overlaps the main
+// loop of the next.
 //   warp 0      TMA producer (one lane): A tile and B tile(s) of each 64-wide K block
 //   warp 1      tensor-memory allocation, MMA issue (one lane), deallocation
 //   warps 2..5  epilogue, one 32-row quarter of the accumulator each
 // Every mbarrier wait is bounded; when a bound is hit the kernel raises the status
-// word, skips its stores, and still releases its tensor memory.
+// word, the role that hit it stops, the others run into their own bounds, nothing
+// more is stored, and the tensor memory is still released.
 #include <cuda_fp16.h>
 
 #include <map>
@@ -42,6 +46,7 @@ struct alignas(64) GemmArgs {
     const int32_t* offsets;             // device [groups + 1], or null: one group [0, M)
     const int32_t* group_map;           // device [groups]: which N-row block of B a group uses; null = its own index
     int M, groups, N, K;
+    int m_slots, n_tiles;               // tile grid: slots along the rows (an upper bound when grouped) x column tiles
     float* c;                           // STORE: fp32 [M, ldc]
     __half* c16;                        // SWIGLU: fp16 [M, ldc]  silu(A.B^T) * (A.B2^T)
     int64_t ldc;
@@ -58,20 +63,48 @@ struct GemmShape {
     static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-// Epilogue of one 128 x 128 tile, run by the four warps whose index modulo 4 selects
-// the 32 accumulator rows (tensor-memory lanes) a warp may read.  Waits (bounded) for
-// the accumulator; a failed wait anywhere in the CTA leaves the status word set and
-// the stores are skipped (decided per warp: tcgen05.ld is a warp-wide instruction).
+// One tile of the walk.
+struct GemmTile {
+    int group, row0, row_end, n0, brow0;
+};
+
+// Tile t of the list -> coordinates; false when the slot lies past the last row tile
+// (the grouped list is sized by an upper bound).
+__device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, int t, GemmTile& w) {
+    int slot = t / a.n_tiles;
+    w.n0 = (t - slot * a.n_tiles) * GM_TILE_N;
+    w.group = 0; w.row0 = 0; w.row_end = a.M;
+    bool found = false;
+    if (!a.offsets) {
+        w.row0 = slot * GM_TILE_M;
+        found = w.row0 < a.M;
+    } else {
+        int lo = a.offsets[0];
+        for (int g = 0; g < a.groups; ++g) {
+            const int hi = a.offsets[g + 1];
+            const int tiles = (hi - lo + GM_TILE_M - 1) / GM_TILE_M;
+            if (slot < tiles) {
+                w.group = g; w.row0 = lo + slot * GM_TILE_M; w.row_end = hi;
+                found = true;
+                break;
+            }
+            slot -= tiles;
+            lo = hi;
+        }
+    }
+    w.brow0 = (a.group_map && found ? a.group_map[w.group] : w.group) * a.N + w.n0;
+    return found;
+}
+
+// Epilogue of one 128 x 128 tile out of the accumulator at `tacc`, run by the four
+// warps whose index modulo 4 selects the 32 accumulator rows (tensor-memory lanes) a
+// warp may read.
 template <int EPI>
-__device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tmem, uint64_t* accum, int warp, int lane,
-                                              int row0, int row_end, int n0) {
+__device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tacc, int warp, int lane, const GemmTile& w) {
     const int q = warp & 3;
-    const int row = row0 + q * 32 + lane;
-    bool ok = mbar_wait(accum, 0, a.status);
-    tc_fence_after();
-    ok = __all_sync(0xffffffffu, ok && *reinterpret_cast<volatile int*>(a.status) == 0);
-    if (!ok) return;
-    const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16);
+    const int row = w.row0 + q * 32 + lane;
+    const int row_end = w.row_end, n0 = w.n0;
+    const uint32_t tbase = tacc + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
     for (int c0 = 0; c0 < GM_TILE_N; c0 += 32) {
         float v[32];
@@ -107,26 +140,26 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tmem, 
     }
 }
 
-// Which tile blockIdx.y is: (group, first row, row limit); false when past the last tile.
-__device__ __forceinline__ bool gemm_find_tile(const GemmArgs& a, int& group, int& row0, int& row_end) {
-    int slot = blockIdx.y;
-    group = 0; row0 = 0; row_end = a.M;
-    if (!a.offsets) {
-        row0 = slot * GM_TILE_M;
-        return row0 < a.M;
+// The epilogue warps' loop over this CTA's tiles: wait for the accumulator, drain it,
+// hand it back to the MMA warp.  Stops storing as soon as the status word is raised.
+template <int EPI, int UN>
+__device__ __forceinline__ void gemm_epilogue_loop(const GemmArgs& a, uint32_t tmem, uint64_t* acc_full, uint64_t* acc_empty,
+                                                   int warp, int lane, int total) {
+    uint32_t ti = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x) {
+        GemmTile w;
+        if (!gemm_tile_at(a, t, w)) continue;
+        const int as = ti & 1;
+        bool ok = mbar_wait(&acc_full[as], (ti >> 1) & 1, a.status);
+        ok = __all_sync(0xffffffffu, ok && *reinterpret_cast<volatile int*>(a.status) == 0);
+        if (!ok) break;
+        tc_fence_after();
+        gemm_epilogue<EPI>(a, tmem + as * UN, warp, lane, w);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[as]);
+        ++ti;
     }
-    int lo = a.offsets[0];
-    for (int g = 0; g < a.groups; ++g) {
-        const int hi = a.offsets[g + 1];
-        const int tiles = (hi - lo + GM_TILE_M - 1) / GM_TILE_M;
-        if (slot < tiles) {
-            group = g; row0 = lo + slot * GM_TILE_M; row_end = hi;
-            return true;
-        }
-        slot -= tiles;
-        lo = hi;
-    }
-    return false;
 }
 
 template <int EPI>
@@ -136,14 +169,11 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE);
     uint64_t* empty = full + S::STAGES;
-    uint64_t* accum = empty + S::STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+    uint64_t* acc_full = empty + S::STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    int group, row0, row_end;
-    if (!gemm_find_tile(a, group, row0, row_end)) return;     // uniform for the whole CTA
-    const int n0 = blockIdx.x * GM_TILE_N;            // first output column inside the group
-    const int brow0 = (a.group_map ? a.group_map[group] : group) * a.N + n0;   // first row of B
+    const int total = a.m_slots * a.n_tiles;
     const int KB = (a.K + GM_TILE_K - 1) / GM_TILE_K;
 
     if (threadIdx.x == 0) {
@@ -151,11 +181,14 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(accum, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], 4);
+        }
         mbar_fence_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, S::UN);
+        tmem_alloc(tmem_slot, 2 * S::UN);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -165,49 +198,67 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
 
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < KB; ++kb) {
-                const int s = kb % S::STAGES;
-                if (kb >= S::STAGES && !mbar_wait(&empty[s], ((kb / S::STAGES) - 1) & 1, a.status)) break;
-                uint8_t* st = smem + (size_t)s * S::STAGE;
-                mbar_expect_tx(&full[s], S::STAGE);
-                tma_load_2d(st, &a.map_a, kb * GM_TILE_K, row0, &full[s]);
-                tma_load_2d(st + GM_STAGE_A, &a.map_b, kb * GM_TILE_K, brow0, &full[s]);
-                if (EPI == GEMM_EPI_SWIGLU)
-                    tma_load_2d(st + GM_STAGE_A + GM_TILE_N * GM_TILE_K * 2, &a.map_b2, kb * GM_TILE_K, brow0, &full[s]);
-                issued = kb + 1;
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                GemmTile w;
+                if (!gemm_tile_at(a, t, w)) continue;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % S::STAGES;
+                    if (it >= S::STAGES) ok = mbar_wait(&empty[s], ((it / S::STAGES) - 1) & 1, a.status);
+                    if (!ok) break;
+                    uint8_t* st = smem + (size_t)s * S::STAGE;
+                    mbar_expect_tx(&full[s], S::STAGE);
+                    tma_load_2d(st, &a.map_a, kb * GM_TILE_K, w.row0, &full[s]);
+                    tma_load_2d(st + GM_STAGE_A, &a.map_b, kb * GM_TILE_K, w.brow0, &full[s]);
+                    if (EPI == GEMM_EPI_SWIGLU)
+                        tma_load_2d(st + GM_STAGE_A + GM_TILE_N * GM_TILE_K * 2, &a.map_b2, kb * GM_TILE_K, w.brow0,
+                                    &full[s]);
+                }
             }
-            if (issued < KB) {
+            if (!ok) {
                 // gave up: do not leave with copies of this CTA still landing in shared memory
-                for (int kb = max(0, issued - S::STAGES); kb < issued; ++kb)
-                    if (!mbar_wait(&full[kb % S::STAGES], (kb / S::STAGES) & 1, a.status)) break;
+                for (uint32_t j = it > S::STAGES ? it - S::STAGES : 0; j < it; ++j)
+                    if (!mbar_wait(&full[j % S::STAGES], (j / S::STAGES) & 1, a.status)) break;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_f16(GM_TILE_M, S::UN);
+            uint32_t it = 0, ti = 0;
             bool ok = true;
-            for (int kb = 0; kb < KB && ok; ++kb) {
-                const int s = kb % S::STAGES;
-                ok = mbar_wait(&full[s], (kb / S::STAGES) & 1, a.status);
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                GemmTile w;
+                if (!gemm_tile_at(a, t, w)) continue;
+                const int as = ti & 1;
+                if (ti >= 2) ok = mbar_wait(&acc_empty[as], ((ti >> 1) - 1) & 1, a.status);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + (size_t)s * S::STAGE);
-                const uint32_t b_addr = a_addr + GM_STAGE_A;
+                const uint32_t tacc = tmem + as * S::UN;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % S::STAGES;
+                    ok = mbar_wait(&full[s], (it / S::STAGES) & 1, a.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)s * S::STAGE);
+                    const uint32_t b_addr = a_addr + GM_STAGE_A;
 #pragma unroll
-                for (int k = 0; k < GM_TILE_K / 16; ++k)
-                    umma_f16(tmem, umma_smem_desc(a_addr + k * 32), umma_smem_desc(b_addr + k * 32), idesc,
-                             kb > 0 || k > 0);
-                umma_commit(&empty[s]);               // the stage is free once these MMAs have read it
+                    for (int k = 0; k < GM_TILE_K / 16; ++k)
+                        umma_f16(tacc, umma_smem_desc(a_addr + k * 32), umma_smem_desc(b_addr + k * 32), idesc,
+                                 kb > 0 || k > 0);
+                    umma_commit(&empty[s]);           // the stage is free once these MMAs have read it
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[as]);           // accumulator complete
+                ++ti;
             }
-            umma_commit(accum);                       // accumulator complete (or as far as we got)
         }
     } else {
-        gemm_epilogue<EPI>(a, tmem, accum, warp, lane, row0, row_end, n0);
+        gemm_epilogue_loop<EPI, S::UN>(a, tmem, acc_full, acc_empty, warp, lane, total);
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, S::UN);
+    if (warp == 1) tmem_dealloc(tmem, 2 * S::UN);
 }
 
 // ===========================================================================
@@ -221,9 +272,10 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
 // fp16 (core/ops.cpp:313-336, :392), to within one fp16 ulp - and store the result in
 // the swizzled K-major layout the MMA reads.  HBM sees the packed bytes only.
 //
-//   warp 0      TMA: A tile per 64 of K, packed B per 256 of K
-//   warps 2..9  packed B (shared) -> fp16 B tile (shared, 2 buffers); 2..5 then run the epilogue
-//   warp 1      MMA when an A stage and a B tile are both ready
+//   warp 0       TMA: A tile per 64 of K, packed B per 256 of K
+//   warps 6..13  packed B (shared) -> fp16 B tile (shared, 2 buffers)
+//   warp 1       MMA when an A stage and a B tile are both ready
+//   warps 2..5   epilogue
 template <int KIND>
 struct PackedShape {
     static constexpr int SBB = 8 * (KIND == 3 ? 18 : q_block_bytes(KIND));   // bytes per row per 256 of K
@@ -319,8 +371,10 @@ __device__ __forceinline__ void dequant_half_block(const uint8_t* seg, int j, in
         *reinterpret_cast<uint4*>(rowp + (((4 * hh + c) ^ sw) << 4)) = *reinterpret_cast<const uint4*>(&out[4 * c]);
 }
 
+
 constexpr int GQ_EXPAND_WARPS = 8;
-constexpr int GQ_THREADS = 64 + GQ_EXPAND_WARPS * 32;
+constexpr int GQ_FIRST_EXPAND = 6;                 // warps 0, 1: TMA, MMA; 2..5: epilogue; 6..13: expansion
+constexpr int GQ_THREADS = (GQ_FIRST_EXPAND + GQ_EXPAND_WARPS) * 32;
 
 template <int EPI, int KIND>
 __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid_constant__ GemmArgs a) {
@@ -336,25 +390,22 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
     uint64_t* b_empty = b_full + S::SB;
     uint64_t* p_full = b_empty + S::SB;
     uint64_t* p_empty = p_full + 4;
-    uint64_t* accum = p_empty + 4;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+    uint64_t* acc_full = p_empty + 4;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    int group, row0, row_end;
-    if (!gemm_find_tile(a, group, row0, row_end)) return;
-    const int n0 = blockIdx.x * GM_TILE_N;
-    const int brow0 = (a.group_map ? a.group_map[group] : group) * a.N + n0;
+    const int total = a.m_slots * a.n_tiles;
     const int KB = a.K / GM_TILE_K;                   // K % 256 == 0 (host)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::SA; ++s) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
         for (int s = 0; s < S::SB; ++s) { mbar_init(&b_full[s], GQ_EXPAND_WARPS); mbar_init(&b_empty[s], 1); }
         for (int s = 0; s < S::SP; ++s) { mbar_init(&p_full[s], 1); mbar_init(&p_empty[s], GQ_EXPAND_WARPS); }
-        mbar_init(accum, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
         mbar_fence_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, S::UN);
+        tmem_alloc(tmem_slot, 2 * S::UN);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -364,73 +415,101 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
 
     if (warp == 0) {
         if (lane == 0) {
+            uint32_t it = 0, sbi = 0;                 // K blocks and packed super-blocks issued so far
             bool ok = true;
-            for (int kb = 0; kb < KB && ok; ++kb) {
-                if ((kb & 3) == 0) {
-                    const int sb = kb >> 2, p = sb % S::SP;
-                    if (sb >= S::SP) ok = mbar_wait(&p_empty[p], ((sb / S::SP) - 1) & 1, a.status);
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                GemmTile w;
+                if (!gemm_tile_at(a, t, w)) continue;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    if ((kb & 3) == 0) {
+                        const int p = sbi % S::SP;
+                        if (sbi >= S::SP) ok = mbar_wait(&p_empty[p], ((sbi / S::SP) - 1) & 1, a.status);
+                        if (!ok) break;
+                        uint8_t* dst = sm_p + (size_t)p * S::PACKED;
+                        mbar_expect_tx(&p_full[p], S::PACKED);
+                        tma_load_2d(dst, &a.map_b, (kb >> 2) * (S::SBB / 4), w.brow0, &p_full[p]);
+                        if (EPI == GEMM_EPI_SWIGLU)
+                            tma_load_2d(dst + GM_TILE_N * S::SBB, &a.map_b2, (kb >> 2) * (S::SBB / 4), w.brow0, &p_full[p]);
+                        ++sbi;
+                    }
+                    const int s = it % S::SA;
+                    if (it >= S::SA) ok = mbar_wait(&a_empty[s], ((it / S::SA) - 1) & 1, a.status);
                     if (!ok) break;
-                    uint8_t* dst = sm_p + (size_t)p * S::PACKED;
-                    mbar_expect_tx(&p_full[p], S::PACKED);
-                    tma_load_2d(dst, &a.map_b, sb * (S::SBB / 4), brow0, &p_full[p]);
-                    if (EPI == GEMM_EPI_SWIGLU)
-                        tma_load_2d(dst + GM_TILE_N * S::SBB, &a.map_b2, sb * (S::SBB / 4), brow0, &p_full[p]);
+                    mbar_expect_tx(&a_full[s], GM_STAGE_A);
+                    tma_load_2d(sm_a + (size_t)s * GM_STAGE_A, &a.map_a, kb * GM_TILE_K, w.row0, &a_full[s]);
                 }
-                const int s = kb % S::SA;
-                if (kb >= S::SA) ok = mbar_wait(&a_empty[s], ((kb / S::SA) - 1) & 1, a.status);
-                if (!ok) break;
-                mbar_expect_tx(&a_full[s], GM_STAGE_A);
-                tma_load_2d(sm_a + (size_t)s * GM_STAGE_A, &a.map_a, kb * GM_TILE_K, row0, &a_full[s]);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_f16(GM_TILE_M, S::UN);
-            for (int kb = 0; kb < KB; ++kb) {
-                const int s = kb % S::SA, b = kb % S::SB;
-                if (!mbar_wait(&a_full[s], (kb / S::SA) & 1, a.status)) break;
-                if (!mbar_wait(&b_full[b], (kb / S::SB) & 1, a.status)) break;
+            uint32_t it = 0, ti = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                GemmTile w;
+                if (!gemm_tile_at(a, t, w)) continue;
+                const int as = ti & 1;
+                if (ti >= 2) ok = mbar_wait(&acc_empty[as], ((ti >> 1) - 1) & 1, a.status);
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(sm_a + (size_t)s * GM_STAGE_A);
-                const uint32_t b_addr = smem_u32(sm_b + (size_t)b * S::B16);
+                const uint32_t tacc = tmem + as * S::UN;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % S::SA, b = it % S::SB;
+                    ok = mbar_wait(&a_full[s], (it / S::SA) & 1, a.status) &&
+                         mbar_wait(&b_full[b], (it / S::SB) & 1, a.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(sm_a + (size_t)s * GM_STAGE_A);
+                    const uint32_t b_addr = smem_u32(sm_b + (size_t)b * S::B16);
 #pragma unroll
-                for (int k = 0; k < GM_TILE_K / 16; ++k)
-                    umma_f16(tmem, umma_smem_desc(a_addr + k * 32), umma_smem_desc(b_addr + k * 32), idesc,
-                             kb > 0 || k > 0);
-                umma_commit(&a_empty[s]);
-                umma_commit(&b_empty[b]);
+                    for (int k = 0; k < GM_TILE_K / 16; ++k)
+                        umma_f16(tacc, umma_smem_desc(a_addr + k * 32), umma_smem_desc(b_addr + k * 32), idesc,
+                                 kb > 0 || k > 0);
+                    umma_commit(&a_empty[s]);
+                    umma_commit(&b_empty[b]);
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[as]);
+                ++ti;
             }
-            umma_commit(accum);
         }
+    } else if (warp < GQ_FIRST_EXPAND) {
+        gemm_epilogue_loop<EPI, S::UN>(a, tmem, acc_full, acc_empty, warp, lane, total);
     } else {
         // eight expanding warps: thread -> (B row, which 32 of the block's 64 weights)
-        const int t = threadIdx.x - 64, row_t = t & 127, hh = t >> 7;
+        const int x = threadIdx.x - GQ_FIRST_EXPAND * 32, row_t = x & 127, hh = x >> 7;
+        uint32_t it = 0, sbi = 0;
         bool ok = true;
-        for (int kb = 0; kb < KB && ok; ++kb) {
-            const int sb = kb >> 2, j = kb & 3, p = sb % S::SP, b = kb % S::SB;
-            if (j == 0) ok = mbar_wait(&p_full[p], (sb / S::SP) & 1, a.status);
-            if (ok && kb >= S::SB) ok = mbar_wait(&b_empty[b], ((kb / S::SB) - 1) & 1, a.status);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            const uint8_t* packed = sm_p + (size_t)p * S::PACKED;
-            uint8_t* tile = sm_b + (size_t)b * S::B16;
+        for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+            GemmTile w;
+            if (!gemm_tile_at(a, t, w)) continue;
+            for (int kb = 0; kb < KB; ++kb, ++it) {
+                const int j = kb & 3, b = it % S::SB;
+                if (j == 0) ++sbi;                    // sbi - 1 is the super-block in use
+                const int p = (sbi - 1) % S::SP;
+                if (j == 0) ok = mbar_wait(&p_full[p], ((sbi - 1) / S::SP) & 1, a.status);
+                if (ok && it >= S::SB) ok = mbar_wait(&b_empty[b], ((it / S::SB) - 1) & 1, a.status);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const uint8_t* packed = sm_p + (size_t)p * S::PACKED;
+                uint8_t* tile = sm_b + (size_t)b * S::B16;
 #pragma unroll
-            for (int rr = 0; rr < S::UN / 128; ++rr) {
-                const int r = row_t + rr * 128;
-                dequant_half_block<KIND>(packed + (size_t)r * S::SBB, j, hh, tile, r);
-            }
-            fence_proxy_async();                      // generic-proxy stores -> visible to the MMA
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&b_full[b]);
-                if (j == 3) mbar_arrive(&p_empty[p]);
+                for (int rr = 0; rr < S::UN / 128; ++rr) {
+                    const int r = row_t + rr * 128;
+                    dequant_half_block<KIND>(packed + (size_t)r * S::SBB, j, hh, tile, r);
+                }
+                fence_proxy_async();                  // generic-proxy stores -> visible to the MMA
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&b_full[b]);
+                    if (j == 3) mbar_arrive(&p_empty[p]);
+                }
             }
         }
-        if (warp < 6) gemm_epilogue<EPI>(a, tmem, accum, warp, lane, row0, row_end, n0);
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, S::UN);
+    if (warp == 1) tmem_dealloc(tmem, 2 * S::UN);
 }
 
 // ===========================================================================
@@ -555,10 +634,11 @@ static int launch_gemm_q(const GemmArgs& a) {
         B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM));
         configured = true;
     }
-    const int m_slots = (a.M + GM_TILE_M - 1) / GM_TILE_M + (a.offsets ? a.groups : 0);
-    B200_REQUIRE(m_slots <= 65535, "umma_gemm_q: too many row tiles (%d)", m_slots);
-    dim3 grid((a.N + GM_TILE_N - 1) / GM_TILE_N, m_slots);
-    kern<<<grid, GQ_THREADS, S::SMEM, stream()>>>(a);
+    GemmArgs b = a;
+    b.m_slots = (a.M + GM_TILE_M - 1) / GM_TILE_M + (a.offsets ? a.groups : 0);
+    b.n_tiles = (a.N + GM_TILE_N - 1) / GM_TILE_N;
+    const int grid = std::min(b.m_slots * b.n_tiles, num_sms());
+    kern<<<grid, GQ_THREADS, S::SMEM, stream()>>>(b);
     B200_LAUNCH_CHECK("umma_gemm_q_kernel");
     return B200_OK;
 }
@@ -611,10 +691,11 @@ static int launch_gemm(const GemmArgs& a) {
         B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM));
         configured = true;
     }
-    const int m_slots = (a.M + GM_TILE_M - 1) / GM_TILE_M + (a.offsets ? a.groups : 0);
-    dim3 grid((a.N + GM_TILE_N - 1) / GM_TILE_N, m_slots);
-    B200_REQUIRE(m_slots <= 65535, "umma_gemm: too many row tiles (%d)", m_slots);
-    kern<<<grid, GM_THREADS, S::SMEM, stream()>>>(a);
+    GemmArgs b = a;
+    b.m_slots = (a.M + GM_TILE_M - 1) / GM_TILE_M + (a.offsets ? a.groups : 0);
+    b.n_tiles = (a.N + GM_TILE_N - 1) / GM_TILE_N;
+    const int grid = std::min(b.m_slots * b.n_tiles, num_sms());
+    kern<<<grid, GM_THREADS, S::SMEM, stream()>>>(b);
     B200_LAUNCH_CHECK("umma_gemm_kernel");
     return B200_OK;
 }

@@ -13,10 +13,10 @@ namespace b200 {
 __device__ __forceinline__ void route_finish_warp(const float* __restrict__ logits, const float* __restrict__ bias,
                                                   int ne, int K, float* s_p, float* s_sel, int* s_idx, float* s_w,
                                                   float* probs_out, int lane) {
-    float mx = logits[0];
-    for (int e = lane; e < ne; e += 32) mx = fmaxf(mx, logits[e]);
+    float mx = __ldcg(logits);   // L2 loads: another CTA of the same kernel may have written the logits
+    for (int e = lane; e < ne; e += 32) mx = fmaxf(mx, __ldcg(logits + e));
     mx = warp_max(mx);
-    for (int e = lane; e < ne; e += 32) s_p[e] = (float)exp((double)__fsub_rn(logits[e], mx));
+    for (int e = lane; e < ne; e += 32) s_p[e] = (float)exp((double)__fsub_rn(__ldcg(logits + e), mx));
     __syncwarp();
     float inv = 0.0f;
     if (lane == 0) {
