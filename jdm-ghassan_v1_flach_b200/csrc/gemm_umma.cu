@@ -322,7 +322,7 @@ __device__ __forceinline__ void dequant_half_block(const uint8_t* seg, int j, in
     if (KIND == 3) {
         const uint4 hdr = *reinterpret_cast<const uint4*>(seg);
         int s, m;
-        q4k_scale_min(2 * j + hh, reinterpret_cast<const uint8_t*>(&hdr) + 4, s, m);
+        q4k_scale_min_regs(2 * j + hh, hdr.y, hdr.z, hdr.w, s, m);
         const __half d = __ushort_as_half((unsigned short)(hdr.x & 0xFFFF));
         const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
         const __half2 sc2 = __half2half2(__int2half_rn(s));

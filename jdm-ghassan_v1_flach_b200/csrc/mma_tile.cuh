@@ -90,9 +90,8 @@ __device__ __forceinline__ void tile_dot_q4k(const uint8_t* tile, int rb, int K,
             const int row = lane & 15, hi = lane >> 4;
             const uint8_t* hdr = tile + (size_t)row * rb + sb * 144;
             const uint4 h4 = *reinterpret_cast<const uint4*>(hdr);
-            const uint8_t* hb = reinterpret_cast<const uint8_t*>(&h4);
             int s, m;
-            q4k_scale_min(2 * j + hi, hb + 4, s, m);
+            q4k_scale_min_regs(2 * j + hi, h4.y, h4.z, h4.w, s, m);
             const float d = half_bits_to_float((uint16_t)(h4.x & 0xFFFF));
             const float dmin = half_bits_to_float((uint16_t)(h4.x >> 16));
             P = d * (float)s * (hi ? 0.0625f : 1.0f);

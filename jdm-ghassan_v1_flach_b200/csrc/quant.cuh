@@ -46,6 +46,21 @@ __device__ __forceinline__ void q4k_scale_min(int j, const uint8_t* sc, int& s, 
     }
 }
 
+// The same from the three 32-bit words that hold the 12 bytes (bytes 4..15 of the
+// super-block: y, z, w of a 16-byte header load): shifts and selects only, so a header
+// held in registers is never spilled to be indexed bytewise.
+__device__ __forceinline__ void q4k_scale_min_regs(int j, uint32_t y, uint32_t z, uint32_t w, int& s, int& m) {
+    const int sh = 8 * (j & 3);
+    const uint32_t by = (y >> sh) & 0xFFu, bz = (z >> sh) & 0xFFu, bw = (w >> sh) & 0xFFu;
+    if (j < 4) {
+        s = (int)(by & 63u);
+        m = (int)(bz & 63u);
+    } else {
+        s = (int)((bw & 0x0Fu) | ((by >> 6) << 4));
+        m = (int)((bw >> 4) | ((bz >> 6) << 4));
+    }
+}
+
 // One weight by flat index i, exact fp32 (used by the materialising dequantiser
 // and by slow general paths).
 template <int KIND>
@@ -110,10 +125,9 @@ __device__ __forceinline__ void load_unit(const uint8_t* row, int u, float (&w)[
         const int c = u & 7, grp = c >> 1;
         const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
         const uint4 qs = *reinterpret_cast<const uint4*>(blk + 16 + 16 * c);
-        const uint8_t* hb = reinterpret_cast<const uint8_t*>(&hdr);
         int s0, m0, s1, m1;
-        q4k_scale_min(2 * grp, hb + 4, s0, m0);
-        q4k_scale_min(2 * grp + 1, hb + 4, s1, m1);
+        q4k_scale_min_regs(2 * grp, hdr.y, hdr.z, hdr.w, s0, m0);
+        q4k_scale_min_regs(2 * grp + 1, hdr.y, hdr.z, hdr.w, s1, m1);
         const float d = half_bits_to_float((uint16_t)(hdr.x & 0xFFFF));
         const float dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
         const float d_lo = __fmul_rn(d, (float)s0), d_hi = __fmul_rn(d, (float)s1);
