@@ -287,12 +287,15 @@ struct GemmQShape {
     static constexpr int SBB = PackedShape<KIND>::SBB;
     static constexpr int B16 = UN * GM_TILE_K * 2;                  // one fp16 B tile
     static constexpr int PACKED = UN * SBB;                         // one packed stage
-    static constexpr int SA = 4, SB = 2;
+    // fp16 B tiles: enough of them that the expanding warps run ahead of the MMA rather
+    // than in lock-step with it (a hand-off costs a few hundred cycles either way)
+    static constexpr int SA = UN == 128 ? 4 : 3, SB = UN == 128 ? 4 : 3;
     static constexpr int FIXED = SA * GM_STAGE_A + SB * B16 + 1024 + 256;
     // packed stages: as many as fit (up to 4) - with few rows of A the kernel is a pure
     // weight stream and needs tens of KB in flight per SM to keep HBM busy
     static constexpr int ROOM = (227 * 1024 - FIXED) / PACKED;
     static constexpr int SP = ROOM >= 4 ? 4 : (ROOM >= 1 ? ROOM : 1);
+    static_assert(FIXED + PACKED <= 227 * 1024, "the stages do not fit the shared memory of an SM");
     static constexpr int SMEM = FIXED + SP * PACKED;
 };
 
