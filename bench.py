@@ -313,7 +313,7 @@ def run_reference_arm(args, rank):
         return
     cfg = H_TINY
     # every "step" is the same bounded sample; repeat it at most three times
-    secs, info = cpu_decode_token_seconds(cfg, args.ctx, reps=min(max(1, args.steps), 3))
+    secs, info = cpu_decode_token_seconds(cfg, args.ctx, reps=min(max(1, args.steps), 8))
     val = args.batch / secs
     line = {"impl": "reference", "metric": "decode tok/s", "value": val, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3, "higher_is_better": True,
@@ -401,6 +401,37 @@ def moe_layer_bench(lib, rank, world, tokens=4096, iters=10):
             "frac_of_dense_peak": flops / (ms * 1e-3) / 1e12 / (peak_tf * world), "n_gpus": world,
             "mode": "single GPU" if world == 1 else "expert parallel, NCCL all-to-all",
             "shape": "hidden 1536, 64 experts, top-6, ffn 512, shared 1024, Q4_K"}
+
+
+def batch_decode_bench(cfg, batch, ctx, steps, seed):
+    """Greedy decode of `batch` sequences at once (per-op mode: every projection and the
+    MoE layer run as tensor-core GEMMs over the batch; one CUDA graph per step).  Device
+    time only; returns the extra JSON object."""
+    import torch
+    model = DeviceModel(cfg, batch, ctx + steps + 16, seed=seed)
+    model.configure(0, 1)
+    g = torch.Generator(device="cuda").manual_seed(7 + seed)
+    tok = torch.randint(0, cfg["vocab"], (batch,), device="cuda", generator=g, dtype=torch.int32)
+    for _ in range(ctx):
+        model.step_dev(tok)
+    for _ in range(3):
+        model.step_dev(tok)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        model.step_dev(tok)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    step_bytes = model.step_bytes()
+    launches = model.launches()
+    model.close()
+    peak, _ = peaks()
+    return {"batch": batch, "ctx": ctx, "steps": steps, "ms_per_step": ms, "tok_s": batch / (ms * 1e-3),
+            "algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms * 1e-3) / 1e9,
+            "frac_of_hbm_peak": step_bytes / (ms * 1e-3) / 1e9 / peak, "launches_per_step": launches,
+            "mode": "per-op, tensor-core GEMM path, CUDA graph"}
 
 
 def gemm_only_bench():
@@ -554,6 +585,11 @@ def main():
     q4k_bytes = proj_n * d // 256 * 144
     q4k_gbs, q4k_ms = time_kernel_gbs(q4k_call, q4k_bytes, iters=len(mamba_layers) * 2)
     moe = moe_layer_bench(lib, rank, world)
+    batch64 = None
+    if world == 1 and B == 1 and not args.small:
+        model.close()
+        model = None
+        batch64 = batch_decode_bench(cfg, 64, 256, 16, seed=rank)
 
     if rank == 0:
         tok_s = B * args.steps * world / (ms_dev * 1e-3)
@@ -582,14 +618,16 @@ def main():
                                   "frac": q4k_gbs / peak, "kernel": "streamed Q4_K GEMV (in_proj [%d,%d])" % (proj_n, d),
                                   "ms_per_launch": q4k_ms, "algorithmic_bytes_per_launch": q4k_bytes},
             "moe_layer": moe,
+            "batch64": batch64,
         }
         if not args.no_cpu and world == 1:
-            secs, info = cpu_decode_token_seconds(cfg, args.ctx)
+            secs, info = cpu_decode_token_seconds(cfg, args.ctx, reps=8)
             line["cpu_baseline"] = dict(info, value=B / secs, unit="tok/s")
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line))
-    model.close()
+    if model is not None:
+        model.close()
     if world > 1:
         dist.destroy_process_group()
 
