@@ -95,10 +95,23 @@ mamba_step_scan_kernel(const float* __restrict__ bc, const float* __restrict__ d
     const float* Cv = Bv + p.d_state;
     float* s = ssm_state + ((int64_t)m * rows + row) * p.d_state;
     float acc = 0.0f;
-    for (int j = lane; j < p.d_state; j += 32) {
-        const float sn = __fadd_rn(__fmul_rn(dA, s[j]), __fmul_rn(__fmul_rn(dt, Bv[j]), xv));
-        s[j] = sn;
-        acc += Cv[j] * sn;
+    if (p.d_state == 128) {
+        // one 128-bit access per lane covers the row (same products, same order per element)
+        float4 sv = *reinterpret_cast<const float4*>(s + lane * 4);
+        const float4 b4 = *reinterpret_cast<const float4*>(Bv + lane * 4);
+        const float4 c4 = *reinterpret_cast<const float4*>(Cv + lane * 4);
+        sv.x = __fadd_rn(__fmul_rn(dA, sv.x), __fmul_rn(__fmul_rn(dt, b4.x), xv));
+        sv.y = __fadd_rn(__fmul_rn(dA, sv.y), __fmul_rn(__fmul_rn(dt, b4.y), xv));
+        sv.z = __fadd_rn(__fmul_rn(dA, sv.z), __fmul_rn(__fmul_rn(dt, b4.z), xv));
+        sv.w = __fadd_rn(__fmul_rn(dA, sv.w), __fmul_rn(__fmul_rn(dt, b4.w), xv));
+        *reinterpret_cast<float4*>(s + lane * 4) = sv;
+        acc = c4.x * sv.x + c4.y * sv.y + c4.z * sv.z + c4.w * sv.w;
+    } else {
+        for (int j = lane; j < p.d_state; j += 32) {
+            const float sn = __fadd_rn(__fmul_rn(dA, s[j]), __fmul_rn(__fmul_rn(dt, Bv[j]), xv));
+            s[j] = sn;
+            acc += Cv[j] * sn;
+        }
     }
     acc = warp_sum(acc);
     if (lane == 0) y[(int64_t)m * p.d_inner + row] = acc + Dv[h] * xv;

@@ -351,23 +351,47 @@ route_logits_kernel(const float* __restrict__ x, const float* __restrict__ route
     const int64_t t0 = (int64_t)blockIdx.x * RT_TOK;
     const int e0 = blockIdx.y * RT_EXP;
     float acc[TPT][EPT] = {};
-    for (int k0 = 0; k0 < d; k0 += RT_K) {
-        const int kc = min(RT_K, d - k0);              // a multiple of 4
-        __syncthreads();
-        for (int i = threadIdx.x; i < (RT_TOK + RT_EXP) * (RT_K / 4); i += 256) {
+    // The next 64 columns of the tile are fetched into registers while the current ones
+    // are consumed from shared memory, so the global-memory latency of a chunk is paid
+    // once, not once per chunk.
+    constexpr int ITEMS = (RT_TOK + RT_EXP) * (RT_K / 4);
+    constexpr int PER = (ITEMS + 255) / 256;
+    float4 pre[PER];
+    auto fetch = [&](int k0) {
+        const int kc = min(RT_K, d - k0);
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            const int i = u * 256 + threadIdx.x;
             const int row = i / (RT_K / 4), c4 = (i % (RT_K / 4)) * 4;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c4 < kc) {
+            if (i < ITEMS && c4 < kc) {
                 if (row < RT_TOK) {
                     if (t0 + row < N) v = *reinterpret_cast<const float4*>(x + (t0 + row) * d + k0 + c4);
                 } else if (e0 + row - RT_TOK < ne) {
                     v = *reinterpret_cast<const float4*>(router_w + (int64_t)(e0 + row - RT_TOK) * d + k0 + c4);
                 }
             }
-            float* dst = row < RT_TOK ? &xs[row][c4] : &ws[row - RT_TOK][c4];
-            *reinterpret_cast<float4*>(dst) = v;
+            pre[u] = v;
         }
+    };
+    auto park = [&]() {
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            const int i = u * 256 + threadIdx.x;
+            if (i < ITEMS) {
+                const int row = i / (RT_K / 4), c4 = (i % (RT_K / 4)) * 4;
+                float* dst = row < RT_TOK ? &xs[row][c4] : &ws[row - RT_TOK][c4];
+                *reinterpret_cast<float4*>(dst) = pre[u];
+            }
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < d; k0 += RT_K) {
+        const int kc = min(RT_K, d - k0);              // a multiple of 4
+        __syncthreads();                               // the previous chunk has been consumed
+        park();
         __syncthreads();
+        if (k0 + RT_K < d) fetch(k0 + RT_K);
         for (int g = 0; g < kc; g += 4) {
             float4 a[TPT], b[EPT];
 #pragma unroll
