@@ -47,6 +47,7 @@ struct alignas(64) GemmArgs {
     const int32_t* group_map;           // device [groups]: which N-row block of B a group uses; null = its own index
     int M, groups, N, K;
     int m_slots, n_tiles;               // tile grid: slots along the rows (an upper bound when grouped) x column tiles
+    int tile_m;                         // rows of A per slot: 128, or 256 = two accumulator halves sharing one B tile
     float* c;                           // STORE: fp32 [M, ldc]
     __half* c16;                        // SWIGLU: fp16 [M, ldc]  silu(A.B^T) * (A.B2^T)
     int64_t ldc;
@@ -76,15 +77,15 @@ __device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, int t, GemmTile&
     w.group = 0; w.row0 = 0; w.row_end = a.M;
     bool found = false;
     if (!a.offsets) {
-        w.row0 = slot * GM_TILE_M;
+        w.row0 = slot * a.tile_m;
         found = w.row0 < a.M;
     } else {
         int lo = a.offsets[0];
         for (int g = 0; g < a.groups; ++g) {
             const int hi = a.offsets[g + 1];
-            const int tiles = (hi - lo + GM_TILE_M - 1) / GM_TILE_M;
+            const int tiles = (hi - lo + a.tile_m - 1) / a.tile_m;
             if (slot < tiles) {
-                w.group = g; w.row0 = lo + slot * GM_TILE_M; w.row_end = hi;
+                w.group = g; w.row0 = lo + slot * a.tile_m; w.row_end = hi;
                 found = true;
                 break;
             }
@@ -142,19 +143,27 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tacc, 
 
 // The epilogue warps' loop over this CTA's tiles: wait for the accumulator, drain it,
 // hand it back to the MMA warp.  Stops storing as soon as the status word is raised.
-template <int EPI, int UN>
+// ACC accumulator sets of HALVES x UN columns each; half h holds rows row0 + 128 h ...
+template <int EPI, int UN, int ACC, int HALVES>
 __device__ __forceinline__ void gemm_epilogue_loop(const GemmArgs& a, uint32_t tmem, uint64_t* acc_full, uint64_t* acc_empty,
                                                    int warp, int lane, int total) {
     uint32_t ti = 0;
     for (int t = blockIdx.x; t < total; t += gridDim.x) {
         GemmTile w;
         if (!gemm_tile_at(a, t, w)) continue;
-        const int as = ti & 1;
-        bool ok = mbar_wait(&acc_full[as], (ti >> 1) & 1, a.status);
+        const int as = ti % ACC;
+        bool ok = mbar_wait(&acc_full[as], (ti / ACC) & 1, a.status);
         ok = __all_sync(0xffffffffu, ok && *reinterpret_cast<volatile int*>(a.status) == 0);
         if (!ok) break;
         tc_fence_after();
-        gemm_epilogue<EPI>(a, tmem + as * UN, warp, lane, w);
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h) {
+            if (w.row0 + GM_TILE_M * h < w.row_end) {
+                GemmTile wh = w;
+                wh.row0 += GM_TILE_M * h;
+                gemm_epilogue<EPI>(a, tmem + as * (HALVES * UN) + h * UN, warp, lane, wh);
+            }
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[as]);
@@ -254,7 +263,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
             }
         }
     } else {
-        gemm_epilogue_loop<EPI, S::UN>(a, tmem, acc_full, acc_empty, warp, lane, total);
+        gemm_epilogue_loop<EPI, S::UN, 2, 1>(a, tmem, acc_full, acc_empty, warp, lane, total);
     }
     tc_fence_before();
     __syncthreads();
@@ -289,8 +298,13 @@ struct GemmQShape {
     static constexpr int PACKED = UN * SBB;                         // one packed stage
     // fp16 B tiles: enough of them that the expanding warps run ahead of the MMA rather
     // than in lock-step with it (a hand-off costs a few hundred cycles either way)
-    static constexpr int SA = UN == 128 ? 4 : 3, SB = UN == 128 ? 4 : 3;
-    static constexpr int FIXED = SA * GM_STAGE_A + SB * B16 + 1024 + 256;
+    // A CTA owns 256 rows of A: two 128-row accumulator halves are fed by the same
+    // expanded B tile, which halves the expansion work per flop.  With 128 accumulator
+    // columns per half there is room for two sets (epilogue under the next main loop);
+    // the SwiGLU form (256 columns per half) has one.
+    static constexpr int A_STAGE = 2 * GM_STAGE_A;
+    static constexpr int SA = UN == 128 ? 3 : 2, SB = UN == 128 ? 3 : 2, ACC = UN == 128 ? 2 : 1;
+    static constexpr int FIXED = SA * A_STAGE + SB * B16 + 1024 + 256;
     // packed stages: as many as fit (up to 4) - with few rows of A the kernel is a pure
     // weight stream and needs tens of KB in flight per SM to keep HBM busy
     static constexpr int ROOM = (227 * 1024 - FIXED) / PACKED;
@@ -385,7 +399,7 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sm_a = smem;
-    uint8_t* sm_b = sm_a + S::SA * GM_STAGE_A;
+    uint8_t* sm_b = sm_a + S::SA * S::A_STAGE;
     uint8_t* sm_p = sm_b + S::SB * S::B16;
     uint64_t* a_full = reinterpret_cast<uint64_t*>(sm_p + S::SP * S::PACKED);
     uint64_t* a_empty = a_full + S::SA;
@@ -404,11 +418,11 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
         for (int s = 0; s < S::SA; ++s) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
         for (int s = 0; s < S::SB; ++s) { mbar_init(&b_full[s], GQ_EXPAND_WARPS); mbar_init(&b_empty[s], 1); }
         for (int s = 0; s < S::SP; ++s) { mbar_init(&p_full[s], 1); mbar_init(&p_empty[s], GQ_EXPAND_WARPS); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+        for (int s = 0; s < S::ACC; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
         mbar_fence_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 2 * S::UN);
+        tmem_alloc(tmem_slot, S::ACC * 2 * S::UN);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -438,8 +452,12 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
                     const int s = it % S::SA;
                     if (it >= S::SA) ok = mbar_wait(&a_empty[s], ((it / S::SA) - 1) & 1, a.status);
                     if (!ok) break;
-                    mbar_expect_tx(&a_full[s], GM_STAGE_A);
-                    tma_load_2d(sm_a + (size_t)s * GM_STAGE_A, &a.map_a, kb * GM_TILE_K, w.row0, &a_full[s]);
+                    const bool two = w.row0 + GM_TILE_M < w.row_end;      // second half holds rows of this tile
+                    mbar_expect_tx(&a_full[s], two ? S::A_STAGE : GM_STAGE_A);
+                    tma_load_2d(sm_a + (size_t)s * S::A_STAGE, &a.map_a, kb * GM_TILE_K, w.row0, &a_full[s]);
+                    if (two)
+                        tma_load_2d(sm_a + (size_t)s * S::A_STAGE + GM_STAGE_A, &a.map_a, kb * GM_TILE_K,
+                                    w.row0 + GM_TILE_M, &a_full[s]);
                 }
             }
         }
@@ -451,23 +469,30 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 GemmTile w;
                 if (!gemm_tile_at(a, t, w)) continue;
-                const int as = ti & 1;
-                if (ti >= 2) ok = mbar_wait(&acc_empty[as], ((ti >> 1) - 1) & 1, a.status);
+                const int as = ti % S::ACC;
+                if (ti >= S::ACC) ok = mbar_wait(&acc_empty[as], ((ti / S::ACC) - 1) & 1, a.status);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t tacc = tmem + as * S::UN;
+                const uint32_t tacc = tmem + as * (2 * S::UN);
+                const bool two = w.row0 + GM_TILE_M < w.row_end;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % S::SA, b = it % S::SB;
                     ok = mbar_wait(&a_full[s], (it / S::SA) & 1, a.status) &&
                          mbar_wait(&b_full[b], (it / S::SB) & 1, a.status);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(sm_a + (size_t)s * GM_STAGE_A);
+                    const uint32_t a_addr = smem_u32(sm_a + (size_t)s * S::A_STAGE);
                     const uint32_t b_addr = smem_u32(sm_b + (size_t)b * S::B16);
 #pragma unroll
                     for (int k = 0; k < GM_TILE_K / 16; ++k)
                         umma_f16(tacc, umma_smem_desc(a_addr + k * 32), umma_smem_desc(b_addr + k * 32), idesc,
                                  kb > 0 || k > 0);
+                    if (two) {
+#pragma unroll
+                        for (int k = 0; k < GM_TILE_K / 16; ++k)
+                            umma_f16(tacc + S::UN, umma_smem_desc(a_addr + GM_STAGE_A + k * 32),
+                                     umma_smem_desc(b_addr + k * 32), idesc, kb > 0 || k > 0);
+                    }
                     umma_commit(&a_empty[s]);
                     umma_commit(&b_empty[b]);
                 }
@@ -477,7 +502,7 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
             }
         }
     } else if (warp < GQ_FIRST_EXPAND) {
-        gemm_epilogue_loop<EPI, S::UN>(a, tmem, acc_full, acc_empty, warp, lane, total);
+        gemm_epilogue_loop<EPI, S::UN, S::ACC, 2>(a, tmem, acc_full, acc_empty, warp, lane, total);
     } else {
         // eight expanding warps: thread -> (B row, which 32 of the block's 64 weights)
         const int x = threadIdx.x - GQ_FIRST_EXPAND * 32, row_t = x & 127, hh = x >> 7;
@@ -512,7 +537,7 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, 2 * S::UN);
+    if (warp == 1) tmem_dealloc(tmem, S::ACC * 2 * S::UN);
 }
 
 // ===========================================================================
@@ -638,7 +663,8 @@ static int launch_gemm_q(const GemmArgs& a) {
         configured = true;
     }
     GemmArgs b = a;
-    b.m_slots = (a.M + GM_TILE_M - 1) / GM_TILE_M + (a.offsets ? a.groups : 0);
+    b.tile_m = 2 * GM_TILE_M;
+    b.m_slots = (a.M + b.tile_m - 1) / b.tile_m + (a.offsets ? a.groups : 0);
     b.n_tiles = (a.N + GM_TILE_N - 1) / GM_TILE_N;
     const int grid = std::min(b.m_slots * b.n_tiles, num_sms());
     kern<<<grid, GQ_THREADS, S::SMEM, stream()>>>(b);
@@ -695,7 +721,8 @@ static int launch_gemm(const GemmArgs& a) {
         configured = true;
     }
     GemmArgs b = a;
-    b.m_slots = (a.M + GM_TILE_M - 1) / GM_TILE_M + (a.offsets ? a.groups : 0);
+    b.tile_m = GM_TILE_M;
+    b.m_slots = (a.M + b.tile_m - 1) / b.tile_m + (a.offsets ? a.groups : 0);
     b.n_tiles = (a.N + GM_TILE_N - 1) / GM_TILE_N;
     const int grid = std::min(b.m_slots * b.n_tiles, num_sms());
     kern<<<grid, GM_THREADS, S::SMEM, stream()>>>(b);
