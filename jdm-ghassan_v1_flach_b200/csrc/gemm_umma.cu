@@ -40,6 +40,10 @@ namespace b200 {
 constexpr int GM_TILE_M = 128, GM_TILE_N = 128, GM_TILE_K = 64;
 constexpr int GM_THREADS = 192;
 constexpr int GM_STAGE_A = GM_TILE_M * GM_TILE_K * 2;
+// Per epilogue warp: a 32 x 32 fp32 block (rows padded to 33) through which the
+// accumulator rows a lane holds are turned into stores of whole 128-byte lines.
+constexpr int GM_EPI_LD = 33;
+constexpr int GM_EPI_SCRATCH = 4 * 32 * GM_EPI_LD * 4;
 
 struct alignas(64) GemmArgs {
     CUtensorMap map_a, map_b, map_b2;   // b2: the "up" matrix of the SwiGLU form
@@ -61,7 +65,7 @@ struct GemmShape {
     static constexpr int STAGE_B = UN * GM_TILE_K * 2;
     static constexpr int STAGE = GM_STAGE_A + STAGE_B;
     static constexpr int STAGES = EPI == GEMM_EPI_SWIGLU ? 4 : 6;
-    static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int SMEM = STAGES * STAGE + GM_EPI_SCRATCH + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 // One tile of the walk.
@@ -101,8 +105,10 @@ __device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, int t, GemmTile&
 // warps whose index modulo 4 selects the 32 accumulator rows (tensor-memory lanes) a
 // warp may read.
 template <int EPI>
-__device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tacc, int warp, int lane, const GemmTile& w) {
+__device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tacc, int warp, int lane, const GemmTile& w,
+                                              float* scratch) {
     const int q = warp & 3;
+    float* stg = scratch + q * 32 * GM_EPI_LD;
     const int row = w.row0 + q * 32 + lane;
     const int row_end = w.row_end, n0 = w.n0;
     const uint32_t tbase = tacc + ((uint32_t)(q * 32) << 16);
@@ -125,18 +131,28 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tacc, 
                     }
                 }
             }
+        } else if (n0 + c0 + 32 <= a.N && (a.ldc & 3) == 0) {
+            // lane = row in registers -> shared block -> eight lanes per row write one
+            // 128-byte line, four rows per instruction
+#pragma unroll
+            for (int i = 0; i < 32; ++i) stg[lane * GM_EPI_LD + i] = v[i] * a.scale;
+            __syncwarp();
+            const int cq = 4 * (lane & 7);
+#pragma unroll
+            for (int itr = 0; itr < 8; ++itr) {
+                const int r = itr * 4 + (lane >> 3);
+                const int grow = w.row0 + q * 32 + r;
+                const float* sp = stg + r * GM_EPI_LD + cq;
+                if (grow < row_end)
+                    *reinterpret_cast<float4*>(a.c + (int64_t)grow * a.ldc + n0 + c0 + cq) =
+                        make_float4(sp[0], sp[1], sp[2], sp[3]);
+            }
+            __syncwarp();
         } else if (row < row_end) {
             float* dst = a.c + (int64_t)row * a.ldc + n0 + c0;
-            if (n0 + c0 + 32 <= a.N && (a.ldc & 3) == 0) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 4)
-                    *reinterpret_cast<float4*>(dst + i) =
-                        make_float4(v[i] * a.scale, v[i + 1] * a.scale, v[i + 2] * a.scale, v[i + 3] * a.scale);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (n0 + c0 + i < a.N) dst[i] = v[i] * a.scale;
-            }
+            for (int i = 0; i < 32; ++i)
+                if (n0 + c0 + i < a.N) dst[i] = v[i] * a.scale;
         }
     }
 }
@@ -146,7 +162,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tacc, 
 // ACC accumulator sets of HALVES x UN columns each; half h holds rows row0 + 128 h ...
 template <int EPI, int UN, int ACC, int HALVES>
 __device__ __forceinline__ void gemm_epilogue_loop(const GemmArgs& a, uint32_t tmem, uint64_t* acc_full, uint64_t* acc_empty,
-                                                   int warp, int lane, int total) {
+                                                   int warp, int lane, int total, float* scratch) {
     uint32_t ti = 0;
     for (int t = blockIdx.x; t < total; t += gridDim.x) {
         GemmTile w;
@@ -161,7 +177,7 @@ __device__ __forceinline__ void gemm_epilogue_loop(const GemmArgs& a, uint32_t t
             if (w.row0 + GM_TILE_M * h < w.row_end) {
                 GemmTile wh = w;
                 wh.row0 += GM_TILE_M * h;
-                gemm_epilogue<EPI>(a, tmem + as * (HALVES * UN) + h * UN, warp, lane, wh);
+                gemm_epilogue<EPI>(a, tmem + as * (HALVES * UN) + h * UN, warp, lane, wh, scratch);
             }
         }
         tc_fence_before();
@@ -176,7 +192,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
     using S = GemmShape<EPI>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE);
+    float* epi_scratch = reinterpret_cast<float*>(smem + S::STAGES * S::STAGE);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE + GM_EPI_SCRATCH);
     uint64_t* empty = full + S::STAGES;
     uint64_t* acc_full = empty + S::STAGES;
     uint64_t* acc_empty = acc_full + 2;
@@ -263,7 +280,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
             }
         }
     } else {
-        gemm_epilogue_loop<EPI, S::UN, 2, 1>(a, tmem, acc_full, acc_empty, warp, lane, total);
+        gemm_epilogue_loop<EPI, S::UN, 2, 1>(a, tmem, acc_full, acc_empty, warp, lane, total, epi_scratch);
     }
     tc_fence_before();
     __syncthreads();
@@ -304,7 +321,7 @@ struct GemmQShape {
     // the SwiGLU form (256 columns per half) has one.
     static constexpr int A_STAGE = 2 * GM_STAGE_A;
     static constexpr int SA = UN == 128 ? 3 : 2, SB = UN == 128 ? 3 : 2, ACC = UN == 128 ? 2 : 1;
-    static constexpr int FIXED = SA * A_STAGE + SB * B16 + 1024 + 256;
+    static constexpr int FIXED = SA * A_STAGE + SB * B16 + GM_EPI_SCRATCH + 1024 + 256;
     // packed stages: as many as fit (up to 4) - with few rows of A the kernel is a pure
     // weight stream and needs tens of KB in flight per SM to keep HBM busy
     static constexpr int ROOM = (227 * 1024 - FIXED) / PACKED;
@@ -401,7 +418,8 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
     uint8_t* sm_a = smem;
     uint8_t* sm_b = sm_a + S::SA * S::A_STAGE;
     uint8_t* sm_p = sm_b + S::SB * S::B16;
-    uint64_t* a_full = reinterpret_cast<uint64_t*>(sm_p + S::SP * S::PACKED);
+    float* epi_scratch = reinterpret_cast<float*>(sm_p + S::SP * S::PACKED);
+    uint64_t* a_full = reinterpret_cast<uint64_t*>(sm_p + S::SP * S::PACKED + GM_EPI_SCRATCH);
     uint64_t* a_empty = a_full + S::SA;
     uint64_t* b_full = a_empty + S::SA;
     uint64_t* b_empty = b_full + S::SB;
@@ -502,7 +520,7 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
             }
         }
     } else if (warp < GQ_FIRST_EXPAND) {
-        gemm_epilogue_loop<EPI, S::UN, S::ACC, 2>(a, tmem, acc_full, acc_empty, warp, lane, total);
+        gemm_epilogue_loop<EPI, S::UN, S::ACC, 2>(a, tmem, acc_full, acc_empty, warp, lane, total, epi_scratch);
     } else {
         // eight expanding warps: thread -> (B row, which 32 of the block's 64 weights)
         const int x = threadIdx.x - GQ_FIRST_EXPAND * 32, row_t = x & 127, hh = x >> 7;
