@@ -399,6 +399,11 @@ int mamba2_step(const float* x, const void* w_in, const float* conv_w, const flo
     return linear(y, w_out, kind, out, batch, p.d_inner, p.d);
 }
 
+// mamba_ssd.cu
+int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, const float* a_log, const float* D,
+                   float* state, float* y, int B, int T, const MambaDims& p);
+constexpr int SSD_MIN_STEPS = 64;
+
 int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const float* conv_b,
                    const float* dt_bias, const float* a_log, const float* D, const float* norm_w,
                    const void* w_out, float* state, float* out, int B, int T, MambaDims p, int kind) {
@@ -425,7 +430,15 @@ int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const 
         mamba_conv_seq_kernel<<<grid, 256, 0, stream()>>>(proj, conv_w, conv_b, bc, B, T, p);
         B200_LAUNCH_CHECK("mamba_conv_seq_kernel");
     }
-    {
+    // Long sequences: the chunked form (all steps in parallel, a short carry over chunks);
+    // short ones and shapes outside its tiling: the sequential register-resident scan.
+    bool scanned = false;
+    if (T >= SSD_MIN_STEPS) {
+        rc = mamba_ssd_scan(proj, bc, dt_bias, a_log, D, state, y, B, T, p);
+        if (rc == B200_OK) scanned = true;
+        else if (rc != B200_EUNSUPPORTED) return rc;
+    }
+    if (!scanned) {
         // register-resident scan: 256 threads = rows_per_pass * parts, parts a power of two <= 32
         int npt = 0;
         for (int cand : {32, 16, 8, 4}) {

@@ -83,10 +83,12 @@ def test_step_batched(oracle, batch):
         close(host(dcs)[b], wcs, batch, SUM_ORDER)
 
 
-@pytest.mark.parametrize("B,T", [(1, 1), (2, 7), (1, 33), (3, 64), (1, 300)])
+@pytest.mark.parametrize("B,T", [(1, 1), (2, 7), (1, 33), (3, 64), (1, 300), (2, 513)])
 @pytest.mark.parametrize("wkind", [-2, 2, 3])
 def test_forward_sequence(oracle, B, T, wkind):
-    from gpu_util import SUM_ORDER, close, dev, empty, host, ops
+    """T >= 64 runs the chunked (SSD) scan: 64 = one partial chunk, 300 = two chunks and a
+    tail, 513 = four chunks and one step; shorter sequences the sequential scan."""
+    from gpu_util import SUM_ORDER, close, dev, empty, fp16_close, host, ops
     c = mamba_case(oracle, B * 1000 + T + wkind, B=B, T=T, d=256, n_heads=4, d_head=64, d_state=128, k=4, wkind=wkind)
     a = c["args"]
     want, want_state = oracle.mamba2_forward(*a, wkind)
@@ -97,8 +99,14 @@ def test_forward_sequence(oracle, B, T, wkind):
     else:
         ops.mamba2_forward_half(dev(a[0]), *pw, dstate, out, *a[10:], wkind)
     rows = B * T if wkind != -2 else 1          # fp32 weights never take the tensor-core path
-    close(host(out), want, rows, dict(rtol=5e-4, atol=5e-5))
-    close(host(dstate), want_state, rows, dict(rtol=5e-4, atol=5e-6))
+    if wkind == -2 and T >= 64:
+        # the chunked scan adds the same fp32 products in another order: bounded against
+        # the output scale (elementwise bounds trip on outputs that cancel to ~0)
+        fp16_close(host(out), want, frac=1e-4)
+        fp16_close(host(dstate), want_state, frac=1e-4)
+    else:
+        close(host(out), want, rows, dict(rtol=5e-4, atol=5e-5))
+        close(host(dstate), want_state, rows, dict(rtol=5e-4, atol=5e-6))
 
 
 def test_forward_small_state_general_path(oracle):
