@@ -331,6 +331,13 @@ attn_prefill_kernel(const float* __restrict__ q, const float* __restrict__ k, co
 
 }  // namespace b200
 
+// attention_flash.cu
+namespace b200 {
+int attention_flash(const float* q, const float* k, const float* v, float* out, int B, int T, int H, int KV, int hd,
+                    float scale, int window, const int32_t* seg);
+constexpr int FLASH_MIN_T = 128;
+}  // namespace b200
+
 using namespace b200;
 
 extern "C" {
@@ -377,6 +384,11 @@ int b200_attention_forward_ex(const float* q, const float* k, const float* v, fl
     B200_REQUIRE(H <= 65535 && B <= 65535, "attention_forward_ex: H and B must be <= 65535");
     int rc = check_hd("attention_forward_ex", hd);
     if (rc) return rc;
+    // long sequences without the probability output: the tensor-core kernel (attention_flash.cu)
+    auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (!probs && T >= FLASH_MIN_T && (hd == 64 || hd == 128) && aligned16(q) && aligned16(k) && aligned16(v) &&
+        aligned16(out))
+        return attention_flash(q, k, v, out, B, T, H, KV, hd, scale, window, segment_ids);
     const dim3 grid(T, H, B);
     switch (hd / 32) {
         case 1: attn_prefill_kernel<1><<<grid, ATT_WARPS * 32, 0, stream()>>>(q, k, v, out, probs, T, H, KV, hd, scale, window, segment_ids); break;

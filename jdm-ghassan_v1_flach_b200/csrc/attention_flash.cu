@@ -1,0 +1,188 @@
+// Prefill attention for long sequences: causal (optionally windowed / segment-masked)
+// softmax(q k^T) v without ever forming the [T, T] score matrix, on tensor cores.
+//
+// Same result as attn_prefill_kernel (attention.cu) and as cpu::attention_forward_ex
+// (core/attn_cpu.cpp:29-94) up to fp16 rounding of q, k, v and of the probabilities
+// (accumulation and the softmax statistics are fp32) - the reference's CUDA path feeds
+// its batched cuBLAS GEMMs fp16 copies as well (cuda/attention.cu:432-499).
+//
+// One CTA = 64 queries of one (sequence, head); each of its 4 warps owns 16 query rows.
+// Keys and values arrive 64 at a time through shared memory (K row-major, V transposed,
+// both fp16, padded so that fragment loads are conflict-free); scores and outputs live
+// in mma.sync.m16n8k16 accumulator fragments, and the score fragment of a 16-key slice
+// is reused directly as the A operand of the probability-times-value product.
+#include <cuda_fp16.h>
+
+#include "mma_tile.cuh"
+
+namespace b200 {
+
+constexpr int FA_BM = 64, FA_BN = 64, FA_THREADS = 128;
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS)
+attn_flash_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                  float* __restrict__ out, int T, int H, int KV, float scale, int window,
+                  const int32_t* __restrict__ seg) {
+    constexpr int LDK = HD + 8, LDV = FA_BN + 8;
+    __shared__ __align__(16) __half Ks[FA_BN * LDK];
+    __shared__ __align__(16) __half Vt[HD * LDV];
+    __shared__ int32_t s_seg[FA_BN];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int q0 = blockIdx.x * FA_BM, h = blockIdx.y, b = blockIdx.z;
+    const int kvh = h / (H / KV);
+    const int64_t qs = (int64_t)T * H * HD, kvs = (int64_t)T * KV * HD;
+    const float* qb = q + b * qs + (int64_t)h * HD;
+    const float* kb = k + b * kvs + (int64_t)kvh * HD;
+    const float* vb = v + b * kvs + (int64_t)kvh * HD;
+    const int r0 = q0 + warp * 16 + g, r1 = r0 + 8;        // this lane's two query rows
+    const float qscale = scale * 1.44269504088896f;         // scores in log2 units: p = 2^(s - m)
+
+    // query fragments (pre-scaled), rows past T read as zero
+    uint32_t qa[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        const int c = ks * 16 + 2 * t4;
+        float2 x0 = make_float2(0.f, 0.f), x1 = x0, x2 = x0, x3 = x0;
+        if (r0 < T) {
+            x0 = *reinterpret_cast<const float2*>(qb + (int64_t)r0 * H * HD + c);
+            x2 = *reinterpret_cast<const float2*>(qb + (int64_t)r0 * H * HD + c + 8);
+        }
+        if (r1 < T) {
+            x1 = *reinterpret_cast<const float2*>(qb + (int64_t)r1 * H * HD + c);
+            x3 = *reinterpret_cast<const float2*>(qb + (int64_t)r1 * H * HD + c + 8);
+        }
+        qa[ks][0] = pack_half2(x0.x * qscale, x0.y * qscale);
+        qa[ks][1] = pack_half2(x1.x * qscale, x1.y * qscale);
+        qa[ks][2] = pack_half2(x2.x * qscale, x2.y * qscale);
+        qa[ks][3] = pack_half2(x3.x * qscale, x3.y * qscale);
+    }
+    const int32_t seg0 = (seg && r0 < T) ? seg[(int64_t)b * T + r0] : -1;
+    const int32_t seg1 = (seg && r1 < T) ? seg[(int64_t)b * T + r1] : -1;
+    const int lo0 = window > 0 ? max(0, r0 - window + 1) : 0, lo1 = window > 0 ? max(0, r1 - window + 1) : 0;
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+
+    const int q_last = min(T - 1, q0 + FA_BM - 1);
+    const int j_first = window > 0 ? max(0, q0 - window + 1) : 0;
+    for (int kv0 = (j_first / FA_BN) * FA_BN; kv0 <= q_last; kv0 += FA_BN) {
+        __syncthreads();                                    // the previous tile has been consumed
+        for (int i = threadIdx.x; i < FA_BN * (HD / 4); i += FA_THREADS) {
+            const int key = i / (HD / 4), c = (i - key * (HD / 4)) * 4;
+            float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+            if (kv0 + key < T) {
+                kk = *reinterpret_cast<const float4*>(kb + (int64_t)(kv0 + key) * KV * HD + c);
+                vv = *reinterpret_cast<const float4*>(vb + (int64_t)(kv0 + key) * KV * HD + c);
+            }
+            *reinterpret_cast<uint2*>(&Ks[key * LDK + c]) = make_uint2(pack_half2(kk.x, kk.y), pack_half2(kk.z, kk.w));
+            Vt[(c + 0) * LDV + key] = __float2half_rn(vv.x);
+            Vt[(c + 1) * LDV + key] = __float2half_rn(vv.y);
+            Vt[(c + 2) * LDV + key] = __float2half_rn(vv.z);
+            Vt[(c + 3) * LDV + key] = __float2half_rn(vv.w);
+        }
+        if (threadIdx.x < FA_BN) s_seg[threadIdx.x] = (seg && kv0 + threadIdx.x < T) ? seg[(int64_t)b * T + kv0 + threadIdx.x] : 0;
+        __syncthreads();
+
+        // scores of this warp's 16 rows against the 64 keys
+        float s[FA_BN / 8][4];
+#pragma unroll
+        for (int nt = 0; nt < FA_BN / 8; ++nt) {
+            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+            const __half* krow = &Ks[(nt * 8 + g) * LDK + 2 * t4];
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
+                mma_16816(s[nt], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+            }
+        }
+        // mask, running maximum
+        float mx0 = m0, mx1 = m1;
+#pragma unroll
+        for (int nt = 0; nt < FA_BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int kl = nt * 8 + 2 * t4 + e, j = kv0 + kl;
+                const int32_t sj = s_seg[kl];
+                const bool ok0 = j <= r0 && j >= lo0 && r0 < T && !(seg && seg0 >= 0 && sj != seg0);
+                const bool ok1 = j <= r1 && j >= lo1 && r1 < T && !(seg && seg1 >= 0 && sj != seg1);
+                s[nt][e] = ok0 ? s[nt][e] : -INFINITY;
+                s[nt][2 + e] = ok1 ? s[nt][2 + e] : -INFINITY;
+                mx0 = fmaxf(mx0, s[nt][e]);
+                mx1 = fmaxf(mx1, s[nt][2 + e]);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        // rows with nothing visible yet keep a finite reference so that 2^(-inf - ref) = 0
+        const float ref0 = mx0 == -INFINITY ? 0.0f : mx0, ref1 = mx1 == -INFINITY ? 0.0f : mx1;
+        const float al0 = exp2f(m0 - ref0), al1 = exp2f(m1 - ref1);   // m = -inf -> 0
+        m0 = mx0;
+        m1 = mx1;
+        l0 *= al0;
+        l1 *= al1;
+#pragma unroll
+        for (int d = 0; d < HD / 8; ++d) {
+            o[d][0] *= al0; o[d][1] *= al0;
+            o[d][2] *= al1; o[d][3] *= al1;
+        }
+        // probabilities -> A fragments; P V
+#pragma unroll
+        for (int kk = 0; kk < FA_BN / 16; ++kk) {
+            float p[2][4];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                p[u][0] = exp2f(s[2 * kk + u][0] - ref0);
+                p[u][1] = exp2f(s[2 * kk + u][1] - ref0);
+                p[u][2] = exp2f(s[2 * kk + u][2] - ref1);
+                p[u][3] = exp2f(s[2 * kk + u][3] - ref1);
+                l0 += p[u][0] + p[u][1];
+                l1 += p[u][2] + p[u][3];
+            }
+            const uint32_t a0 = pack_half2(p[0][0], p[0][1]), a1 = pack_half2(p[0][2], p[0][3]);
+            const uint32_t a2 = pack_half2(p[1][0], p[1][1]), a3 = pack_half2(p[1][2], p[1][3]);
+#pragma unroll
+            for (int d = 0; d < HD / 8; ++d) {
+                const __half* vrow = &Vt[(d * 8 + g) * LDV + kk * 16 + 2 * t4];
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(vrow);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(vrow + 8);
+                mma_16816(o[d], a0, a1, a2, a3, b0, b1);
+            }
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, inv1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+    float* ob = out + b * qs + (int64_t)h * HD;
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) {
+        const int c = d * 8 + 2 * t4;
+        if (r0 < T) *reinterpret_cast<float2*>(ob + (int64_t)r0 * H * HD + c) = make_float2(o[d][0] * inv0, o[d][1] * inv0);
+        if (r1 < T) *reinterpret_cast<float2*>(ob + (int64_t)r1 * H * HD + c) = make_float2(o[d][2] * inv1, o[d][3] * inv1);
+    }
+}
+
+// Returns B200_EUNSUPPORTED for head sizes it has no instance for.
+int attention_flash(const float* q, const float* k, const float* v, float* out, int B, int T, int H, int KV, int hd,
+                    float scale, int window, const int32_t* seg) {
+    const dim3 grid(ceil_div(T, FA_BM), H, B);
+    if (hd == 128) attn_flash_kernel<128><<<grid, FA_THREADS, 0, stream()>>>(q, k, v, out, T, H, KV, scale, window, seg);
+    else if (hd == 64) attn_flash_kernel<64><<<grid, FA_THREADS, 0, stream()>>>(q, k, v, out, T, H, KV, scale, window, seg);
+    else return fail(B200_EUNSUPPORTED, "attention_flash: head_dim %d", hd);
+    B200_LAUNCH_CHECK("attn_flash_kernel");
+    return B200_OK;
+}
+
+}  // namespace b200

@@ -102,4 +102,8 @@ def test_prefill(oracle, B, T, H, KV, hd):
         np.testing.assert_allclose(host(probs), wp, rtol=2e-4, atol=1e-6)
         out2 = empty((B, T, H, hd))
         ops.attention_forward_ex(dev(q), dev(k), dev(v), out2, None, B, T, H, KV, hd, hd ** -0.5, window, dev(s))
-        assert np.array_equal(host(out2), host(out))
+        if T < 128:
+            assert np.array_equal(host(out2), host(out))     # same kernel with and without the probabilities
+        else:
+            from gpu_util import fp16_close                  # 128 tokens and more: tensor-core kernel
+            fp16_close(host(out2), host(out), frac=4e-3)
