@@ -16,6 +16,12 @@ One step = one decoded token per sequence.
                   against the measured copy bandwidth
     cpu_baseline  the reference engine's CPU ops (oracle/_ref) or the oracle port on
                   this box's host cores, on a bounded sample of the same token
+    prefill       the `--ctx`-token prompt through b200_decoder_prefill (tok/s, device time)
+    moe_layer     one MoE layer of this shape over 4096 tokens (tensor-core grouped GEMM;
+                  expert-parallel over NCCL all-to-all when N > 1)
+    batch64       64 sequences decoded together after a 256-token prompt each
+
+`--only gemm` times the many-token kernels alone (also the small profiling case).
 
 `--impl reference` prints the CPU arm alone.  Under torchrun (N > 1) every rank runs
 an independent replica of the model (only the MoE layer shards in this workload and
@@ -155,6 +161,13 @@ class DeviceModel:
 
     def step_dev(self, tok_dev):
         self.lib.b200_decoder_step(self.handle, tok_dev, tok_dev)       # in place: next token feeds the next step
+
+    def prefill(self, prompt_dev, next_dev):
+        """prompt_dev [batch, T] int32 on the device: the whole prompt through the many-token kernels."""
+        self.lib.b200_decoder_prefill(self.handle, prompt_dev, int(prompt_dev.shape[1]), next_dev)
+
+    def reset(self):
+        self.lib.b200_decoder_reset(self.handle)
 
     def step_host(self, tok_np, out_np):
         self.lib.b200_decoder_step_host(self.handle, tok_np.ctypes.data, out_np.ctypes.data)
@@ -421,9 +434,9 @@ def batch_decode_bench(cfg, batch, ctx, steps, seed):
     model = DeviceModel(cfg, batch, ctx + steps + 16, seed=seed)
     model.configure(0, 1)
     g = torch.Generator(device="cuda").manual_seed(7 + seed)
-    tok = torch.randint(0, cfg["vocab"], (batch,), device="cuda", generator=g, dtype=torch.int32)
-    for _ in range(ctx):
-        model.step_dev(tok)
+    prompt = torch.randint(0, cfg["vocab"], (batch, ctx), device="cuda", generator=g, dtype=torch.int32)
+    tok = torch.empty(batch, dtype=torch.int32, device="cuda")
+    model.prefill(prompt, tok)
     for _ in range(3):
         model.step_dev(tok)
     torch.cuda.synchronize()
@@ -522,14 +535,24 @@ def main():
     lib = model.lib
     model.configure(args.fused, args.graph)
 
-    # prompt: ctx uniform token ids per sequence, fed through the decoder one token at a time
+    # prompt: ctx uniform token ids per sequence through the prompt path (once untimed: it
+    # grows the workspaces; then timed from empty sequences)
     g = torch.Generator(device="cuda").manual_seed(1 + rank)
-    prompt = torch.randint(0, cfg["vocab"], (args.ctx, B), device="cuda", generator=g, dtype=torch.int32)
+    prompt = torch.randint(0, cfg["vocab"], (B, max(args.ctx, 1)), device="cuda", generator=g, dtype=torch.int32)
     tok = torch.empty(B, dtype=torch.int32, device="cuda")
-    for t in range(args.ctx):
-        tok.copy_(prompt[t])
-        model.step_dev(tok)
-    torch.cuda.synchronize()
+    prefill_ms = None
+    if args.ctx >= 1:
+        model.prefill(prompt, tok)
+        model.reset()
+        torch.cuda.synchronize()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        model.prefill(prompt, tok)
+        p1.record()
+        torch.cuda.synchronize()
+        prefill_ms = p0.elapsed_time(p1)
+    else:
+        tok.copy_(prompt[:, 0])
 
     def barrier():
         if world > 1:
@@ -629,6 +652,9 @@ def main():
                                   "ms_per_launch": q4k_ms, "algorithmic_bytes_per_launch": q4k_bytes},
             "moe_layer": moe,
             "batch64": batch64,
+            "prefill": None if prefill_ms is None else {
+                "tokens": B * args.ctx, "ms": prefill_ms, "tok_s": B * args.ctx / (prefill_ms * 1e-3),
+                "mode": "b200_decoder_prefill: tensor-core GEMMs, chunked SSD scan, tensor-core attention, grouped MoE"},
         }
         if not args.no_cpu and world == 1:
             secs, info = cpu_decode_token_seconds(cfg, args.ctx, reps=8)

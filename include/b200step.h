@@ -70,6 +70,13 @@ int b200_decoder_configure(b200_decoder* dec, int fused, int use_graph);
 /* One token per sequence.  tokens_dev [batch] int32 in; next_dev [batch] int32 out
  * (greedy arg-max of the logits); both device pointers; no host synchronisation. */
 int b200_decoder_step(b200_decoder* dec, const int32_t* tokens_dev, int32_t* next_dev);
+/* The prompt: T tokens of every sequence at once (tokens_dev [batch, T] int32, sequence-
+ * major) through the many-token kernels - what Generator::forward_prefill does with its
+ * batched path (inference/generator.cpp:627-915), here including the Mamba layers.  The
+ * sequences must be empty (after create or reset).  Afterwards the state is where T
+ * calls of b200_decoder_step would have left it; next_dev (optional) receives the greedy
+ * pick after the last prompt token, b200_decoder_logits its logits. */
+int b200_decoder_prefill(b200_decoder* dec, const int32_t* tokens_dev, int T, int32_t* next_dev);
 /* Same through host buffers: H2D of the token ids, the step, D2H of the picks,
  * then a stream synchronise (what Generator::decode_step + ops::argmax_token do). */
 int b200_decoder_step_host(b200_decoder* dec, const int32_t* tokens_host, int32_t* next_host);

@@ -404,9 +404,25 @@ int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, con
                    float* state, float* y, int B, int T, const MambaDims& p);
 constexpr int SSD_MIN_STEPS = 64;
 
+// The last k-1 raw (pre-convolution) inputs of every channel, oldest first: the window a
+// decode step expects after this sequence (zeros where the sequence is shorter).
+__global__ void mamba_conv_window_kernel(const float* __restrict__ proj, float* __restrict__ conv_state, int B, int T,
+                                         MambaDims p) {
+    const int win = p.k - 1;
+    const int64_t total = (int64_t)B * p.conv_dim * win;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int j = (int)(i % win);
+        const int64_t bc_i = i / win;
+        const int c = (int)(bc_i % p.conv_dim), b = (int)(bc_i / p.conv_dim);
+        const int t = T - win + j;
+        conv_state[i] = t >= 0 ? proj[((int64_t)b * T + t) * p.proj + p.d_inner + c] : 0.0f;
+    }
+}
+
 int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const float* conv_b,
                    const float* dt_bias, const float* a_log, const float* D, const float* norm_w,
-                   const void* w_out, float* state, float* out, int B, int T, MambaDims p, int kind) {
+                   const void* w_out, float* state, float* out, int B, int T, MambaDims p, int kind,
+                   float* conv_state_out) {
     if (B <= 0 || T <= 0) return B200_OK;
     int rc = check_dims("mamba2_forward", p);
     if (rc) return rc;
@@ -429,6 +445,12 @@ int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const 
         const int grid = (int)std::min<int64_t>(ceil_div64(total, 256), (int64_t)num_sms() * 32);
         mamba_conv_seq_kernel<<<grid, 256, 0, stream()>>>(proj, conv_w, conv_b, bc, B, T, p);
         B200_LAUNCH_CHECK("mamba_conv_seq_kernel");
+        if (conv_state_out && p.k > 1) {
+            const int64_t n = (int64_t)B * p.conv_dim * (p.k - 1);
+            mamba_conv_window_kernel<<<(unsigned)std::min<int64_t>(ceil_div64(n, 256), 4096), 256, 0, stream()>>>(
+                proj, conv_state_out, B, T, p);
+            B200_LAUNCH_CHECK("mamba_conv_window_kernel");
+        }
     }
     // Long sequences: the chunked form (all steps in parallel, a short carry over chunks);
     // short ones and shapes outside its tiling: the sequential register-resident scan.

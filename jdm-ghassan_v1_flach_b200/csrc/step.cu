@@ -303,6 +303,125 @@ static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t*
     return B200_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Prompt processing: T tokens of every sequence at once through the many-token
+// kernels (tensor-core GEMMs, chunked SSD scan, tensor-core attention, grouped MoE),
+// leaving the per-sequence state exactly where T decode steps would have left it:
+// ssm state, convolution window, KV pages, lengths.
+// ---------------------------------------------------------------------------
+__global__ void prefill_pos_kernel(int32_t* __restrict__ pos, int B, int T) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < B * T) pos[i] = i % T;
+}
+__global__ void prefill_len_kernel(int32_t* __restrict__ len, int32_t* __restrict__ pos, int B, int T) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < B) { len[b] = T; pos[b] = T - 1; }
+}
+// k, v [B, T, kvd] fp32 -> fp16 rows of the sequences' pages
+__global__ void kv_prefill_kernel(const float* __restrict__ k, const float* __restrict__ v, uint16_t* __restrict__ k_pages,
+                                  uint16_t* __restrict__ v_pages, const int32_t* __restrict__ page_table, int T,
+                                  int max_pages, int page, int kvd) {
+    const int t = blockIdx.y, b = blockIdx.z;
+    const int64_t row = (int64_t)page_table[(int64_t)b * max_pages + t / page] * page + t % page;
+    const int64_t src = ((int64_t)b * T + t) * kvd;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < kvd; c += gridDim.x * blockDim.x) {
+        k_pages[row * kvd + c] = float_to_half_bits(k[src + c]);
+        v_pages[row * kvd + c] = float_to_half_bits(v[src + c]);
+    }
+}
+// dst[b, :] = src[b, T-1, :]
+__global__ void last_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int B, int T, int d) {
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i < (int64_t)B * d) {
+        const int b = (int)(i / d), c = (int)(i - (int64_t)b * d);
+        dst[i] = src[((int64_t)b * T + T - 1) * d + c];
+    }
+}
+
+static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* next) {
+    const int B = dec->batch, d = dec->d;
+    const int64_t NT = (int64_t)B * T;
+    const int qd = dec->H * dec->hd, kvd = dec->KV * dec->hd;
+    cudaStream_t st = stream();
+    int rc;
+#define STEP(call)              \
+    do {                        \
+        rc = (call);            \
+        if (rc) return rc;      \
+    } while (0)
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
+    const size_t o_x = take(NT * d * 4), o_xb = take(NT * d * 4), o_y = take(NT * d * 4), o_q = take(NT * qd * 4),
+                 o_k = take(NT * kvd * 4), o_v = take(NT * kvd * 4), o_at = take(NT * qd * 4), o_pos = take(NT * 4);
+    void* wsp;
+    STEP(workspace(WS_PREFILL).ensure(off + 256, &wsp));
+    char* base = static_cast<char*>(wsp);
+    float *x = reinterpret_cast<float*>(base + o_x), *xb = reinterpret_cast<float*>(base + o_xb),
+          *y = reinterpret_cast<float*>(base + o_y), *q = reinterpret_cast<float*>(base + o_q),
+          *k = reinterpret_cast<float*>(base + o_k), *v = reinterpret_cast<float*>(base + o_v),
+          *at = reinterpret_cast<float*>(base + o_at);
+    int32_t* pos = reinterpret_cast<int32_t*>(base + o_pos);
+    const int kind = tag_of_qkind(dec->qkind);
+    MambaDims p;
+    p.d = d; p.d_inner = dec->d_inner; p.conv_dim = dec->conv_dim; p.n_heads = dec->mh; p.d_head = dec->mdh;
+    p.d_state = dec->mds; p.k = dec->mk; p.eps = dec->eps; p.proj = dec->d_inner + dec->conv_dim + dec->mh;
+    auto lin = [&](const float* in, const void* w, float* out, int K, int N) {
+        return dec->qkind >= 0 ? b200_linear_forward_q4(in, static_cast<const uint16_t*>(w), out, (int)NT, K, N, dec->qkind)
+                               : b200_linear_forward_fp16(in, static_cast<const uint16_t*>(w), out, (int)NT, K, N);
+    };
+    const int res_grid = (int)std::min<int64_t>(ceil_div64(NT * d, 256), (int64_t)num_sms() * 16);
+    STEP(b200_embedding_forward_half(tokens, dec->embed, x, NT, d, dec->vocab));
+    if (dec->emb_mult != 1.0f) STEP(b200_scale_inplace(x, dec->emb_mult, NT * d));
+    if (dec->rope_type >= 0) {
+        prefill_pos_kernel<<<(unsigned)ceil_div64(NT, 256), 256, 0, st>>>(pos, B, T);
+        B200_LAUNCH_CHECK("prefill_pos_kernel");
+    }
+    for (int l = 0; l < dec->n_layers; ++l) {
+        LayerW& w = dec->L[l];
+        STEP(b200_rmsnorm_forward(x, w.attn_norm, xb, nullptr, NT, d, dec->eps));
+        if (dec->types[l] == 0) {
+            STEP(mamba2_forward(xb, w.mamba_in, w.conv_w, w.conv_b, w.dt_bias, w.a_log, w.D, w.mamba_norm, w.mamba_out,
+                                w.ssm_state, y, B, T, p, kind, w.conv_state));
+        } else {
+            STEP(lin(xb, w.wq, q, d, qd));
+            STEP(lin(xb, w.wk, k, d, kvd));
+            STEP(lin(xb, w.wv, v, d, kvd));
+            if (dec->rope_type >= 0)
+                STEP(b200_rope_forward_cached(q, k, pos, dec->inv_freq, NT, dec->H, dec->KV, dec->hd, dec->rope_type));
+            kv_prefill_kernel<<<dim3(ceil_div(kvd, 256), T, B), 256, 0, st>>>(k, v, w.k_pages, w.v_pages, dec->page_table, T,
+                                                                            dec->max_pages, dec->page, kvd);
+            B200_LAUNCH_CHECK("kv_prefill_kernel");
+            STEP(b200_attention_forward_ex(q, k, v, at, nullptr, B, T, dec->H, dec->KV, dec->hd, dec->attn_scale, 0, nullptr));
+            STEP(lin(at, w.wo, y, qd, d));
+        }
+        residual_kernel<<<res_grid, 256, 0, st>>>(x, y, dec->res_mult, NT * d);
+        B200_LAUNCH_CHECK("residual_kernel");
+        STEP(b200_rmsnorm_forward(x, w.ffn_norm, xb, nullptr, NT, d, dec->eps));
+        STEP(b200_moe_forward_bias_half(xb, w.router, w.router_bias, static_cast<const uint16_t*>(w.gate),
+                                        static_cast<const uint16_t*>(w.up), static_cast<const uint16_t*>(w.down),
+                                        static_cast<const uint16_t*>(w.sh_gate), static_cast<const uint16_t*>(w.sh_up),
+                                        static_cast<const uint16_t*>(w.sh_down), y, nullptr, nullptr, nullptr, nullptr,
+                                        nullptr, nullptr, NT, d, dec->E, dec->ne, dec->K, dec->SH, dec->qkind));
+        residual_kernel<<<res_grid, 256, 0, st>>>(x, y, dec->res_mult, NT * d);
+        B200_LAUNCH_CHECK("residual_kernel");
+    }
+    // logits of the last token of every sequence
+    last_rows_kernel<<<(unsigned)ceil_div64((int64_t)B * d, 256), 256, 0, st>>>(x, dec->x, B, T, d);
+    B200_LAUNCH_CHECK("last_rows_kernel");
+    STEP(b200_rmsnorm_forward(dec->x, dec->final_norm, dec->xb, nullptr, B, d, dec->eps));
+    STEP(b200_linear_forward_fp16(dec->xb, dec->lm_head, dec->logits, B, d, dec->vocab));
+    if (dec->logits_scaling != 1.0f)
+        STEP(b200_scale_inplace(dec->logits, 1.0f / dec->logits_scaling, (int64_t)B * dec->vocab));
+    if (next) {
+        argmax_rows_kernel<<<B, 1024, 0, st>>>(dec->logits, dec->vocab, next);
+        B200_LAUNCH_CHECK("argmax_rows_kernel");
+    }
+    prefill_len_kernel<<<ceil_div(B, 128), 128, 0, st>>>(dec->len, dec->pos, B, T);
+    B200_LAUNCH_CHECK("prefill_len_kernel");
+#undef STEP
+    return B200_OK;
+}
+
 static int enqueue(b200_decoder* dec, const int32_t* tokens, int32_t* next) {
     if (dec->fused && dec->batch <= 8) return enqueue_step_fused(dec, tokens, next);
     return enqueue_step(dec, tokens, next);
@@ -567,6 +686,20 @@ int b200_decoder_step_host(b200_decoder* dec, const int32_t* tokens_host, int32_
     B200_CUDA(cudaStreamSynchronize(stream()));
     memcpy(next_host, dec->h_next, bytes);
     if (dec->h_next[dec->batch] != 0) return stream_status_check("decoder_step_host");
+    return B200_OK;
+}
+
+int b200_decoder_prefill(b200_decoder* dec, const int32_t* tokens_dev, int T, int32_t* next_dev) {
+    int rc = check_ready(dec);
+    if (rc) return rc;
+    B200_REQUIRE(tokens_dev && T >= 1, "decoder_prefill: bad arguments");
+    B200_REQUIRE(dec->position == 0, "decoder_prefill: the sequences already hold %d tokens (reset first)", dec->position);
+    B200_REQUIRE(T <= dec->max_ctx, "decoder_prefill: %d tokens exceed the context of %d", T, dec->max_ctx);
+    B200_REQUIRE((int64_t)dec->batch * T <= 0x7fffffff / std::max(dec->K, 1), "decoder_prefill: batch * T too large");
+    B200_REQUIRE(dec->batch <= 65535 && T <= 65535, "decoder_prefill: batch and T must be <= 65535");
+    rc = prefill(dec, tokens_dev, T, next_dev);
+    if (rc) return rc;
+    dec->position = T;
     return B200_OK;
 }
 

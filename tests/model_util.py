@@ -183,6 +183,17 @@ class CudaDecoder:
         self.lib.b200_decoder_step_host(self.handle, tokens.ctypes.data, nxt.ctypes.data)
         return nxt
 
+    def prefill(self, tokens):
+        """tokens [batch, T]: the whole prompt at once; returns the greedy picks."""
+        import torch
+        from gpu_util import dev
+        tokens = np.ascontiguousarray(tokens, np.int32).reshape(self.batch, -1)
+        t = dev(tokens)
+        nxt = torch.empty(self.batch, dtype=torch.int32, device="cuda")
+        self.lib.b200_decoder_prefill(self.handle, t, tokens.shape[1], nxt)
+        self.lib.b200_synchronize()
+        return nxt.cpu().numpy()
+
     def logits(self):
         import torch
         p = C.c_void_p()
