@@ -493,6 +493,36 @@ def gemm_only_bench():
     print(json.dumps(out))
 
 
+def prefill_only_bench(args):
+    """The prompt path alone: `--ctx` tokens per sequence, `--batch` sequences."""
+    import torch
+    cfg = dict(H_TINY)
+    if args.small:
+        cfg.update(n_layers=4, layer_types=[0, 1, 0, 0], vocab=8192)
+    model = DeviceModel(cfg, args.batch, args.ctx + 8, seed=0)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    prompt = torch.randint(0, cfg["vocab"], (args.batch, args.ctx), device="cuda", generator=g, dtype=torch.int32)
+    tok = torch.empty(args.batch, dtype=torch.int32, device="cuda")
+    model.prefill(prompt, tok)
+    times = []
+    for _ in range(3):
+        model.reset()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        model.prefill(prompt, tok)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    if model.lib.raw("b200_stream_status") != 0:
+        raise RuntimeError(model.lib.last_error())
+    n = args.batch * args.ctx
+    ms = min(times)
+    print(json.dumps({"prefill": {"batch": args.batch, "tokens_per_sequence": args.ctx, "layers": cfg["n_layers"],
+                                  "ms": ms, "tok_s": n / (ms * 1e-3)}}))
+    model.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -505,11 +535,15 @@ def main():
     ap.add_argument("--graph", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--small", action="store_true", help="4-layer model (development only; not a bench number)")
-    ap.add_argument("--only", default="", choices=["", "gemm"],
-                    help="gemm: time the tensor-core linears and the MoE layer alone (small; also the profiling case)")
+    ap.add_argument("--only", default="", choices=["", "gemm", "prefill"],
+                    help="gemm: time the tensor-core linears and the MoE layer alone (small; also the profiling case); "
+                         "prefill: time the prompt path alone (with --small: the profiling case)")
     args = ap.parse_args()
     if args.only == "gemm":
         gemm_only_bench()
+        return
+    if args.only == "prefill":
+        prefill_only_bench(args)
         return
 
     rank = int(os.environ.get("RANK", "0"))

@@ -401,7 +401,7 @@ int mamba2_step(const float* x, const void* w_in, const float* conv_w, const flo
 
 // mamba_ssd.cu
 int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, const float* a_log, const float* D,
-                   float* state, float* y, int B, int T, const MambaDims& p);
+                   float* state, float* y, int B, int T, const MambaDims& p, bool precise);
 constexpr int SSD_MIN_STEPS = 64;
 
 // The last k-1 raw (pre-convolution) inputs of every channel, oldest first: the window a
@@ -456,7 +456,7 @@ int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const 
     // short ones and shapes outside its tiling: the sequential register-resident scan.
     bool scanned = false;
     if (T >= SSD_MIN_STEPS) {
-        rc = mamba_ssd_scan(proj, bc, dt_bias, a_log, D, state, y, B, T, p);
+        rc = mamba_ssd_scan(proj, bc, dt_bias, a_log, D, state, y, B, T, p, kind == KIND_F32);
         if (rc == B200_OK) scanned = true;
         else if (rc != B200_EUNSUPPORTED) return rc;
     }

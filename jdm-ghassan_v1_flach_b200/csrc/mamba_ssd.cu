@@ -10,9 +10,13 @@
 //     inter   Y[t] += exp(cum_t) C_t . S_prev(c)
 // so all T steps of all heads run in parallel except the short carry over chunks.
 // B and C are shared by the heads (n_groups == 1), hence C_t . B_s is computed once per
-// (sequence, chunk).  Everything is fp32; only the order of additions differs from the
-// sequential scan (which the reference itself has no chunked form of: its
-// mamba_chunk_size option is parsed and unused).
+// (sequence, chunk).  dt, the running sums, the exponentials, the carry and all
+// accumulation are fp32.  With fp32 weights (`precise`) the two per-head products run as
+// split-TF32 (3 MMAs per product, fp32-level accuracy: only the order of additions differs
+// from the sequential scan); with fp16 / packed weights - where the projections around the
+// scan already round their activations to fp16 - their operands are rounded to TF32 once.
+// (The reference has no chunked form to compare with: its mamba_chunk_size option is
+// parsed and unused, and its scan is the sequential one.)
 //
 //   ssd_cb_kernel           G[b,c] = C B^T                         [Q, Q]
 //   ssd_chunk_state_kernel  dt, cum per step; S_c per (b, c, h)   [d_head, d_state]
@@ -69,17 +73,63 @@ ssd_cb_kernel(const float* __restrict__ bc, float* __restrict__ G, int T, MambaD
         for (int j = 0; j < 8; ++j) g[(ty * 8 + i) * SSD_Q + tx * 8 + j] = acc[i][j];
 }
 
+// ---- tensor-core pieces ---------------------------------------------------------------
+// The two dense products per (chunk, head) run on mma.sync.m16n8k8 with TF32 operands
+// (fp32 range, 11 significant bits) and fp32 accumulation; shared memory holds the fp32
+// operands and they are rounded (or split, see Tf32Val) as fragments are loaded.  Leading
+// dimensions are padded so that every fragment load of a warp touches 32 different banks.
+__device__ __forceinline__ float tf32_round(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const float (&a)[4], float b0, float b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(__float_as_uint(a[0])), "r"(__float_as_uint(a[1])), "r"(__float_as_uint(a[2])),
+          "r"(__float_as_uint(a[3])), "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
+}
+
+// One operand element as the tensor core sees it.  X3 = false: the value rounded to
+// TF32.  X3 = true: the value split into a TF32 head and a TF32 tail, and a product is
+// three MMAs (tail x head, head x tail, head x head), which restores fp32-level accuracy
+// (the dropped tail x tail term is below 2^-22 relative).
+template <bool X3>
+struct Tf32Val {
+    float hi, lo;
+    __device__ __forceinline__ explicit Tf32Val(float v) : hi(tf32_round(v)), lo(X3 ? tf32_round(v - hi) : 0.0f) {}
+    __device__ __forceinline__ Tf32Val() : hi(0.0f), lo(0.0f) {}
+};
+template <bool X3>
+__device__ __forceinline__ void mma_x(float (&c)[4], const Tf32Val<X3> (&a)[4], const Tf32Val<X3>& b0, const Tf32Val<X3>& b1) {
+    const float ah[4] = {a[0].hi, a[1].hi, a[2].hi, a[3].hi};
+    if (X3) {
+        const float al[4] = {a[0].lo, a[1].lo, a[2].lo, a[3].lo};
+        mma_tf32(c, al, b0.hi, b1.hi);
+        mma_tf32(c, ah, b0.lo, b1.lo);
+    }
+    mma_tf32(c, ah, b0.hi, b1.hi);
+}
+
+constexpr int SSD_P = 64;                  // d_head of the tensor-core kernels
+constexpr int SSD_LDX = SSD_P + 8;         // x tile [Q][P + 8]
+
 // ---- per (chunk, head, sequence): dt, cum, chunk state ----------------------------
 // dtcum: [B, H, T, 2] (dt, cum).  chunk_state: [B, NC, H, P, N].  decay: [B, NC, H].
-__global__ void __launch_bounds__(SSD_THREADS)
+// S[p][n] = sum_s (w_s x[s][p]) B[s][n]: warp w owns rows 16 (w & 3) .. +16 and the
+// (w >> 2)-th half of the columns.
+template <bool X3>
+__global__ void __launch_bounds__(SSD_THREADS, 2)
 ssd_chunk_state_kernel(const float* __restrict__ proj, const float* __restrict__ bc, const float* __restrict__ dt_bias,
                        const float* __restrict__ a_log, float* __restrict__ dtcum, float* __restrict__ chunk_state,
                        float* __restrict__ decay, int T, int NC, MambaDims p) {
     extern __shared__ float sm[];
-    const int N = p.d_state, P = p.d_head;
-    float* sB = sm;                         // [Q][N]
-    float* sX = sB + SSD_Q * N;             // [Q][P]   (already multiplied by w_s)
-    float* sDt = sX + SSD_Q * P;            // [Q]
+    constexpr int P = SSD_P;
+    const int N = p.d_state, ldb = N + 8;
+    float* sB = sm;                         // [Q][N + 8]
+    float* sX = sB + SSD_Q * ldb;           // [Q][P + 8]   (already multiplied by w_s)
+    float* sDt = sX + SSD_Q * SSD_LDX;      // [Q]
     float* sCum = sDt + SSD_Q;              // [Q]
     const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int t0 = c * SSD_Q, nt = min(SSD_Q, T - t0);
@@ -93,12 +143,23 @@ ssd_chunk_state_kernel(const float* __restrict__ proj, const float* __restrict__
         sDt[threadIdx.x] = dt;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        float run = 0.0f;
-        for (int t = 0; t < SSD_Q; ++t) {
-            run += __fmul_rn(A, sDt[t]);
-            sCum[t] = run;
+    if (threadIdx.x < 32) {                 // running sum of A dt over the chunk: 4 steps per lane
+        const int l = threadIdx.x;
+        float v[4], run = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            run += __fmul_rn(A, sDt[l * 4 + i]);
+            v[i] = run;
         }
+        float incl = run;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (l >= o) incl += up;
+        }
+        const float before = incl - run;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sCum[l * 4 + i] = before + v[i];
     }
     __syncthreads();
     const float cum_last = sCum[SSD_Q - 1];
@@ -108,71 +169,99 @@ ssd_chunk_state_kernel(const float* __restrict__ proj, const float* __restrict__
         o[1] = sCum[threadIdx.x];
     }
     if (threadIdx.x == 0) decay[((int64_t)b * NC + c) * p.n_heads + h] = expf(cum_last);
-    for (int e = threadIdx.x; e < SSD_Q * N; e += SSD_THREADS) {
-        const int t = e / N, n = e - t * N;
-        sB[e] = t < nt ? bc[((int64_t)b * T + t0 + t) * p.conv_dim + p.d_inner + n] : 0.0f;
+    const int n4 = N >> 2;
+    for (int e = threadIdx.x; e < SSD_Q * n4; e += SSD_THREADS) {
+        const int t = e / n4, n = (e - t * n4) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < nt) v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + p.d_inner + n);
+        *reinterpret_cast<float4*>(sB + t * ldb + n) = v;
     }
-    for (int e = threadIdx.x; e < SSD_Q * P; e += SSD_THREADS) {
-        const int t = e / P, i = e - t * P;
-        const float w = expf(cum_last - sCum[t]) * sDt[t];
-        sX[e] = t < nt ? w * bc[((int64_t)b * T + t0 + t) * p.conv_dim + h * P + i] : 0.0f;
+    for (int e = threadIdx.x; e < SSD_Q * (P / 4); e += SSD_THREADS) {
+        const int t = e / (P / 4), i = (e - t * (P / 4)) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < nt) {
+            const float w = expf(cum_last - sCum[t]) * sDt[t];
+            v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + h * P + i);
+            v = make_float4(w * v.x, w * v.y, w * v.z, w * v.w);
+        }
+        *reinterpret_cast<float4*>(sX + t * SSD_LDX + i) = v;
     }
     __syncthreads();
-    // thread -> 8 rows (p) x 4 columns (n) of the state
-    const int pgroups = P >> 3, ngroups = N >> 2;
-    float* out = chunk_state + (((int64_t)b * NC + c) * p.n_heads + h) * P * N;
-    for (int g = threadIdx.x; g < pgroups * ngroups; g += SSD_THREADS) {
-        const int pg = g / ngroups, ng = g - pg * ngroups;
-        float acc[8][4] = {};
-        for (int s = 0; s < SSD_Q; ++s) {
-            const float4 bv = *reinterpret_cast<const float4*>(sB + s * N + ng * 4);
-            const float4 x0 = *reinterpret_cast<const float4*>(sX + s * P + pg * 8);
-            const float4 x1 = *reinterpret_cast<const float4*>(sX + s * P + pg * 8 + 4);
-            const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int mt = warp & 3, nh = warp >> 2;
+    const int nth = N >> 4;                 // column tiles (of 8) per half, <= 8
+    float acc[8][4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                acc[i][0] += xv[i] * bv.x;
-                acc[i][1] += xv[i] * bv.y;
-                acc[i][2] += xv[i] * bv.z;
-                acc[i][3] += xv[i] * bv.w;
-            }
-        }
+    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+    const int ksteps = (nt + 7) >> 3;
+    for (int ks = 0; ks < ksteps; ++ks) {
+        const float* xa = sX + (ks * 8 + t4) * SSD_LDX + mt * 16 + g;
+        const Tf32Val<X3> a[4] = {Tf32Val<X3>(xa[0]), Tf32Val<X3>(xa[8]), Tf32Val<X3>(xa[4 * SSD_LDX]),
+                                  Tf32Val<X3>(xa[4 * SSD_LDX + 8])};
+        const float* bb = sB + (ks * 8 + t4) * ldb + nh * nth * 8 + g;
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<float4*>(out + (pg * 8 + i) * N + ng * 4) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        for (int j = 0; j < 8; ++j)
+            if (j < nth) mma_x<X3>(acc[j], a, Tf32Val<X3>(bb[j * 8]), Tf32Val<X3>(bb[j * 8 + 4 * ldb]));
     }
+    float* out = chunk_state + (((int64_t)b * NC + c) * p.n_heads + h) * P * N;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if (j < nth) {
+            const int n = (nh * nth + j) * 8 + 2 * t4;
+            *reinterpret_cast<float2*>(out + (mt * 16 + g) * N + n) = make_float2(acc[j][0], acc[j][1]);
+            *reinterpret_cast<float2*>(out + (mt * 16 + g + 8) * N + n) = make_float2(acc[j][2], acc[j][3]);
+        }
 }
 
 // ---- carry over chunks: chunk_state[c] becomes the state BEFORE chunk c ------------
-// one thread per state element of (b, h); sequential over the chunks.
+// one thread per state element of (b, h); sequential over the chunks, eight chunks'
+// loads in flight at a time.
 __global__ void __launch_bounds__(256)
 ssd_carry_kernel(float* __restrict__ chunk_state, const float* __restrict__ decay, float* __restrict__ state, int B,
                  int NC, MambaDims p) {
     const int64_t per = (int64_t)p.d_head * p.d_state;
     const int64_t total = (int64_t)B * p.n_heads * per;
+    const int64_t cstride = (int64_t)p.n_heads * per;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t bh = i / per, e = i - bh * per;
         const int b = (int)(bh / p.n_heads), h = (int)(bh - (int64_t)b * p.n_heads);
+        float* cs = chunk_state + ((int64_t)b * NC * p.n_heads + h) * per + e;
+        const float* dc = decay + (int64_t)b * NC * p.n_heads + h;
         float s = state[i];
-        for (int c = 0; c < NC; ++c) {
-            float* cs = chunk_state + (((int64_t)b * NC + c) * p.n_heads + h) * per + e;
-            const float own = *cs;
-            *cs = s;
-            s = decay[((int64_t)b * NC + c) * p.n_heads + h] * s + own;
+        for (int c0 = 0; c0 < NC; c0 += 8) {
+            float own[8], de[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (c0 + j < NC) {
+                    own[j] = __ldcs(cs + (c0 + j) * cstride);
+                    de[j] = dc[(int64_t)(c0 + j) * p.n_heads];
+                }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (c0 + j < NC) {
+                    cs[(c0 + j) * cstride] = s;
+                    s = de[j] * s + own[j];
+                }
         }
         state[i] = s;
     }
 }
 
 // ---- per (chunk, head, sequence): outputs ------------------------------------------
-// thread -> 4 steps (t) x 8 channels (p).  Shared memory is used twice: first C and the
-// transposed incoming state (inter-chunk term), then the masked, decayed G and x.
-__global__ void __launch_bounds__(SSD_THREADS)
+// y[t][p] = sum_n (e^{cum_t} C[t][n]) S_prev[p][n] + sum_{s<=t} M[t][s] x[s][p] + D x[t][p],
+// M[t][s] = G[t][s] e^{cum_t - cum_s} dt_s.  Both sums are TF32 tensor-core products
+// into the same accumulators; shared memory holds first (C, S_prev), then (M, x).
+// Warp w owns 32 channels (half w >> 2) of the row tiles w & 3 and 7 - (w & 3): the
+// causal product skips the step tiles above the diagonal, and this pairing gives
+// every warp the same number of them.
+template <bool X3>
+__global__ void __launch_bounds__(SSD_THREADS, 2)
 ssd_chunk_out_kernel(const float* __restrict__ bc, const float* __restrict__ G, const float* __restrict__ dtcum,
                      const float* __restrict__ chunk_state, const float* __restrict__ Dv, float* __restrict__ y, int T,
                      int NC, MambaDims p) {
     extern __shared__ float sm[];
-    const int N = p.d_state, P = p.d_head;
+    constexpr int P = SSD_P, LDM = SSD_Q + 4;
+    const int N = p.d_state, ldc = N + 4;
     const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int t0 = c * SSD_Q, nt = min(SSD_Q, T - t0);
     float* sDt = sm;                        // [Q]
@@ -181,108 +270,133 @@ ssd_chunk_out_kernel(const float* __restrict__ bc, const float* __restrict__ G, 
     if (threadIdx.x < SSD_Q) {
         float dt = 0.0f, cum = 0.0f;
         if (threadIdx.x < nt) {
-            const float* o = dtcum + (((int64_t)b * p.n_heads + h) * T + t0 + threadIdx.x) * 2;
-            dt = o[0];
-            cum = o[1];
+            const float2 o = *reinterpret_cast<const float2*>(dtcum + (((int64_t)b * p.n_heads + h) * T + t0 + threadIdx.x) * 2);
+            dt = o.x;
+            cum = o.y;
         }
         sDt[threadIdx.x] = dt;
         sCum[threadIdx.x] = cum;
     }
-    const int tgroups = SSD_Q >> 2, pgroups = P >> 3;
-    const int items = tgroups * pgroups;    // <= SSD_THREADS for d_head <= 64; looped otherwise
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int ph = warp >> 2;
+    const int mts[2] = {warp & 3, 7 - (warp & 3)};
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.0f;
     // phase 1: inter-chunk term
     {
-        float* sC = buf;                    // [Q][N]
-        float* sS = buf + SSD_Q * N;        // [N][P + 4]  (transposed state)
-        const int lds = P + 4;
-        for (int e = threadIdx.x; e < SSD_Q * N; e += SSD_THREADS) {
-            const int t = e / N, n = e - t * N;
-            sC[e] = t < nt ? bc[((int64_t)b * T + t0 + t) * p.conv_dim + p.d_inner + N + n] : 0.0f;
+        float* sC = buf;                    // [Q][N + 4], rows scaled by e^{cum_t}
+        float* sS = buf + SSD_Q * ldc;      // [P][N + 4]
+        const int n4 = N >> 2;
+        for (int e = threadIdx.x; e < SSD_Q * n4; e += SSD_THREADS) {
+            const int t = e / n4, n = (e - t * n4) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < nt) {
+                const float w = expf(sCum[t]);
+                v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + p.d_inner + N + n);
+                v = make_float4(w * v.x, w * v.y, w * v.z, w * v.w);
+            }
+            *reinterpret_cast<float4*>(sC + t * ldc + n) = v;
         }
         const float* sp = chunk_state + (((int64_t)b * NC + c) * p.n_heads + h) * P * N;
-        for (int e = threadIdx.x; e < P * N; e += SSD_THREADS) {
-            const int i = e / N, n = e - i * N;
-            sS[n * lds + i] = sp[e];
+        for (int e = threadIdx.x; e < P * n4; e += SSD_THREADS) {
+            const int i = e / n4, n = (e - i * n4) * 4;
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(sp + i * N + n));
+            *reinterpret_cast<float4*>(sS + i * ldc + n) = v;
+        }
+        __syncthreads();
+        for (int ks = 0; ks < (N >> 3); ++ks) {
+            Tf32Val<X3> a[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float* ca = sC + (mts[i] * 16 + g) * ldc + ks * 8 + t4;
+                a[i][0] = Tf32Val<X3>(ca[0]);
+                a[i][1] = Tf32Val<X3>(ca[8 * ldc]);
+                a[i][2] = Tf32Val<X3>(ca[4]);
+                a[i][3] = Tf32Val<X3>(ca[8 * ldc + 4]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float* sb = sS + (ph * 32 + j * 8 + g) * ldc + ks * 8 + t4;
+                const Tf32Val<X3> b0(sb[0]), b1(sb[4]);
+                mma_x<X3>(acc[0][j], a[0], b0, b1);
+                mma_x<X3>(acc[1][j], a[1], b0, b1);
+            }
         }
     }
     __syncthreads();
-    for (int it = threadIdx.x; it < items; it += SSD_THREADS) {
-        const int tg = it / pgroups, pg = it - tg * pgroups;
-        float acc[4][8] = {};
-        {
-            const float* sC = buf;
-            const float* sS = buf + SSD_Q * N;
-            const int lds = P + 4;
-            for (int n = 0; n < N; ++n) {
-                const float4 s0 = *reinterpret_cast<const float4*>(sS + n * lds + pg * 8);
-                const float4 s1 = *reinterpret_cast<const float4*>(sS + n * lds + pg * 8 + 4);
-                const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float cv = sC[(tg * 4 + i) * N + n];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[i][j] += cv * sv[j];
-                }
+    // phase 2: intra-chunk term
+    {
+        float* sM = buf;                    // [Q][Q + 4]
+        float* sX = buf + SSD_Q * LDM;      // [Q][P + 8]
+        const float* gm = G + ((int64_t)b * NC + c) * SSD_Q * SSD_Q;
+        for (int e = threadIdx.x; e < SSD_Q * (SSD_Q / 4); e += SSD_THREADS) {
+            const int t = e / (SSD_Q / 4), s = (e - t * (SSD_Q / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s <= t && t < nt) {
+                const float4 gv = *reinterpret_cast<const float4*>(gm + t * SSD_Q + s);
+                const float ct = sCum[t];
+                v.x = gv.x * expf(ct - sCum[s]) * sDt[s];
+                if (s + 1 <= t) v.y = gv.y * expf(ct - sCum[s + 1]) * sDt[s + 1];
+                if (s + 2 <= t) v.z = gv.z * expf(ct - sCum[s + 2]) * sDt[s + 2];
+                if (s + 3 <= t) v.w = gv.w * expf(ct - sCum[s + 3]) * sDt[s + 3];
             }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float e = expf(sCum[tg * 4 + i]);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] *= e;
-            }
+            *reinterpret_cast<float4*>(sM + t * LDM + s) = v;
         }
-        __syncthreads();                     // (items <= SSD_THREADS: every thread passes here exactly once)
-        // phase 2: intra-chunk term with M[t][s] = G[t][s] exp(cum_t - cum_s) dt_s for s <= t
-        float* sM = buf;                    // [Q][Q + 1]
-        float* sX = buf + SSD_Q * (SSD_Q + 1);   // [Q][P]
-        {
-            const float* g = G + ((int64_t)b * NC + c) * SSD_Q * SSD_Q;
-            for (int e = threadIdx.x; e < SSD_Q * SSD_Q; e += SSD_THREADS) {
-                const int t = e / SSD_Q, s = e - t * SSD_Q;
-                sM[t * (SSD_Q + 1) + s] = (s <= t && t < nt) ? g[e] * expf(sCum[t] - sCum[s]) * sDt[s] : 0.0f;
-            }
-            for (int e = threadIdx.x; e < SSD_Q * P; e += SSD_THREADS) {
-                const int t = e / P, i = e - t * P;
-                sX[e] = t < nt ? bc[((int64_t)b * T + t0 + t) * p.conv_dim + h * P + i] : 0.0f;
-            }
+        for (int e = threadIdx.x; e < SSD_Q * (P / 4); e += SSD_THREADS) {
+            const int t = e / (P / 4), i = (e - t * (P / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < nt) v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + h * P + i);
+            *reinterpret_cast<float4*>(sX + t * SSD_LDX + i) = v;
         }
         __syncthreads();
-        const int s_end = min(nt, tg * 4 + 4);
-        for (int s = 0; s < s_end; ++s) {
-            const float4 x0 = *reinterpret_cast<const float4*>(sX + s * P + pg * 8);
-            const float4 x1 = *reinterpret_cast<const float4*>(sX + s * P + pg * 8 + 4);
-            const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        const int kmax = (nt + 7) >> 3;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float m = sM[(tg * 4 + i) * (SSD_Q + 1) + s];
+        for (int i = 0; i < 2; ++i) {
+            const int kend = min(2 * (mts[i] + 1), kmax);
+            for (int ks = 0; ks < kend; ++ks) {
+                const float* ma = sM + (mts[i] * 16 + g) * LDM + ks * 8 + t4;
+                const Tf32Val<X3> a[4] = {Tf32Val<X3>(ma[0]), Tf32Val<X3>(ma[8 * LDM]), Tf32Val<X3>(ma[4]),
+                                          Tf32Val<X3>(ma[8 * LDM + 4])};
+                const float* xb = sX + (ks * 8 + t4) * SSD_LDX + ph * 32 + g;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] += m * xv[j];
-            }
-        }
-        const float dskip = Dv[h];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int t = tg * 4 + i;
-            if (t < nt) {
-                float* o = y + ((int64_t)b * T + t0 + t) * p.d_inner + h * P + pg * 8;
-                const float* xr = sX + t * P + pg * 8;
-                *reinterpret_cast<float4*>(o) = make_float4(acc[i][0] + dskip * xr[0], acc[i][1] + dskip * xr[1],
-                                                            acc[i][2] + dskip * xr[2], acc[i][3] + dskip * xr[3]);
-                *reinterpret_cast<float4*>(o + 4) = make_float4(acc[i][4] + dskip * xr[4], acc[i][5] + dskip * xr[5],
-                                                                acc[i][6] + dskip * xr[6], acc[i][7] + dskip * xr[7]);
+                for (int j = 0; j < 4; ++j)
+                    mma_x<X3>(acc[i][j], a, Tf32Val<X3>(xb[j * 8]), Tf32Val<X3>(xb[j * 8 + 4 * SSD_LDX]));
             }
         }
     }
+    const float dskip = Dv[h];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int t = mts[i] * 16 + g + 8 * r;
+            if (t < nt) {
+                const float* xr = bc + ((int64_t)b * T + t0 + t) * p.conv_dim + h * P + ph * 32 + 2 * t4;
+                float* o = y + ((int64_t)b * T + t0 + t) * p.d_inner + h * P + ph * 32 + 2 * t4;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 xv = *reinterpret_cast<const float2*>(xr + j * 8);
+                    *reinterpret_cast<float2*>(o + j * 8) =
+                        make_float2(acc[i][j][2 * r] + dskip * xv.x, acc[i][j][2 * r + 1] + dskip * xv.y);
+                }
+            }
+        }
 }
 
 // The chunked scan over proj / bc (as produced by the projection and the convolution):
 // y [B*T, d_inner], state [B, H, P, N] updated in place.  Returns B200_EUNSUPPORTED for
 // shapes outside its tiling (the caller then runs the sequential scan).
 int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, const float* a_log, const float* D,
-                   float* state, float* y, int B, int T, const MambaDims& p) {
+                   float* state, float* y, int B, int T, const MambaDims& p, bool precise) {
     const int N = p.d_state, P = p.d_head;
-    if (N % 4 != 0 || P % 8 != 0 || (SSD_Q / 4) * (P / 8) != SSD_THREADS || N > 128 || (p.d_inner & 3) != 0)
+    if (P != SSD_P || N % 16 != 0 || N > 128 || (p.d_inner & 3) != 0 || (p.conv_dim & 3) != 0)
         return fail(B200_EUNSUPPORTED, "mamba_ssd_scan: d_head %d / d_state %d outside the chunked kernels' tiling", P, N);
+    if (((uintptr_t)bc | (uintptr_t)y) & 15)
+        return fail(B200_EUNSUPPORTED, "mamba_ssd_scan: buffers must be 16-byte aligned");
     const int NC = ceil_div(T, SSD_Q);
     const size_t g_f = (size_t)B * NC * SSD_Q * SSD_Q, dc_f = (size_t)B * p.n_heads * T * 2,
                  cs_f = (size_t)B * NC * p.n_heads * P * N, de_f = (size_t)B * NC * p.n_heads;
@@ -294,27 +408,35 @@ int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, con
     float* cstate = dtcum + ((dc_f + 3) & ~(size_t)3);
     float* decay = cstate + cs_f;
     const size_t smem_cb = (size_t)2 * SSD_Q * (N + 1) * 4;
-    const size_t smem_st = (size_t)(SSD_Q * N + SSD_Q * P + 2 * SSD_Q) * 4;
-    const size_t smem_out = (size_t)(2 * SSD_Q + std::max(SSD_Q * N + N * (P + 4), SSD_Q * (SSD_Q + 1) + SSD_Q * P)) * 4;
+    const size_t smem_st = (size_t)(SSD_Q * (N + 8) + SSD_Q * SSD_LDX + 2 * SSD_Q) * 4;
+    const size_t smem_out = (size_t)(2 * SSD_Q + std::max(SSD_Q * (N + 4) + P * (N + 4), SSD_Q * (SSD_Q + 4) + SSD_Q * SSD_LDX)) * 4;
     static bool configured = false;
     if (!configured) {
         B200_CUDA(cudaFuncSetAttribute(ssd_cb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-        B200_CUDA(cudaFuncSetAttribute(ssd_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-        B200_CUDA(cudaFuncSetAttribute(ssd_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(ssd_chunk_state_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(ssd_chunk_state_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(ssd_chunk_out_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(ssd_chunk_out_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         configured = true;
     }
     B200_REQUIRE(smem_cb <= 160 * 1024 && smem_st <= 160 * 1024 && smem_out <= 160 * 1024, "mamba_ssd_scan: shared memory");
     B200_REQUIRE(NC <= 65535 * 32 && B <= 65535 && p.n_heads <= 65535, "mamba_ssd_scan: grid too large");
     ssd_cb_kernel<<<dim3(NC, B), SSD_THREADS, smem_cb, stream()>>>(bc, G, T, p);
     B200_LAUNCH_CHECK("ssd_cb_kernel");
-    ssd_chunk_state_kernel<<<dim3(NC, p.n_heads, B), SSD_THREADS, smem_st, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate,
-                                                                                      decay, T, NC, p);
+    const dim3 grid(NC, p.n_heads, B);
+    if (precise)
+        ssd_chunk_state_kernel<true><<<grid, SSD_THREADS, smem_st, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate, decay, T, NC, p);
+    else
+        ssd_chunk_state_kernel<false><<<grid, SSD_THREADS, smem_st, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate, decay, T, NC, p);
     B200_LAUNCH_CHECK("ssd_chunk_state_kernel");
     const int64_t elems = (int64_t)B * p.n_heads * P * N;
     ssd_carry_kernel<<<(unsigned)std::min<int64_t>(ceil_div64(elems, 256), (int64_t)num_sms() * 16), 256, 0, stream()>>>(
         cstate, decay, state, B, NC, p);
     B200_LAUNCH_CHECK("ssd_carry_kernel");
-    ssd_chunk_out_kernel<<<dim3(NC, p.n_heads, B), SSD_THREADS, smem_out, stream()>>>(bc, G, dtcum, cstate, D, y, T, NC, p);
+    if (precise)
+        ssd_chunk_out_kernel<true><<<grid, SSD_THREADS, smem_out, stream()>>>(bc, G, dtcum, cstate, D, y, T, NC, p);
+    else
+        ssd_chunk_out_kernel<false><<<grid, SSD_THREADS, smem_out, stream()>>>(bc, G, dtcum, cstate, D, y, T, NC, p);
     B200_LAUNCH_CHECK("ssd_chunk_out_kernel");
     return B200_OK;
 }
