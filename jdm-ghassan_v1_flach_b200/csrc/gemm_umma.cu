@@ -44,6 +44,9 @@ constexpr int GM_STAGE_A = GM_TILE_M * GM_TILE_K * 2;
 // accumulator rows a lane holds are turned into stores of whole 128-byte lines.
 constexpr int GM_EPI_LD = 33;
 constexpr int GM_EPI_SCRATCH = 4 * 32 * GM_EPI_LD * 4;
+// Row-slot table of the grouped form (see gemm_build_slots).
+constexpr int GM_MAX_SLOTS = 448;
+constexpr int GM_SLOT_TABLE = (1 + 3 * GM_MAX_SLOTS) * 4 + 12;
 
 struct alignas(64) GemmArgs {
     CUtensorMap map_a, map_b, map_b2;   // b2: the "up" matrix of the SwiGLU form
@@ -65,7 +68,7 @@ struct GemmShape {
     static constexpr int STAGE_B = UN * GM_TILE_K * 2;
     static constexpr int STAGE = GM_STAGE_A + STAGE_B;
     static constexpr int STAGES = EPI == GEMM_EPI_SWIGLU ? 4 : 6;
-    static constexpr int SMEM = STAGES * STAGE + GM_EPI_SCRATCH + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int SMEM = STAGES * STAGE + GM_EPI_SCRATCH + 1024 /*alignment slack*/ + 256 /*barriers*/ + GM_SLOT_TABLE;
 };
 
 // One tile of the walk.
@@ -73,9 +76,61 @@ struct GemmTile {
     int group, row0, row_end, n0, brow0;
 };
 
+// Grouped form: row slot -> (group, first row, end of the group), built once per CTA in
+// shared memory so that every role finds a tile with one load instead of a walk over the
+// offsets (with K of a few hundred a tile lasts a few microseconds, and a walk over 64
+// groups costs about two).  tab[0] = slots in use, then 3 ints per slot.
+
+// All threads of the CTA; `scan` is scratch for 2 * (groups + 1) ints.  Leaves tab[0] = -1
+// (callers then walk the offsets) when there are more groups or slots than the table holds.
+__device__ __noinline__ void gemm_build_slots(const GemmArgs& a, int* tab, int* scan) {
+    if (!a.offsets) return;
+    const bool fits = a.groups <= 256 && a.m_slots <= GM_MAX_SLOTS;
+    if (!fits) {
+        if (threadIdx.x == 0) tab[0] = -1;
+        return;
+    }
+    int* cnt = scan;                 // [groups]
+    int* base = scan + a.groups;     // [groups + 1]
+    for (int g = threadIdx.x; g < a.groups; g += blockDim.x)
+        cnt[g] = (a.offsets[g + 1] - a.offsets[g] + a.tile_m - 1) / a.tile_m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int per = (a.groups + 31) >> 5, g0 = threadIdx.x * per;
+        int sum = 0;
+        for (int i = 0; i < per; ++i)
+            if (g0 + i < a.groups) sum += cnt[g0 + i];
+        int incl = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((int)threadIdx.x >= o) incl += up;
+        }
+        int run = incl - sum;
+        for (int i = 0; i < per; ++i)
+            if (g0 + i < a.groups) {
+                base[g0 + i] = run;
+                run += cnt[g0 + i];
+            }
+        if (threadIdx.x == 31) tab[0] = min(incl, GM_MAX_SLOTS);
+    }
+    __syncthreads();
+    for (int g = threadIdx.x; g < a.groups; g += blockDim.x) {
+        const int lo = a.offsets[g], hi = a.offsets[g + 1];
+        for (int i = 0; i < cnt[g]; ++i) {
+            const int s = base[g] + i;
+            if (s < GM_MAX_SLOTS) {
+                tab[1 + 3 * s] = g;
+                tab[2 + 3 * s] = lo + i * a.tile_m;
+                tab[3 + 3 * s] = hi;
+            }
+        }
+    }
+}
+
 // Tile t of the list -> coordinates; false when the slot lies past the last row tile
 // (the grouped list is sized by an upper bound).
-__device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, int t, GemmTile& w) {
+__device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, const int* tab, int t, GemmTile& w) {
     int slot = t / a.n_tiles;
     w.n0 = (t - slot * a.n_tiles) * GM_TILE_N;
     w.group = 0; w.row0 = 0; w.row_end = a.M;
@@ -83,6 +138,9 @@ __device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, int t, GemmTile&
     if (!a.offsets) {
         w.row0 = slot * a.tile_m;
         found = w.row0 < a.M;
+    } else if (tab[0] >= 0) {
+        found = slot < tab[0];
+        if (found) { w.group = tab[1 + 3 * slot]; w.row0 = tab[2 + 3 * slot]; w.row_end = tab[3 + 3 * slot]; }
     } else {
         int lo = a.offsets[0];
         for (int g = 0; g < a.groups; ++g) {
@@ -162,11 +220,11 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tacc, 
 // ACC accumulator sets of HALVES x UN columns each; half h holds rows row0 + 128 h ...
 template <int EPI, int UN, int ACC, int HALVES>
 __device__ __forceinline__ void gemm_epilogue_loop(const GemmArgs& a, uint32_t tmem, uint64_t* acc_full, uint64_t* acc_empty,
-                                                   int warp, int lane, int total, float* scratch) {
+                                                   int warp, int lane, int total, float* scratch, const int* tab) {
     uint32_t ti = 0;
     for (int t = blockIdx.x; t < total; t += gridDim.x) {
         GemmTile w;
-        if (!gemm_tile_at(a, t, w)) continue;
+        if (!gemm_tile_at(a, tab, t, w)) continue;
         const int as = ti % ACC;
         bool ok = mbar_wait(&acc_full[as], (ti / ACC) & 1, a.status);
         ok = __all_sync(0xffffffffu, ok && *reinterpret_cast<volatile int*>(a.status) == 0);
@@ -198,9 +256,11 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
     uint64_t* acc_full = empty + S::STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    int* tab = reinterpret_cast<int*>(smem + S::STAGES * S::STAGE + GM_EPI_SCRATCH + 256);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total = a.m_slots * a.n_tiles;
     const int KB = (a.K + GM_TILE_K - 1) / GM_TILE_K;
+    gemm_build_slots(a, tab, reinterpret_cast<int*>(epi_scratch));
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::STAGES; ++s) {
@@ -228,7 +288,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
             bool ok = true;
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 GemmTile w;
-                if (!gemm_tile_at(a, t, w)) continue;
+                if (!gemm_tile_at(a, tab, t, w)) continue;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % S::STAGES;
                     if (it >= S::STAGES) ok = mbar_wait(&empty[s], ((it / S::STAGES) - 1) & 1, a.status);
@@ -255,7 +315,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
             bool ok = true;
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 GemmTile w;
-                if (!gemm_tile_at(a, t, w)) continue;
+                if (!gemm_tile_at(a, tab, t, w)) continue;
                 const int as = ti & 1;
                 if (ti >= 2) ok = mbar_wait(&acc_empty[as], ((ti >> 1) - 1) & 1, a.status);
                 if (!ok) break;
@@ -280,7 +340,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
             }
         }
     } else {
-        gemm_epilogue_loop<EPI, S::UN, 2, 1>(a, tmem, acc_full, acc_empty, warp, lane, total, epi_scratch);
+        gemm_epilogue_loop<EPI, S::UN, 2, 1>(a, tmem, acc_full, acc_empty, warp, lane, total, epi_scratch, tab);
     }
     tc_fence_before();
     __syncthreads();
@@ -321,7 +381,7 @@ struct GemmQShape {
     // the SwiGLU form (256 columns per half) has one.
     static constexpr int A_STAGE = 2 * GM_STAGE_A;
     static constexpr int SA = UN == 128 ? 3 : 2, SB = UN == 128 ? 3 : 2, ACC = UN == 128 ? 2 : 1;
-    static constexpr int FIXED = SA * A_STAGE + SB * B16 + GM_EPI_SCRATCH + 1024 + 256;
+    static constexpr int FIXED = SA * A_STAGE + SB * B16 + GM_EPI_SCRATCH + 1024 + 256 + GM_SLOT_TABLE;
     // packed stages: as many as fit (up to 4) - with few rows of A the kernel is a pure
     // weight stream and needs tens of KB in flight per SM to keep HBM busy
     static constexpr int ROOM = (227 * 1024 - FIXED) / PACKED;
@@ -428,9 +488,11 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
     uint64_t* acc_full = p_empty + 4;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    int* tab = reinterpret_cast<int*>(sm_p + S::SP * S::PACKED + GM_EPI_SCRATCH + 256);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total = a.m_slots * a.n_tiles;
     const int KB = a.K / GM_TILE_K;                   // K % 256 == 0 (host)
+    gemm_build_slots(a, tab, reinterpret_cast<int*>(epi_scratch));
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::SA; ++s) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
@@ -454,7 +516,7 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
             bool ok = true;
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 GemmTile w;
-                if (!gemm_tile_at(a, t, w)) continue;
+                if (!gemm_tile_at(a, tab, t, w)) continue;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     if ((kb & 3) == 0) {
                         const int p = sbi % S::SP;
@@ -486,7 +548,7 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
             bool ok = true;
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 GemmTile w;
-                if (!gemm_tile_at(a, t, w)) continue;
+                if (!gemm_tile_at(a, tab, t, w)) continue;
                 const int as = ti % S::ACC;
                 if (ti >= S::ACC) ok = mbar_wait(&acc_empty[as], ((ti / S::ACC) - 1) & 1, a.status);
                 if (!ok) break;
@@ -520,7 +582,7 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
             }
         }
     } else if (warp < GQ_FIRST_EXPAND) {
-        gemm_epilogue_loop<EPI, S::UN, S::ACC, 2>(a, tmem, acc_full, acc_empty, warp, lane, total, epi_scratch);
+        gemm_epilogue_loop<EPI, S::UN, S::ACC, 2>(a, tmem, acc_full, acc_empty, warp, lane, total, epi_scratch, tab);
     } else {
         // eight expanding warps: thread -> (B row, which 32 of the block's 64 weights)
         const int x = threadIdx.x - GQ_FIRST_EXPAND * 32, row_t = x & 127, hh = x >> 7;
@@ -528,7 +590,7 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
         bool ok = true;
         for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
             GemmTile w;
-            if (!gemm_tile_at(a, t, w)) continue;
+            if (!gemm_tile_at(a, tab, t, w)) continue;
             for (int kb = 0; kb < KB; ++kb, ++it) {
                 const int j = kb & 3, b = it % S::SB;
                 if (j == 0) ++sbi;                    // sbi - 1 is the super-block in use

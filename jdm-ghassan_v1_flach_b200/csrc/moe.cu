@@ -151,7 +151,7 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ router_w
 // __match_any_sync and warps are ordered through shared-memory prefix sums.
 // ---------------------------------------------------------------------------
 constexpr int PERM_THREADS = 256;
-constexpr int PERM_ITERS = 16;                             // slots per block = 256 * 16
+constexpr int PERM_ITERS = 4;                              // slots per block = 256 * 4
 constexpr int PERM_CHUNK = PERM_THREADS * PERM_ITERS;
 
 __global__ void __launch_bounds__(PERM_THREADS)
