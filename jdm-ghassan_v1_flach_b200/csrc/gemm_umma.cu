@@ -128,13 +128,26 @@ __device__ __noinline__ void gemm_build_slots(const GemmArgs& a, int* tab, int* 
     }
 }
 
+// The walk over the offsets for group lists the table does not hold.
+__device__ __noinline__ int4 gemm_slot_walk(const int32_t* offsets, int groups, int tile_m, int slot) {
+    int lo = offsets[0];
+    for (int g = 0; g < groups; ++g) {
+        const int hi = offsets[g + 1];
+        const int tiles = (hi - lo + tile_m - 1) / tile_m;
+        if (slot < tiles) return make_int4(1, g, lo + slot * tile_m, hi);
+        slot -= tiles;
+        lo = hi;
+    }
+    return make_int4(0, 0, 0, 0);
+}
+
 // Tile t of the list -> coordinates; false when the slot lies past the last row tile
 // (the grouped list is sized by an upper bound).
 __device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, const int* tab, int t, GemmTile& w) {
-    int slot = t / a.n_tiles;
+    const int slot = t / a.n_tiles;
     w.n0 = (t - slot * a.n_tiles) * GM_TILE_N;
     w.group = 0; w.row0 = 0; w.row_end = a.M;
-    bool found = false;
+    bool found;
     if (!a.offsets) {
         w.row0 = slot * a.tile_m;
         found = w.row0 < a.M;
@@ -142,18 +155,9 @@ __device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, const int* tab, 
         found = slot < tab[0];
         if (found) { w.group = tab[1 + 3 * slot]; w.row0 = tab[2 + 3 * slot]; w.row_end = tab[3 + 3 * slot]; }
     } else {
-        int lo = a.offsets[0];
-        for (int g = 0; g < a.groups; ++g) {
-            const int hi = a.offsets[g + 1];
-            const int tiles = (hi - lo + a.tile_m - 1) / a.tile_m;
-            if (slot < tiles) {
-                w.group = g; w.row0 = lo + slot * a.tile_m; w.row_end = hi;
-                found = true;
-                break;
-            }
-            slot -= tiles;
-            lo = hi;
-        }
+        const int4 r = gemm_slot_walk(a.offsets, a.groups, a.tile_m, slot);
+        found = r.x != 0;
+        if (found) { w.group = r.y; w.row0 = r.z; w.row_end = r.w; }
     }
     w.brow0 = (a.group_map && found ? a.group_map[w.group] : w.group) * a.N + w.n0;
     return found;

@@ -193,6 +193,48 @@ __global__ void mamba_conv_seq_kernel(const float* __restrict__ proj, const floa
     }
 }
 
+// The same for a window of four taps: a thread owns four adjacent channels and walks
+// CONV_TT consecutive steps with the window in registers (one 16-byte load and one
+// 16-byte store per step instead of four scalar loads per output).  Same products and
+// the same order of additions as the kernel above.
+constexpr int CONV_TT = 8;
+__global__ void __launch_bounds__(256)
+mamba_conv_seq4_kernel(const float* __restrict__ proj, const float* __restrict__ conv_w, const float* __restrict__ conv_b,
+                       float* __restrict__ bc, int T, MambaDims p) {
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (c >= p.conv_dim) return;
+    const int t0 = blockIdx.y * CONV_TT, b = blockIdx.z;
+    float w[4][4];
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {
+        const float4 v = *reinterpret_cast<const float4*>(conv_w + (int64_t)(c + ch) * 4);
+        w[ch][0] = v.x; w[ch][1] = v.y; w[ch][2] = v.z; w[ch][3] = v.w;
+    }
+    float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (conv_b) bias = *reinterpret_cast<const float4*>(conv_b + c);
+    const float* src = proj + (int64_t)b * T * p.proj + p.d_inner + c;
+    auto at = [&](int t) {
+        return t >= 0 ? *reinterpret_cast<const float4*>(src + (int64_t)t * p.proj) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    float4 x0 = at(t0 - 3), x1 = at(t0 - 2), x2 = at(t0 - 1);
+    float* dst = bc + ((int64_t)b * T + t0) * p.conv_dim + c;
+    const int nt = min(CONV_TT, T - t0);
+    for (int i = 0; i < nt; ++i) {
+        const float4 x3 = at(t0 + i);
+        auto tap = [&](float bi, const float (&wc)[4], float a0, float a1, float a2, float a3) {
+            float a = __fadd_rn(bi, __fmul_rn(wc[0], a0));
+            a = __fadd_rn(a, __fmul_rn(wc[1], a1));
+            a = __fadd_rn(a, __fmul_rn(wc[2], a2));
+            a = __fadd_rn(a, __fmul_rn(wc[3], a3));
+            return silu_acc(a);
+        };
+        *reinterpret_cast<float4*>(dst + (int64_t)i * p.conv_dim) =
+            make_float4(tap(bias.x, w[0], x0.x, x1.x, x2.x, x3.x), tap(bias.y, w[1], x0.y, x1.y, x2.y, x3.y),
+                        tap(bias.z, w[2], x0.z, x1.z, x2.z, x3.z), tap(bias.w, w[3], x0.w, x1.w, x2.w, x3.w));
+        x0 = x1; x1 = x2; x2 = x3;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Prefill: sequential selective scan.  One block per (b, h); thread (i, part)
 // keeps d_state/PARTS state elements of row i in registers for the whole
@@ -443,8 +485,16 @@ int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const 
     {
         const int64_t total = NT * p.conv_dim;
         const int grid = (int)std::min<int64_t>(ceil_div64(total, 256), (int64_t)num_sms() * 32);
-        mamba_conv_seq_kernel<<<grid, 256, 0, stream()>>>(proj, conv_w, conv_b, bc, B, T, p);
-        B200_LAUNCH_CHECK("mamba_conv_seq_kernel");
+        auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+        if (p.k == 4 && p.conv_dim % 4 == 0 && p.d_inner % 4 == 0 && p.proj % 4 == 0 && al16(proj) && al16(bc) &&
+            al16(conv_w) && (!conv_b || al16(conv_b)) && B <= 65535 && ceil_div(T, CONV_TT) <= 65535) {
+            mamba_conv_seq4_kernel<<<dim3(ceil_div(p.conv_dim / 4, 256), ceil_div(T, CONV_TT), B), 256, 0, stream()>>>(
+                proj, conv_w, conv_b, bc, T, p);
+            B200_LAUNCH_CHECK("mamba_conv_seq4_kernel");
+        } else {
+            mamba_conv_seq_kernel<<<grid, 256, 0, stream()>>>(proj, conv_w, conv_b, bc, B, T, p);
+            B200_LAUNCH_CHECK("mamba_conv_seq_kernel");
+        }
         if (conv_state_out && p.k > 1) {
             const int64_t n = (int64_t)B * p.conv_dim * (p.k - 1);
             mamba_conv_window_kernel<<<(unsigned)std::min<int64_t>(ceil_div64(n, 256), 4096), 256, 0, stream()>>>(
