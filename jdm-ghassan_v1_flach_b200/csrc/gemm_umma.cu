@@ -163,6 +163,12 @@ __device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, const int* tab, 
     return found;
 }
 
+// silu for the SwiGLU epilogue, whose result is rounded to fp16 (2^-11) right away: the
+// fast exponential and reciprocal (a few fp32 ulp) are invisible at that precision and
+// cost a fifth of the accurate forms, which matters because this epilogue (65536
+// activations per tile on four warps) is not hidden behind a second accumulator set.
+__device__ __forceinline__ float silu_fast(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+
 // Epilogue of one 128 x 128 tile out of the accumulator at `tacc`, run by the four
 // warps whose index modulo 4 selects the 32 accumulator rows (tensor-memory lanes) a
 // warp may read.
@@ -181,15 +187,36 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tacc, 
         if (EPI == GEMM_EPI_SWIGLU) {
             float u[32];
             tmem_ld32(tbase + GM_TILE_N + c0, u);
-            if (row < row_end) {
+            if (n0 + c0 + 32 <= a.N && (a.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(a.c16) & 7) == 0) {
+                // as the store form below: through the warp's shared block, so that eight
+                // lanes write one row's 64 bytes and an instruction covers four rows
+#pragma unroll
+                for (int i = 0; i < 32; ++i) stg[lane * GM_EPI_LD + i] = silu_fast(v[i]) * u[i];
+                __syncwarp();
+                const int cq = 4 * (lane & 7);
+#pragma unroll
+                for (int itr = 0; itr < 8; ++itr) {
+                    const int r = itr * 4 + (lane >> 3);
+                    const int grow = w.row0 + q * 32 + r;
+                    const float* sp = stg + r * GM_EPI_LD + cq;
+                    if (grow < row_end) {
+                        const __half2 h01 = __floats2half2_rn(sp[0], sp[1]), h23 = __floats2half2_rn(sp[2], sp[3]);
+                        uint2 pk;
+                        pk.x = *reinterpret_cast<const uint32_t*>(&h01);
+                        pk.y = *reinterpret_cast<const uint32_t*>(&h23);
+                        *reinterpret_cast<uint2*>(a.c16 + (int64_t)grow * a.ldc + n0 + c0 + cq) = pk;
+                    }
+                }
+                __syncwarp();
+            } else if (row < row_end) {
                 __half* dst = a.c16 + (int64_t)row * a.ldc + n0 + c0;
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     if (n0 + c0 + i + 1 < a.N) {
                         *reinterpret_cast<__half2*>(dst + i) =
-                            __floats2half2_rn(silu_acc(v[i]) * u[i], silu_acc(v[i + 1]) * u[i + 1]);
+                            __floats2half2_rn(silu_fast(v[i]) * u[i], silu_fast(v[i + 1]) * u[i + 1]);
                     } else if (n0 + c0 + i < a.N) {
-                        dst[i] = __float2half_rn(silu_acc(v[i]) * u[i]);
+                        dst[i] = __float2half_rn(silu_fast(v[i]) * u[i]);
                     }
                 }
             }
