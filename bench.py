@@ -487,7 +487,8 @@ def gemm_only_bench():
     msq = timed(lambda: lib.b200_linear_forward_q4(x, wq, y, M, K, N, 3))
     out = {"linear_fp16": {"M": M, "K": K, "N": N, "ms": ms16, "tflops": flops / ms16 / 1e9},
            "linear_q4k": {"M": M, "K": K, "N": N, "ms": msq, "tflops": flops / msq / 1e9},
-           "moe_512": moe_layer_bench(lib, 0, 1, tokens=512), "moe_4096": moe_layer_bench(lib, 0, 1, tokens=4096)}
+           "moe_512": moe_layer_bench(lib, 0, 1, tokens=512), "moe_4096": moe_layer_bench(lib, 0, 1, tokens=4096),
+           "moe_16384": moe_layer_bench(lib, 0, 1, tokens=16384)}
     if lib.raw("b200_stream_status") != 0:
         raise RuntimeError(lib.last_error())
     print(json.dumps(out))

@@ -47,7 +47,7 @@ struct Workspace {
     int ensure(size_t need, void** out);
     void release();
 };
-enum { WS_LINEAR = 0, WS_MOE = 1, WS_MAMBA = 2, WS_ATTN = 3, WS_SAMPLE = 4, WS_PERM = 5, WS_ROUTE = 6, WS_PREFILL = 7, WS_COUNT = 8 };
+enum { WS_LINEAR = 0, WS_MOE = 1, WS_MAMBA = 2, WS_ATTN = 3, WS_SAMPLE = 4, WS_PERM = 5, WS_ROUTE = 6, WS_PREFILL = 7, WS_SPLITK = 8, WS_COUNT = 9 };
 Workspace& workspace(int which);
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

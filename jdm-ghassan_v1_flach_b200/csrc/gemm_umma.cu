@@ -60,6 +60,11 @@ struct alignas(64) GemmArgs {
     int64_t ldc;
     float scale;
     int* status;
+    // split K (packed-weight store form with few tiles): the tile list is repeated k_splits
+    // times, repetition s covers K steps [s * kb_split, (s + 1) * kb_split) and stores its
+    // partial product at c + s * split_stride; a second kernel adds the partials in order
+    int k_splits, kb_split;
+    int64_t split_stride;
 };
 
 template <int EPI>
@@ -74,6 +79,7 @@ struct GemmShape {
 // One tile of the walk.
 struct GemmTile {
     int group, row0, row_end, n0, brow0;
+    int split;                          // which K range (0 unless the launch splits K)
 };
 
 // Grouped form: row slot -> (group, first row, end of the group), built once per CTA in
@@ -144,6 +150,11 @@ __device__ __noinline__ int4 gemm_slot_walk(const int32_t* offsets, int groups, 
 // Tile t of the list -> coordinates; false when the slot lies past the last row tile
 // (the grouped list is sized by an upper bound).
 __device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, const int* tab, int t, GemmTile& w) {
+    w.split = 0;
+    if (a.k_splits > 1) {
+        w.split = t % a.k_splits;
+        t /= a.k_splits;
+    }
     const int slot = t / a.n_tiles;
     w.n0 = (t - slot * a.n_tiles) * GM_TILE_N;
     w.group = 0; w.row0 = 0; w.row_end = a.M;
@@ -233,12 +244,12 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tacc, 
                 const int grow = w.row0 + q * 32 + r;
                 const float* sp = stg + r * GM_EPI_LD + cq;
                 if (grow < row_end)
-                    *reinterpret_cast<float4*>(a.c + (int64_t)grow * a.ldc + n0 + c0 + cq) =
+                    *reinterpret_cast<float4*>(a.c + w.split * a.split_stride + (int64_t)grow * a.ldc + n0 + c0 + cq) =
                         make_float4(sp[0], sp[1], sp[2], sp[3]);
             }
             __syncwarp();
         } else if (row < row_end) {
-            float* dst = a.c + (int64_t)row * a.ldc + n0 + c0;
+            float* dst = a.c + w.split * a.split_stride + (int64_t)row * a.ldc + n0 + c0;
 #pragma unroll
             for (int i = 0; i < 32; ++i)
                 if (n0 + c0 + i < a.N) dst[i] = v[i] * a.scale;
@@ -521,8 +532,8 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     int* tab = reinterpret_cast<int*>(sm_p + S::SP * S::PACKED + GM_EPI_SCRATCH + 256);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int total = a.m_slots * a.n_tiles;
-    const int KB = a.K / GM_TILE_K;                   // K % 256 == 0 (host)
+    const int total = a.m_slots * a.n_tiles * a.k_splits;
+    const int KB_ALL = a.K / GM_TILE_K;               // K % 256 == 0 (host)
     gemm_build_slots(a, tab, reinterpret_cast<int*>(epi_scratch));
 
     if (threadIdx.x == 0) {
@@ -548,7 +559,8 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 GemmTile w;
                 if (!gemm_tile_at(a, tab, t, w)) continue;
-                for (int kb = 0; kb < KB; ++kb, ++it) {
+                const int kb0 = w.split * a.kb_split, kb1 = min(KB_ALL, kb0 + a.kb_split);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     if ((kb & 3) == 0) {
                         const int p = sbi % S::SP;
                         if (sbi >= S::SP) ok = mbar_wait(&p_empty[p], ((sbi / S::SP) - 1) & 1, a.status);
@@ -586,7 +598,8 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
                 tc_fence_after();
                 const uint32_t tacc = tmem + as * (2 * S::UN);
                 const bool two = w.row0 + GM_TILE_M < w.row_end;
-                for (int kb = 0; kb < KB; ++kb, ++it) {
+                const int kb0 = w.split * a.kb_split, kb1 = min(KB_ALL, kb0 + a.kb_split);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % S::SA, b = it % S::SB;
                     ok = mbar_wait(&a_full[s], (it / S::SA) & 1, a.status) &&
                          mbar_wait(&b_full[b], (it / S::SB) & 1, a.status);
@@ -597,12 +610,12 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
 #pragma unroll
                     for (int k = 0; k < GM_TILE_K / 16; ++k)
                         umma_f16(tacc, umma_smem_desc(a_addr + k * 32), umma_smem_desc(b_addr + k * 32), idesc,
-                                 kb > 0 || k > 0);
+                                 kb > kb0 || k > 0);
                     if (two) {
 #pragma unroll
                         for (int k = 0; k < GM_TILE_K / 16; ++k)
                             umma_f16(tacc + S::UN, umma_smem_desc(a_addr + GM_STAGE_A + k * 32),
-                                     umma_smem_desc(b_addr + k * 32), idesc, kb > 0 || k > 0);
+                                     umma_smem_desc(b_addr + k * 32), idesc, kb > kb0 || k > 0);
                     }
                     umma_commit(&a_empty[s]);
                     umma_commit(&b_empty[b]);
@@ -622,7 +635,8 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
         for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
             GemmTile w;
             if (!gemm_tile_at(a, tab, t, w)) continue;
-            for (int kb = 0; kb < KB; ++kb, ++it) {
+            const int kb0 = w.split * a.kb_split, kb1 = min(KB_ALL, kb0 + a.kb_split);
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const int j = kb & 3, b = it % S::SB;
                 if (j == 0) ++sbi;                    // sbi - 1 is the super-block in use
                 const int p = (sbi - 1) % S::SP;
@@ -764,6 +778,18 @@ static int make_packed_map(CUtensorMap* out, const void* base, int64_t rows, int
     return B200_OK;
 }
 
+// c[m, n] = sum over the splits, in split order (deterministic), of the partial products.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, float* __restrict__ c, int splits,
+                                                           int64_t stride, int M, int N, int64_t ldc) {
+    const int64_t total = (int64_t)M * N;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / N, o = m * ldc + (i - m * N);
+        float v = part[o];
+        for (int s = 1; s < splits; ++s) v += part[s * stride + o];
+        c[o] = v;
+    }
+}
+
 template <int EPI, int KIND>
 static int launch_gemm_q(const GemmArgs& a) {
     using S = GemmQShape<EPI, KIND>;
@@ -777,9 +803,35 @@ static int launch_gemm_q(const GemmArgs& a) {
     b.tile_m = 2 * GM_TILE_M;
     b.m_slots = (a.M + b.tile_m - 1) / b.tile_m + (a.offsets ? a.groups : 0);
     b.n_tiles = (a.N + GM_TILE_N - 1) / GM_TILE_N;
-    const int grid = std::min(b.m_slots * b.n_tiles, num_sms());
+    b.k_splits = 1;
+    b.kb_split = a.K / GM_TILE_K;
+    b.split_stride = 0;
+    // Few tiles (few rows and a narrow matrix: batched decode, the attention projections):
+    // every CTA would stream its 128 weight rows over all of K while most SMs idle, so K is
+    // cut across CTAs and the partial products are added afterwards in a fixed order.
+    const int tiles = b.m_slots * b.n_tiles, sb = a.K / 256;
+    if (EPI == GEMM_EPI_STORE && sb >= 2 && tiles * 2 <= num_sms()) {
+        const int want = std::min(sb, num_sms() / tiles);
+        const int per = (sb + want - 1) / want;
+        b.k_splits = (sb + per - 1) / per;
+        b.kb_split = per * 4;
+    }
+    if (b.k_splits > 1) {
+        b.split_stride = (int64_t)a.M * a.ldc;
+        void* wsp;
+        int rc = workspace(WS_SPLITK).ensure((size_t)b.k_splits * b.split_stride * sizeof(float) + 256, &wsp);
+        if (rc) return rc;
+        b.c = static_cast<float*>(wsp);
+    }
+    const int grid = std::min(tiles * b.k_splits, num_sms());
     kern<<<grid, GQ_THREADS, S::SMEM, stream()>>>(b);
     B200_LAUNCH_CHECK("umma_gemm_q_kernel");
+    if (b.k_splits > 1) {
+        const int64_t total = (int64_t)a.M * a.N;
+        splitk_reduce_kernel<<<(unsigned)std::min<int64_t>(ceil_div64(total, 256), (int64_t)num_sms() * 8), 256, 0, stream()>>>(
+            b.c, a.c, b.k_splits, b.split_stride, a.M, a.N, a.ldc);
+        B200_LAUNCH_CHECK("splitk_reduce_kernel");
+    }
     return B200_OK;
 }
 
@@ -835,6 +887,9 @@ static int launch_gemm(const GemmArgs& a) {
     b.tile_m = GM_TILE_M;
     b.m_slots = (a.M + b.tile_m - 1) / b.tile_m + (a.offsets ? a.groups : 0);
     b.n_tiles = (a.N + GM_TILE_N - 1) / GM_TILE_N;
+    b.k_splits = 1;
+    b.kb_split = 0;
+    b.split_stride = 0;
     const int grid = std::min(b.m_slots * b.n_tiles, num_sms());
     kern<<<grid, GM_THREADS, S::SMEM, stream()>>>(b);
     B200_LAUNCH_CHECK("umma_gemm_kernel");
