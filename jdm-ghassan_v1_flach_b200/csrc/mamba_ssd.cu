@@ -32,45 +32,47 @@ constexpr int SSD_THREADS = 256;
 __device__ __forceinline__ float softplus_dt(float u) { return (u > 20.0f) ? u : log1pf(expf(u)); }
 
 // ---- G = C B^T per (sequence, chunk) ---------------------------------------------
-// grid (chunks, B); thread (ty, tx) of a 16 x 16 block owns an 8 x 8 block of G.
+// Only s <= t is ever used, so of the four 64 x 64 quadrants of G the upper right one is
+// skipped: grid (3 * chunks, B), quadrant (0,0), (1,0) or (1,1) per block; thread
+// (ty, tx) of a 16 x 16 block owns a 4 x 4 block of its quadrant.  fp32 throughout.
 __global__ void __launch_bounds__(SSD_THREADS)
 ssd_cb_kernel(const float* __restrict__ bc, float* __restrict__ G, int T, MambaDims p) {
     extern __shared__ float sm[];
+    constexpr int H = SSD_Q / 2;
     const int N = p.d_state, ld = N + 1;
-    float* sC = sm;                         // [Q][ld]
-    float* sB = sm + SSD_Q * ld;            // [Q][ld]
-    const int c = blockIdx.x, b = blockIdx.y;
+    float* sC = sm;                         // [H][ld]
+    float* sB = sm + H * ld;                // [H][ld]
+    const int c = blockIdx.x / 3, quad = blockIdx.x - 3 * c, b = blockIdx.y;
+    const int NC = gridDim.x / 3;
+    const int ti = quad == 0 ? 0 : H, si = quad == 2 ? H : 0;        // first row (t) and column (s)
     const int t0 = c * SSD_Q, nt = min(SSD_Q, T - t0);
-    for (int e = threadIdx.x; e < SSD_Q * N; e += SSD_THREADS) {
-        const int t = e / N, n = e - t * N;
+    for (int e = threadIdx.x; e < H * N; e += SSD_THREADS) {
+        const int r = e / N, n = e - r * N;
         float bv = 0.0f, cv = 0.0f;
-        if (t < nt) {
-            const float* row = bc + ((int64_t)b * T + t0 + t) * p.conv_dim + p.d_inner;
-            bv = row[n];
-            cv = row[N + n];
-        }
-        sB[t * ld + n] = bv;
-        sC[t * ld + n] = cv;
+        if (si + r < nt) bv = bc[((int64_t)b * T + t0 + si + r) * p.conv_dim + p.d_inner + n];
+        if (ti + r < nt) cv = bc[((int64_t)b * T + t0 + ti + r) * p.conv_dim + p.d_inner + N + n];
+        sB[r * ld + n] = bv;
+        sC[r * ld + n] = cv;
     }
     __syncthreads();
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
-    float acc[8][8] = {};
+    float acc[4][4] = {};
     for (int n = 0; n < N; ++n) {
-        float cv[8], bv[8];
+        float cv[4], bv[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) cv[i] = sC[(ty * 8 + i) * ld + n];
+        for (int i = 0; i < 4; ++i) cv[i] = sC[(ty * 4 + i) * ld + n];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) bv[j] = sB[(tx * 8 + j) * ld + n];
+        for (int j = 0; j < 4; ++j) bv[j] = sB[(tx * 4 + j) * ld + n];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[i][j] += cv[i] * bv[j];
+            for (int j = 0; j < 4; ++j) acc[i][j] += cv[i] * bv[j];
     }
-    float* g = G + ((int64_t)b * gridDim.x + c) * SSD_Q * SSD_Q;
+    float* g = G + ((int64_t)b * NC + c) * SSD_Q * SSD_Q;
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) g[(ty * 8 + i) * SSD_Q + tx * 8 + j] = acc[i][j];
+    for (int i = 0; i < 4; ++i)
+        *reinterpret_cast<float4*>(g + (ti + ty * 4 + i) * SSD_Q + si + tx * 4) =
+            make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
 }
 
 // ---- tensor-core pieces ---------------------------------------------------------------
@@ -407,7 +409,7 @@ int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, con
     float* dtcum = G + g_f;
     float* cstate = dtcum + ((dc_f + 3) & ~(size_t)3);
     float* decay = cstate + cs_f;
-    const size_t smem_cb = (size_t)2 * SSD_Q * (N + 1) * 4;
+    const size_t smem_cb = (size_t)SSD_Q * (N + 1) * 4;
     const size_t smem_st = (size_t)(SSD_Q * (N + 8) + SSD_Q * SSD_LDX + 2 * SSD_Q) * 4;
     const size_t smem_out = (size_t)(2 * SSD_Q + std::max(SSD_Q * (N + 4) + P * (N + 4), SSD_Q * (SSD_Q + 4) + SSD_Q * SSD_LDX)) * 4;
     static bool configured = false;
@@ -421,7 +423,8 @@ int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, con
     }
     B200_REQUIRE(smem_cb <= 160 * 1024 && smem_st <= 160 * 1024 && smem_out <= 160 * 1024, "mamba_ssd_scan: shared memory");
     B200_REQUIRE(NC <= 65535 * 32 && B <= 65535 && p.n_heads <= 65535, "mamba_ssd_scan: grid too large");
-    ssd_cb_kernel<<<dim3(NC, B), SSD_THREADS, smem_cb, stream()>>>(bc, G, T, p);
+    // (the upper right quadrant of every G is never written and never read: s <= t only)
+    ssd_cb_kernel<<<dim3(3 * NC, B), SSD_THREADS, smem_cb, stream()>>>(bc, G, T, p);
     B200_LAUNCH_CHECK("ssd_cb_kernel");
     const dim3 grid(NC, p.n_heads, B);
     if (precise)
