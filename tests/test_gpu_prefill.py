@@ -17,7 +17,7 @@ def _stepwise(dec, prompt):
     return nxt, dec.logits()
 
 
-@pytest.mark.parametrize("T", [5, 48, 200])
+@pytest.mark.parametrize("T", [1, 5, 48, 200])
 def test_prefill_matches_stepwise_decode(oracle, T):
     """Short prompts take the per-row kernels (fp32), long ones the tensor-core path
     (fp16 operands): logits agree within the fp16 scale-relative bound either way, and
@@ -77,7 +77,28 @@ def test_prefill_needs_empty_sequences(oracle):
     with pytest.raises(Exception):
         dec.prefill(np.zeros((1, 4), np.int32))
     dec.reset()
+    with pytest.raises(Exception):
+        dec.prefill(np.zeros((1, 65), np.int32))      # longer than the context (16 rounds up to one 64-token page)
     dec.prefill(np.zeros((1, 4), np.int32))
     with pytest.raises(Exception):
-        dec.prefill(np.zeros((1, 32), np.int32))      # sequences no longer empty
+        dec.prefill(np.zeros((1, 4), np.int32))       # sequences no longer empty
     dec.close()
+
+
+def test_prefill_fp16_weights_and_reset(oracle):
+    """qkind -1 (fp16 matrices: the GEMM without the in-kernel expansion), and a second prompt
+    after reset reproduces the first run bit for bit (no state leaks through the workspaces)."""
+    cfg = dict(TINY, qkind=-1)
+    model = make_model(oracle, cfg, 11)
+    prompt = np.random.default_rng(3).integers(0, cfg["vocab"], (2, 150))
+    a = CudaDecoder(model, batch=2, max_ctx=160)
+    b = CudaDecoder(model, batch=2, max_ctx=160)
+    _, want = _stepwise(a, prompt)
+    b.prefill(prompt)
+    first = b.logits().copy()
+    fp16_close(first, want)
+    b.reset()
+    b.prefill(prompt)
+    assert np.array_equal(b.logits(), first)
+    a.close()
+    b.close()
