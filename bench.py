@@ -61,6 +61,13 @@ T_IDS = dict(embed=0, final_norm=1, lm_head=2, inv_freq=3, attn_norm=10, ffn_nor
              sh_gate=45, sh_up=46, sh_down=47)
 
 
+# DRAM bytes (read + written) of one decode step of the default workload (H-Tiny shape, Q4_K,
+# batch 1, ctx 4096, fused mode, graph): the sum over the step's 261 launches of an ncu capture,
+# summarised in profiles/decode_step_htiny_q4k_bs1_dram_bytes.md.  Reported as roofline.traffic
+# for exactly that workload, null otherwise.
+STEP_DRAM_TRAFFIC_BYTES = 1176.5e6
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -544,6 +551,9 @@ def main():
     ap.add_argument("--graph", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--small", action="store_true", help="4-layer model (development only; not a bench number)")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="after the timed steps run ONE more step between cudaProfilerStart/Stop and exit "
+                         "(for ncu --profile-from-start off: DRAM bytes of every launch of a step)")
     ap.add_argument("--only", default="", choices=["", "gemm", "prefill"],
                     help="gemm: time the tensor-core linears and the MoE layer alone (small; also the profiling case); "
                          "prefill: time the prompt path alone (with --small: the profiling case)")
@@ -645,6 +655,17 @@ def main():
     clocks = sampler.stop()
     clocks["window"] = "timed region, then the same decode load until two samples existed" if extended else "timed region"
 
+    if args.profile_step:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        model.step_dev(tok)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled_step": {"ms_per_step_before": ms_dev / args.steps, "launches": launches_per_step,
+                                            "algorithmic_bytes": step_bytes}}))
+        model.close()
+        return
+
     times = torch.tensor([ms_dev, sec_e2e * 1e3], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -678,6 +699,8 @@ def main():
         model = None
         batch64 = batch_decode_bench(cfg, 64, 256, 16, seed=rank)
 
+    default_workload = (B == 1 and args.ctx == 4096 and args.fused == 1 and args.graph == 1 and not args.small)
+    step_traffic = STEP_DRAM_TRAFFIC_BYTES if default_workload else None
     if rank == 0:
         tok_s = B * args.steps * world / (ms_dev * 1e-3)
         e2e_tok_s = B * args.steps * world / (ms_e2e * 1e-3)
@@ -694,7 +717,7 @@ def main():
             # holds a majority of the time: the step itself is the unit whose bytes / time
             # is compared with the copy bandwidth; its two extremes follow as separate keys
             "roofline": {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s",
-                         "frac": step_gbs / peak, "traffic": None, "peak_source": peak_src,
+                         "frac": step_gbs / peak, "traffic": step_traffic, "peak_source": peak_src,
                          "kernel": "decode step (%d launches in one CUDA graph)" % launches_per_step,
                          "ms_per_launch": ms_dev / args.steps, "algorithmic_bytes_per_launch": step_bytes,
                          "fused": args.fused, "graph": args.graph},
