@@ -38,6 +38,13 @@
 namespace b200 {
 
 constexpr int GM_TILE_M = 128, GM_TILE_N = 128, GM_TILE_K = 64;
+// Third epilogue, chosen by the launchers for large store-form problems: the store form on
+// 256-column tiles (one N = 256 MMA per K step over two 128-row boxes of B).  With
+// cta_group::1 both MMA operands come out of shared memory, so a 128 x 128 x 16 MMA moves
+// 8 KB per 32 tensor-core cycles and a 128 x 256 x 16 one 12 KB per 64: the wide tile lifts
+// the operand-bandwidth cap from about half to about two thirds of the tensor peak, and A is
+// re-streamed from L2 half as often.
+constexpr int GEMM_EPI_STORE_WIDE = 2;
 constexpr int GM_THREADS = 192;
 constexpr int GM_STAGE_A = GM_TILE_M * GM_TILE_K * 2;
 // Per epilogue warp: a 32 x 32 fp32 block (rows padded to 33) through which the
@@ -54,6 +61,7 @@ struct alignas(64) GemmArgs {
     const int32_t* group_map;           // device [groups]: which N-row block of B a group uses; null = its own index
     int M, groups, N, K;
     int m_slots, n_tiles;               // tile grid: slots along the rows (an upper bound when grouped) x column tiles
+    int tile_n;                         // output columns per tile: 128, or 256 (wide store form)
     int tile_m;                         // rows of A per slot: 128, or 256 = two accumulator halves sharing one B tile
     float* c;                           // STORE: fp32 [M, ldc]
     __half* c16;                        // SWIGLU: fp16 [M, ldc]  silu(A.B^T) * (A.B2^T)
@@ -69,10 +77,11 @@ struct alignas(64) GemmArgs {
 
 template <int EPI>
 struct GemmShape {
-    static constexpr int UN = EPI == GEMM_EPI_SWIGLU ? 2 * GM_TILE_N : GM_TILE_N;   // MMA N = accumulator columns
+    static constexpr int UN = EPI == GEMM_EPI_STORE ? GM_TILE_N : 2 * GM_TILE_N;   // MMA N = accumulator columns
+    static constexpr int TN = EPI == GEMM_EPI_STORE_WIDE ? 2 * GM_TILE_N : GM_TILE_N;   // output columns of a tile
     static constexpr int STAGE_B = UN * GM_TILE_K * 2;
     static constexpr int STAGE = GM_STAGE_A + STAGE_B;
-    static constexpr int STAGES = EPI == GEMM_EPI_SWIGLU ? 4 : 6;
+    static constexpr int STAGES = EPI == GEMM_EPI_STORE ? 6 : 4;
     static constexpr int SMEM = STAGES * STAGE + GM_EPI_SCRATCH + 1024 /*alignment slack*/ + 256 /*barriers*/ + GM_SLOT_TABLE;
 };
 
@@ -156,7 +165,7 @@ __device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, const int* tab, 
         t /= a.k_splits;
     }
     const int slot = t / a.n_tiles;
-    w.n0 = (t - slot * a.n_tiles) * GM_TILE_N;
+    w.n0 = (t - slot * a.n_tiles) * a.tile_n;
     w.group = 0; w.row0 = 0; w.row_end = a.M;
     bool found;
     if (!a.offsets) {
@@ -192,7 +201,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tacc, 
     const int row_end = w.row_end, n0 = w.n0;
     const uint32_t tbase = tacc + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-    for (int c0 = 0; c0 < GM_TILE_N; c0 += 32) {
+    for (int c0 = 0; c0 < GemmShape<EPI>::TN; c0 += 32) {
         float v[32];
         tmem_ld32(tbase + c0, v);
         if (EPI == GEMM_EPI_SWIGLU) {
@@ -342,6 +351,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) umma_gemm_kernel(const __grid_c
                     if (EPI == GEMM_EPI_SWIGLU)
                         tma_load_2d(st + GM_STAGE_A + GM_TILE_N * GM_TILE_K * 2, &a.map_b2, kb * GM_TILE_K, w.brow0,
                                     &full[s]);
+                    if (EPI == GEMM_EPI_STORE_WIDE)
+                        tma_load_2d(st + GM_STAGE_A + GM_TILE_N * GM_TILE_K * 2, &a.map_b, kb * GM_TILE_K,
+                                    w.brow0 + GM_TILE_N, &full[s]);
                 }
             }
             if (!ok) {
@@ -570,6 +582,9 @@ __global__ void __launch_bounds__(GQ_THREADS, 1) umma_gemm_q_kernel(const __grid
                         tma_load_2d(dst, &a.map_b, (kb >> 2) * (S::SBB / 4), w.brow0, &p_full[p]);
                         if (EPI == GEMM_EPI_SWIGLU)
                             tma_load_2d(dst + GM_TILE_N * S::SBB, &a.map_b2, (kb >> 2) * (S::SBB / 4), w.brow0, &p_full[p]);
+                        if (EPI == GEMM_EPI_STORE_WIDE)
+                            tma_load_2d(dst + GM_TILE_N * S::SBB, &a.map_b, (kb >> 2) * (S::SBB / 4), w.brow0 + GM_TILE_N,
+                                        &p_full[p]);
                         ++sbi;
                     }
                     const int s = it % S::SA;
@@ -802,7 +817,8 @@ static int launch_gemm_q(const GemmArgs& a) {
     GemmArgs b = a;
     b.tile_m = 2 * GM_TILE_M;
     b.m_slots = (a.M + b.tile_m - 1) / b.tile_m + (a.offsets ? a.groups : 0);
-    b.n_tiles = (a.N + GM_TILE_N - 1) / GM_TILE_N;
+    b.tile_n = GemmShape<EPI>::TN;
+    b.n_tiles = (a.N + b.tile_n - 1) / b.tile_n;
     b.k_splits = 1;
     b.kb_split = a.K / GM_TILE_K;
     b.split_stride = 0;
@@ -863,8 +879,17 @@ int umma_gemm_q(int epi, int kind, const __half* A, int64_t a_rows, const void* 
     a.c = c; a.c16 = c16; a.ldc = ldc; a.scale = scale;
     a.status = stream_status_ptr();
     B200_REQUIRE(a.status, "umma_gemm_q: status word allocation failed");
+    // wide store tiles when they still fill the machine (row slots are an upper bound when
+    // grouped) and K is long: this kernel's wide form has a single accumulator set, so its
+    // epilogue is not hidden, which costs more than the wide MMA gains when a tile has only a
+    // few K steps (measured: the K = 512 expert down-projections lose 20 %, K = 1536 gains 16 %)
+    const int slots256 = (M + 2 * GM_TILE_M - 1) / (2 * GM_TILE_M) + (offsets ? groups / 2 : 0);
+    const bool wide = epi == GEMM_EPI_STORE && N >= 2 * GM_TILE_N && K >= 1024 &&
+                      slots256 * ((N + 2 * GM_TILE_N - 1) / (2 * GM_TILE_N)) >= num_sms();
 #define GQ(KIND_)                                                                        \
-    return epi == GEMM_EPI_SWIGLU ? launch_gemm_q<GEMM_EPI_SWIGLU, KIND_>(a) : launch_gemm_q<GEMM_EPI_STORE, KIND_>(a);
+    return epi == GEMM_EPI_SWIGLU ? launch_gemm_q<GEMM_EPI_SWIGLU, KIND_>(a)             \
+           : wide                 ? launch_gemm_q<GEMM_EPI_STORE_WIDE, KIND_>(a)         \
+                                  : launch_gemm_q<GEMM_EPI_STORE, KIND_>(a);
     switch (kind) {
         case 0: GQ(0)
         case 1: GQ(1)
@@ -886,7 +911,8 @@ static int launch_gemm(const GemmArgs& a) {
     GemmArgs b = a;
     b.tile_m = GM_TILE_M;
     b.m_slots = (a.M + b.tile_m - 1) / b.tile_m + (a.offsets ? a.groups : 0);
-    b.n_tiles = (a.N + GM_TILE_N - 1) / GM_TILE_N;
+    b.tile_n = GemmShape<EPI>::TN;
+    b.n_tiles = (a.N + b.tile_n - 1) / b.tile_n;
     b.k_splits = 1;
     b.kb_split = 0;
     b.split_stride = 0;
@@ -922,7 +948,11 @@ int umma_gemm(int epi, const __half* A, int64_t a_rows, const __half* B, const _
     a.c = c; a.c16 = c16; a.ldc = ldc; a.scale = scale;
     a.status = stream_status_ptr();
     B200_REQUIRE(a.status, "umma_gemm: status word allocation failed");
-    return epi == GEMM_EPI_SWIGLU ? launch_gemm<GEMM_EPI_SWIGLU>(a) : launch_gemm<GEMM_EPI_STORE>(a);
+    const int slots128 = (M + GM_TILE_M - 1) / GM_TILE_M + (offsets ? groups / 2 : 0);
+    const bool wide = epi == GEMM_EPI_STORE && N >= 2 * GM_TILE_N && slots128 * ((N + 2 * GM_TILE_N - 1) / (2 * GM_TILE_N)) >= num_sms();
+    return epi == GEMM_EPI_SWIGLU ? launch_gemm<GEMM_EPI_SWIGLU>(a)
+           : wide                 ? launch_gemm<GEMM_EPI_STORE_WIDE>(a)
+                                  : launch_gemm<GEMM_EPI_STORE>(a);
 }
 
 }  // namespace b200

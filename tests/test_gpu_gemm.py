@@ -20,8 +20,9 @@ def _fp16_product(x, w16_bits):
 
 
 @pytest.mark.parametrize("M,K,N", [(128, 64, 128), (32, 64, 8), (128, 128, 128), (129, 192, 132), (300, 1536, 200),
-                                   (64, 1536, 6448), (1000, 3072, 1536)])
+                                   (64, 1536, 6448), (1000, 3072, 1536), (2048, 256, 2500)])
 def test_linear_fp16_many_tokens(oracle, M, K, N):
+    """The last shape has enough tiles for the 256-column store form (ragged last tile)."""
     from gpu_util import ACTIVATION, SUM_ORDER, dev, empty, host, ops
     r = np.random.default_rng(M + K + N)
     x = r.standard_normal((M, K)).astype(np.float32)
@@ -36,11 +37,12 @@ def test_linear_fp16_many_tokens(oracle, M, K, N):
 
 @pytest.mark.parametrize("kind", [0, 1, 2, 3])
 @pytest.mark.parametrize("M,K,N", [(64, 1536, 6448), (257, 512, 1536), (40, 160, 72), (300, 256, 128),
-                                   (48, 3072, 256), (33, 1024, 136)])
+                                   (48, 3072, 256), (33, 1024, 136), (4100, 1024, 2500)])
 def test_linear_packed_many_tokens(oracle, kind, M, K, N):
     """K a multiple of 256: weights dequantised inside the GEMM; otherwise (160 for the
     32-weight kinds) through an fp16 copy.  Few output tiles and K >= 512: K is cut
-    across CTAs (2, 2, 12 and 4 ways in the cases here) and the partials are added."""
+    across CTAs (2, 2, 12 and 4 ways in the cases here) and the partials are added; the
+    last shape has enough tiles for the 256-column store form (ragged rows and columns)."""
     if kind == 3 and K % 256:
         pytest.skip("Q4_K rows are multiples of 256 weights")
     from gpu_util import ACTIVATION, SUM_ORDER, dev, empty, fp16_close, host, ops
