@@ -166,21 +166,41 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_split_kernel(Decod
     }
 }
 
-// grid (H, batch), hd threads: merge the splits.  An empty range gives zeros
-// (the reference's sum > 0 guard).
-__global__ void attn_decode_merge_kernel(const float* __restrict__ part, float* __restrict__ out, int H,
-                                         int hd, int splits) {
+// grid (H, batch), hd * G threads: merge the splits.  Thread (c, g) adds the splits
+// s = g, g + G, ... of output channel c (so up to G * hd loads are in flight instead of
+// one dependent chain over all splits), the G partial sums are then added in g order.
+// An empty range gives zeros (the reference's sum > 0 guard).
+constexpr int MERGE_MAX_THREADS = 1024;
+__global__ void __launch_bounds__(MERGE_MAX_THREADS)
+attn_decode_merge_kernel(const float* __restrict__ part, float* __restrict__ out, int H, int hd, int splits) {
+    __shared__ float s_red[32];
+    __shared__ float s_acc[MERGE_MAX_THREADS];
+    __shared__ float s_l[MERGE_MAX_THREADS];
     const int h = blockIdx.x, b = blockIdx.y;
+    const int G = blockDim.x / hd, c = threadIdx.x % hd, g = threadIdx.x / hd;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const float* p = part + ((int64_t)b * H + h) * splits * (hd + 2);
     float mm = -INFINITY;
-    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, p[(int64_t)s * (hd + 2) + hd]);
-    for (int c = threadIdx.x; c < hd; c += blockDim.x) {
-        float ll = 0.0f, acc = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float* ps = p + (int64_t)s * (hd + 2);
-            const float w = (ps[hd] == -INFINITY) ? 0.0f : expf(ps[hd] - mm);
-            ll += ps[hd + 1] * w;
-            acc += ps[c] * w;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) mm = fmaxf(mm, p[(int64_t)s * (hd + 2) + hd]);
+    mm = warp_max(mm);
+    if (lane == 0) s_red[wid] = mm;
+    __syncthreads();
+    mm = lane < nw ? s_red[lane] : -INFINITY;
+    mm = warp_max(mm);
+    float ll = 0.0f, acc = 0.0f;
+    for (int s = g; s < splits; s += G) {
+        const float* ps = p + (int64_t)s * (hd + 2);
+        const float w = (ps[hd] == -INFINITY) ? 0.0f : expf(ps[hd] - mm);
+        ll += ps[hd + 1] * w;
+        acc += ps[c] * w;
+    }
+    s_acc[threadIdx.x] = acc;
+    s_l[threadIdx.x] = ll;
+    __syncthreads();
+    if (g == 0) {
+        for (int k = 1; k < G; ++k) {
+            acc += s_acc[k * hd + c];
+            ll += s_l[k * hd + c];
         }
         out[((int64_t)b * H + h) * hd + c] = ll > 0.0f ? acc / ll : 0.0f;
     }
@@ -207,7 +227,8 @@ static int launch_decode(DecodeArgs& a, int batch, int max_len, float* out) {
         default: attn_decode_split_kernel<8, HALF, PAGED><<<grid, ATT_WARPS * 32, 0, stream()>>>(a); break;
     }
     B200_LAUNCH_CHECK("attn_decode_split_kernel");
-    attn_decode_merge_kernel<<<dim3(a.H, batch), std::min(a.hd, 256), 0, stream()>>>(a.part, out, a.H, a.hd, a.splits);
+    const int merge_groups = std::max(1, std::min(std::min(MERGE_MAX_THREADS / a.hd, 16), a.splits));
+    attn_decode_merge_kernel<<<dim3(a.H, batch), a.hd * merge_groups, 0, stream()>>>(a.part, out, a.H, a.hd, a.splits);
     B200_LAUNCH_CHECK("attn_decode_merge_kernel");
     return B200_OK;
 }
@@ -485,7 +506,8 @@ extern "C" int b200_attention_decode_ring_fp16_noalloc(const float* q, const uin
         default: attn_decode_split_kernel<8, true, false><<<grid, ATT_WARPS * 32, 0, stream()>>>(a); break;
     }
     B200_LAUNCH_CHECK("attn_decode_split_kernel");
-    attn_decode_merge_kernel<<<dim3(a.H, 1), std::min(a.hd, 256), 0, stream()>>>(a.part, out, a.H, a.hd, a.splits);
+    const int merge_groups = std::max(1, std::min(std::min(MERGE_MAX_THREADS / a.hd, 16), a.splits));
+    attn_decode_merge_kernel<<<dim3(a.H, 1), a.hd * merge_groups, 0, stream()>>>(a.part, out, a.H, a.hd, a.splits);
     B200_LAUNCH_CHECK("attn_decode_merge_kernel");
     return B200_OK;
 }

@@ -338,6 +338,40 @@ __global__ void last_rows_kernel(const float* __restrict__ src, float* __restric
     }
 }
 
+// x = x + s * y, then out = rmsnorm(x) * w: the residual update and the norm that follows it
+// in one pass over the row (the same operations in the same order as residual_kernel and
+// rmsnorm_kernel: double sum of squares, inv rounded to float).  One block per row.
+constexpr int RRN_PER = 16;      // row elements a thread keeps in registers: dim <= 4096
+__global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, float s,
+                                                               const float* __restrict__ w, float* __restrict__ out,
+                                                               int dim, float eps) {
+    __shared__ double red[32];
+    const int64_t r = blockIdx.x;
+    float* xr = x + r * dim;
+    const float* yr = y + r * dim;
+    float v[RRN_PER];
+    double ss = 0.0;
+#pragma unroll
+    for (int j = 0; j < RRN_PER; ++j) {
+        const int i = j * 256 + threadIdx.x;
+        v[j] = 0.0f;
+        if (i < dim) {
+            v[j] = xr[i] + yr[i] * s;
+            xr[i] = v[j];
+            ss += (double)v[j] * (double)v[j];
+        }
+    }
+    ss = block_sum_d(ss, red);
+    const double inv_d = 1.0 / sqrt(ss / (double)dim + (double)eps);
+    const float inv = isfinite(inv_d) ? (float)inv_d : 0.0f;
+    float* o = out + r * dim;
+#pragma unroll
+    for (int j = 0; j < RRN_PER; ++j) {
+        const int i = j * 256 + threadIdx.x;
+        if (i < dim) o[i] = v[j] * inv * w[i];
+    }
+}
+
 static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* next) {
     const int B = dec->batch, d = dec->d;
     const int64_t NT = (int64_t)B * T;
@@ -376,9 +410,20 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
         prefill_pos_kernel<<<(unsigned)ceil_div64(NT, 256), 256, 0, st>>>(pos, B, T);
         B200_LAUNCH_CHECK("prefill_pos_kernel");
     }
+    // x += res_mult * y followed by the next norm; fused when the row fits the registers
+    auto residual_norm = [&](const float* norm_w) -> int {
+        if (norm_w && d <= RRN_PER * 256) {
+            residual_rmsnorm_kernel<<<(unsigned)NT, 256, 0, st>>>(x, y, dec->res_mult, norm_w, xb, d, dec->eps);
+            B200_LAUNCH_CHECK("residual_rmsnorm_kernel");
+            return B200_OK;
+        }
+        residual_kernel<<<res_grid, 256, 0, st>>>(x, y, dec->res_mult, NT * d);
+        B200_LAUNCH_CHECK("residual_kernel");
+        return norm_w ? b200_rmsnorm_forward(x, norm_w, xb, nullptr, NT, d, dec->eps) : B200_OK;
+    };
+    if (dec->n_layers > 0) STEP(b200_rmsnorm_forward(x, dec->L[0].attn_norm, xb, nullptr, NT, d, dec->eps));
     for (int l = 0; l < dec->n_layers; ++l) {
         LayerW& w = dec->L[l];
-        STEP(b200_rmsnorm_forward(x, w.attn_norm, xb, nullptr, NT, d, dec->eps));
         if (dec->types[l] == 0) {
             STEP(mamba2_forward(xb, w.mamba_in, w.conv_w, w.conv_b, w.dt_bias, w.a_log, w.D, w.mamba_norm, w.mamba_out,
                                 w.ssm_state, y, B, T, p, kind, w.conv_state));
@@ -394,16 +439,13 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
             STEP(b200_attention_forward_ex(q, k, v, at, nullptr, B, T, dec->H, dec->KV, dec->hd, dec->attn_scale, 0, nullptr));
             STEP(lin(at, w.wo, y, qd, d));
         }
-        residual_kernel<<<res_grid, 256, 0, st>>>(x, y, dec->res_mult, NT * d);
-        B200_LAUNCH_CHECK("residual_kernel");
-        STEP(b200_rmsnorm_forward(x, w.ffn_norm, xb, nullptr, NT, d, dec->eps));
+        STEP(residual_norm(w.ffn_norm));
         STEP(b200_moe_forward_bias_half(xb, w.router, w.router_bias, static_cast<const uint16_t*>(w.gate),
                                         static_cast<const uint16_t*>(w.up), static_cast<const uint16_t*>(w.down),
                                         static_cast<const uint16_t*>(w.sh_gate), static_cast<const uint16_t*>(w.sh_up),
                                         static_cast<const uint16_t*>(w.sh_down), y, nullptr, nullptr, nullptr, nullptr,
                                         nullptr, nullptr, NT, d, dec->E, dec->ne, dec->K, dec->SH, dec->qkind));
-        residual_kernel<<<res_grid, 256, 0, st>>>(x, y, dec->res_mult, NT * d);
-        B200_LAUNCH_CHECK("residual_kernel");
+        STEP(residual_norm(l + 1 < dec->n_layers ? dec->L[l + 1].attn_norm : nullptr));
     }
     // logits of the last token of every sequence
     last_rows_kernel<<<(unsigned)ceil_div64((int64_t)B * d, 256), 256, 0, st>>>(x, dec->x, B, T, d);
