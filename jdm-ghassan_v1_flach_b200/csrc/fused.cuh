@@ -27,6 +27,14 @@ struct SgArgs {
     float out_scale = 1.0f;         // EPI_STORE: y = acc * out_scale
     float* y = nullptr;             // EPI_STORE output, rows y_stride apart
     int y_stride = 0;
+    // EPI_STORE only: up to two more matrices over the same activations in the same launch
+    // (the q / k / v projections of an attention layer): [N2,K] -> y2, [N3,K] -> y3, same
+    // kind, same y_stride convention (rows y2_stride / y3_stride apart)
+    const uint8_t *w2 = nullptr, *w3 = nullptr;
+    int N2 = 0, N3 = 0;
+    float *y2 = nullptr, *y3 = nullptr;
+    int y2_stride = 0, y3_stride = 0;
+    int t1 = 0, t2 = 0;             // first tile of the second / third matrix (filled by stream_gemv())
     float* resid = nullptr;         // EPI_RESIDUAL: resid += res_mult * acc (rows y_stride apart)
     float res_mult = 1.0f;
     // EPI_INPROJ (Mamba in_proj): gate | conv step | dt

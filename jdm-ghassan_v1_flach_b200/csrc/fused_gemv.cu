@@ -63,11 +63,19 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemv_kernel(SgArgs a) {
             int issued = 0;
             for (int i = 0; i < n_my; ++i) {
                 if (!ring.acquire(i)) break;
-                const int tile = first + i * step;
-                const int rows = min(a.rows_per_tile, a.N - tile * a.rows_per_tile);
+                int tile = first + i * step;
+                const uint8_t* wseg = a.w;
+                int nseg = a.N;
+                if (EPI == EPI_STORE && tile >= a.t1) {       // second / third matrix of the launch
+                    const bool third = tile >= a.t2;
+                    wseg = third ? a.w3 : a.w2;
+                    nseg = third ? a.N3 : a.N2;
+                    tile -= third ? a.t2 : a.t1;
+                }
+                const int rows = min(a.rows_per_tile, nseg - tile * a.rows_per_tile);
                 const uint32_t bytes = (uint32_t)(rows * a.row_bytes);
                 ring.expect(i, bytes);
-                ring.copy(i, 0, a.w + (int64_t)tile * a.rows_per_tile * a.row_bytes, bytes);
+                ring.copy(i, 0, wseg + (int64_t)tile * a.rows_per_tile * a.row_bytes, bytes);
                 issued = i + 1;
             }
             ring.drain(issued);
@@ -98,8 +106,18 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemv_kernel(SgArgs a) {
     }
 
     for (int i = 0; i < n_my; ++i) {
-        const int tile = first + i * step;
-        const int rows = min(a.rows_per_tile, a.N - tile * a.rows_per_tile);
+        int tile = first + i * step;
+        int nseg = a.N;
+        float* yseg = a.y;
+        int ystride = a.y_stride;
+        if (EPI == EPI_STORE && tile >= a.t1) {
+            const bool third = tile >= a.t2;
+            nseg = third ? a.N3 : a.N2;
+            yseg = third ? a.y3 : a.y2;
+            ystride = third ? a.y3_stride : a.y2_stride;
+            tile -= third ? a.t2 : a.t1;
+        }
+        const int rows = min(a.rows_per_tile, nseg - tile * a.rows_per_tile);
         const int n = tile * a.rows_per_tile + e_row;
         const bool owner = e_row < rows && e_m < a.M;
         // epilogue operands are fetched before the dot products so their latency hides
@@ -132,7 +150,7 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemv_kernel(SgArgs a) {
             float v = red_value<KIND>(red_pass, e_row, e_m) * in_scale;
             const int m = e_m;
             if (EPI == EPI_STORE) {
-                a.y[(int64_t)m * a.y_stride + n] = v * a.out_scale;
+                yseg[(int64_t)m * ystride + n] = v * a.out_scale;
             } else if (EPI == EPI_RESIDUAL) {
                 *dst = pre + v * a.res_mult;
             } else {
@@ -296,6 +314,17 @@ int stream_gemv(SgArgs a, int kind, int pro, int epi) {
         return fail(B200_EUNSUPPORTED, "stream_gemv: %d rows of %lld bytes cannot be tiled to 16 bytes", a.N, (long long)a.row_bytes);
     a.rows_per_tile = R;
     a.num_tiles = ceil_div(a.N, R);
+    a.t1 = a.t2 = a.num_tiles;
+    if (a.N2 > 0 || a.N3 > 0) {
+        B200_REQUIRE(epi == EPI_STORE && a.N2 > 0 && a.w2 && a.y2 && (a.N3 == 0 || (a.w3 && a.y3)),
+                     "stream_gemv: extra matrices need the store epilogue and their pointers");
+        B200_REQUIRE(((reinterpret_cast<uintptr_t>(a.w2) | reinterpret_cast<uintptr_t>(a.w3)) & 15) == 0,
+                     "stream_gemv: weights must be 16-byte aligned");
+        if (!tail_tile_ok(a.N2, R, a.row_bytes) || (a.N3 > 0 && !tail_tile_ok(a.N3, R, a.row_bytes)))
+            return fail(B200_EUNSUPPORTED, "stream_gemv: rows of %lld bytes cannot be tiled to 16 bytes", (long long)a.row_bytes);
+        a.t2 = a.t1 + ceil_div(a.N2, R);
+        a.num_tiles = a.t2 + ceil_div(a.N3, R);
+    }
     a.stage_bytes = (int)((R * a.row_bytes + 127) / 128 * 128);
     a.status = stream_status_ptr();
     B200_REQUIRE(a.status, "stream_gemv: status word allocation failed");

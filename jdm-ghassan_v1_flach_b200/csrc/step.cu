@@ -256,15 +256,12 @@ static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t*
             STEP(stream_gemv(c, kind, PRO_NONE, EPI_RESIDUAL));
         } else {
             const int qd = dec->H * dec->hd, kvd = dec->KV * dec->hd;
+            // q, k and v in one launch: one norm, one staging of the activations
             SgArgs aq = base(w.wq, qd, d, dec->x, d);
             aq.norm_w = w.attn_norm; aq.y = dec->q; aq.y_stride = qd;
+            aq.w2 = static_cast<const uint8_t*>(w.wk); aq.N2 = kvd; aq.y2 = dec->k; aq.y2_stride = kvd;
+            aq.w3 = static_cast<const uint8_t*>(w.wv); aq.N3 = kvd; aq.y3 = dec->v; aq.y3_stride = kvd;
             STEP(stream_gemv(aq, kind, PRO_RMS, EPI_STORE));
-            SgArgs ak = base(w.wk, kvd, d, dec->x, d);
-            ak.norm_w = w.attn_norm; ak.y = dec->k; ak.y_stride = kvd;
-            STEP(stream_gemv(ak, kind, PRO_RMS, EPI_STORE));
-            SgArgs av = base(w.wv, kvd, d, dec->x, d);
-            av.norm_w = w.attn_norm; av.y = dec->v; av.y_stride = kvd;
-            STEP(stream_gemv(av, kind, PRO_RMS, EPI_STORE));
             if (!dry) {
                 if (dec->rope_type >= 0)
                     STEP(b200_rope_forward_cached(dec->q, dec->k, dec->pos, dec->inv_freq, B, dec->H, dec->KV, dec->hd,
