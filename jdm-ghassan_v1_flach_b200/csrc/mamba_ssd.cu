@@ -389,6 +389,276 @@ ssd_chunk_out_kernel(const float* __restrict__ bc, const float* __restrict__ G, 
         }
 }
 
+// ===========================================================================
+// fp16 forms of the two chunk kernels (fp16 / packed weights only)
+// ===========================================================================
+// Same algebra with the operands staged as fp16 (11 significant bits like TF32; values
+// clamped to the fp16 range, as the activations of the projections around the scan are)
+// and read with ldmatrix into mma.sync.m16n8k16 fragments: half the shared memory of the
+// TF32 forms (four CTAs per SM instead of two - the kernels are latency-bound, so resident
+// warps are what they need) and an eighth of the fragment-load instructions.  Rows are
+// padded by 16 bytes so that the eight row addresses of an 8 x 8 ldmatrix tile fall into
+// eight different 16-byte bank groups.
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const __half* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const __half* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// four floats -> four clamped halfs, one 8-byte store
+__device__ __forceinline__ void store_half4(__half* dst, float4 v) {
+    auto cl = [](float x) { return fminf(fmaxf(x, -65504.0f), 65504.0f); };
+    const __half2 a = __floats2half2_rn(cl(v.x), cl(v.y)), b = __floats2half2_rn(cl(v.z), cl(v.w));
+    *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
+constexpr int SSD_LDX16 = SSD_P + 8;       // x tile [Q][P + 8] halfs
+constexpr int SSD_LDM16 = SSD_Q + 8;       // M tile [Q][Q + 8] halfs
+
+// As ssd_chunk_state_kernel; d_state a multiple of 32.  S[p][n] = sum_s Xw[s][p] B[s][n]:
+// both operands are stored step-major, so both fragments come from transposing loads.
+__global__ void __launch_bounds__(SSD_THREADS, 4)
+ssd_chunk_state16_kernel(const float* __restrict__ proj, const float* __restrict__ bc, const float* __restrict__ dt_bias,
+                         const float* __restrict__ a_log, float* __restrict__ dtcum, float* __restrict__ chunk_state,
+                         float* __restrict__ decay, int T, int NC, MambaDims p) {
+    extern __shared__ __align__(16) uint8_t sm16[];
+    constexpr int P = SSD_P;
+    const int N = p.d_state, ldb = N + 8;
+    __half* sB = reinterpret_cast<__half*>(sm16);      // [Q][N + 8]
+    __half* sX = sB + SSD_Q * ldb;                      // [Q][P + 8]   (already multiplied by w_s)
+    float* sDt = reinterpret_cast<float*>(sX + SSD_Q * SSD_LDX16);   // [Q]
+    float* sCum = sDt + SSD_Q;                          // [Q]
+    const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int t0 = c * SSD_Q, nt = min(SSD_Q, T - t0);
+    const float A = -expf(a_log[h]);
+    if (threadIdx.x < SSD_Q) {
+        float dt = 0.0f;
+        if (threadIdx.x < nt) {
+            const float u = proj[((int64_t)b * T + t0 + threadIdx.x) * p.proj + p.proj - p.n_heads + h] + dt_bias[h];
+            dt = softplus_dt(u);
+        }
+        sDt[threadIdx.x] = dt;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {                 // running sum of A dt over the chunk: 4 steps per lane
+        const int l = threadIdx.x;
+        float v[4], run = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            run += __fmul_rn(A, sDt[l * 4 + i]);
+            v[i] = run;
+        }
+        float incl = run;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (l >= o) incl += up;
+        }
+        const float before = incl - run;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sCum[l * 4 + i] = before + v[i];
+    }
+    __syncthreads();
+    const float cum_last = sCum[SSD_Q - 1];
+    if (threadIdx.x < nt) {
+        float* o = dtcum + (((int64_t)b * p.n_heads + h) * T + t0 + threadIdx.x) * 2;
+        o[0] = sDt[threadIdx.x];
+        o[1] = sCum[threadIdx.x];
+    }
+    if (threadIdx.x == 0) decay[((int64_t)b * NC + c) * p.n_heads + h] = expf(cum_last);
+    const int n4 = N >> 2;
+    for (int e = threadIdx.x; e < SSD_Q * n4; e += SSD_THREADS) {
+        const int t = e / n4, n = (e - t * n4) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < nt) v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + p.d_inner + n);
+        store_half4(sB + t * ldb + n, v);
+    }
+    for (int e = threadIdx.x; e < SSD_Q * (P / 4); e += SSD_THREADS) {
+        const int t = e / (P / 4), i = (e - t * (P / 4)) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < nt) {
+            const float w = expf(cum_last - sCum[t]) * sDt[t];
+            v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + h * P + i);
+            v = make_float4(w * v.x, w * v.y, w * v.z, w * v.w);
+        }
+        store_half4(sX + t * SSD_LDX16 + i, v);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int mt = warp & 3, nh = warp >> 2;
+    const int lj = lane >> 3, lr = lane & 7;            // ldmatrix: which 8 x 8 tile, which of its rows
+    const int npairs = N >> 5;                          // pairs of 8-column tiles per half, <= 4
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+    const int ksteps = (nt + 15) >> 4;
+    for (int ks = 0; ks < ksteps; ++ks) {
+        const int s0 = ks * 16;
+        uint32_t a[4];
+        ldsm_x4_t(a, sX + (s0 + (lj >> 1) * 8 + lr) * SSD_LDX16 + mt * 16 + (lj & 1) * 8);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+            if (jj < npairs) {
+                uint32_t bb[4];
+                ldsm_x4_t(bb, sB + (s0 + (lj & 1) * 8 + lr) * ldb + (nh * npairs + jj) * 16 + (lj >> 1) * 8);
+                mma_f16(acc[2 * jj], a, bb[0], bb[1]);
+                mma_f16(acc[2 * jj + 1], a, bb[2], bb[3]);
+            }
+    }
+    float* out = chunk_state + (((int64_t)b * NC + c) * p.n_heads + h) * P * N;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if (j < 2 * npairs) {
+            const int n = (nh * 2 * npairs + j) * 8 + 2 * t4;
+            *reinterpret_cast<float2*>(out + (mt * 16 + g) * N + n) = make_float2(acc[j][0], acc[j][1]);
+            *reinterpret_cast<float2*>(out + (mt * 16 + g + 8) * N + n) = make_float2(acc[j][2], acc[j][3]);
+        }
+}
+
+// As ssd_chunk_out_kernel; d_state a multiple of 16.
+__global__ void __launch_bounds__(SSD_THREADS, 4)
+ssd_chunk_out16_kernel(const float* __restrict__ bc, const float* __restrict__ G, const float* __restrict__ dtcum,
+                       const float* __restrict__ chunk_state, const float* __restrict__ Dv, float* __restrict__ y, int T,
+                       int NC, MambaDims p) {
+    extern __shared__ __align__(16) uint8_t sm16[];
+    constexpr int P = SSD_P;
+    const int N = p.d_state, ldc = N + 8;
+    const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int t0 = c * SSD_Q, nt = min(SSD_Q, T - t0);
+    float* sDt = reinterpret_cast<float*>(sm16);        // [Q]
+    float* sCum = sDt + SSD_Q;                          // [Q]
+    __half* buf = reinterpret_cast<__half*>(sCum + SSD_Q);
+    if (threadIdx.x < SSD_Q) {
+        float dt = 0.0f, cum = 0.0f;
+        if (threadIdx.x < nt) {
+            const float2 o = *reinterpret_cast<const float2*>(dtcum + (((int64_t)b * p.n_heads + h) * T + t0 + threadIdx.x) * 2);
+            dt = o.x;
+            cum = o.y;
+        }
+        sDt[threadIdx.x] = dt;
+        sCum[threadIdx.x] = cum;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int lj = lane >> 3, lr = lane & 7;
+    const int ph = warp >> 2;
+    const int mts[2] = {warp & 3, 7 - (warp & 3)};
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.0f;
+    // phase 1: inter-chunk term, A = e^{cum_t} C [t][n] (row-major), B = S_prev [p][n] (row-major)
+    {
+        __half* sC = buf;                   // [Q][N + 8]
+        __half* sS = buf + SSD_Q * ldc;     // [P][N + 8]
+        const int n4 = N >> 2;
+        for (int e = threadIdx.x; e < SSD_Q * n4; e += SSD_THREADS) {
+            const int t = e / n4, n = (e - t * n4) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < nt) {
+                const float w = expf(sCum[t]);
+                v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + p.d_inner + N + n);
+                v = make_float4(w * v.x, w * v.y, w * v.z, w * v.w);
+            }
+            store_half4(sC + t * ldc + n, v);
+        }
+        const float* sp = chunk_state + (((int64_t)b * NC + c) * p.n_heads + h) * P * N;
+        for (int e = threadIdx.x; e < P * n4; e += SSD_THREADS) {
+            const int i = e / n4, n = (e - i * n4) * 4;
+            store_half4(sS + i * ldc + n, __ldcs(reinterpret_cast<const float4*>(sp + i * N + n)));
+        }
+        __syncthreads();
+        for (int ks = 0; ks < (N >> 4); ++ks) {
+            const int k0 = ks * 16;
+            uint32_t a[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) ldsm_x4(a[i], sC + (mts[i] * 16 + (lj & 1) * 8 + lr) * ldc + k0 + (lj >> 1) * 8);
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+                uint32_t bb[4];
+                ldsm_x4(bb, sS + (ph * 32 + jj * 16 + (lj >> 1) * 8 + lr) * ldc + k0 + (lj & 1) * 8);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mma_f16(acc[i][2 * jj], a[i], bb[0], bb[1]);
+                    mma_f16(acc[i][2 * jj + 1], a[i], bb[2], bb[3]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // phase 2: intra-chunk term, A = M [t][s] (row-major), B = x [s][p] (step-major: transposing loads)
+    {
+        __half* sM = buf;                   // [Q][Q + 8]
+        __half* sX = buf + SSD_Q * SSD_LDM16;   // [Q][P + 8]
+        const float* gm = G + ((int64_t)b * NC + c) * SSD_Q * SSD_Q;
+        for (int e = threadIdx.x; e < SSD_Q * (SSD_Q / 4); e += SSD_THREADS) {
+            const int t = e / (SSD_Q / 4), s = (e - t * (SSD_Q / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s <= t && t < nt) {
+                const float4 gv = *reinterpret_cast<const float4*>(gm + t * SSD_Q + s);
+                const float ct = sCum[t];
+                v.x = gv.x * expf(ct - sCum[s]) * sDt[s];
+                if (s + 1 <= t) v.y = gv.y * expf(ct - sCum[s + 1]) * sDt[s + 1];
+                if (s + 2 <= t) v.z = gv.z * expf(ct - sCum[s + 2]) * sDt[s + 2];
+                if (s + 3 <= t) v.w = gv.w * expf(ct - sCum[s + 3]) * sDt[s + 3];
+            }
+            store_half4(sM + t * SSD_LDM16 + s, v);
+        }
+        for (int e = threadIdx.x; e < SSD_Q * (P / 4); e += SSD_THREADS) {
+            const int t = e / (P / 4), i = (e - t * (P / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < nt) v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + h * P + i);
+            store_half4(sX + t * SSD_LDX16 + i, v);
+        }
+        __syncthreads();
+        const int kmax = (nt + 15) >> 4;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int kend = min(mts[i] + 1, kmax);
+            for (int ks = 0; ks < kend; ++ks) {
+                const int s0 = ks * 16;
+                uint32_t a[4];
+                ldsm_x4(a, sM + (mts[i] * 16 + (lj & 1) * 8 + lr) * SSD_LDM16 + s0 + (lj >> 1) * 8);
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj) {
+                    uint32_t bb[4];
+                    ldsm_x4_t(bb, sX + (s0 + (lj & 1) * 8 + lr) * SSD_LDX16 + ph * 32 + jj * 16 + (lj >> 1) * 8);
+                    mma_f16(acc[i][2 * jj], a, bb[0], bb[1]);
+                    mma_f16(acc[i][2 * jj + 1], a, bb[2], bb[3]);
+                }
+            }
+        }
+    }
+    const float dskip = Dv[h];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int t = mts[i] * 16 + g + 8 * r;
+            if (t < nt) {
+                const float* xr = bc + ((int64_t)b * T + t0 + t) * p.conv_dim + h * P + ph * 32 + 2 * t4;
+                float* o = y + ((int64_t)b * T + t0 + t) * p.d_inner + h * P + ph * 32 + 2 * t4;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 xv = *reinterpret_cast<const float2*>(xr + j * 8);
+                    *reinterpret_cast<float2*>(o + j * 8) =
+                        make_float2(acc[i][j][2 * r] + dskip * xv.x, acc[i][j][2 * r + 1] + dskip * xv.y);
+                }
+            }
+        }
+}
+
 // The chunked scan over proj / bc (as produced by the projection and the convolution):
 // y [B*T, d_inner], state [B, H, P, N] updated in place.  Returns B200_EUNSUPPORTED for
 // shapes outside its tiling (the caller then runs the sequential scan).
@@ -419,6 +689,8 @@ int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, con
         B200_CUDA(cudaFuncSetAttribute(ssd_chunk_state_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         B200_CUDA(cudaFuncSetAttribute(ssd_chunk_out_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         B200_CUDA(cudaFuncSetAttribute(ssd_chunk_out_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(ssd_chunk_state16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(ssd_chunk_out16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
         configured = true;
     }
     B200_REQUIRE(smem_cb <= 160 * 1024 && smem_st <= 160 * 1024 && smem_out <= 160 * 1024, "mamba_ssd_scan: shared memory");
@@ -427,7 +699,12 @@ int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, con
     ssd_cb_kernel<<<dim3(3 * NC, B), SSD_THREADS, smem_cb, stream()>>>(bc, G, T, p);
     B200_LAUNCH_CHECK("ssd_cb_kernel");
     const dim3 grid(NC, p.n_heads, B);
-    if (precise)
+    const bool half_tiles = !precise && N % 32 == 0;
+    const size_t smem_st16 = (size_t)(SSD_Q * (N + 8) + SSD_Q * SSD_LDX16) * 2 + 2 * SSD_Q * 4;
+    const size_t smem_out16 = (size_t)std::max(SSD_Q * (N + 8) + P * (N + 8), SSD_Q * SSD_LDM16 + SSD_Q * SSD_LDX16) * 2 + 2 * SSD_Q * 4;
+    if (half_tiles)
+        ssd_chunk_state16_kernel<<<grid, SSD_THREADS, smem_st16, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate, decay, T, NC, p);
+    else if (precise)
         ssd_chunk_state_kernel<true><<<grid, SSD_THREADS, smem_st, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate, decay, T, NC, p);
     else
         ssd_chunk_state_kernel<false><<<grid, SSD_THREADS, smem_st, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate, decay, T, NC, p);
@@ -436,7 +713,9 @@ int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, con
     ssd_carry_kernel<<<(unsigned)std::min<int64_t>(ceil_div64(elems, 256), (int64_t)num_sms() * 16), 256, 0, stream()>>>(
         cstate, decay, state, B, NC, p);
     B200_LAUNCH_CHECK("ssd_carry_kernel");
-    if (precise)
+    if (half_tiles)
+        ssd_chunk_out16_kernel<<<grid, SSD_THREADS, smem_out16, stream()>>>(bc, G, dtcum, cstate, D, y, T, NC, p);
+    else if (precise)
         ssd_chunk_out_kernel<true><<<grid, SSD_THREADS, smem_out, stream()>>>(bc, G, dtcum, cstate, D, y, T, NC, p);
     else
         ssd_chunk_out_kernel<false><<<grid, SSD_THREADS, smem_out, stream()>>>(bc, G, dtcum, cstate, D, y, T, NC, p);
