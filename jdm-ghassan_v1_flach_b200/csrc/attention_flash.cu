@@ -7,10 +7,12 @@
 // its batched cuBLAS GEMMs fp16 copies as well (cuda/attention.cu:432-499).
 //
 // One CTA = 64 queries of one (sequence, head); each of its 4 warps owns 16 query rows.
-// Keys and values arrive 64 at a time through shared memory (K row-major, V transposed,
-// both fp16, padded so that fragment loads are conflict-free); scores and outputs live
-// in mma.sync.m16n8k16 accumulator fragments, and the score fragment of a 16-key slice
-// is reused directly as the A operand of the probability-times-value product.
+// Keys and values arrive 64 at a time through shared memory (both row-major fp16, rows
+// padded by 16 bytes so that the eight row addresses of an ldmatrix tile fall into
+// different bank groups); K fragments come from plain ldmatrix loads, V fragments from
+// transposing ones.  Scores and outputs live in mma.sync.m16n8k16 accumulator fragments,
+// and the score fragment of a 16-key slice is reused directly as the A operand of the
+// probability-times-value product.
 #include <cuda_fp16.h>
 
 #include "mma_tile.cuh"
@@ -18,6 +20,17 @@
 namespace b200 {
 
 constexpr int FA_BM = 64, FA_BN = 64, FA_THREADS = 128;
+
+__device__ __forceinline__ void fa_ldsm_x4(uint32_t (&r)[4], const __half* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void fa_ldsm_x4_t(uint32_t (&r)[4], const __half* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
@@ -29,11 +42,12 @@ __global__ void __launch_bounds__(FA_THREADS)
 attn_flash_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   float* __restrict__ out, int T, int H, int KV, float scale, int window,
                   const int32_t* __restrict__ seg) {
-    constexpr int LDK = HD + 8, LDV = FA_BN + 8;
+    constexpr int LDK = HD + 8;
     __shared__ __align__(16) __half Ks[FA_BN * LDK];
-    __shared__ __align__(16) __half Vt[HD * LDV];
+    __shared__ __align__(16) __half Vs[FA_BN * LDK];
     __shared__ int32_t s_seg[FA_BN];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int lj = lane >> 3, lr = lane & 7;                // ldmatrix: which 8 x 8 tile, which of its rows
     const int q0 = blockIdx.x * FA_BM, h = blockIdx.y, b = blockIdx.z;
     const int kvh = h / (H / KV);
     const int64_t qs = (int64_t)T * H * HD, kvs = (int64_t)T * KV * HD;
@@ -83,10 +97,7 @@ attn_flash_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                 vv = *reinterpret_cast<const float4*>(vb + (int64_t)(kv0 + key) * KV * HD + c);
             }
             *reinterpret_cast<uint2*>(&Ks[key * LDK + c]) = make_uint2(pack_half2(kk.x, kk.y), pack_half2(kk.z, kk.w));
-            Vt[(c + 0) * LDV + key] = __float2half_rn(vv.x);
-            Vt[(c + 1) * LDV + key] = __float2half_rn(vv.y);
-            Vt[(c + 2) * LDV + key] = __float2half_rn(vv.z);
-            Vt[(c + 3) * LDV + key] = __float2half_rn(vv.w);
+            *reinterpret_cast<uint2*>(&Vs[key * LDK + c]) = make_uint2(pack_half2(vv.x, vv.y), pack_half2(vv.z, vv.w));
         }
         if (threadIdx.x < FA_BN) s_seg[threadIdx.x] = (seg && kv0 + threadIdx.x < T) ? seg[(int64_t)b * T + kv0 + threadIdx.x] : 0;
         __syncthreads();
@@ -94,14 +105,17 @@ attn_flash_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         // scores of this warp's 16 rows against the 64 keys
         float s[FA_BN / 8][4];
 #pragma unroll
-        for (int nt = 0; nt < FA_BN / 8; ++nt) {
-            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
-            const __half* krow = &Ks[(nt * 8 + g) * LDK + 2 * t4];
+        for (int np = 0; np < FA_BN / 16; ++np) {           // two 8-key tiles per ldmatrix
+            s[2 * np][0] = s[2 * np][1] = s[2 * np][2] = s[2 * np][3] = 0.0f;
+            s[2 * np + 1][0] = s[2 * np + 1][1] = s[2 * np + 1][2] = s[2 * np + 1][3] = 0.0f;
+            // tiles: (keys +0..7, k 0..7) (keys +0..7, k 8..15) (keys +8..15, k 0..7) (keys +8..15, k 8..15)
+            const __half* kp = &Ks[(np * 16 + (lj >> 1) * 8 + lr) * LDK + (lj & 1) * 8];
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
-                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
-                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
-                mma_16816(s[nt], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+                uint32_t kb[4];
+                fa_ldsm_x4(kb, kp + ks * 16);
+                mma_16816(s[2 * np], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[0], kb[1]);
+                mma_16816(s[2 * np + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[2], kb[3]);
             }
         }
         // mask, running maximum
@@ -151,12 +165,14 @@ attn_flash_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
             }
             const uint32_t a0 = pack_half2(p[0][0], p[0][1]), a1 = pack_half2(p[0][2], p[0][3]);
             const uint32_t a2 = pack_half2(p[1][0], p[1][1]), a3 = pack_half2(p[1][2], p[1][3]);
+            // V tiles of this 16-key slice: (keys 0..7, d +0..7) (keys 8..15, d +0..7) (keys 0..7, d +8..15) ...
+            const __half* vp = &Vs[(kk * 16 + (lj & 1) * 8 + lr) * LDK + (lj >> 1) * 8];
 #pragma unroll
-            for (int d = 0; d < HD / 8; ++d) {
-                const __half* vrow = &Vt[(d * 8 + g) * LDV + kk * 16 + 2 * t4];
-                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(vrow);
-                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(vrow + 8);
-                mma_16816(o[d], a0, a1, a2, a3, b0, b1);
+            for (int dp = 0; dp < HD / 16; ++dp) {
+                uint32_t vb[4];
+                fa_ldsm_x4_t(vb, vp + dp * 16);
+                mma_16816(o[2 * dp], a0, a1, a2, a3, vb[0], vb[1]);
+                mma_16816(o[2 * dp + 1], a0, a1, a2, a3, vb[2], vb[3]);
             }
         }
     }

@@ -159,6 +159,24 @@ mamba_gated_norm_kernel(const float* y, const float* __restrict__ gate, int64_t 
     const float* gr = gate + r * gate_stride;
     float* o = out + r * d_inner;
     double var = 0.0;
+    constexpr int PER = 16;                  // values a thread keeps in registers: d_inner <= 4096
+    if (d_inner <= PER * 256 && blockDim.x == 256) {
+        float v[PER];
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int c = j * 256 + threadIdx.x;
+            v[j] = c < d_inner ? yr[c] * silu_acc(gr[c]) : 0.0f;
+            var += (double)v[j] * v[j];
+        }
+        var = block_sum_d(var, red) / (double)d_inner;
+        const float inv = 1.0f / sqrtf((float)var + eps);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int c = j * 256 + threadIdx.x;
+            if (c < d_inner) o[c] = v[j] * inv * norm_w[c];
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < d_inner; c += blockDim.x) {
         const float v = yr[c] * silu_acc(gr[c]);
         o[c] = v;
