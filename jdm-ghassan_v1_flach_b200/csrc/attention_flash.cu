@@ -6,7 +6,9 @@
 // (accumulation and the softmax statistics are fp32) - the reference's CUDA path feeds
 // its batched cuBLAS GEMMs fp16 copies as well (cuda/attention.cu:432-499).
 //
-// One CTA = 64 queries of one (sequence, head); each of its 4 warps owns 16 query rows.
+// One CTA = 128 queries of one (sequence, head); each of its 8 warps owns 16 query rows
+// (a key / value tile staged once serves 128 queries; a warp skips the tiles that lie
+// entirely above its rows' diagonal).
 // Keys and values arrive 64 at a time through shared memory (both row-major fp16, rows
 // padded by 16 bytes so that the eight row addresses of an ldmatrix tile fall into
 // different bank groups); K fragments come from plain ldmatrix loads, V fragments from
@@ -19,7 +21,7 @@
 
 namespace b200 {
 
-constexpr int FA_BM = 64, FA_BN = 64, FA_THREADS = 128;
+constexpr int FA_BM = 128, FA_BN = 64, FA_THREADS = 256;
 
 __device__ __forceinline__ void fa_ldsm_x4(uint32_t (&r)[4], const __half* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -102,6 +104,9 @@ attn_flash_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         if (threadIdx.x < FA_BN) s_seg[threadIdx.x] = (seg && kv0 + threadIdx.x < T) ? seg[(int64_t)b * T + kv0 + threadIdx.x] : 0;
         __syncthreads();
 
+        // tiles entirely in this warp's future (or before its window) contribute nothing
+        const int w_first = q0 + warp * 16, w_last = w_first + 15;
+        if (kv0 > w_last || (window > 0 && kv0 + FA_BN - 1 < w_first - window + 1)) continue;
         // scores of this warp's 16 rows against the 64 keys
         float s[FA_BN / 8][4];
 #pragma unroll
