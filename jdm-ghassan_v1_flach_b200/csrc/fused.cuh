@@ -52,10 +52,12 @@ int stream_gemv(SgArgs a, int kind, int pro, int epi);
 
 // Whole-sequence Mamba-2 layer (mamba.cu).  kind: template tag of the projections'
 // storage.  conv_state_out (optional) [B, conv_dim, k-1] receives the convolution
-// window a following decode step continues from.
+// window a following decode step continues from.  x16 (optional): the same activations
+// already rounded to fp16 rows [B*T, d] by their producer, used instead of converting x
+// when the projection runs as a tensor-core GEMM.
 int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const float* conv_b, const float* dt_bias,
                    const float* a_log, const float* D, const float* norm_w, const void* w_out, float* state, float* out,
-                   int B, int T, MambaDims p, int kind, float* conv_state_out = nullptr);
+                   int B, int T, MambaDims p, int kind, float* conv_state_out = nullptr, const void* x16 = nullptr);
 
 // Decode state update; partials: [batch, mamba_scan_norm_blocks()] doubles.
 int mamba_scan_norm(const float* bc, const float* dt_raw, const float* gate, const float* dt_bias,

@@ -103,6 +103,21 @@ static int launch_gemv_kind(const GemvArgs& a) {
 }
 
 // kind: KIND_F32 / KIND_F16 / 0..3.  Any M; tokens are processed 8 at a time.
+bool linear_uses_gemm(const void* w, int kind, const float* y, int M, int K, int N) {
+    const bool known = (kind >= 0 && kind <= 3) || kind == KIND_F16;
+    return known && M >= GEMM_MIN_ROWS && K > 0 && K % 32 == 0 && (kind == KIND_F16 || K % 256 == 0) &&
+           (reinterpret_cast<uintptr_t>(w) & 15) == 0 && N % 4 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
+}
+
+int linear_a16(const void* a16, const void* w, int kind, float* y, int M, int K, int N) {
+    B200_REQUIRE(a16 && w && y && linear_uses_gemm(w, kind, y, M, K, N) && (reinterpret_cast<uintptr_t>(a16) & 15) == 0,
+                 "linear_a16: shape outside the tensor-core path");
+    const __half* a = static_cast<const __half*>(a16);
+    if (kind == KIND_F16)
+        return umma_gemm(GEMM_EPI_STORE, a, M, static_cast<const __half*>(w), nullptr, N, nullptr, 1, M, N, K, y, nullptr, N, 1.0f);
+    return umma_gemm_q(GEMM_EPI_STORE, kind, a, M, w, nullptr, N, nullptr, 1, M, N, K, y, nullptr, N, 1.0f);
+}
+
 int linear(const float* x, const void* w, int kind, float* y, int M, int K, int N) {
     if (M <= 0 || N <= 0) return B200_OK;   // the reference returns silently too
     B200_REQUIRE(x && w && y, "linear: null pointer");

@@ -33,6 +33,10 @@ struct GemvArgs {
 };
 
 int linear(const float* x, const void* w, int kind, float* y, int M, int K, int N);
+// True when linear() would take the tensor-core GEMM for this call; linear_a16() then runs that
+// GEMM straight from fp16 rows a16 [M, K] (the producer rounded them, as pack_rows_f16 would).
+bool linear_uses_gemm(const void* w, int kind, const float* y, int M, int K, int N);
+int linear_a16(const void* a16, const void* w, int kind, float* y, int M, int K, int N);
 int dequantize(const uint8_t* src, uint16_t* dst, int64_t n, int kind);
 
 #ifdef __CUDACC__

@@ -150,9 +150,12 @@ mamba_conv_step_kernel(const float* __restrict__ proj, const float* __restrict__
 // eps is added (core/mamba_cpu.cpp:176-193).  gate rows are gate_stride apart.
 // y may alias out.
 // ---------------------------------------------------------------------------
+// out16 (optional, with d_inner <= 4096): the result as fp16 rows instead of fp32 (values
+// clamped to the fp16 range, as pack_rows_f16 does), for a tensor-core GEMM that follows.
 __global__ void __launch_bounds__(256)
 mamba_gated_norm_kernel(const float* y, const float* __restrict__ gate, int64_t gate_stride,
-                        const float* __restrict__ norm_w, float* out, int d_inner, float eps) {
+                        const float* __restrict__ norm_w, float* out, int d_inner, float eps,
+                        __half* __restrict__ out16 = nullptr) {
     __shared__ double red[32];
     const int64_t r = blockIdx.x;
     const float* yr = y + r * d_inner;
@@ -173,7 +176,11 @@ mamba_gated_norm_kernel(const float* y, const float* __restrict__ gate, int64_t 
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
             const int c = j * 256 + threadIdx.x;
-            if (c < d_inner) o[c] = v[j] * inv * norm_w[c];
+            if (c < d_inner) {
+                const float r = v[j] * inv * norm_w[c];
+                if (out16) out16[(int64_t)blockIdx.x * d_inner + c] = __float2half_rn(fminf(fmaxf(r, -65504.0f), 65504.0f));
+                else o[c] = r;
+            }
         }
         return;
     }
@@ -482,7 +489,7 @@ __global__ void mamba_conv_window_kernel(const float* __restrict__ proj, float* 
 int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const float* conv_b,
                    const float* dt_bias, const float* a_log, const float* D, const float* norm_w,
                    const void* w_out, float* state, float* out, int B, int T, MambaDims p, int kind,
-                   float* conv_state_out) {
+                   float* conv_state_out, const void* x16) {
     if (B <= 0 || T <= 0) return B200_OK;
     int rc = check_dims("mamba2_forward", p);
     if (rc) return rc;
@@ -493,12 +500,19 @@ int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const 
     B200_REQUIRE(NT <= 0x7fffffff, "mamba2_forward: B*T too large");
     const size_t proj_f = (size_t)NT * p.proj, bc_f = (size_t)NT * p.conv_dim, y_f = (size_t)NT * p.d_inner;
     void* wsp;
-    rc = workspace(WS_MAMBA).ensure((proj_f + bc_f + y_f) * sizeof(float) + 1024, &wsp);
+    // when the out-projection runs as a GEMM the gated norm hands it fp16 rows directly
+    const bool out_gemm = p.d_inner <= 4096 && linear_uses_gemm(w_out, kind, out, (int)NT, p.d_inner, p.d);
+    const size_t y16_f = out_gemm ? (y_f + 1) / 2 : 0;                      // fp16 rows, counted in floats
+    rc = workspace(WS_MAMBA).ensure((proj_f + bc_f + y_f + y16_f) * sizeof(float) + 1024, &wsp);
     if (rc) return rc;
     float* proj = static_cast<float*>(wsp);
     float* bc = proj + ((proj_f + 3) & ~(size_t)3);
     float* y = bc + ((bc_f + 3) & ~(size_t)3);
-    rc = linear(x, w_in, kind, proj, (int)NT, p.d, p.proj);
+    __half* y16 = reinterpret_cast<__half*>(y + ((y_f + 3) & ~(size_t)3));
+    if (x16 && linear_uses_gemm(w_in, kind, proj, (int)NT, p.d, p.proj) && (reinterpret_cast<uintptr_t>(x16) & 15) == 0)
+        rc = linear_a16(x16, w_in, kind, proj, (int)NT, p.d, p.proj);
+    else
+        rc = linear(x, w_in, kind, proj, (int)NT, p.d, p.proj);
     if (rc) return rc;
     {
         const int64_t total = NT * p.conv_dim;
@@ -553,8 +567,10 @@ int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const 
             B200_LAUNCH_CHECK("mamba_scan_seq_general_kernel");
         }
     }
-    mamba_gated_norm_kernel<<<(unsigned)NT, 256, 0, stream()>>>(y, proj, p.proj, norm_w, y, p.d_inner, p.eps);
+    mamba_gated_norm_kernel<<<(unsigned)NT, 256, 0, stream()>>>(y, proj, p.proj, norm_w, y, p.d_inner, p.eps,
+                                                                out_gemm ? y16 : nullptr);
     B200_LAUNCH_CHECK("mamba_gated_norm_kernel");
+    if (out_gemm) return linear_a16(y16, w_out, kind, out, (int)NT, p.d_inner, p.d);
     return linear(y, w_out, kind, out, (int)NT, p.d_inner, p.d);
 }
 

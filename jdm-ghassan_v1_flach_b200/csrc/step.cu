@@ -10,6 +10,8 @@
 #include <vector>
 
 #include "fused.cuh"
+#include "gemm.cuh"
+#include "linear.cuh"
 #include "../../include/b200step.h"
 
 namespace b200 {
@@ -339,9 +341,10 @@ __global__ void last_rows_kernel(const float* __restrict__ src, float* __restric
 // in one pass over the row (the same operations in the same order as residual_kernel and
 // rmsnorm_kernel: double sum of squares, inv rounded to float).  One block per row.
 constexpr int RRN_PER = 16;      // row elements a thread keeps in registers: dim <= 4096
+// out16 (optional): the normalised row once more as fp16 (clamped), for the tensor-core GEMMs.
 __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, float s,
                                                                const float* __restrict__ w, float* __restrict__ out,
-                                                               int dim, float eps) {
+                                                               int dim, float eps, __half* __restrict__ out16) {
     __shared__ double red[32];
     const int64_t r = blockIdx.x;
     float* xr = x + r * dim;
@@ -365,7 +368,11 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
 #pragma unroll
     for (int j = 0; j < RRN_PER; ++j) {
         const int i = j * 256 + threadIdx.x;
-        if (i < dim) o[i] = v[j] * inv * w[i];
+        if (i < dim) {
+            const float r2 = v[j] * inv * w[i];
+            o[i] = r2;
+            if (out16) out16[r * dim + i] = __float2half_rn(fminf(fmaxf(r2, -65504.0f), 65504.0f));
+        }
     }
 }
 
@@ -383,7 +390,8 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
     size_t off = 0;
     auto take = [&](size_t bytes) { const size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
     const size_t o_x = take(NT * d * 4), o_xb = take(NT * d * 4), o_y = take(NT * d * 4), o_q = take(NT * qd * 4),
-                 o_k = take(NT * kvd * 4), o_v = take(NT * kvd * 4), o_at = take(NT * qd * 4), o_pos = take(NT * 4);
+                 o_k = take(NT * kvd * 4), o_v = take(NT * kvd * 4), o_at = take(NT * qd * 4), o_pos = take(NT * 4),
+                 o_xb16 = take(NT * d * 2);
     void* wsp;
     STEP(workspace(WS_PREFILL).ensure(off + 256, &wsp));
     char* base = static_cast<char*>(wsp);
@@ -392,11 +400,14 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
           *k = reinterpret_cast<float*>(base + o_k), *v = reinterpret_cast<float*>(base + o_v),
           *at = reinterpret_cast<float*>(base + o_at);
     int32_t* pos = reinterpret_cast<int32_t*>(base + o_pos);
+    __half* xb16 = reinterpret_cast<__half*>(base + o_xb16);      // fp16 copy of xb for the GEMMs (when d % 8 == 0)
+    const bool want16 = d % 8 == 0 && d <= RRN_PER * 256;
     const int kind = tag_of_qkind(dec->qkind);
     MambaDims p;
     p.d = d; p.d_inner = dec->d_inner; p.conv_dim = dec->conv_dim; p.n_heads = dec->mh; p.d_head = dec->mdh;
     p.d_state = dec->mds; p.k = dec->mk; p.eps = dec->eps; p.proj = dec->d_inner + dec->conv_dim + dec->mh;
-    auto lin = [&](const float* in, const void* w, float* out, int K, int N) {
+    auto lin = [&](const float* in, const void* w, float* out, int K, int N, const __half* in16 = nullptr) {
+        if (in16 && linear_uses_gemm(w, kind, out, (int)NT, K, N)) return linear_a16(in16, w, kind, out, (int)NT, K, N);
         return dec->qkind >= 0 ? b200_linear_forward_q4(in, static_cast<const uint16_t*>(w), out, (int)NT, K, N, dec->qkind)
                                : b200_linear_forward_fp16(in, static_cast<const uint16_t*>(w), out, (int)NT, K, N);
     };
@@ -410,7 +421,8 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
     // x += res_mult * y followed by the next norm; fused when the row fits the registers
     auto residual_norm = [&](const float* norm_w) -> int {
         if (norm_w && d <= RRN_PER * 256) {
-            residual_rmsnorm_kernel<<<(unsigned)NT, 256, 0, st>>>(x, y, dec->res_mult, norm_w, xb, d, dec->eps);
+            residual_rmsnorm_kernel<<<(unsigned)NT, 256, 0, st>>>(x, y, dec->res_mult, norm_w, xb, d, dec->eps,
+                                                                  want16 ? xb16 : nullptr);
             B200_LAUNCH_CHECK("residual_rmsnorm_kernel");
             return B200_OK;
         }
@@ -418,16 +430,19 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
         B200_LAUNCH_CHECK("residual_kernel");
         return norm_w ? b200_rmsnorm_forward(x, norm_w, xb, nullptr, NT, d, dec->eps) : B200_OK;
     };
-    if (dec->n_layers > 0) STEP(b200_rmsnorm_forward(x, dec->L[0].attn_norm, xb, nullptr, NT, d, dec->eps));
+    if (dec->n_layers > 0) {
+        STEP(b200_rmsnorm_forward(x, dec->L[0].attn_norm, xb, nullptr, NT, d, dec->eps));
+        if (want16) STEP(pack_rows_f16(xb, nullptr, 1, xb16, NT, d));
+    }
     for (int l = 0; l < dec->n_layers; ++l) {
         LayerW& w = dec->L[l];
         if (dec->types[l] == 0) {
             STEP(mamba2_forward(xb, w.mamba_in, w.conv_w, w.conv_b, w.dt_bias, w.a_log, w.D, w.mamba_norm, w.mamba_out,
-                                w.ssm_state, y, B, T, p, kind, w.conv_state));
+                                w.ssm_state, y, B, T, p, kind, w.conv_state, want16 ? xb16 : nullptr));
         } else {
-            STEP(lin(xb, w.wq, q, d, qd));
-            STEP(lin(xb, w.wk, k, d, kvd));
-            STEP(lin(xb, w.wv, v, d, kvd));
+            STEP(lin(xb, w.wq, q, d, qd, want16 ? xb16 : nullptr));
+            STEP(lin(xb, w.wk, k, d, kvd, want16 ? xb16 : nullptr));
+            STEP(lin(xb, w.wv, v, d, kvd, want16 ? xb16 : nullptr));
             if (dec->rope_type >= 0)
                 STEP(b200_rope_forward_cached(q, k, pos, dec->inv_freq, NT, dec->H, dec->KV, dec->hd, dec->rope_type));
             kv_prefill_kernel<<<dim3(ceil_div(kvd, 256), T, B), 256, 0, st>>>(k, v, w.k_pages, w.v_pages, dec->page_table, T,
