@@ -152,7 +152,11 @@ mamba_conv_step_kernel(const float* __restrict__ proj, const float* __restrict__
 // ---------------------------------------------------------------------------
 // out16 (optional, with d_inner <= 4096): the result as fp16 rows instead of fp32 (values
 // clamped to the fp16 range, as pack_rows_f16 does), for a tensor-core GEMM that follows.
-__global__ void __launch_bounds__(256)
+// PER: values of the row a thread keeps in registers (d_inner <= PER * 256), 0 = two passes
+// through `out`.  Six CTAs per SM: the kernel is a chain of load -> block reduction -> store
+// per row, so resident rows are what hides its latencies.
+template <int PER>
+__global__ void __launch_bounds__(256, 6)
 mamba_gated_norm_kernel(const float* y, const float* __restrict__ gate, int64_t gate_stride,
                         const float* __restrict__ norm_w, float* out, int d_inner, float eps,
                         __half* __restrict__ out16 = nullptr) {
@@ -162,9 +166,8 @@ mamba_gated_norm_kernel(const float* y, const float* __restrict__ gate, int64_t 
     const float* gr = gate + r * gate_stride;
     float* o = out + r * d_inner;
     double var = 0.0;
-    constexpr int PER = 16;                  // values a thread keeps in registers: d_inner <= 4096
-    if (d_inner <= PER * 256 && blockDim.x == 256) {
-        float v[PER];
+    if (PER > 0) {
+        float v[PER > 0 ? PER : 1];
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
             const int c = j * 256 + threadIdx.x;
@@ -177,21 +180,31 @@ mamba_gated_norm_kernel(const float* y, const float* __restrict__ gate, int64_t 
         for (int j = 0; j < PER; ++j) {
             const int c = j * 256 + threadIdx.x;
             if (c < d_inner) {
-                const float r = v[j] * inv * norm_w[c];
-                if (out16) out16[(int64_t)blockIdx.x * d_inner + c] = __float2half_rn(fminf(fmaxf(r, -65504.0f), 65504.0f));
-                else o[c] = r;
+                const float res = v[j] * inv * norm_w[c];
+                if (out16) out16[r * d_inner + c] = __float2half_rn(fminf(fmaxf(res, -65504.0f), 65504.0f));
+                else o[c] = res;
             }
         }
-        return;
+    } else {
+        for (int c = threadIdx.x; c < d_inner; c += blockDim.x) {
+            const float v = yr[c] * silu_acc(gr[c]);
+            o[c] = v;
+            var += (double)v * v;
+        }
+        var = block_sum_d(var, red) / (double)d_inner;
+        const float inv = 1.0f / sqrtf((float)var + eps);
+        for (int c = threadIdx.x; c < d_inner; c += blockDim.x) o[c] = o[c] * inv * norm_w[c];
     }
-    for (int c = threadIdx.x; c < d_inner; c += blockDim.x) {
-        const float v = yr[c] * silu_acc(gr[c]);
-        o[c] = v;
-        var += (double)v * v;
-    }
-    var = block_sum_d(var, red) / (double)d_inner;
-    const float inv = 1.0f / sqrtf((float)var + eps);
-    for (int c = threadIdx.x; c < d_inner; c += blockDim.x) o[c] = o[c] * inv * norm_w[c];
+}
+
+static void launch_gated_norm(const float* y, const float* gate, int64_t gate_stride, const float* norm_w, float* out,
+                              int d_inner, float eps, __half* out16, int64_t rows) {
+    const unsigned g = (unsigned)rows;
+    if (d_inner <= 1024) mamba_gated_norm_kernel<4><<<g, 256, 0, stream()>>>(y, gate, gate_stride, norm_w, out, d_inner, eps, out16);
+    else if (d_inner <= 2048) mamba_gated_norm_kernel<8><<<g, 256, 0, stream()>>>(y, gate, gate_stride, norm_w, out, d_inner, eps, out16);
+    else if (d_inner <= 3072) mamba_gated_norm_kernel<12><<<g, 256, 0, stream()>>>(y, gate, gate_stride, norm_w, out, d_inner, eps, out16);
+    else if (d_inner <= 4096) mamba_gated_norm_kernel<16><<<g, 256, 0, stream()>>>(y, gate, gate_stride, norm_w, out, d_inner, eps, out16);
+    else mamba_gated_norm_kernel<0><<<g, 256, 0, stream()>>>(y, gate, gate_stride, norm_w, out, d_inner, eps, nullptr);
 }
 
 // ---------------------------------------------------------------------------
@@ -436,7 +449,7 @@ int mamba2_step(const float* x, const void* w_in, const float* conv_w, const flo
         mamba_step_scan_kernel<<<dim3(ceil_div(rows, SCAN_WARPS), batch), SCAN_WARPS * 32, 0, stream()>>>(
             bc, proj + p.d_inner + p.conv_dim, dt_bias, a_log, D, ssm_state, y, p.proj, p);
         B200_LAUNCH_CHECK("mamba_step_scan_kernel");
-        mamba_gated_norm_kernel<<<batch, 256, 0, stream()>>>(y, proj, p.proj, norm_w, y, p.d_inner, p.eps);
+        launch_gated_norm(y, proj, p.proj, norm_w, y, p.d_inner, p.eps, nullptr, batch);
         B200_LAUNCH_CHECK("mamba_gated_norm_kernel");
         return linear(y, w_out, kind, out, batch, p.d_inner, p.d);
     }
@@ -461,7 +474,7 @@ int mamba2_step(const float* x, const void* w_in, const float* conv_w, const flo
     mamba_step_scan_kernel<<<dim3(ceil_div(rows, SCAN_WARPS), batch), SCAN_WARPS * 32, 0, stream()>>>(
         bc, dt_raw, dt_bias, a_log, D, ssm_state, y, p.n_heads, p);
     B200_LAUNCH_CHECK("mamba_step_scan_kernel");
-    mamba_gated_norm_kernel<<<batch, 256, 0, stream()>>>(y, gate, p.d_inner, norm_w, y, p.d_inner, p.eps);
+    launch_gated_norm(y, gate, p.d_inner, norm_w, y, p.d_inner, p.eps, nullptr, batch);
     B200_LAUNCH_CHECK("mamba_gated_norm_kernel");
     return linear(y, w_out, kind, out, batch, p.d_inner, p.d);
 }
@@ -567,8 +580,7 @@ int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const 
             B200_LAUNCH_CHECK("mamba_scan_seq_general_kernel");
         }
     }
-    mamba_gated_norm_kernel<<<(unsigned)NT, 256, 0, stream()>>>(y, proj, p.proj, norm_w, y, p.d_inner, p.eps,
-                                                                out_gemm ? y16 : nullptr);
+    launch_gated_norm(y, proj, p.proj, norm_w, y, p.d_inner, p.eps, out_gemm ? y16 : nullptr, NT);
     B200_LAUNCH_CHECK("mamba_gated_norm_kernel");
     if (out_gemm) return linear_a16(y16, w_out, kind, out, (int)NT, p.d_inner, p.d);
     return linear(y, w_out, kind, out, (int)NT, p.d_inner, p.d);
