@@ -404,30 +404,36 @@ def moe_layer_bench(lib, rank, world, tokens=4096, iters=10):
                                  ep.shard_experts(ups, ne, rank, world), ep.shard_experts(downs, ne, rank, world), sh)
     out = torch.empty(tokens, d, device="cuda")
 
-    def run():
+    def run(reduce_form=False):
         if world == 1:      # the plain layer call: no exchange, no host read of split sizes
             lib.b200_moe_forward_bias_half(x, router, bias, gates, ups, downs, sh[0], sh[1], sh[2], out, None, None, None,
                                            None, None, None, tokens, d, E, ne, K, SH, q)
+        elif reduce_form:
+            layer.forward_reduce(x)
         else:
             layer.forward(x)
 
+    def timed(reduce_form):
+        for _ in range(3):
+            run(reduce_form)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(iters):
+            run(reduce_form)
+        t1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([t0.elapsed_time(t1) / iters], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
     if world > 1:
         del gates, ups, downs
-    for _ in range(3):
-        run()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        run()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms = float(ms[0])
+    ms = timed(False)
+    ms_reduce = timed(True) if world > 1 else None
     flops = tokens * K * 3 * 2 * E * d + tokens * 3 * 2 * SH * d
     peak_tf = 1646.6
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -438,6 +444,8 @@ def moe_layer_bench(lib, rank, world, tokens=4096, iters=10):
     return {"tokens": tokens, "ms_per_layer": ms, "tok_s": tokens / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
             "frac_of_dense_peak": flops / (ms * 1e-3) / 1e12 / (peak_tf * world), "n_gpus": world,
             "mode": "single GPU" if world == 1 else "expert parallel, NCCL all-to-all",
+            "ms_per_layer_reduce_form": ms_reduce,
+            "reduce_form": None if ms_reduce is None else "replicated routing, local experts, one NCCL all-reduce of the output",
             "shape": "hidden 1536, 64 experts, top-6, ffn 512, shared 1024, Q4_K"}
 
 

@@ -53,9 +53,11 @@ class CudaBackend:
             self.lib.b200_moe_dispatch_pack(x, idx, n, d, ne, K, rows, inv, offsets)
         return rows, inv, offsets
 
-    def experts_rows(self, rows, offsets, group_map, gates, ups, downs, n_local, d, E, qkind):
+    def experts_rows(self, rows, offsets, group_map, gates, ups, downs, n_local, d, E, qkind, y=None):
+        """y (optional): a [R, d] fp32 buffer to write into; rows outside the groups are left as they are."""
         R = rows.shape[0]
-        y = torch.empty((R, d), dtype=torch.float32, device=rows.device)
+        if y is None:
+            y = torch.empty((R, d), dtype=torch.float32, device=rows.device)
         if R:
             self.lib.b200_moe_experts_rows(rows, offsets, group_map, group_map.numel(), R, gates, ups, downs, n_local,
                                            y, d, E, qkind)
@@ -146,6 +148,44 @@ class ExpertParallelMoE:
         y = self._all_to_all(y_remote, recv_rows, send_rows)
         part = be.shared_combine(xs, self.sh, y, inv, w, self.K, self.SH, self.qkind)
         return self._gather_slices(part, T), idx
+
+    def forward_reduce(self, x):
+        """The same layer without any dispatch.  The activations are replicated, so every rank
+        routes all T tokens (identical indices everywhere), runs only ITS experts on the slots
+        that hit them, and forms a partial output: the weighted sum of its experts' results
+        for every token, plus the shared expert for the tokens of its own slice.  One
+        all-reduce adds the partials.  No split sizes travel and the host reads nothing, at
+        the price of routing every token on every rank and of an output-sized reduction
+        ([T, d] fp32) instead of two row exchanges.  The K expert outputs of a token are added
+        per rank first, so the result equals forward()'s up to the order of those additions."""
+        T = x.shape[0]
+        G, nl, be, K = self.world, self.n_local, self.backend, self.K
+        idx, w = be.route(x, self.router_w, self.router_bias, self.ne, K)
+        rows, inv, offsets = be.dispatch_pack(x, idx, self.ne)
+        e0 = self.rank * nl
+        key = (rows.shape[0], x.device)
+        if getattr(self, "_y_key", None) != key:
+            # persistent and zero-initialised: rows no local expert writes in a call keep finite
+            # values (zeros, or results of earlier calls), so a weight of 0 masks them exactly
+            self._y_buf = torch.zeros((rows.shape[0], self.d), dtype=torch.float32, device=x.device)
+            self._y_key = key
+        gmap = torch.arange(nl, dtype=torch.int32, device=x.device)
+        y = be.experts_rows(rows, offsets[e0:e0 + nl + 1].contiguous(), gmap, self.gates, self.ups, self.downs, nl, self.d,
+                            self.E, self.qkind, y=self._y_buf)
+        w_local = torch.where((idx >= e0) & (idx < e0 + nl), w, torch.zeros_like(w))
+        lo, hi = token_slice(T, self.rank, G)
+        parts = []
+        for a, b, sh in ((0, lo, None), (lo, hi, self.sh), (hi, T, None)):
+            if b > a:
+                parts.append(be.shared_combine(x[a:b], sh, y, inv[a * K:b * K], w_local[a:b], K, self.SH, self.qkind))
+        out = parts[0] if len(parts) == 1 else torch.cat(parts, 0)
+        return self._reduce(out), idx
+
+    def _reduce(self, partial):
+        """Sum of the ranks' partial outputs (in place)."""
+        if self.world > 1:
+            dist.all_reduce(partial, group=self.group)
+        return partial
 
 
 def shard_experts(t, ne, rank, world):

@@ -42,8 +42,9 @@ class CheckerBackend:
         rows = x.numpy()[grouped // K]
         return torch.from_numpy(rows.copy()), torch.from_numpy(inv), torch.from_numpy(offsets)
 
-    def experts_rows(self, rows, offsets, group_map, gates, ups, downs, n_local, d, E, qkind):
-        y = np.zeros((rows.shape[0], d), np.float32)
+    def experts_rows(self, rows, offsets, group_map, gates, ups, downs, n_local, d, E, qkind, y=None):
+        keep = y
+        y = np.zeros((rows.shape[0], d), np.float32) if keep is None else keep.numpy()
         off, gm = offsets.numpy(), group_map.numpy()
         g3, u3, d3 = gates.numpy().reshape(n_local, E, d), ups.numpy().reshape(n_local, E, d), downs.numpy().reshape(n_local, d, E)
         for g in range(len(gm)):
@@ -53,7 +54,7 @@ class CheckerBackend:
                 xr = rows.numpy()[lo:hi]
                 act = self.o.swiglu(self.o.linear(xr, g3[e], -2, hi - lo, d, E), self.o.linear(xr, u3[e], -2, hi - lo, d, E))
                 y[lo:hi] = self.o.linear(act, d3[e], -2, hi - lo, E, d)
-        return torch.from_numpy(y)
+        return torch.from_numpy(y) if keep is None else keep
 
     def shared_combine(self, x, sh, y, inv, w, K, SH, qkind):
         n, d = x.shape
@@ -102,6 +103,11 @@ def _worker(rank, world, port, T, q):
         ok = bool(np.allclose(out.numpy(), want, rtol=1e-5, atol=1e-6)) and np.array_equal(idx.numpy(), want_idx[lo:hi])
         again, _ = layer.forward(torch.from_numpy(c["x"]))
         ok = ok and np.array_equal(out.numpy().view(np.uint32), again.numpy().view(np.uint32))
+        # the dispatch-free form: every rank holds the whole output and all indices
+        red, ridx = layer.forward_reduce(torch.from_numpy(c["x"]))
+        ok = ok and bool(np.allclose(red.numpy(), want, rtol=1e-5, atol=1e-6)) and np.array_equal(ridx.numpy(), want_idx)
+        red2, _ = layer.forward_reduce(torch.from_numpy(c["x"]))      # second call reuses the row buffer
+        ok = ok and bool(np.allclose(red2.numpy(), want, rtol=1e-5, atol=1e-6))
         q.put((rank, ok, sum(layer.last_counts)))
     finally:
         dist.destroy_process_group()
@@ -119,6 +125,9 @@ def test_single_process_equals_layer():
     want, want_idx = _want(o, c)
     np.testing.assert_allclose(out.numpy(), want, rtol=1e-5, atol=1e-6)
     assert np.array_equal(idx.numpy(), want_idx)
+    red, ridx = _layer(o, c, 0, 1).forward_reduce(torch.from_numpy(c["x"]))
+    np.testing.assert_allclose(red.numpy(), want, rtol=1e-5, atol=1e-6)
+    assert np.array_equal(ridx.numpy(), want_idx)
 
 
 @pytest.mark.parametrize("world,T", [(2, 13), (2, 1), (4, 30)])

@@ -101,3 +101,38 @@ def test_virtual_ranks_equal_the_layer(oracle, G):
     ref, _, _, _ = oracle.moe_forward(sub["x"], c["router_w"], c["router_bias"], c["gates"], c["ups"], c["downs"],
                                       c["sh_g"], c["sh_u"], c["sh_d"], d, E, ne, K, SH, wkind)
     fp16_close(out[sample], ref)
+
+
+@pytest.mark.parametrize("G", [2, 8])
+def test_dispatch_free_form_with_virtual_ranks(oracle, G):
+    """forward_reduce(): every virtual rank routes all tokens, runs its own experts and forms
+    a partial output; the sum of the partials (what the all-reduce computes) is the layer.
+    The K expert outputs of a token are added per rank first, so the comparison with the
+    single-GPU layer is to summation order, not bit for bit.  Two rounds: the second one
+    reuses each rank's persistent row buffer with different tokens."""
+    from gpu_util import SUM_ORDER, host
+    T, d, E, ne, K, SH, wkind = 200, 1536, 512, 64, 6, 1024, 3
+    layers = None
+    for seed in (11, 12):
+        c, dc = _dev_case(oracle, seed, T, d, E, ne, K, SH, wkind)
+        if layers is None:
+            weights = dc
+            layers = []
+            for r in range(G):
+                sh = tuple(ep.shard_experts(dc[k], ne, r, G) for k in ("gates", "ups", "downs"))
+                layer = ep.ExpertParallelMoE(d, E, ne, K, SH, wkind, dc["router_w"], dc["router_bias"], *sh,
+                                             (dc["sh_g"], dc["sh_u"], dc["sh_d"]))
+                layer.rank, layer.world, layer.n_local = r, G, ne // G
+                layer._reduce = lambda t: t                       # the test adds the partials itself
+                layers.append(layer)
+        x = dc["x"]
+        total, idx0 = None, None
+        for layer in layers:
+            part, idx = layer.forward_reduce(x)
+            total = part.clone() if total is None else total + part
+            idx0 = idx if idx0 is None else idx0
+            assert torch.equal(idx, idx0)                           # the same routing on every rank
+        wd = dict(weights, x=x)
+        want, want_idx = _single_gpu_layer(wd, T, d, E, ne, K, SH, wkind)
+        assert np.array_equal(host(idx0), want_idx)
+        np.testing.assert_allclose(host(total), want, **SUM_ORDER)
