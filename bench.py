@@ -404,10 +404,14 @@ def moe_layer_bench(lib, rank, world, tokens=4096, iters=10):
                                  ep.shard_experts(ups, ne, rank, world), ep.shard_experts(downs, ne, rank, world), sh)
     out = torch.empty(tokens, d, device="cuda")
 
+    replay = {"fn": None}
+
     def run(reduce_form=False):
         if world == 1:      # the plain layer call: no exchange, no host read of split sizes
             lib.b200_moe_forward_bias_half(x, router, bias, gates, ups, downs, sh[0], sh[1], sh[2], out, None, None, None,
                                            None, None, None, tokens, d, E, ne, K, SH, q)
+        elif reduce_form == "graph":
+            replay["fn"](x)
         elif reduce_form:
             layer.forward_reduce(x)
         else:
@@ -434,6 +438,13 @@ def moe_layer_bench(lib, rank, world, tokens=4096, iters=10):
         del gates, ups, downs
     ms = timed(False)
     ms_reduce = timed(True) if world > 1 else None
+    ms_graph, graph_note = None, None
+    if world > 1:
+        try:
+            replay["fn"] = layer.graphed_reduce(x)
+            ms_graph = timed("graph")
+        except Exception as e:                       # capture is an optimisation: report, do not fail the bench
+            graph_note = "capture failed: %s" % (str(e).splitlines()[0][:160] if str(e) else type(e).__name__)
     flops = tokens * K * 3 * 2 * E * d + tokens * 3 * 2 * SH * d
     peak_tf = 1646.6
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -445,6 +456,7 @@ def moe_layer_bench(lib, rank, world, tokens=4096, iters=10):
             "frac_of_dense_peak": flops / (ms * 1e-3) / 1e12 / (peak_tf * world), "n_gpus": world,
             "mode": "single GPU" if world == 1 else "expert parallel, NCCL all-to-all",
             "ms_per_layer_reduce_form": ms_reduce,
+            "ms_per_layer_reduce_form_graph": ms_graph if ms_graph is not None else graph_note,
             "reduce_form": None if ms_reduce is None else "replicated routing, local experts, one NCCL all-reduce of the output",
             "shape": "hidden 1536, 64 experts, top-6, ffn 512, shared 1024, Q4_K"}
 

@@ -181,6 +181,36 @@ class ExpertParallelMoE:
         out = parts[0] if len(parts) == 1 else torch.cat(parts, 0)
         return self._reduce(out), idx
 
+    def graphed_reduce(self, x):
+        """forward_reduce() for inputs of x's shape, captured once into a CUDA graph (the
+        dispatch-free form reads nothing on the host and has static shapes, so the whole layer -
+        kernels, the small torch ops between them and the NCCL all-reduce - replays as one
+        launch).  Returns replay(x_new) -> (out, idx); the tensors it returns are reused by the
+        next replay.  CUDA backend only."""
+        lib = self.backend.lib
+        side = torch.cuda.Stream(device=x.device)
+        static_x = x.clone()
+        side.wait_stream(torch.cuda.current_stream(x.device))
+        lib.b200_set_stream(side.cuda_stream)
+        try:
+            with torch.cuda.stream(side):
+                for _ in range(2):                       # grows workspaces, builds tensor maps, warms NCCL
+                    self.forward_reduce(static_x)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                out, idx = self.forward_reduce(static_x)
+        finally:
+            lib.b200_set_stream(None)
+        torch.cuda.current_stream(x.device).wait_stream(side)
+
+        def replay(x_new):
+            static_x.copy_(x_new)
+            graph.replay()
+            return out, idx
+
+        return replay
+
     def _reduce(self, partial):
         """Sum of the ranks' partial outputs (in place)."""
         if self.world > 1:

@@ -136,3 +136,23 @@ def test_dispatch_free_form_with_virtual_ranks(oracle, G):
         want, want_idx = _single_gpu_layer(wd, T, d, E, ne, K, SH, wkind)
         assert np.array_equal(host(idx0), want_idx)
         np.testing.assert_allclose(host(total), want, **SUM_ORDER)
+
+
+def test_dispatch_free_form_replays_as_a_cuda_graph(oracle):
+    """graphed_reduce(): the captured layer gives the same bits as the eager call, also for a
+    second input of the same shape."""
+    from gpu_util import host, pkg
+    T, d, E, ne, K, SH, wkind = 128, 256, 256, 16, 2, 512, 3
+    c, dc = _dev_case(oracle, 21, T, d, E, ne, K, SH, wkind)
+    layer = ep.ExpertParallelMoE(d, E, ne, K, SH, wkind, dc["router_w"], dc["router_bias"], dc["gates"], dc["ups"],
+                                 dc["downs"], (dc["sh_g"], dc["sh_u"], dc["sh_d"]))
+    replay = layer.graphed_reduce(dc["x"])
+    for seed in (21, 22):
+        x = _dev_case(oracle, seed, T, d, E, ne, K, SH, wkind)[1]["x"]
+        want, want_idx = layer.forward_reduce(x)
+        torch.cuda.synchronize()
+        got, got_idx = replay(x)
+        torch.cuda.synchronize()
+        assert torch.equal(got_idx, want_idx)
+        assert np.array_equal(host(got).view(np.uint32), host(want).view(np.uint32))
+    assert pkg.lib().raw("b200_stream_status") == 0
