@@ -378,7 +378,7 @@ def time_kernel_gbs(fn, bytes_per_launch, iters=20):
     return bytes_per_launch / (ms * 1e-3) / 1e9, ms
 
 
-def moe_layer_bench(lib, rank, world, tokens=4096, iters=10):
+def moe_layer_bench(lib, rank, world, tokens=4096, iters=10, graph=False):
     """The MoE layer alone at the H-Tiny shape (hidden 1536, 64 experts, top-6, ffn 512,
     shared 1024, Q4_K) on `tokens` replicated tokens: the single-GPU layer at world 1,
     expert-parallel over NCCL all-to-all at world > 1 (experts sharded, tokens sliced,
@@ -439,7 +439,7 @@ def moe_layer_bench(lib, rank, world, tokens=4096, iters=10):
     ms = timed(False)
     ms_reduce = timed(True) if world > 1 else None
     ms_graph, graph_note = None, None
-    if world > 1:
+    if world > 1 and graph:
         try:
             replay["fn"] = layer.graphed_reduce(x)
             ms_graph = timed("graph")
@@ -571,6 +571,9 @@ def main():
     ap.add_argument("--graph", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--small", action="store_true", help="4-layer model (development only; not a bench number)")
+    ap.add_argument("--ep-graph", action="store_true",
+                    help="N > 1: also time the dispatch-free expert-parallel layer replayed as one CUDA graph "
+                         "(NCCL all-reduce captured with it)")
     ap.add_argument("--profile-step", action="store_true",
                     help="after the timed steps run ONE more step between cudaProfilerStart/Stop and exit "
                          "(for ncu --profile-from-start off: DRAM bytes of every launch of a step)")
@@ -712,7 +715,7 @@ def main():
 
     q4k_bytes = proj_n * d // 256 * 144
     q4k_gbs, q4k_ms = time_kernel_gbs(q4k_call, q4k_bytes, iters=len(mamba_layers) * 2)
-    moe = moe_layer_bench(lib, rank, world)
+    moe = moe_layer_bench(lib, rank, world, graph=args.ep_graph)
     batch64 = None
     if world == 1 and B == 1 and not args.small:
         model.close()
