@@ -50,7 +50,9 @@ attn_flash_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     __shared__ int32_t s_seg[FA_BN];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const int lj = lane >> 3, lr = lane & 7;                // ldmatrix: which 8 x 8 tile, which of its rows
-    const int q0 = blockIdx.x * FA_BM, h = blockIdx.y, b = blockIdx.z;
+    // query tiles are handed out last first: under the causal mask a tile's work grows with
+    // its position, and the heavy ones should not be what the last wave is made of
+    const int q0 = (gridDim.x - 1 - blockIdx.x) * FA_BM, h = blockIdx.y, b = blockIdx.z;
     const int kvh = h / (H / KV);
     const int64_t qs = (int64_t)T * H * HD, kvs = (int64_t)T * KV * HD;
     const float* qb = q + b * qs + (int64_t)h * HD;
