@@ -160,7 +160,16 @@ class ExpertParallelMoE:
         per rank first, so the result equals forward()'s up to the order of those additions."""
         T = x.shape[0]
         G, nl, be, K = self.world, self.n_local, self.backend, self.K
-        idx, w = be.route(x, self.router_w, self.router_bias, self.ne, K)
+        if G > 1 and T % G == 0 and T > 0:
+            # routing is per token: each rank routes its slice and the (small) results are gathered
+            lo, hi = token_slice(T, self.rank, G)
+            idx_s, w_s = be.route(x[lo:hi], self.router_w, self.router_bias, self.ne, K)
+            idx = torch.empty((T, K), dtype=idx_s.dtype, device=x.device)
+            w = torch.empty((T, K), dtype=w_s.dtype, device=x.device)
+            dist.all_gather_into_tensor(idx, idx_s.contiguous(), group=self.group)
+            dist.all_gather_into_tensor(w, w_s.contiguous(), group=self.group)
+        else:
+            idx, w = be.route(x, self.router_w, self.router_bias, self.ne, K)
         rows, inv, offsets = be.dispatch_pack(x, idx, self.ne)
         e0 = self.rank * nl
         key = (rows.shape[0], x.device)

@@ -130,9 +130,10 @@ def test_single_process_equals_layer():
     assert np.array_equal(ridx.numpy(), want_idx)
 
 
-@pytest.mark.parametrize("world,T", [(2, 13), (2, 1), (4, 30)])
+@pytest.mark.parametrize("world,T", [(2, 13), (2, 1), (4, 30), (2, 8), (4, 16)])
 def test_expert_parallel_over_gloo(world, T):
-    """T = 1 leaves ranks without tokens; 13 and 30 give ragged slices and ragged expert loads."""
+    """T = 1 leaves ranks without tokens; 13 and 30 give ragged slices and ragged expert loads;
+    8 and 16 divide evenly (the dispatch-free form then routes per slice and gathers the indices)."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
