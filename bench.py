@@ -457,7 +457,7 @@ def moe_layer_bench(lib, rank, world, tokens=4096, iters=10, graph=False):
             "mode": "single GPU" if world == 1 else "expert parallel, NCCL all-to-all",
             "ms_per_layer_reduce_form": ms_reduce,
             "ms_per_layer_reduce_form_graph": ms_graph if ms_graph is not None else graph_note,
-            "reduce_form": None if ms_reduce is None else "replicated routing, local experts, one NCCL all-reduce of the output",
+            "reduce_form": None if ms_reduce is None else "no dispatch: routing per token slice + all-gather of the indices, local experts on the packed rows, one NCCL all-reduce of the output",
             "shape": "hidden 1536, 64 experts, top-6, ffn 512, shared 1024, Q4_K"}
 
 
