@@ -160,7 +160,7 @@ class ExpertParallelMoE:
         per rank first, so the result equals forward()'s up to the order of those additions."""
         T = x.shape[0]
         G, nl, be, K = self.world, self.n_local, self.backend, self.K
-        if G > 1 and T % G == 0 and T > 0:
+        if G > 1 and dist.is_initialized() and T % G == 0 and T > 0:
             # routing is per token: each rank routes its slice and the (small) results are gathered
             lo, hi = token_slice(T, self.rank, G)
             idx_s, w_s = be.route(x[lo:hi], self.router_w, self.router_bias, self.ne, K)
