@@ -64,8 +64,15 @@ int b200_decoder_reset(b200_decoder* dec);
  * fused = 1: cross-op fusions (norm into the following projection's prologue,
  * residual add into the epilogue); returns B200_EUNSUPPORTED, leaving the mode
  * unchanged, when a matrix of the model cannot be cut into 16-byte-aligned row
- * tiles (the per-op mode has no such limit).  use_graph = 1 captures the step
- * once and replays it. */
+ * tiles (the per-op mode has no such limit).
+ * fused = 2 (batch 1 only): the Mamba and MoE phases of the token run inside one
+ * persistent cooperative kernel per run of layers between attention layers (all CTAs
+ * resident, weights streamed across phase boundaries, bounded grid barriers); attention
+ * mixers and the lm_head use the fused = 1 kernels.  Needs every tensor set (it copies the
+ * layer table to the device; b200_decoder_set_tensor afterwards drops back to fused = 0)
+ * and widths that are multiples of 256; B200_EUNSUPPORTED otherwise.
+ * use_graph = 1 captures the step once and replays it; the recording is dropped and made
+ * again whenever one of the library's workspaces has been reallocated or released since. */
 int b200_decoder_configure(b200_decoder* dec, int fused, int use_graph);
 /* One token per sequence.  tokens_dev [batch] int32 in; next_dev [batch] int32 out
  * (greedy arg-max of the logits); both device pointers; no host synchronisation. */
@@ -80,6 +87,19 @@ int b200_decoder_prefill(b200_decoder* dec, const int32_t* tokens_dev, int T, in
 /* Same through host buffers: H2D of the token ids, the step, D2H of the picks,
  * then a stream synchronise (what Generator::decode_step + ops::argmax_token do). */
 int b200_decoder_step_host(b200_decoder* dec, const int32_t* tokens_host, int32_t* next_host);
+/* Diagnostic hook for the bounded grid barrier of the persistent step (fused = 2):
+ * spin_limit > 0 replaces the iteration bound of its global-memory waits (0 restores the
+ * default), skip_cta >= 0 makes that CTA leave at its first barrier without arriving (-1:
+ * none).  With a CTA skipped the other CTAs' waits run out, the kernel returns and the step
+ * reports B200_ECUDA through b200_decoder_step_host / b200_stream_status; the sequences'
+ * state is then undefined until b200_decoder_reset. */
+int b200_decoder_test_barrier(b200_decoder* dec, int spin_limit, int skip_cta);
+/* Phase timers of the persistent step (the reference's phase timers, cuda/cuda_ops.h:315-319,
+ * at the granularity of this kernel).  stamps_host == NULL arms (cta >= 0: the CTA that
+ * records) or disarms (cta < 0) them; with a buffer of cap >= 4 * *n_phases entries it
+ * synchronises and returns, per phase of the last step, four %globaltimer stamps in ns:
+ * phase entered, activations staged, last tile done, barrier passed. */
+int b200_decoder_phase_trace(b200_decoder* dec, int cta, uint64_t* stamps_host, int cap, int* n_phases);
 /* Device pointer to the logits of the last step, [batch, vocab] fp32. */
 int b200_decoder_logits(b200_decoder* dec, const float** logits_dev);
 /* Tokens in each sequence's KV cache / state so far (all sequences advance together). */

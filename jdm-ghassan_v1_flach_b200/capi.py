@@ -21,6 +21,10 @@ _SCALARS = {
 }
 
 
+# int-returning functions whose result is a value, not a status code
+VALUE_RETURNING = {"b200_version", "b200_fp16_gemm_enabled", "b200_bf16_gemm_enabled"}
+
+
 class B200Error(RuntimeError):
     def __init__(self, name, code, message):
         super().__init__(f"{name}: status {code}: {message}")
@@ -100,7 +104,7 @@ class Library:
 
     def call(self, name, *args):
         rc = self.raw(name, *args)
-        if self.protos[name][0] == "int" and rc != 0:
+        if self.protos[name][0] == "int" and rc != 0 and name not in VALUE_RETURNING:
             raise B200Error(name, rc, self.last_error())
         return rc
 

@@ -49,6 +49,7 @@ struct Workspace {
 };
 enum { WS_LINEAR = 0, WS_MOE = 1, WS_MAMBA = 2, WS_ATTN = 3, WS_SAMPLE = 4, WS_PERM = 5, WS_ROUTE = 6, WS_PREFILL = 7, WS_SPLITK = 8, WS_COUNT = 9 };
 Workspace& workspace(int which);
+unsigned long long workspace_generation();   // changes whenever a workspace address goes stale
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }

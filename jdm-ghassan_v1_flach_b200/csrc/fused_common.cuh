@@ -37,15 +37,18 @@ struct UsesMma {
 };
 
 #ifdef __CUDACC__
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(SG_CTHREADS) : "memory"); }
+// NC consumer warps (the default is the fused per-phase kernels' count; the persistent
+// step kernel runs more).
+template <int NC = SG_CONSUMERS>
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NC * 32) : "memory"); }
 
 // Sum over the consumer threads; result in every consumer thread.  red: >= SG_CONSUMERS doubles.
 __device__ __forceinline__ double consumer_sum_d(double v, double* red) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     v = warp_sum_d(v);
-    consumer_sync();
+    consumer_sync<>();
     if (lane == 0) red[wid] = v;
-    consumer_sync();
+    consumer_sync<>();
     double t = 0.0;
 #pragma unroll
     for (int w = 0; w < SG_CONSUMERS; ++w) t += red[w];
@@ -139,8 +142,9 @@ __device__ __forceinline__ uint8_t* xact_carve(XAct& xa, uint8_t* p, int K, int 
 }
 
 // Zero row of the tensor-core layout (stands in for tokens beyond M).
-template <int KIND>
+template <int KIND, int NC = SG_CONSUMERS>
 __device__ __forceinline__ void xact_zero_row(const XAct& xa) {
+    constexpr int SG_CTHREADS = NC * 32;
     if (UsesMma<KIND>::value) {
         const size_t row = (size_t)(xa.K + XH_PAD);
         for (int k = threadIdx.x; k < xa.K + XH_PAD; k += SG_CTHREADS) {
@@ -157,18 +161,19 @@ __device__ __forceinline__ void split_half(float v, __half& h, __half& l) {
     l = __float2half_rn(v - __half2float(h));
 }
 
-// Two sums over the consumer threads at once; red: >= 2 * SG_CONSUMERS doubles.
+// Two sums over the consumer threads at once; red: >= 2 * NC doubles.
+template <int NC = SG_CONSUMERS>
 __device__ __forceinline__ void consumer_sum_d2(double& a, double& b, double* red) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     a = warp_sum_d(a);
     b = warp_sum_d(b);
-    consumer_sync();
-    if (lane == 0) { red[wid] = a; red[SG_CONSUMERS + wid] = b; }
-    consumer_sync();
+    consumer_sync<NC>();
+    if (lane == 0) { red[wid] = a; red[NC + wid] = b; }
+    consumer_sync<NC>();
     a = 0.0;
     b = 0.0;
 #pragma unroll
-    for (int w = 0; w < SG_CONSUMERS; ++w) { a += red[w]; b += red[SG_CONSUMERS + w]; }
+    for (int w = 0; w < NC; ++w) { a += red[w]; b += red[NC + w]; }
 }
 
 // Token m's activations from global memory (K floats at x) into shared memory.
@@ -182,10 +187,19 @@ __device__ __forceinline__ void consumer_sum_d2(double& a, double& b, double* re
 // already in shared memory.  `extra` is summed over the consumer threads in the same
 // reduction and returned (used for the gated-norm partial sums).  Consumer threads
 // only; ends with a consumer barrier.  K % 32 == 0.
+// CG: x was written by other CTAs of the running kernel (persistent step kernel): every
+// load goes to L2 (ld.global.cg) so that no stale L1 line is read.
 constexpr int XQ_REG = 4;                          // runs per thread held in registers: K <= 4096
-template <int KIND, bool RMS, bool EXTRA>
-__device__ __forceinline__ double stage_x(const float* __restrict__ x, const float* nw_s, const XAct& xa, int m,
+template <bool CG>
+__device__ __forceinline__ float4 ld_f4(const float* p) {
+    return CG ? __ldcg(reinterpret_cast<const float4*>(p)) : *reinterpret_cast<const float4*>(p);
+}
+template <bool CG>
+__device__ __forceinline__ float ld_f1(const float* p) { return CG ? __ldcg(p) : *p; }
+template <int KIND, bool RMS, bool EXTRA, bool CG = false, int NC = SG_CONSUMERS>
+__device__ __forceinline__ double stage_x(const float* x, const float* nw_s, const XAct& xa, int m,
                                           float eps, double* red, double extra) {
+    constexpr int SG_CTHREADS = NC * 32;
     const int K = xa.K;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* xs = UsesMma<KIND>::value ? nullptr : xa.xs + (size_t)m * xa.xs_tok;
@@ -234,17 +248,17 @@ __device__ __forceinline__ double stage_x(const float* __restrict__ x, const flo
 #pragma unroll
         for (int j = 0; j < XQ_REG; ++j) {
             const int q = j * SG_CTHREADS + threadIdx.x;
-            v[j] = (j < nrun && q < nq) ? *reinterpret_cast<const float4*>(x + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[j] = (j < nrun && q < nq) ? ld_f4<CG>(x + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
             if (RMS) ss += (double)v[j].x * v[j].x + (double)v[j].y * v[j].y + (double)v[j].z * v[j].z + (double)v[j].w * v[j].w;
         }
         float inv = 1.0f;
         if (RMS) {
-            consumer_sum_d2(ss, extra, red);
+            consumer_sum_d2<NC>(ss, extra, red);
             const double inv_d = 1.0 / sqrt(ss / (double)K + (double)eps);
             inv = isfinite(inv_d) ? (float)inv_d : 0.0f;
         } else if (EXTRA) {
             double z = 0.0;
-            consumer_sum_d2(extra, z, red);
+            consumer_sum_d2<NC>(extra, z, red);
         }
 #pragma unroll
         for (int j = 0; j < XQ_REG; ++j) {
@@ -259,7 +273,7 @@ __device__ __forceinline__ double stage_x(const float* __restrict__ x, const flo
                 emit4(q, ok, o);
             }
         }
-        consumer_sync();
+        consumer_sync<NC>();
         return extra;
     }
     // wide or unaligned rows: one value per thread and pass, raw values parked in shared
@@ -286,14 +300,14 @@ __device__ __forceinline__ double stage_x(const float* __restrict__ x, const flo
     if (!RMS) {
         if (EXTRA) {
             double z = 0.0;
-            consumer_sum_d2(extra, z, red);
+            consumer_sum_d2<NC>(extra, z, red);
         }
 #pragma unroll 4
         for (int j = 0; j < nv; ++j) {
             const int k = j * SG_CTHREADS + threadIdx.x;
-            emit(j, k < K ? x[k] : 0.0f);
+            emit(j, k < K ? ld_f1<CG>(x + k) : 0.0f);
         }
-        consumer_sync();
+        consumer_sync<NC>();
         return extra;
     }
     double ss = 0.0;
@@ -301,32 +315,33 @@ __device__ __forceinline__ double stage_x(const float* __restrict__ x, const flo
     for (int j = 0; j < nv; ++j) {
         const int k = j * SG_CTHREADS + threadIdx.x;
         if (k < K) {
-            const float val = x[k];
+            const float val = ld_f1<CG>(x + k);
             stash[UsesMma<KIND>::value ? k : xs_index<KIND>(k)] = val;
             ss += (double)val * val;
         }
     }
-    consumer_sum_d2(ss, extra, red);
+    consumer_sum_d2<NC>(ss, extra, red);
     const double inv_d = 1.0 / sqrt(ss / (double)K + (double)eps);
     const float inv = isfinite(inv_d) ? (float)inv_d : 0.0f;
     for (int j = 0; j < nv; ++j) {
         const int k = j * SG_CTHREADS + threadIdx.x;
         emit(j, k < K ? stash[UsesMma<KIND>::value ? k : xs_index<KIND>(k)] * inv * nw_s[k] : 0.0f);
     }
-    consumer_sync();
+    consumer_sync<NC>();
     return extra;
 }
 
 // `cnt` vectors of K floats (src + r * src_stride) into token rows 0..cnt-1 of xa in
 // one pass: all loads in flight together, one barrier.  No normalisation.  Falls back
 // to one stage_x per vector when the runs do not fit the registers.
-template <int KIND>
-__device__ __forceinline__ void stage_rows(const float* __restrict__ src, int64_t src_stride, const XAct& xa, int cnt,
+template <int KIND, bool CG = false, int NC = SG_CONSUMERS>
+__device__ __forceinline__ void stage_rows(const float* src, int64_t src_stride, const XAct& xa, int cnt,
                                            double* red) {
+    constexpr int SG_CTHREADS = NC * 32;
     const int K = xa.K, nq = K >> 2, total = cnt * nq;
     const int nrun = (total + SG_CTHREADS - 1) / SG_CTHREADS;
     if (nrun > XQ_REG || (reinterpret_cast<uintptr_t>(src) & 15) != 0 || (src_stride & 3) != 0) {
-        for (int r = 0; r < cnt; ++r) stage_x<KIND, false, false>(src + r * src_stride, nullptr, xa, r, 0.0f, red, 0.0);
+        for (int r = 0; r < cnt; ++r) stage_x<KIND, false, false, CG, NC>(src + r * src_stride, nullptr, xa, r, 0.0f, red, 0.0);
         return;
     }
     const int lane = threadIdx.x & 31;
@@ -336,8 +351,7 @@ __device__ __forceinline__ void stage_rows(const float* __restrict__ src, int64_
     for (int j = 0; j < XQ_REG; ++j) {
         const int i = j * SG_CTHREADS + threadIdx.x;
         const int r = i / nq, q = i - r * nq;
-        v[j] = (j < nrun && i < total) ? *reinterpret_cast<const float4*>(src + r * src_stride + 4 * q)
-                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[j] = (j < nrun && i < total) ? ld_f4<CG>(src + r * src_stride + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
     for (int j = 0; j < XQ_REG; ++j) {
@@ -374,7 +388,7 @@ __device__ __forceinline__ void stage_rows(const float* __restrict__ src, int64_
             }
         }
     }
-    consumer_sync();
+    consumer_sync<NC>();
 }
 
 // Dot products of a tile's rows with the staged activations of M tokens into

@@ -43,8 +43,14 @@ int num_sms() {
     return g_sms;
 }
 
+// Bumped whenever a workspace's device address stops being valid (reallocation or
+// release): what a captured CUDA graph compares against before it is replayed.
+static unsigned long long g_ws_generation = 0;
+unsigned long long workspace_generation() { return g_ws_generation; }
+
 int Workspace::ensure(size_t need, void** out) {
     if (need > bytes) {
+        ++g_ws_generation;
         if (ptr) {
             B200_CUDA(cudaFree(ptr));
             ptr = nullptr;
@@ -60,6 +66,7 @@ int Workspace::ensure(size_t need, void** out) {
 }
 
 void Workspace::release() {
+    if (ptr) ++g_ws_generation;
     if (ptr) cudaFree(ptr);
     ptr = nullptr;
     bytes = 0;

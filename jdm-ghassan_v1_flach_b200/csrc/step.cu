@@ -12,6 +12,7 @@
 #include "fused.cuh"
 #include "gemm.cuh"
 #include "linear.cuh"
+#include "persist.cuh"
 #include "../../include/b200step.h"
 
 namespace b200 {
@@ -125,6 +126,22 @@ struct b200_decoder {
     int f_blocks = 0;
     float *f_logits = nullptr, *f_w = nullptr, *f_act = nullptr, *f_shact = nullptr;
     int32_t* f_idx = nullptr;
+    // persistent mode (fused == 2, batch 1): device copies of the layer table and the phase
+    // list, the launch arguments, and the runs of phases between attention layers
+    PArgs pa;
+    PLayer* p_layers = nullptr;
+    POp* p_ops = nullptr;
+    struct Segment { int op_begin, op_end, attn_layer; };
+    std::vector<Segment> segments;
+    bool p_ready = false;
+    unsigned long long* pa_bar = nullptr;
+    unsigned int *pa_done = nullptr, *pa_flag = nullptr, *pa_rt = nullptr;
+    float *pa_bcd = nullptr, *pa_shout = nullptr;
+    double* pa_partials = nullptr;
+    unsigned long long* pa_trace = nullptr;
+    unsigned int test_spin_limit = 0;          // test hook (b200_decoder_test_barrier)
+    int test_skip_cta = -1;
+    unsigned long long ws_generation = 0;      // workspace generation the captured graph was recorded at
 };
 
 static int dev_alloc(b200_decoder* dec, void** p, size_t bytes) {
@@ -476,7 +493,172 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
     return B200_OK;
 }
 
+static int check_ready(const b200_decoder* dec);
+
+// The attention mixer of one layer on the fused few-token kernels (shared by the fused and
+// the persistent modes): q/k/v in one launch with the norm as prologue, RoPE, K/V append,
+// split-KV attention, output projection with the residual add as epilogue.
+static int enqueue_attention_fused(b200_decoder* dec, LayerW& w, int kind, bool dry) {
+    const int B = dec->batch, d = dec->d;
+    cudaStream_t st = stream();
+    const int qd = dec->H * dec->hd, kvd = dec->KV * dec->hd;
+    int rc;
+    auto base = [&](const void* wt, int N, int K, const float* x, int xs) {
+        SgArgs a;
+        a.w = static_cast<const uint8_t*>(wt); a.N = N; a.K = K; a.M = B; a.x = x; a.x_stride = xs; a.eps = dec->eps;
+        a.dry = dry;
+        return a;
+    };
+    SgArgs aq = base(w.wq, qd, d, dec->x, d);
+    aq.norm_w = w.attn_norm; aq.y = dec->q; aq.y_stride = qd;
+    aq.w2 = static_cast<const uint8_t*>(w.wk); aq.N2 = kvd; aq.y2 = dec->k; aq.y2_stride = kvd;
+    aq.w3 = static_cast<const uint8_t*>(w.wv); aq.N3 = kvd; aq.y3 = dec->v; aq.y3_stride = kvd;
+    rc = stream_gemv(aq, kind, PRO_RMS, EPI_STORE);
+    if (rc) return rc;
+    if (!dry) {
+        if (dec->rope_type >= 0) {
+            rc = b200_rope_forward_cached(dec->q, dec->k, dec->pos, dec->inv_freq, B, dec->H, dec->KV, dec->hd,
+                                          dec->rope_type);
+            if (rc) return rc;
+        }
+        kv_append_kernel<<<dim3(ceil_div(kvd, 256), B), 256, 0, st>>>(dec->k, dec->v, w.k_pages, w.v_pages,
+                                                                     dec->page_table, dec->pos, dec->max_pages,
+                                                                     dec->page, kvd);
+        B200_LAUNCH_CHECK("kv_append_kernel");
+        rc = b200_attention_decode_paged_fp16(dec->q, w.k_pages, w.v_pages, dec->page_table, dec->len, dec->attn, B,
+                                              dec->max_pages, dec->page, dec->H, dec->KV, dec->hd, dec->attn_scale);
+        if (rc) return rc;
+    }
+    SgArgs ao = base(w.wo, d, qd, dec->attn, qd);
+    ao.resid = dec->x; ao.y_stride = d; ao.res_mult = dec->res_mult;
+    return stream_gemv(ao, kind, PRO_NONE, EPI_RESIDUAL);
+}
+
+// Persistent mode: the phase list cut into runs at the attention layers, each run one
+// cooperative launch of the persistent kernel; attention mixers and the lm_head on the
+// fused few-token kernels between and after them.
+static int build_persistent(b200_decoder* dec) {
+    B200_REQUIRE(dec->batch == 1, "decoder_configure: the persistent step serves batch 1 (batch is %d)", dec->batch);
+    int rc = check_ready(dec);
+    if (rc) return rc;
+    const int kind = tag_of_qkind(dec->qkind);
+    std::vector<PLayer> layers(dec->n_layers);
+    std::vector<POp> ops;
+    dec->segments.clear();
+    int seg_begin = 0;
+    ops.push_back({POP_EMBED, 0});
+    auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    for (int l = 0; l < dec->n_layers; ++l) {
+        const LayerW& w = dec->L[l];
+        PLayer& P = layers[l];
+        memset(&P, 0, sizeof(P));
+        P.attn_norm = w.attn_norm; P.ffn_norm = w.ffn_norm;
+        P.mamba_in = static_cast<const uint8_t*>(w.mamba_in); P.mamba_out = static_cast<const uint8_t*>(w.mamba_out);
+        P.conv_w = w.conv_w; P.conv_b = w.conv_b; P.dt_bias = w.dt_bias; P.a_log = w.a_log; P.D = w.D;
+        P.mamba_norm = w.mamba_norm; P.conv_state = w.conv_state; P.ssm_state = w.ssm_state;
+        P.router = w.router; P.router_bias = w.router_bias;
+        P.gate = static_cast<const uint8_t*>(w.gate); P.up = static_cast<const uint8_t*>(w.up);
+        P.down = static_cast<const uint8_t*>(w.down); P.sh_gate = static_cast<const uint8_t*>(w.sh_gate);
+        P.sh_up = static_cast<const uint8_t*>(w.sh_up); P.sh_down = static_cast<const uint8_t*>(w.sh_down);
+        P.has_shared = (dec->SH > 0 && w.sh_gate && w.sh_up && w.sh_down) ? 1 : 0;
+        B200_REQUIRE(aligned(P.mamba_in) && aligned(P.mamba_out) && aligned(P.router) && aligned(P.gate) && aligned(P.up) &&
+                         aligned(P.down) && aligned(P.sh_gate) && aligned(P.sh_up) && aligned(P.sh_down) &&
+                         aligned(P.attn_norm) && aligned(P.ffn_norm) && aligned(P.conv_w) && aligned(P.conv_b) &&
+                         aligned(P.mamba_norm),
+                     "decoder_configure: layer %d: tensors must be 16-byte aligned", l);
+        if (dec->types[l] == 0) {
+            ops.push_back({POP_MAMBA_A, l});
+            ops.push_back({POP_MAMBA_B, l});
+        } else {
+            dec->segments.push_back({seg_begin, (int)ops.size(), l});
+            seg_begin = (int)ops.size();
+        }
+        ops.push_back({POP_MOE_C, l});
+        ops.push_back({POP_MOE_D, l});
+        ops.push_back({POP_MOE_E, l});
+    }
+    dec->segments.push_back({seg_begin, (int)ops.size(), -1});
+    PArgs& a = dec->pa;
+    a = PArgs();
+    a.d = dec->d; a.d_inner = dec->d_inner; a.conv_dim = dec->conv_dim; a.n_heads = dec->mh; a.d_head = dec->mdh;
+    a.d_state = dec->mds; a.dconv = dec->mk; a.proj = dec->d_inner + dec->conv_dim + dec->mh;
+    a.ne = dec->ne; a.K = dec->K; a.E = dec->E; a.SH = dec->SH; a.vocab = dec->vocab;
+    a.eps = dec->eps; a.res_mult = dec->res_mult; a.emb_mult = dec->emb_mult;
+    a.n_layers = dec->n_layers;
+    for (const b200_decoder::Segment& sg : dec->segments) a.max_ops = std::max(a.max_ops, sg.op_end - sg.op_begin);
+    rc = persist_plan(a, kind);
+    if (rc) return rc;
+    // the attention mixers and the lm_head run on the fused kernels: their tiling must fit too
+    for (int l = 0; l < dec->n_layers; ++l)
+        if (dec->types[l] != 0) {
+            rc = enqueue_attention_fused(dec, dec->L[l], kind, true);
+            if (rc) return rc;
+        }
+    if (!dec->p_layers) {
+        rc = dev_alloc(dec, (void**)&dec->p_layers, layers.size() * sizeof(PLayer));
+        if (rc) return rc;
+        // at most 1 + 5 phases per layer
+        rc = dev_alloc(dec, (void**)&dec->p_ops, (size_t)(1 + 5 * dec->n_layers) * sizeof(POp));
+        if (rc) return rc;
+        char* sync_words = nullptr;
+        rc = dev_alloc(dec, (void**)&sync_words, 256);
+        if (rc) return rc;
+        dec->pa_bar = reinterpret_cast<unsigned long long*>(sync_words);
+        dec->pa_done = reinterpret_cast<unsigned int*>(sync_words + 64);
+        dec->pa_flag = reinterpret_cast<unsigned int*>(sync_words + 128);
+        dec->pa_rt = reinterpret_cast<unsigned int*>(sync_words + 192);
+        rc = dev_alloc(dec, (void**)&dec->pa_bcd, (size_t)(2 * dec->mds + dec->mh + 8) * 4);
+        if (rc) return rc;
+        rc = dev_alloc(dec, (void**)&dec->pa_partials, (size_t)num_sms() * 8);
+        if (rc) return rc;
+        rc = dev_alloc(dec, (void**)&dec->pa_shout, (size_t)dec->d * 4);
+        if (rc) return rc;
+    }
+    B200_CUDA(cudaMemcpy(dec->p_layers, layers.data(), layers.size() * sizeof(PLayer), cudaMemcpyHostToDevice));
+    B200_CUDA(cudaMemcpy(dec->p_ops, ops.data(), ops.size() * sizeof(POp), cudaMemcpyHostToDevice));
+    a.layers = dec->p_layers; a.ops = dec->p_ops;
+    a.embed = dec->embed; a.len = dec->len; a.pos = dec->pos;
+    a.x = dec->x; a.bcd = dec->pa_bcd; a.u = dec->f_u; a.partials = dec->pa_partials; a.logits = dec->f_logits;
+    a.sh_act = dec->f_shact; a.sh_out = dec->pa_shout; a.act = dec->f_act;
+    a.bar = dec->pa_bar; a.done = dec->pa_done; a.bc_flag = dec->pa_flag; a.rt_flag = dec->pa_rt;
+    a.status = stream_status_ptr();
+    B200_REQUIRE(a.status, "decoder_configure: status word allocation failed");
+    a.spin_limit = dec->test_spin_limit ? dec->test_spin_limit : (1u << 22);
+    a.skip_cta = dec->test_skip_cta;
+    dec->p_ready = true;
+    return B200_OK;
+}
+
+static int enqueue_step_persistent(b200_decoder* dec, const int32_t* tokens, int32_t* next) {
+    B200_REQUIRE(dec->p_ready, "decoder_step: persistent mode not configured");
+    const int kind = tag_of_qkind(dec->qkind);
+    cudaStream_t st = stream();
+    int rc;
+    for (const b200_decoder::Segment& sg : dec->segments) {
+        PArgs a = dec->pa;
+        a.tok = tokens;
+        a.op_begin = sg.op_begin;
+        a.op_end = sg.op_end;
+        rc = persist_launch(a, kind);
+        if (rc) return rc;
+        if (sg.attn_layer >= 0) {
+            rc = enqueue_attention_fused(dec, dec->L[sg.attn_layer], kind, false);
+            if (rc) return rc;
+        }
+    }
+    SgArgs h;
+    h.w = reinterpret_cast<const uint8_t*>(dec->lm_head); h.N = dec->vocab; h.K = dec->d; h.M = 1; h.x = dec->x;
+    h.x_stride = dec->d; h.eps = dec->eps;
+    h.norm_w = dec->final_norm; h.y = dec->logits; h.y_stride = dec->vocab; h.out_scale = 1.0f / dec->logits_scaling;
+    rc = stream_gemv(h, KIND_F16, PRO_RMS, EPI_STORE);
+    if (rc) return rc;
+    argmax_rows_kernel<<<1, 1024, 0, st>>>(dec->logits, dec->vocab, next);
+    B200_LAUNCH_CHECK("argmax_rows_kernel");
+    return B200_OK;
+}
+
 static int enqueue(b200_decoder* dec, const int32_t* tokens, int32_t* next) {
+    if (dec->fused == 2) return enqueue_step_persistent(dec, tokens, next);
     if (dec->fused && dec->batch <= 8) return enqueue_step_fused(dec, tokens, next);
     return enqueue_step(dec, tokens, next);
 }
@@ -603,6 +785,8 @@ int b200_decoder_destroy(b200_decoder* dec) {
 int b200_decoder_set_tensor(b200_decoder* dec, int layer, int id, const void* p) {
     B200_REQUIRE(dec, "decoder_set_tensor: null handle");
     drop_graph(dec);
+    if (dec->fused == 2) dec->fused = 0;        // the layer table on the device is stale: configure again
+    dec->p_ready = false;
     if (layer < 0) {
         switch (id) {
             case B200_T_EMBED: dec->embed = static_cast<const uint16_t*>(p); return B200_OK;
@@ -661,14 +845,18 @@ int b200_decoder_reset(b200_decoder* dec) {
 
 int b200_decoder_configure(b200_decoder* dec, int fused, int use_graph) {
     B200_REQUIRE(dec, "decoder_configure: null handle");
+    B200_REQUIRE(fused >= 0 && fused <= 2, "decoder_configure: fused must be 0, 1 or 2");
     drop_graph(dec);
-    if (fused && dec->batch <= 8) {
+    if (fused == 2) {
+        const int rc = build_persistent(dec);
+        if (rc) return rc;
+    } else if (fused && dec->batch <= 8) {
         // every matrix of the model must fit the streaming kernels' tiling: say so now,
         // not in the middle of a step
         const int rc = enqueue_step_fused(dec, nullptr, nullptr, true);
         if (rc) return rc;
     }
-    dec->fused = fused ? 1 : 0;
+    dec->fused = fused;
     dec->use_graph = use_graph ? 1 : 0;
     dec->launches = 0;
     return B200_OK;
@@ -686,6 +874,12 @@ int b200_decoder_step(b200_decoder* dec, const int32_t* tokens_dev, int32_t* nex
         if (rc) return rc;
         dec->position += 1;
         return B200_OK;
+    }
+    // A captured step holds the addresses of the library's workspaces: once one of them
+    // has been reallocated or released the recording is stale.
+    if (dec->graph && dec->ws_generation != workspace_generation()) {
+        drop_graph(dec);
+        dec->launches = 0;          // one eager step first: it sizes the workspaces again
     }
     if (!dec->graph || dec->graph_tok != tokens_dev || dec->graph_next != next_dev) {
         drop_graph(dec);
@@ -719,6 +913,7 @@ int b200_decoder_step(b200_decoder* dec, const int32_t* tokens_dev, int32_t* nex
         if (e != cudaSuccess) return cuda_status(e, "decoder_step: cudaGraphInstantiate");
         dec->graph_tok = tokens_dev;
         dec->graph_next = next_dev;
+        dec->ws_generation = workspace_generation();
     }
     B200_CUDA(cudaGraphLaunch(dec->graph, stream()));
     dec->position += 1;
@@ -753,7 +948,42 @@ int b200_decoder_prefill(b200_decoder* dec, const int32_t* tokens_dev, int T, in
     B200_REQUIRE(dec->batch <= 65535 && T <= 65535, "decoder_prefill: batch and T must be <= 65535");
     rc = prefill(dec, tokens_dev, T, next_dev);
     if (rc) return rc;
+    if (dec->graph && dec->ws_generation != workspace_generation()) {
+        drop_graph(dec);
+        dec->launches = 0;
+    }
     dec->position = T;
+    return B200_OK;
+}
+
+int b200_decoder_test_barrier(b200_decoder* dec, int spin_limit, int skip_cta) {
+    B200_REQUIRE(dec && spin_limit >= 0, "decoder_test_barrier: bad arguments");
+    drop_graph(dec);
+    dec->test_spin_limit = (unsigned)spin_limit;
+    dec->test_skip_cta = skip_cta;
+    dec->pa.spin_limit = spin_limit ? (unsigned)spin_limit : (1u << 22);
+    dec->pa.skip_cta = skip_cta;
+    return B200_OK;
+}
+
+int b200_decoder_phase_trace(b200_decoder* dec, int cta, uint64_t* stamps_host, int cap, int* n_phases) {
+    B200_REQUIRE(dec && dec->p_ready, "decoder_phase_trace: the persistent mode is not configured");
+    const int n_ops = dec->segments.empty() ? 0 : dec->segments.back().op_end;
+    if (n_phases) *n_phases = n_ops;
+    if (!stamps_host) {
+        // arm (cta >= 0) or disarm (cta < 0) the timers
+        drop_graph(dec);
+        if (cta >= 0 && !dec->pa_trace) {
+            int rc = dev_alloc(dec, (void**)&dec->pa_trace, (size_t)n_ops * PS_TRACE_SLOTS * 8);
+            if (rc) return rc;
+        }
+        dec->pa.trace = cta >= 0 ? dec->pa_trace : nullptr;
+        dec->pa.trace_cta = cta >= 0 ? cta : 0;
+        return B200_OK;
+    }
+    B200_REQUIRE(dec->pa_trace && cap >= n_ops * PS_TRACE_SLOTS, "decoder_phase_trace: timers not armed or buffer too small");
+    B200_CUDA(cudaStreamSynchronize(stream()));
+    B200_CUDA(cudaMemcpy(stamps_host, dec->pa_trace, (size_t)n_ops * PS_TRACE_SLOTS * 8, cudaMemcpyDeviceToHost));
     return B200_OK;
 }
 

@@ -11,8 +11,16 @@ model.npz  a two-layer hybrid model (Mamba-2 layer + GQA layer, MoE after each) 
            logits the reference's Model + Generator produced for each token on its
            CPU device from the same fp32 source weights.
 
-The fixtures are read by tests/test_golden.py; nothing at test time needs the
-reference sources.
+config1.npz  (`python tests/golden/make_golden.py config1`, about twenty minutes of CPU)
+           the 8-layer Q8_0 hybrid model of CONFIG_1 at its full vocabulary of 32768,
+           weights from random_f32_params(CONFIG_1, seed 0): a 128-token prompt (uniform
+           ids, seed 1) followed by 128 greedy steps of the reference's Model + Generator
+           on its CPU device.  Stored per step: the token fed, the arg-max, the ids and
+           values of the eight largest logits, and mean / max |logit| (the weights are
+           regenerated from the seed at test time, so the file stays a few KB).
+
+The fixtures are read by tests/test_golden.py and tests/test_gpu_golden_model.py; nothing
+at test time needs the reference sources.
 """
 import os
 import sys
@@ -63,7 +71,42 @@ def make_model(oracle):
     return out
 
 
+CONFIG1_PROMPT, CONFIG1_STEPS, CONFIG1_TOP = 128, 128, 8
+
+
+def make_config1():
+    from model_util import CONFIG_1
+    cfg = CONFIG_1
+    params = random_f32_params(cfg, seed=0)
+    total = CONFIG1_PROMPT + CONFIG1_STEPS
+    gen = RefGenerator(cfg, params, max_ctx=total + 1)
+    prompt = np.random.default_rng(1).integers(0, cfg["vocab"], CONFIG1_PROMPT)
+    fed = np.zeros(total, np.int32)
+    arg = np.zeros(total, np.int32)
+    top_i = np.zeros((total, CONFIG1_TOP), np.int32)
+    top_v = np.zeros((total, CONFIG1_TOP), np.float32)
+    stats = np.zeros((total, 2), np.float32)
+    tok = int(prompt[0])
+    for s in range(total):
+        logits = gen.step(tok)
+        fed[s] = tok
+        order = np.argsort(-logits, kind="stable")[:CONFIG1_TOP]
+        top_i[s], top_v[s] = order, logits[order]
+        arg[s] = order[0]
+        stats[s] = (np.abs(logits).mean(), np.abs(logits).max())
+        tok = int(prompt[s + 1]) if s + 1 < CONFIG1_PROMPT else int(arg[s])
+        if s % 16 == 0:
+            print("config1 step", s, flush=True)
+    gen.close()
+    return dict(fed=fed, argmax=arg, top_ids=top_i, top_vals=top_v, stats=stats,
+                prompt_len=np.int32(CONFIG1_PROMPT))
+
+
 def main():
+    if len(sys.argv) > 1 and sys.argv[1] == "config1":
+        np.savez_compressed(os.path.join(HERE, "config1.npz"), **make_config1())
+        print("config1.npz", os.path.getsize(os.path.join(HERE, "config1.npz")), "bytes")
+        return
     oracle, ref = OracleOnly(), Ref()
     np.savez_compressed(os.path.join(HERE, "ops.npz"), **make_ops(oracle, ref))
     np.savez_compressed(os.path.join(HERE, "model.npz"), **make_model(oracle))

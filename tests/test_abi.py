@@ -54,3 +54,12 @@ def test_argument_errors_are_status_codes_not_aborts(so):
 def test_python_binding_fails_loudly_without_the_library(tmp_path):
     with pytest.raises(OSError, match="no CPU or PyTorch fallback"):
         capi.Library(str(tmp_path / "absent.so"))
+
+
+def test_value_returning_functions_do_not_raise():
+    """b200_version and the gemm toggles' getters return values, not status codes: the
+    Python binding must hand them back instead of raising on a non-zero result."""
+    lib = pkg.lib()
+    assert lib.b200_version() == 100
+    assert lib.b200_fp16_gemm_enabled() in (0, 1)
+    assert "b200_version" in capi.VALUE_RETURNING

@@ -52,6 +52,100 @@ def test_tiny_model_fused_teacher_forced(oracle, graph):
     assert worst < 2e-3
 
 
+@pytest.mark.parametrize("graph", [0, 1])
+def test_tiny_model_persistent_teacher_forced(oracle, graph):
+    """Persistent step kernel (fused = 2): Mamba and MoE phases of the token in one
+    cooperative launch per run of layers, grid barriers between the phases."""
+    rate, worst, _ = _teacher_forced(oracle, TINY, steps=24, graph=graph, fused=2)
+    assert rate >= 0.99, f"greedy agreement {rate:.3f}"
+    assert worst < 2e-3
+
+
+def test_config1_persistent_teacher_forced(oracle):
+    cfg = dict(CONFIG_1, vocab=4096)
+    rate, worst, margins = _teacher_forced(oracle, cfg, steps=32, graph=1, fused=2)
+    assert rate >= 0.99, f"greedy agreement {rate:.3f} (min top-2 margin {min(margins):.2e})"
+    assert worst < 2e-3
+
+
+def test_persistent_equals_fused_bitwise_stable(oracle):
+    """Two runs of the persistent step give identical bits (fixed summation orders, no
+    atomics on data), and it stays within summation-order distance of the fused mode."""
+    model = make_model(oracle, TINY, 9)
+    toks = [3, 77, 5, 400, 12, 12, 9, 250]
+    runs = []
+    for fused in (2, 2, 1):
+        dec = CudaDecoder(model, batch=1, max_ctx=16)
+        dec.configure(fused, 0)
+        out = []
+        for t in toks:
+            dec.step_host([t])
+            out.append(dec.logits()[0].copy())
+        runs.append(np.stack(out))
+        dec.close()
+    assert np.array_equal(runs[0].view(np.uint32), runs[1].view(np.uint32))
+    np.testing.assert_allclose(runs[0], runs[2], rtol=1e-3, atol=1e-4)
+
+
+def test_persistent_barrier_timeout_reports_and_recovers(oracle):
+    """A grid barrier one CTA never reaches: the other CTAs' bounded waits run out, the
+    kernel returns, the step reports B200_ECUDA - and after a reset the decoder works."""
+    from gpu_util import B200Error
+    model = make_model(oracle, TINY, 2)
+    dec = CudaDecoder(model, batch=1, max_ctx=16)
+    dec.configure(2, 0)
+    dec.step_host([1])
+    dec.lib.b200_decoder_test_barrier(dec.handle, 20000, 3)
+    with pytest.raises(B200Error, match="bounded wait"):
+        dec.step_host([2])
+    dec.lib.b200_decoder_test_barrier(dec.handle, 0, -1)
+    assert dec.lib.raw("b200_stream_status") == 0
+    dec.reset()
+    ora = OracleDecoder(oracle, model, max_ctx=16)
+    for t in (1, 2, 3):
+        want = ora.step(t)
+        dec.step_host([t])
+        np.testing.assert_allclose(dec.logits()[0], want, rtol=1e-3, atol=1e-4)
+    dec.close()
+
+
+def test_persistent_needs_batch_one(oracle):
+    from gpu_util import B200Error
+    model = make_model(oracle, TINY, 2)
+    dec = CudaDecoder(model, batch=2, max_ctx=8)
+    with pytest.raises(B200Error, match="batch 1"):
+        dec.configure(2, 0)
+    dec.close()
+
+
+@pytest.mark.parametrize("fused", [0, 1, 2])
+def test_graph_is_recaptured_after_workspaces_move(oracle, fused):
+    """Steps replayed from a captured graph, then a longer prefill that makes the library's
+    workspaces grow (their old addresses are freed), then steps again: the stale recording
+    must not be replayed.  Compared with the same sequence run without graphs."""
+    model = make_model(oracle, TINY, 6)
+    r = np.random.default_rng(8)
+    first, second = r.integers(0, TINY["vocab"], 40), r.integers(0, TINY["vocab"], 200)
+    tail = r.integers(0, TINY["vocab"], 4)
+    outs = []
+    for graph in (0, 1):
+        dec = CudaDecoder(model, batch=1, max_ctx=256)
+        dec.configure(fused, graph)
+        got = []
+        dec.prefill(first[None])
+        for t in tail:
+            dec.step_host([t])
+            got.append(dec.logits()[0].copy())
+        dec.reset()
+        dec.prefill(second[None])           # grows the prefill / GEMM / attention workspaces
+        for t in tail:
+            dec.step_host([t])
+            got.append(dec.logits()[0].copy())
+        outs.append(np.stack(got))
+        dec.close()
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+
+
 def test_config1_fused_teacher_forced(oracle):
     cfg = dict(CONFIG_1, vocab=4096)
     rate, worst, margins = _teacher_forced(oracle, cfg, steps=32, graph=1, fused=1)
