@@ -87,6 +87,15 @@ int b200_decoder_prefill(b200_decoder* dec, const int32_t* tokens_dev, int T, in
 /* Same through host buffers: H2D of the token ids, the step, D2H of the picks,
  * then a stream synchronise (what Generator::decode_step + ops::argmax_token do). */
 int b200_decoder_step_host(b200_decoder* dec, const int32_t* tokens_host, int32_t* next_host);
+/* Which position RoPE rotates by.  as_reference = 0 (default): the token's position in its
+ * sequence.  as_reference = 1: what Generator::decode_step_logits does
+ * (inference/generator.cpp:340-345): it uploads the position only while processing layer 0
+ * and only if that layer is an attention layer, so on a hybrid model whose first layer is a
+ * Mamba layer every token is rotated by the same never-refreshed word; a common rotation
+ * leaves every q.k unchanged, so this mode applies no rotation on such models (and is the
+ * default behaviour on all others).  Needed to reproduce the reference's own outputs on the
+ * RoPE hybrid of the benchmark's first configuration; Granite-4.0-H itself has no RoPE. */
+int b200_decoder_set_rope_refresh(b200_decoder* dec, int as_reference);
 /* Diagnostic hook for the bounded grid barrier of the persistent step (fused = 2):
  * spin_limit > 0 replaces the iteration bound of its global-memory waits (0 restores the
  * default), skip_cta >= 0 makes that CTA leave at its first barrier without arriving (-1:

@@ -114,6 +114,7 @@ struct b200_decoder {
     int32_t *tok = nullptr, *next = nullptr, *len = nullptr, *pos = nullptr, *page_table = nullptr;
     int position = 0;
     int fused = 0, use_graph = 0;
+    int rope_refresh_as_reference = 0;
     cudaGraphExec_t graph = nullptr;
     const int32_t* graph_tok = nullptr;
     int32_t* graph_next = nullptr;
@@ -143,6 +144,12 @@ struct b200_decoder {
     int test_skip_cta = -1;
     unsigned long long ws_generation = 0;      // workspace generation the captured graph was recorded at
 };
+
+// RoPE is applied unless the decoder mirrors the reference Generator's handling of the
+// position word (b200_decoder_set_rope_refresh) on a model whose first layer is a Mamba layer.
+static bool rope_on(const b200_decoder* dec) {
+    return dec->rope_type >= 0 && !(dec->rope_refresh_as_reference && !dec->types.empty() && dec->types[0] == 0);
+}
 
 static int dev_alloc(b200_decoder* dec, void** p, size_t bytes) {
     B200_CUDA(cudaMalloc(p, bytes ? bytes : 4));
@@ -191,7 +198,7 @@ static int enqueue_step(b200_decoder* dec, const int32_t* tokens, int32_t* next)
                 STEP(b200_linear_forward_fp16(dec->xb, static_cast<const uint16_t*>(w.wk), dec->k, B, d, kvd));
                 STEP(b200_linear_forward_fp16(dec->xb, static_cast<const uint16_t*>(w.wv), dec->v, B, d, kvd));
             }
-            if (dec->rope_type >= 0)
+            if (rope_on(dec))
                 STEP(b200_rope_forward_cached(dec->q, dec->k, dec->pos, dec->inv_freq, B, dec->H, dec->KV, dec->hd,
                                               dec->rope_type));
             kv_append_kernel<<<dim3(ceil_div(kvd, 256), B), 256, 0, st>>>(dec->k, dec->v, w.k_pages, w.v_pages,
@@ -282,7 +289,7 @@ static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t*
             aq.w3 = static_cast<const uint8_t*>(w.wv); aq.N3 = kvd; aq.y3 = dec->v; aq.y3_stride = kvd;
             STEP(stream_gemv(aq, kind, PRO_RMS, EPI_STORE));
             if (!dry) {
-                if (dec->rope_type >= 0)
+                if (rope_on(dec))
                     STEP(b200_rope_forward_cached(dec->q, dec->k, dec->pos, dec->inv_freq, B, dec->H, dec->KV, dec->hd,
                                                   dec->rope_type));
                 kv_append_kernel<<<dim3(ceil_div(kvd, 256), B), 256, 0, st>>>(dec->k, dec->v, w.k_pages, w.v_pages,
@@ -431,7 +438,7 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
     const int res_grid = (int)std::min<int64_t>(ceil_div64(NT * d, 256), (int64_t)num_sms() * 16);
     STEP(b200_embedding_forward_half(tokens, dec->embed, x, NT, d, dec->vocab));
     if (dec->emb_mult != 1.0f) STEP(b200_scale_inplace(x, dec->emb_mult, NT * d));
-    if (dec->rope_type >= 0) {
+    if (rope_on(dec)) {
         prefill_pos_kernel<<<(unsigned)ceil_div64(NT, 256), 256, 0, st>>>(pos, B, T);
         B200_LAUNCH_CHECK("prefill_pos_kernel");
     }
@@ -460,7 +467,7 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
             STEP(lin(xb, w.wq, q, d, qd, want16 ? xb16 : nullptr));
             STEP(lin(xb, w.wk, k, d, kvd, want16 ? xb16 : nullptr));
             STEP(lin(xb, w.wv, v, d, kvd, want16 ? xb16 : nullptr));
-            if (dec->rope_type >= 0)
+            if (rope_on(dec))
                 STEP(b200_rope_forward_cached(q, k, pos, dec->inv_freq, NT, dec->H, dec->KV, dec->hd, dec->rope_type));
             kv_prefill_kernel<<<dim3(ceil_div(kvd, 256), T, B), 256, 0, st>>>(k, v, w.k_pages, w.v_pages, dec->page_table, T,
                                                                             dec->max_pages, dec->page, kvd);
@@ -516,7 +523,7 @@ static int enqueue_attention_fused(b200_decoder* dec, LayerW& w, int kind, bool 
     rc = stream_gemv(aq, kind, PRO_RMS, EPI_STORE);
     if (rc) return rc;
     if (!dry) {
-        if (dec->rope_type >= 0) {
+        if (rope_on(dec)) {
             rc = b200_rope_forward_cached(dec->q, dec->k, dec->pos, dec->inv_freq, B, dec->H, dec->KV, dec->hd,
                                           dec->rope_type);
             if (rc) return rc;
@@ -953,6 +960,13 @@ int b200_decoder_prefill(b200_decoder* dec, const int32_t* tokens_dev, int T, in
         dec->launches = 0;
     }
     dec->position = T;
+    return B200_OK;
+}
+
+int b200_decoder_set_rope_refresh(b200_decoder* dec, int as_reference) {
+    B200_REQUIRE(dec, "decoder_set_rope_refresh: null handle");
+    drop_graph(dec);
+    dec->rope_refresh_as_reference = as_reference ? 1 : 0;
     return B200_OK;
 }
 

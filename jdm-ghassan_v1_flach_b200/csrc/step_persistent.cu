@@ -140,10 +140,14 @@ __device__ __forceinline__ float ps_red_val(const float* red, int row) {
 // `extra` is summed over the consumer threads in the same reduction and returned.  One
 // shared, compact copy: K % 32 == 0, cnt * K <= 16 * PS_CT, 16-byte aligned rows.
 constexpr int PS_XQ = 4;
+// Every phase calls this one copy (arguments by value: nothing of the caller's goes
+// through local memory).
 template <int KIND>
-__device__ __forceinline__ double ps_stage(const float* src, int64_t stride, int cnt, const float* nw, const XAct& xa,
-                                        float eps, double* red, double extra, bool rms, bool reduce) {
-    const int K = xa.K, nq = K >> 2, total = cnt * nq;
+__device__ __noinline__ double ps_stage_impl(const float* src, int64_t stride, int cnt, const float* nw, __half* xa_hi,
+                                             __half* xa_lo, float* xa_sumx, float* xa_f32, float* xa_xs, int xa_xs_tok,
+                                             int K, float eps, double* red, double extra, bool rms, bool reduce) {
+    struct { __half *hi, *lo; float *sumx, *f32, *xs; int xs_tok; } xa = {xa_hi, xa_lo, xa_sumx, xa_f32, xa_xs, xa_xs_tok};
+    const int nq = K >> 2, total = cnt * nq;
     const int lane = threadIdx.x & 31;
     const size_t row = (size_t)(K + XH_PAD);
     float4 v[PS_XQ];
@@ -210,6 +214,12 @@ __device__ __forceinline__ double ps_stage(const float* src, int64_t stride, int
     }
     consumer_sync<PS_CW>();
     return extra;
+}
+template <int KIND>
+__device__ __forceinline__ double ps_stage(const float* src, int64_t stride, int cnt, const float* nw, const XAct& xa,
+                                           float eps, double* red, double extra, bool rms, bool reduce) {
+    return ps_stage_impl<KIND>(src, stride, cnt, nw, xa.hi, xa.lo, xa.sumx, xa.f32, xa.xs, xa.xs_tok, xa.K, eps, red, extra,
+                               rms, reduce);
 }
 
 // One causal-convolution step of a channel: window of raw inputs, oldest first, unfused
@@ -738,6 +748,75 @@ struct PConsumer {
 };
 
 // ---- producer side -----------------------------------------------------------------
+// Routing of the kernel's one token by one warp: softmax over the ne logits, K rounds of
+// arg-max, renormalised mixture weights - the arithmetic of route_finish_warp (route.cuh;
+// core/math_cpu.cpp:546-558, core/moe_cpu.cpp:85-98, 233-254) operation for operation,
+// including the sequential e = 0, 1, ... order of the softmax denominator.  Written as
+// small rolled loops over shared memory: this runs once per layer on cold instructions,
+// and on this part an instruction fetched from L2 costs tens of cycles, so the size of
+// the code, not its operation count, is what the routed experts' weights wait for.
+// s_p, s_sel: ne floats each.
+__device__ __noinline__ void ps_route_warp(const float* logits, const float* bias, int ne, int K, float* s_p,
+                                           float* s_sel, int* s_idx, float* s_w, int lane) {
+    float mx = -INFINITY;
+#pragma unroll 1
+    for (int e = lane; e < ne; e += 32) {
+        const float v = __ldcg(logits + e);
+        s_sel[e] = v;
+        mx = fmaxf(mx, v);
+    }
+    mx = warp_max(mx);
+#pragma unroll 1
+    for (int e = lane; e < ne; e += 32) s_p[e] = (float)exp((double)__fsub_rn(s_sel[e], mx));
+    __syncwarp();
+    // denominator in the order e = 0, 1, 2, ... (every lane adds the same sequence)
+    float sum = 0.0f;
+#pragma unroll 4
+    for (int e = 0; e < ne; ++e) sum = __fadd_rn(sum, s_p[e]);
+    const float inv = (sum > 1e-12f) ? __fdiv_rn(1.0f, sum) : 0.0f;
+    __syncwarp();
+#pragma unroll 1
+    for (int e = lane; e < ne; e += 32) {
+        const float pr = __fmul_rn(s_p[e], inv);
+        s_p[e] = pr;
+        s_sel[e] = bias ? __fadd_rn(pr, bias[e]) : pr;
+    }
+    __syncwarp();
+#pragma unroll 1
+    for (int k = 0; k < K; ++k) {
+        float bv = -1e30f;
+        int bi = -1;
+#pragma unroll 1
+        for (int e = lane; e < ne; e += 32) {
+            const float v = s_sel[e];
+            if (v > bv) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+        }
+        const int pick = bi < 0 ? 0 : bi;
+        if (lane == 0) {
+            s_idx[k] = pick;
+            s_w[k] = s_p[pick];
+            s_sel[pick] = -INFINITY;          // taken: never above the -1e30 floor again
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        float sum_w = 0.0f;
+#pragma unroll 1
+        for (int k = 0; k < K; ++k) sum_w = __fadd_rn(sum_w, s_w[k]);
+        const bool renorm = sum_w > 1e-8f;
+        const float f = renorm ? __fdiv_rn(1.0f, sum_w) : __fdiv_rn(1.0f, (float)K);
+#pragma unroll 1
+        for (int k = 0; k < K; ++k) s_w[k] = renorm ? __fmul_rn(s_w[k], f) : f;
+    }
+    __syncwarp();
+}
+
 __device__ __forceinline__ bool ps_slot(const PArgs& a, const PView& s, const PRingPos& rp, unsigned seq, uint8_t*& dst,
                                      uint64_t*& full) {
     if (seq >= (unsigned)a.n_stages && !ps_mbar_wait<true>(&s.c->empty[rp.st], rp.ph ^ 1u, s.c, a.status)) return false;
@@ -871,14 +950,20 @@ struct PProducer {
                 const int r0 = t * 16, rows = min(16, d - r0);
                 if (!one(L.sh_down + r0 * rb_sh, (uint32_t)(rows * rb_sh))) { ok = 0; break; }
             }
+            const long long t0 = clock64();
             if (ok && !ps_wait_counter(a, a.rt_flag, moe_seen * (unsigned)a.ne, s.c)) ok = 0;
+            if (a.trace && (int)blockIdx.x == a.trace_cta)
+                a.trace[(size_t)op_index * PS_TRACE_SLOTS + 6] = (unsigned long long)(clock64() - t0);
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         t = __shfl_sync(0xffffffffu, t, 0);
         if (!ok) return false;
         int* r_idx = s.c->r_idx[layer & 1];
         float* r_w = s.c->r_w[layer & 1];
-        route_finish_warp(a.logits, L.router_bias ? s.rbias : nullptr, a.ne, a.K, s.r_p, s.r_sel, r_idx, r_w, nullptr, lane);
+        const long long t1 = clock64();
+        ps_route_warp(a.logits, L.router_bias ? s.rbias : nullptr, a.ne, a.K, s.r_p, s.r_sel, r_idx, r_w, lane);
+        if (a.trace && lane == 0 && (int)blockIdx.x == a.trace_cta)
+            a.trace[(size_t)op_index * PS_TRACE_SLOTS + 7] = (unsigned long long)(clock64() - t1);
         __syncwarp();
         if (lane == 0) {
             __threadfence_block();

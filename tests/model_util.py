@@ -69,8 +69,13 @@ class OracleDecoder:
     oracle standing in for every op.  The KV cache is the reference's fp16 ring with
     no pinned prefix and ring_start 0 (a contiguous cache)."""
 
-    def __init__(self, oracle, model, max_ctx):
+    def __init__(self, oracle, model, max_ctx, rope_as_reference=False):
+        """rope_as_reference: mirror Generator::decode_step_logits' handling of the position
+        word (inference/generator.cpp:340-345: uploaded only when layer 0 is an attention
+        layer; otherwise every token is rotated by one stale angle, i.e. q.k is as without
+        rotation)."""
         self.o, self.m, self.cfg = oracle, model, model["cfg"]
+        self.rope = model["cfg"]["rope_type"] >= 0 and not (rope_as_reference and model["cfg"]["layer_types"][0] == 0)
         c = self.cfg
         self.max_ctx = max_ctx
         self.conv_dim = c["mamba_heads"] * c["mamba_d_head"] + 2 * c["mamba_d_state"]
@@ -109,7 +114,7 @@ class OracleDecoder:
                 qv = o.linear(xb[None], L["wq"], q, 1, d, H * hd)
                 kv = o.linear(xb[None], L["wk"], q, 1, d, KV * hd)
                 vv = o.linear(xb[None], L["wv"], q, 1, d, KV * hd)
-                if c["rope_type"] >= 0:
+                if self.rope:
                     qv, kv = o.rope_cached(qv.reshape(1, H, hd), kv.reshape(1, KV, hd),
                                            np.array([self.pos], np.int32), m["inv_freq"], H, KV, hd, c["rope_type"])
                 st["k"][self.pos] = o.f32_to_f16(kv.reshape(-1))
@@ -141,7 +146,7 @@ T = dict(embed=0, final_norm=1, lm_head=2, inv_freq=3, attn_norm=10, ffn_norm=11
 class CudaDecoder:
     """b200_decoder over device copies of a make_model() model."""
 
-    def __init__(self, model, batch, max_ctx, kv_page=64):
+    def __init__(self, model, batch, max_ctx, kv_page=64, rope_as_reference=False):
         from gpu_util import dev, pkg
         self.lib = pkg.lib()
         c = model["cfg"]
@@ -155,6 +160,8 @@ class CudaDecoder:
                                      c["qkind"], c["rms_eps"], c["embedding_multiplier"], c["residual_multiplier"],
                                      c["attn_scale"], c["logits_scaling"])
         self.keep = []
+        if rope_as_reference:
+            self.lib.b200_decoder_set_rope_refresh(self.handle, 1)
 
         def put(layer, name, arr):
             t = dev(arr)
