@@ -1,7 +1,7 @@
 // Host interface of the persistent decode-step kernel (step_persistent.cu): one
 // cooperative launch walks a list of layer phases for a single token with all CTAs
-// resident, a weight stream that runs on across phase boundaries, and activations that
-// pass from phase to phase as tagged words the readers poll (no grid-wide barrier).
+// resident, a weight stream that runs on across phase boundaries and bounded grid
+// barriers between the phases.
 #pragma once
 
 #include "fused.cuh"
@@ -22,7 +22,7 @@ struct PLayer {
     int pad_;
 };
 
-// Phases.  A phase's outputs carry the phase's tag; the next phase polls for them.
+// Phases.  Every phase but the last of a launch ends with a grid barrier.
 enum {
     POP_EMBED = 0,    // x = embed[token] * multiplier; position bookkeeping
     POP_MAMBA_A = 1,  // RMSNorm -> in_proj -> conv step -> state update -> gated-norm statistics
@@ -37,7 +37,7 @@ struct POp {
 
 constexpr int PS_MAX_STAGES = 8;
 constexpr int PS_TRACE_SLOTS = 8;           // phase start, activations staged, tiles done, barrier passed
-constexpr int PS_SMEM_MAX = 226 * 1024;     // dynamic shared memory of the one CTA per SM (227 KB is the limit)
+constexpr int PS_SMEM_MAX = 224 * 1024;     // dynamic shared memory of the one CTA per SM
 
 struct PArgs {
     const PLayer* layers = nullptr;
@@ -52,33 +52,30 @@ struct PArgs {
     const int32_t* tok = nullptr;
     const uint16_t* embed = nullptr;
     int32_t *len = nullptr, *pos = nullptr;
-    // residual stream as plain floats: read by the first phase of a launch, written by every
-    // phase that updates it (the kernels between two launches work on it)
-    float* x = nullptr;            // [d]
-    // Activations exchanged between phases: (value, tag) pairs written with one 8-byte
-    // store each; a reader polls until every pair it needs carries the tag of the phase
-    // that produces it - the data is its own flag, no fence and no barrier in between.
-    uint2* ll_x[2] = {nullptr, nullptr};   // [d] residual stream: [0] from the embedding / routed-down phase, [1] from out_proj
-    uint2* ll_bcd = nullptr;       // [2 * d_state + n_heads] conv'd B, C and raw dt
-    uint2* ll_u = nullptr;         // [d_inner] y * silu(gate) * norm_w
-    uint2* ll_part = nullptr;      // [2 * grid] per-CTA sum of squares of y * silu(gate), as a float pair (head, tail)
-    uint2* ll_logits = nullptr;    // [ne]
-    uint2* ll_shact = nullptr;     // [SH]
-    uint2* ll_shout = nullptr;     // [d]
-    uint2* ll_act = nullptr;       // [K, E]
-    uint2* ll_hb = nullptr;        // [grid] per CTA: tag of the last phase whose inputs it has finished reading
-    unsigned int* epoch = nullptr; // tags handed out so far (advanced by the last CTA out of a launch)
-    unsigned int* done = nullptr;  // CTAs that left the kernel
+    // activations exchanged between phases (global memory, L2 resident)
+    float* x = nullptr;            // [d] residual stream
+    float* bcd = nullptr;          // [2 * d_state + n_heads] conv'd B, C and raw dt
+    float* u = nullptr;            // [d_inner] y * silu(gate) * norm_w
+    double* partials = nullptr;    // [grid] sum of squares of y * silu(gate) per CTA
+    float* logits = nullptr;       // [ne]
+    float* sh_act = nullptr;       // [SH]
+    float* sh_out = nullptr;       // [d]
+    float* act = nullptr;          // [K, E]
+    // synchronisation words (zero between launches)
+    unsigned long long* bar = nullptr;   // grid-barrier arrivals
+    unsigned int* done = nullptr;        // CTAs that left the kernel
+    unsigned int* bc_flag = nullptr;     // B/C/dt tiles finished
+    unsigned int* rt_flag = nullptr;     // router logits published (one count per expert and layer)
     int* status = nullptr;               // 0 = ok, 1 = a bounded wait ran out
     unsigned int spin_limit = 1u << 22;  // iterations of a global-memory wait
-    int skip_cta = -1;                   // test hook: this CTA leaves at once, so its tagged words never appear
+    int skip_cta = -1;                   // test hook: this CTA leaves at its first barrier without arriving
     // optional phase timers: [n_ops][PS_TRACE_SLOTS] globaltimer stamps written by CTA trace_cta
     unsigned long long* trace = nullptr;
     int trace_cta = 0;
     // shared-memory plan (bytes from the start of dynamic shared memory)
     int stage_bytes = 0, n_stages = 0;
     int off_xa1 = 0, off_xa2 = 0, off_xa3 = 0, off_nw = 0, off_gs = 0, off_red = 0, off_route = 0, off_bcd = 0,
-        off_xraw = 0, off_prog = 0, off_ctl = 0, smem_bytes = 0;
+        off_prog = 0, off_ctl = 0, smem_bytes = 0;
 };
 
 // Fills the shared-memory plan for `kind` (template tag) and checks that every phase's

@@ -135,8 +135,10 @@ struct b200_decoder {
     struct Segment { int op_begin, op_end, attn_layer; };
     std::vector<Segment> segments;
     bool p_ready = false;
-    char* pa_words = nullptr;                  // tag counter, exit counter and the tagged-word buffers
-    char* pa_ll[10] = {};
+    unsigned long long* pa_bar = nullptr;
+    unsigned int *pa_done = nullptr, *pa_flag = nullptr, *pa_rt = nullptr;
+    float *pa_bcd = nullptr, *pa_shout = nullptr;
+    double* pa_partials = nullptr;
     unsigned long long* pa_trace = nullptr;
     unsigned int test_spin_limit = 0;          // test hook (b200_decoder_test_barrier)
     int test_skip_cta = -1;
@@ -605,31 +607,27 @@ static int build_persistent(b200_decoder* dec) {
         // at most 1 + 5 phases per layer
         rc = dev_alloc(dec, (void**)&dec->p_ops, (size_t)(1 + 5 * dec->n_layers) * sizeof(POp));
         if (rc) return rc;
-        // tagged-word buffers (zero = no valid tag) and the two counters, in one allocation
-        const size_t n_x = (size_t)dec->d, n_bcd = (size_t)2 * dec->mds + dec->mh, n_u = (size_t)dec->d_inner,
-                     n_part = (size_t)2 * num_sms(), n_log = (size_t)dec->ne, n_sha = (size_t)std::max(dec->SH, 1),
-                     n_act = (size_t)dec->K * dec->E, n_hb = (size_t)num_sms();
-        size_t off = 256;
-        auto take = [&](size_t words) { const size_t o = off; off += (words * 8 + 255) / 256 * 256; return o; };
-        const size_t o_x0 = take(n_x), o_x1 = take(n_x), o_bcd = take(n_bcd), o_u = take(n_u), o_part = take(n_part),
-                     o_log = take(n_log), o_sha = take(n_sha), o_sho = take(n_x), o_act = take(n_act), o_hb = take(n_hb);
-        rc = dev_alloc(dec, (void**)&dec->pa_words, off);
+        char* sync_words = nullptr;
+        rc = dev_alloc(dec, (void**)&sync_words, 256);
         if (rc) return rc;
-        char* w = dec->pa_words;
-        dec->pa_ll[0] = w + o_x0; dec->pa_ll[1] = w + o_x1; dec->pa_ll[2] = w + o_bcd; dec->pa_ll[3] = w + o_u;
-        dec->pa_ll[4] = w + o_part; dec->pa_ll[5] = w + o_log; dec->pa_ll[6] = w + o_sha; dec->pa_ll[7] = w + o_sho;
-        dec->pa_ll[8] = w + o_act; dec->pa_ll[9] = w + o_hb;
+        dec->pa_bar = reinterpret_cast<unsigned long long*>(sync_words);
+        dec->pa_done = reinterpret_cast<unsigned int*>(sync_words + 64);
+        dec->pa_flag = reinterpret_cast<unsigned int*>(sync_words + 128);
+        dec->pa_rt = reinterpret_cast<unsigned int*>(sync_words + 192);
+        rc = dev_alloc(dec, (void**)&dec->pa_bcd, (size_t)(2 * dec->mds + dec->mh + 8) * 4);
+        if (rc) return rc;
+        rc = dev_alloc(dec, (void**)&dec->pa_partials, (size_t)num_sms() * 8);
+        if (rc) return rc;
+        rc = dev_alloc(dec, (void**)&dec->pa_shout, (size_t)dec->d * 4);
+        if (rc) return rc;
     }
     B200_CUDA(cudaMemcpy(dec->p_layers, layers.data(), layers.size() * sizeof(PLayer), cudaMemcpyHostToDevice));
     B200_CUDA(cudaMemcpy(dec->p_ops, ops.data(), ops.size() * sizeof(POp), cudaMemcpyHostToDevice));
     a.layers = dec->p_layers; a.ops = dec->p_ops;
     a.embed = dec->embed; a.len = dec->len; a.pos = dec->pos;
-    a.x = dec->x;
-    auto ll = [&](int i) { return reinterpret_cast<uint2*>(dec->pa_ll[i]); };
-    a.ll_x[0] = ll(0); a.ll_x[1] = ll(1); a.ll_bcd = ll(2); a.ll_u = ll(3); a.ll_part = ll(4); a.ll_logits = ll(5);
-    a.ll_shact = ll(6); a.ll_shout = ll(7); a.ll_act = ll(8); a.ll_hb = ll(9);
-    a.epoch = reinterpret_cast<unsigned int*>(dec->pa_words);
-    a.done = reinterpret_cast<unsigned int*>(dec->pa_words + 64);
+    a.x = dec->x; a.bcd = dec->pa_bcd; a.u = dec->f_u; a.partials = dec->pa_partials; a.logits = dec->f_logits;
+    a.sh_act = dec->f_shact; a.sh_out = dec->pa_shout; a.act = dec->f_act;
+    a.bar = dec->pa_bar; a.done = dec->pa_done; a.bc_flag = dec->pa_flag; a.rt_flag = dec->pa_rt;
     a.status = stream_status_ptr();
     B200_REQUIRE(a.status, "decoder_configure: status word allocation failed");
     a.spin_limit = dec->test_spin_limit ? dec->test_spin_limit : (1u << 22);

@@ -3,26 +3,23 @@
 //
 // A token's step is a chain of ~200 dependent matrix-vector phases of 1-6 MB each.  As
 // separate launches every phase pays a launch, a cold start of its weight stream and a
-// drain.  Here all CTAs stay resident and two things never stop:
-//  * the weight stream - the producer warp of each CTA walks the phase list ahead of the
-//    consumers and keeps its shared-memory ring full across phase boundaries (weights
-//    never depend on activations; only the routed experts' tiles wait for the router, and
-//    they are requested as soon as the router's logits exist);
-//  * the activations - a phase's outputs (a few thousand floats) are written as (value,
-//    tag) pairs with one 8-byte store each, tag = the phase's number, and the next phase
-//    polls the pairs it needs until they carry that tag.  The data is its own flag: no
-//    fence, no arrival counter, no barrier - one L2 round trip from the last writer to
-//    every reader.  A per-CTA heartbeat word polled the same way keeps every CTA within
-//    one phase of the others, so a buffer is never overwritten under a reader.
+// drain.  Here all CTAs stay resident: the producer warp of each CTA walks the phase
+// list ahead of the consumers and keeps its shared-memory ring full across phase
+// boundaries (weights never depend on activations; only the routed experts' tiles wait
+// for the router, and they are requested as soon as the router's logits exist, not when
+// the phase that uses them begins), and the phases are separated by grid barriers - one
+// arrival counter in global memory, release-add + acquire-spin with an iteration bound.
 // Everything small and cold a phase needs (norm weights, per-head constants, the
-// convolution taps and window of a tile's channels) is fetched ahead.  Every poll is
-// bounded: when a bound runs out the CTA raises the status word, the others see it and
-// leave too, every producer drains its own copies, and the last CTA out advances the tag
-// counter, so the call returns with an error and the next launch starts clean.
+// convolution taps and window of a tile's channels) is fetched ahead: the per-channel
+// data rides in the tile's ring stage, the per-phase vectors are loaded while the
+// preceding barrier is being waited for.  When a bound runs out the CTA raises the
+// status word, the others see it and leave too, every producer drains its own copies,
+// and the last CTA out zeroes the counters, so the call returns with an error and the
+// next launch starts clean.
 //
 // Phase order and arithmetic: Generator::decode_step_logits / decode_mamba_layer
 // (inference/generator.cpp:221-443, :456-617) and cpu::moe_forward_bias
-// (core/moe_cpu.cpp:198-288); the dot-product engine, activation layouts and exact-order
+// (core/moe_cpu.cpp:198-288); the dot-product engine, activation staging and exact-order
 // router are those of the per-phase fused kernels (fused_common.cuh, fused_moe.cu).
 #include "fused_common.cuh"
 #include "persist.cuh"
@@ -50,7 +47,6 @@ struct PCtl {
     volatile int abort;        // a bounded wait of this CTA ran out (or the status word was seen raised)
     int snap;                  // abort as thread 0 saw it before a consumer barrier: one value for all threads
     volatile int route_gen;    // layer + 1 whose routing sits in r_idx / r_w [layer & 1]
-    unsigned tag0;             // tag of this launch's first phase
     int r_idx[2][16];
     float r_w[2][16];
     float s_gate[PS_UNIT], s_xv[PS_UNIT];
@@ -80,60 +76,6 @@ __device__ __forceinline__ void ps_stamp(const PArgs& a, int oi, int slot) {
         a.trace[(size_t)oi * PS_TRACE_SLOTS + slot] = ps_now();
 }
 
-// ---- tagged words -------------------------------------------------------------------
-__device__ __forceinline__ void ll_store(uint2* buf, int i, float v, unsigned tag) {
-    asm volatile("st.relaxed.gpu.global.v2.b32 [%0], {%1, %2};" ::"l"(buf + i), "r"(__float_as_uint(v)), "r"(tag) : "memory");
-}
-__device__ __forceinline__ uint2 ll_load1(const uint2* buf, int i) {
-    uint2 r;
-    asm volatile("ld.relaxed.gpu.global.v2.b32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(buf + i) : "memory");
-    return r;
-}
-__device__ __forceinline__ uint4 ll_load2(const uint2* buf, int i) {      // pairs i, i + 1 (i even)
-    uint4 r;
-    asm volatile("ld.relaxed.gpu.global.v4.b32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(buf + i)
-                 : "memory");
-    return r;
-}
-// Barrier of the consumer threads that also ORs a predicate over them: one result for all.
-__device__ __forceinline__ bool consumer_any(bool p) {
-    unsigned r;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.u32 p, %1, 0;\n\t"
-        "bar.red.or.pred q, 1, %2, p;\n\t"
-        "selp.u32 %0, 1, 0, q;\n\t}"
-        : "=r"(r)
-        : "r"((unsigned)p), "n"(PS_CT)
-        : "memory");
-    return r != 0;
-}
-// n tagged words of `buf` into dst[0..n) (shared memory), polled by the consumer threads
-// until they all carry `tag`.  Returns false - to every thread - when the bound ran out.
-__device__ __forceinline__ bool ll_pull(const PArgs& a, PCtl* c, const uint2* buf, int n, unsigned tag, float* dst) {
-    bool pending = false;
-    for (int i = threadIdx.x; i < n; i += PS_CT) {
-        pending = true;
-        for (unsigned it = 0; it < a.spin_limit; ++it) {
-            const uint2 w = ll_load1(buf, i);
-            if (w.y == tag) {
-                dst[i] = __uint_as_float(w.x);
-                pending = false;
-                break;
-            }
-            if ((it & 63) == 63 && ld_volatile_s32(a.status) != 0) break;
-        }
-        if (pending) break;
-    }
-    if (pending) {
-        atomicExch(a.status, 1);
-        c->abort = 1;
-    }
-    return !consumer_any(pending);
-}
-
 // Bounded mbarrier wait.  The producer lane (WATCH_ABORT) also gives up when the CTA is
 // aborting; the consumer warps do not look at that flag here: they all wait on the same
 // barrier phase, so they pass or run out together and never split at a CTA barrier.
@@ -144,6 +86,17 @@ __device__ __forceinline__ bool ps_mbar_wait(uint64_t* bar, uint32_t parity, PCt
         if (WATCH_ABORT && (it & 15) == 15 && c->abort) return false;
     }
     atomicExch(status, 1);
+    c->abort = 1;
+    return false;
+}
+
+// Bounded wait of one thread for a global counter to reach `target`.
+__device__ __forceinline__ bool ps_wait_counter(const PArgs& a, const unsigned int* ctr, unsigned target, PCtl* c) {
+    for (unsigned it = 0; it < a.spin_limit; ++it) {
+        if (ld_acquire_u32(ctr) >= target) return true;
+        if ((it & 63) == 63 && (c->abort || ld_volatile_s32(a.status) != 0)) break;
+    }
+    atomicExch(a.status, 1);
     c->abort = 1;
     return false;
 }
@@ -179,36 +132,27 @@ __device__ __forceinline__ float ps_red_val(const float* red, int row) {
     return v;
 }
 
-// Activation staging for the kernel's one token: `cnt` vectors of K floats into rows
-// 0..cnt-1 of xa - fp16 hi + lo parts and 32-wide sums for the tensor-core kinds, fp32
-// unit-major for the scalar kinds (the layouts of fused_common.cuh / mma_tile.cuh).
-// Source: tagged words ll[r * stride + k] polled until they carry `tag` (outputs of the
-// preceding phase), or plain floats src[r * stride + k] (first phase of a launch).  With
-// the tagged source the heartbeat words hb[0..nhb) are polled for hb_tag as well: every
-// CTA has then finished reading what the phase before the preceding one produced.
-// rms: v <- v * inv_rms * nw in the reference's operand order (core/math_cpu.cpp:299-316,
-// double sum of squares); reduce: `extra` is summed over the consumer threads in the same
-// reduction and returned; xraw (optional, cnt == 1): the raw vector in shared memory.
-// aux (optional): aux_n more tagged words of the same tag, polled in the same loop into
-// aux_dst (shared memory) - at most 8 * PS_CT of them; aux_pairs: the words are (head,
-// tail) pairs of a double each, summed into `extra` instead of being stored.
-// Returns -1 - to every thread - when a poll ran out of its bound.  One shared copy for all
-// phases, arguments by value; K % 32 == 0, cnt * K <= 16 * PS_CT, 16-byte aligned rows.
+// Activation staging for the kernel's one token: `cnt` vectors of K floats (src + r *
+// stride; written by other CTAs, hence L2 loads) into rows 0..cnt-1 of xa - fp16 hi + lo
+// parts and 32-wide sums for the tensor-core kinds, fp32 unit-major for the scalar kinds
+// (the layouts of fused_common.cuh / mma_tile.cuh).  rms: v <- v * inv_rms * nw in the
+// reference's operand order (core/math_cpu.cpp:299-316, double sum of squares); reduce:
+// `extra` is summed over the consumer threads in the same reduction and returned.  One
+// shared, compact copy: K % 32 == 0, cnt * K <= 16 * PS_CT, 16-byte aligned rows.
 constexpr int PS_XQ = 4;
+// Every phase calls this one copy (arguments by value: nothing of the caller's goes
+// through local memory).
 template <int KIND>
-__device__ __noinline__ double ps_stage_impl(const float* plain, const uint2* ll, unsigned tag, const uint2* hb, int nhb,
-                                             unsigned hb_tag, int64_t stride, int cnt, const float* nw, __half* xa_hi,
+__device__ __noinline__ double ps_stage_impl(const float* src, int64_t stride, int cnt, const float* nw, __half* xa_hi,
                                              __half* xa_lo, float* xa_sumx, float* xa_f32, float* xa_xs, int xa_xs_tok,
-                                             int K, float eps, double* red, double extra, bool rms, bool reduce,
-                                             float* xraw, const uint2* aux, int aux_n, float* aux_dst, bool aux_pairs,
-                                             unsigned spin_limit, int* status, PCtl* c) {
+                                             int K, float eps, double* red, double extra, bool rms, bool reduce) {
     struct { __half *hi, *lo; float *sumx, *f32, *xs; int xs_tok; } xa = {xa_hi, xa_lo, xa_sumx, xa_f32, xa_xs, xa_xs_tok};
     const int nq = K >> 2, total = cnt * nq;
     const int lane = threadIdx.x & 31;
     const size_t row = (size_t)(K + XH_PAD);
     float4 v[PS_XQ];
     int rr[PS_XQ], qq[PS_XQ];
-    unsigned need = 0;
+    double ss = 0.0;
 #pragma unroll
     for (int j = 0; j < PS_XQ; ++j) {
         const int i = j * PS_CT + (int)threadIdx.x;
@@ -216,60 +160,8 @@ __device__ __noinline__ double ps_stage_impl(const float* plain, const uint2* ll
         const int r = (ok && cnt > 1) ? i / nq : 0;
         rr[j] = r;
         qq[j] = ok ? i - r * nq : 0;
-        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (ok) {
-            if (ll) need |= 1u << j;
-            else v[j] = __ldcg(reinterpret_cast<const float4*>(plain + r * stride + 4 * qq[j]));
-        }
-    }
-    bool pending = false;
-    if (ll) {
-        bool hb_need = hb != nullptr && (int)threadIdx.x < nhb;
-        unsigned aux_need = 0;
-        for (int m = 0, idx = threadIdx.x; idx < aux_n; ++m, idx += PS_CT) aux_need |= 1u << m;
-        for (unsigned it = 0; it < spin_limit; ++it) {
-#pragma unroll
-            for (int j = 0; j < PS_XQ; ++j) {
-                if ((need >> j) & 1u) {
-                    const int at = (int)(rr[j] * stride) + 4 * qq[j];
-                    const uint4 p0 = ll_load2(ll, at), p1 = ll_load2(ll, at + 2);
-                    if (p0.y == tag && p0.w == tag && p1.y == tag && p1.w == tag) {
-                        v[j] = make_float4(__uint_as_float(p0.x), __uint_as_float(p0.z), __uint_as_float(p1.x),
-                                           __uint_as_float(p1.z));
-                        need &= ~(1u << j);
-                    }
-                }
-            }
-            if (hb_need && (int)(ll_load1(hb, threadIdx.x).y - hb_tag) >= 0) hb_need = false;   // that CTA may be a phase ahead
-            if (aux_need) {
-                // all of this thread's outstanding words are requested before any is looked at
-                uint2 w[8];
-#pragma unroll
-                for (int m = 0; m < 8; ++m)
-                    if ((aux_need >> m) & 1u) w[m] = ll_load1(aux, m * PS_CT + (int)threadIdx.x);
-#pragma unroll
-                for (int m = 0; m < 8; ++m) {
-                    if (((aux_need >> m) & 1u) && w[m].y == tag) {
-                        if (aux_pairs) extra += (double)__uint_as_float(w[m].x);
-                        else aux_dst[m * PS_CT + (int)threadIdx.x] = __uint_as_float(w[m].x);
-                        aux_need &= ~(1u << m);
-                    }
-                }
-            }
-            pending = need != 0 || hb_need || aux_need != 0;
-            if (!pending) break;
-            if ((it & 63) == 63 && ld_volatile_s32(status) != 0) break;
-        }
-        if (pending) {
-            atomicExch(status, 1);
-            c->abort = 1;
-        }
-    }
-    double ss = 0.0;
-#pragma unroll
-    for (int j = 0; j < PS_XQ; ++j) {
+        v[j] = ok ? __ldcg(reinterpret_cast<const float4*>(src + r * stride + 4 * qq[j])) : make_float4(0.f, 0.f, 0.f, 0.f);
         if (rms) ss += (double)v[j].x * v[j].x + (double)v[j].y * v[j].y + (double)v[j].z * v[j].z + (double)v[j].w * v[j].w;
-        if (xraw && j * PS_CT + (int)threadIdx.x < total) *reinterpret_cast<float4*>(xraw + 4 * qq[j]) = v[j];
     }
     float inv = 1.0f;
     if (rms || reduce) {
@@ -320,7 +212,14 @@ __device__ __noinline__ double ps_stage_impl(const float* plain, const uint2* ll
             }
         }
     }
-    return consumer_any(pending) ? -1.0 : extra;
+    consumer_sync<PS_CW>();
+    return extra;
+}
+template <int KIND>
+__device__ __forceinline__ double ps_stage(const float* src, int64_t stride, int cnt, const float* nw, const XAct& xa,
+                                           float eps, double* red, double extra, bool rms, bool reduce) {
+    return ps_stage_impl<KIND>(src, stride, cnt, nw, xa.hi, xa.lo, xa.sumx, xa.f32, xa.xs, xa.xs_tok, xa.K, eps, red, extra,
+                               rms, reduce);
 }
 
 // One causal-convolution step of a channel: window of raw inputs, oldest first, unfused
@@ -360,8 +259,6 @@ struct PView {          // this CTA's shared memory, carved by the host's plan
     XAct xa1, xa2, xa3;
     uint8_t* xa2_base;
     float *nw, *gs, *red, *r_p, *r_sel, *bcd, *hp, *rbias;
-    float* xraw;            // [d] the residual stream as last staged (the phases that add to it read it here)
-    unsigned tag0;          // tag of this launch's phase i is tag0 + i
     const POp* ops;         // [op_end - op_begin]
     const PLayer* layers;   // [n_layers]
     PCtl* c;
@@ -444,23 +341,16 @@ __device__ __forceinline__ PTileExtra ps_bc_extra(const PArgs& a, int rb) {
 }
 
 // ---- consumer side of each phase ---------------------------------------------------
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
 template <int KIND>
 struct PConsumer {
     const PArgs& a;
     PView& s;
     int warp, lane;
     PRingPos rp;                 // next tile to take from the ring
+    unsigned mamba_seen = 0;     // POP_MAMBA_A phases finished in this launch
     int cur_op = 0;              // phase index, for the phase timers
-    long long wait_cyc = 0, rows_cyc = 0;    // phase timers: cycles spent waiting for tiles / in the dot routine
 
+    long long wait_cyc = 0, rows_cyc = 0;    // phase timers: cycles spent waiting for tiles / in the dot routine
     __device__ __forceinline__ const uint8_t* take(bool& ok) {
         const long long t0 = a.trace ? clock64() : 0;
         const uint8_t* p = ps_take(a, s, rp, ok);
@@ -489,48 +379,30 @@ struct PConsumer {
         return ps_silu(v) * u;
     }
 
-    // Static vectors the phase `op` will want (norm weights, per-head constants): requested
-    // with asynchronous copies one phase ahead, collected by staged() of that phase.
-    __device__ __forceinline__ void prefetch(const POp op) {
+    // Loads that do not depend on the phases before `op`: issued by the warps that do not
+    // run the grid barrier while it is being waited for (or by all before the first phase).
+    __device__ __forceinline__ void prefetch(const POp op, int first_thread) {
         if (op.op != POP_MAMBA_A && op.op != POP_MOE_C) return;
         const PLayer& L = s.layers[op.layer];
+        const int nt = PS_CT - first_thread, t0 = (int)threadIdx.x - first_thread;
+        if (t0 < 0) return;
         const float* nw = op.op == POP_MAMBA_A ? L.attn_norm : L.ffn_norm;
-        for (int k = threadIdx.x * 4; k < a.d; k += PS_CT * 4) cp_async16(s.nw + k, nw + k);
+        for (int k = t0 * 4; k < a.d; k += nt * 4)
+            *reinterpret_cast<float4*>(s.nw + k) = __ldg(reinterpret_cast<const float4*>(nw + k));
         if (op.op == POP_MAMBA_A)
-            for (int h = threadIdx.x; h < a.n_heads; h += PS_CT) {
-                cp_async4(s.hp + h, L.dt_bias + h);
-                cp_async4(s.hp + a.n_heads + h, L.a_log + h);
-                cp_async4(s.hp + 2 * a.n_heads + h, L.D + h);
+            for (int h = t0; h < a.n_heads; h += nt) {
+                s.hp[h] = L.dt_bias[h];
+                s.hp[a.n_heads + h] = L.a_log[h];
+                s.hp[2 * a.n_heads + h] = L.D[h];
             }
     }
 
-    // The phase's activations into shared memory.  i: index of the phase in this launch;
-    // ll: the tagged words the preceding phase wrote (phase 0 of a launch reads `plain`).
-    // Afterwards this CTA's heartbeat says that it is done with everything older.
-    __device__ __forceinline__ double staged(int i, const float* plain, const uint2* ll, int64_t stride, int cnt,
-                                             const float* nw, const XAct& xa, double extra, bool rms, bool reduce,
-                                             float* xraw, const uint2* aux = nullptr, int aux_n = 0,
-                                             float* aux_dst = nullptr, bool aux_pairs = false) {
-        if (rms) cp_async_wait_all();
-        const bool first = i == 0;
-        const double r = ps_stage_impl<KIND>(plain, first ? nullptr : ll, s.tag0 + i - 1, i >= 2 ? a.ll_hb : nullptr,
-                                             (int)gridDim.x, s.tag0 + i - 1, stride, cnt, nw, xa.hi, xa.lo, xa.sumx, xa.f32,
-                                             xa.xs, xa.xs_tok, xa.K, a.eps, s.c->red_d, extra, rms, reduce, xraw,
-                                             first ? nullptr : aux, first ? 0 : aux_n, aux_dst, aux_pairs, a.spin_limit,
-                                             a.status, s.c);
-        if (threadIdx.x == 0) ll_store(a.ll_hb, blockIdx.x, 0.0f, s.tag0 + i);
-        return r;
-    }
-
-    __device__ bool embed(int i) {
-        const unsigned tag = s.tag0 + i;
-        if (threadIdx.x == 0) ll_store(a.ll_hb, blockIdx.x, 0.0f, tag);
+    __device__ bool embed() {
         const int64_t tok = a.tok[0];
-        for (int k = blockIdx.x * PS_CT + threadIdx.x; k < a.d; k += gridDim.x * PS_CT) {
-            float v = half_bits_to_float(a.embed[tok * a.d + k]);
+        for (int i = blockIdx.x * PS_CT + threadIdx.x; i < a.d; i += gridDim.x * PS_CT) {
+            float v = half_bits_to_float(a.embed[tok * a.d + i]);
             if (a.emb_mult != 1.0f) v *= a.emb_mult;
-            a.x[k] = v;
-            ll_store(a.ll_x[0], k, v, tag);
+            a.x[i] = v;
         }
         if (blockIdx.x == 0 && threadIdx.x == 0) {
             const int p = a.len[0];
@@ -554,11 +426,10 @@ struct PConsumer {
         bias = has_bias ? reinterpret_cast<const float*>(ts + e.bias)[i] : 0.0f;
     }
 
-    __device__ bool mamba_a(const PLayer& L, int i, int op_index) {
+    __device__ bool mamba_a(const PLayer& L, int op_index) {
         const int d = a.d, ds = a.d_state, nh = a.n_heads, k = a.dconv, win = k - 1;
         const int rb = (int)row_bytes_of(KIND, d);
-        const unsigned tag = s.tag0 + i;
-        if (staged(i, a.x, a.ll_x[0], 0, 1, s.nw, s.xa1, 0.0, true, false, s.xraw) < 0.0) return false;
+        ps_stage<KIND>(a.x, 0, 1, s.nw, s.xa1, a.eps, s.c->red_d, 0.0, true, false);
         ps_stamp(a, cur_op, 1);
         const int nbc = ps_mamba_bc_tiles(a), nconv_tiles = (2 * ds) / 16, ntiles = nbc + a.d_inner / PS_UNIT;
         const int ns = ds >> 5;                              // state elements per lane
@@ -569,7 +440,7 @@ struct PConsumer {
             const uint8_t* ts = take(ok);
             if (!ok) return false;
             if (t < nbc) {
-                // rows of B, C (one convolution step each) or dt
+                // rows of B, C (convolved below) or dt
                 const int r0 = 2 * a.d_inner + t * 16, nrows = min(16, a.proj - r0);
                 const bool conv_tile = t < nconv_tiles;
                 float tp[8], sw[8], bias = 0.0f;
@@ -579,13 +450,21 @@ struct PConsumer {
                     if (conv_tile) {
                         const int c = r0 - a.d_inner + (int)threadIdx.x;       // convolution channel
                         const float pre = ps_conv_step(k, tp, sw, bias, L.conv_state + (int64_t)c * win, wv);
-                        ll_store(a.ll_bcd, c - a.d_inner, ps_silu(pre), tag);
+                        a.bcd[c - a.d_inner] = ps_silu(pre);
                     } else {
-                        ll_store(a.ll_bcd, 2 * ds + (r0 + (int)threadIdx.x - a.d_inner - a.conv_dim), wv, tag);
+                        a.bcd[2 * ds + (r0 + (int)threadIdx.x - a.d_inner - a.conv_dim)] = wv;
+                    }
+                    __threadfence();
+                }
+                if (warp == 0) {
+                    __syncwarp();
+                    if (lane == 0) {
+                        __threadfence();
+                        atomicAdd(a.bc_flag, 1u);
                     }
                 }
             } else {
-                // 8 gate rows over the 8 matching x rows; their 8 state rows ride in the same stage
+                // 8 gate rows + the 8 matching x rows + their 8 state rows
                 const int u = t - nbc;
                 const PTileExtra e = ps_unit_extra(a, rb);
                 float sv[PS_NS_MAX];
@@ -612,12 +491,17 @@ struct PConsumer {
                     const int c = u * PS_UNIT + threadIdx.x - PS_UNIT;
                     s.c->s_xv[threadIdx.x - PS_UNIT] = ps_silu(ps_conv_step(k, tp, sw, bias, L.conv_state + (int64_t)c * win, v));
                 }
+                if (!bc_loaded && threadIdx.x == 0) {
+                    // B, C and dt of this token come from other CTAs' tiles of this phase
+                    ps_wait_counter(a, a.bc_flag, (mamba_seen + 1) * (unsigned)nbc, s.c);
+                    s.c->snap = s.c->abort;
+                }
+                consumer_sync<PS_CW>();
+                if (!bc_loaded && s.c->snap) return false;
                 if (!bc_loaded) {
-                    // B, C and dt of this token: other CTAs' tiles of this same phase
-                    if (!ll_pull(a, s.c, a.ll_bcd, 2 * ds + nh, tag, s.bcd)) return false;
-                    bc_loaded = true;
-                } else {
+                    for (int j = threadIdx.x; j < 2 * ds + nh; j += PS_CT) s.bcd[j] = __ldcg(a.bcd + j);
                     consumer_sync<PS_CW>();
+                    bc_loaded = true;
                 }
                 // state update of row r (one warp per row): core of decode_mamba_layer,
                 // inference/generator.cpp:562-600
@@ -656,50 +540,44 @@ struct PConsumer {
                 acc = warp_sum(acc);
                 if (lane == 0) {
                     const float y = acc + s.hp[2 * nh + h] * xv;
-                    const float yv = y * ps_silu(gt);
-                    ll_store(a.ll_u, r, yv * nwr, tag);
-                    sq += (double)yv * yv;
+                    const float v = y * ps_silu(gt);
+                    a.u[r] = v * nwr;
+                    sq += (double)v * v;
                 }
             }
         }
-        // gated-norm statistic of this CTA's rows, as a (head, tail) pair of floats
         if (lane == 0) s.c->warp_sq[warp] = sq;
         consumer_sync<PS_CW>();
         if (threadIdx.x == 0) {
             double t = 0.0;
             for (int w = 0; w < PS_CW; ++w) t += s.c->warp_sq[w];
-            const float hi = (float)t;
-            ll_store(a.ll_part, 2 * blockIdx.x, hi, tag);
-            ll_store(a.ll_part, 2 * blockIdx.x + 1, (float)(t - (double)hi), tag);
+            a.partials[blockIdx.x] = t;
         }
+        ++mamba_seen;
         return true;
     }
 
-    __device__ bool mamba_b(const PLayer& L, int i, int op_index) {
+    __device__ bool mamba_b(const PLayer& L, int op_index) {
         const int K = a.d_inner;
         const int rb = (int)row_bytes_of(KIND, K);
-        const unsigned tag = s.tag0 + i;
         xact_carve<KIND>(s.xa2, s.xa2_base, K, 1, false);
         xact_zero_row<KIND, PS_CW>(s.xa2);
-        // u, and with it the CTAs' partial sums of squares (head + tail floats of a double each)
-        double t = staged(i, nullptr, a.ll_u, 0, 1, nullptr, s.xa2, 0.0, false, true, nullptr, a.ll_part,
-                          2 * (int)gridDim.x, nullptr, true);
-        if (t < 0.0) return false;
-        const float in_scale = 1.0f / sqrtf((float)(t / (double)K) + a.eps);
+        double t = 0.0;
+        for (int i = threadIdx.x; i < (int)gridDim.x; i += PS_CT) t += __ldcg(a.partials + i);
+        t = ps_stage<KIND>(a.u, 0, 1, nullptr, s.xa2, 0.0f, s.c->red_d, t, false, true) / (double)K;
+        const float in_scale = 1.0f / sqrtf((float)t + a.eps);
         ps_stamp(a, cur_op, 1);
         const int ntiles = (a.d + 15) / 16;
         for (int tl = ps_rot(op_index); tl < ntiles; tl += gridDim.x) {
             const int r0 = tl * 16, nrows = min(16, a.d - r0);
             const bool owner = (int)threadIdx.x < nrows;
+            float* dst = a.x + r0 + threadIdx.x;
+            const float pre = owner ? __ldcg(dst) : 0.0f;
             bool ok;
             const uint8_t* ts = take(ok);
             if (!ok) return false;
             const float v = rows(ts, rb, nrows, K, s.xa2);
-            if (owner) {
-                const float o = s.xraw[r0 + threadIdx.x] + v * in_scale * a.res_mult;
-                a.x[r0 + threadIdx.x] = o;
-                ll_store(a.ll_x[1], r0 + threadIdx.x, o, tag);
-            }
+            if (owner) *dst = pre + v * in_scale * a.res_mult;
         }
         return true;
     }
@@ -728,11 +606,10 @@ struct PConsumer {
         return chain;
     }
 
-    __device__ bool moe_c(const PLayer& L, int i, int op_index) {
+    __device__ bool moe_c(const PLayer& L, int op_index) {
         const int d = a.d;
         const int rb = (int)row_bytes_of(KIND, d);
-        const unsigned tag = s.tag0 + i;
-        if (staged(i, a.x, a.ll_x[1], 0, 1, s.nw, s.xa1, 0.0, true, false, s.xraw) < 0.0) return false;
+        ps_stage<KIND>(a.x, 0, 1, s.nw, s.xa1, a.eps, s.c->red_d, 0.0, true, false);
         ps_stamp(a, cur_op, 1);
         const int n_router = (a.ne + PS_ROUTER_ROWS - 1) / PS_ROUTER_ROWS;
         const int ntiles = n_router + (L.has_shared ? a.SH / PS_UNIT : 0);
@@ -745,7 +622,11 @@ struct PConsumer {
                 if (warp < PS_ROUTER_ROWS && e < a.ne) {
                     const float* wrow = reinterpret_cast<const float*>(ts) + (int64_t)warp * d;
                     const float lg = router_logit_ps(wrow, s.gs + warp * (d >> 2), d);
-                    if (lane == 0) ll_store(a.ll_logits, e, lg, tag);     // the producers route when all are in
+                    if (lane == 0) {
+                        a.logits[e] = lg;
+                        __threadfence();
+                        atomicAdd(a.rt_flag, 1u);      // one count per expert: the producers route when all are in
+                    }
                 }
                 give();
             } else {
@@ -753,17 +634,16 @@ struct PConsumer {
                 const float v = rows(ts, rb, 16, d, s.xa1);
                 if (warp == 0) {
                     const float o = swiglu8(v);
-                    if (lane < PS_UNIT) ll_store(a.ll_shact, r0 + lane, o, tag);
+                    if (lane < PS_UNIT) a.sh_act[r0 + lane] = o;
                 }
             }
         }
         return true;
     }
 
-    __device__ bool moe_d(const PLayer& L, int i, int op_index) {
+    __device__ bool moe_d(const PLayer& L, int op_index) {
         const int d = a.d;
         const int rb_d = (int)row_bytes_of(KIND, d);
-        const unsigned tag = s.tag0 + i;
         const int n_sd = L.has_shared ? (d + 15) / 16 : 0;
         const int per_slot = a.E / PS_UNIT;
         const int ntiles = n_sd + a.K * per_slot;
@@ -772,9 +652,7 @@ struct PConsumer {
             rb_sh = (int)row_bytes_of(KIND, a.SH);
             xact_carve<KIND>(s.xa2, s.xa2_base, a.SH, 1, false);
             xact_zero_row<KIND, PS_CW>(s.xa2);
-            if (staged(i, nullptr, a.ll_shact, 0, 1, nullptr, s.xa2, 0.0, false, false, nullptr) < 0.0) return false;
-        } else if (threadIdx.x == 0) {
-            ll_store(a.ll_hb, blockIdx.x, 0.0f, tag);
+            ps_stage<KIND>(a.sh_act, 0, 1, nullptr, s.xa2, 0.0f, s.c->red_d, 0.0, false, false);
         }
         ps_stamp(a, cur_op, 1);
         for (int t = ps_rot(op_index); t < ntiles; t += gridDim.x) {
@@ -784,30 +662,24 @@ struct PConsumer {
             if (t < n_sd) {
                 const int r0 = t * 16, nrows = min(16, d - r0);
                 const float v = rows(ts, rb_sh, nrows, a.SH, s.xa2);
-                if ((int)threadIdx.x < nrows) ll_store(a.ll_shout, r0 + threadIdx.x, v, tag);
+                if ((int)threadIdx.x < nrows) a.sh_out[r0 + threadIdx.x] = v;
             } else {
-                const int q = t - n_sd, k = q / per_slot, r0 = (q % per_slot) * PS_UNIT;
+                const int i = t - n_sd, k = i / per_slot, r0 = (i % per_slot) * PS_UNIT;
                 const float v = rows(ts, rb_d, 16, d, s.xa1);
                 if (warp == 0) {
                     const float o = swiglu8(v);
-                    if (lane < PS_UNIT) ll_store(a.ll_act, k * a.E + r0 + lane, o, tag);
+                    if (lane < PS_UNIT) a.act[(int64_t)k * a.E + r0 + lane] = o;
                 }
             }
         }
         return true;
     }
 
-    __device__ bool moe_e(const PLayer& L, int layer, int i, int op_index) {
+    __device__ bool moe_e(const PLayer& L, int layer, int op_index) {
         const int d = a.d, E = a.E, K = a.K;
         const int rb = (int)row_bytes_of(KIND, E);
         const int sub = 16 * rb;
-        const unsigned tag = s.tag0 + i;
-        // the routed activations, and with them the shared expert's output (both from the
-        // previous phase; the latter into the router scratch, free in this phase)
-        float* sho = s.gs;
-        if (staged(i, nullptr, a.ll_act, E, K, nullptr, s.xa3, 0.0, false, false, nullptr, L.has_shared ? a.ll_shout : nullptr,
-                   L.has_shared ? d : 0, sho) < 0.0)
-            return false;
+        ps_stage<KIND>(a.act, E, K, nullptr, s.xa3, 0.0f, s.c->red_d, 0.0, false, false);
         // mixture weights: left in shared memory by this CTA's producer warp
         if (threadIdx.x == 0) {
             bool got = false;
@@ -829,17 +701,49 @@ struct PConsumer {
         for (int tl = ps_rot(op_index); tl < ntiles; tl += gridDim.x) {
             const int r0 = tl * 16, nrows = min(16, d - r0);
             const bool owner = (int)threadIdx.x < nrows;
+            float* dst = a.x + r0 + threadIdx.x;
+            float pre = 0.0f, sho = 0.0f;
+            if (owner) {
+                pre = __ldcg(dst);
+                if (L.has_shared) sho = __ldcg(a.sh_out + r0 + threadIdx.x);
+            }
             bool ok;
             const uint8_t* ts = take(ok);
             if (!ok) return false;
             const float v = rows(ts, rb, nrows, E, s.xa3, K, sub, wk);
-            if (owner) {
-                const float o = s.xraw[r0 + threadIdx.x] + ((L.has_shared ? sho[r0 + threadIdx.x] : 0.0f) + v) * a.res_mult;
-                a.x[r0 + threadIdx.x] = o;
-                ll_store(a.ll_x[0], r0 + threadIdx.x, o, tag);
-            }
+            if (owner) *dst = pre + (sho + v) * a.res_mult;
         }
         return true;
+    }
+
+    // Grid barrier of the consumer threads (barriers passed so far: nbar).  Thread 0
+    // arrives and waits; the other warps meanwhile fetch what the next phase needs that
+    // no earlier phase produces.
+    __device__ __forceinline__ bool grid_sync(unsigned& nbar, const POp next) {
+        __threadfence();
+        consumer_sync<PS_CW>();
+        if (threadIdx.x == 0) {
+            if ((int)blockIdx.x == a.skip_cta && nbar == 0) {
+                s.c->abort = 1;                                   // test hook: never arrives
+            } else {
+                const unsigned long long target = (unsigned long long)(nbar + 1) * gridDim.x;
+                atomicAdd(a.bar, 1ULL);
+                bool ok = false;
+                for (unsigned it = 0; it < a.spin_limit; ++it) {
+                    if (ld_acquire_u64(a.bar) >= target) { ok = true; break; }
+                    if ((it & 63) == 63 && ld_volatile_s32(a.status) != 0) break;
+                }
+                if (!ok) {
+                    atomicExch(a.status, 1);
+                    s.c->abort = 1;
+                }
+            }
+            s.c->snap = s.c->abort;
+        }
+        prefetch(next, 32);
+        consumer_sync<PS_CW>();
+        ++nbar;
+        return s.c->snap == 0;
     }
 };
 
@@ -852,33 +756,14 @@ struct PConsumer {
 // and on this part an instruction fetched from L2 costs tens of cycles, so the size of
 // the code, not its operation count, is what the routed experts' weights wait for.
 // s_p, s_sel: ne floats each.
-// The logits are the tagged words the router phase writes: polled here (bounded).
-__device__ __noinline__ bool ps_route_warp(const PArgs& a, PCtl* c, unsigned tag, const float* bias, int ne, int K,
-                                           float* s_p, float* s_sel, int* s_idx, float* s_w, int lane) {
+__device__ __noinline__ void ps_route_warp(const float* logits, const float* bias, int ne, int K, float* s_p,
+                                           float* s_sel, int* s_idx, float* s_w, int lane) {
     float mx = -INFINITY;
-    bool pending = false;
 #pragma unroll 1
     for (int e = lane; e < ne; e += 32) {
-        pending = true;
-        for (unsigned it = 0; it < a.spin_limit; ++it) {
-            const uint2 w = ll_load1(a.ll_logits, e);
-            if (w.y == tag) {
-                const float v = __uint_as_float(w.x);
-                s_sel[e] = v;
-                mx = fmaxf(mx, v);
-                pending = false;
-                break;
-            }
-            if ((it & 63) == 63 && (c->abort || ld_volatile_s32(a.status) != 0)) break;
-        }
-        if (pending) break;
-    }
-    if (__any_sync(0xffffffffu, pending)) {
-        if (lane == 0) {
-            atomicExch(a.status, 1);
-            c->abort = 1;
-        }
-        return false;
+        const float v = __ldcg(logits + e);
+        s_sel[e] = v;
+        mx = fmaxf(mx, v);
     }
     mx = warp_max(mx);
 #pragma unroll 1
@@ -930,7 +815,6 @@ __device__ __noinline__ bool ps_route_warp(const PArgs& a, PCtl* c, unsigned tag
         for (int k = 0; k < K; ++k) s_w[k] = renorm ? __fmul_rn(s_w[k], f) : f;
     }
     __syncwarp();
-    return true;
 }
 
 __device__ __forceinline__ bool ps_slot(const PArgs& a, const PView& s, const PRingPos& rp, unsigned seq, uint8_t*& dst,
@@ -948,6 +832,7 @@ struct PProducer {
     int lane;
     PRingPos rp;             // next stage to fill
     unsigned seq = 0;        // tiles issued so far
+    unsigned moe_seen = 0;   // POP_MOE_D phases issued in this launch
 
     // lane 0 only: the stage for the next tile, once the consumers have handed it back.
     // The caller fills it and calls issued().
@@ -1048,10 +933,10 @@ struct PProducer {
         return true;
     }
     // The whole warp: the shared expert's down rows are requested at once; then the warp
-    // polls the router's logits (tagged words of the router phase, `tag`), turns them into
-    // (idx, w) and requests the routed tiles - normally while the consumers are still
-    // inside the router phase.
-    __device__ bool moe_d(const PLayer& L, int layer, int op_index, unsigned tag) {
+    // waits for the router's logits (one count per expert on rt_flag, raised during the
+    // router phase), turns them into (idx, w) and requests the routed tiles - normally
+    // while the consumers are still inside the router phase or its barrier.
+    __device__ bool moe_d(const PLayer& L, int layer, int op_index) {
         const int d = a.d;
         const int64_t rb_d = row_bytes_of(KIND, d), rb_sh = L.has_shared ? row_bytes_of(KIND, a.SH) : 0;
         const int n_sd = L.has_shared ? (d + 15) / 16 : 0;
@@ -1059,11 +944,16 @@ struct PProducer {
         const int ntiles = n_sd + a.K * per_slot;
         int t = ps_rot(op_index);
         int ok = 1;
+        ++moe_seen;
         if (lane == 0) {
             for (; t < n_sd; t += gridDim.x) {
                 const int r0 = t * 16, rows = min(16, d - r0);
                 if (!one(L.sh_down + r0 * rb_sh, (uint32_t)(rows * rb_sh))) { ok = 0; break; }
             }
+            const long long t0 = clock64();
+            if (ok && !ps_wait_counter(a, a.rt_flag, moe_seen * (unsigned)a.ne, s.c)) ok = 0;
+            if (a.trace && (int)blockIdx.x == a.trace_cta)
+                a.trace[(size_t)op_index * PS_TRACE_SLOTS + 6] = (unsigned long long)(clock64() - t0);
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         t = __shfl_sync(0xffffffffu, t, 0);
@@ -1071,10 +961,10 @@ struct PProducer {
         int* r_idx = s.c->r_idx[layer & 1];
         float* r_w = s.c->r_w[layer & 1];
         const long long t1 = clock64();
-        if (!ps_route_warp(a, s.c, tag, L.router_bias ? s.rbias : nullptr, a.ne, a.K, s.r_p, s.r_sel, r_idx, r_w, lane))
-            return false;
+        ps_route_warp(a.logits, L.router_bias ? s.rbias : nullptr, a.ne, a.K, s.r_p, s.r_sel, r_idx, r_w, lane);
         if (a.trace && lane == 0 && (int)blockIdx.x == a.trace_cta)
             a.trace[(size_t)op_index * PS_TRACE_SLOTS + 7] = (unsigned long long)(clock64() - t1);
+        __syncwarp();
         if (lane == 0) {
             __threadfence_block();
             s.c->route_gen = layer + 1;
@@ -1142,9 +1032,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) persist_step_kernel(PArgs a) {
     s.rbias = s.r_sel + a.ne;
     s.bcd = reinterpret_cast<float*>(smem + a.off_bcd);
     s.hp = s.bcd + 2 * a.d_state + a.n_heads;
-    s.xraw = reinterpret_cast<float*>(smem + a.off_xraw);
     const int n_ops = a.op_end - a.op_begin;
-    PCtl* ctl = s.c;
     {
         // the phase list of this launch and the layer table: into shared memory once
         uint64_t* prog = reinterpret_cast<uint64_t*>(smem + a.off_prog);
@@ -1167,19 +1055,8 @@ __global__ void __launch_bounds__(PS_THREADS, 1) persist_step_kernel(PArgs a) {
         s.c->abort = 0;
         s.c->snap = 0;
         s.c->route_gen = 0;
-        s.c->tag0 = *reinterpret_cast<volatile unsigned int*>(a.epoch) + 1u;     // tags of this launch: tag0 + phase index
     }
     __syncthreads();
-    s.tag0 = ctl->tag0;
-    if ((int)blockIdx.x == a.skip_cta) {
-        // test hook: this CTA takes no part; the others' bounded polls for its heartbeat run out
-        if (threadIdx.x == 0 && atomicAdd(a.done, 1u) == gridDim.x - 1) {
-            *a.epoch = s.tag0 - 1u + (unsigned)n_ops;
-            __threadfence();
-            *a.done = 0u;
-        }
-        return;
-    }
 
     if (warp == PS_CW) {
         PProducer<KIND> p{a, s, lane};
@@ -1193,7 +1070,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) persist_step_kernel(PArgs a) {
                 case POP_MAMBA_A: ok = p.mamba_a(L, oi); break;
                 case POP_MAMBA_B: ok = p.rows16(L.mamba_out, a.d, a.d_inner, oi); break;
                 case POP_MOE_C: ok = p.moe_c(L, oi); break;
-                case POP_MOE_D: ok = p.moe_d(L, op.layer, oi, s.tag0 + i - 1); break;
+                case POP_MOE_D: ok = p.moe_d(L, op.layer, oi); break;
                 case POP_MOE_E: ok = p.moe_e(L, op.layer, oi); break;
                 default: break;
             }
@@ -1207,7 +1084,8 @@ __global__ void __launch_bounds__(PS_THREADS, 1) persist_step_kernel(PArgs a) {
     xact_zero_row<KIND, PS_CW>(s.xa1);
     xact_zero_row<KIND, PS_CW>(s.xa3);
     PConsumer<KIND> c{a, s, warp, lane};
-    c.prefetch(s.ops[0]);
+    c.prefetch(s.ops[0], 0);
+    unsigned nbar = 0;
     bool ok = true;
     for (int i = 0; i < n_ops && ok; ++i) {
         const POp op = s.ops[i];
@@ -1215,16 +1093,13 @@ __global__ void __launch_bounds__(PS_THREADS, 1) persist_step_kernel(PArgs a) {
         const PLayer& L = s.layers[op.layer];
         ps_stamp(a, oi, 0);
         c.cur_op = oi;
-        // the next phase's static vectors are requested now, a whole phase ahead (the
-        // phases that use the norm-weight buffer are never adjacent)
-        if (i + 1 < n_ops && op.op != POP_MAMBA_A && op.op != POP_MOE_C) c.prefetch(s.ops[i + 1]);
         switch (op.op) {
-            case POP_EMBED: ok = c.embed(i); break;
-            case POP_MAMBA_A: ok = c.mamba_a(L, i, oi); break;
-            case POP_MAMBA_B: ok = c.mamba_b(L, i, oi); break;
-            case POP_MOE_C: ok = c.moe_c(L, i, oi); break;
-            case POP_MOE_D: ok = c.moe_d(L, i, oi); break;
-            case POP_MOE_E: ok = c.moe_e(L, op.layer, i, oi); break;
+            case POP_EMBED: ok = c.embed(); break;
+            case POP_MAMBA_A: ok = c.mamba_a(L, oi); break;
+            case POP_MAMBA_B: ok = c.mamba_b(L, oi); break;
+            case POP_MOE_C: ok = c.moe_c(L, oi); break;
+            case POP_MOE_D: ok = c.moe_d(L, oi); break;
+            case POP_MOE_E: ok = c.moe_e(L, op.layer, oi); break;
             default: break;
         }
         ps_stamp(a, oi, 2);
@@ -1233,17 +1108,19 @@ __global__ void __launch_bounds__(PS_THREADS, 1) persist_step_kernel(PArgs a) {
             a.trace[(size_t)oi * PS_TRACE_SLOTS + 5] = (unsigned long long)c.rows_cyc;
         }
         c.wait_cyc = c.rows_cyc = 0;
+        if (ok && i + 1 < n_ops) ok = c.grid_sync(nbar, s.ops[i + 1]);
         ps_stamp(a, oi, 3);
     }
-    cp_async_wait_all();
     if (!ok) s.c->abort = 1;      // the producer sees it at its next wait
-    // Last CTA out moves the tag counter past this launch's tags: no word written by this
-    // launch (complete or not) can be taken for one of the next.
+    // Last CTA out puts the synchronisation words back to zero for the next launch: a CTA
+    // counts itself out only after its last look at them.
     consumer_sync<PS_CW>();
     if (threadIdx.x == 0) {
         __threadfence();
         if (atomicAdd(a.done, 1u) == gridDim.x - 1) {
-            *a.epoch = s.tag0 - 1u + (unsigned)n_ops;
+            *a.bar = 0ULL;
+            *a.bc_flag = 0u;
+            *a.rt_flag = 0u;
             __threadfence();
             *a.done = 0u;
         }
@@ -1289,7 +1166,6 @@ static int plan_kind(PArgs& a) {
     a.off_red = take((size_t)2 * PS_CW * 16 * 4);
     a.off_route = take((size_t)3 * a.ne * 4);
     a.off_bcd = take((size_t)(2 * a.d_state + 4 * a.n_heads) * 4);
-    a.off_xraw = take((size_t)d * 4);
     a.off_prog = take((size_t)(a.max_ops + 2) * sizeof(POp) + (size_t)a.n_layers * sizeof(PLayer));
     a.off_ctl = take(sizeof(PCtl));
     const size_t other = off;
@@ -1302,7 +1178,7 @@ static int plan_kind(PArgs& a) {
     a.n_stages = ns;
     const int ring = ns * a.stage_bytes;
     a.off_xa1 += ring; a.off_xa2 += ring; a.off_xa3 += ring; a.off_nw += ring; a.off_gs += ring; a.off_red += ring;
-    a.off_route += ring; a.off_bcd += ring; a.off_xraw += ring; a.off_prog += ring; a.off_ctl += ring;
+    a.off_route += ring; a.off_bcd += ring; a.off_prog += ring; a.off_ctl += ring;
     a.smem_bytes = ring + (int)other;
     return B200_OK;
 }
