@@ -826,7 +826,10 @@ static int launch_gemm_q(const GemmArgs& a) {
     // every CTA would stream its 128 weight rows over all of K while most SMs idle, so K is
     // cut across CTAs and the partial products are added afterwards in a fixed order.
     const int tiles = b.m_slots * b.n_tiles, sb = a.K / 256;
-    if (EPI == GEMM_EPI_STORE && sb >= 2 && tiles * 2 <= num_sms()) {
+    // Not for the grouped form: the reduction pass walks all M rows, but a grouped launch
+    // writes partial sums only for the rows its offsets cover - rows outside them (other
+    // ranks' experts in the expert-parallel layer) must be left exactly as they are.
+    if (EPI == GEMM_EPI_STORE && a.offsets == nullptr && sb >= 2 && tiles * 2 <= num_sms()) {
         const int want = std::min(sb, num_sms() / tiles);
         const int per = (sb + want - 1) / want;
         b.k_splits = (sb + per - 1) / per;

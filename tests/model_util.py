@@ -28,8 +28,23 @@ TINY = dict(vocab=512, hidden=256, n_layers=4, layer_types=[0, 1, 0, 1],
             attn_scale=0.0078125, logits_scaling=6.0)
 
 
-def make_model(oracle, cfg, seed=0, w_std=0.02):
+_MODEL_CACHE = {}
+
+
+def cached_model(oracle, cfg, seed=0, share_experts=False):
+    """make_model() memoised per (configuration, seed): the wide test models take tens of
+    seconds to draw and quantise."""
+    key = (tuple(sorted((k, tuple(v) if isinstance(v, list) else v) for k, v in cfg.items())), seed, share_experts)
+    if key not in _MODEL_CACHE:
+        _MODEL_CACHE[key] = make_model(oracle, cfg, seed, share_experts=share_experts)
+    return _MODEL_CACHE[key]
+
+
+def make_model(oracle, cfg, seed=0, w_std=0.02, share_experts=False):
+    """share_experts: every layer uses the same routed-expert matrices (drawn once; the wide
+    models spend most of their set-up time there), everything else differs per layer."""
     r = np.random.default_rng(seed)
+    shared = {}
     d, q = cfg["hidden"], cfg["qkind"]
     m = {"cfg": cfg, "layers": []}
     emb = (r.standard_normal((cfg["vocab"], d)) * w_std).astype(np.float32)
@@ -53,9 +68,13 @@ def make_model(oracle, cfg, seed=0, w_std=0.02):
             L["wo"] = store_weight(oracle, r.standard_normal((d, qd)) * w_std, q)
         L["router"] = (r.standard_normal((ne, d)) / np.sqrt(d)).astype(np.float32)
         L["router_bias"] = (r.standard_normal(ne) * 0.5 / ne).astype(np.float32)
-        L["gate"] = store_weight(oracle, r.standard_normal((ne * E, d)) * w_std, q)
-        L["up"] = store_weight(oracle, r.standard_normal((ne * E, d)) * w_std, q)
-        L["down"] = store_weight(oracle, r.standard_normal((ne * d, E)) * w_std, q)
+        if not (share_experts and shared):
+            shared = dict(gate=store_weight(oracle, r.standard_normal((ne * E, d)) * w_std, q),
+                          up=store_weight(oracle, r.standard_normal((ne * E, d)) * w_std, q),
+                          down=store_weight(oracle, r.standard_normal((ne * d, E)) * w_std, q))
+        L.update(shared if share_experts else dict(shared))
+        if not share_experts:
+            shared = {}
         L["sh_gate"] = store_weight(oracle, r.standard_normal((SH, d)) * w_std, q)
         L["sh_up"] = store_weight(oracle, r.standard_normal((SH, d)) * w_std, q)
         L["sh_down"] = store_weight(oracle, r.standard_normal((d, SH)) * w_std, q)

@@ -3,15 +3,15 @@ reference's per-token op sequence, teacher-forced."""
 import numpy as np
 import pytest
 
-from model_util import CONFIG_1, TINY, CudaDecoder, OracleDecoder, make_model
+from model_util import CONFIG_1, TINY, CudaDecoder, OracleDecoder, cached_model, make_model
 
 pytestmark = pytest.mark.gpu
 
 
-def _teacher_forced(oracle, cfg, steps, graph, fused, seed=0):
+def _teacher_forced(oracle, cfg, steps, graph, fused, seed=0, model=None):
     """Feed the same seeded token stream to both sides (greedy continuation of the
     oracle after a random prompt), compare logits and arg-max every step."""
-    model = make_model(oracle, cfg, seed)
+    model = model or make_model(oracle, cfg, seed)
     ora = OracleDecoder(oracle, model, max_ctx=steps + 1)
     dec = CudaDecoder(model, batch=1, max_ctx=steps + 1)
     dec.configure(fused, graph)
@@ -158,6 +158,25 @@ def test_config1_teacher_forced(oracle):
     oracle finishes in seconds."""
     cfg = dict(CONFIG_1, vocab=4096)
     rate, worst, margins = _teacher_forced(oracle, cfg, steps=32, graph=1, fused=0)
+    assert rate >= 0.99, f"greedy agreement {rate:.3f} (min top-2 margin {min(margins):.2e})"
+    assert worst < 2e-3
+
+
+H_TINY_CUT = dict(vocab=2048, hidden=1536, n_layers=4, layer_types=[0, 1, 0, 0],
+                  n_heads=12, n_kv=4, head_dim=128, rope_type=-1, rope_theta=1e4,
+                  mamba_heads=48, mamba_d_head=64, mamba_d_state=128, mamba_d_conv=4,
+                  n_experts=64, top_k=6, expert_dim=512, shared_dim=1024, qkind=3,
+                  rms_eps=1e-5, embedding_multiplier=12.0, residual_multiplier=0.22,
+                  attn_scale=0.0078125, logits_scaling=6.0)
+
+
+@pytest.mark.parametrize("fused", [1, 2])
+def test_h_tiny_width_cut_teacher_forced(oracle, fused):
+    """Four layers at the widths of the Granite-4.0-H-Tiny-shaped model (hidden 1536, Mamba
+    48 x 64 / state 128, 12 q / 4 kv heads x 128 without RoPE, 64 experts top-6 ffn 512, shared
+    1024, Q4_K; reduced vocabulary) against the oracle's walk, fused and persistent modes."""
+    model = cached_model(oracle, H_TINY_CUT, 0, share_experts=True)
+    rate, worst, margins = _teacher_forced(oracle, H_TINY_CUT, steps=10, graph=1, fused=fused, model=model)
     assert rate >= 0.99, f"greedy agreement {rate:.3f} (min top-2 margin {min(margins):.2e})"
     assert worst < 2e-3
 

@@ -138,6 +138,36 @@ def test_dispatch_free_form_with_virtual_ranks(oracle, G):
         np.testing.assert_allclose(host(total), want, **SUM_ORDER)
 
 
+def test_dispatch_free_form_few_rows_leaves_other_ranks_rows_alone(oracle):
+    """Few tokens and few local experts: the shape at which a plain GEMM cuts K across CTAs
+    and adds the partial sums in a second pass over all rows.  The grouped GEMM of a rank
+    covers only its own experts' rows, so that pass must not run there: the rows of other
+    ranks' experts keep the persistent buffer's (finite) contents.  The split-K workspace is
+    filled with NaN first by a plain linear on NaN activations."""
+    from gpu_util import SUM_ORDER, dev, empty, host, ops
+    T, d, E, ne, K, SH, wkind, G = 48, 1024, 256, 8, 2, 256, 3, 4
+    c, dc = _dev_case(oracle, 31, T, d, E, ne, K, SH, wkind)
+    # a plain linear of the same few rows takes the split-K path: poison its workspace
+    r = np.random.default_rng(5)
+    w = dev(oracle.quantize((r.standard_normal(512 * d) * 0.02).astype(np.float32), 3))
+    nan_x = torch.full((T * K, d), float("nan"), device="cuda")
+    ops.linear_forward_q4(nan_x, w, empty((T * K, 512)), T * K, d, 512, 3)
+    total, idx0 = None, None
+    for rank in range(G):
+        sh = tuple(ep.shard_experts(dc[k], ne, rank, G) for k in ("gates", "ups", "downs"))
+        layer = ep.ExpertParallelMoE(d, E, ne, K, SH, wkind, dc["router_w"], dc["router_bias"], *sh,
+                                     (dc["sh_g"], dc["sh_u"], dc["sh_d"]))
+        layer.rank, layer.world, layer.n_local = rank, G, ne // G
+        layer._reduce = lambda t: t
+        part, idx = layer.forward_reduce(dc["x"])
+        assert torch.isfinite(part).all()
+        total = part.clone() if total is None else total + part
+        idx0 = idx
+    want, want_idx = _single_gpu_layer(dc, T, d, E, ne, K, SH, wkind)
+    assert np.array_equal(host(idx0), want_idx)
+    np.testing.assert_allclose(host(total), want, **SUM_ORDER)
+
+
 def test_dispatch_free_form_replays_as_a_cuda_graph(oracle):
     """graphed_reduce(): the captured layer gives the same bits as the eager call, also for a
     second input of the same shape."""

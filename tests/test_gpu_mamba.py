@@ -109,6 +109,25 @@ def test_forward_sequence(oracle, B, T, wkind):
         close(host(dstate), want_state, rows, dict(rtol=5e-4, atol=5e-6))
 
 
+@pytest.mark.parametrize("B,T", [(2, 4096), (1, 4096 + 77), (8, 4096)])
+def test_forward_at_the_op_level_benchmark_shape(oracle, B, T):
+    """48 heads x 64, d_state 128, 4096 tokens (32 chunks of 128: the state is carried over
+    all of them; 4096 + 77 adds a partial tail chunk), Q4_K projections, against the oracle's
+    sequential scan (core/mamba_cpu.cpp:81-194).  The model width in front of the projections
+    is kept at 256 so the scalar oracle finishes in seconds; conv, scan and gated norm run at
+    the full inner width of 3072."""
+    from gpu_util import dev, empty, fp16_close, host, ops
+    c = mamba_case(oracle, 4000 + B + T, B=B, T=T, d=256, n_heads=48, d_head=64, d_state=128, k=4, wkind=3, w_std=0.1)
+    a = c["args"]
+    want, want_state = oracle.mamba2_forward(*a, 3)
+    dstate, out = dev(a[9]), empty((B, T, a[12]))
+    ops.mamba2_forward_half(dev(a[0]), *_dev_params(a[1:9]), dstate, out, *a[10:], 3)
+    fp16_close(host(out), want)
+    fp16_close(host(dstate), want_state)
+    # the tail of the sequence separately: an error in the carried state would show here first
+    fp16_close(host(out)[:, -64:], want[:, -64:])
+
+
 def test_forward_small_state_general_path(oracle):
     """d_state 16 / d_head 32 (shapes outside the register-resident scan's fast cases)."""
     from gpu_util import dev, empty, host, ops

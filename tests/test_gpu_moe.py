@@ -102,6 +102,20 @@ def test_layer_config3_4096_tokens(oracle):
     _close(got["out"][sample], out, N, 3)
 
 
+@pytest.mark.parametrize("N", [1, 64])
+def test_layer_h_small_shape(oracle, N):
+    """The widest configuration of the benchmark list: hidden 4096, 72 experts, top-10, expert
+    ffn 768, shared ffn 1536, Q4_K (beyond the reference kernels' 64-expert / top-8 limits).
+    Indices bit-exact, outputs within the tolerance of their path."""
+    d, E, ne, K, SH = 4096, 768, 72, 10, 1536
+    c = moe_case(oracle, 5000 + N, N, d, E, ne, K, SH, 3)
+    got = _run(c, N, d, E, ne, K, SH, 3)
+    out, probs, idx, w = _oracle(oracle, c, d, E, ne, K, SH, 3)
+    assert np.array_equal(got["idx"], idx)
+    _ulp_close(got["w"], w)
+    _close(got["out"], out, N, 3)
+
+
 def test_routing_bit_exact_many_tokens(oracle):
     """4096 tokens at the config-3 router shape: every top-k index identical, probabilities
     and weights within a few ulp."""

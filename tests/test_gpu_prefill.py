@@ -70,6 +70,45 @@ def test_prefill_matches_oracle(oracle):
     dec.close()
 
 
+def test_prefill_4096_tokens_at_h_tiny_widths(oracle):
+    """A 4096-token prompt through the four-layer cut at the H-Tiny widths (Mamba, attention,
+    Mamba, Mamba, an MoE after each; Q4_K): the prompt path against the same tokens fed
+    through the decode step (which the oracle pins at these widths in
+    tests/test_gpu_decoder.py), logits and the following steps; and the first 48 tokens of
+    the same prompt against the oracle's own walk."""
+    from model_util import cached_model
+    from test_gpu_decoder import H_TINY_CUT
+    cfg = H_TINY_CUT
+    T = 4096
+    model = cached_model(oracle, cfg, 0, share_experts=True)
+    r = np.random.default_rng(22)
+    prompt = r.integers(0, cfg["vocab"], (1, T))
+    a = CudaDecoder(model, batch=1, max_ctx=T + 8)
+    b = CudaDecoder(model, batch=1, max_ctx=T + 8)
+    a.configure(1, 1)
+    _, want = _stepwise(a, prompt)
+    b.prefill(prompt)
+    fp16_close(b.logits(), want)
+    b.configure(2, 1)
+    for s in range(4):
+        toks = r.integers(0, cfg["vocab"], 1)
+        a.step_host(toks)
+        b.step_host(toks)
+        fp16_close(b.logits(), a.logits())
+    a.close()
+    b.close()
+    # oracle: 48 tokens of the same prompt
+    T0 = 48
+    ora = OracleDecoder(oracle, model, max_ctx=T0 + 4)
+    for t in range(T0):
+        want0 = ora.step(int(prompt[0, t]))
+    c = CudaDecoder(model, batch=1, max_ctx=T0 + 8)
+    c.prefill(prompt[:, :T0])
+    err = np.abs(c.logits()[0] - want0)
+    assert np.all(err <= 2e-2 + 1e-2 * np.abs(want0)), f"max abs err {err.max()}"
+    c.close()
+
+
 def test_prefill_needs_empty_sequences(oracle):
     model = make_model(oracle, TINY, 1)
     dec = CudaDecoder(model, batch=1, max_ctx=16)

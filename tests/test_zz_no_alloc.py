@@ -52,9 +52,34 @@ def test_noalloc_other_shapes_and_limit():
         ops.attention_decode_ring_fp16(dev(q), dev(kc), dev(vc), want, H, KV, hd, 0, 0, 600, 600, 0.1, None, 0)
         ops.attention_decode_ring_fp16_noalloc(dev(q), dev(kc), dev(vc), got, H, KV, hd, 0, 0, 600, 600, 0.1, 0)
         np.testing.assert_allclose(host(got), host(want), **TOL)
+    # and where the built-in array, not the sequence length, limits the number of KV splits:
+    # H 32 / head_dim 128 allows 262144 / (32 * 130) = 63 splits, a 4096-token context asks for more
+    H, KV, hd, cur = 32, 8, 128, 4096
+    q, kc, vc = _case(99, H, KV, hd, cur)
+    want, got = empty((H, hd)), empty((H, hd))
+    ops.attention_decode_ring_fp16(dev(q), dev(kc), dev(vc), want, H, KV, hd, 0, 0, cur, cur, hd ** -0.5, None, 0)
+    ops.attention_decode_ring_fp16_noalloc(dev(q), dev(kc), dev(vc), got, H, KV, hd, 0, 0, cur, cur, hd ** -0.5, 0)
+    np.testing.assert_allclose(host(got), host(want), **TOL)
     t = empty(1 << 12)
     with pytest.raises(B200Error, match="exceeds the built-in scratch"):
         # H * (hd + 2) = 2048 * 258 floats is beyond the 262144-float array: refused before any launch
         ops.attention_decode_ring_fp16_noalloc(t, t, t, t, 2048, 2048, 256, 0, 0, 1, 1, 0.1, 0)
     with pytest.raises(B200Error, match="exceeds cache"):
         ops.attention_decode_ring_fp16_noalloc(t, t, t, t, 12, 4, 64, 0, 0, 30, 20, 0.1, 0)
+
+
+def test_noalloc_matches_the_oracle(oracle):
+    """Against the CPU restatement of cpu::attention_decode_ring_fp16 (core/attn_cpu.cpp:158-254):
+    ring with a pinned prefix and a wrapped start, a window, and the 4096-token / 32-head case in
+    which the scratch capacity caps the splits."""
+    from gpu_util import dev, empty, host, ops
+    for seed, (H, KV, hd), cache_max, rs, pin, cur, win in (
+            (5, (12, 4, 128), 512, 37, 8, 300, 0),
+            (6, (12, 4, 64), 256, 0, 0, 256, 100),
+            (7, (32, 8, 128), 4096, 0, 0, 4096, 0)):
+        q, kc, vc = _case(seed, H, KV, hd, cache_max)
+        scale = float(hd) ** -0.5
+        want = oracle.attention_decode_ring(q, kc, vc, 1, H, KV, hd, rs, pin, cur, cache_max, scale, win)
+        got = empty((H, hd))
+        ops.attention_decode_ring_fp16_noalloc(dev(q), dev(kc), dev(vc), got, H, KV, hd, rs, pin, cur, cache_max, scale, win)
+        np.testing.assert_allclose(host(got), want, **TOL)
