@@ -16,10 +16,16 @@ One step = one decoded token per sequence.
                   against the measured copy bandwidth
     cpu_baseline  the reference engine's CPU ops (oracle/_ref) or the oracle port on
                   this box's host cores, on a bounded sample of the same token
+    cpu_baseline_fp32  the same sample with fp32 weights (no per-call dequantisation): the
+                  reference CPU path at its best
     prefill       the `--ctx`-token prompt through b200_decoder_prefill (tok/s, device time)
     moe_layer     one MoE layer of this shape over 4096 tokens (tensor-core grouped GEMM;
-                  expert-parallel over NCCL all-to-all when N > 1)
-    batch64       64 sequences decoded together after a 256-token prompt each
+                  expert-parallel over NCCL all-to-all when N > 1); moe_sweep: the same layer
+                  at 1 / 64 / 512 / 4096 tokens with the roofline that bounds each size
+    batch64       64 sequences decoded together after a 4096-token prompt each (the prompt
+                  of 64 x 4096 tokens through b200_decoder_prefill is timed as well)
+    mamba_ops     Mamba-2 at the op level: the chunked SSD scan over [8, 4096, 48, 64] with
+                  d_state 128, and the batch-64 single-token state update
 
 `--only gemm` times the many-token kernels alone (also the small profiling case).
 
@@ -61,11 +67,20 @@ T_IDS = dict(embed=0, final_norm=1, lm_head=2, inv_freq=3, attn_norm=10, ffn_nor
              sh_gate=45, sh_up=46, sh_down=47)
 
 
-# DRAM bytes (read + written) of one decode step of the default workload (H-Tiny shape, Q4_K,
-# batch 1, ctx 4096, fused mode, graph): the sum over the step's 261 launches of an ncu capture,
-# summarised in profiles/decode_step_htiny_q4k_bs1_dram_bytes.md.  Reported as roofline.traffic
-# for exactly that workload, null otherwise.
-STEP_DRAM_TRAFFIC_BYTES = 1176.5e6
+def measured_step_traffic(launches_per_step):
+    """DRAM bytes (read + written) of one decode step of the default workload, from the
+    committed ncu summary of that step: the summary carries a line
+    `traffic_bytes_per_step: <bytes> launches_per_step: <n>`; the figure is used only while the
+    step still has that many launches (null otherwise: the capture is then out of date)."""
+    import re
+    path = os.path.join(ROOT, "profiles", "decode_step_htiny_q4k_bs1_dram_bytes.md")
+    try:
+        m = re.search(r"traffic_bytes_per_step:\s*([0-9.eE+]+)\s+launches_per_step:\s*(\d+)", open(path).read())
+    except OSError:
+        return None
+    if not m or int(m.group(2)) != int(launches_per_step):
+        return None
+    return float(m.group(1))
 
 
 def peaks():
@@ -259,12 +274,15 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 # CPU arm
 # ---------------------------------------------------------------------------
-def cpu_decode_token_seconds(cfg, ctx, reps=1, seed=0):
+def cpu_decode_token_seconds(cfg, ctx, reps=1, seed=0, fp32_weights=False):
     """Seconds per decoded token of the CPU path, from a bounded sample: one Mamba-2
     layer, one attention layer, one MoE layer and the lm_head of a single token are
     timed and scaled by the layer counts.  Uses the reference engine's own CPU ops
     (oracle/_ref) on fp16-materialised weights - what its CPU inference path feeds them
-    after ops::quant_materialize - when that library exists, else the oracle port."""
+    after ops::quant_materialize - when that library exists, else the oracle port.
+    fp32_weights: the same ops on fp32 matrices (the engine's unquantised CPU path: nothing
+    is dequantised per call).  Returns (seconds per token scaled to the whole model, info);
+    info["sample_seconds"] is what one pass over the sample really took."""
     from oracle_lib import OracleOnly, Ref
     ora = OracleOnly()
     use_ref = Ref.available()
@@ -272,10 +290,12 @@ def cpu_decode_token_seconds(cfg, ctx, reps=1, seed=0):
     r = np.random.default_rng(seed)
     d = cfg["hidden"]
     q = cfg["qkind"] if cfg["qkind"] >= 0 else 3
-    wkind = -1 if use_ref else q
+    wkind = -2 if fp32_weights else (-1 if use_ref else q)
 
     def weight(rows, cols):
         w = (r.standard_normal(rows * cols) * 0.02).astype(np.float32)
+        if fp32_weights:
+            return w
         packed = ora.quantize(w, q)
         return ora.dequantize(packed, rows * cols, q) if use_ref else packed     # fp16 bits or packed
 
@@ -327,11 +347,14 @@ def cpu_decode_token_seconds(cfg, ctx, reps=1, seed=0):
     n_mamba = sum(1 for t_ in cfg["layer_types"] if t_ == 0)
     n_attn = cfg["n_layers"] - n_mamba
     total = n_mamba * times["mamba"] + n_attn * times["attention"] + cfg["n_layers"] * times["moe"] + times["lm_head"]
+    sample = times["mamba"] + times["attention"] + times["moe"] + times["lm_head"] * vs / cfg["vocab"]
+    what = ("fp32 weights" if fp32_weights else
+            "reference CPU ops on fp16-materialised Q4_K values" if use_ref else "oracle port on packed Q4_K")
     info = {"kind": "reference" if use_ref else "port", "cores": cpu.num_threads(),
-            "sample": ("1 Mamba-2 layer + 1 attention layer (ctx %d) + 1 MoE layer + lm_head of one decode token, "
-                       "each timed %d time(s) (best kept) and scaled by the layer counts; %s" %
-                       (ctx, max(1, reps), "reference CPU ops on fp16-materialised Q4_K values" if use_ref
-                        else "oracle port on packed Q4_K")),
+            "sample": ("1 Mamba-2 layer + 1 attention layer (ctx %d) + 1 MoE layer + lm_head (%d of %d rows) of one "
+                       "decode token, each timed %d time(s) (best kept) and scaled by the layer counts; %s" %
+                       (ctx, vs, cfg["vocab"], max(1, reps), what)),
+            "sample_seconds": round(sample, 4), "scale_to_full_step": round(total / sample, 2),
             "seconds": {k_: round(v, 4) for k_, v in times.items()}}
     return total, info
 
@@ -340,13 +363,18 @@ def run_reference_arm(args, rank):
     if rank != 0:
         return
     cfg = H_TINY
-    # every "step" is the same bounded sample; repeat it at most three times
-    secs, info = cpu_decode_token_seconds(cfg, args.ctx, reps=min(max(1, args.steps), 8))
+    # A step of this arm is one pass over the bounded sample (one layer of each kind + a slice
+    # of the lm_head); `steps` and `ms_per_step` say what was really timed, `value` is the
+    # token rate that sample scales to over the model's 40 layers (cpu_baseline.scale_to_full_step).
+    reps = min(max(1, args.steps), 8)
+    secs, info = cpu_decode_token_seconds(cfg, args.ctx, reps=reps)
     val = args.batch / secs
     line = {"impl": "reference", "metric": "decode tok/s", "value": val, "unit": "tok/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3, "higher_is_better": True,
+            "steps": reps, "warmup": 0, "ms_per_step": info["sample_seconds"] * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(cfg, args),
+            "sampled": "ms_per_step is one pass over the sample; one full decode step = ms_per_step x "
+                       "cpu_baseline.scale_to_full_step, value = batch / that",
             "cpu_baseline": dict(info, value=val, unit="tok/s"),
             "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -471,10 +499,17 @@ def batch_decode_bench(cfg, batch, ctx, steps, seed):
     g = torch.Generator(device="cuda").manual_seed(7 + seed)
     prompt = torch.randint(0, cfg["vocab"], (batch, ctx), device="cuda", generator=g, dtype=torch.int32)
     tok = torch.empty(batch, dtype=torch.int32, device="cuda")
+    model.prefill(prompt, tok)              # untimed: grows the workspaces
+    model.reset()
+    torch.cuda.synchronize()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
     model.prefill(prompt, tok)
+    p1.record()
     for _ in range(3):
         model.step_dev(tok)
     torch.cuda.synchronize()
+    prefill_ms = p0.elapsed_time(p1)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
@@ -489,7 +524,134 @@ def batch_decode_bench(cfg, batch, ctx, steps, seed):
     return {"batch": batch, "ctx": ctx, "steps": steps, "ms_per_step": ms, "tok_s": batch / (ms * 1e-3),
             "algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms * 1e-3) / 1e9,
             "frac_of_hbm_peak": step_bytes / (ms * 1e-3) / 1e9 / peak, "launches_per_step": launches,
-            "mode": "per-op, tensor-core GEMM path, CUDA graph"}
+            "operands": "fp16 activations x fp16 / in-kernel dequantised Q4_K weights, fp32 accumulation",
+            "mode": "per-op, tensor-core GEMM path, CUDA graph",
+            "prefill": {"tokens": batch * ctx, "ms": prefill_ms, "tok_s": batch * ctx / (prefill_ms * 1e-3),
+                        "note": "%d sequences x %d tokens through b200_decoder_prefill in groups of <= 32768 tokens"
+                                % (batch, ctx)}}
+
+
+def moe_sweep_bench(lib, sizes=(1, 64, 512, 4096)):
+    """The MoE layer of the H-Tiny shape at the token counts of the op-level configuration,
+    each against the roofline that bounds it: HBM (weights of the experts the tokens touch +
+    router + shared expert, read once) for few tokens, dense tensor peak for many."""
+    import torch
+    d, E, ne, K, SH, q = 1536, 512, 64, 6, 1024, 3
+    g = torch.Generator(device="cuda").manual_seed(4321)
+
+    def packed(n):
+        w = torch.randn(n, device="cuda", generator=g) * 0.02
+        out = torch.empty(n // 256 * 144, dtype=torch.uint8, device="cuda")
+        lib.b200_quantize(w, out, n, q)
+        return out
+
+    # two weight sets, alternated, so that a size whose weights fit the 126 MB L2 still streams from HBM
+    sets = []
+    for _ in range(2):
+        sets.append(dict(gates=packed(ne * E * d), ups=packed(ne * E * d), downs=packed(ne * d * E),
+                         sh=(packed(SH * d), packed(SH * d), packed(d * SH)),
+                         router=torch.randn(ne, d, device="cuda", generator=g) / d ** 0.5,
+                         bias=torch.randn(ne, device="cuda", generator=g) * 0.5 / ne))    # on the scale of a probability: skewed, ragged loads
+    hbm_peak, _ = peaks()
+    tf_peak = 1646.6
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            tf_peak = float(json.load(f).get("bf16_tflops", tf_peak))
+    out = []
+    for T in sizes:
+        x = torch.randn(T, d, device="cuda", generator=g)
+        y = torch.empty(T, d, device="cuda")
+        idx = torch.empty(T, K, dtype=torch.int32, device="cuda")
+        state = {"i": 0}
+
+        def run():
+            w = sets[state["i"] & 1]
+            state["i"] += 1
+            lib.b200_moe_forward_bias_half(x, w["router"], w["bias"], w["gates"], w["ups"], w["downs"], w["sh"][0],
+                                           w["sh"][1], w["sh"][2], y, None, idx, None, None, None, None, T, d, E, ne, K,
+                                           SH, q)
+
+        _, ms = time_kernel_gbs(run, 0, iters=20)
+        touched = int(torch.unique(idx).numel())
+        wbytes = (touched * 3 * E * d + 3 * SH * d) // 256 * 144 + ne * d * 4
+        flops = T * K * 3 * 2 * E * d + T * 3 * 2 * SH * d
+        gbs, tfs = wbytes / (ms * 1e-3) / 1e9, flops / (ms * 1e-3) / 1e12
+        bound = "hbm" if wbytes / (hbm_peak * 1e9) > flops / (tf_peak * 1e12) else "tensor"
+        out.append({"tokens": T, "ms_per_layer": ms, "experts_touched": touched, "weight_bytes": wbytes,
+                    "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / hbm_peak, "tflops": tfs,
+                    "frac_of_dense_peak": tfs / tf_peak, "bound": bound,
+                    "operands": "fp32 (exact dequantised weights)" if T < 32 else "fp16 x in-kernel dequantised Q4_K, fp32 accumulation"})
+    return out
+
+
+def mamba_ops_bench(lib):
+    """Mamba-2 at the op level (the shapes of the op-level configuration): b200_mamba2_forward_half
+    over [8, 4096] tokens with 48 heads x 64 and d_state 128 - causal conv, chunked SSD scan,
+    gated norm at the full inner width of 3072; the projections in front and behind run at a
+    model width of 256 so that they stay a small part (their time is inside the figure) - and
+    the single-token state update for 64 sequences (b200_mamba2_step_batched)."""
+    import torch
+    B, T, d, nh, dh, ds, k, q = 8, 4096, 256, 48, 64, 128, 4, 3
+    d_inner, conv_dim = nh * dh, nh * dh + 2 * ds
+    proj = d_inner + conv_dim + nh
+    g = torch.Generator(device="cuda").manual_seed(99)
+
+    def packed(n, std):
+        w = torch.randn(n, device="cuda", generator=g) * std
+        o = torch.empty(n // 256 * 144, dtype=torch.uint8, device="cuda")
+        lib.b200_quantize(w, o, n, q)
+        return o
+
+    w_in, w_out = packed(proj * d, 0.05), packed(d * d_inner, 0.02)
+    conv_w = torch.randn(conv_dim * k, device="cuda", generator=g) * 0.1
+    conv_b = torch.zeros(conv_dim, device="cuda")
+    dt_bias = torch.log(torch.expm1(torch.rand(nh, device="cuda", generator=g) * (1e-1 - 1e-3) + 1e-3))
+    a_log = torch.rand(nh, device="cuda", generator=g) * float(np.log(16.0))
+    D = torch.randn(nh, device="cuda", generator=g)
+    norm_w = torch.ones(d_inner, device="cuda")
+    x = torch.randn(B * T * d, device="cuda", generator=g)
+    state = torch.zeros(B * nh * dh * ds, device="cuda")
+    out = torch.empty(B * T * d, device="cuda")
+
+    def fwd():
+        lib.b200_mamba2_forward_half(x, w_in, conv_w, conv_b, dt_bias, a_log, D, norm_w, w_out, state, out, B, T, d,
+                                     d_inner, conv_dim, nh, dh, ds, k, 1e-5, q)
+
+    # algorithmic traffic of the scan itself: x and y [B,T,d_inner] bf16-sized in the op-level
+    # description; here the post-projection tensors are fp32: x, B, C, dt in, y out, state in + out
+    scan_bytes = B * T * (d_inner * 4 + 2 * ds * 4 + nh * 4 + d_inner * 4) + 2 * B * nh * dh * ds * 4
+    config_bytes = 451e6          # the same tensors with x and y in bf16, as the op-level configuration states them
+    scan_flops = B * nh * (T // 128) * 2 * 128 * (128 * ds + 128 * dh + 2 * ds * dh)
+    gbs, ms = time_kernel_gbs(fwd, scan_bytes, iters=5)
+    peak, _ = peaks()
+    res = {"ssd_prefill": {"shape": "[8, 4096, 48, 64], d_state 128, chunk 128, Q4_K projections at width 256 included",
+                           "ms": ms, "tok_s": B * T / (ms * 1e-3), "algorithmic_bytes": scan_bytes,
+                           "algorithmic_bytes_bf16_boundary": config_bytes,
+                           "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / peak,
+                           "scan_tflops": scan_flops / (ms * 1e-3) / 1e12,
+                           "operands": "fp16 per-head operands, fp32 dt / decays / carry / accumulation"}}
+    # batch-64 single-token update: state read + written
+    Bs = 64
+    xs = torch.randn(Bs * d, device="cuda", generator=g)
+    conv_state = torch.zeros(Bs * conv_dim * (k - 1), device="cuda")
+    # several state sets, alternated: 64 sequences are 100 MB, below the L2 size
+    states = [torch.zeros(Bs * nh * dh * ds, device="cuda") for _ in range(3)]
+    outs = torch.empty(Bs * d, device="cuda")
+    it = {"i": 0}
+
+    def step():
+        st = states[it["i"] % 3]
+        it["i"] += 1
+        lib.b200_mamba2_step_batched(xs, w_in, conv_w, conv_b, dt_bias, a_log, D, norm_w, w_out, conv_state, st, outs, Bs,
+                                     d, d_inner, conv_dim, nh, dh, ds, k, 1e-5, q)
+
+    step_bytes = 2 * Bs * nh * dh * ds * 4
+    gbs2, ms2 = time_kernel_gbs(step, step_bytes, iters=30)
+    res["state_update_b64"] = {"shape": "64 sequences x [48, 64, 128] fp32 state", "ms": ms2,
+                               "algorithmic_bytes": step_bytes, "achieved_gbs": gbs2, "frac_of_hbm_peak": gbs2 / peak,
+                               "operands": "fp32"}
+    return res
 
 
 def gemm_only_bench():
@@ -571,6 +733,7 @@ def main():
     ap.add_argument("--graph", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--small", action="store_true", help="4-layer model (development only; not a bench number)")
+    ap.add_argument("--quick", action="store_true", help="skip the op-level and batch-64 blocks")
     ap.add_argument("--ep-graph", action="store_true",
                     help="N > 1: also time the dispatch-free expert-parallel layer replayed as one CUDA graph "
                          "(NCCL all-reduce captured with it)")
@@ -716,14 +879,16 @@ def main():
     q4k_bytes = proj_n * d // 256 * 144
     q4k_gbs, q4k_ms = time_kernel_gbs(q4k_call, q4k_bytes, iters=len(mamba_layers) * 2)
     moe = moe_layer_bench(lib, rank, world, graph=args.ep_graph)
-    batch64 = None
-    if world == 1 and B == 1 and not args.small:
+    batch64 = moe_sweep = mamba_ops = None
+    if world == 1 and B == 1 and not args.small and not args.quick:
         model.close()
         model = None
-        batch64 = batch_decode_bench(cfg, 64, 256, 16, seed=rank)
+        moe_sweep = moe_sweep_bench(lib)
+        mamba_ops = mamba_ops_bench(lib)
+        batch64 = batch_decode_bench(cfg, 64, 4096, 16, seed=rank)
 
     default_workload = (B == 1 and args.ctx == 4096 and args.fused == 1 and args.graph == 1 and not args.small)
-    step_traffic = STEP_DRAM_TRAFFIC_BYTES if default_workload else None
+    step_traffic = measured_step_traffic(launches_per_step) if default_workload else None
     if rank == 0:
         tok_s = B * args.steps * world / (ms_dev * 1e-3)
         e2e_tok_s = B * args.steps * world / (ms_e2e * 1e-3)
@@ -732,6 +897,8 @@ def main():
             "metric": "decode tok/s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": W, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(cfg, args),
+            "dtype_note": "the decode step computes in fp32 on exact dequantised weights (activations enter the "
+                          "dot products as fp16 head + tail pairs, 22 bits); every many-token block states its own operands",
             "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches_per_step * args.steps,
@@ -751,14 +918,19 @@ def main():
                                   "frac": q4k_gbs / peak, "kernel": "streamed Q4_K GEMV (in_proj [%d,%d])" % (proj_n, d),
                                   "ms_per_launch": q4k_ms, "algorithmic_bytes_per_launch": q4k_bytes},
             "moe_layer": moe,
+            "moe_sweep": moe_sweep,
+            "mamba_ops": mamba_ops,
             "batch64": batch64,
             "prefill": None if prefill_ms is None else {
                 "tokens": B * args.ctx, "ms": prefill_ms, "tok_s": B * args.ctx / (prefill_ms * 1e-3),
+                "operands": "fp16 activations x fp16 / in-kernel dequantised Q4_K weights, fp32 accumulation",
                 "mode": "b200_decoder_prefill: tensor-core GEMMs, chunked SSD scan, tensor-core attention, grouped MoE"},
         }
         if not args.no_cpu and world == 1:
             secs, info = cpu_decode_token_seconds(cfg, args.ctx, reps=8)
             line["cpu_baseline"] = dict(info, value=B / secs, unit="tok/s")
+            secs32, info32 = cpu_decode_token_seconds(cfg, args.ctx, reps=4, fp32_weights=True)
+            line["cpu_baseline_fp32"] = dict(info32, value=B / secs32, unit="tok/s")
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line))

@@ -54,6 +54,11 @@ unsigned long long workspace_generation();   // changes whenever a workspace add
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 int num_sms();
+// Second stream for work independent of the current stream's (see runtime.cu): between
+// side_begin() and side_end() stream() is the side stream; side_wait() joins.
+int side_begin();
+int side_end();
+int side_wait();
 
 // Status word of the kernels with bounded waits (0 = ok).  Device pointer, allocated
 // on first use; the check reads it back (synchronising copy) and clears it.

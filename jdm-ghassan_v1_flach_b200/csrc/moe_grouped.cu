@@ -117,6 +117,20 @@ int moe_forward_grouped(const float* x, const float* router_w, const float* rout
         int32_t* offsets = reinterpret_cast<int32_t*>(base + o_off);
         float* y = reinterpret_cast<float*>(base + o_y);
 
+        // The shared expert shares no data with routing, permutation, gather and the routed
+        // experts until the combine: it runs on the side stream next to them, straight into out.
+        if (shared) {
+            if ((rc = side_begin())) return rc;
+            rc = pack_rows_f16(xc, nullptr, 1, H(o_xs), T, d);
+            if (!rc)
+                rc = gemm(GEMM_EPI_SWIGLU, H(o_xs), T, sh_g, sh_u, sg16, su16, SH, nullptr, 1, T, SH, d, nullptr,
+                          H(o_sact), SH);
+            if (!rc)
+                rc = gemm(GEMM_EPI_STORE, H(o_sact), T, sh_d, nullptr, sd16, nullptr, d, nullptr, 1, T, d, SH, oc, nullptr, d);
+            const int rc2 = side_end();
+            if (rc) return rc;
+            if (rc2) return rc2;
+        }
         rc = moe_route(xc, router_w, router_bias, probs_cache ? probs_cache + t0 * ne : nullptr, idx, w, T, d, ne, K);
         if (rc) return rc;
         rc = moe_permutation(idx, NK, ne, grouped, offsets);
@@ -132,16 +146,7 @@ int moe_forward_grouped(const float* x, const float* router_w, const float* rout
         rc = gemm(GEMM_EPI_STORE, H(o_act), NK, downs, nullptr, d16, nullptr, (int64_t)ne * d, offsets, ne, (int)NK, d, E,
                   y, nullptr, d);
         if (rc) return rc;
-        // shared expert straight into out
-        if (shared) {
-            rc = pack_rows_f16(xc, nullptr, 1, H(o_xs), T, d);
-            if (rc) return rc;
-            rc = gemm(GEMM_EPI_SWIGLU, H(o_xs), T, sh_g, sh_u, sg16, su16, SH, nullptr, 1, T, SH, d, nullptr, H(o_sact),
-                      SH);
-            if (rc) return rc;
-            rc = gemm(GEMM_EPI_STORE, H(o_sact), T, sh_d, nullptr, sd16, nullptr, d, nullptr, 1, T, d, SH, oc, nullptr, d);
-            if (rc) return rc;
-        }
+        if (shared && (rc = side_wait())) return rc;
         const int64_t total = (int64_t)T * (d >> 2);
         const int grid = (int)std::min<int64_t>(ceil_div64(total, 256), (int64_t)num_sms() * 16);
         moe_combine_kernel<<<grid, 256, 0, stream()>>>(y, inv, w, oc, T, K, d, shared ? 1 : 0);

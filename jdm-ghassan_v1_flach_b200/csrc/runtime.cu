@@ -74,6 +74,35 @@ void Workspace::release() {
 
 Workspace& workspace(int which) { return g_ws[which]; }
 
+// ---- side stream ----------------------------------------------------------
+// Work that does not depend on what the current stream is doing (the shared expert of an
+// MoE layer next to the routing of the same tokens) is enqueued on a second stream between
+// side_begin() and side_end(); side_wait() makes the current stream wait for it.  Events
+// only: legal inside a stream capture (the side stream joins the capture and rejoins).
+static cudaStream_t g_side = nullptr, g_side_prev = nullptr;
+static cudaEvent_t g_side_fork = nullptr, g_side_join = nullptr;
+int side_begin() {
+    if (!g_side) {
+        B200_CUDA(cudaStreamCreateWithFlags(&g_side, cudaStreamNonBlocking));
+        B200_CUDA(cudaEventCreateWithFlags(&g_side_fork, cudaEventDisableTiming));
+        B200_CUDA(cudaEventCreateWithFlags(&g_side_join, cudaEventDisableTiming));
+    }
+    B200_CUDA(cudaEventRecord(g_side_fork, g_stream));
+    B200_CUDA(cudaStreamWaitEvent(g_side, g_side_fork, 0));
+    g_side_prev = g_stream;
+    g_stream = g_side;
+    return B200_OK;
+}
+int side_end() {
+    g_stream = g_side_prev;
+    B200_CUDA(cudaEventRecord(g_side_join, g_side));
+    return B200_OK;
+}
+int side_wait() {
+    B200_CUDA(cudaStreamWaitEvent(g_stream, g_side_join, 0));
+    return B200_OK;
+}
+
 }  // namespace b200
 
 using namespace b200;

@@ -332,6 +332,7 @@ static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t*
 // leaving the per-sequence state exactly where T decode steps would have left it:
 // ssm state, convolution window, KV pages, lengths.
 // ---------------------------------------------------------------------------
+constexpr int PREFILL_GROUP_TOKENS = 32768;
 __global__ void prefill_pos_kernel(int32_t* __restrict__ pos, int B, int T) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < B * T) pos[i] = i % T;
@@ -400,8 +401,11 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
     }
 }
 
-static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* next) {
-    const int B = dec->batch, d = dec->d;
+// Sequences [b0, b0 + B) of the decoder; tokens / next point at that group's first sequence.
+static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* next, int b0, int B) {
+    const int d = dec->d;
+    float *dx = dec->x + (int64_t)b0 * d, *dxb = dec->xb + (int64_t)b0 * d, *dlogits = dec->logits + (int64_t)b0 * dec->vocab;
+    const int32_t* page_table = dec->page_table + (int64_t)b0 * dec->max_pages;
     const int64_t NT = (int64_t)B * T;
     const int qd = dec->H * dec->hd, kvd = dec->KV * dec->hd;
     cudaStream_t st = stream();
@@ -462,14 +466,16 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
         LayerW& w = dec->L[l];
         if (dec->types[l] == 0) {
             STEP(mamba2_forward(xb, w.mamba_in, w.conv_w, w.conv_b, w.dt_bias, w.a_log, w.D, w.mamba_norm, w.mamba_out,
-                                w.ssm_state, y, B, T, p, kind, w.conv_state, want16 ? xb16 : nullptr));
+                                w.ssm_state + (int64_t)b0 * dec->d_inner * dec->mds, y, B, T, p, kind,
+                                w.conv_state + (int64_t)b0 * dec->conv_dim * std::max(dec->mk - 1, 1),
+                                want16 ? xb16 : nullptr));
         } else {
             STEP(lin(xb, w.wq, q, d, qd, want16 ? xb16 : nullptr));
             STEP(lin(xb, w.wk, k, d, kvd, want16 ? xb16 : nullptr));
             STEP(lin(xb, w.wv, v, d, kvd, want16 ? xb16 : nullptr));
             if (rope_on(dec))
                 STEP(b200_rope_forward_cached(q, k, pos, dec->inv_freq, NT, dec->H, dec->KV, dec->hd, dec->rope_type));
-            kv_prefill_kernel<<<dim3(ceil_div(kvd, 256), T, B), 256, 0, st>>>(k, v, w.k_pages, w.v_pages, dec->page_table, T,
+            kv_prefill_kernel<<<dim3(ceil_div(kvd, 256), T, B), 256, 0, st>>>(k, v, w.k_pages, w.v_pages, page_table, T,
                                                                             dec->max_pages, dec->page, kvd);
             B200_LAUNCH_CHECK("kv_prefill_kernel");
             STEP(b200_attention_forward_ex(q, k, v, at, nullptr, B, T, dec->H, dec->KV, dec->hd, dec->attn_scale, 0, nullptr));
@@ -484,17 +490,17 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
         STEP(residual_norm(l + 1 < dec->n_layers ? dec->L[l + 1].attn_norm : nullptr));
     }
     // logits of the last token of every sequence
-    last_rows_kernel<<<(unsigned)ceil_div64((int64_t)B * d, 256), 256, 0, st>>>(x, dec->x, B, T, d);
+    last_rows_kernel<<<(unsigned)ceil_div64((int64_t)B * d, 256), 256, 0, st>>>(x, dx, B, T, d);
     B200_LAUNCH_CHECK("last_rows_kernel");
-    STEP(b200_rmsnorm_forward(dec->x, dec->final_norm, dec->xb, nullptr, B, d, dec->eps));
-    STEP(b200_linear_forward_fp16(dec->xb, dec->lm_head, dec->logits, B, d, dec->vocab));
+    STEP(b200_rmsnorm_forward(dx, dec->final_norm, dxb, nullptr, B, d, dec->eps));
+    STEP(b200_linear_forward_fp16(dxb, dec->lm_head, dlogits, B, d, dec->vocab));
     if (dec->logits_scaling != 1.0f)
-        STEP(b200_scale_inplace(dec->logits, 1.0f / dec->logits_scaling, (int64_t)B * dec->vocab));
+        STEP(b200_scale_inplace(dlogits, 1.0f / dec->logits_scaling, (int64_t)B * dec->vocab));
     if (next) {
-        argmax_rows_kernel<<<B, 1024, 0, st>>>(dec->logits, dec->vocab, next);
+        argmax_rows_kernel<<<B, 1024, 0, st>>>(dlogits, dec->vocab, next);
         B200_LAUNCH_CHECK("argmax_rows_kernel");
     }
-    prefill_len_kernel<<<ceil_div(B, 128), 128, 0, st>>>(dec->len, dec->pos, B, T);
+    prefill_len_kernel<<<ceil_div(B, 128), 128, 0, st>>>(dec->len + b0, dec->pos + b0, B, T);
     B200_LAUNCH_CHECK("prefill_len_kernel");
 #undef STEP
     return B200_OK;
@@ -953,8 +959,14 @@ int b200_decoder_prefill(b200_decoder* dec, const int32_t* tokens_dev, int T, in
     B200_REQUIRE(T <= dec->max_ctx, "decoder_prefill: %d tokens exceed the context of %d", T, dec->max_ctx);
     B200_REQUIRE((int64_t)dec->batch * T <= 0x7fffffff / std::max(dec->K, 1), "decoder_prefill: batch * T too large");
     B200_REQUIRE(dec->batch <= 65535 && T <= 65535, "decoder_prefill: batch and T must be <= 65535");
-    rc = prefill(dec, tokens_dev, T, next_dev);
-    if (rc) return rc;
+    // Groups of sequences of at most PREFILL_GROUP_TOKENS tokens: bounds the prompt path's
+    // workspaces (tens of bytes per token and layer width) whatever the batch is.
+    const int group = std::max(1, std::min(dec->batch, PREFILL_GROUP_TOKENS / T));
+    for (int b0 = 0; b0 < dec->batch; b0 += group) {
+        const int B = std::min(group, dec->batch - b0);
+        rc = prefill(dec, tokens_dev + (int64_t)b0 * T, T, next_dev ? next_dev + b0 : nullptr, b0, B);
+        if (rc) return rc;
+    }
     if (dec->graph && dec->ws_generation != workspace_generation()) {
         drop_graph(dec);
         dec->launches = 0;
