@@ -654,6 +654,23 @@ def mamba_ops_bench(lib):
     return res
 
 
+def quantize_bench(lib):
+    """The load-time quantisers on one H-Tiny expert tensor (64 x 512 x 1536 fp32 = 201 MB in, larger than
+    L2): fp32 read + packed bytes written per second, per storage kind."""
+    import torch
+    n = 64 * 512 * 1536
+    x = torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)) * 0.02
+    peak, _ = peaks()
+    out = {}
+    for kind, name, be, bb in ((2, "q8_0", 32, 34), (0, "q4_0", 32, 18), (4, "q4_0_gguf_rule", 32, 18), (1, "q4_1", 32, 20),
+                               (3, "q4_k", 256, 144)):
+        dst = torch.empty(n // be * bb, dtype=torch.uint8, device="cuda")
+        nbytes = n * 4 + dst.numel()
+        gbs, ms = time_kernel_gbs(lambda: lib.b200_quantize(x, dst, n, kind), nbytes, iters=10)
+        out[name] = {"ms": ms, "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / peak, "weights_per_s": n / (ms * 1e-3)}
+    return out
+
+
 def gemm_only_bench():
     """The many-token kernels alone: fp16 and Q4_K linears of the in_proj shape at 4096 rows,
     and the MoE layer at 512 and 4096 tokens.  One JSON line; ~1 GB on the device."""
@@ -885,6 +902,7 @@ def main():
         model = None
         moe_sweep = moe_sweep_bench(lib)
         mamba_ops = mamba_ops_bench(lib)
+        quantizers = quantize_bench(lib)
         batch64 = batch_decode_bench(cfg, 64, 4096, 16, seed=rank)
 
     default_workload = (B == 1 and args.ctx == 4096 and args.fused == 1 and args.graph == 1 and not args.small)
@@ -920,6 +938,7 @@ def main():
             "moe_layer": moe,
             "moe_sweep": moe_sweep,
             "mamba_ops": mamba_ops,
+            "quantizers": quantizers,
             "batch64": batch64,
             "prefill": None if prefill_ms is None else {
                 "tokens": B * args.ctx, "ms": prefill_ms, "tok_s": B * args.ctx / (prefill_ms * 1e-3),

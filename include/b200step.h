@@ -120,9 +120,13 @@ int b200_decoder_launches_per_step(b200_decoder* dec, int* launches);
 int b200_decoder_step_bytes(b200_decoder* dec, double* bytes);
 
 /* ---- quantisers on the device (reference host code: quant::quantize_q8_0 /
- * q4_0 / q4_1, quantization/quantize.cpp:20-246; kind 3 = Q4_K, this library's own
- * single-pass quantiser).  n must be a multiple of the block size (32 or 256).
- * Bit-identical to the CPU functions for finite inputs. */
+ * q4_0 / q4_1, quantization/quantize.cpp:20-246): kind 0 Q4_0, 1 Q4_1, 2 Q8_0; kind 3 =
+ * Q4_K, this library's own single-pass quantiser; kind 4 = the Q4_0 layout filled by the
+ * rule of the reference's GGUF writer (format/gguf_codec.cpp:408-460: scale from the signed
+ * extreme, truncating codes).  n must be a multiple of the block size (256 for kind 3,
+ * else 32); src 16-byte and dst 8-byte aligned.  Bit-identical to the CPU functions,
+ * non-finite inputs included (the block becomes the zero block; under kind 4 a NaN that
+ * is not the extreme gets code 0). */
 int b200_quantize(const float* src, void* dst, int64_t n, int kind);
 
 #ifdef __cplusplus

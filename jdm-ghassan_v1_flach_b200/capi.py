@@ -13,11 +13,12 @@ import re
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 LIB_PATH = os.path.join(HERE, "libb200ops.so")
-HEADERS = [os.path.join(ROOT, "include", "b200ops.h"), os.path.join(ROOT, "include", "b200step.h")]
+HEADERS = [os.path.join(ROOT, "include", "b200ops.h"), os.path.join(ROOT, "include", "b200step.h"),
+           os.path.join(ROOT, "include", "b200gguf.h")]
 
 _SCALARS = {
     "int": C.c_int, "float": C.c_float, "int64_t": C.c_int64, "uint64_t": C.c_uint64,
-    "size_t": C.c_size_t, "int32_t": C.c_int32,
+    "size_t": C.c_size_t, "int32_t": C.c_int32, "double": C.c_double,
 }
 
 

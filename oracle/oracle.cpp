@@ -241,6 +241,31 @@ static void quant_block_q4_0(const float* x, u8* out) {
     }
 }
 
+// Q4_0 as the GGUF writer packs it (format/gguf_codec.cpp:408-460, GGML's
+// quantize_row_q4_0_ref): the scale follows the SIGNED extreme, d = vmax / -8 with vmax
+// the first element of largest magnitude; codes min(15, (int)(x / d + 8.5)), truncated.
+// A block that is all zero or holds a non-finite value becomes the zero block.
+static void quant_block_q4_0_ggml(const float* x, u8* out) {
+    float amax = 0.0f, vmax = 0.0f;
+    for (int i = 0; i < 32; ++i) {
+        const float a = std::fabs(x[i]);
+        if (a > amax) { amax = a; vmax = x[i]; }
+    }
+    const bool bad = !std::isfinite(amax) || amax == 0.0f;
+    if (bad) { wr16(out, f32_to_f16_bits(0.0f)); std::memset(out + 2, 0x88, 16); return; }
+    const float d = vmax / -8.0f;
+    const float id = 1.0f / d;
+    wr16(out, f32_to_f16_bits(d));
+    for (int j = 0; j < 16; ++j) {
+        // a NaN element never wins `a > amax`; its code is what the reference's float -> int
+        // conversion yields on x86 (INT_MIN) after the clamp: 0
+        const float f0 = x[j] * id + 8.5f, f1 = x[j + 16] * id + 8.5f;
+        const int lo = std::isnan(f0) ? 0 : iclamp((int)f0, 0, 15);
+        const int hi = std::isnan(f1) ? 0 : iclamp((int)f1, 0, 15);
+        out[2 + j] = (u8)((hi << 4) | lo);
+    }
+}
+
 static void quant_block_q4_1(const float* x, u8* out) {
     for (int i = 0; i < 32; ++i)
         if (!std::isfinite(x[i])) { std::memset(out, 0, 20); return; }
@@ -325,10 +350,12 @@ static void quant_block_q4_k(const float* x, u8* out) {
             qs[32 * g + l] = (u8)(q[64 * g + l] | (q[64 * g + 32 + l] << 4));
 }
 
+// kind 4: the Q4_0 layout (kind 0) filled by the GGUF writer's rule.
 ORA_API int ora_quantize(const float* src, void* dst, i64 n, int kind) {
-    const int be = kind_block_elems(kind);
+    const int layout = kind == 4 ? 0 : kind;
+    const int be = kind_block_elems(layout);
     if (n < 0 || n % be != 0) return -1;
-    const int bb = kind_block_bytes(kind);
+    const int bb = kind_block_bytes(layout);
     u8* out = (u8*)dst;
     const i64 nb = n / be;
 #pragma omp parallel for schedule(static) if (nb > 1024)
@@ -336,6 +363,7 @@ ORA_API int ora_quantize(const float* src, void* dst, i64 n, int kind) {
         const float* x = src + b * be;
         u8* o = out + b * bb;
         if (kind == 0) quant_block_q4_0(x, o);
+        else if (kind == 4) quant_block_q4_0_ggml(x, o);
         else if (kind == 1) quant_block_q4_1(x, o);
         else if (kind == 2) quant_block_q8_0(x, o);
         else quant_block_q4_k(x, o);

@@ -329,3 +329,45 @@ REF_API int ref_decode_step(void* h, int token, int position, float* logits_out)
         std::memcpy(logits_out, lp, sizeof(float) * static_cast<size_t>(s->cfg.vocab_size));
     });
 }
+
+// ---------------------------------------------------------------------------
+// GGUF: the reference's own writer and reader (format/gguf_codec.cpp).  Used to make
+// the committed fixture tests/golden/tiny.gguf and to check the device loader against
+// GGUFReader::read_tensor_quant / read_tensor_f32.
+// ---------------------------------------------------------------------------
+#include "format/gguf_codec.h"
+
+// n two-dimensional fp32 tensors [rows, cols] (cols == 0: one-dimensional [rows]) written in
+// the given GGML types by GGUFWriter.
+REF_API int ref_gguf_write(const char* path, int n, const char* const* names, const i64* rows, const i64* cols,
+                           const float* const* data, const int* ggml_types) {
+    return guarded([&] {
+        GGUFWriter w(path);
+        w.set_arch("granitehybrid");
+        w.set_model_name("b200-fixture");
+        w.set_hidden_size(64);
+        w.set_num_layers(1);
+        w.set_rms_eps(1e-5f);
+        w.add_custom_metadata("b200.fixture.answer", static_cast<uint64_t>(42));
+        for (int i = 0; i < n; ++i) {
+            std::vector<i64> shape = cols[i] > 0 ? std::vector<i64>{rows[i], cols[i]} : std::vector<i64>{rows[i]};
+            Tensor t(shape, DType::F32, Device::CPU);
+            std::memcpy(t.data_ptr(), data[i], sizeof(float) * static_cast<size_t>(t.numel()));
+            w.add_tensor(names[i], t, static_cast<GGMLType>(ggml_types[i]));
+        }
+        w.write();
+    });
+}
+
+// kind: 0 Q4_0, 1 Q4_1, 2 Q8_0 (read_tensor_quant: verbatim blocks or quantise on load); -2: fp32
+REF_API int ref_gguf_read(const char* path, const char* name, int kind, void* out, i64 cap, i64* nbytes) {
+    return guarded([&] {
+        GGUFReader r;
+        GAI_CHECK(r.open(path), std::string("cannot open ") + path);
+        Tensor t = kind == -2 ? r.read_tensor_f32(name)
+                              : r.read_tensor_quant(name, kind == 0 ? DType::Q4_0 : kind == 1 ? DType::Q4_1 : DType::Q8_0);
+        GAI_CHECK(static_cast<i64>(t.nbytes()) <= cap, "output buffer too small");
+        std::memcpy(out, t.data_ptr(), t.nbytes());
+        *nbytes = static_cast<i64>(t.nbytes());
+    });
+}

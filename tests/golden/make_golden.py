@@ -19,8 +19,15 @@ config1.npz  (`python tests/golden/make_golden.py config1`, about twenty minutes
            values of the eight largest logits, and mean / max |logit| (the weights are
            regenerated from the seed at test time, so the file stays a few KB).
 
-The fixtures are read by tests/test_golden.py and tests/test_gpu_golden_model.py; nothing
-at test time needs the reference sources.
+tiny.gguf  (`python tests/golden/make_golden.py gguf`) a GGUF v3 file written by the
+           reference's own GGUFWriter (format/gguf_codec.cpp:514-640) from the tensors of
+           tests/golden_gguf.py: F32, F16, Q8_0, Q4_1 and Q4_0 payloads (the last by the
+           writer's signed-extreme rule, :408-460); gguf_expected.npz holds what the
+           reference's GGUFReader returns for them (read_tensor_f32, and read_tensor_quant
+           to Q8_0 / Q4_0 / Q4_1: the verbatim and the quantise-on-load paths).
+
+The fixtures are read by tests/test_golden.py, tests/test_gpu_golden_model.py and
+tests/test_gguf.py; nothing at test time needs the reference sources.
 """
 import os
 import sys
@@ -102,7 +109,41 @@ def make_config1():
                 prompt_len=np.int32(CONFIG1_PROMPT))
 
 
+def make_gguf():
+    import ctypes as C
+    import golden_gguf as gg
+    from oracle_lib import ROOT
+    lib = C.CDLL(os.path.join(ROOT, "oracle", "_ref", "libgai_ref.so"))
+    lib.ref_last_error.restype = C.c_char_p
+    path = os.path.join(HERE, "tiny.gguf")
+    n = len(gg.TENSORS)
+    srcs = [np.ascontiguousarray(gg.source(t[0])) for t in gg.TENSORS]
+    names = (C.c_char_p * n)(*[t[0].encode() for t in gg.TENSORS])
+    rows = (C.c_int64 * n)(*[t[1] for t in gg.TENSORS])
+    cols = (C.c_int64 * n)(*[t[2] for t in gg.TENSORS])
+    data = (C.c_void_p * n)(*[a.ctypes.data for a in srcs])
+    types = (C.c_int * n)(*[t[3] for t in gg.TENSORS])
+    if lib.ref_gguf_write(path.encode(), n, names, rows, cols, data, types) != 0:
+        raise RuntimeError(lib.ref_last_error().decode())
+    expected = {}
+    for (name, r_, c_, _), a in zip(gg.TENSORS, srcs):
+        for kind, label in ((-2, "f32"), (2, "q8_0"), (0, "q4_0"), (1, "q4_1")):
+            if kind >= 0 and a.size % 32:
+                continue
+            buf = np.zeros(a.size * 4 + 64, np.uint8)
+            nb = C.c_int64()
+            if lib.ref_gguf_read(path.encode(), name.encode(), kind, buf.ctypes.data_as(C.c_void_p), C.c_int64(buf.size),
+                                 C.byref(nb)) != 0:
+                raise RuntimeError(lib.ref_last_error().decode())
+            expected[f"{name}/{label}"] = buf[:nb.value].copy()
+    np.savez_compressed(os.path.join(HERE, "gguf_expected.npz"), **expected)
+    print("tiny.gguf", os.path.getsize(path), "bytes;", len(expected), "expected reads")
+
+
 def main():
+    if len(sys.argv) > 1 and sys.argv[1] == "gguf":
+        make_gguf()
+        return
     if len(sys.argv) > 1 and sys.argv[1] == "config1":
         np.savez_compressed(os.path.join(HERE, "config1.npz"), **make_config1())
         print("config1.npz", os.path.getsize(os.path.join(HERE, "config1.npz")), "bytes")

@@ -15,8 +15,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 ORACLE_SO = os.path.join(ROOT, "oracle", "liboracle.so")
 REF_SO = os.path.join(ROOT, "oracle", "_ref", "libgai_ref.so")
 
-BLOCK_ELEMS = {0: 32, 1: 32, 2: 32, 3: 256}
-BLOCK_BYTES = {0: 18, 1: 20, 2: 34, 3: 144}
+BLOCK_ELEMS = {0: 32, 1: 32, 2: 32, 3: 256, 4: 32}
+BLOCK_BYTES = {0: 18, 1: 20, 2: 34, 3: 144, 4: 18}
 KIND_NAMES = {0: "q4_0", 1: "q4_1", 2: "q8_0", 3: "q4_k"}
 
 

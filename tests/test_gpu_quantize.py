@@ -6,7 +6,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+@pytest.mark.parametrize("kind", [0, 1, 2, 3, 4])
 def test_quantize_bit_exact(oracle, kind):
     from gpu_util import dev, empty, host, pkg
     from oracle_lib import packed_bytes
@@ -18,6 +18,9 @@ def test_quantize_bit_exact(oracle, kind):
     x[512:768] = 0.5                               # constant block (zero range)
     x[1024 + 7] = np.inf                           # non-finite -> zero block
     x[2048:2304] *= 1e-6
+    x[4096 + 3] = np.nan                           # zero block; kind 4: the element's code is 0
+    x[8192:8448] = -np.abs(x[8192:8448])           # all negative (kind 4: positive scale)
+    x[8448:8480] = np.float32(-0.125)              # every element the extreme
     want = oracle.quantize(x, kind)
     out = empty(packed_bytes(kind, n), torch.uint8)
     pkg.lib().b200_quantize(dev(x), out, n, kind)
@@ -48,3 +51,15 @@ def test_quantize_roundtrip_full_size(oracle):
     err = (xs - ys).abs().amax((1, 2))
     assert bool((err <= bound * 1.05).all())
     assert float((xs - ys).abs().mean()) < 1.5e-3
+
+
+def test_quantize_rejects_misaligned_buffers():
+    from gpu_util import B200Error, empty, pkg
+    x = torch.zeros(1024 + 1, device="cuda")
+    out = empty(2048, torch.uint8)
+    with pytest.raises(B200Error):
+        pkg.lib().b200_quantize(x[1:], out, 1024, 2)          # source not 16-byte aligned
+    with pytest.raises(B200Error):
+        pkg.lib().b200_quantize(x, out, 1000, 2)              # not whole blocks
+    with pytest.raises(B200Error):
+        pkg.lib().b200_quantize(x, out, 1024, 7)              # unknown kind
