@@ -229,6 +229,11 @@ int b200_attention_decode_ring_fp16_noalloc(const float* q, const uint16_t* kc, 
 
 /* ---- sampling tail: cuda_ops.h:289-293 ------------------------------------------ */
 int b200_topk_select(const float* logits, int V, int K, float* out_vals, int32_t* out_ids);  /* :289; outputs on device */
+/* cuda_ops.h:278, forward part (dlogits must be NULL: the gradient is a training op): sum over
+ * rows with a target in [0, V) of logZ - logit[target] + z_scale * logZ^2, and their count;
+ * host outputs, synchronises.  A negative target skips the row; a target >= V is an error. */
+int b200_softmax_cross_entropy(const float* logits, const int32_t* targets, float* dlogits, int64_t n, int V,
+                               double* out_loss_sum, int64_t* out_count, float z_scale);
 int b200_argmax_token(const float* logits, int V, int32_t* token_host);                      /* :290; synchronous D2H */
 int b200_argmax_token_device(const float* logits, int V, int32_t* token_dev);                /* extension: no sync */
 int b200_apply_rep_penalties(float* logits, int V, const int32_t* hist, int hist_n,

@@ -119,6 +119,54 @@ int b200_decoder_launches_per_step(b200_decoder* dec, int* launches);
  * shared per token), Mamba state read+written, KV read for the current length. */
 int b200_decoder_step_bytes(b200_decoder* dec, double* bytes);
 
+/* ---- sampling tail on the device ----------------------------------------------------
+ * The reference samples on the host after every token: Sampler::sample on a host copy of
+ * the logits, or - its CUDA fast path, Generator::generate, inference/generator.cpp:1038-1056 -
+ * penalties and top-K on the device, a copy of the K candidates to the host and
+ * Sampler::sample_candidates there.  Here the generator state (core/rng.h: xoshiro256**
+ * seeded by splitmix64), the token history and the pick stay in device memory. */
+typedef struct b200_sampling {          /* SamplingConfig, inference/sampler.h:9-24 */
+    float temperature, top_p, min_p, repetition_penalty, frequency_penalty, presence_penalty;
+    int32_t top_k, repetition_window, no_repeat_ngram, greedy;
+    uint64_t seed;
+} b200_sampling;
+/* The clamps of SamplingConfig::validate (inference/sampler.cpp:36-73), in place. */
+int b200_sampling_validate(b200_sampling* cfg);
+/* state_dev [streams, 4] uint64: stream i becomes Rng(seed + i) (core/rng.h:12-22). */
+int b200_rng_seed(uint64_t seed, uint64_t* state_dev, int streams);
+/* n values of Rng::uniform() (core/rng.h:39-41) from stream 0, which advances. */
+int b200_rng_uniform(uint64_t* state_dev, float* out_dev, int n);
+/* Sampler::sample_candidates (inference/sampler.cpp:194-266) for `rows` independent rows of
+ * K <= 2048 candidates each (vals / ids [rows, K], any order): sort by value, softmax at the
+ * temperature in double, min-p and top-p cuts, one uniform draw from row r's stream
+ * (rng_state_dev + 4 r).  temperature <= 0 picks the largest.  next_dev [rows]. */
+int b200_sample_candidates(const float* vals_dev, const int32_t* ids_dev, int K, int rows, const b200_sampling* cfg,
+                           uint64_t* rng_state_dev, int32_t* next_dev);
+/* Sampler::sample (inference/sampler.cpp:126-192) for `rows` rows of V logits, which are
+ * modified in place as the reference's are: repetition / frequency / presence penalties over
+ * the last repetition_window history tokens (0: all), the no-repeat n-gram ban, then greedy
+ * pick, unfiltered softmax draw, or top-k / top-p / min-p draw.  hist_dev [rows, hist_stride]
+ * int32 with hist_len_dev [rows] valid tokens each (oldest first; both NULL: no history);
+ * hist_stride <= 8192 (Generator::HIST_MAX).  cfg is validated first. */
+int b200_sample_logits(float* logits_dev, int V, int rows, const int32_t* hist_dev, int hist_stride,
+                       const int32_t* hist_len_dev, const b200_sampling* cfg, uint64_t* rng_state_dev, int32_t* next_dev);
+/* Makes b200_decoder_step / _prefill pick the next token by Sampler::sample instead of the
+ * arg-max: the decoder keeps, per sequence, the history of fed tokens (ring of 8192) and a
+ * generator stream Rng(cfg->seed + sequence), all on the device, so the step still runs
+ * without host synchronisation and replays as one graph.  cfg == NULL returns to greedy.
+ * History and streams start afresh here and at b200_decoder_reset. */
+int b200_decoder_set_sampling(b200_decoder* dec, const b200_sampling* cfg);
+/* Generator::score_tokens (inference/generator.cpp:1217-1294): the mean negative log-likelihood
+ * of tokens[1..T) given their prefixes (position i predicts token i + 1; mask_host, optional,
+ * [T] bytes: token i + 1 counts only if mask[i + 1] != 0), through the prompt kernels and a
+ * chunked lm_head + cross-entropy (cuda/kernels.cu:1113-1200; sums in double as the CPU
+ * function does, core/math_cpu.cpp:560-612).  Sequence 0 of an empty decoder (after create or
+ * reset) is used and afterwards holds the T tokens.  T is cut to the decoder's context.  The
+ * reference scores in windows of 512 tokens whose attention does not see earlier windows;
+ * here every position sees its whole prefix (identical for T <= 513). */
+int b200_decoder_score_tokens(b200_decoder* dec, const int32_t* tokens_host, int T, const uint8_t* mask_host,
+                              double* mean_nll, int64_t* n_scored);
+
 /* ---- quantisers on the device (reference host code: quant::quantize_q8_0 /
  * q4_0 / q4_1, quantization/quantize.cpp:20-246): kind 0 Q4_0, 1 Q4_1, 2 Q8_0; kind 3 =
  * Q4_K, this library's own single-pass quantiser; kind 4 = the Q4_0 layout filled by the

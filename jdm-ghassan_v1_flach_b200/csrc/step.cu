@@ -13,6 +13,7 @@
 #include "gemm.cuh"
 #include "linear.cuh"
 #include "persist.cuh"
+#include "sampler.cuh"
 #include "../../include/b200step.h"
 
 namespace b200 {
@@ -143,7 +144,16 @@ struct b200_decoder {
     unsigned int test_spin_limit = 0;          // test hook (b200_decoder_test_barrier)
     int test_skip_cta = -1;
     unsigned long long ws_generation = 0;      // workspace generation the captured graph was recorded at
+    // sampling (b200_decoder_set_sampling): per-sequence history ring, pushed-token counts and
+    // generator streams, all on the device; scratch of the selection kernels
+    bool sampling = false;
+    b200_sampling samp{};
+    int32_t *hist = nullptr, *hist_total = nullptr;
+    uint64_t* rng = nullptr;
+    void* samp_ws = nullptr;
+    size_t samp_ws_bytes = 0;
 };
+constexpr int DEC_HIST_CAP = 8192;             // Generator::HIST_MAX, inference/generator.h:96
 
 // RoPE is applied unless the decoder mirrors the reference Generator's handling of the
 // position word (b200_decoder_set_rope_refresh) on a model whose first layer is a Mamba layer.
@@ -161,6 +171,23 @@ static int dev_alloc(b200_decoder* dec, void** p, size_t bytes) {
 static void drop_graph(b200_decoder* dec) {
     if (dec->graph) cudaGraphExecDestroy(dec->graph);
     dec->graph = nullptr;
+}
+
+// The next token of sequences [b0, b0 + B) from their logits: the greedy arg-max, or - with
+// b200_decoder_set_sampling - Sampler::sample on the device after the T tokens just fed
+// (fed [B, T]) have joined the sequences' histories.  next == nullptr only records the history.
+static int pick_next(b200_decoder* dec, float* logits, const int32_t* fed, int T, int32_t* next, int b0, int B) {
+    if (!dec->sampling) {
+        if (!next) return B200_OK;
+        argmax_rows_kernel<<<B, 1024, 0, stream()>>>(logits, dec->vocab, next);
+        B200_LAUNCH_CHECK("argmax_rows_kernel");
+        return B200_OK;
+    }
+    int32_t* hist = dec->hist + (int64_t)b0 * DEC_HIST_CAP;
+    int rc = history_push_prompt(hist, DEC_HIST_CAP, dec->hist_total + b0, fed, B, T);
+    if (rc || !next) return rc;
+    return sample_rows(logits, dec->vocab, B, hist, DEC_HIST_CAP, dec->hist_total + b0, dec->samp, dec->rng + 4 * b0, next,
+                       dec->samp_ws);
 }
 
 // The op sequence of one token, enqueued on the library's current stream.
@@ -228,8 +255,7 @@ static int enqueue_step(b200_decoder* dec, const int32_t* tokens, int32_t* next)
     STEP(b200_linear_forward_fp16(dec->xb, dec->lm_head, dec->logits, B, d, dec->vocab));
     if (dec->logits_scaling != 1.0f)
         STEP(b200_scale_inplace(dec->logits, 1.0f / dec->logits_scaling, (int64_t)B * dec->vocab));
-    argmax_rows_kernel<<<B, 1024, 0, st>>>(dec->logits, dec->vocab, next);
-    B200_LAUNCH_CHECK("argmax_rows_kernel");
+    STEP(pick_next(dec, dec->logits, tokens, 1, next, 0, B));
 #undef STEP
     return B200_OK;
 }
@@ -320,8 +346,7 @@ static int enqueue_step_fused(b200_decoder* dec, const int32_t* tokens, int32_t*
     h.norm_w = dec->final_norm; h.y = dec->logits; h.y_stride = dec->vocab; h.out_scale = 1.0f / dec->logits_scaling;
     STEP(stream_gemv(h, KIND_F16, PRO_RMS, EPI_STORE));
     if (dry) return B200_OK;
-    argmax_rows_kernel<<<B, 1024, 0, st>>>(dec->logits, dec->vocab, next);
-    B200_LAUNCH_CHECK("argmax_rows_kernel");
+    STEP(pick_next(dec, dec->logits, tokens, 1, next, 0, B));
 #undef STEP
     return B200_OK;
 }
@@ -402,7 +427,12 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
 }
 
 // Sequences [b0, b0 + B) of the decoder; tokens / next point at that group's first sequence.
-static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* next, int b0, int B) {
+// score_targets (device, [B * T], optional): instead of the last token's logits, every row's
+// cross-entropy against its target is added to score_acc (cross_entropy_accumulate), the
+// lm_head running over SCORE_ROWS rows at a time.
+constexpr int SCORE_ROWS = 512;
+static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* next, int b0, int B,
+                   const int32_t* score_targets = nullptr, double* score_acc = nullptr) {
     const int d = dec->d;
     float *dx = dec->x + (int64_t)b0 * d, *dxb = dec->xb + (int64_t)b0 * d, *dlogits = dec->logits + (int64_t)b0 * dec->vocab;
     const int32_t* page_table = dec->page_table + (int64_t)b0 * dec->max_pages;
@@ -489,16 +519,30 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
                                         nullptr, nullptr, NT, d, dec->E, dec->ne, dec->K, dec->SH, dec->qkind));
         STEP(residual_norm(l + 1 < dec->n_layers ? dec->L[l + 1].attn_norm : nullptr));
     }
-    // logits of the last token of every sequence
-    last_rows_kernel<<<(unsigned)ceil_div64((int64_t)B * d, 256), 256, 0, st>>>(x, dx, B, T, d);
-    B200_LAUNCH_CHECK("last_rows_kernel");
-    STEP(b200_rmsnorm_forward(dx, dec->final_norm, dxb, nullptr, B, d, dec->eps));
-    STEP(b200_linear_forward_fp16(dxb, dec->lm_head, dlogits, B, d, dec->vocab));
-    if (dec->logits_scaling != 1.0f)
-        STEP(b200_scale_inplace(dlogits, 1.0f / dec->logits_scaling, (int64_t)B * dec->vocab));
-    if (next) {
-        argmax_rows_kernel<<<B, 1024, 0, st>>>(dlogits, dec->vocab, next);
-        B200_LAUNCH_CHECK("argmax_rows_kernel");
+    if (score_targets) {
+        const int V = dec->vocab;
+        const int rows_max = (int)std::min<int64_t>(SCORE_ROWS, NT);
+        void* sws;
+        STEP(workspace(WS_SAMPLE).ensure(256 + (size_t)rows_max * 8 + 256 + (size_t)rows_max * V * 4, &sws));
+        double* losses = reinterpret_cast<double*>(static_cast<char*>(sws) + 256);
+        float* lg = reinterpret_cast<float*>(static_cast<char*>(sws) + 256 + (((size_t)rows_max * 8 + 255) & ~(size_t)255));
+        for (int64_t r0 = 0; r0 < NT; r0 += SCORE_ROWS) {
+            const int rows = (int)std::min<int64_t>(SCORE_ROWS, NT - r0);
+            STEP(b200_rmsnorm_forward(x + r0 * d, dec->final_norm, xb + r0 * d, nullptr, rows, d, dec->eps));
+            STEP(b200_linear_forward_fp16(xb + r0 * d, dec->lm_head, lg, rows, d, V));
+            if (dec->logits_scaling != 1.0f) STEP(b200_scale_inplace(lg, 1.0f / dec->logits_scaling, (int64_t)rows * V));
+            STEP(cross_entropy_accumulate(lg, score_targets + r0, rows, V, 0.0f, losses, score_acc));
+        }
+        STEP(pick_next(dec, nullptr, tokens, T, nullptr, b0, B));
+    } else {
+        // logits of the last token of every sequence
+        last_rows_kernel<<<(unsigned)ceil_div64((int64_t)B * d, 256), 256, 0, st>>>(x, dx, B, T, d);
+        B200_LAUNCH_CHECK("last_rows_kernel");
+        STEP(b200_rmsnorm_forward(dx, dec->final_norm, dxb, nullptr, B, d, dec->eps));
+        STEP(b200_linear_forward_fp16(dxb, dec->lm_head, dlogits, B, d, dec->vocab));
+        if (dec->logits_scaling != 1.0f)
+            STEP(b200_scale_inplace(dlogits, 1.0f / dec->logits_scaling, (int64_t)B * dec->vocab));
+        STEP(pick_next(dec, dlogits, tokens, T, next, b0, B));
     }
     prefill_len_kernel<<<ceil_div(B, 128), 128, 0, st>>>(dec->len + b0, dec->pos + b0, B, T);
     B200_LAUNCH_CHECK("prefill_len_kernel");
@@ -665,9 +709,7 @@ static int enqueue_step_persistent(b200_decoder* dec, const int32_t* tokens, int
     h.norm_w = dec->final_norm; h.y = dec->logits; h.y_stride = dec->vocab; h.out_scale = 1.0f / dec->logits_scaling;
     rc = stream_gemv(h, KIND_F16, PRO_RMS, EPI_STORE);
     if (rc) return rc;
-    argmax_rows_kernel<<<1, 1024, 0, st>>>(dec->logits, dec->vocab, next);
-    B200_LAUNCH_CHECK("argmax_rows_kernel");
-    return B200_OK;
+    return pick_next(dec, dec->logits, tokens, 1, next, 0, 1);
 }
 
 static int enqueue(b200_decoder* dec, const int32_t* tokens, int32_t* next) {
@@ -784,11 +826,98 @@ int b200_decoder_create(b200_decoder** out, int batch, int vocab, int hidden, in
     return rc;
 }
 
+static int seed_sampling(b200_decoder* dec) {
+    B200_CUDA(cudaMemsetAsync(dec->hist_total, 0, (size_t)dec->batch * 4, stream()));
+    return b200_rng_seed(dec->samp.seed, dec->rng, dec->batch);
+}
+
+int b200_decoder_set_sampling(b200_decoder* dec, const b200_sampling* cfg) {
+    B200_REQUIRE(dec, "decoder_set_sampling: null handle");
+    drop_graph(dec);
+    dec->launches = 0;
+    if (!cfg) {
+        dec->sampling = false;
+        return B200_OK;
+    }
+    b200_sampling c = *cfg;
+    b200_sampling_validate(&c);
+    if (!dec->hist) {
+        int rc = dev_alloc(dec, reinterpret_cast<void**>(&dec->hist), (size_t)dec->batch * DEC_HIST_CAP * 4);
+        if (!rc) rc = dev_alloc(dec, reinterpret_cast<void**>(&dec->hist_total), (size_t)dec->batch * 4);
+        if (!rc) rc = dev_alloc(dec, reinterpret_cast<void**>(&dec->rng), (size_t)dec->batch * 32);
+        if (rc) return rc;
+    }
+    const size_t need = sample_workspace_bytes(c, dec->vocab, dec->batch);
+    if (need > dec->samp_ws_bytes) {
+        if (dec->samp_ws) B200_CUDA(cudaFree(dec->samp_ws));
+        dec->samp_ws = nullptr;
+        dec->samp_ws_bytes = 0;
+        B200_CUDA(cudaMalloc(&dec->samp_ws, need));
+        dec->samp_ws_bytes = need;
+    }
+    dec->samp = c;
+    dec->sampling = true;
+    return seed_sampling(dec);
+}
+
+int b200_decoder_score_tokens(b200_decoder* dec, const int32_t* tokens_host, int T, const uint8_t* mask_host,
+                              double* mean_nll, int64_t* n_scored) {
+    int rc = check_ready(dec);
+    if (rc) return rc;
+    B200_REQUIRE(tokens_host && mean_nll && T >= 0, "decoder_score_tokens: bad arguments");
+    B200_REQUIRE(dec->position == 0, "decoder_score_tokens: the sequences already hold %d tokens (reset first)", dec->position);
+    *mean_nll = 0.0;
+    if (n_scored) *n_scored = 0;
+    if (T < 2) return B200_OK;
+    T = std::min(T, std::min(dec->max_ctx, 65535));
+    // position i is scored against token i + 1 when that token is supervised; the last
+    // position has nothing to predict
+    std::vector<int32_t> host((size_t)2 * T);
+    for (int i = 0; i < T; ++i) {
+        host[i] = tokens_host[i];
+        const bool supervised = i + 1 < T && (!mask_host || mask_host[i + 1] != 0);
+        host[T + i] = supervised ? tokens_host[i + 1] : -100;
+        B200_REQUIRE(host[T + i] < dec->vocab, "decoder_score_tokens: token %d at %d is outside the vocabulary", host[T + i], i + 1);
+    }
+    // ids, targets and the accumulator in a buffer of their own (the library's workspaces are
+    // all in use by the prompt kernels)
+    const size_t acc_off = ((size_t)2 * T * 4 + 255) & ~(size_t)255;
+    void* buf = nullptr;
+    B200_CUDA(cudaMalloc(&buf, acc_off + 256));
+    int32_t* ids = static_cast<int32_t*>(buf);
+    double* acc = reinterpret_cast<double*>(static_cast<char*>(buf) + acc_off);
+    unsigned long long out[2] = {0, 0};
+    auto run = [&]() -> int {
+        B200_CUDA(cudaMemcpyAsync(ids, host.data(), (size_t)2 * T * 4, cudaMemcpyHostToDevice, stream()));
+        B200_CUDA(cudaMemsetAsync(acc, 0, 32, stream()));
+        const int prc = prefill(dec, ids, T, nullptr, 0, 1, ids + T, acc);
+        if (prc) return prc;
+        B200_CUDA(cudaMemcpyAsync(out, acc, 16, cudaMemcpyDeviceToHost, stream()));
+        B200_CUDA(cudaStreamSynchronize(stream()));
+        return B200_OK;
+    };
+    rc = run();
+    cudaFree(buf);
+    if (rc) return rc;
+    if (dec->graph && dec->ws_generation != workspace_generation()) {
+        drop_graph(dec);
+        dec->launches = 0;
+    }
+    dec->position = T;
+    double sum;
+    memcpy(&sum, &out[0], 8);
+    const int64_t n = (int64_t)out[1];
+    if (n_scored) *n_scored = n;
+    *mean_nll = n > 0 ? sum / (double)n : 0.0;
+    return B200_OK;
+}
+
 int b200_decoder_destroy(b200_decoder* dec) {
     if (!dec) return B200_OK;
     drop_graph(dec);
     if (dec->own_stream) cudaStreamDestroy(dec->own_stream);
     for (void* p : dec->owned) cudaFree(p);
+    if (dec->samp_ws) cudaFree(dec->samp_ws);
     if (dec->h_tok) cudaFreeHost(dec->h_tok);
     if (dec->h_next) cudaFreeHost(dec->h_next);
     delete dec;
@@ -853,6 +982,7 @@ int b200_decoder_reset(b200_decoder* dec) {
         }
     }
     dec->position = 0;
+    if (dec->sampling) return seed_sampling(dec);
     return B200_OK;
 }
 

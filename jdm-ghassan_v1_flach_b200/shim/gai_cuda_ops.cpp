@@ -304,7 +304,15 @@ void attention_backward_ex(const float*, const float*, const float*, const float
 void moe_aux_frac_gpu(const float*, const i32*, float*, float*, float*, i64, int, int, double*) { training("moe_aux_frac_gpu"); }
 double* moe_aux_begin() { training("moe_aux_begin"); }
 double moe_aux_end() { training("moe_aux_end"); }
-void softmax_cross_entropy(const float*, const i32*, float*, i64, int, double*, i64*, float) { training("softmax_cross_entropy"); }
+// The loss value alone (dlogits == nullptr) is what Generator::score_tokens asks for; with a
+// gradient buffer it is a training call.
+void softmax_cross_entropy(const float* logits, const i32* targets, float* dlogits, i64 n, int V, double* out_loss_sum,
+                           i64* out_count, float z_scale) {
+    if (dlogits) training("softmax_cross_entropy (with gradient)");
+    int64_t count = 0;
+    ck(b200_softmax_cross_entropy(logits, targets, nullptr, n, V, out_loss_sum, &count, z_scale), "softmax_cross_entropy");
+    if (out_count) *out_count = count;
+}
 void sce_acc_begin() { training("sce_acc_begin"); }
 void sce_accumulate(const float*, const i32*, float*, i64, int, float) { training("sce_accumulate"); }
 void sce_acc_end(double*, i64*) { training("sce_acc_end"); }

@@ -35,6 +35,7 @@ typedef int8_t i8;
 typedef uint16_t u16;
 typedef int32_t i32;
 typedef int64_t i64;
+typedef uint64_t u64;
 
 #define ORA_API extern "C" __attribute__((visibility("default")))
 
@@ -615,6 +616,211 @@ ORA_API void ora_rep_penalties(float* logits, int V, const i32* hist, int hist_n
         if (freq != 0.0f) l -= freq * (float)count[t];
         if (pres != 0.0f) l -= pres;
     }
+}
+
+// ----------------------------------------------------------------------------
+// Sampling tail: the generator (core/rng.h:8-45), the sampler (inference/sampler.cpp)
+// and the cross-entropy used for perplexity (core/math_cpu.cpp:560-612, forward part).
+// ----------------------------------------------------------------------------
+
+// core/rng.h:12-22: four splitmix64 outputs of the running seed fill the state.
+ORA_API void ora_rng_seed(u64 seed, u64* s) {
+    for (int i = 0; i < 4; ++i) {
+        seed += 0x9E3779B97F4A7C15ULL;
+        u64 z = seed;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+        s[i] = z ^ (z >> 31);
+    }
+}
+static inline u64 rotl64(u64 x, int k) { return (x << k) | (x >> (64 - k)); }
+// core/rng.h:24-35 (xoshiro256**).
+ORA_API u64 ora_rng_next(u64* s) {
+    const u64 r = rotl64(s[1] * 5, 7) * 9;
+    const u64 t = s[1] << 17;
+    s[2] ^= s[0];
+    s[3] ^= s[1];
+    s[1] ^= s[2];
+    s[0] ^= s[3];
+    s[2] ^= t;
+    s[3] = rotl64(s[3], 45);
+    return r;
+}
+// core/rng.h:39-41: the top 24 bits as a float in [0, 1).
+ORA_API float ora_rng_uniform(u64* s) { return (float)((ora_rng_next(s) >> 40) * (1.0 / 16777216.0)); }
+
+// SamplingConfig::validate, inference/sampler.cpp:36-73.  cfg = {temperature, top_p, min_p,
+// repetition_penalty, frequency_penalty, presence_penalty}, icfg = {top_k, repetition_window,
+// no_repeat_ngram, greedy}.
+ORA_API void ora_sampling_validate(float* f, int* ic) {
+    if (!std::isfinite(f[0]) || f[0] < 0.0f) f[0] = 0.0f;
+    if (f[0] > 5.0f) f[0] = 5.0f;
+    if (!std::isfinite(f[1]) || f[1] < 0.0f) f[1] = 1.0f;
+    if (f[1] > 1.0f) f[1] = 1.0f;
+    if (!std::isfinite(f[2]) || f[2] < 0.0f) f[2] = 0.0f;
+    if (f[2] >= 1.0f) f[2] = 0.0f;
+    if (ic[0] < 0) ic[0] = 0;
+    if (ic[0] > 2048) ic[0] = 2048;
+    if (!std::isfinite(f[3]) || f[3] <= 0.0f) f[3] = 1.0f;
+    if (f[3] > 5.0f) f[3] = 5.0f;
+    if (!std::isfinite(f[4])) f[4] = 0.0f;
+    if (!std::isfinite(f[5])) f[5] = 0.0f;
+    f[4] = std::min(5.0f, std::max(-5.0f, f[4]));
+    f[5] = std::min(5.0f, std::max(-5.0f, f[5]));
+    ic[1] = std::min(8192, std::max(0, ic[1]));
+    if (ic[2] < 0) ic[2] = 0;
+    if (ic[2] == 1) ic[2] = 2;
+    if (ic[2] > 8) ic[2] = 8;
+}
+
+namespace {
+struct Cand { float v; i32 id; };
+// Candidates in descending value; equal values by ascending id (the reference's std::sort
+// leaves the order of equal values unspecified; this is the order the device uses).
+void sort_candidates(std::vector<Cand>& c) {
+    std::sort(c.begin(), c.end(), [](const Cand& a, const Cand& b) { return a.v != b.v ? a.v > b.v : a.id < b.id; });
+}
+// Sampler::draw_from_scratch, inference/sampler.cpp:206-266.
+i32 draw_sorted(const std::vector<Cand>& c, float temperature, float top_p, float min_p, u64* rng) {
+    if (!(temperature > 0.0f)) return c[0].id;
+    const float inv_t = 1.0f / temperature;
+    const float mx = c[0].v;
+    std::vector<double> probs(c.size());
+    double sum = 0.0;
+    for (size_t i = 0; i < c.size(); ++i) {
+        probs[i] = std::exp((double)((c[i].v - mx) * inv_t));
+        sum += probs[i];
+    }
+    if (!std::isfinite(sum) || sum <= 0.0) return c[0].id;
+    for (size_t i = 0; i < c.size(); ++i) probs[i] /= sum;
+    size_t limit = c.size();
+    if (min_p > 0.0f) {
+        const double thresh = min_p * probs[0];
+        size_t n = 0;
+        while (n < c.size() && probs[n] >= thresh) ++n;
+        limit = std::max<size_t>(1, n);
+    }
+    if (top_p > 0.0f && top_p < 1.0f) {
+        double cum = 0.0;
+        size_t n = 0;
+        while (n < limit) {
+            cum += probs[n];
+            ++n;
+            if (cum >= (double)top_p) break;
+        }
+        limit = std::max<size_t>(1, n);
+    }
+    double renorm = 0.0;
+    for (size_t i = 0; i < limit; ++i) renorm += probs[i];
+    const double r = (double)ora_rng_uniform(rng) * renorm;
+    double acc = 0.0;
+    for (size_t i = 0; i < limit; ++i) {
+        acc += probs[i];
+        if (r <= acc) return c[i].id;
+    }
+    return c[limit - 1].id;
+}
+}  // namespace
+
+// Sampler::sample_candidates, inference/sampler.cpp:194-204: the device top-K, sorted, drawn.
+ORA_API i32 ora_sample_candidates(const float* vals, const i32* ids, int K, float temperature, float top_p,
+                                  float min_p, u64* rng) {
+    std::vector<Cand> c((size_t)K);
+    for (int i = 0; i < K; ++i) c[i] = Cand{vals[i], ids[i]};
+    sort_candidates(c);
+    return draw_sorted(c, temperature, top_p, min_p, rng);
+}
+
+// Sampler::sample, inference/sampler.cpp:126-192 (with apply_penalties :75-107 and
+// ban_no_repeat_ngram :109-124).  The logits are modified in place like the reference's.
+// f / ic as in ora_sampling_validate (already validated).
+ORA_API i32 ora_sample(float* logits, int vocab, const i32* hist, int nh, const float* f, const int* ic, u64* rng) {
+    const float temperature = f[0], top_p = f[1], min_p = f[2], rep_pen = f[3], freq_pen = f[4], pres_pen = f[5];
+    const int top_k = ic[0], window_cfg = ic[1], ngram = ic[2], greedy = ic[3];
+    const bool rep = rep_pen != 1.0f, freq = freq_pen != 0.0f, pres = pres_pen != 0.0f;
+    if (nh > 0 && (rep || freq || pres)) {
+        const int window = window_cfg > 0 ? std::min(nh, window_cfg) : nh;
+        std::vector<i32> win;
+        for (int i = nh - window; i < nh; ++i)
+            if (hist[i] >= 0 && hist[i] < vocab) win.push_back(hist[i]);
+        std::sort(win.begin(), win.end());
+        for (size_t i = 0; i < win.size();) {
+            size_t j = i + 1;
+            while (j < win.size() && win[j] == win[i]) ++j;
+            float& l = logits[win[i]];
+            if (rep) l = (l > 0.0f) ? l / rep_pen : l * rep_pen;
+            if (freq) l -= freq_pen * (float)(j - i);
+            if (pres) l -= pres_pen;
+            i = j;
+        }
+    }
+    if (ngram > 0 && nh >= ngram - 1) {
+        const int pre = ngram - 1;
+        for (int i = 0; i + ngram <= nh; ++i) {
+            bool match = true;
+            for (int k = 0; k < pre; ++k)
+                if (hist[i + k] != hist[nh - pre + k]) { match = false; break; }
+            if (!match) continue;
+            const i32 nxt = hist[i + pre];
+            if (nxt >= 0 && nxt < vocab) logits[nxt] = -1e30f;
+        }
+    }
+    if (greedy || temperature <= 0.0f || top_k == 1) return ora_argmax(logits, vocab);
+    const bool no_filter = (top_k <= 0 || top_k >= vocab) && (top_p <= 0.0f || top_p >= 1.0f) && min_p <= 0.0f;
+    if (no_filter) {
+        // the largest logit (first of equals) changes places with element 0, then one pass
+        std::vector<Cand> c((size_t)vocab);
+        for (int i = 0; i < vocab; ++i) c[i] = Cand{logits[i], i};
+        size_t bi = 0;
+        for (size_t i = 1; i < c.size(); ++i)
+            if (c[i].v > c[bi].v) bi = i;
+        if (bi != 0) std::swap(c[0], c[bi]);
+        const float inv_t = 1.0f / temperature;
+        const float mx = c[0].v;
+        std::vector<double> probs(c.size());
+        double sum = 0.0;
+        for (size_t i = 0; i < c.size(); ++i) {
+            probs[i] = std::exp((double)((c[i].v - mx) * inv_t));
+            sum += probs[i];
+        }
+        if (!std::isfinite(sum) || sum <= 0.0) return c[0].id;
+        const double r = (double)ora_rng_uniform(rng) * sum;
+        double acc = 0.0;
+        for (size_t i = 0; i < c.size(); ++i) {
+            acc += probs[i];
+            if (r <= acc) return c[i].id;
+        }
+        return c.back().id;
+    }
+    const int k = (top_k > 0 && top_k < vocab) ? top_k : vocab;
+    std::vector<Cand> c((size_t)vocab);
+    for (int i = 0; i < vocab; ++i) c[i] = Cand{logits[i], i};
+    sort_candidates(c);
+    c.resize((size_t)k);
+    return draw_sorted(c, temperature, top_p, min_p, rng);
+}
+
+// core/math_cpu.cpp:560-612, forward part: rows with a target in [0, V) contribute
+// logZ - logit[target] (+ z_scale * logZ^2), everything accumulated in double.
+ORA_API void ora_softmax_cross_entropy(const float* logits, const i32* targets, i64 n, int V, float z_scale,
+                                       double* loss_sum, i64* count) {
+    double total = 0.0;
+    i64 cnt = 0;
+    for (i64 i = 0; i < n; ++i) {
+        const i32 tgt = targets[i];
+        if (tgt < 0 || tgt >= V) continue;
+        ++cnt;
+        const float* row = logits + i * V;
+        float mx = row[0];
+        for (int j = 1; j < V; ++j) mx = std::max(mx, row[j]);
+        double sum = 0.0;
+        for (int j = 0; j < V; ++j) sum += std::exp((double)(row[j] - mx));
+        const double logZ = std::log(sum) + (double)mx;
+        total += logZ - (double)row[tgt];
+        if (z_scale != 0.0f) total += (double)z_scale * logZ * logZ;
+    }
+    *loss_sum = total;
+    *count = cnt;
 }
 
 // ----------------------------------------------------------------------------

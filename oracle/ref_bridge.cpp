@@ -371,3 +371,76 @@ REF_API int ref_gguf_read(const char* path, const char* name, int kind, void* ou
         *nbytes = static_cast<i64>(t.nbytes());
     });
 }
+
+// ---------------------------------------------------------------------------
+// Sampling tail: the reference's Sampler (inference/sampler.cpp), its generator
+// (core/rng.h) and the cross-entropy behind Generator::score_tokens.
+// ---------------------------------------------------------------------------
+#include "inference/sampler.h"
+
+static SamplingConfig sampling_of(const float* f, const int* ic, u64 seed) {
+    SamplingConfig c;
+    c.temperature = f[0]; c.top_p = f[1]; c.min_p = f[2]; c.repetition_penalty = f[3];
+    c.frequency_penalty = f[4]; c.presence_penalty = f[5];
+    c.top_k = ic[0]; c.repetition_window = ic[1]; c.no_repeat_ngram = ic[2]; c.greedy = ic[3] != 0;
+    c.seed = seed;
+    return c;
+}
+
+// SamplingConfig::validate on the same packed fields.
+REF_API int ref_sampling_validate(float* f, int* ic) {
+    return guarded([&] {
+        SamplingConfig c = sampling_of(f, ic, 1);
+        c.validate();
+        f[0] = c.temperature; f[1] = c.top_p; f[2] = c.min_p; f[3] = c.repetition_penalty;
+        f[4] = c.frequency_penalty; f[5] = c.presence_penalty;
+        ic[0] = c.top_k; ic[1] = c.repetition_window; ic[2] = c.no_repeat_ngram; ic[3] = c.greedy ? 1 : 0;
+    });
+}
+
+// n_draws calls of Sampler::sample on fresh copies of the same logits (one Sampler, so the
+// generator runs on from draw to draw).
+REF_API int ref_sampler_sample(const float* logits, int V, const i32* hist, int nh, const float* f, const int* ic,
+                               u64 seed, int n_draws, i32* out) {
+    return guarded([&] {
+        Sampler s(sampling_of(f, ic, seed));
+        std::vector<i32> h(hist, hist + nh);
+        std::vector<float> work(static_cast<size_t>(V));
+        for (int i = 0; i < n_draws; ++i) {
+            std::memcpy(work.data(), logits, sizeof(float) * static_cast<size_t>(V));
+            out[i] = s.sample(work.data(), V, h);
+        }
+    });
+}
+
+REF_API int ref_sampler_candidates(const float* vals, const i32* ids, int K, const float* f, const int* ic, u64 seed,
+                                   int n_draws, i32* out) {
+    return guarded([&] {
+        Sampler s(sampling_of(f, ic, seed));
+        for (int i = 0; i < n_draws; ++i) out[i] = s.sample_candidates(vals, ids, K);
+    });
+}
+
+REF_API int ref_rng_uniform(u64 seed, int n, float* out) {
+    return guarded([&] {
+        Rng r(seed);
+        for (int i = 0; i < n; ++i) out[i] = r.uniform();
+    });
+}
+
+REF_API int ref_softmax_cross_entropy(const float* logits, const i32* targets, i64 n, int V, float z_scale,
+                                      double* loss_sum, i64* count) {
+    return guarded([&] { cpu::softmax_cross_entropy(logits, targets, nullptr, n, V, loss_sum, count, z_scale); });
+}
+
+// Generator::score_tokens (inference/generator.cpp:1217-1294): mean negative log-likelihood.
+REF_API int ref_score_tokens(void* h, const i32* tokens, int T, const unsigned char* mask, double* mean_nll,
+                             i64* n_scored) {
+    return guarded([&] {
+        RefSession* s = static_cast<RefSession*>(h);
+        std::vector<i32> t(tokens, tokens + T);
+        std::vector<u8> m;
+        if (mask) m.assign(mask, mask + T);
+        *mean_nll = s->gen->score_tokens(t, mask ? &m : nullptr, n_scored, nullptr);
+    });
+}

@@ -26,7 +26,11 @@ tiny.gguf  (`python tests/golden/make_golden.py gguf`) a GGUF v3 file written by
            reference's GGUFReader returns for them (read_tensor_f32, and read_tensor_quant
            to Q8_0 / Q4_0 / Q4_1: the verbatim and the quantise-on-load paths).
 
-The fixtures are read by tests/test_golden.py, tests/test_gpu_golden_model.py and
+sampler.npz (`python tests/golden/make_golden.py sampler`) draws of the reference's Sampler
+           (inference/sampler.cpp) for the configurations of tests/sampler_cases.py, 500
+           outputs of its generator (core/rng.h) and one cross-entropy sum (core/math_cpu.cpp:560).
+
+The fixtures are read by tests/test_sampler_oracle.py, tests/test_golden.py, tests/test_gpu_golden_model.py and
 tests/test_gguf.py; nothing at test time needs the reference sources.
 """
 import os
@@ -140,7 +144,26 @@ def make_gguf():
     print("tiny.gguf", os.path.getsize(path), "bytes;", len(expected), "expected reads")
 
 
+def make_sampler():
+    import sampler_cases as sc
+    from oracle_lib import Ref
+    ref = Ref()
+    out = {}
+    for name, cfg in sc.CONFIGS.items():
+        for seed in (1, 2):
+            out[f"{name}/{seed}"] = ref.sample(sc.logits(seed), sc.history(seed), cfg, 77 + seed, sc.DRAWS)
+    out["uniform/42"] = ref.rng_uniform(42, 500)
+    t = np.array([5, -100, 999, 0], np.int32)
+    total, count = ref.cross_entropy(sc.logits(3, 4000).reshape(4, 1000), t, 1e-4)
+    out["ce/targets"], out["ce/sum"], out["ce/count"] = t, np.float64(total), np.int64(count)
+    np.savez_compressed(os.path.join(HERE, "sampler.npz"), **out)
+    print("sampler.npz:", len(out), "arrays")
+
+
 def main():
+    if len(sys.argv) > 1 and sys.argv[1] == "sampler":
+        make_sampler()
+        return
     if len(sys.argv) > 1 and sys.argv[1] == "gguf":
         make_gguf()
         return

@@ -28,6 +28,20 @@ TINY = dict(vocab=512, hidden=256, n_layers=4, layer_types=[0, 1, 0, 1],
             attn_scale=0.0078125, logits_scaling=6.0)
 
 
+class B200Sampling(C.Structure):
+    """struct b200_sampling of include/b200step.h."""
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("min_p", C.c_float), ("repetition_penalty", C.c_float),
+                ("frequency_penalty", C.c_float), ("presence_penalty", C.c_float), ("top_k", C.c_int32),
+                ("repetition_window", C.c_int32), ("no_repeat_ngram", C.c_int32), ("greedy", C.c_int32),
+                ("seed", C.c_uint64)]
+
+    @classmethod
+    def of(cls, cfg, seed=0):
+        """From an oracle_lib.Sampling."""
+        return cls(cfg.temperature, cfg.top_p, cfg.min_p, cfg.repetition_penalty, cfg.frequency_penalty,
+                   cfg.presence_penalty, cfg.top_k, cfg.repetition_window, cfg.no_repeat_ngram, int(cfg.greedy), seed)
+
+
 _MODEL_CACHE = {}
 
 
@@ -230,6 +244,21 @@ class CudaDecoder:
         torch.cuda.synchronize()
         return buf.cpu().numpy().reshape(self.batch, self.cfg["vocab"])
 
+    def set_sampling(self, cfg, seed=0):
+        """cfg: oracle_lib.Sampling, or None for the greedy arg-max."""
+        if cfg is None:
+            self.lib.b200_decoder_set_sampling(self.handle, None)
+        else:
+            self.lib.b200_decoder_set_sampling(self.handle, C.byref(B200Sampling.of(cfg, seed)))
+
+    def score_tokens(self, tokens, mask=None):
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        m = None if mask is None else np.ascontiguousarray(mask, np.uint8)
+        nll, n = C.c_double(), C.c_int64()
+        self.lib.b200_decoder_score_tokens(self.handle, tokens.ctypes.data, tokens.size,
+                                           None if m is None else m.ctypes.data, C.byref(nll), C.byref(n))
+        return nll.value, n.value
+
     def launches(self):
         n = C.c_int()
         self.lib.b200_decoder_launches_per_step(self.handle, C.byref(n))
@@ -385,6 +414,16 @@ class RefGenerator:
         self._ck(self.lib.ref_decode_step(self.h, int(token), self.pos, out.ctypes.data_as(C.c_void_p)), "decode_step")
         self.pos += 1
         return out
+
+    def score_tokens(self, tokens, mask=None):
+        """Generator::score_tokens: (mean negative log-likelihood, scored tokens)."""
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        m = None if mask is None else np.ascontiguousarray(mask, np.uint8)
+        nll, n = C.c_double(), C.c_int64()
+        self._ck(self.lib.ref_score_tokens(self.h, tokens.ctypes.data_as(C.c_void_p), tokens.size,
+                                           None if m is None else m.ctypes.data_as(C.c_void_p), C.byref(nll), C.byref(n)),
+                 "score_tokens")
+        return nll.value, n.value
 
     def close(self):
         if self.h:

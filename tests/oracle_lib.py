@@ -56,6 +56,31 @@ def _wt(w, wkind):
     return a
 
 
+class Sampling:
+    """SamplingConfig (inference/sampler.h:9-24) as the two packed arrays the checkers take."""
+
+    def __init__(self, temperature=0.8, top_k=40, top_p=0.92, min_p=0.05, repetition_penalty=1.12,
+                 repetition_window=128, frequency_penalty=0.0, presence_penalty=0.0, no_repeat_ngram=0, greedy=False):
+        self.f = np.array([temperature, top_p, min_p, repetition_penalty, frequency_penalty, presence_penalty], np.float32)
+        self.i = np.array([top_k, repetition_window, no_repeat_ngram, int(greedy)], np.int32)
+
+    temperature = property(lambda s: float(s.f[0]))
+    top_p = property(lambda s: float(s.f[1]))
+    min_p = property(lambda s: float(s.f[2]))
+    repetition_penalty = property(lambda s: float(s.f[3]))
+    frequency_penalty = property(lambda s: float(s.f[4]))
+    presence_penalty = property(lambda s: float(s.f[5]))
+    top_k = property(lambda s: int(s.i[0]))
+    repetition_window = property(lambda s: int(s.i[1]))
+    no_repeat_ngram = property(lambda s: int(s.i[2]))
+    greedy = property(lambda s: bool(s.i[3]))
+
+    def copy(self):
+        c = Sampling()
+        c.f, c.i = self.f.copy(), self.i.copy()
+        return c
+
+
 class _Base:
     prefix = ""
 
@@ -82,6 +107,12 @@ class Oracle(_Base):
             build_oracle()
         super().__init__(ORACLE_SO)
         self.lib.ora_argmax.restype = C.c_int32
+        self.lib.ora_sample.restype = C.c_int32
+        self.lib.ora_sample_candidates.restype = C.c_int32
+        self.lib.ora_rng_uniform.restype = C.c_float
+        self.lib.ora_rng_next.restype = C.c_uint64
+        for n in ("rng_seed", "sampling_validate", "softmax_cross_entropy"):
+            self.fn(n).restype = None
         self.lib.ora_packed_bytes.restype = C.c_int64
         for n in ("f32_to_f16", "f16_to_f32", "dequantize", "dequantize_f32", "linear_f16",
                   "linear_f32", "embedding", "rmsnorm", "rope_cached", "swiglu", "topk",
@@ -184,6 +215,48 @@ class Oracle(_Base):
         self.fn("rep_penalties")(_p(logits), logits.size, _p(hist), hist.size, C.c_float(rep),
                                  C.c_float(freq), C.c_float(pres))
         return logits
+
+    # --- sampling tail -------------------------------------------------------
+    def rng_state(self, seed):
+        st = np.zeros(4, np.uint64)
+        self.lib.ora_rng_seed(C.c_uint64(seed), _p(st))
+        return st
+
+    def rng_uniform(self, seed, n):
+        st = self.rng_state(seed)
+        return np.array([self.lib.ora_rng_uniform(_p(st)) for _ in range(n)], np.float32)
+
+    def sampling_validate(self, cfg):
+        c = cfg.copy()
+        self.fn("sampling_validate")(_p(c.f), _p(c.i))
+        return c
+
+    def sample_with_state(self, logits, hist, cfg, state):
+        """One Sampler::sample call; `logits` (modified in place) and `state` advance."""
+        hist = _i32(hist if hist is not None else [])
+        return int(self.lib.ora_sample(_p(logits), logits.size, _p(hist), hist.size, _p(cfg.f), _p(cfg.i), _p(state)))
+
+    def sample(self, logits, hist, cfg, seed, n_draws):
+        st = self.rng_state(seed)
+        logits = _f32(logits)
+        return np.array([self.sample_with_state(logits.copy(), hist, cfg, st) for _ in range(n_draws)], np.int32)
+
+    def candidates_with_state(self, vals, ids, cfg, state):
+        vals, ids = _f32(vals), _i32(ids)
+        return int(self.lib.ora_sample_candidates(_p(vals), _p(ids), vals.size, C.c_float(cfg.temperature),
+                                                  C.c_float(cfg.top_p), C.c_float(cfg.min_p), _p(state)))
+
+    def sample_candidates(self, vals, ids, cfg, seed, n_draws):
+        st = self.rng_state(seed)
+        return np.array([self.candidates_with_state(vals, ids, cfg, st) for _ in range(n_draws)], np.int32)
+
+    def cross_entropy(self, logits, targets, z_scale=0.0):
+        logits, targets = _f32(logits), _i32(targets)
+        n, V = logits.shape
+        total, count = C.c_double(), C.c_int64()
+        self.fn("softmax_cross_entropy")(_p(logits), _p(targets), C.c_int64(n), V, C.c_float(z_scale), C.byref(total),
+                                         C.byref(count))
+        return total.value, count.value
 
     # --- MoE ---------------------------------------------------------------
     def moe_route(self, x, router_w, router_bias, ne, K):
@@ -333,6 +406,38 @@ class Ref(Oracle):
         out = C.c_int32(0)
         self._call("argmax", _p(logits), logits.size, C.byref(out))
         return out.value
+
+    def rng_uniform(self, seed, n):
+        out = np.empty(n, np.float32)
+        self._call("rng_uniform", C.c_uint64(seed), n, _p(out))
+        return out
+
+    def sampling_validate(self, cfg):
+        c = cfg.copy()
+        self._call("sampling_validate", _p(c.f), _p(c.i))
+        return c
+
+    def sample(self, logits, hist, cfg, seed, n_draws):
+        logits, hist = _f32(logits), _i32(hist if hist is not None else [])
+        out = np.empty(n_draws, np.int32)
+        self._call("sampler_sample", _p(logits), logits.size, _p(hist), hist.size, _p(cfg.f), _p(cfg.i),
+                   C.c_uint64(seed), n_draws, _p(out))
+        return out
+
+    def sample_candidates(self, vals, ids, cfg, seed, n_draws):
+        vals, ids = _f32(vals), _i32(ids)
+        out = np.empty(n_draws, np.int32)
+        self._call("sampler_candidates", _p(vals), _p(ids), vals.size, _p(cfg.f), _p(cfg.i), C.c_uint64(seed), n_draws,
+                   _p(out))
+        return out
+
+    def cross_entropy(self, logits, targets, z_scale=0.0):
+        logits, targets = _f32(logits), _i32(targets)
+        n, V = logits.shape
+        total, count = C.c_double(), C.c_int64()
+        self._call("softmax_cross_entropy", _p(logits), _p(targets), C.c_int64(n), V, C.c_float(z_scale),
+                   C.byref(total), C.byref(count))
+        return total.value, count.value
 
     def moe_route(self, x, router_w, router_bias, ne, K):
         raise NotImplementedError("the reference exposes routing only through moe_forward")
