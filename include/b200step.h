@@ -84,6 +84,16 @@ int b200_decoder_step(b200_decoder* dec, const int32_t* tokens_dev, int32_t* nex
  * calls of b200_decoder_step would have left it; next_dev (optional) receives the greedy
  * pick after the last prompt token, b200_decoder_logits its logits. */
 int b200_decoder_prefill(b200_decoder* dec, const int32_t* tokens_dev, int T, int32_t* next_dev);
+/* The same for prompts of different lengths (the batch-64 ragged prompt of a serving batch;
+ * the reference would run them one after the other through Generator::prefill,
+ * inference/generator.cpp:917-983): sequence b has lengths_host[b] tokens (1 .. max_ctx), the
+ * sequences' tokens lie back to back in tokens_dev.  All token-wise work (projections, MoE,
+ * norms) runs over the packed rows at once; the convolution window, the chunks of the SSD
+ * scan, the causal attention and the KV pages never cross a sequence boundary.  Afterwards
+ * every sequence stands where its own prefill would have left it, and b200_decoder_step
+ * continues all of them (each at its own position); b200_decoder_position reports the longest. */
+int b200_decoder_prefill_ragged(b200_decoder* dec, const int32_t* tokens_dev, const int32_t* lengths_host,
+                                int32_t* next_dev);
 /* Same through host buffers: H2D of the token ids, the step, D2H of the picks,
  * then a stream synchronise (what Generator::decode_step + ops::argmax_token do). */
 int b200_decoder_step_host(b200_decoder* dec, const int32_t* tokens_host, int32_t* next_host);

@@ -10,6 +10,21 @@ struct MambaDims {
     float eps;
 };
 
+// Sequences of different lengths packed back to back (row = token): what the sequence-aware
+// prompt kernels need to know.  Device arrays unless noted.
+constexpr int SSD_Q = 128;                // steps per chunk of the chunked Mamba-2 scan
+struct SeqLayout {
+    int n_seq = 0;
+    int64_t rows = 0;                     // tokens of all sequences
+    int n_chunks = 0;
+    const int32_t* seq_off = nullptr;     // [n_seq + 1] first row of each sequence
+    const int32_t* pos = nullptr;         // [rows] position of a row inside its sequence
+    const int32_t* seq = nullptr;         // [rows] sequence a row belongs to
+    const int2* chunks = nullptr;         // [n_chunks] (first row, steps <= SSD_Q); no chunk crosses a sequence boundary
+    const int32_t* seq_chunk0 = nullptr;  // [n_seq + 1] first chunk of each sequence
+    const int32_t* host_off = nullptr;    // host copy of seq_off
+};
+
 enum { PRO_NONE = 0, PRO_RMS = 1 };
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_INPROJ = 2 };
 
@@ -54,10 +69,13 @@ int stream_gemv(SgArgs a, int kind, int pro, int epi);
 // storage.  conv_state_out (optional) [B, conv_dim, k-1] receives the convolution
 // window a following decode step continues from.  x16 (optional): the same activations
 // already rounded to fp16 rows [B*T, d] by their producer, used instead of converting x
-// when the projection runs as a tensor-core GEMM.
+// when the projection runs as a tensor-core GEMM.  lay (optional): the B sequences have
+// different lengths and lie packed as lay describes (T is ignored); state and
+// conv_state_out stay [B, ...].
 int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const float* conv_b, const float* dt_bias,
                    const float* a_log, const float* D, const float* norm_w, const void* w_out, float* state, float* out,
-                   int B, int T, MambaDims p, int kind, float* conv_state_out = nullptr, const void* x16 = nullptr);
+                   int B, int T, MambaDims p, int kind, float* conv_state_out = nullptr, const void* x16 = nullptr,
+                   const SeqLayout* lay = nullptr);
 
 // Decode state update; partials: [batch, mamba_scan_norm_blocks()] doubles.
 int mamba_scan_norm(const float* bc, const float* dt_raw, const float* gate, const float* dt_bias,

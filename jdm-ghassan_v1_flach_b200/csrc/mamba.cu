@@ -211,20 +211,23 @@ static void launch_gated_norm(const float* y, const float* gate, int64_t gate_st
 // Prefill: causal depthwise conv + SiLU over [B,T]; the window before t = 0 is
 // zero on every call (core/mamba_cpu.cpp:90-99).  One thread per (b,t,c).
 // ---------------------------------------------------------------------------
+// pos (optional, packed sequences: B = 1, T = all rows): a row's position inside its own
+// sequence; taps that would reach before the sequence's first row read zero.
 __global__ void mamba_conv_seq_kernel(const float* __restrict__ proj, const float* __restrict__ conv_w,
                                       const float* __restrict__ conv_b, float* __restrict__ bc,
-                                      int B, int T, MambaDims p) {
+                                      int B, int T, MambaDims p, const int32_t* __restrict__ pos) {
     const int64_t total = (int64_t)B * T * p.conv_dim;
     for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
          idx += (int64_t)gridDim.x * blockDim.x) {
         const int c = (int)(idx % p.conv_dim);
         const int64_t bt = idx / p.conv_dim;
         const int t = (int)(bt % T);
+        const int first = pos ? t - pos[bt] : 0;          // first step of the row's sequence
         const float* wc = conv_w + (int64_t)c * p.k;
         float a = conv_b ? conv_b[c] : 0.0f;
         for (int j = 0; j < p.k; ++j) {
             const int tt = t - (p.k - 1) + j;
-            const float v = tt >= 0 ? proj[(bt - (t - tt)) * p.proj + p.d_inner + c] : 0.0f;
+            const float v = tt >= first ? proj[(bt - (t - tt)) * p.proj + p.d_inner + c] : 0.0f;
             a = __fadd_rn(a, __fmul_rn(wc[j], v));
         }
         bc[idx] = silu_acc(a);
@@ -238,7 +241,7 @@ __global__ void mamba_conv_seq_kernel(const float* __restrict__ proj, const floa
 constexpr int CONV_TT = 8;
 __global__ void __launch_bounds__(256)
 mamba_conv_seq4_kernel(const float* __restrict__ proj, const float* __restrict__ conv_w, const float* __restrict__ conv_b,
-                       float* __restrict__ bc, int T, MambaDims p) {
+                       float* __restrict__ bc, int T, MambaDims p, const int32_t* __restrict__ pos) {
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (c >= p.conv_dim) return;
     const int t0 = blockIdx.y * CONV_TT, b = blockIdx.z;
@@ -257,8 +260,16 @@ mamba_conv_seq4_kernel(const float* __restrict__ proj, const float* __restrict__
     float4 x0 = at(t0 - 3), x1 = at(t0 - 2), x2 = at(t0 - 1);
     float* dst = bc + ((int64_t)b * T + t0) * p.conv_dim + c;
     const int nt = min(CONV_TT, T - t0);
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int i = 0; i < nt; ++i) {
         const float4 x3 = at(t0 + i);
+        if (pos) {
+            // packed sequences: the window does not reach into the previous sequence
+            const int m = pos[(int64_t)b * T + t0 + i];
+            if (m < 3) x0 = zero4;
+            if (m < 2) x1 = zero4;
+            if (m < 1) x2 = zero4;
+        }
         auto tap = [&](float bi, const float (&wc)[4], float a0, float a1, float a2, float a3) {
             float a = __fadd_rn(bi, __fmul_rn(wc[0], a0));
             a = __fadd_rn(a, __fmul_rn(wc[1], a1));
@@ -481,36 +492,46 @@ int mamba2_step(const float* x, const void* w_in, const float* conv_w, const flo
 
 // mamba_ssd.cu
 int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, const float* a_log, const float* D,
-                   float* state, float* y, int B, int T, const MambaDims& p, bool precise);
+                   float* state, float* y, int B, int T, const MambaDims& p, bool precise, const SeqLayout* lay);
 constexpr int SSD_MIN_STEPS = 64;
 
 // The last k-1 raw (pre-convolution) inputs of every channel, oldest first: the window a
 // decode step expects after this sequence (zeros where the sequence is shorter).
 __global__ void mamba_conv_window_kernel(const float* __restrict__ proj, float* __restrict__ conv_state, int B, int T,
-                                         MambaDims p) {
+                                         MambaDims p, const int32_t* __restrict__ seq_off) {
     const int win = p.k - 1;
     const int64_t total = (int64_t)B * p.conv_dim * win;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int j = (int)(i % win);
         const int64_t bc_i = i / win;
         const int c = (int)(bc_i % p.conv_dim), b = (int)(bc_i / p.conv_dim);
-        const int t = T - win + j;
-        conv_state[i] = t >= 0 ? proj[((int64_t)b * T + t) * p.proj + p.d_inner + c] : 0.0f;
+        const int64_t first = seq_off ? seq_off[b] : (int64_t)b * T;
+        const int len = seq_off ? seq_off[b + 1] - seq_off[b] : T;
+        const int t = len - win + j;
+        conv_state[i] = t >= 0 ? proj[(first + t) * p.proj + p.d_inner + c] : 0.0f;
     }
 }
 
 int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const float* conv_b,
                    const float* dt_bias, const float* a_log, const float* D, const float* norm_w,
                    const void* w_out, float* state, float* out, int B, int T, MambaDims p, int kind,
-                   float* conv_state_out, const void* x16) {
+                   float* conv_state_out, const void* x16, const SeqLayout* lay) {
+    if (lay) {
+        B200_REQUIRE(lay->n_seq == B && lay->rows > 0 && lay->seq_off && lay->pos && lay->host_off,
+                     "mamba2_forward: incomplete sequence layout");
+        T = 1;
+    }
     if (B <= 0 || T <= 0) return B200_OK;
     int rc = check_dims("mamba2_forward", p);
     if (rc) return rc;
     B200_REQUIRE(x && w_in && conv_w && dt_bias && a_log && D && norm_w && w_out && state && out,
                  "mamba2_forward: null pointer");
     p.proj = p.d_inner + p.conv_dim + p.n_heads;
-    const int64_t NT = (int64_t)B * T;
+    const int64_t NT = lay ? lay->rows : (int64_t)B * T;
     B200_REQUIRE(NT <= 0x7fffffff, "mamba2_forward: B*T too large");
+    // the convolution sees packed sequences as one long one whose rows know their position
+    const int cB = lay ? 1 : B, cT = lay ? (int)NT : T;
+    const int32_t* pos = lay ? lay->pos : nullptr;
     const size_t proj_f = (size_t)NT * p.proj, bc_f = (size_t)NT * p.conv_dim, y_f = (size_t)NT * p.d_inner;
     void* wsp;
     // when the out-projection runs as a GEMM the gated norm hands it fp16 rows directly
@@ -532,30 +553,34 @@ int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const 
         const int grid = (int)std::min<int64_t>(ceil_div64(total, 256), (int64_t)num_sms() * 32);
         auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
         if (p.k == 4 && p.conv_dim % 4 == 0 && p.d_inner % 4 == 0 && p.proj % 4 == 0 && al16(proj) && al16(bc) &&
-            al16(conv_w) && (!conv_b || al16(conv_b)) && B <= 65535 && ceil_div(T, CONV_TT) <= 65535) {
-            mamba_conv_seq4_kernel<<<dim3(ceil_div(p.conv_dim / 4, 256), ceil_div(T, CONV_TT), B), 256, 0, stream()>>>(
-                proj, conv_w, conv_b, bc, T, p);
+            al16(conv_w) && (!conv_b || al16(conv_b)) && cB <= 65535 && ceil_div(cT, CONV_TT) <= 65535) {
+            mamba_conv_seq4_kernel<<<dim3(ceil_div(p.conv_dim / 4, 256), ceil_div(cT, CONV_TT), cB), 256, 0, stream()>>>(
+                proj, conv_w, conv_b, bc, cT, p, pos);
             B200_LAUNCH_CHECK("mamba_conv_seq4_kernel");
         } else {
-            mamba_conv_seq_kernel<<<grid, 256, 0, stream()>>>(proj, conv_w, conv_b, bc, B, T, p);
+            mamba_conv_seq_kernel<<<grid, 256, 0, stream()>>>(proj, conv_w, conv_b, bc, cB, cT, p, pos);
             B200_LAUNCH_CHECK("mamba_conv_seq_kernel");
         }
         if (conv_state_out && p.k > 1) {
             const int64_t n = (int64_t)B * p.conv_dim * (p.k - 1);
             mamba_conv_window_kernel<<<(unsigned)std::min<int64_t>(ceil_div64(n, 256), 4096), 256, 0, stream()>>>(
-                proj, conv_state_out, B, T, p);
+                proj, conv_state_out, B, T, p, lay ? lay->seq_off : nullptr);
             B200_LAUNCH_CHECK("mamba_conv_window_kernel");
         }
     }
     // Long sequences: the chunked form (all steps in parallel, a short carry over chunks);
     // short ones and shapes outside its tiling: the sequential register-resident scan.
     bool scanned = false;
-    if (T >= SSD_MIN_STEPS) {
-        rc = mamba_ssd_scan(proj, bc, dt_bias, a_log, D, state, y, B, T, p, kind == KIND_F32);
+    if (lay ? lay->chunks != nullptr : T >= SSD_MIN_STEPS) {
+        rc = mamba_ssd_scan(proj, bc, dt_bias, a_log, D, state, y, B, T, p, kind == KIND_F32, lay);
         if (rc == B200_OK) scanned = true;
         else if (rc != B200_EUNSUPPORTED) return rc;
     }
-    if (!scanned) {
+    // the sequential scan of `nb` equally long sequences starting at row `row0`
+    auto sequential = [&](int64_t row0, int nb, int steps, float* st) -> int {
+        const float* pj = proj + row0 * p.proj;
+        const float* bcs = bc + row0 * p.conv_dim;
+        float* ys = y + row0 * p.d_inner;
         // register-resident scan: 256 threads = rows_per_pass * parts, parts a power of two <= 32
         int npt = 0;
         for (int cand : {32, 16, 8, 4}) {
@@ -567,17 +592,29 @@ int mamba2_forward(const float* x, const void* w_in, const float* conv_w, const 
         }
         const size_t smem = (size_t)SEQ_TT * (2 * p.d_state + p.d_head + 2) * sizeof(float);
         if (npt && smem <= 48 * 1024) {
-            const int grid = B * p.n_heads;
-            if (npt == 32) mamba_scan_seq_kernel<32><<<grid, 256, smem, stream()>>>(proj, bc, dt_bias, a_log, D, state, y, B, T, p);
-            else if (npt == 16) mamba_scan_seq_kernel<16><<<grid, 256, smem, stream()>>>(proj, bc, dt_bias, a_log, D, state, y, B, T, p);
-            else if (npt == 8) mamba_scan_seq_kernel<8><<<grid, 256, smem, stream()>>>(proj, bc, dt_bias, a_log, D, state, y, B, T, p);
-            else mamba_scan_seq_kernel<4><<<grid, 256, smem, stream()>>>(proj, bc, dt_bias, a_log, D, state, y, B, T, p);
+            const int grid = nb * p.n_heads;
+            if (npt == 32) mamba_scan_seq_kernel<32><<<grid, 256, smem, stream()>>>(pj, bcs, dt_bias, a_log, D, st, ys, nb, steps, p);
+            else if (npt == 16) mamba_scan_seq_kernel<16><<<grid, 256, smem, stream()>>>(pj, bcs, dt_bias, a_log, D, st, ys, nb, steps, p);
+            else if (npt == 8) mamba_scan_seq_kernel<8><<<grid, 256, smem, stream()>>>(pj, bcs, dt_bias, a_log, D, st, ys, nb, steps, p);
+            else mamba_scan_seq_kernel<4><<<grid, 256, smem, stream()>>>(pj, bcs, dt_bias, a_log, D, st, ys, nb, steps, p);
             B200_LAUNCH_CHECK("mamba_scan_seq_kernel");
         } else {
-            const int64_t warps = (int64_t)B * p.n_heads * p.d_head;
+            const int64_t warps = (int64_t)nb * p.n_heads * p.d_head;
             mamba_scan_seq_general_kernel<<<(unsigned)ceil_div64(warps * 32, 256), 256, 0, stream()>>>(
-                proj, bc, dt_bias, a_log, D, state, y, B, T, p);
+                pj, bcs, dt_bias, a_log, D, st, ys, nb, steps, p);
             B200_LAUNCH_CHECK("mamba_scan_seq_general_kernel");
+        }
+        return B200_OK;
+    };
+    if (!scanned && !lay) {
+        rc = sequential(0, B, T, state);
+        if (rc) return rc;
+    } else if (!scanned) {
+        // packed sequences on a shape outside the chunked kernels: one scan per sequence
+        for (int b = 0; b < B; ++b) {
+            rc = sequential(lay->host_off[b], 1, lay->host_off[b + 1] - lay->host_off[b],
+                            state + (int64_t)b * p.d_inner * p.d_state);
+            if (rc) return rc;
         }
     }
     launch_gated_norm(y, proj, p.proj, norm_w, y, p.d_inner, p.eps, out_gemm ? y16 : nullptr, NT);

@@ -26,8 +26,36 @@
 
 namespace b200 {
 
-constexpr int SSD_Q = 128;                 // steps per chunk
-constexpr int SSD_THREADS = 256;
+constexpr int SSD_THREADS = 256;            // (SSD_Q, the steps per chunk, is in fused.cuh)
+
+// Where chunk c of sequence b lives.  Rectangular batches [B, T]: chunk c covers steps
+// c SSD_Q .. of every sequence.  Packed sequences of different lengths (tab != nullptr,
+// grid z = 1): chunk c is entry c of the table (first row, steps), which never crosses a
+// sequence boundary; per-chunk arrays are indexed by c and dtcum is [H, NT, 2].
+struct SsdChunk {
+    int64_t row0;      // first row of the chunk in proj / bc / y
+    int64_t ci;        // index into the per-chunk arrays (G, chunk_state, decay)
+    int64_t dt0;       // index of the chunk's first (dt, cum) pair for head h
+    int nt;            // steps in the chunk
+};
+__device__ __forceinline__ SsdChunk ssd_chunk(const int2* __restrict__ tab, int64_t NT, int c, int b, int h, int T, int NC,
+                                              int H) {
+    SsdChunk k;
+    if (tab) {
+        const int2 e = tab[c];
+        k.row0 = e.x;
+        k.nt = e.y;
+        k.ci = c;
+        k.dt0 = (int64_t)h * NT + e.x;
+    } else {
+        const int t0 = c * SSD_Q;
+        k.row0 = (int64_t)b * T + t0;
+        k.nt = min(SSD_Q, T - t0);
+        k.ci = (int64_t)b * NC + c;
+        k.dt0 = ((int64_t)b * H + h) * T + t0;
+    }
+    return k;
+}
 
 __device__ __forceinline__ float softplus_dt(float u) { return (u > 20.0f) ? u : log1pf(expf(u)); }
 
@@ -36,7 +64,7 @@ __device__ __forceinline__ float softplus_dt(float u) { return (u > 20.0f) ? u :
 // skipped: grid (3 * chunks, B), quadrant (0,0), (1,0) or (1,1) per block; thread
 // (ty, tx) of a 16 x 16 block owns a 4 x 4 block of its quadrant.  fp32 throughout.
 __global__ void __launch_bounds__(SSD_THREADS)
-ssd_cb_kernel(const float* __restrict__ bc, float* __restrict__ G, int T, MambaDims p) {
+ssd_cb_kernel(const float* __restrict__ bc, float* __restrict__ G, int T, MambaDims p, const int2* __restrict__ tab) {
     extern __shared__ float sm[];
     constexpr int H = SSD_Q / 2;
     const int N = p.d_state, ld = N + 1;
@@ -45,12 +73,13 @@ ssd_cb_kernel(const float* __restrict__ bc, float* __restrict__ G, int T, MambaD
     const int c = blockIdx.x / 3, quad = blockIdx.x - 3 * c, b = blockIdx.y;
     const int NC = gridDim.x / 3;
     const int ti = quad == 0 ? 0 : H, si = quad == 2 ? H : 0;        // first row (t) and column (s)
-    const int t0 = c * SSD_Q, nt = min(SSD_Q, T - t0);
+    const SsdChunk ck = ssd_chunk(tab, 0, c, b, 0, T, NC, 1);
+    const int nt = ck.nt;
     for (int e = threadIdx.x; e < H * N; e += SSD_THREADS) {
         const int r = e / N, n = e - r * N;
         float bv = 0.0f, cv = 0.0f;
-        if (si + r < nt) bv = bc[((int64_t)b * T + t0 + si + r) * p.conv_dim + p.d_inner + n];
-        if (ti + r < nt) cv = bc[((int64_t)b * T + t0 + ti + r) * p.conv_dim + p.d_inner + N + n];
+        if (si + r < nt) bv = bc[(ck.row0 + si + r) * p.conv_dim + p.d_inner + n];
+        if (ti + r < nt) cv = bc[(ck.row0 + ti + r) * p.conv_dim + p.d_inner + N + n];
         sB[r * ld + n] = bv;
         sC[r * ld + n] = cv;
     }
@@ -68,7 +97,7 @@ ssd_cb_kernel(const float* __restrict__ bc, float* __restrict__ G, int T, MambaD
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[i][j] += cv[i] * bv[j];
     }
-    float* g = G + ((int64_t)b * NC + c) * SSD_Q * SSD_Q;
+    float* g = G + (ck.ci) * SSD_Q * SSD_Q;
 #pragma unroll
     for (int i = 0; i < 4; ++i)
         *reinterpret_cast<float4*>(g + (ti + ty * 4 + i) * SSD_Q + si + tx * 4) =
@@ -125,7 +154,7 @@ template <bool X3>
 __global__ void __launch_bounds__(SSD_THREADS, 2)
 ssd_chunk_state_kernel(const float* __restrict__ proj, const float* __restrict__ bc, const float* __restrict__ dt_bias,
                        const float* __restrict__ a_log, float* __restrict__ dtcum, float* __restrict__ chunk_state,
-                       float* __restrict__ decay, int T, int NC, MambaDims p) {
+                       float* __restrict__ decay, int T, int NC, MambaDims p, const int2* __restrict__ tab, int64_t NT) {
     extern __shared__ float sm[];
     constexpr int P = SSD_P;
     const int N = p.d_state, ldb = N + 8;
@@ -134,12 +163,13 @@ ssd_chunk_state_kernel(const float* __restrict__ proj, const float* __restrict__
     float* sDt = sX + SSD_Q * SSD_LDX;      // [Q]
     float* sCum = sDt + SSD_Q;              // [Q]
     const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-    const int t0 = c * SSD_Q, nt = min(SSD_Q, T - t0);
+    const SsdChunk ck = ssd_chunk(tab, NT, c, b, h, T, NC, p.n_heads);
+    const int nt = ck.nt;
     const float A = -expf(a_log[h]);
     if (threadIdx.x < SSD_Q) {
         float dt = 0.0f;
         if (threadIdx.x < nt) {
-            const float u = proj[((int64_t)b * T + t0 + threadIdx.x) * p.proj + p.proj - p.n_heads + h] + dt_bias[h];
+            const float u = proj[(ck.row0 + threadIdx.x) * p.proj + p.proj - p.n_heads + h] + dt_bias[h];
             dt = softplus_dt(u);
         }
         sDt[threadIdx.x] = dt;
@@ -166,16 +196,16 @@ ssd_chunk_state_kernel(const float* __restrict__ proj, const float* __restrict__
     __syncthreads();
     const float cum_last = sCum[SSD_Q - 1];
     if (threadIdx.x < nt) {
-        float* o = dtcum + (((int64_t)b * p.n_heads + h) * T + t0 + threadIdx.x) * 2;
+        float* o = dtcum + (ck.dt0 + threadIdx.x) * 2;
         o[0] = sDt[threadIdx.x];
         o[1] = sCum[threadIdx.x];
     }
-    if (threadIdx.x == 0) decay[((int64_t)b * NC + c) * p.n_heads + h] = expf(cum_last);
+    if (threadIdx.x == 0) decay[(ck.ci) * p.n_heads + h] = expf(cum_last);
     const int n4 = N >> 2;
     for (int e = threadIdx.x; e < SSD_Q * n4; e += SSD_THREADS) {
         const int t = e / n4, n = (e - t * n4) * 4;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (t < nt) v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + p.d_inner + n);
+        if (t < nt) v = *reinterpret_cast<const float4*>(bc + (ck.row0 + t) * p.conv_dim + p.d_inner + n);
         *reinterpret_cast<float4*>(sB + t * ldb + n) = v;
     }
     for (int e = threadIdx.x; e < SSD_Q * (P / 4); e += SSD_THREADS) {
@@ -183,7 +213,7 @@ ssd_chunk_state_kernel(const float* __restrict__ proj, const float* __restrict__
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (t < nt) {
             const float w = expf(cum_last - sCum[t]) * sDt[t];
-            v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + h * P + i);
+            v = *reinterpret_cast<const float4*>(bc + (ck.row0 + t) * p.conv_dim + h * P + i);
             v = make_float4(w * v.x, w * v.y, w * v.z, w * v.w);
         }
         *reinterpret_cast<float4*>(sX + t * SSD_LDX + i) = v;
@@ -205,7 +235,7 @@ ssd_chunk_state_kernel(const float* __restrict__ proj, const float* __restrict__
         for (int j = 0; j < 8; ++j)
             if (j < nth) mma_x<X3>(acc[j], a, Tf32Val<X3>(bb[j * 8]), Tf32Val<X3>(bb[j * 8 + 4 * ldb]));
     }
-    float* out = chunk_state + (((int64_t)b * NC + c) * p.n_heads + h) * P * N;
+    float* out = chunk_state + ((ck.ci) * p.n_heads + h) * P * N;
 #pragma unroll
     for (int j = 0; j < 8; ++j)
         if (j < nth) {
@@ -220,27 +250,30 @@ ssd_chunk_state_kernel(const float* __restrict__ proj, const float* __restrict__
 // loads in flight at a time.
 __global__ void __launch_bounds__(256)
 ssd_carry_kernel(float* __restrict__ chunk_state, const float* __restrict__ decay, float* __restrict__ state, int B,
-                 int NC, MambaDims p) {
+                 int NC, MambaDims p, const int32_t* __restrict__ seq_chunk0) {
     const int64_t per = (int64_t)p.d_head * p.d_state;
     const int64_t total = (int64_t)B * p.n_heads * per;
     const int64_t cstride = (int64_t)p.n_heads * per;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t bh = i / per, e = i - bh * per;
         const int b = (int)(bh / p.n_heads), h = (int)(bh - (int64_t)b * p.n_heads);
-        float* cs = chunk_state + ((int64_t)b * NC * p.n_heads + h) * per + e;
-        const float* dc = decay + (int64_t)b * NC * p.n_heads + h;
+        // the sequence's chunks are consecutive entries of the per-chunk arrays
+        const int64_t c_first = seq_chunk0 ? seq_chunk0[b] : (int64_t)b * NC;
+        const int nc = seq_chunk0 ? seq_chunk0[b + 1] - seq_chunk0[b] : NC;
+        float* cs = chunk_state + (c_first * p.n_heads + h) * per + e;
+        const float* dc = decay + c_first * p.n_heads + h;
         float s = state[i];
-        for (int c0 = 0; c0 < NC; c0 += 8) {
+        for (int c0 = 0; c0 < nc; c0 += 8) {
             float own[8], de[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                if (c0 + j < NC) {
+                if (c0 + j < nc) {
                     own[j] = __ldcs(cs + (c0 + j) * cstride);
                     de[j] = dc[(int64_t)(c0 + j) * p.n_heads];
                 }
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                if (c0 + j < NC) {
+                if (c0 + j < nc) {
                     cs[(c0 + j) * cstride] = s;
                     s = de[j] * s + own[j];
                 }
@@ -260,19 +293,20 @@ template <bool X3>
 __global__ void __launch_bounds__(SSD_THREADS, 2)
 ssd_chunk_out_kernel(const float* __restrict__ bc, const float* __restrict__ G, const float* __restrict__ dtcum,
                      const float* __restrict__ chunk_state, const float* __restrict__ Dv, float* __restrict__ y, int T,
-                     int NC, MambaDims p) {
+                     int NC, MambaDims p, const int2* __restrict__ tab, int64_t NT) {
     extern __shared__ float sm[];
     constexpr int P = SSD_P, LDM = SSD_Q + 4;
     const int N = p.d_state, ldc = N + 4;
     const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-    const int t0 = c * SSD_Q, nt = min(SSD_Q, T - t0);
+    const SsdChunk ck = ssd_chunk(tab, NT, c, b, h, T, NC, p.n_heads);
+    const int nt = ck.nt;
     float* sDt = sm;                        // [Q]
     float* sCum = sDt + SSD_Q;              // [Q]
     float* buf = sCum + SSD_Q;
     if (threadIdx.x < SSD_Q) {
         float dt = 0.0f, cum = 0.0f;
         if (threadIdx.x < nt) {
-            const float2 o = *reinterpret_cast<const float2*>(dtcum + (((int64_t)b * p.n_heads + h) * T + t0 + threadIdx.x) * 2);
+            const float2 o = *reinterpret_cast<const float2*>(dtcum + (ck.dt0 + threadIdx.x) * 2);
             dt = o.x;
             cum = o.y;
         }
@@ -298,12 +332,12 @@ ssd_chunk_out_kernel(const float* __restrict__ bc, const float* __restrict__ G, 
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (t < nt) {
                 const float w = expf(sCum[t]);
-                v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + p.d_inner + N + n);
+                v = *reinterpret_cast<const float4*>(bc + (ck.row0 + t) * p.conv_dim + p.d_inner + N + n);
                 v = make_float4(w * v.x, w * v.y, w * v.z, w * v.w);
             }
             *reinterpret_cast<float4*>(sC + t * ldc + n) = v;
         }
-        const float* sp = chunk_state + (((int64_t)b * NC + c) * p.n_heads + h) * P * N;
+        const float* sp = chunk_state + ((ck.ci) * p.n_heads + h) * P * N;
         for (int e = threadIdx.x; e < P * n4; e += SSD_THREADS) {
             const int i = e / n4, n = (e - i * n4) * 4;
             const float4 v = __ldcs(reinterpret_cast<const float4*>(sp + i * N + n));
@@ -334,7 +368,7 @@ ssd_chunk_out_kernel(const float* __restrict__ bc, const float* __restrict__ G, 
     {
         float* sM = buf;                    // [Q][Q + 4]
         float* sX = buf + SSD_Q * LDM;      // [Q][P + 8]
-        const float* gm = G + ((int64_t)b * NC + c) * SSD_Q * SSD_Q;
+        const float* gm = G + (ck.ci) * SSD_Q * SSD_Q;
         for (int e = threadIdx.x; e < SSD_Q * (SSD_Q / 4); e += SSD_THREADS) {
             const int t = e / (SSD_Q / 4), s = (e - t * (SSD_Q / 4)) * 4;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -351,7 +385,7 @@ ssd_chunk_out_kernel(const float* __restrict__ bc, const float* __restrict__ G, 
         for (int e = threadIdx.x; e < SSD_Q * (P / 4); e += SSD_THREADS) {
             const int t = e / (P / 4), i = (e - t * (P / 4)) * 4;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t < nt) v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + h * P + i);
+            if (t < nt) v = *reinterpret_cast<const float4*>(bc + (ck.row0 + t) * p.conv_dim + h * P + i);
             *reinterpret_cast<float4*>(sX + t * SSD_LDX + i) = v;
         }
         __syncthreads();
@@ -377,8 +411,8 @@ ssd_chunk_out_kernel(const float* __restrict__ bc, const float* __restrict__ G, 
         for (int r = 0; r < 2; ++r) {
             const int t = mts[i] * 16 + g + 8 * r;
             if (t < nt) {
-                const float* xr = bc + ((int64_t)b * T + t0 + t) * p.conv_dim + h * P + ph * 32 + 2 * t4;
-                float* o = y + ((int64_t)b * T + t0 + t) * p.d_inner + h * P + ph * 32 + 2 * t4;
+                const float* xr = bc + (ck.row0 + t) * p.conv_dim + h * P + ph * 32 + 2 * t4;
+                float* o = y + (ck.row0 + t) * p.d_inner + h * P + ph * 32 + 2 * t4;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 xv = *reinterpret_cast<const float2*>(xr + j * 8);
@@ -430,7 +464,7 @@ constexpr int SSD_LDM16 = SSD_Q + 8;       // M tile [Q][Q + 8] halfs
 __global__ void __launch_bounds__(SSD_THREADS, 4)
 ssd_chunk_state16_kernel(const float* __restrict__ proj, const float* __restrict__ bc, const float* __restrict__ dt_bias,
                          const float* __restrict__ a_log, float* __restrict__ dtcum, float* __restrict__ chunk_state,
-                         float* __restrict__ decay, int T, int NC, MambaDims p) {
+                         float* __restrict__ decay, int T, int NC, MambaDims p, const int2* __restrict__ tab, int64_t NT) {
     extern __shared__ __align__(16) uint8_t sm16[];
     constexpr int P = SSD_P;
     const int N = p.d_state, ldb = N + 8;
@@ -439,12 +473,13 @@ ssd_chunk_state16_kernel(const float* __restrict__ proj, const float* __restrict
     float* sDt = reinterpret_cast<float*>(sX + SSD_Q * SSD_LDX16);   // [Q]
     float* sCum = sDt + SSD_Q;                          // [Q]
     const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-    const int t0 = c * SSD_Q, nt = min(SSD_Q, T - t0);
+    const SsdChunk ck = ssd_chunk(tab, NT, c, b, h, T, NC, p.n_heads);
+    const int nt = ck.nt;
     const float A = -expf(a_log[h]);
     if (threadIdx.x < SSD_Q) {
         float dt = 0.0f;
         if (threadIdx.x < nt) {
-            const float u = proj[((int64_t)b * T + t0 + threadIdx.x) * p.proj + p.proj - p.n_heads + h] + dt_bias[h];
+            const float u = proj[(ck.row0 + threadIdx.x) * p.proj + p.proj - p.n_heads + h] + dt_bias[h];
             dt = softplus_dt(u);
         }
         sDt[threadIdx.x] = dt;
@@ -471,16 +506,16 @@ ssd_chunk_state16_kernel(const float* __restrict__ proj, const float* __restrict
     __syncthreads();
     const float cum_last = sCum[SSD_Q - 1];
     if (threadIdx.x < nt) {
-        float* o = dtcum + (((int64_t)b * p.n_heads + h) * T + t0 + threadIdx.x) * 2;
+        float* o = dtcum + (ck.dt0 + threadIdx.x) * 2;
         o[0] = sDt[threadIdx.x];
         o[1] = sCum[threadIdx.x];
     }
-    if (threadIdx.x == 0) decay[((int64_t)b * NC + c) * p.n_heads + h] = expf(cum_last);
+    if (threadIdx.x == 0) decay[(ck.ci) * p.n_heads + h] = expf(cum_last);
     const int n4 = N >> 2;
     for (int e = threadIdx.x; e < SSD_Q * n4; e += SSD_THREADS) {
         const int t = e / n4, n = (e - t * n4) * 4;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (t < nt) v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + p.d_inner + n);
+        if (t < nt) v = *reinterpret_cast<const float4*>(bc + (ck.row0 + t) * p.conv_dim + p.d_inner + n);
         store_half4(sB + t * ldb + n, v);
     }
     for (int e = threadIdx.x; e < SSD_Q * (P / 4); e += SSD_THREADS) {
@@ -488,7 +523,7 @@ ssd_chunk_state16_kernel(const float* __restrict__ proj, const float* __restrict
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (t < nt) {
             const float w = expf(cum_last - sCum[t]) * sDt[t];
-            v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + h * P + i);
+            v = *reinterpret_cast<const float4*>(bc + (ck.row0 + t) * p.conv_dim + h * P + i);
             v = make_float4(w * v.x, w * v.y, w * v.z, w * v.w);
         }
         store_half4(sX + t * SSD_LDX16 + i, v);
@@ -515,7 +550,7 @@ ssd_chunk_state16_kernel(const float* __restrict__ proj, const float* __restrict
                 mma_f16(acc[2 * jj + 1], a, bb[2], bb[3]);
             }
     }
-    float* out = chunk_state + (((int64_t)b * NC + c) * p.n_heads + h) * P * N;
+    float* out = chunk_state + ((ck.ci) * p.n_heads + h) * P * N;
 #pragma unroll
     for (int j = 0; j < 8; ++j)
         if (j < 2 * npairs) {
@@ -529,19 +564,20 @@ ssd_chunk_state16_kernel(const float* __restrict__ proj, const float* __restrict
 __global__ void __launch_bounds__(SSD_THREADS, 4)
 ssd_chunk_out16_kernel(const float* __restrict__ bc, const float* __restrict__ G, const float* __restrict__ dtcum,
                        const float* __restrict__ chunk_state, const float* __restrict__ Dv, float* __restrict__ y, int T,
-                       int NC, MambaDims p) {
+                       int NC, MambaDims p, const int2* __restrict__ tab, int64_t NT) {
     extern __shared__ __align__(16) uint8_t sm16[];
     constexpr int P = SSD_P;
     const int N = p.d_state, ldc = N + 8;
     const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-    const int t0 = c * SSD_Q, nt = min(SSD_Q, T - t0);
+    const SsdChunk ck = ssd_chunk(tab, NT, c, b, h, T, NC, p.n_heads);
+    const int nt = ck.nt;
     float* sDt = reinterpret_cast<float*>(sm16);        // [Q]
     float* sCum = sDt + SSD_Q;                          // [Q]
     __half* buf = reinterpret_cast<__half*>(sCum + SSD_Q);
     if (threadIdx.x < SSD_Q) {
         float dt = 0.0f, cum = 0.0f;
         if (threadIdx.x < nt) {
-            const float2 o = *reinterpret_cast<const float2*>(dtcum + (((int64_t)b * p.n_heads + h) * T + t0 + threadIdx.x) * 2);
+            const float2 o = *reinterpret_cast<const float2*>(dtcum + (ck.dt0 + threadIdx.x) * 2);
             dt = o.x;
             cum = o.y;
         }
@@ -568,12 +604,12 @@ ssd_chunk_out16_kernel(const float* __restrict__ bc, const float* __restrict__ G
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (t < nt) {
                 const float w = expf(sCum[t]);
-                v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + p.d_inner + N + n);
+                v = *reinterpret_cast<const float4*>(bc + (ck.row0 + t) * p.conv_dim + p.d_inner + N + n);
                 v = make_float4(w * v.x, w * v.y, w * v.z, w * v.w);
             }
             store_half4(sC + t * ldc + n, v);
         }
-        const float* sp = chunk_state + (((int64_t)b * NC + c) * p.n_heads + h) * P * N;
+        const float* sp = chunk_state + ((ck.ci) * p.n_heads + h) * P * N;
         for (int e = threadIdx.x; e < P * n4; e += SSD_THREADS) {
             const int i = e / n4, n = (e - i * n4) * 4;
             store_half4(sS + i * ldc + n, __ldcs(reinterpret_cast<const float4*>(sp + i * N + n)));
@@ -601,7 +637,7 @@ ssd_chunk_out16_kernel(const float* __restrict__ bc, const float* __restrict__ G
     {
         __half* sM = buf;                   // [Q][Q + 8]
         __half* sX = buf + SSD_Q * SSD_LDM16;   // [Q][P + 8]
-        const float* gm = G + ((int64_t)b * NC + c) * SSD_Q * SSD_Q;
+        const float* gm = G + (ck.ci) * SSD_Q * SSD_Q;
         for (int e = threadIdx.x; e < SSD_Q * (SSD_Q / 4); e += SSD_THREADS) {
             const int t = e / (SSD_Q / 4), s = (e - t * (SSD_Q / 4)) * 4;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -618,7 +654,7 @@ ssd_chunk_out16_kernel(const float* __restrict__ bc, const float* __restrict__ G
         for (int e = threadIdx.x; e < SSD_Q * (P / 4); e += SSD_THREADS) {
             const int t = e / (P / 4), i = (e - t * (P / 4)) * 4;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t < nt) v = *reinterpret_cast<const float4*>(bc + ((int64_t)b * T + t0 + t) * p.conv_dim + h * P + i);
+            if (t < nt) v = *reinterpret_cast<const float4*>(bc + (ck.row0 + t) * p.conv_dim + h * P + i);
             store_half4(sX + t * SSD_LDX16 + i, v);
         }
         __syncthreads();
@@ -647,8 +683,8 @@ ssd_chunk_out16_kernel(const float* __restrict__ bc, const float* __restrict__ G
         for (int r = 0; r < 2; ++r) {
             const int t = mts[i] * 16 + g + 8 * r;
             if (t < nt) {
-                const float* xr = bc + ((int64_t)b * T + t0 + t) * p.conv_dim + h * P + ph * 32 + 2 * t4;
-                float* o = y + ((int64_t)b * T + t0 + t) * p.d_inner + h * P + ph * 32 + 2 * t4;
+                const float* xr = bc + (ck.row0 + t) * p.conv_dim + h * P + ph * 32 + 2 * t4;
+                float* o = y + (ck.row0 + t) * p.d_inner + h * P + ph * 32 + 2 * t4;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 xv = *reinterpret_cast<const float2*>(xr + j * 8);
@@ -660,18 +696,23 @@ ssd_chunk_out16_kernel(const float* __restrict__ bc, const float* __restrict__ G
 }
 
 // The chunked scan over proj / bc (as produced by the projection and the convolution):
-// y [B*T, d_inner], state [B, H, P, N] updated in place.  Returns B200_EUNSUPPORTED for
-// shapes outside its tiling (the caller then runs the sequential scan).
+// y [rows, d_inner], state [B, H, P, N] updated in place.  Rectangular batches: B sequences
+// of T steps.  With lay (sequences of different lengths packed back to back, T ignored):
+// the chunks of lay's table.  Returns B200_EUNSUPPORTED for shapes outside its tiling (the
+// caller then runs the sequential scan).
 int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, const float* a_log, const float* D,
-                   float* state, float* y, int B, int T, const MambaDims& p, bool precise) {
+                   float* state, float* y, int B, int T, const MambaDims& p, bool precise, const SeqLayout* lay) {
     const int N = p.d_state, P = p.d_head;
     if (P != SSD_P || N % 16 != 0 || N > 128 || (p.d_inner & 3) != 0 || (p.conv_dim & 3) != 0)
         return fail(B200_EUNSUPPORTED, "mamba_ssd_scan: d_head %d / d_state %d outside the chunked kernels' tiling", P, N);
     if (((uintptr_t)bc | (uintptr_t)y) & 15)
         return fail(B200_EUNSUPPORTED, "mamba_ssd_scan: buffers must be 16-byte aligned");
-    const int NC = ceil_div(T, SSD_Q);
-    const size_t g_f = (size_t)B * NC * SSD_Q * SSD_Q, dc_f = (size_t)B * p.n_heads * T * 2,
-                 cs_f = (size_t)B * NC * p.n_heads * P * N, de_f = (size_t)B * NC * p.n_heads;
+    const int NC = lay ? lay->n_chunks : ceil_div(T, SSD_Q);          // chunks per grid x
+    const int64_t chunks = lay ? lay->n_chunks : (int64_t)B * NC;     // entries of the per-chunk arrays
+    const int64_t NT = lay ? lay->rows : (int64_t)B * T;
+    const int2* tab = lay ? lay->chunks : nullptr;
+    const size_t g_f = (size_t)chunks * SSD_Q * SSD_Q, dc_f = (size_t)p.n_heads * NT * 2,
+                 cs_f = (size_t)chunks * p.n_heads * P * N, de_f = (size_t)chunks * p.n_heads;
     void* wsp;
     int rc = workspace(WS_ATTN).ensure((g_f + dc_f + cs_f + de_f) * sizeof(float) + 1024, &wsp);
     if (rc) return rc;
@@ -695,30 +736,31 @@ int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, con
     }
     B200_REQUIRE(smem_cb <= 160 * 1024 && smem_st <= 160 * 1024 && smem_out <= 160 * 1024, "mamba_ssd_scan: shared memory");
     B200_REQUIRE(NC <= 65535 * 32 && B <= 65535 && p.n_heads <= 65535, "mamba_ssd_scan: grid too large");
+    const int gz = lay ? 1 : B;
     // (the upper right quadrant of every G is never written and never read: s <= t only)
-    ssd_cb_kernel<<<dim3(3 * NC, B), SSD_THREADS, smem_cb, stream()>>>(bc, G, T, p);
+    ssd_cb_kernel<<<dim3(3 * NC, gz), SSD_THREADS, smem_cb, stream()>>>(bc, G, T, p, tab);
     B200_LAUNCH_CHECK("ssd_cb_kernel");
-    const dim3 grid(NC, p.n_heads, B);
+    const dim3 grid(NC, p.n_heads, gz);
     const bool half_tiles = !precise && N % 32 == 0;
     const size_t smem_st16 = (size_t)(SSD_Q * (N + 8) + SSD_Q * SSD_LDX16) * 2 + 2 * SSD_Q * 4;
     const size_t smem_out16 = (size_t)std::max(SSD_Q * (N + 8) + P * (N + 8), SSD_Q * SSD_LDM16 + SSD_Q * SSD_LDX16) * 2 + 2 * SSD_Q * 4;
     if (half_tiles)
-        ssd_chunk_state16_kernel<<<grid, SSD_THREADS, smem_st16, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate, decay, T, NC, p);
+        ssd_chunk_state16_kernel<<<grid, SSD_THREADS, smem_st16, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate, decay, T, NC, p, tab, NT);
     else if (precise)
-        ssd_chunk_state_kernel<true><<<grid, SSD_THREADS, smem_st, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate, decay, T, NC, p);
+        ssd_chunk_state_kernel<true><<<grid, SSD_THREADS, smem_st, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate, decay, T, NC, p, tab, NT);
     else
-        ssd_chunk_state_kernel<false><<<grid, SSD_THREADS, smem_st, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate, decay, T, NC, p);
+        ssd_chunk_state_kernel<false><<<grid, SSD_THREADS, smem_st, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate, decay, T, NC, p, tab, NT);
     B200_LAUNCH_CHECK("ssd_chunk_state_kernel");
     const int64_t elems = (int64_t)B * p.n_heads * P * N;
     ssd_carry_kernel<<<(unsigned)std::min<int64_t>(ceil_div64(elems, 256), (int64_t)num_sms() * 16), 256, 0, stream()>>>(
-        cstate, decay, state, B, NC, p);
+        cstate, decay, state, B, NC, p, lay ? lay->seq_chunk0 : nullptr);
     B200_LAUNCH_CHECK("ssd_carry_kernel");
     if (half_tiles)
-        ssd_chunk_out16_kernel<<<grid, SSD_THREADS, smem_out16, stream()>>>(bc, G, dtcum, cstate, D, y, T, NC, p);
+        ssd_chunk_out16_kernel<<<grid, SSD_THREADS, smem_out16, stream()>>>(bc, G, dtcum, cstate, D, y, T, NC, p, tab, NT);
     else if (precise)
-        ssd_chunk_out_kernel<true><<<grid, SSD_THREADS, smem_out, stream()>>>(bc, G, dtcum, cstate, D, y, T, NC, p);
+        ssd_chunk_out_kernel<true><<<grid, SSD_THREADS, smem_out, stream()>>>(bc, G, dtcum, cstate, D, y, T, NC, p, tab, NT);
     else
-        ssd_chunk_out_kernel<false><<<grid, SSD_THREADS, smem_out, stream()>>>(bc, G, dtcum, cstate, D, y, T, NC, p);
+        ssd_chunk_out_kernel<false><<<grid, SSD_THREADS, smem_out, stream()>>>(bc, G, dtcum, cstate, D, y, T, NC, p, tab, NT);
     B200_LAUNCH_CHECK("ssd_chunk_out_kernel");
     return B200_OK;
 }

@@ -372,10 +372,17 @@ __global__ void __launch_bounds__(1024) penalty_kernel(float* __restrict__ logit
     }
 }
 
+// seq_off (optional): row r's tokens are tokens[seq_off[r] .. seq_off[r + 1]) instead of
+// tokens[r T .. (r + 1) T).
 __global__ void history_push_kernel(int32_t* __restrict__ hist, int cap, int32_t* __restrict__ totals,
-                                    const int32_t* __restrict__ tokens, int rows, int T) {
+                                    const int32_t* __restrict__ tokens, int rows, int T,
+                                    const int32_t* __restrict__ seq_off) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= rows) return;
+    if (seq_off) {
+        tokens += seq_off[r] - (int64_t)r * (seq_off[r + 1] - seq_off[r]);
+        T = seq_off[r + 1] - seq_off[r];
+    }
     int total = totals[r];
     const int first = T > cap ? T - cap : 0;       // older prompt tokens would be overwritten anyway
     total += first;
@@ -505,10 +512,11 @@ int sample_rows(float* logits, int V, int rows, const int32_t* hist, int cap, co
 }
 
 int history_push(int32_t* hist, int cap, int32_t* totals, const int32_t* tokens, int rows) {
-    return history_push_prompt(hist, cap, totals, tokens, rows, 1);
+    return history_push_prompt(hist, cap, totals, tokens, rows, 1, nullptr);
 }
-int history_push_prompt(int32_t* hist, int cap, int32_t* totals, const int32_t* tokens, int rows, int T) {
-    history_push_kernel<<<ceil_div(rows, 128), 128, 0, stream()>>>(hist, cap, totals, tokens, rows, T);
+int history_push_prompt(int32_t* hist, int cap, int32_t* totals, const int32_t* tokens, int rows, int T,
+                        const int32_t* seq_off) {
+    history_push_kernel<<<ceil_div(rows, 128), 128, 0, stream()>>>(hist, cap, totals, tokens, rows, T, seq_off);
     B200_LAUNCH_CHECK("history_push_kernel");
     return B200_OK;
 }

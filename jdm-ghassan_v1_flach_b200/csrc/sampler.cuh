@@ -22,8 +22,10 @@ int sample_rows(float* logits, int V, int rows, const int32_t* hist, int cap, co
 
 // hist[r] <- tokens[r] appended (ring), totals[r] += 1, for every row.
 int history_push(int32_t* hist, int cap, int32_t* totals, const int32_t* tokens, int rows);
-// The prompt: tokens [rows, T] appended row by row.
-int history_push_prompt(int32_t* hist, int cap, int32_t* totals, const int32_t* tokens, int rows, int T);
+// The prompt: tokens [rows, T] appended row by row; with seq_off (device, [rows + 1]) row r's
+// tokens are tokens[seq_off[r] .. seq_off[r + 1]) and T is ignored.
+int history_push_prompt(int32_t* hist, int cap, int32_t* totals, const int32_t* tokens, int rows, int T,
+                        const int32_t* seq_off = nullptr);
 
 // Sum over rows with a target in [0, V) of logZ - logit[target] (+ z * logZ^2), added to
 // acc[0] (double) and the number of such rows to acc[1] (as a double-sized int64); losses:

@@ -176,7 +176,8 @@ static void drop_graph(b200_decoder* dec) {
 // The next token of sequences [b0, b0 + B) from their logits: the greedy arg-max, or - with
 // b200_decoder_set_sampling - Sampler::sample on the device after the T tokens just fed
 // (fed [B, T]) have joined the sequences' histories.  next == nullptr only records the history.
-static int pick_next(b200_decoder* dec, float* logits, const int32_t* fed, int T, int32_t* next, int b0, int B) {
+static int pick_next(b200_decoder* dec, float* logits, const int32_t* fed, int T, int32_t* next, int b0, int B,
+                     const int32_t* seq_off = nullptr) {
     if (!dec->sampling) {
         if (!next) return B200_OK;
         argmax_rows_kernel<<<B, 1024, 0, stream()>>>(logits, dec->vocab, next);
@@ -184,7 +185,7 @@ static int pick_next(b200_decoder* dec, float* logits, const int32_t* fed, int T
         return B200_OK;
     }
     int32_t* hist = dec->hist + (int64_t)b0 * DEC_HIST_CAP;
-    int rc = history_push_prompt(hist, DEC_HIST_CAP, dec->hist_total + b0, fed, B, T);
+    int rc = history_push_prompt(hist, DEC_HIST_CAP, dec->hist_total + b0, fed, B, T, seq_off);
     if (rc || !next) return rc;
     return sample_rows(logits, dec->vocab, B, hist, DEC_HIST_CAP, dec->hist_total + b0, dec->samp, dec->rng + 4 * b0, next,
                        dec->samp_ws);
@@ -378,6 +379,37 @@ __global__ void kv_prefill_kernel(const float* __restrict__ k, const float* __re
         v_pages[row * kvd + c] = float_to_half_bits(v[src + c]);
     }
 }
+// The same for packed sequences: row r belongs to sequence seq[r] at position pos[r].
+__global__ void kv_prefill_packed_kernel(const float* __restrict__ k, const float* __restrict__ v,
+                                         uint16_t* __restrict__ k_pages, uint16_t* __restrict__ v_pages,
+                                         const int32_t* __restrict__ page_table, const int32_t* __restrict__ seq,
+                                         const int32_t* __restrict__ pos, int max_pages, int page, int kvd) {
+    const int64_t r = blockIdx.y;
+    const int b = seq[r], t = pos[r];
+    const int64_t row = (int64_t)page_table[(int64_t)b * max_pages + t / page] * page + t % page;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < kvd; c += gridDim.x * blockDim.x) {
+        k_pages[row * kvd + c] = float_to_half_bits(k[r * kvd + c]);
+        v_pages[row * kvd + c] = float_to_half_bits(v[r * kvd + c]);
+    }
+}
+// dst[b, :] = src[last row of sequence b, :]; len[b], pos[b] from the sequence's length
+__global__ void last_rows_packed_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                        const int32_t* __restrict__ seq_off, int B, int d) {
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i < (int64_t)B * d) {
+        const int b = (int)(i / d), c = (int)(i - (int64_t)b * d);
+        dst[i] = src[(int64_t)(seq_off[b + 1] - 1) * d + c];
+    }
+}
+__global__ void prefill_len_packed_kernel(int32_t* __restrict__ len, int32_t* __restrict__ pos,
+                                          const int32_t* __restrict__ seq_off, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < B) {
+        const int n = seq_off[b + 1] - seq_off[b];
+        len[b] = n;
+        pos[b] = n - 1;
+    }
+}
 // dst[b, :] = src[b, T-1, :]
 __global__ void last_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int B, int T, int d) {
     const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -431,12 +463,14 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict
 // cross-entropy against its target is added to score_acc (cross_entropy_accumulate), the
 // lm_head running over SCORE_ROWS rows at a time.
 constexpr int SCORE_ROWS = 512;
+// lay (optional): the B sequences have different lengths and their tokens lie packed back to
+// back as lay describes; T is then ignored.
 static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* next, int b0, int B,
-                   const int32_t* score_targets = nullptr, double* score_acc = nullptr) {
+                   const int32_t* score_targets = nullptr, double* score_acc = nullptr, const SeqLayout* lay = nullptr) {
     const int d = dec->d;
     float *dx = dec->x + (int64_t)b0 * d, *dxb = dec->xb + (int64_t)b0 * d, *dlogits = dec->logits + (int64_t)b0 * dec->vocab;
     const int32_t* page_table = dec->page_table + (int64_t)b0 * dec->max_pages;
-    const int64_t NT = (int64_t)B * T;
+    const int64_t NT = lay ? lay->rows : (int64_t)B * T;
     const int qd = dec->H * dec->hd, kvd = dec->KV * dec->hd;
     cudaStream_t st = stream();
     int rc;
@@ -457,7 +491,7 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
           *y = reinterpret_cast<float*>(base + o_y), *q = reinterpret_cast<float*>(base + o_q),
           *k = reinterpret_cast<float*>(base + o_k), *v = reinterpret_cast<float*>(base + o_v),
           *at = reinterpret_cast<float*>(base + o_at);
-    int32_t* pos = reinterpret_cast<int32_t*>(base + o_pos);
+    const int32_t* pos = lay ? lay->pos : reinterpret_cast<int32_t*>(base + o_pos);
     __half* xb16 = reinterpret_cast<__half*>(base + o_xb16);      // fp16 copy of xb for the GEMMs (when d % 8 == 0)
     const bool want16 = d % 8 == 0 && d <= RRN_PER * 256;
     const int kind = tag_of_qkind(dec->qkind);
@@ -472,8 +506,8 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
     const int res_grid = (int)std::min<int64_t>(ceil_div64(NT * d, 256), (int64_t)num_sms() * 16);
     STEP(b200_embedding_forward_half(tokens, dec->embed, x, NT, d, dec->vocab));
     if (dec->emb_mult != 1.0f) STEP(b200_scale_inplace(x, dec->emb_mult, NT * d));
-    if (rope_on(dec)) {
-        prefill_pos_kernel<<<(unsigned)ceil_div64(NT, 256), 256, 0, st>>>(pos, B, T);
+    if (rope_on(dec) && !lay) {
+        prefill_pos_kernel<<<(unsigned)ceil_div64(NT, 256), 256, 0, st>>>(reinterpret_cast<int32_t*>(base + o_pos), B, T);
         B200_LAUNCH_CHECK("prefill_pos_kernel");
     }
     // x += res_mult * y followed by the next norm; fused when the row fits the registers
@@ -498,17 +532,30 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
             STEP(mamba2_forward(xb, w.mamba_in, w.conv_w, w.conv_b, w.dt_bias, w.a_log, w.D, w.mamba_norm, w.mamba_out,
                                 w.ssm_state + (int64_t)b0 * dec->d_inner * dec->mds, y, B, T, p, kind,
                                 w.conv_state + (int64_t)b0 * dec->conv_dim * std::max(dec->mk - 1, 1),
-                                want16 ? xb16 : nullptr));
+                                want16 ? xb16 : nullptr, lay));
         } else {
             STEP(lin(xb, w.wq, q, d, qd, want16 ? xb16 : nullptr));
             STEP(lin(xb, w.wk, k, d, kvd, want16 ? xb16 : nullptr));
             STEP(lin(xb, w.wv, v, d, kvd, want16 ? xb16 : nullptr));
             if (rope_on(dec))
                 STEP(b200_rope_forward_cached(q, k, pos, dec->inv_freq, NT, dec->H, dec->KV, dec->hd, dec->rope_type));
-            kv_prefill_kernel<<<dim3(ceil_div(kvd, 256), T, B), 256, 0, st>>>(k, v, w.k_pages, w.v_pages, page_table, T,
-                                                                            dec->max_pages, dec->page, kvd);
-            B200_LAUNCH_CHECK("kv_prefill_kernel");
-            STEP(b200_attention_forward_ex(q, k, v, at, nullptr, B, T, dec->H, dec->KV, dec->hd, dec->attn_scale, 0, nullptr));
+            if (!lay) {
+                kv_prefill_kernel<<<dim3(ceil_div(kvd, 256), T, B), 256, 0, st>>>(k, v, w.k_pages, w.v_pages, page_table, T,
+                                                                                dec->max_pages, dec->page, kvd);
+                B200_LAUNCH_CHECK("kv_prefill_kernel");
+                STEP(b200_attention_forward_ex(q, k, v, at, nullptr, B, T, dec->H, dec->KV, dec->hd, dec->attn_scale, 0, nullptr));
+            } else {
+                kv_prefill_packed_kernel<<<dim3(ceil_div(kvd, 256), (unsigned)NT), 256, 0, st>>>(
+                    k, v, w.k_pages, w.v_pages, page_table, lay->seq, lay->pos, dec->max_pages, dec->page, kvd);
+                B200_LAUNCH_CHECK("kv_prefill_packed_kernel");
+                // causal attention inside each sequence: one call per sequence on its rows
+                for (int b = 0; b < B; ++b) {
+                    const int64_t r0 = lay->host_off[b];
+                    STEP(b200_attention_forward_ex(q + r0 * qd, k + r0 * kvd, v + r0 * kvd, at + r0 * qd, nullptr, 1,
+                                                   lay->host_off[b + 1] - lay->host_off[b], dec->H, dec->KV, dec->hd,
+                                                   dec->attn_scale, 0, nullptr));
+                }
+            }
             STEP(lin(at, w.wo, y, qd, d));
         }
         STEP(residual_norm(w.ffn_norm));
@@ -533,18 +580,20 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
             if (dec->logits_scaling != 1.0f) STEP(b200_scale_inplace(lg, 1.0f / dec->logits_scaling, (int64_t)rows * V));
             STEP(cross_entropy_accumulate(lg, score_targets + r0, rows, V, 0.0f, losses, score_acc));
         }
-        STEP(pick_next(dec, nullptr, tokens, T, nullptr, b0, B));
+        STEP(pick_next(dec, nullptr, tokens, T, nullptr, b0, B, lay ? lay->seq_off : nullptr));
     } else {
         // logits of the last token of every sequence
-        last_rows_kernel<<<(unsigned)ceil_div64((int64_t)B * d, 256), 256, 0, st>>>(x, dx, B, T, d);
+        if (lay) last_rows_packed_kernel<<<(unsigned)ceil_div64((int64_t)B * d, 256), 256, 0, st>>>(x, dx, lay->seq_off, B, d);
+        else last_rows_kernel<<<(unsigned)ceil_div64((int64_t)B * d, 256), 256, 0, st>>>(x, dx, B, T, d);
         B200_LAUNCH_CHECK("last_rows_kernel");
         STEP(b200_rmsnorm_forward(dx, dec->final_norm, dxb, nullptr, B, d, dec->eps));
         STEP(b200_linear_forward_fp16(dxb, dec->lm_head, dlogits, B, d, dec->vocab));
         if (dec->logits_scaling != 1.0f)
             STEP(b200_scale_inplace(dlogits, 1.0f / dec->logits_scaling, (int64_t)B * dec->vocab));
-        STEP(pick_next(dec, dlogits, tokens, T, next, b0, B));
+        STEP(pick_next(dec, dlogits, tokens, T, next, b0, B, lay ? lay->seq_off : nullptr));
     }
-    prefill_len_kernel<<<ceil_div(B, 128), 128, 0, st>>>(dec->len + b0, dec->pos + b0, B, T);
+    if (lay) prefill_len_packed_kernel<<<ceil_div(B, 128), 128, 0, st>>>(dec->len + b0, dec->pos + b0, lay->seq_off, B);
+    else prefill_len_kernel<<<ceil_div(B, 128), 128, 0, st>>>(dec->len + b0, dec->pos + b0, B, T);
     B200_LAUNCH_CHECK("prefill_len_kernel");
 #undef STEP
     return B200_OK;
@@ -1102,6 +1151,89 @@ int b200_decoder_prefill(b200_decoder* dec, const int32_t* tokens_dev, int T, in
         dec->launches = 0;
     }
     dec->position = T;
+    return B200_OK;
+}
+
+int b200_decoder_prefill_ragged(b200_decoder* dec, const int32_t* tokens_dev, const int32_t* lengths_host,
+                                int32_t* next_dev) {
+    int rc = check_ready(dec);
+    if (rc) return rc;
+    B200_REQUIRE(tokens_dev && lengths_host, "decoder_prefill_ragged: null pointer");
+    B200_REQUIRE(dec->position == 0, "decoder_prefill_ragged: the sequences already hold %d tokens (reset first)", dec->position);
+    int longest = 0;
+    for (int b = 0; b < dec->batch; ++b) {
+        B200_REQUIRE(lengths_host[b] >= 1 && lengths_host[b] <= dec->max_ctx,
+                     "decoder_prefill_ragged: sequence %d has %d tokens (1 .. %d allowed)", b, lengths_host[b], dec->max_ctx);
+        longest = std::max(longest, lengths_host[b]);
+    }
+    // Groups of consecutive sequences of at most PREFILL_GROUP_TOKENS tokens together (a longer
+    // sequence forms a group of its own): bounds the prompt path's workspaces.
+    std::vector<int32_t> h;            // host image of one group's tables
+    int32_t* tables = nullptr;         // its device copy, sized for the largest group
+    size_t tables_cap = 0;
+    int64_t tok0 = 0;
+    for (int b0 = 0; b0 < dec->batch && rc == B200_OK;) {
+        int B = 0;
+        int64_t rows = 0;
+        while (b0 + B < dec->batch && (B == 0 || rows + lengths_host[b0 + B] <= PREFILL_GROUP_TOKENS)) rows += lengths_host[b0 + B++];
+        int n_chunks = 0;
+        for (int b = 0; b < B; ++b) n_chunks += ceil_div(lengths_host[b0 + b], SSD_Q);
+        // layout of the tables (int32 words): seq_off [B+1] | seq_chunk0 [B+1] | pos [rows] | seq [rows] | chunks [2 n_chunks]
+        const size_t o_off = 0, o_c0 = o_off + B + 1, o_pos = (o_c0 + B + 1 + 3) & ~(size_t)3, o_seq = o_pos + rows,
+                     o_chunks = (o_seq + rows + 3) & ~(size_t)3, words = o_chunks + 2 * (size_t)n_chunks;
+        h.assign(words, 0);
+        int64_t r = 0;
+        int c = 0;
+        for (int b = 0; b < B; ++b) {
+            const int n = lengths_host[b0 + b];
+            h[o_off + b] = (int32_t)r;
+            h[o_c0 + b] = c;
+            for (int t = 0; t < n; ++t) {
+                h[o_pos + r + t] = t;
+                h[o_seq + r + t] = b;
+            }
+            for (int t = 0; t < n; t += SSD_Q, ++c) {
+                h[o_chunks + 2 * c] = (int32_t)(r + t);
+                h[o_chunks + 2 * c + 1] = std::min(SSD_Q, n - t);
+            }
+            r += n;
+        }
+        h[o_off + B] = (int32_t)r;
+        h[o_c0 + B] = c;
+        if (words > tables_cap) {
+            if (tables) cudaFree(tables);
+            tables = nullptr;
+            cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&tables), words * 4);
+            if (e != cudaSuccess) return cuda_status(e, "decoder_prefill_ragged: cudaMalloc");
+            tables_cap = words;
+        }
+        cudaError_t e = cudaMemcpyAsync(tables, h.data(), words * 4, cudaMemcpyHostToDevice, stream());
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream());      // h is reused by the next group
+        if (e != cudaSuccess) { rc = cuda_status(e, "decoder_prefill_ragged: table upload"); break; }
+        SeqLayout lay;
+        lay.n_seq = B;
+        lay.rows = rows;
+        lay.n_chunks = n_chunks;
+        lay.seq_off = tables + o_off;
+        lay.seq_chunk0 = tables + o_c0;
+        lay.pos = tables + o_pos;
+        lay.seq = tables + o_seq;
+        lay.chunks = reinterpret_cast<const int2*>(tables + o_chunks);
+        lay.host_off = h.data() + o_off;
+        rc = prefill(dec, tokens_dev + tok0, 0, next_dev ? next_dev + b0 : nullptr, b0, B, nullptr, nullptr, &lay);
+        tok0 += rows;
+        b0 += B;
+    }
+    if (tables) {
+        cudaStreamSynchronize(stream());       // the kernels of the last group still read the tables
+        cudaFree(tables);
+    }
+    if (rc) return rc;
+    if (dec->graph && dec->ws_generation != workspace_generation()) {
+        drop_graph(dec);
+        dec->launches = 0;
+    }
+    dec->position = longest;
     return B200_OK;
 }
 

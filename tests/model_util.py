@@ -234,6 +234,18 @@ class CudaDecoder:
         self.lib.b200_synchronize()
         return nxt.cpu().numpy()
 
+    def prefill_ragged(self, prompts):
+        """prompts: one 1-D token array per sequence (different lengths); returns the picks."""
+        import torch
+        from gpu_util import dev
+        assert len(prompts) == self.batch
+        lengths = np.array([len(p) for p in prompts], np.int32)
+        t = dev(np.concatenate([np.asarray(p, np.int32) for p in prompts]))
+        nxt = torch.empty(self.batch, dtype=torch.int32, device="cuda")
+        self.lib.b200_decoder_prefill_ragged(self.handle, t, lengths.ctypes.data, nxt)
+        self.lib.b200_synchronize()
+        return nxt.cpu().numpy()
+
     def logits(self):
         import torch
         p = C.c_void_p()

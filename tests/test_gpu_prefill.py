@@ -141,3 +141,78 @@ def test_prefill_fp16_weights_and_reset(oracle):
     assert np.array_equal(b.logits(), first)
     a.close()
     b.close()
+
+
+RAGGED = [1, 63, 64, 129, 300, 2, 128, 257]
+
+
+@pytest.mark.parametrize("cfg_name", ["tiny", "narrow_heads"])
+def test_ragged_prefill_matches_one_sequence_at_a_time(oracle, cfg_name):
+    """Prompts of different lengths in one batch (b200_decoder_prefill_ragged): every sequence
+    ends where its own single-sequence prefill ends (logits, pick), and the batch then decodes
+    on, each sequence at its own position, like the single decoders do.  'narrow_heads' has a
+    Mamba head width outside the chunked scan's tiling, so its scan runs per sequence."""
+    cfg = TINY if cfg_name == "tiny" else dict(TINY, mamba_heads=16, mamba_d_head=32, mamba_d_state=64)
+    model = make_model(oracle, cfg, 6)
+    r = np.random.default_rng(11)
+    prompts = [r.integers(0, cfg["vocab"], n).astype(np.int32) for n in RAGGED]
+    B = len(prompts)
+    batch = CudaDecoder(model, batch=B, max_ctx=320)
+    got_next = batch.prefill_ragged(prompts)
+    got = batch.logits()
+    singles = []
+    for b, p in enumerate(prompts):
+        one = CudaDecoder(model, batch=1, max_ctx=320)
+        nxt = one.prefill(p[None, :])
+        want = one.logits()[0]
+        fp16_close(got[b], want)
+        if np.sort(want)[-1] - np.sort(want)[-2] > 1e-2:          # a clear winner: the picks agree
+            assert int(got_next[b]) == int(nxt[0])
+        singles.append(one)
+    assert np.array_equal(got_next, got.argmax(axis=1))
+    for s in range(3):
+        toks = r.integers(0, cfg["vocab"], B).astype(np.int32)
+        batch.step_host(toks)
+        now = batch.logits()
+        for b, one in enumerate(singles):
+            one.step_host(toks[b:b + 1])
+            fp16_close(now[b], one.logits()[0])
+    for one in singles:
+        one.close()
+    batch.close()
+
+
+def test_ragged_prefill_rejects_bad_lengths(oracle):
+    from gpu_util import B200Error
+    model = make_model(oracle, TINY, 6)
+    dec = CudaDecoder(model, batch=2, max_ctx=64)          # one KV page of 64 tokens
+    with pytest.raises(B200Error):
+        dec.prefill_ragged([np.zeros(0, np.int32), np.zeros(4, np.int32)])
+    with pytest.raises(B200Error):
+        dec.prefill_ragged([np.zeros(4, np.int32), np.zeros(65, np.int32)])
+    assert dec.prefill_ragged([np.zeros(4, np.int32), np.ones(64, np.int32)]).shape == (2,)
+    with pytest.raises(B200Error):                                     # not empty any more
+        dec.prefill_ragged([np.zeros(4, np.int32), np.ones(4, np.int32)])
+    dec.close()
+
+
+def test_ragged_prefill_in_several_groups(oracle):
+    """More tokens than one group holds (32768): the sequences are processed in groups of
+    consecutive sequences; equal lengths must reproduce the rectangular prefill bit for bit
+    where the grouping coincides."""
+    cfg = dict(TINY, n_layers=2, layer_types=[0, 1])
+    model = make_model(oracle, cfg, 7)
+    r = np.random.default_rng(3)
+    lengths = [9000, 12000, 20000, 700]
+    prompts = [r.integers(0, cfg["vocab"], n).astype(np.int32) for n in lengths]
+    dec = CudaDecoder(model, batch=4, max_ctx=20000)
+    nxt = dec.prefill_ragged(prompts)
+    got = dec.logits()
+    one = CudaDecoder(model, batch=1, max_ctx=20000)
+    for b in (2, 3):
+        one.reset()
+        one.prefill(prompts[b][None, :])
+        fp16_close(got[b], one.logits()[0])
+    assert np.array_equal(nxt, got.argmax(axis=1))
+    one.close()
+    dec.close()
