@@ -164,6 +164,13 @@ int b200_moe_experts_rows(const uint16_t* rows16, const int32_t* offsets, const 
                           int d, int E, int qkind);
 int b200_moe_shared_combine(const float* x, const void* sh_g, const void* sh_u, const void* sh_d, const float* y,
                             const int32_t* inv, const float* w, float* out, int64_t N, int d, int K, int SH, int qkind);
+/* The two halves of shared_combine, for callers that overlap the shared expert with the
+ * exchange: out = shared_expert(x) (nothing when a matrix is null or SH == 0), then
+ * out (+)= sum_k w[t,k] * y[inv[t*K+k]] (accumulate != 0: onto what out holds). */
+int b200_moe_shared_expert(const float* x, const void* sh_g, const void* sh_u, const void* sh_d, float* out, int64_t N,
+                           int d, int SH, int qkind);
+int b200_moe_combine(const float* y, const int32_t* inv, const float* w, float* out, int64_t N, int d, int K,
+                     int accumulate);
 
 /* ---- Mamba-2: cuda_ops.h:142-189 ------------------------------------------------ */
 int b200_mamba2_forward(const float* x, const float* w_in, const float* conv_w, const float* conv_b,

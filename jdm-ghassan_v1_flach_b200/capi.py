@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 LIB_PATH = os.path.join(HERE, "libb200ops.so")
 HEADERS = [os.path.join(ROOT, "include", "b200ops.h"), os.path.join(ROOT, "include", "b200step.h"),
-           os.path.join(ROOT, "include", "b200gguf.h")]
+           os.path.join(ROOT, "include", "b200gguf.h"), os.path.join(ROOT, "include", "b200ep.h")]
 
 _SCALARS = {
     "int": C.c_int, "float": C.c_float, "int64_t": C.c_int64, "uint64_t": C.c_uint64,

@@ -107,8 +107,9 @@ __device__ __noinline__ void gemm_build_slots(const GemmArgs& a, int* tab, int* 
     }
     int* cnt = scan;                 // [groups]
     int* base = scan + a.groups;     // [groups + 1]
+    // a group mapped to a negative block is a gap between groups: its rows are skipped
     for (int g = threadIdx.x; g < a.groups; g += blockDim.x)
-        cnt[g] = (a.offsets[g + 1] - a.offsets[g] + a.tile_m - 1) / a.tile_m;
+        cnt[g] = (a.group_map && a.group_map[g] < 0) ? 0 : (a.offsets[g + 1] - a.offsets[g] + a.tile_m - 1) / a.tile_m;
     __syncthreads();
     if (threadIdx.x < 32) {
         const int per = (a.groups + 31) >> 5, g0 = threadIdx.x * per;
@@ -144,11 +145,12 @@ __device__ __noinline__ void gemm_build_slots(const GemmArgs& a, int* tab, int* 
 }
 
 // The walk over the offsets for group lists the table does not hold.
-__device__ __noinline__ int4 gemm_slot_walk(const int32_t* offsets, int groups, int tile_m, int slot) {
+__device__ __noinline__ int4 gemm_slot_walk(const int32_t* offsets, const int32_t* group_map, int groups, int tile_m,
+                                            int slot) {
     int lo = offsets[0];
     for (int g = 0; g < groups; ++g) {
         const int hi = offsets[g + 1];
-        const int tiles = (hi - lo + tile_m - 1) / tile_m;
+        const int tiles = (group_map && group_map[g] < 0) ? 0 : (hi - lo + tile_m - 1) / tile_m;
         if (slot < tiles) return make_int4(1, g, lo + slot * tile_m, hi);
         slot -= tiles;
         lo = hi;
@@ -175,7 +177,7 @@ __device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, const int* tab, 
         found = slot < tab[0];
         if (found) { w.group = tab[1 + 3 * slot]; w.row0 = tab[2 + 3 * slot]; w.row_end = tab[3 + 3 * slot]; }
     } else {
-        const int4 r = gemm_slot_walk(a.offsets, a.groups, a.tile_m, slot);
+        const int4 r = gemm_slot_walk(a.offsets, a.group_map, a.groups, a.tile_m, slot);
         found = r.x != 0;
         if (found) { w.group = r.y; w.row0 = r.z; w.row_end = r.w; }
     }

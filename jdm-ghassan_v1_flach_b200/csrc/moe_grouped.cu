@@ -213,42 +213,54 @@ int moe_experts_rows(const __half* rows16, const int32_t* offsets, const int32_t
                        nullptr, d, 1.0f, group_map);
 }
 
+// out [N, d] = shared_expert(x); false "shared" (a null matrix or SH == 0) leaves out untouched.
+int moe_shared_expert(const float* x, const void* sh_g, const void* sh_u, const void* sh_d, float* out, int64_t N, int d,
+                      int SH, int kind) {
+    if (N <= 0) return B200_OK;
+    if (!(sh_g && sh_u && sh_d && SH > 0)) return B200_OK;
+    B200_REQUIRE(x && out, "moe_shared_expert: null pointer");
+    int rc = check_ep_kind("moe_shared_combine", kind, d, SH);
+    if (rc) return rc;
+    void* wsp;
+    const size_t xs_bytes = ((size_t)N * d * 2 + 255) & ~(size_t)255;
+    rc = workspace(WS_MOE).ensure(xs_bytes + (size_t)N * SH * 2 + 256, &wsp);
+    if (rc) return rc;
+    __half* xs = static_cast<__half*>(wsp);
+    __half* sact = reinterpret_cast<__half*>(static_cast<char*>(wsp) + xs_bytes);
+    rc = pack_rows_f16(x, nullptr, 1, xs, N, d);
+    if (rc) return rc;
+    if (kind == KIND_F16) {
+        rc = umma_gemm(GEMM_EPI_SWIGLU, xs, N, static_cast<const __half*>(sh_g), static_cast<const __half*>(sh_u), SH,
+                       nullptr, 1, (int)N, SH, d, nullptr, sact, SH, 1.0f);
+        if (rc) return rc;
+        return umma_gemm(GEMM_EPI_STORE, sact, N, static_cast<const __half*>(sh_d), nullptr, d, nullptr, 1, (int)N, d, SH,
+                         out, nullptr, d, 1.0f);
+    }
+    rc = umma_gemm_q(GEMM_EPI_SWIGLU, kind, xs, N, sh_g, sh_u, SH, nullptr, 1, (int)N, SH, d, nullptr, sact, SH, 1.0f);
+    if (rc) return rc;
+    return umma_gemm_q(GEMM_EPI_STORE, kind, sact, N, sh_d, nullptr, d, nullptr, 1, (int)N, d, SH, out, nullptr, d, 1.0f);
+}
+
+// out [N, d] (+)= sum_k w[t, k] * y[inv[t K + k]] in k order; accumulate: onto the shared
+// expert's result already in out.
+int moe_combine(const float* y, const int32_t* inv, const float* w, float* out, int64_t N, int d, int K, bool accumulate) {
+    if (N <= 0) return B200_OK;
+    B200_REQUIRE(y && inv && w && out && d % 4 == 0, "moe_combine: bad arguments");
+    const int64_t total = N * (d >> 2);
+    const int grid = (int)std::min<int64_t>(ceil_div64(total, 256), (int64_t)num_sms() * 16);
+    moe_combine_kernel<<<grid, 256, 0, stream()>>>(y, inv, w, out, (int)N, K, d, accumulate ? 1 : 0);
+    B200_LAUNCH_CHECK("moe_combine_kernel");
+    return B200_OK;
+}
+
 int moe_shared_combine(const float* x, const void* sh_g, const void* sh_u, const void* sh_d, const float* y,
                        const int32_t* inv, const float* w, float* out, int64_t N, int d, int K, int SH, int kind) {
     if (N <= 0) return B200_OK;
     B200_REQUIRE(x && y && inv && w && out && d % 4 == 0, "moe_shared_combine: bad arguments");
     const bool shared = sh_g && sh_u && sh_d && SH > 0;
-    if (shared) {
-        int rc = check_ep_kind("moe_shared_combine", kind, d, SH);
-        if (rc) return rc;
-        void* wsp;
-        const size_t xs_bytes = ((size_t)N * d * 2 + 255) & ~(size_t)255;
-        rc = workspace(WS_MOE).ensure(xs_bytes + (size_t)N * SH * 2 + 256, &wsp);
-        if (rc) return rc;
-        __half* xs = static_cast<__half*>(wsp);
-        __half* sact = reinterpret_cast<__half*>(static_cast<char*>(wsp) + xs_bytes);
-        rc = pack_rows_f16(x, nullptr, 1, xs, N, d);
-        if (rc) return rc;
-        if (kind == KIND_F16) {
-            rc = umma_gemm(GEMM_EPI_SWIGLU, xs, N, static_cast<const __half*>(sh_g), static_cast<const __half*>(sh_u), SH,
-                           nullptr, 1, (int)N, SH, d, nullptr, sact, SH, 1.0f);
-            if (rc) return rc;
-            rc = umma_gemm(GEMM_EPI_STORE, sact, N, static_cast<const __half*>(sh_d), nullptr, d, nullptr, 1, (int)N, d, SH,
-                           out, nullptr, d, 1.0f);
-        } else {
-            rc = umma_gemm_q(GEMM_EPI_SWIGLU, kind, xs, N, sh_g, sh_u, SH, nullptr, 1, (int)N, SH, d, nullptr, sact, SH,
-                             1.0f);
-            if (rc) return rc;
-            rc = umma_gemm_q(GEMM_EPI_STORE, kind, sact, N, sh_d, nullptr, d, nullptr, 1, (int)N, d, SH, out, nullptr, d,
-                             1.0f);
-        }
-        if (rc) return rc;
-    }
-    const int64_t total = N * (d >> 2);
-    const int grid = (int)std::min<int64_t>(ceil_div64(total, 256), (int64_t)num_sms() * 16);
-    moe_combine_kernel<<<grid, 256, 0, stream()>>>(y, inv, w, out, (int)N, K, d, shared ? 1 : 0);
-    B200_LAUNCH_CHECK("moe_combine_kernel");
-    return B200_OK;
+    const int rc = moe_shared_expert(x, sh_g, sh_u, sh_d, out, N, d, SH, kind);
+    if (rc) return rc;
+    return moe_combine(y, inv, w, out, N, d, K, shared);
 }
 
 }  // namespace b200
@@ -274,6 +286,15 @@ int b200_moe_experts_rows(const uint16_t* rows16, const int32_t* offsets, const 
     B200_REQUIRE(qkind >= -1 && qkind <= 3, "moe_experts_rows: unknown qkind %d", qkind);
     return moe_experts_rows(reinterpret_cast<const __half*>(rows16), offsets, group_map, groups, R, gates, ups, downs,
                             n_local, y, d, E, tag_of_qkind(qkind));
+}
+int b200_moe_shared_expert(const float* x, const void* sh_g, const void* sh_u, const void* sh_d, float* out, int64_t N,
+                           int d, int SH, int qkind) {
+    B200_REQUIRE(qkind >= -1 && qkind <= 3, "moe_shared_expert: unknown qkind %d", qkind);
+    return moe_shared_expert(x, sh_g, sh_u, sh_d, out, N, d, SH, tag_of_qkind(qkind));
+}
+int b200_moe_combine(const float* y, const int32_t* inv, const float* w, float* out, int64_t N, int d, int K,
+                     int accumulate) {
+    return moe_combine(y, inv, w, out, N, d, K, accumulate != 0);
 }
 int b200_moe_shared_combine(const float* x, const void* sh_g, const void* sh_u, const void* sh_d, const float* y,
                             const int32_t* inv, const float* w, float* out, int64_t N, int d, int K, int SH, int qkind) {

@@ -186,3 +186,119 @@ def test_dispatch_free_form_replays_as_a_cuda_graph(oracle):
         assert torch.equal(got_idx, want_idx)
         assert np.array_equal(host(got).view(np.uint32), host(want).view(np.uint32))
     assert pkg.lib().raw("b200_stream_status") == 0
+
+
+# ---------------------------------------------------------------------------
+# The C host over peer memory (include/b200ep.h).  G ranks live in this process on one GPU,
+# connected by plain pointers; the phases run in lockstep (phase p of every rank before
+# phase p + 1 of any), so every flag is already raised when its wait starts.
+# ---------------------------------------------------------------------------
+import ctypes as C
+
+
+class _EpRanks:
+    def __init__(self, dc, G, T_max, d, E, ne, K, SH, wkind, capacity=0):
+        from gpu_util import pkg
+        self.lib, self.G, self.d = pkg.lib(), G, d
+        self.keep = []
+        self.h = []
+        for r in range(G):
+            h = C.c_void_p()
+            self.lib.b200_ep_create(C.byref(h), r, G, d, E, ne, K, SH, wkind, T_max, capacity)
+            sh = [ep.shard_experts(dc[k], ne, r, G) for k in ("gates", "ups", "downs")]
+            self.keep.append(sh)
+            self.lib.b200_ep_set_weights(h, dc["router_w"], dc["router_bias"], sh[0], sh[1], sh[2], dc["sh_g"], dc["sh_u"],
+                                         dc["sh_d"])
+            self.h.append(h)
+        arr = (C.c_void_p * G)(*[h.value for h in self.h])
+        for h in self.h:
+            self.lib.b200_ep_connect_local(h, arr)
+
+    def forward(self, x):
+        T = x.shape[0]
+        for phase in range(4):
+            for h in self.h:
+                self.lib.b200_ep_phase(h, phase, x, T)
+        outs, idxs = [], []
+        for h in self.h:
+            p, n = C.c_void_p(), C.c_int()
+            self.lib.b200_ep_output(h, C.byref(p))
+            o = torch.empty((T, self.d), device="cuda")
+            self.lib.b200_copy(o, 1, p.value, 1, T * self.d * 4)
+            outs.append(o)
+            pi = C.c_void_p()
+            self.lib.b200_ep_routing(h, C.byref(pi), None, C.byref(n))
+            K = self.K
+            i = torch.empty((n.value, K), dtype=torch.int32, device="cuda")
+            if n.value:
+                self.lib.b200_copy(i, 1, pi.value, 1, n.value * K * 4)
+            idxs.append(i)
+        torch.cuda.synchronize()
+        return outs, torch.cat(idxs, 0)
+
+    def close(self):
+        for h in self.h:
+            self.lib.b200_ep_destroy(h)
+
+
+@pytest.mark.parametrize("G", [1, 2, 8])
+def test_peer_memory_host_with_ranks_in_one_process(oracle, G):
+    """Config-3 shape; several passes of different sizes through the same buffers (the epoch
+    flags must tell them apart), a ragged token count, fewer tokens than ranks."""
+    from gpu_util import dev, fp16_close, host, pkg
+    d, E, ne, K, SH, wkind = 1536, 512, 64, 6, 1024, 3
+    c, dc = _dev_case(oracle, 11, 200, d, E, ne, K, SH, wkind)
+    ranks = _EpRanks(dc, G, 200, d, E, ne, K, SH, wkind)
+    ranks.K = K
+    r = np.random.default_rng(5)
+    for T in (200, 77, 3, 200):
+        x = dev(r.standard_normal((T, d)).astype(np.float32))
+        outs, idx = ranks.forward(x)
+        want, want_idx = _single_gpu_layer(dict(dc, x=x), T, d, E, ne, K, SH, wkind)
+        assert np.array_equal(host(idx), want_idx)
+        for o in outs:                                   # every rank holds the whole output
+            if T >= 32:      # the same tensor-core kernels, the same order of additions: identical bits
+                assert np.array_equal(host(o).view(np.uint32), want.view(np.uint32))
+            else:            # a few tokens take the single GPU's fp32 few-token kernels instead
+                fp16_close(host(o), want)
+                assert np.array_equal(host(o), host(outs[0]))
+    assert pkg.lib().raw("b200_stream_status") == 0
+    ranks.close()
+
+
+def test_peer_memory_host_capacity_overflow_is_reported(oracle):
+    """A per-pair capacity below what the routing sends: the pass completes (rows beyond the
+    capacity are dropped) and the status word reports it."""
+    from gpu_util import pkg
+    d, E, ne, K, SH, wkind = 256, 256, 8, 2, 256, 3
+    c, dc = _dev_case(oracle, 3, 64, d, E, ne, K, SH, wkind)
+    ranks = _EpRanks(dc, 2, 64, d, E, ne, K, SH, wkind, capacity=4)
+    ranks.K = K
+    ranks.forward(dc["x"])
+    assert pkg.lib().raw("b200_stream_status") != 0
+    assert pkg.lib().raw("b200_stream_status") == 0          # cleared by the read
+    ranks.close()
+
+
+def test_peer_memory_host_wait_runs_out(oracle):
+    """A rank whose peers never dispatch: its bounded wait gives up, the kernel returns, the
+    status word says so and the library stays usable."""
+    from gpu_util import B200Error, pkg
+    lib = pkg.lib()
+    d, E, ne, K, SH, wkind = 256, 256, 8, 2, 256, 3
+    c, dc = _dev_case(oracle, 3, 64, d, E, ne, K, SH, wkind)
+    ranks = _EpRanks(dc, 2, 64, d, E, ne, K, SH, wkind)
+    ranks.K = K
+    lib.b200_ep_set_spin_limit(ranks.h[0], 2000)
+    lib.b200_ep_phase(ranks.h[0], 0, dc["x"], 64)            # rank 1 never runs phase 0
+    lib.b200_ep_phase(ranks.h[0], 1, dc["x"], 64)
+    assert lib.raw("b200_stream_status") != 0
+    assert lib.raw("b200_stream_status") == 0
+    # a complete pass afterwards is clean: rank 1 catches up with the same epoch
+    lib.b200_ep_phase(ranks.h[1], 0, dc["x"], 64)
+    for phase in (1, 2, 3):
+        for h in ranks.h:
+            lib.b200_ep_phase(h, phase, dc["x"], 64)
+    torch.cuda.synchronize()
+    assert lib.raw("b200_stream_status") == 0
+    ranks.close()
