@@ -406,6 +406,14 @@ def time_kernel_gbs(fn, bytes_per_launch, iters=20):
     return bytes_per_launch / (ms * 1e-3) / 1e9, ms
 
 
+def peak_bf16_tflops():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f).get("bf16_tflops", 1646.6))
+    return 1646.6
+
+
 def moe_layer_bench(lib, rank, world, tokens=4096, iters=10, graph=False):
     """The MoE layer alone at the H-Tiny shape (hidden 1536, 64 experts, top-6, ffn 512,
     shared 1024, Q4_K) on `tokens` replicated tokens: the single-GPU layer at world 1,
@@ -462,8 +470,75 @@ def moe_layer_bench(lib, rank, world, tokens=4096, iters=10, graph=False):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0])
 
+    peer = None
     if world > 1:
-        del gates, ups, downs
+        # the same layer through the C host over peer memory (include/b200ep.h): no NCCL, no host read
+        import ctypes as C
+        want = torch.empty(tokens, d, device="cuda")
+        want_idx = torch.empty(tokens, K, dtype=torch.int32, device="cuda")
+        lib.b200_moe_forward_bias_half(x, router, bias, gates, ups, downs, sh[0], sh[1], sh[2], want, None, want_idx, None,
+                                       None, None, None, tokens, d, E, ne, K, SH, q)
+        single_ms = time_kernel_gbs(lambda: lib.b200_moe_forward_bias_half(
+            x, router, bias, gates, ups, downs, sh[0], sh[1], sh[2], want, None, None, None, None, None, None, tokens, d, E, ne,
+            K, SH, q), 1, iters=iters)[1]
+        h = C.c_void_p()
+        lib.b200_ep_create(C.byref(h), rank, world, d, E, ne, K, SH, q, tokens, 0)
+        lib.b200_ep_set_weights(h, router, bias, layer.gates, layer.ups, layer.downs, sh[0], sh[1], sh[2])
+        rdv = "/tmp/b200ep_%s_%d" % (os.environ.get("MASTER_PORT", "0"), tokens)
+        if rank == 0:
+            os.makedirs(rdv, exist_ok=True)
+            for f in os.listdir(rdv):
+                os.remove(os.path.join(rdv, f))
+        dist.barrier()
+        lib.b200_ep_rendezvous_dir(h, rdv.encode(), 60000)
+        dist.barrier()
+
+        def peer_pass():
+            lib.b200_ep_forward(h, x, tokens)
+
+        run_saved = run
+        ms_peer = None
+        for _ in range(3):
+            peer_pass()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(iters):
+            peer_pass()
+        t1.record()
+        torch.cuda.synchronize()
+        tt = torch.tensor([t0.elapsed_time(t1) / iters], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_peer = float(tt[0])
+        po = C.c_void_p()
+        lib.b200_ep_output(h, C.byref(po))
+        got = torch.empty(tokens, d, device="cuda")
+        lib.b200_copy(got, 1, po.value, 1, tokens * d * 4)
+        link = C.c_double()
+        lib.b200_ep_link_bytes(h, C.byref(link))
+        torch.cuda.synchronize()
+        diff = (got - want).abs().max()
+        same = torch.tensor([float(torch.equal(got, want)), float(lib.raw("b200_stream_status") == 0)], device="cuda",
+                            dtype=torch.float64)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+        link_t = torch.tensor([link.value], device="cuda", dtype=torch.float64)
+        dist.all_reduce(link_t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        lib.b200_ep_destroy(h)
+        flops_rank = (tokens * K * 3 * 2 * E * d + tokens * 3 * 2 * SH * d) / world
+        t_math = flops_rank / (peak_bf16_tflops() * 1e12)
+        t_link = float(link_t[0]) / 770e9
+        peer = {"ms_per_layer": ms_peer, "single_gpu_ms_per_layer": single_ms, "speedup_vs_single_gpu": single_ms / ms_peer,
+                "link_bytes_per_rank": float(link_t[0]),
+                "roofline": {"target_ms": max(t_math, t_link) * 1e3, "bound": "tensor" if t_math >= t_link else "nvlink",
+                             "math_ms": t_math * 1e3, "link_ms_at_770_GBs": t_link * 1e3,
+                             "frac": max(t_math, t_link) * 1e3 / ms_peer},
+                "ep_parity": {"bit_identical_to_single_gpu": bool(same[0] == 1.0), "max_abs_diff": float(diff),
+                              "status_clean": bool(same[1] == 1.0)},
+                "mode": "expert parallel over peer memory: dispatch / return / gather kernels with NVLink stores and epoch flags"}
+        del gates, ups, downs, want, got
     ms = timed(False)
     ms_reduce = timed(True) if world > 1 else None
     ms_graph, graph_note = None, None
@@ -486,6 +561,7 @@ def moe_layer_bench(lib, rank, world, tokens=4096, iters=10, graph=False):
             "ms_per_layer_reduce_form": ms_reduce,
             "ms_per_layer_reduce_form_graph": ms_graph if ms_graph is not None else graph_note,
             "reduce_form": None if ms_reduce is None else "no dispatch: routing per token slice + all-gather of the indices, local experts on the packed rows, one NCCL all-reduce of the output",
+            "peer_memory": peer,
             "shape": "hidden 1536, 64 experts, top-6, ffn 512, shared 1024, Q4_K"}
 
 
@@ -896,7 +972,11 @@ def main():
     q4k_bytes = proj_n * d // 256 * 144
     q4k_gbs, q4k_ms = time_kernel_gbs(q4k_call, q4k_bytes, iters=len(mamba_layers) * 2)
     moe = moe_layer_bench(lib, rank, world, graph=args.ep_graph)
-    batch64 = moe_sweep = mamba_ops = None
+    ep_sweep = None
+    if world > 1 and not args.quick:
+        # where the exchange pays: more tokens per pass (the prompt side of the workload)
+        ep_sweep = [moe_layer_bench(lib, rank, world, tokens=t, iters=5) for t in (16384, 65536)]
+    batch64 = moe_sweep = mamba_ops = quantizers = None
     if world == 1 and B == 1 and not args.small and not args.quick:
         model.close()
         model = None
@@ -939,6 +1019,7 @@ def main():
             "moe_sweep": moe_sweep,
             "mamba_ops": mamba_ops,
             "quantizers": quantizers,
+            "moe_layer_ep_sweep": ep_sweep,
             "batch64": batch64,
             "prefill": None if prefill_ms is None else {
                 "tokens": B * args.ctx, "ms": prefill_ms, "tok_s": B * args.ctx / (prefill_ms * 1e-3),

@@ -16,7 +16,8 @@
 #include <vector>
 
 #include "../../include/b200ep.h"
-#include "common.cuh"
+#include "gemm.cuh"
+#include "linear.cuh"
 
 namespace b200 {
 
@@ -68,22 +69,32 @@ __device__ __forceinline__ int32_t* hdr_of(const EpDev& e, int r, int src) {
     return reinterpret_cast<int32_t*>(e.peers[r] + e.off_hdr) + (size_t)src * (e.nl + 2);
 }
 
-// rows [NK, d] fp16 sorted by expert, offsets [ne + 1]: the rows of rank r's experts go to
-// region `rank` of r's receive buffer; header = rows per local expert, first row in my
-// order, rows sent.  One warp per row.
-__global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDev e, const uint4* __restrict__ rows,
-                                                          const int32_t* __restrict__ offsets, int64_t NK, uint32_t epoch) {
+// x [n, d] fp32 (my token slice), grouped [NK] (slot numbers sorted by expert; slot / K is the
+// token), offsets [ne + 1]: row i of that order is rounded to fp16 (clamped, as the packing of
+// the single-GPU layer does) and stored into region `rank` of the receive buffer of the rank
+// that owns its expert; header = rows per local expert, first row in my order, rows sent.
+// One warp per row.
+__global__ void __launch_bounds__(256) ep_pack_dispatch_kernel(EpDev e, const float* __restrict__ x,
+                                                               const int32_t* __restrict__ grouped, int K,
+                                                               const int32_t* __restrict__ offsets, int64_t NK,
+                                                               uint32_t epoch) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    const int v_per_row = e.d >> 3;
     for (int64_t i = warp; i < NK; i += nwarps) {
         int r = 0;
         while (r + 1 < e.world && i >= offsets[(r + 1) * e.nl]) ++r;
         const int64_t j = i - offsets[r * e.nl];
         if (j >= e.cap) continue;
-        uint4* dst = reinterpret_cast<uint4*>(e.peers[r] + e.off_rows) + ((int64_t)e.rank * e.cap + j) * v_per_row;
-        const uint4* src = rows + i * v_per_row;
-        for (int v = lane; v < v_per_row; v += 32) dst[v] = src[v];
+        __half* dst = reinterpret_cast<__half*>(e.peers[r] + e.off_rows) + ((int64_t)e.rank * e.cap + j) * e.d;
+        const float* src = x + (int64_t)(grouped[i] / K) * e.d;
+        for (int k = lane * 8; k < e.d; k += 256) {
+            const float4 a = *reinterpret_cast<const float4*>(src + k);
+            const float4 b = *reinterpret_cast<const float4*>(src + k + 4);
+            auto cl = [](float v) { return fminf(fmaxf(v, -65504.0f), 65504.0f); };
+            __half2 h[4] = {__floats2half2_rn(cl(a.x), cl(a.y)), __floats2half2_rn(cl(a.z), cl(a.w)),
+                            __floats2half2_rn(cl(b.x), cl(b.y)), __floats2half2_rn(cl(b.z), cl(b.w))};
+            *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<uint4*>(h);
+        }
     }
     if (blockIdx.x == 0) {
         const int per = e.nl + 2;
@@ -111,7 +122,10 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDev e, const uint4* 
 // 2 gather.  With goff / gmap (dispatch only) the headers become the group list of the
 // expert GEMMs: per sender nl groups (its rows per local expert, in arrival order) and one
 // gap group (mapped to -1) up to the end of the sender's region.
-__global__ void ep_wait_kernel(EpDev e, int which, uint32_t epoch, int32_t* __restrict__ goff, int32_t* __restrict__ gmap) {
+// gc[g]: where group g's result rows go - the sender's y buffer at the position its header
+// named - as a base to which the GEMM adds (row of the receive buffer) * d.
+__global__ void ep_wait_kernel(EpDev e, int which, uint32_t epoch, int32_t* __restrict__ goff, int32_t* __restrict__ gmap,
+                               float** __restrict__ gc) {
     const EpCtrl* c = ctrl_of(e, e.rank);
     const uint32_t* flags = which == 0 ? c->flag_dispatch : which == 1 ? c->flag_return : c->flag_gather;
     if ((int)threadIdx.x < e.world) {
@@ -129,44 +143,57 @@ __global__ void ep_wait_kernel(EpDev e, int which, uint32_t epoch, int32_t* __re
             const int32_t* h = hdr_of(e, e.rank, s);
             int at = s * e.cap;
             const int end = (s + 1) * e.cap;
+            // row (s cap + j) of the receive buffer is row (base + j) of sender s's order
+            float* const home = reinterpret_cast<float*>(e.peers[s] + e.off_y) + ((int64_t)h[e.nl] - (int64_t)s * e.cap) * e.d;
             for (int x = 0; x < e.nl; ++x, ++g) {
                 goff[g] = at;
                 gmap[g] = x;
+                gc[g] = home;
                 at = min(at + max(h[x], 0), end);
             }
             goff[g] = at;
             gmap[g] = -1;
+            gc[g] = home;
             ++g;
         }
         goff[g] = e.world * e.cap;
     }
 }
 
-// y_remote [world * cap, d] fp32 (region s = results of sender s's rows) -> the senders' y
-// buffers at the positions their headers named.  grid (x, world); one warp per row.
-__global__ void __launch_bounds__(256) ep_return_kernel(EpDev e, const uint4* __restrict__ y_remote, uint32_t epoch) {
-    const int s = blockIdx.y, lane = threadIdx.x & 31;
-    const int32_t* h = hdr_of(e, e.rank, s);
-    const int base = h[e.nl], total = min(max(h[e.nl + 1], 0), e.cap);
-    const int v_per_row = e.d >> 2;
-    const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    uint4* dst0 = reinterpret_cast<uint4*>(e.peers[s] + e.off_y);
-    for (int64_t j = warp; j < total; j += nwarps) {
-        const uint4* src = y_remote + ((int64_t)s * e.cap + j) * v_per_row;
-        uint4* dst = dst0 + ((int64_t)base + j) * v_per_row;
-        for (int v = lane; v < v_per_row; v += 32) dst[v] = src[v];
-    }
-    if (grid_last_cta(&ctrl_of(e, e.rank)->done[1]))
+// The down projection stored its result rows straight into the senders' y buffers (per-group
+// output bases); all of that kernel's stores are complete when this one starts, so one
+// thread fences and tells every sender that its results are home.
+__global__ void ep_returned_kernel(EpDev e, uint32_t epoch) {
+    if (threadIdx.x == 0) {
+        __threadfence_system();
         for (int r = 0; r < e.world; ++r) st_release_sys(&ctrl_of(e, r)->flag_return[e.rank], epoch);
+    }
 }
 
-// part [n, d] fp32 (my slice, tokens lo ..) -> every rank's output.  grid (x, world).
-__global__ void __launch_bounds__(256) ep_gather_kernel(EpDev e, const uint4* __restrict__ part, int64_t n, int64_t lo,
-                                                        uint32_t epoch) {
-    const int r = blockIdx.y;
-    const int64_t total = n * (e.d >> 2);
-    uint4* dst = reinterpret_cast<uint4*>(e.peers[r] + e.off_out) + lo * (e.d >> 2);
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) dst[i] = part[i];
+// The combination of my slice stored straight into every rank's output:
+// out[lo + t, :] = (shared ? part[t, :] : 0) + sum_k w[t, k] * y[inv[t K + k], :], k ascending
+// (the arithmetic of the single-GPU layer's combination, separate multiply and add).
+__global__ void __launch_bounds__(256) ep_combine_gather_kernel(EpDev e, const float* __restrict__ y,
+                                                                const int32_t* __restrict__ inv, const float* __restrict__ w,
+                                                                const float* __restrict__ part, int n, int K, int64_t lo,
+                                                                int has_shared, uint32_t epoch) {
+    const int d4 = e.d >> 2;
+    const int64_t total = (int64_t)n * d4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / d4), j = (int)(i - (int64_t)t * d4);
+        float4 acc = has_shared ? *(reinterpret_cast<const float4*>(part + (int64_t)t * e.d) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < K; ++k) {
+            const int slot = t * K + k;
+            const float wk = w[slot];
+            const float4 v = *(reinterpret_cast<const float4*>(y + (int64_t)inv[slot] * e.d) + j);
+            acc.x = __fadd_rn(acc.x, __fmul_rn(wk, v.x));
+            acc.y = __fadd_rn(acc.y, __fmul_rn(wk, v.y));
+            acc.z = __fadd_rn(acc.z, __fmul_rn(wk, v.z));
+            acc.w = __fadd_rn(acc.w, __fmul_rn(wk, v.w));
+        }
+        for (int r = 0; r < e.world; ++r)
+            *(reinterpret_cast<float4*>(e.peers[r] + e.off_out) + (lo + t) * d4 + j) = acc;
+    }
     if (grid_last_cta(&ctrl_of(e, e.rank)->done[2]))
         for (int q = 0; q < e.world; ++q) st_release_sys(&ctrl_of(e, q)->flag_gather[e.rank], epoch);
 }
@@ -186,14 +213,17 @@ struct b200_ep {
     bool connected = false;
     // local buffers
     int32_t *idx = nullptr, *inv = nullptr, *offsets = nullptr, *goff = nullptr, *gmap = nullptr;
-    float *w = nullptr, *y_remote = nullptr, *part = nullptr;
-    uint16_t* rows = nullptr;
+    float *w = nullptr, *part = nullptr;
+    float** gc = nullptr;                        // per GEMM group: where its result rows go (peer memory)
+    void* sh_scratch = nullptr;                  // the shared expert's own scratch: it runs on a second stream
+    int32_t* grouped = nullptr;
     // weights
     const float *router_w = nullptr, *router_bias = nullptr;
     const void *gates = nullptr, *ups = nullptr, *downs = nullptr, *sh_g = nullptr, *sh_u = nullptr, *sh_d = nullptr;
     uint32_t epoch = 0;
     uint32_t spin_limit = EP_SPIN_DEFAULT;
     int T = 0, lo = 0, n = 0;                    // the pass in flight
+    bool shared_pending = false;                 // the shared expert of this pass runs on the second stream
 };
 
 static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -256,12 +286,13 @@ int b200_ep_create(b200_ep** out, int rank, int world, int d, int E, int ne, int
     if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->idx), (size_t)worst * 4);
     if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->w), (size_t)worst * 4);
     if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->inv), (size_t)worst * 4);
-    if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->rows), (size_t)worst * d * 2);
+    if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->grouped), (size_t)worst * 4);
     if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->offsets), (size_t)(ne + 1) * 4);
     if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->goff), (size_t)(world * (ep->nl + 1) + 1) * 4);
     if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->gmap), (size_t)(world * (ep->nl + 1)) * 4);
-    if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->y_remote), (size_t)world * ep->cap * d * 4);
+    if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->gc), (size_t)(world * (ep->nl + 1)) * sizeof(float*));
     if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->part), (size_t)ep->slice_max * d * 4);
+    if (!rc && SH > 0) rc = alloc(&ep->sh_scratch, moe_shared_scratch_bytes(ep->slice_max, d, SH));
     if (rc) return fail_free(rc);
     ep->peer[rank] = ep->block;
     if (world == 1) {
@@ -277,8 +308,8 @@ int b200_ep_destroy(b200_ep* ep) {
     cudaDeviceSynchronize();
     for (int r = 0; r < ep->world; ++r)
         if (ep->opened[r] && ep->peer[r]) cudaIpcCloseMemHandle(ep->peer[r]);
-    for (void* p : {(void*)ep->block, (void*)ep->peers_dev, (void*)ep->idx, (void*)ep->w, (void*)ep->inv, (void*)ep->rows,
-                    (void*)ep->offsets, (void*)ep->goff, (void*)ep->gmap, (void*)ep->y_remote, (void*)ep->part})
+    for (void* p : {(void*)ep->block, (void*)ep->peers_dev, (void*)ep->idx, (void*)ep->w, (void*)ep->inv, (void*)ep->grouped,
+                    (void*)ep->offsets, (void*)ep->goff, (void*)ep->gmap, (void*)ep->gc, (void*)ep->part, ep->sh_scratch})
         if (p) cudaFree(p);
     delete ep;
     return B200_OK;
@@ -386,48 +417,59 @@ int b200_ep_phase(b200_ep* ep, int phase, const float* x, int T) {
         ep->epoch += 1;
         const int n = ep->n;
         const float* xs = x + (int64_t)lo * d;
+        // the shared expert of my own tokens: on the second stream, next to everything up to
+        // the combination (its scratch is the handle's own)
+        ep->shared_pending = false;
+        if (n > 0 && ep->sh_g && ep->sh_u && ep->sh_d && ep->SH > 0) {
+            rc = side_begin();
+            if (rc) return rc;
+            rc = moe_shared_expert(xs, ep->sh_g, ep->sh_u, ep->sh_d, ep->part, n, d, ep->SH, tag_of_qkind(ep->qkind),
+                                   ep->sh_scratch);
+            const int rc2 = side_end();
+            if (rc || rc2) return rc ? rc : rc2;
+            ep->shared_pending = true;
+        }
         if (n > 0) {
             rc = b200_moe_route(xs, ep->router_w, ep->router_bias, nullptr, ep->idx, ep->w, n, d, ep->ne, K);
             if (rc) return rc;
-            rc = b200_moe_dispatch_pack(xs, ep->idx, n, d, ep->ne, K, ep->rows, ep->inv, ep->offsets);
+            rc = moe_dispatch_perm(ep->idx, n, ep->ne, K, ep->grouped, ep->inv, ep->offsets);
             if (rc) return rc;
         } else {
             B200_CUDA(cudaMemsetAsync(ep->offsets, 0, (size_t)(ep->ne + 1) * 4, st));
         }
         const int64_t NK = (int64_t)n * K;
         const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div64(NK, 8), (int64_t)num_sms() * 8));
-        ep_dispatch_kernel<<<grid, 256, 0, st>>>(dev_args(ep), reinterpret_cast<const uint4*>(ep->rows), ep->offsets, NK, ep->epoch);
-        B200_LAUNCH_CHECK("ep_dispatch_kernel");
-        // the shared expert of my own tokens runs while the rows travel
-        return b200_moe_shared_expert(xs, ep->sh_g, ep->sh_u, ep->sh_d, ep->part, n, d, ep->SH, ep->qkind);
+        ep_pack_dispatch_kernel<<<grid, 256, 0, st>>>(dev_args(ep), xs, ep->grouped, K, ep->offsets, NK, ep->epoch);
+        B200_LAUNCH_CHECK("ep_pack_dispatch_kernel");
+        return B200_OK;
     }
     B200_REQUIRE(ep->epoch > 0, "ep_phase: phase %d before phase 0", phase);
     if (phase == 1) {
-        ep_wait_kernel<<<1, 32, 0, st>>>(dev_args(ep), 0, ep->epoch, ep->goff, ep->gmap);
+        ep_wait_kernel<<<1, 32, 0, st>>>(dev_args(ep), 0, ep->epoch, ep->goff, ep->gmap, ep->gc);
         B200_LAUNCH_CHECK("ep_wait_kernel");
         const int groups = G * (ep->nl + 1);
-        rc = b200_moe_experts_rows(reinterpret_cast<const uint16_t*>(ep->block + ep->off_rows), ep->goff, ep->gmap, groups,
-                                   (int64_t)G * ep->cap, ep->gates, ep->ups, ep->downs, ep->nl, ep->y_remote, d, ep->E, ep->qkind);
+        rc = moe_experts_rows(reinterpret_cast<const __half*>(ep->block + ep->off_rows), ep->goff, ep->gmap, groups,
+                              (int64_t)G * ep->cap, ep->gates, ep->ups, ep->downs, ep->nl, nullptr, d, ep->E,
+                              tag_of_qkind(ep->qkind), ep->gc);
         if (rc) return rc;
-        const int gx = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div64(ep->cap, 8), (int64_t)num_sms() * 8 / G + 1));
-        ep_return_kernel<<<dim3(gx, G), 256, 0, st>>>(dev_args(ep), reinterpret_cast<const uint4*>(ep->y_remote), ep->epoch);
-        B200_LAUNCH_CHECK("ep_return_kernel");
+        ep_returned_kernel<<<1, 32, 0, st>>>(dev_args(ep), ep->epoch);
+        B200_LAUNCH_CHECK("ep_returned_kernel");
         return B200_OK;
     }
     if (phase == 2) {
-        ep_wait_kernel<<<1, 32, 0, st>>>(dev_args(ep), 1, ep->epoch, nullptr, nullptr);
+        ep_wait_kernel<<<1, 32, 0, st>>>(dev_args(ep), 1, ep->epoch, nullptr, nullptr, nullptr);
         B200_LAUNCH_CHECK("ep_wait_kernel");
-        const bool shared = ep->sh_g && ep->sh_u && ep->sh_d && ep->SH > 0;
-        rc = b200_moe_combine(reinterpret_cast<const float*>(ep->block + ep->off_y), ep->inv, ep->w, ep->part, ep->n, d, K,
-                              shared ? 1 : 0);
-        if (rc) return rc;
+        const bool shared = ep->shared_pending;
+        if (shared && (rc = side_wait())) return rc;
+        ep->shared_pending = false;
         const int64_t vecs = (int64_t)ep->n * (d >> 2);
-        const int gx = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div64(vecs, 256), (int64_t)num_sms() * 8 / G + 1));
-        ep_gather_kernel<<<dim3(gx, G), 256, 0, st>>>(dev_args(ep), reinterpret_cast<const uint4*>(ep->part), ep->n, ep->lo, ep->epoch);
-        B200_LAUNCH_CHECK("ep_gather_kernel");
+        const int gx = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div64(vecs, 256), (int64_t)num_sms() * 16));
+        ep_combine_gather_kernel<<<gx, 256, 0, st>>>(dev_args(ep), reinterpret_cast<const float*>(ep->block + ep->off_y), ep->inv,
+                                                     ep->w, ep->part, ep->n, K, ep->lo, shared ? 1 : 0, ep->epoch);
+        B200_LAUNCH_CHECK("ep_combine_gather_kernel");
         return B200_OK;
     }
-    ep_wait_kernel<<<1, 32, 0, st>>>(dev_args(ep), 2, ep->epoch, nullptr, nullptr);
+    ep_wait_kernel<<<1, 32, 0, st>>>(dev_args(ep), 2, ep->epoch, nullptr, nullptr, nullptr);
     B200_LAUNCH_CHECK("ep_wait_kernel");
     return B200_OK;
 }

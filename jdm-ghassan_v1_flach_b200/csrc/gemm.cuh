@@ -25,12 +25,25 @@ int pack_rows_f16(const float* src, const int32_t* row_map, int div, __half* dst
 //   GEMM_EPI_SWIGLU  c16[row, n] = silu(A.B^T) * (A.B2^T)           (fp16, ld = ldc)
 int umma_gemm(int epi, const __half* A, int64_t a_rows, const __half* B, const __half* B2, int64_t b_rows,
               const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc, float scale,
-              const int32_t* group_map = nullptr);
+              const int32_t* group_map = nullptr, float* const* group_c = nullptr);
 
 // The same with B (and B2) in packed form, `kind` 0..3, dequantised inside the kernel
 // (values rounded to fp16).  K % 256 == 0.
 int umma_gemm_q(int epi, int kind, const __half* A, int64_t a_rows, const void* B, const void* B2, int64_t b_rows,
                 const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc,
-                float scale, const int32_t* group_map = nullptr);
+                float scale, const int32_t* group_map = nullptr, float* const* group_c = nullptr);
+
+// moe_grouped.cu: the shared expert alone, out [N, d] = shared_expert(x); kind is a template
+// tag; scratch (optional) replaces the library's MoE workspace.
+// The routed experts on packed rows (see b200_moe_experts_rows).  y_groups (optional, device
+// [groups]): where each group's result rows go instead of y, in umma_gemm's group_c
+// convention; y may then be null.
+int moe_experts_rows(const __half* rows16, const int32_t* offsets, const int32_t* group_map, int groups, int64_t R,
+                     const void* gates, const void* ups, const void* downs, int n_local, float* y, int d, int E, int kind,
+                     float* const* y_groups = nullptr);
+int moe_dispatch_perm(const int32_t* idx, int64_t N, int ne, int K, int32_t* grouped, int32_t* inv, int32_t* offsets);
+size_t moe_shared_scratch_bytes(int64_t N, int d, int SH);
+int moe_shared_expert(const float* x, const void* sh_g, const void* sh_u, const void* sh_d, float* out, int64_t N, int d,
+                      int SH, int kind, void* scratch);
 
 }  // namespace b200

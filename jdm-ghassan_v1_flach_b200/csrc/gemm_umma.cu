@@ -64,6 +64,11 @@ struct alignas(64) GemmArgs {
     int tile_n;                         // output columns per tile: 128, or 256 (wide store form)
     int tile_m;                         // rows of A per slot: 128, or 256 = two accumulator halves sharing one B tile
     float* c;                           // STORE: fp32 [M, ldc]
+    // STORE, grouped, optional: device [groups] of bases that replace `c` for a group's rows:
+    // row r of group g is stored at group_c[g] + r * ldc (r counted like the rows of A, so a
+    // caller that wants the group's first row at p passes p - offsets[g] * ldc).  The
+    // targets may be peer memory (plain stores).
+    float* const* group_c;
     __half* c16;                        // SWIGLU: fp16 [M, ldc]  silu(A.B^T) * (A.B2^T)
     int64_t ldc;
     float scale;
@@ -100,7 +105,9 @@ struct GemmTile {
 // (callers then walk the offsets) when there are more groups or slots than the table holds.
 __device__ __noinline__ void gemm_build_slots(const GemmArgs& a, int* tab, int* scan) {
     if (!a.offsets) return;
-    const bool fits = a.groups <= 256 && a.m_slots <= GM_MAX_SLOTS;
+    // (m_slots is the host's upper bound from the row count; lists with gaps between their
+    // groups hold far fewer tiles, so the bound only decides for lists the scan cannot hold)
+    const bool fits = a.groups <= 256;
     if (!fits) {
         if (threadIdx.x == 0) tab[0] = -1;
         return;
@@ -128,9 +135,19 @@ __device__ __noinline__ void gemm_build_slots(const GemmArgs& a, int* tab, int* 
                 base[g0 + i] = run;
                 run += cnt[g0 + i];
             }
-        if (threadIdx.x == 31) tab[0] = min(incl, GM_MAX_SLOTS);
+        // more row tiles than slots: keep the first slot of every group instead (tab[0] = -2,
+        // tab[1 + g] = first slot of group g, tab[1 + groups] = slots in all) and let the roles
+        // find a slot's group by bisection
+        if (threadIdx.x == 31) {
+            tab[0] = incl <= GM_MAX_SLOTS ? incl : -2;
+            base[a.groups] = incl;
+        }
     }
     __syncthreads();
+    if (tab[0] == -2) {
+        for (int g = threadIdx.x; g <= a.groups; g += blockDim.x) tab[1 + g] = base[g];
+        return;
+    }
     for (int g = threadIdx.x; g < a.groups; g += blockDim.x) {
         const int lo = a.offsets[g], hi = a.offsets[g + 1];
         for (int i = 0; i < cnt[g]; ++i) {
@@ -176,6 +193,21 @@ __device__ __forceinline__ bool gemm_tile_at(const GemmArgs& a, const int* tab, 
     } else if (tab[0] >= 0) {
         found = slot < tab[0];
         if (found) { w.group = tab[1 + 3 * slot]; w.row0 = tab[2 + 3 * slot]; w.row_end = tab[3 + 3 * slot]; }
+    } else if (tab[0] == -2) {
+        const int* first = tab + 1;
+        found = slot < first[a.groups];
+        if (found) {
+            int lo = 0, hi = a.groups;               // the last group whose first slot is <= slot
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (first[mid] <= slot) lo = mid; else hi = mid;
+            }
+            // groups without tiles share their first slot with the next one: lo is the last of
+            // such a run, which is the one that owns the slot
+            w.group = lo;
+            w.row0 = a.offsets[lo] + (slot - first[lo]) * a.tile_m;
+            w.row_end = a.offsets[lo + 1];
+        }
     } else {
         const int4 r = gemm_slot_walk(a.offsets, a.group_map, a.groups, a.tile_m, slot);
         found = r.x != 0;
@@ -202,6 +234,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tacc, 
     const int row = w.row0 + q * 32 + lane;
     const int row_end = w.row_end, n0 = w.n0;
     const uint32_t tbase = tacc + ((uint32_t)(q * 32) << 16);
+    float* const cbase = (EPI != GEMM_EPI_SWIGLU && a.group_c) ? a.group_c[w.group] : a.c + w.split * a.split_stride;
 #pragma unroll 1
     for (int c0 = 0; c0 < GemmShape<EPI>::TN; c0 += 32) {
         float v[32];
@@ -255,12 +288,12 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs& a, uint32_t tacc, 
                 const int grow = w.row0 + q * 32 + r;
                 const float* sp = stg + r * GM_EPI_LD + cq;
                 if (grow < row_end)
-                    *reinterpret_cast<float4*>(a.c + w.split * a.split_stride + (int64_t)grow * a.ldc + n0 + c0 + cq) =
+                    *reinterpret_cast<float4*>(cbase + (int64_t)grow * a.ldc + n0 + c0 + cq) =
                         make_float4(sp[0], sp[1], sp[2], sp[3]);
             }
             __syncwarp();
         } else if (row < row_end) {
-            float* dst = a.c + w.split * a.split_stride + (int64_t)row * a.ldc + n0 + c0;
+            float* dst = cbase + (int64_t)row * a.ldc + n0 + c0;
 #pragma unroll
             for (int i = 0; i < 32; ++i)
                 if (n0 + c0 + i < a.N) dst[i] = v[i] * a.scale;
@@ -859,9 +892,10 @@ static int launch_gemm_q(const GemmArgs& a) {
 // As umma_gemm(), with B (and B2) packed in `kind` (0..3), [b_rows, K]; K % 256 == 0.
 int umma_gemm_q(int epi, int kind, const __half* A, int64_t a_rows, const void* B, const void* B2, int64_t b_rows,
                 const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc,
-                float scale, const int32_t* group_map) {
+                float scale, const int32_t* group_map, float* const* group_c) {
     if (M <= 0 || N <= 0) return B200_OK;
     B200_REQUIRE(kind >= 0 && kind <= 3, "umma_gemm_q: unknown kind %d", kind);
+    B200_REQUIRE(!group_c || (offsets && epi == GEMM_EPI_STORE), "umma_gemm_q: per-group outputs need the grouped store form");
     B200_REQUIRE(A && B && K > 0 && K % 256 == 0, "umma_gemm_q: K must be a positive multiple of 256");
     B200_REQUIRE(groups >= 1 && (offsets || groups == 1), "umma_gemm_q: groups need a device offsets array");
     B200_REQUIRE((group_map || b_rows >= (int64_t)groups * N) && a_rows >= M, "umma_gemm_q: operand shapes do not cover the groups");
@@ -878,10 +912,10 @@ int umma_gemm_q(int epi, int kind, const __half* A, int64_t a_rows, const void* 
         rc = make_packed_map(&a.map_b2, B2, b_rows, row_bytes, sbb);
         if (rc) return rc;
     } else {
-        B200_REQUIRE(c, "umma_gemm_q: null output");
+        B200_REQUIRE(c || group_c, "umma_gemm_q: null output");
     }
     a.offsets = offsets; a.group_map = group_map; a.M = M; a.groups = groups; a.N = N; a.K = K;
-    a.c = c; a.c16 = c16; a.ldc = ldc; a.scale = scale;
+    a.c = c; a.c16 = c16; a.ldc = ldc; a.scale = scale; a.group_c = group_c;
     a.status = stream_status_ptr();
     B200_REQUIRE(a.status, "umma_gemm_q: status word allocation failed");
     // wide store tiles when they still fill the machine (row slots are an upper bound when
@@ -931,9 +965,10 @@ static int launch_gemm(const GemmArgs& a) {
 // offsets: device [groups + 1] or null (then groups must be 1 and all M rows form it).
 int umma_gemm(int epi, const __half* A, int64_t a_rows, const __half* B, const __half* B2, int64_t b_rows,
               const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc, float scale,
-              const int32_t* group_map) {
+              const int32_t* group_map, float* const* group_c) {
     if (M <= 0 || N <= 0) return B200_OK;
     B200_REQUIRE(A && B && K > 0 && K % 8 == 0, "umma_gemm: K must be a positive multiple of 8");
+    B200_REQUIRE(!group_c || (offsets && epi == GEMM_EPI_STORE), "umma_gemm: per-group outputs need the grouped store form");
     B200_REQUIRE(groups >= 1 && (offsets || groups == 1), "umma_gemm: groups need a device offsets array");
     B200_REQUIRE((group_map || b_rows >= (int64_t)groups * N) && a_rows >= M, "umma_gemm: operand shapes do not cover the groups");
     GemmArgs a;
@@ -947,10 +982,10 @@ int umma_gemm(int epi, const __half* A, int64_t a_rows, const __half* B, const _
         rc = make_tile_map(&a.map_b2, B2, b_rows, K, GM_TILE_N);
         if (rc) return rc;
     } else {
-        B200_REQUIRE(c, "umma_gemm: null output");
+        B200_REQUIRE(c || group_c, "umma_gemm: null output");
     }
     a.offsets = offsets; a.group_map = group_map; a.M = M; a.groups = groups; a.N = N; a.K = K;
-    a.c = c; a.c16 = c16; a.ldc = ldc; a.scale = scale;
+    a.c = c; a.c16 = c16; a.ldc = ldc; a.scale = scale; a.group_c = group_c;
     a.status = stream_status_ptr();
     B200_REQUIRE(a.status, "umma_gemm: status word allocation failed");
     const int slots128 = (M + GM_TILE_M - 1) / GM_TILE_M + (offsets ? groups / 2 : 0);

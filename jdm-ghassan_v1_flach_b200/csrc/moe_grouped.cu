@@ -171,6 +171,19 @@ static int check_ep_kind(const char* who, int kind, int d, int E) {
     return B200_OK;
 }
 
+// The permutation alone: grouped [N K] (slot numbers sorted by expert, stable), its inverse
+// and the expert offsets [ne + 1].
+int moe_dispatch_perm(const int32_t* idx, int64_t N, int ne, int K, int32_t* grouped, int32_t* inv, int32_t* offsets) {
+    B200_REQUIRE(idx && grouped && inv && offsets, "moe_dispatch_perm: null pointer");
+    const int64_t NK = N * K;
+    if (NK <= 0) return B200_OK;
+    const int rc = moe_permutation(idx, NK, ne, grouped, offsets);
+    if (rc) return rc;
+    perm_inverse_kernel<<<(unsigned)ceil_div64(NK, 256), 256, 0, stream()>>>(grouped, inv, NK);
+    B200_LAUNCH_CHECK("perm_inverse_kernel");
+    return B200_OK;
+}
+
 int moe_dispatch_pack(const float* x, const int32_t* idx, int64_t N, int d, int ne, int K, __half* rows16, int32_t* inv,
                       int32_t* offsets) {
     B200_REQUIRE(x && idx && rows16 && inv && offsets, "moe_dispatch_pack: null pointer");
@@ -189,9 +202,9 @@ int moe_dispatch_pack(const float* x, const int32_t* idx, int64_t N, int d, int 
 
 int moe_experts_rows(const __half* rows16, const int32_t* offsets, const int32_t* group_map, int groups, int64_t R,
                      const void* gates, const void* ups, const void* downs, int n_local, float* y, int d, int E,
-                     int kind) {
+                     int kind, float* const* y_groups) {
     if (R <= 0) return B200_OK;
-    B200_REQUIRE(rows16 && offsets && gates && ups && downs && y && groups >= 1 && n_local >= 1,
+    B200_REQUIRE(rows16 && offsets && gates && ups && downs && (y || y_groups) && groups >= 1 && n_local >= 1,
                  "moe_experts_rows: bad arguments");
     int rc = check_ep_kind("moe_experts_rows", kind, d, E);
     if (rc) return rc;
@@ -204,27 +217,34 @@ int moe_experts_rows(const __half* rows16, const int32_t* offsets, const int32_t
                        (int64_t)n_local * E, offsets, groups, (int)R, E, d, nullptr, act, E, 1.0f, group_map);
         if (rc) return rc;
         return umma_gemm(GEMM_EPI_STORE, act, R, static_cast<const __half*>(downs), nullptr, (int64_t)n_local * d, offsets,
-                         groups, (int)R, d, E, y, nullptr, d, 1.0f, group_map);
+                         groups, (int)R, d, E, y, nullptr, d, 1.0f, group_map, y_groups);
     }
     rc = umma_gemm_q(GEMM_EPI_SWIGLU, kind, rows16, R, gates, ups, (int64_t)n_local * E, offsets, groups, (int)R, E, d,
                      nullptr, act, E, 1.0f, group_map);
     if (rc) return rc;
     return umma_gemm_q(GEMM_EPI_STORE, kind, act, R, downs, nullptr, (int64_t)n_local * d, offsets, groups, (int)R, d, E, y,
-                       nullptr, d, 1.0f, group_map);
+                       nullptr, d, 1.0f, group_map, y_groups);
 }
 
 // out [N, d] = shared_expert(x); false "shared" (a null matrix or SH == 0) leaves out untouched.
+// scratch (optional): moe_shared_scratch_bytes(N, d, SH) bytes of the caller's instead of the
+// library's MoE workspace (callers that run this next to the routed experts' GEMMs).
+size_t moe_shared_scratch_bytes(int64_t N, int d, int SH) {
+    return (((size_t)N * d * 2 + 255) & ~(size_t)255) + (size_t)N * SH * 2 + 256;
+}
 int moe_shared_expert(const float* x, const void* sh_g, const void* sh_u, const void* sh_d, float* out, int64_t N, int d,
-                      int SH, int kind) {
+                      int SH, int kind, void* scratch) {
     if (N <= 0) return B200_OK;
     if (!(sh_g && sh_u && sh_d && SH > 0)) return B200_OK;
     B200_REQUIRE(x && out, "moe_shared_expert: null pointer");
     int rc = check_ep_kind("moe_shared_combine", kind, d, SH);
     if (rc) return rc;
-    void* wsp;
+    void* wsp = scratch;
     const size_t xs_bytes = ((size_t)N * d * 2 + 255) & ~(size_t)255;
-    rc = workspace(WS_MOE).ensure(xs_bytes + (size_t)N * SH * 2 + 256, &wsp);
-    if (rc) return rc;
+    if (!wsp) {
+        rc = workspace(WS_MOE).ensure(moe_shared_scratch_bytes(N, d, SH), &wsp);
+        if (rc) return rc;
+    }
     __half* xs = static_cast<__half*>(wsp);
     __half* sact = reinterpret_cast<__half*>(static_cast<char*>(wsp) + xs_bytes);
     rc = pack_rows_f16(x, nullptr, 1, xs, N, d);
@@ -258,7 +278,7 @@ int moe_shared_combine(const float* x, const void* sh_g, const void* sh_u, const
     if (N <= 0) return B200_OK;
     B200_REQUIRE(x && y && inv && w && out && d % 4 == 0, "moe_shared_combine: bad arguments");
     const bool shared = sh_g && sh_u && sh_d && SH > 0;
-    const int rc = moe_shared_expert(x, sh_g, sh_u, sh_d, out, N, d, SH, kind);
+    const int rc = moe_shared_expert(x, sh_g, sh_u, sh_d, out, N, d, SH, kind, nullptr);
     if (rc) return rc;
     return moe_combine(y, inv, w, out, N, d, K, shared);
 }
@@ -285,12 +305,12 @@ int b200_moe_experts_rows(const uint16_t* rows16, const int32_t* offsets, const 
                           int E, int qkind) {
     B200_REQUIRE(qkind >= -1 && qkind <= 3, "moe_experts_rows: unknown qkind %d", qkind);
     return moe_experts_rows(reinterpret_cast<const __half*>(rows16), offsets, group_map, groups, R, gates, ups, downs,
-                            n_local, y, d, E, tag_of_qkind(qkind));
+                            n_local, y, d, E, tag_of_qkind(qkind), nullptr);
 }
 int b200_moe_shared_expert(const float* x, const void* sh_g, const void* sh_u, const void* sh_d, float* out, int64_t N,
                            int d, int SH, int qkind) {
     B200_REQUIRE(qkind >= -1 && qkind <= 3, "moe_shared_expert: unknown qkind %d", qkind);
-    return moe_shared_expert(x, sh_g, sh_u, sh_d, out, N, d, SH, tag_of_qkind(qkind));
+    return moe_shared_expert(x, sh_g, sh_u, sh_d, out, N, d, SH, tag_of_qkind(qkind), nullptr);
 }
 int b200_moe_combine(const float* y, const int32_t* inv, const float* w, float* out, int64_t N, int d, int K,
                      int accumulate) {
