@@ -41,6 +41,9 @@ struct EpDev {
     size_t off_hdr, off_rows, off_y, off_out;
     int* status;
     uint32_t spin_limit;
+    // number of the pass in flight, in device memory so that a captured pass can be replayed:
+    // every kernel reads it, the pass's last wait advances it
+    uint32_t* epoch;
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -76,8 +79,8 @@ __device__ __forceinline__ int32_t* hdr_of(const EpDev& e, int r, int src) {
 // One warp per row.
 __global__ void __launch_bounds__(256) ep_pack_dispatch_kernel(EpDev e, const float* __restrict__ x,
                                                                const int32_t* __restrict__ grouped, int K,
-                                                               const int32_t* __restrict__ offsets, int64_t NK,
-                                                               uint32_t epoch) {
+                                                               const int32_t* __restrict__ offsets, int64_t NK) {
+    const uint32_t epoch = *e.epoch;
     const int lane = threadIdx.x & 31;
     const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t i = warp; i < NK; i += nwarps) {
@@ -124,8 +127,9 @@ __global__ void __launch_bounds__(256) ep_pack_dispatch_kernel(EpDev e, const fl
 // gap group (mapped to -1) up to the end of the sender's region.
 // gc[g]: where group g's result rows go - the sender's y buffer at the position its header
 // named - as a base to which the GEMM adds (row of the receive buffer) * d.
-__global__ void ep_wait_kernel(EpDev e, int which, uint32_t epoch, int32_t* __restrict__ goff, int32_t* __restrict__ gmap,
+__global__ void ep_wait_kernel(EpDev e, int which, int32_t* __restrict__ goff, int32_t* __restrict__ gmap,
                                float** __restrict__ gc) {
+    const uint32_t epoch = *e.epoch;
     const EpCtrl* c = ctrl_of(e, e.rank);
     const uint32_t* flags = which == 0 ? c->flag_dispatch : which == 1 ? c->flag_return : c->flag_gather;
     if ((int)threadIdx.x < e.world) {
@@ -158,12 +162,14 @@ __global__ void ep_wait_kernel(EpDev e, int which, uint32_t epoch, int32_t* __re
         }
         goff[g] = e.world * e.cap;
     }
+    if (which == 2 && threadIdx.x == 0) *e.epoch = epoch + 1;       // the pass is complete on this rank
 }
 
 // The down projection stored its result rows straight into the senders' y buffers (per-group
 // output bases); all of that kernel's stores are complete when this one starts, so one
 // thread fences and tells every sender that its results are home.
-__global__ void ep_returned_kernel(EpDev e, uint32_t epoch) {
+__global__ void ep_returned_kernel(EpDev e) {
+    const uint32_t epoch = *e.epoch;
     if (threadIdx.x == 0) {
         __threadfence_system();
         for (int r = 0; r < e.world; ++r) st_release_sys(&ctrl_of(e, r)->flag_return[e.rank], epoch);
@@ -176,7 +182,8 @@ __global__ void ep_returned_kernel(EpDev e, uint32_t epoch) {
 __global__ void __launch_bounds__(256) ep_combine_gather_kernel(EpDev e, const float* __restrict__ y,
                                                                 const int32_t* __restrict__ inv, const float* __restrict__ w,
                                                                 const float* __restrict__ part, int n, int K, int64_t lo,
-                                                                int has_shared, uint32_t epoch) {
+                                                                int has_shared) {
+    const uint32_t epoch = *e.epoch;
     const int d4 = e.d >> 2;
     const int64_t total = (int64_t)n * d4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -220,8 +227,15 @@ struct b200_ep {
     // weights
     const float *router_w = nullptr, *router_bias = nullptr;
     const void *gates = nullptr, *ups = nullptr, *downs = nullptr, *sh_g = nullptr, *sh_u = nullptr, *sh_d = nullptr;
-    uint32_t epoch = 0;
+    uint32_t* epoch_dev = nullptr;               // number of the pass in flight (starts at 1)
+    bool begun = false;                          // phase 0 has run at least once
     uint32_t spin_limit = EP_SPIN_DEFAULT;
+    // b200_ep_forward replays a recording of the pass when called again with the same x and T
+    cudaGraphExec_t graph = nullptr;
+    const float* graph_x = nullptr;
+    int graph_T = 0, eager_passes = 0;
+    unsigned long long graph_ws_generation = 0;
+    cudaStream_t own_stream = nullptr;
     int T = 0, lo = 0, n = 0;                    // the pass in flight
     bool shared_pending = false;                 // the shared expert of this pass runs on the second stream
 };
@@ -239,6 +253,7 @@ static EpDev dev_args(const b200_ep* ep) {
     e.off_hdr = ep->off_hdr; e.off_rows = ep->off_rows; e.off_y = ep->off_y; e.off_out = ep->off_out;
     e.status = stream_status_ptr();
     e.spin_limit = ep->spin_limit;
+    e.epoch = ep->epoch_dev;
     return e;
 }
 
@@ -293,6 +308,12 @@ int b200_ep_create(b200_ep** out, int rank, int world, int d, int E, int ne, int
     if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->gc), (size_t)(world * (ep->nl + 1)) * sizeof(float*));
     if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->part), (size_t)ep->slice_max * d * 4);
     if (!rc && SH > 0) rc = alloc(&ep->sh_scratch, moe_shared_scratch_bytes(ep->slice_max, d, SH));
+    if (!rc) rc = alloc(reinterpret_cast<void**>(&ep->epoch_dev), 256);
+    if (!rc) {
+        const uint32_t one = 1;
+        const cudaError_t e = cudaMemcpy(ep->epoch_dev, &one, 4, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) rc = cuda_status(e, "ep_create: pass counter");
+    }
     if (rc) return fail_free(rc);
     ep->peer[rank] = ep->block;
     if (world == 1) {
@@ -306,10 +327,12 @@ int b200_ep_create(b200_ep** out, int rank, int world, int d, int E, int ne, int
 int b200_ep_destroy(b200_ep* ep) {
     if (!ep) return B200_OK;
     cudaDeviceSynchronize();
+    if (ep->graph) cudaGraphExecDestroy(ep->graph);
+    if (ep->own_stream) cudaStreamDestroy(ep->own_stream);
     for (int r = 0; r < ep->world; ++r)
         if (ep->opened[r] && ep->peer[r]) cudaIpcCloseMemHandle(ep->peer[r]);
     for (void* p : {(void*)ep->block, (void*)ep->peers_dev, (void*)ep->idx, (void*)ep->w, (void*)ep->inv, (void*)ep->grouped,
-                    (void*)ep->offsets, (void*)ep->goff, (void*)ep->gmap, (void*)ep->gc, (void*)ep->part, ep->sh_scratch})
+                    (void*)ep->offsets, (void*)ep->goff, (void*)ep->gmap, (void*)ep->gc, (void*)ep->part, ep->sh_scratch, (void*)ep->epoch_dev})
         if (p) cudaFree(p);
     delete ep;
     return B200_OK;
@@ -414,7 +437,7 @@ int b200_ep_phase(b200_ep* ep, int phase, const float* x, int T) {
         int lo, hi;
         slice_of(T, ep->rank, G, &lo, &hi);
         ep->T = T; ep->lo = lo; ep->n = hi - lo;
-        ep->epoch += 1;
+        ep->begun = true;
         const int n = ep->n;
         const float* xs = x + (int64_t)lo * d;
         // the shared expert of my own tokens: on the second stream, next to everything up to
@@ -439,25 +462,25 @@ int b200_ep_phase(b200_ep* ep, int phase, const float* x, int T) {
         }
         const int64_t NK = (int64_t)n * K;
         const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div64(NK, 8), (int64_t)num_sms() * 8));
-        ep_pack_dispatch_kernel<<<grid, 256, 0, st>>>(dev_args(ep), xs, ep->grouped, K, ep->offsets, NK, ep->epoch);
+        ep_pack_dispatch_kernel<<<grid, 256, 0, st>>>(dev_args(ep), xs, ep->grouped, K, ep->offsets, NK);
         B200_LAUNCH_CHECK("ep_pack_dispatch_kernel");
         return B200_OK;
     }
-    B200_REQUIRE(ep->epoch > 0, "ep_phase: phase %d before phase 0", phase);
+    B200_REQUIRE(ep->begun, "ep_phase: phase %d before phase 0", phase);
     if (phase == 1) {
-        ep_wait_kernel<<<1, 32, 0, st>>>(dev_args(ep), 0, ep->epoch, ep->goff, ep->gmap, ep->gc);
+        ep_wait_kernel<<<1, 32, 0, st>>>(dev_args(ep), 0, ep->goff, ep->gmap, ep->gc);
         B200_LAUNCH_CHECK("ep_wait_kernel");
         const int groups = G * (ep->nl + 1);
         rc = moe_experts_rows(reinterpret_cast<const __half*>(ep->block + ep->off_rows), ep->goff, ep->gmap, groups,
                               (int64_t)G * ep->cap, ep->gates, ep->ups, ep->downs, ep->nl, nullptr, d, ep->E,
                               tag_of_qkind(ep->qkind), ep->gc);
         if (rc) return rc;
-        ep_returned_kernel<<<1, 32, 0, st>>>(dev_args(ep), ep->epoch);
+        ep_returned_kernel<<<1, 32, 0, st>>>(dev_args(ep));
         B200_LAUNCH_CHECK("ep_returned_kernel");
         return B200_OK;
     }
     if (phase == 2) {
-        ep_wait_kernel<<<1, 32, 0, st>>>(dev_args(ep), 1, ep->epoch, nullptr, nullptr, nullptr);
+        ep_wait_kernel<<<1, 32, 0, st>>>(dev_args(ep), 1, nullptr, nullptr, nullptr);
         B200_LAUNCH_CHECK("ep_wait_kernel");
         const bool shared = ep->shared_pending;
         if (shared && (rc = side_wait())) return rc;
@@ -465,20 +488,69 @@ int b200_ep_phase(b200_ep* ep, int phase, const float* x, int T) {
         const int64_t vecs = (int64_t)ep->n * (d >> 2);
         const int gx = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div64(vecs, 256), (int64_t)num_sms() * 16));
         ep_combine_gather_kernel<<<gx, 256, 0, st>>>(dev_args(ep), reinterpret_cast<const float*>(ep->block + ep->off_y), ep->inv,
-                                                     ep->w, ep->part, ep->n, K, ep->lo, shared ? 1 : 0, ep->epoch);
+                                                     ep->w, ep->part, ep->n, K, ep->lo, shared ? 1 : 0);
         B200_LAUNCH_CHECK("ep_combine_gather_kernel");
         return B200_OK;
     }
-    ep_wait_kernel<<<1, 32, 0, st>>>(dev_args(ep), 2, ep->epoch, nullptr, nullptr, nullptr);
+    ep_wait_kernel<<<1, 32, 0, st>>>(dev_args(ep), 2, nullptr, nullptr, nullptr);
     B200_LAUNCH_CHECK("ep_wait_kernel");
     return B200_OK;
 }
 
-int b200_ep_forward(b200_ep* ep, const float* x, int T) {
+static int forward_eager(b200_ep* ep, const float* x, int T) {
     for (int phase = 0; phase < 4; ++phase) {
         const int rc = b200_ep_phase(ep, phase, x, T);
         if (rc) return rc;
     }
+    return B200_OK;
+}
+
+// The first two passes with a given (x, T) run eagerly (they size the library's workspaces);
+// the third is recorded into a CUDA graph - the pass reads nothing on the host, its number
+// lives in device memory - and later ones replay it as one launch.  A recording is dropped
+// when one of the library's workspaces has moved since.
+int b200_ep_forward(b200_ep* ep, const float* x, int T) {
+    B200_REQUIRE(ep && ep->connected, "ep_forward: not connected");
+    if (ep->graph && (ep->graph_x != x || ep->graph_T != T || ep->graph_ws_generation != workspace_generation())) {
+        cudaGraphExecDestroy(ep->graph);
+        ep->graph = nullptr;
+        ep->eager_passes = 0;
+    }
+    if (!ep->graph) {
+        if (ep->graph_x != x || ep->graph_T != T) {
+            ep->graph_x = x;
+            ep->graph_T = T;
+            ep->eager_passes = 0;
+        }
+        if (ep->eager_passes < 2) {
+            ep->eager_passes += 1;
+            return forward_eager(ep, x, T);
+        }
+        if (!ep->own_stream) B200_CUDA(cudaStreamCreateWithFlags(&ep->own_stream, cudaStreamNonBlocking));
+        cudaStream_t prev = stream();
+        // the recording starts after everything enqueued so far
+        cudaEvent_t ev;
+        B200_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        cudaEventRecord(ev, prev);
+        cudaStreamWaitEvent(ep->own_stream, ev, 0);
+        cudaEventDestroy(ev);
+        b200_set_stream(ep->own_stream);
+        cudaGraph_t g = nullptr;
+        int rc = B200_OK;
+        cudaError_t e = cudaStreamBeginCapture(ep->own_stream, cudaStreamCaptureModeThreadLocal);
+        if (e == cudaSuccess) {
+            rc = forward_eager(ep, x, T);
+            e = cudaStreamEndCapture(ep->own_stream, &g);
+        }
+        b200_set_stream(prev);
+        if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+        if (e != cudaSuccess) return cuda_status(e, "ep_forward: stream capture");
+        e = cudaGraphInstantiate(&ep->graph, g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) return cuda_status(e, "ep_forward: cudaGraphInstantiate");
+        ep->graph_ws_generation = workspace_generation();
+    }
+    B200_CUDA(cudaGraphLaunch(ep->graph, stream()));
     return B200_OK;
 }
 
