@@ -43,6 +43,22 @@ uint64_t b200_kernel_launches(void);
  * device, reads the word back, clears it, and returns B200_OK or B200_ECUDA.  (The
  * reference has no such waits; b200_synchronize and b200_decoder_step_host check too.) */
 int b200_stream_status(void);
+/* Self-test of that mechanism: one kernel waits (at most spin_limit tries) on a barrier nobody
+ * arrives on, gives up, raises the status word and returns; outcome_dev (device int) becomes 2
+ * (1 would mean the wait was satisfied).  Enqueues only: read the word with b200_stream_status. */
+int b200_test_bounded_wait(int spin_limit, int* outcome_dev);
+
+/* ---- phase timers: cuda_ops.h:315-319 (phase_start / _stop / _reset / _shutdown / _report).
+ * Event pairs recorded on the library's stream, never blocking the host; a start while a
+ * phase is open closes that one first.  b200_phase_report adds, per phase id 0 .. n_phases-1
+ * (n_phases <= 8), the milliseconds of the intervals that have completed since the last
+ * report (intervals still running are kept for the next one).  The same ids also open and
+ * close NVTX ranges ("b200.phase<id>") for timeline tools. */
+int b200_phase_start(int phase);
+int b200_phase_stop(int phase);
+int b200_phase_reset(void);
+int b200_phase_shutdown(void);
+int b200_phase_report(double* ms_per_phase, int n_phases);
 
 /* ---- device utilities: gai::cuda::*, cuda/cuda_utils.h:14-33 ------------------ */
 int b200_device_count(int* count);                       /* probe(), :14 */

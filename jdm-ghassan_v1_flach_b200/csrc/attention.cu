@@ -10,6 +10,8 @@
 // caller's `scratch` argument is accepted and unused.
 #include <algorithm>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -207,18 +209,28 @@ attn_decode_merge_kernel(const float* __restrict__ part, float* __restrict__ out
 }
 
 template <bool HALF, bool PAGED>
-static int launch_decode(DecodeArgs& a, int batch, int max_len, float* out) {
+// fixed_part / fixed_floats (optional): the split-KV partials go to this caller-supplied
+// array instead of the growing workspace, and the number of splits is capped to what it
+// holds (every (head, split) record the merge kernel reads is written by the split kernel
+// first, so the array needs no clearing between calls).
+static int launch_decode(DecodeArgs& a, int batch, int max_len, float* out, float* fixed_part = nullptr,
+                         int64_t fixed_floats = 0) {
     const int epl = a.hd / 32;
     const int gblocks = ceil_div(a.group, ATT_GMAX);
     // enough blocks to fill the machine, at least 32 positions per block
-    const int want = std::max(1, (4 * num_sms()) / std::max(1, a.KV * gblocks * batch));
+    int want = std::max(1, (4 * num_sms()) / std::max(1, a.KV * gblocks * batch));
+    if (fixed_part) want = std::min<int64_t>(want, fixed_floats / ((int64_t)batch * a.H * (a.hd + 2)));
     a.splits = std::max(1, std::min(want, ceil_div(std::max(max_len, 1), 32)));
     a.chunk = std::max(1, ceil_div(std::max(max_len, 1), a.splits));
     a.splits = std::max(1, ceil_div(std::max(max_len, 1), a.chunk));
-    void* wsp;
-    int rc = workspace(WS_ATTN).ensure((size_t)batch * a.H * a.splits * (a.hd + 2) * sizeof(float) + 256, &wsp);
-    if (rc) return rc;
-    a.part = static_cast<float*>(wsp);
+    if (fixed_part) {
+        a.part = fixed_part;
+    } else {
+        void* wsp;
+        int rc = workspace(WS_ATTN).ensure((size_t)batch * a.H * a.splits * (a.hd + 2) * sizeof(float) + 256, &wsp);
+        if (rc) return rc;
+        a.part = static_cast<float*>(wsp);
+    }
     const dim3 grid(a.splits, a.KV * gblocks, batch);
     switch (epl) {
         case 1: attn_decode_split_kernel<1, HALF, PAGED><<<grid, ATT_WARPS * 32, 0, stream()>>>(a); break;
@@ -240,7 +252,7 @@ static int check_hd(const char* who, int hd) {
 
 static int decode_ring(const char* who, const float* q, const void* kc, const void* vc, bool half, float* out,
                        int H, int KV, int hd, int ring_start, int pinned, int cur_len, int cache_max,
-                       float scale, int window) {
+                       float scale, int window, float* fixed_part = nullptr, int64_t fixed_floats = 0) {
     // the reference's argument checks (core/attn_cpu.cpp:162-174)
     B200_REQUIRE(H > 0 && KV > 0 && hd > 0, "%s: empty shape", who);
     B200_REQUIRE(H % KV == 0, "%s: H must be a multiple of KV", who);
@@ -262,7 +274,8 @@ static int decode_ring(const char* who, const float* q, const void* kc, const vo
     a.ring_start = ring_start; a.pinned = pinned; a.ring_cap = ring_cap > 0 ? ring_cap : 1;
     a.scale = scale;
     const int span = cur_len - a.j0;
-    return half ? launch_decode<true, false>(a, 1, span, out) : launch_decode<false, false>(a, 1, span, out);
+    return half ? launch_decode<true, false>(a, 1, span, out, fixed_part, fixed_floats)
+                : launch_decode<false, false>(a, 1, span, out, fixed_part, fixed_floats);
 }
 
 // ---------------------------------------------------------------------------
@@ -439,11 +452,14 @@ int b200_attention_forward_ex(const float* q, const float* k, const float* v, fl
 // the device address is looked up once per device with cudaGetSymbolAddress and that
 // pointer is what the kernels receive.
 // ---------------------------------------------------------------------------
+// The cached address does not survive a device reset (cudaDeviceReset) or a re-created
+// context: a process that resets a device must not call this entry point afterwards.
 namespace b200 {
 constexpr int NOALLOC_FLOATS = 256 * 1024;
 constexpr int NOALLOC_MAX_DEVICES = 64;
 static __device__ __align__(256) float g_noalloc_partials[NOALLOC_FLOATS];
 static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES];   // device address of the array, per device
+static std::once_flag g_noalloc_once[NOALLOC_MAX_DEVICES];
 }  // namespace b200
 
 extern "C" int b200_attention_decode_ring_fp16_noalloc(const float* q, const uint16_t* kc, const uint16_t* vc,
@@ -451,63 +467,25 @@ extern "C" int b200_attention_decode_ring_fp16_noalloc(const float* q, const uin
                                                        int pinned_prefix, int cur_len, int cache_max,
                                                        float scale, int window) {
     const char* who = "attention_decode_ring_fp16_noalloc";
-    // same argument checks as the allocating entry point
-    B200_REQUIRE(H > 0 && KV > 0 && hd > 0, "%s: empty shape", who);
-    B200_REQUIRE(H % KV == 0, "%s: H must be a multiple of KV", who);
-    B200_REQUIRE(cur_len >= 0 && cache_max >= 0 && cur_len <= cache_max, "%s: length exceeds cache capacity", who);
-    B200_REQUIRE(pinned_prefix >= 0 && pinned_prefix <= cur_len, "%s: pinned prefix out of range", who);
-    const int ring_cap = cache_max - pinned_prefix;
-    if (cur_len > pinned_prefix) {
-        B200_REQUIRE(ring_cap > 0, "%s: ring has no rolling slots", who);
-        B200_REQUIRE(ring_start >= 0 && ring_start < ring_cap, "%s: ring start out of range", who);
-    }
-    B200_REQUIRE(q && kc && vc && out, "%s: null pointer", who);
-    int rc = check_hd(who, hd);
-    if (rc) return rc;
     // The fixed scratch bounds the problem: at least one split of (hd + 2) floats per head.
-    B200_REQUIRE((int64_t)H * (hd + 2) <= NOALLOC_FLOATS,
+    B200_REQUIRE(H > 0 && hd > 0 && (int64_t)H * (hd + 2) <= NOALLOC_FLOATS,
                  "%s: H * (head_dim + 2) = %lld floats exceeds the built-in scratch of %d floats; use "
                  "attention_decode_ring_fp16 for this shape", who, (long long)H * (hd + 2), NOALLOC_FLOATS);
-
     // One-time set-up per device, with that device current: resolve the array's device
-    // address.  This first call should happen outside any stream capture.
+    // address (first callers of a device race to here; exactly one of them looks it up).
+    // This first call should happen outside any stream capture.
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     B200_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, "%s: device index %d not supported", who, dev);
-    if (!g_noalloc_ptr[dev]) {
+    cudaError_t lookup = cudaSuccess;
+    std::call_once(g_noalloc_once[dev], [&] {
         float* p = nullptr;
-        B200_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_partials));
-        g_noalloc_ptr[dev] = p;
-    }
-
-    DecodeArgs a{};
-    a.q = q; a.kc = kc; a.vc = vc;
-    a.H = H; a.KV = KV; a.hd = hd; a.group = H / KV;
-    a.cur_len = cur_len;
-    a.j0 = (window > 0 && cur_len > window) ? cur_len - window : 0;
-    a.ring_start = ring_start; a.pinned = pinned_prefix; a.ring_cap = ring_cap > 0 ? ring_cap : 1;
-    a.scale = scale;
-    const int span = std::max(cur_len - a.j0, 1);
-    // Splits as in the allocating path, then capped to what the array holds.  Every
-    // (head, split) record the merge kernel reads is written by the split kernel first,
-    // so nothing in the array needs clearing between calls.
-    const int gblocks = ceil_div(a.group, ATT_GMAX);
-    const int want = std::max(1, (4 * num_sms()) / std::max(1, a.KV * gblocks));
-    const int cap = (int)(NOALLOC_FLOATS / ((int64_t)H * (hd + 2)));
-    a.splits = std::max(1, std::min(std::min(want, cap), ceil_div(span, 32)));
-    a.chunk = std::max(1, ceil_div(span, a.splits));
-    a.splits = std::max(1, ceil_div(span, a.chunk));
-    a.part = g_noalloc_ptr[dev];
-    const dim3 grid(a.splits, a.KV * gblocks, 1);
-    switch (hd / 32) {
-        case 1: attn_decode_split_kernel<1, true, false><<<grid, ATT_WARPS * 32, 0, stream()>>>(a); break;
-        case 2: attn_decode_split_kernel<2, true, false><<<grid, ATT_WARPS * 32, 0, stream()>>>(a); break;
-        case 4: attn_decode_split_kernel<4, true, false><<<grid, ATT_WARPS * 32, 0, stream()>>>(a); break;
-        default: attn_decode_split_kernel<8, true, false><<<grid, ATT_WARPS * 32, 0, stream()>>>(a); break;
-    }
-    B200_LAUNCH_CHECK("attn_decode_split_kernel");
-    const int merge_groups = std::max(1, std::min(std::min(MERGE_MAX_THREADS / a.hd, 16), a.splits));
-    attn_decode_merge_kernel<<<dim3(a.H, 1), a.hd * merge_groups, 0, stream()>>>(a.part, out, a.H, a.hd, a.splits);
-    B200_LAUNCH_CHECK("attn_decode_merge_kernel");
-    return B200_OK;
+        lookup = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_partials);
+        g_noalloc_ptr[dev] = lookup == cudaSuccess ? p : nullptr;
+    });
+    if (lookup != cudaSuccess) return cuda_status(lookup, "attention_decode_ring_fp16_noalloc: cudaGetSymbolAddress");
+    B200_REQUIRE(g_noalloc_ptr[dev], "%s: the built-in scratch could not be located on device %d", who, dev);
+    // argument checks, split sizing and dispatch are the allocating entry point's
+    return decode_ring(who, q, kc, vc, true, out, H, KV, hd, ring_start, pinned_prefix, cur_len, cache_max, scale, window,
+                       g_noalloc_ptr[dev], NOALLOC_FLOATS);
 }

@@ -56,6 +56,15 @@ static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b;
 int num_sms();
 // Second stream for work independent of the current stream's (see runtime.cu): between
 // side_begin() and side_end() stream() is the side stream; side_wait() joins.
+// Named ranges for timeline tools (NVTX; a no-op without a tool attached).
+void nvtx_push(const char* name);
+void nvtx_pop();
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtx_push(name); }
+    ~NvtxRange() { nvtx_pop(); }
+    NvtxRange(const NvtxRange&) = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
+};
 int side_begin();
 int side_end();
 int side_wait();

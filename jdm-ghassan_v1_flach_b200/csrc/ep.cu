@@ -429,6 +429,9 @@ int b200_ep_phase(b200_ep* ep, int phase, const float* x, int T) {
     B200_REQUIRE(ep && ep->connected, "ep_phase: not connected");
     B200_REQUIRE(ep->gates, "ep_phase: no weights set");
     B200_REQUIRE(phase >= 0 && phase <= 3, "ep_phase: phase %d", phase);
+    static const char* const names[4] = {"b200.ep.route+dispatch", "b200.ep.experts+return", "b200.ep.combine+gather",
+                                         "b200.ep.wait_slices"};
+    NvtxRange range(names[phase]);
     cudaStream_t st = stream();
     const int d = ep->d, K = ep->K, G = ep->world;
     int rc;

@@ -235,6 +235,32 @@ static inline int flat_grid(int64_t n) {
 
 using namespace b200;
 
+// ---------------------------------------------------------------------------
+// Self-test of the bounded wait every TMA-fed kernel of the library uses (mbar_wait):
+// a barrier that expects one arrival and never gets it.  The wait gives up after
+// `spin_limit` tries, raises the status word and the kernel returns normally.
+// ---------------------------------------------------------------------------
+namespace b200 {
+__global__ void bounded_wait_probe_kernel(int* status, uint32_t limit, int* outcome) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *outcome = mbar_wait_limit(&bar, 0, status, limit) ? 1 : 2;
+}
+}  // namespace b200
+
+extern "C" int b200_test_bounded_wait(int spin_limit, int* outcome_dev) {
+    B200_REQUIRE(spin_limit >= 1 && spin_limit <= (1 << 20) && outcome_dev, "test_bounded_wait: bad arguments");
+    int* status = stream_status_ptr();
+    B200_REQUIRE(status, "test_bounded_wait: no status word");
+    bounded_wait_probe_kernel<<<1, 32, 0, stream()>>>(status, (uint32_t)spin_limit, outcome_dev);
+    B200_LAUNCH_CHECK("bounded_wait_probe_kernel");
+    return B200_OK;
+}
+
 extern "C" {
 
 int b200_linear_forward(const float* x, const float* w, float* y, int M, int K, int N) {

@@ -5,6 +5,10 @@
 #include <mutex>
 #include <string>
 
+#include <nvtx3/nvToolsExt.h>
+
+#include <vector>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -103,11 +107,91 @@ int side_wait() {
     return B200_OK;
 }
 
+// ---- phase timers ------------------------------------------------------------------
+// Intervals are (start event, stop event, phase id); events come from a free list and go
+// back to it when a report has read them.
+struct PhaseInterval { cudaEvent_t s, e; int ph; bool open; };
+static std::vector<PhaseInterval> g_intervals;
+static std::vector<cudaEvent_t> g_free_events;
+static int phase_event(cudaEvent_t* ev) {
+    if (!g_free_events.empty()) {
+        *ev = g_free_events.back();
+        g_free_events.pop_back();
+        return B200_OK;
+    }
+    B200_CUDA(cudaEventCreate(ev));
+    return B200_OK;
+}
+static int phase_close_open() {
+    if (!g_intervals.empty() && g_intervals.back().open) {
+        B200_CUDA(cudaEventRecord(g_intervals.back().e, g_stream));
+        g_intervals.back().open = false;
+        nvtxRangePop();
+    }
+    return B200_OK;
+}
+
+void nvtx_push(const char* name) { nvtxRangePushA(name); }
+void nvtx_pop() { nvtxRangePop(); }
+
 }  // namespace b200
 
 using namespace b200;
 
 extern "C" {
+
+int b200_phase_start(int phase) {
+    B200_REQUIRE(phase >= 0 && phase < 8, "phase_start: phase id %d outside 0 .. 7", phase);
+    int rc = phase_close_open();
+    if (rc) return rc;
+    PhaseInterval it{nullptr, nullptr, phase, true};
+    if ((rc = phase_event(&it.s)) || (rc = phase_event(&it.e))) return rc;
+    B200_CUDA(cudaEventRecord(it.s, g_stream));
+    g_intervals.push_back(it);
+    char name[32];
+    snprintf(name, sizeof(name), "b200.phase%d", phase);
+    nvtxRangePushA(name);
+    return B200_OK;
+}
+int b200_phase_stop(int) { return phase_close_open(); }
+int b200_phase_reset(void) {
+    if (!g_intervals.empty() && g_intervals.back().open) nvtxRangePop();
+    for (PhaseInterval& it : g_intervals) {
+        g_free_events.push_back(it.s);
+        g_free_events.push_back(it.e);
+    }
+    g_intervals.clear();
+    return B200_OK;
+}
+int b200_phase_shutdown(void) {
+    b200_phase_reset();
+    for (cudaEvent_t ev : g_free_events) cudaEventDestroy(ev);
+    g_free_events.clear();
+    return B200_OK;
+}
+int b200_phase_report(double* ms, int n_phases) {
+    B200_REQUIRE(ms && n_phases >= 1 && n_phases <= 8, "phase_report: bad arguments");
+    std::vector<PhaseInterval> keep;
+    for (PhaseInterval& it : g_intervals) {
+        bool done = false;
+        if (!it.open && cudaEventQuery(it.e) == cudaSuccess) {
+            float d = 0.0f;
+            if (cudaEventElapsedTime(&d, it.s, it.e) == cudaSuccess) {
+                if (it.ph < n_phases) ms[it.ph] += (double)d;
+                done = true;
+            }
+        }
+        cudaGetLastError();      // a query of a running event is not an error of ours
+        if (done) {
+            g_free_events.push_back(it.s);
+            g_free_events.push_back(it.e);
+        } else {
+            keep.push_back(it);
+        }
+    }
+    g_intervals.swap(keep);
+    return B200_OK;
+}
 
 const char* b200_last_error(void) { return g_err; }
 int b200_version(void) { return 100; }

@@ -467,6 +467,7 @@ constexpr int SCORE_ROWS = 512;
 // back as lay describes; T is then ignored.
 static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* next, int b0, int B,
                    const int32_t* score_targets = nullptr, double* score_acc = nullptr, const SeqLayout* lay = nullptr) {
+    NvtxRange range(score_targets ? "b200.score_tokens" : lay ? "b200.prefill_ragged" : "b200.prefill");
     const int d = dec->d;
     float *dx = dec->x + (int64_t)b0 * d, *dxb = dec->xb + (int64_t)b0 * d, *dlogits = dec->logits + (int64_t)b0 * dec->vocab;
     const int32_t* page_table = dec->page_table + (int64_t)b0 * dec->max_pages;
@@ -528,6 +529,7 @@ static int prefill(b200_decoder* dec, const int32_t* tokens, int T, int32_t* nex
     }
     for (int l = 0; l < dec->n_layers; ++l) {
         LayerW& w = dec->L[l];
+        NvtxRange layer_range(dec->types[l] == 0 ? "b200.prefill.mamba+moe" : "b200.prefill.attention+moe");
         if (dec->types[l] == 0) {
             STEP(mamba2_forward(xb, w.mamba_in, w.conv_w, w.conv_b, w.dt_bias, w.a_log, w.D, w.mamba_norm, w.mamba_out,
                                 w.ssm_state + (int64_t)b0 * dec->d_inner * dec->mds, y, B, T, p, kind,
@@ -762,6 +764,7 @@ static int enqueue_step_persistent(b200_decoder* dec, const int32_t* tokens, int
 }
 
 static int enqueue(b200_decoder* dec, const int32_t* tokens, int32_t* next) {
+    NvtxRange range(dec->fused == 2 ? "b200.step.persistent" : dec->fused ? "b200.step.fused" : "b200.step.per_op");
     if (dec->fused == 2) return enqueue_step_persistent(dec, tokens, next);
     if (dec->fused && dec->batch <= 8) return enqueue_step_fused(dec, tokens, next);
     return enqueue_step(dec, tokens, next);

@@ -48,11 +48,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait (each try_wait already sleeps for a hardware-defined interval).
 constexpr uint32_t MBAR_SPIN_LIMIT = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
-    for (uint32_t it = 0; it < MBAR_SPIN_LIMIT; ++it)
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, int* status, uint32_t limit) {
+    for (uint32_t it = 0; it < limit; ++it)
         if (mbar_try_wait(bar, parity)) return true;
     atomicExch(status, 1);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
+    return mbar_wait_limit(bar, parity, status, MBAR_SPIN_LIMIT);
 }
 // Contiguous global -> shared copy through the TMA unit; src, dst 16-byte aligned,
 // bytes a multiple of 16.  Completion is counted on `bar` (no multicast).

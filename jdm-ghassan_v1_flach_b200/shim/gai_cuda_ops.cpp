@@ -13,6 +13,7 @@
 #include "cuda/cuda_utils.h"
 #include "core/device.h"
 
+#include <cstdio>
 #include <string>
 
 #include "b200ops.h"
@@ -264,13 +265,20 @@ void moe_reserve_workspace(size_t bytes) { ck(b200_moe_reserve_workspace(bytes),
 size_t pool_bytes() { return b200_pool_bytes(); }
 size_t moe_pool_bytes() { return b200_moe_pool_bytes(); }
 
-// Phase timers (cuda/cuda_utils.cu:200-288) attribute training-step time; the
-// inference backend accepts the calls and reports nothing.
-void phase_start(int) {}
-void phase_stop(int) {}
-void phase_reset() {}
-void phase_shutdown() {}
-std::string phase_report() { return std::string(); }
+// Phase timers (cuda/cuda_utils.cu:200-288): event pairs on the library's stream.
+void phase_start(int ph) { ck(b200_phase_start(ph), "phase_start"); }
+void phase_stop(int ph) { ck(b200_phase_stop(ph), "phase_stop"); }
+void phase_reset() { ck(b200_phase_reset(), "phase_reset"); }
+void phase_shutdown() { ck(b200_phase_shutdown(), "phase_shutdown"); }
+std::string phase_report() {
+    // the reference's line: totals per TrainPhase since the last report (cuda/cuda_utils.cu:261-296)
+    double ms[5] = {};
+    ck(b200_phase_report(ms, 5), "phase_report");
+    char buf[256];
+    std::snprintf(buf, sizeof(buf), "ph [attnF %.1f moeF %.1f attnB %.1f moeB %.1f load %.1f]", ms[0], ms[1], ms[2], ms[3],
+                  ms[4]);
+    return std::string(buf);
+}
 
 // ---- training-only entry points: link, fail loudly --------------------------
 void moe_backward_half(const float*, const float*, const u16*, const u16*, const u16*, const u16*, const u16*,

@@ -125,3 +125,55 @@ def test_topk_and_penalties(oracle):
     dl = dev(logits)
     ops.apply_rep_penalties(dl, V, dev(hist), hist.size, 1.12, 0.05, 0.3)
     np.testing.assert_allclose(host(dl), oracle.rep_penalties(logits, hist, 1.12, 0.05, 0.3), rtol=1e-6, atol=1e-6)
+
+
+def test_bounded_wait_runs_out_and_the_library_recovers(oracle):
+    """The wait every TMA-fed kernel uses, on a barrier nobody arrives on: it gives up after its
+    limit, the kernel returns, b200_stream_status reports the raised word once (B200_ECUDA), and
+    the next call runs clean."""
+    import torch
+    from gpu_util import dev, empty, host, pkg
+    lib = pkg.lib()
+    assert lib.raw("b200_stream_status") == 0
+    outcome = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib.b200_test_bounded_wait(500, outcome)
+    assert lib.raw("b200_stream_status") != 0          # the word was raised
+    assert "bounded" in lib.last_error().lower() or "wait" in lib.last_error().lower()
+    assert int(host(outcome)[0]) == 2                  # the wait returned false, the kernel completed
+    assert lib.raw("b200_stream_status") == 0          # read once, cleared
+    x = np.random.default_rng(0).standard_normal(1000).astype(np.float32)
+    out = empty(1000)
+    lib.b200_scale_inplace(dev(x), 2.0, 1000)          # the context is intact
+    w = oracle.quantize(np.random.default_rng(1).standard_normal(64 * 256).astype(np.float32) * 0.02, 3)
+    y = empty((1, 64))
+    xs = np.random.default_rng(2).standard_normal((1, 256)).astype(np.float32)
+    lib.b200_linear_forward_q4(dev(xs), dev(w), y, 1, 256, 64, 3)   # a TMA-fed kernel with the same wait
+    np.testing.assert_allclose(host(y), oracle.linear(xs, w, 3, 1, 256, 64), rtol=2e-4, atol=2e-5)
+    assert lib.raw("b200_stream_status") == 0
+
+
+def test_phase_timers():
+    """cuda_ops.h:315-319: intervals on the stream, reported per phase once complete."""
+    import ctypes as C
+    import torch
+    from gpu_util import pkg
+    lib = pkg.lib()
+    lib.b200_phase_reset()
+    x = torch.zeros(1 << 24, device="cuda")
+    lib.b200_phase_start(1)
+    for _ in range(20):
+        lib.b200_scale_inplace(x, 1.0, x.numel())
+    lib.b200_phase_start(0)                    # closes phase 1, opens phase 0
+    lib.b200_scale_inplace(x, 1.0, x.numel())
+    lib.b200_phase_stop(0)
+    lib.b200_phase_start(4)                    # left open: not reported yet
+    torch.cuda.synchronize()
+    ms = (C.c_double * 5)()
+    lib.b200_phase_report(ms, 5)
+    assert ms[1] > ms[0] > 0.0 and ms[2] == ms[3] == ms[4] == 0.0
+    lib.b200_phase_stop(4)
+    torch.cuda.synchronize()
+    again = (C.c_double * 5)()
+    lib.b200_phase_report(again, 5)
+    assert again[0] == again[1] == 0.0 and again[4] > 0.0      # reported intervals are not counted twice
+    lib.b200_phase_shutdown()

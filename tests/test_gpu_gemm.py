@@ -68,6 +68,32 @@ def test_linear_packed_many_tokens(oracle, kind, M, K, N):
     np.testing.assert_allclose(got[rows], want, **FP16_OPERANDS)
 
 
+def test_activations_beyond_the_fp16_range_are_clamped(oracle):
+    """The tensor-core path rounds its activations to fp16.  Values beyond +-65504 are clamped
+    there (pack_rows_f16 and the fp16-row norms), never turned into infinities: the result is
+    the product with the clamped activations, finite, and the rows without such values are
+    untouched.  (The reference's cuBLAS path converts without a clamp and returns inf / nan
+    for such rows, cuda/kernels.cu:104-116; its CPU path computes them in fp32.)"""
+    from gpu_util import SUM_ORDER, dev, empty, host, ops
+    M, K, N = 64, 512, 256
+    r = np.random.default_rng(3)
+    x = r.standard_normal((M, K)).astype(np.float32)
+    x[5, 7], x[5, 100], x[9, 0] = 1e6, -3e5, 7e4
+    w16 = oracle.f32_to_f16((r.standard_normal((N, K)) * 0.02).astype(np.float32))
+    wq = oracle.quantize((r.standard_normal(N * K) * 0.02).astype(np.float32), 3)
+    clamped = np.clip(x, -65504.0, 65504.0)
+    y = empty((M, N))
+    ops.linear_forward_fp16(dev(x), dev(w16), y, M, K, N)
+    got = host(y)
+    assert np.isfinite(got).all()
+    np.testing.assert_allclose(got, _fp16_product(clamped, w16), **SUM_ORDER)
+    ops.linear_forward_q4(dev(x), dev(wq), y, M, K, N, 3)
+    got = host(y)
+    assert np.isfinite(got).all()
+    from gpu_util import fp16_close
+    fp16_close(got, _fp16_product(clamped, oracle.dequantize(wq, N * K, 3).reshape(N, K)), frac=1e-3)
+
+
 def test_status_word_is_clean_after_gemms():
     """No bounded wait inside the kernels ran out during the tests above."""
     from gpu_util import pkg
