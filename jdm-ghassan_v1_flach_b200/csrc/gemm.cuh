@@ -28,10 +28,13 @@ int umma_gemm(int epi, const __half* A, int64_t a_rows, const __half* B, const _
               const int32_t* group_map = nullptr, float* const* group_c = nullptr);
 
 // The same with B (and B2) in packed form, `kind` 0..3, dequantised inside the kernel
-// (values rounded to fp16).  K % 256 == 0.
+// (values rounded to fp16).  K % 256 == 0.  allow_split_k = false: K is never cut across CTAs,
+// so a row's result does not depend on how many rows the call has (callers that must give
+// the same bits for any slice of the rows).
 int umma_gemm_q(int epi, int kind, const __half* A, int64_t a_rows, const void* B, const void* B2, int64_t b_rows,
                 const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc,
-                float scale, const int32_t* group_map = nullptr, float* const* group_c = nullptr);
+                float scale, const int32_t* group_map = nullptr, float* const* group_c = nullptr,
+                bool allow_split_k = true);
 
 // moe_grouped.cu: the shared expert alone, out [N, d] = shared_expert(x); kind is a template
 // tag; scratch (optional) replaces the library's MoE workspace.

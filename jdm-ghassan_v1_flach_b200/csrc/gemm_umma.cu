@@ -78,6 +78,7 @@ struct alignas(64) GemmArgs {
     // partial product at c + s * split_stride; a second kernel adds the partials in order
     int k_splits, kb_split;
     int64_t split_stride;
+    bool allow_split_k;                 // host only: false keeps one K range whatever the tile count
 };
 
 template <int EPI>
@@ -864,7 +865,7 @@ static int launch_gemm_q(const GemmArgs& a) {
     // Not for the grouped form: the reduction pass walks all M rows, but a grouped launch
     // writes partial sums only for the rows its offsets cover - rows outside them (other
     // ranks' experts in the expert-parallel layer) must be left exactly as they are.
-    if (EPI == GEMM_EPI_STORE && a.offsets == nullptr && sb >= 2 && tiles * 2 <= num_sms()) {
+    if (EPI == GEMM_EPI_STORE && a.offsets == nullptr && a.allow_split_k && sb >= 2 && tiles * 2 <= num_sms()) {
         const int want = std::min(sb, num_sms() / tiles);
         const int per = (sb + want - 1) / want;
         b.k_splits = (sb + per - 1) / per;
@@ -892,7 +893,7 @@ static int launch_gemm_q(const GemmArgs& a) {
 // As umma_gemm(), with B (and B2) packed in `kind` (0..3), [b_rows, K]; K % 256 == 0.
 int umma_gemm_q(int epi, int kind, const __half* A, int64_t a_rows, const void* B, const void* B2, int64_t b_rows,
                 const int32_t* offsets, int groups, int M, int N, int K, float* c, __half* c16, int64_t ldc,
-                float scale, const int32_t* group_map, float* const* group_c) {
+                float scale, const int32_t* group_map, float* const* group_c, bool allow_split_k) {
     if (M <= 0 || N <= 0) return B200_OK;
     B200_REQUIRE(kind >= 0 && kind <= 3, "umma_gemm_q: unknown kind %d", kind);
     B200_REQUIRE(!group_c || (offsets && epi == GEMM_EPI_STORE), "umma_gemm_q: per-group outputs need the grouped store form");
@@ -915,7 +916,7 @@ int umma_gemm_q(int epi, int kind, const __half* A, int64_t a_rows, const void* 
         B200_REQUIRE(c || group_c, "umma_gemm_q: null output");
     }
     a.offsets = offsets; a.group_map = group_map; a.M = M; a.groups = groups; a.N = N; a.K = K;
-    a.c = c; a.c16 = c16; a.ldc = ldc; a.scale = scale; a.group_c = group_c;
+    a.c = c; a.c16 = c16; a.ldc = ldc; a.scale = scale; a.group_c = group_c; a.allow_split_k = allow_split_k;
     a.status = stream_status_ptr();
     B200_REQUIRE(a.status, "umma_gemm_q: status word allocation failed");
     // wide store tiles when they still fill the machine (row slots are an upper bound when
@@ -985,7 +986,7 @@ int umma_gemm(int epi, const __half* A, int64_t a_rows, const __half* B, const _
         B200_REQUIRE(c || group_c, "umma_gemm: null output");
     }
     a.offsets = offsets; a.group_map = group_map; a.M = M; a.groups = groups; a.N = N; a.K = K;
-    a.c = c; a.c16 = c16; a.ldc = ldc; a.scale = scale; a.group_c = group_c;
+    a.c = c; a.c16 = c16; a.ldc = ldc; a.scale = scale; a.group_c = group_c; a.allow_split_k = false;
     a.status = stream_status_ptr();
     B200_REQUIRE(a.status, "umma_gemm: status word allocation failed");
     const int slots128 = (M + GM_TILE_M - 1) / GM_TILE_M + (offsets ? groups / 2 : 0);

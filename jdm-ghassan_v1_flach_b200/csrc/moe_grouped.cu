@@ -99,9 +99,10 @@ int moe_forward_grouped(const float* x, const float* router_w, const float* rout
 
     auto gemm = [&](int epi, const __half* A, int64_t a_rows, const void* Bq, const void* Bq2, const __half* B16,
                     const __half* B16b, int64_t b_rows, const int32_t* offs, int groups, int M, int Nn, int Kk, float* c,
-                    __half* c16, int64_t ldc) {
+                    __half* c16, int64_t ldc, bool split_k_ok = true) {
         if (in_kernel)
-            return umma_gemm_q(epi, kind, A, a_rows, Bq, Bq2, b_rows, offs, groups, M, Nn, Kk, c, c16, ldc, 1.0f);
+            return umma_gemm_q(epi, kind, A, a_rows, Bq, Bq2, b_rows, offs, groups, M, Nn, Kk, c, c16, ldc, 1.0f, nullptr,
+                               nullptr, split_k_ok);
         return umma_gemm(epi, A, a_rows, B16, B16b, b_rows, offs, groups, M, Nn, Kk, c, c16, ldc, 1.0f);
     };
 
@@ -126,7 +127,10 @@ int moe_forward_grouped(const float* x, const float* router_w, const float* rout
                 rc = gemm(GEMM_EPI_SWIGLU, H(o_xs), T, sh_g, sh_u, sg16, su16, SH, nullptr, 1, T, SH, d, nullptr,
                           H(o_sact), SH);
             if (!rc)
-                rc = gemm(GEMM_EPI_STORE, H(o_sact), T, sh_d, nullptr, sd16, nullptr, d, nullptr, 1, T, d, SH, oc, nullptr, d);
+                // (one K range always: the expert-parallel layer runs the same product on a slice of
+                // the tokens and must reproduce these bits)
+                rc = gemm(GEMM_EPI_STORE, H(o_sact), T, sh_d, nullptr, sd16, nullptr, d, nullptr, 1, T, d, SH, oc, nullptr, d,
+                          false);
             const int rc2 = side_end();
             if (rc) return rc;
             if (rc2) return rc2;
@@ -258,7 +262,10 @@ int moe_shared_expert(const float* x, const void* sh_g, const void* sh_u, const 
     }
     rc = umma_gemm_q(GEMM_EPI_SWIGLU, kind, xs, N, sh_g, sh_u, SH, nullptr, 1, (int)N, SH, d, nullptr, sact, SH, 1.0f);
     if (rc) return rc;
-    return umma_gemm_q(GEMM_EPI_STORE, kind, sact, N, sh_d, nullptr, d, nullptr, 1, (int)N, d, SH, out, nullptr, d, 1.0f);
+    // one K range always: a token's result must not depend on how many tokens the call has
+    // (the expert-parallel layer runs this on a slice and must reproduce the single GPU's bits)
+    return umma_gemm_q(GEMM_EPI_STORE, kind, sact, N, sh_d, nullptr, d, nullptr, 1, (int)N, d, SH, out, nullptr, d, 1.0f,
+                       nullptr, nullptr, false);
 }
 
 // out [N, d] (+)= sum_k w[t, k] * y[inv[t K + k]] in k order; accumulate: onto the shared

@@ -248,10 +248,11 @@ def test_peer_memory_host_with_ranks_in_one_process(oracle, G):
     from gpu_util import dev, fp16_close, host, pkg
     d, E, ne, K, SH, wkind = 1536, 512, 64, 6, 1024, 3
     c, dc = _dev_case(oracle, 11, 200, d, E, ne, K, SH, wkind)
-    ranks = _EpRanks(dc, G, 200, d, E, ne, K, SH, wkind)
+    sizes = (200, 77, 3, 200) + ((4096,) if G == 8 else ())     # 4096 / 8: a slice the shared expert's GEMM could cut along K
+    ranks = _EpRanks(dc, G, max(sizes), d, E, ne, K, SH, wkind)
     ranks.K = K
     r = np.random.default_rng(5)
-    for T in (200, 77, 3, 200):
+    for T in sizes:
         x = dev(r.standard_normal((T, d)).astype(np.float32))
         outs, idx = ranks.forward(x)
         want, want_idx = _single_gpu_layer(dict(dc, x=x), T, d, E, ne, K, SH, wkind)
