@@ -61,6 +61,14 @@ H_TINY = dict(vocab=100352, hidden=1536, n_layers=40,
               rms_eps=1e-5, embedding_multiplier=12.0, residual_multiplier=0.22,
               attn_scale=0.0078125, logits_scaling=6.0)
 
+H_SMALL = dict(vocab=100352, hidden=4096, n_layers=40,
+               layer_types=[1 if l in (9, 19, 29, 39) else 0 for l in range(40)],
+               n_heads=32, n_kv=8, head_dim=128, rope_type=-1, rope_theta=1e4,
+               mamba_heads=128, mamba_d_head=64, mamba_d_state=128, mamba_d_conv=4,
+               n_experts=72, top_k=10, expert_dim=768, shared_dim=1536, qkind=3,
+               rms_eps=1e-5, embedding_multiplier=12.0, residual_multiplier=0.22,
+               attn_scale=0.0078125, logits_scaling=16.0)
+
 T_IDS = dict(embed=0, final_norm=1, lm_head=2, inv_freq=3, attn_norm=10, ffn_norm=11,
              w_in=20, conv_w=21, conv_b=22, dt_bias=23, a_log=24, D=25, norm_w=26, w_out=27,
              wq=30, wk=31, wv=32, wo=33, router=40, router_bias=41, gate=42, up=43, down=44,
@@ -747,6 +755,65 @@ def quantize_bench(lib):
     return out
 
 
+def config5_bench(steps=256, n_seq=64, lo=256, hi=8192):
+    """The ragged serving workload on one GPU: the H-Small-shaped model (hidden 4096, 36 Mamba-2 + 4 GQA
+    layers, 72 experts / top-10, Q4_K, random-init), 64 sequences with prompt lengths uniform in
+    [256, 8192] (seed 7) through b200_decoder_prefill_ragged, then `steps` greedy decode steps of all 64
+    sequences at their own positions (paged KV, page 64).  The 8-GPU expert-parallel form of this
+    model's MoE layer is measured separately (the moe blocks under --gpus N)."""
+    import torch
+    cfg = H_SMALL
+    lengths = np.random.default_rng(7).integers(lo, hi + 1, n_seq).astype(np.int32)
+    total = int(lengths.sum())
+    t0 = time.time()
+    model = DeviceModel(cfg, n_seq, int(lengths.max()) + steps + 16, seed=5)
+    model.configure(0, 1)
+    build_s = time.time() - t0
+    g = torch.Generator(device="cuda").manual_seed(8)
+    prompt = torch.randint(0, cfg["vocab"], (total,), device="cuda", generator=g, dtype=torch.int32)
+    tok = torch.empty(n_seq, dtype=torch.int32, device="cuda")
+    lib = model.lib
+    lib.b200_decoder_prefill_ragged(model.handle, prompt, lengths.ctypes.data, tok)      # untimed: sizes the workspaces
+    model.reset()
+    torch.cuda.synchronize()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
+    lib.b200_decoder_prefill_ragged(model.handle, prompt, lengths.ctypes.data, tok)
+    p1.record()
+    for _ in range(3):
+        model.step_dev(tok)
+    torch.cuda.synchronize()
+    prefill_ms = p0.elapsed_time(p1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        model.step_dev(tok)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    status = lib.raw("b200_stream_status")
+    weights = sum(t.numel() * t.element_size() for t in model.tensors.values())
+    free, total_mem = torch.cuda.mem_get_info()
+    peak, _ = peaks()
+    # per step: every weight matrix once (64 sequences x 10 experts touch all 72 experts), Mamba state read + written,
+    # the KV of every sequence at its own length
+    d_inner = cfg["mamba_heads"] * cfg["mamba_d_head"]
+    state = 2 * n_seq * 36 * d_inner * cfg["mamba_d_state"] * 4
+    kv = float((lengths.astype(np.int64) + 3 + steps // 2).sum()) * 4 * 2 * cfg["n_kv"] * cfg["head_dim"] * 2
+    step_bytes = weights - cfg["vocab"] * cfg["hidden"] * 2 * 0 + state + kv
+    out = {"model": "Granite-4.0-H-Small-shaped, random-init Q4_K, %.1f GB of weights" % (weights / 1e9),
+           "sequences": n_seq, "prompt_lengths": "uniform [%d, %d], seed 7: min %d, max %d, %d tokens in all" % (
+               lo, hi, int(lengths.min()), int(lengths.max()), total),
+           "prefill_ms": prefill_ms, "prefill_tok_s": total / (prefill_ms * 1e-3),
+           "decode_steps": steps, "ms_per_step": ms, "decode_tok_s": n_seq / (ms * 1e-3),
+           "algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms * 1e-3) / 1e9,
+           "frac_of_hbm_peak": step_bytes / (ms * 1e-3) / 1e9 / peak,
+           "device_memory_used_gb": (total_mem - free) / 1e9, "model_build_s": build_s, "status_clean": status == 0,
+           "mode": "ragged prefill in groups of <= 32768 tokens; per-op batched decode, tensor-core GEMM path, one CUDA graph per step"}
+    model.close()
+    return out
+
+
 def gemm_only_bench():
     """The many-token kernels alone: fp16 and Q4_K linears of the in_proj shape at 4096 rows,
     and the MoE layer at 512 and 4096 tokens.  One JSON line; ~1 GB on the device."""
@@ -833,15 +900,19 @@ def main():
     ap.add_argument("--profile-step", action="store_true",
                     help="after the timed steps run ONE more step between cudaProfilerStart/Stop and exit "
                          "(for ncu --profile-from-start off: DRAM bytes of every launch of a step)")
-    ap.add_argument("--only", default="", choices=["", "gemm", "prefill"],
+    ap.add_argument("--only", default="", choices=["", "gemm", "prefill", "config5"],
                     help="gemm: time the tensor-core linears and the MoE layer alone (small; also the profiling case); "
-                         "prefill: time the prompt path alone (with --small: the profiling case)")
+                         "prefill: time the prompt path alone (with --small: the profiling case); "
+                         "config5: the H-Small-shaped model on the ragged 64-sequence workload (about 40 GB on the device)")
     args = ap.parse_args()
     if args.only == "gemm":
         gemm_only_bench()
         return
     if args.only == "prefill":
         prefill_only_bench(args)
+        return
+    if args.only == "config5":
+        print(json.dumps({"config5": config5_bench(steps=args.steps if args.steps != 128 else 256)}))
         return
 
     rank = int(os.environ.get("RANK", "0"))

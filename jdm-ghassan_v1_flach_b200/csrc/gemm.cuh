@@ -44,6 +44,12 @@ int umma_gemm_q(int epi, int kind, const __half* A, int64_t a_rows, const void* 
 int moe_experts_rows(const __half* rows16, const int32_t* offsets, const int32_t* group_map, int groups, int64_t R,
                      const void* gates, const void* ups, const void* downs, int n_local, float* y, int d, int E, int kind,
                      float* const* y_groups = nullptr);
+// moe_units.cu: the routed experts of a decode batch as weight streams shared by the tokens
+// that chose them (few-token dot engine, exact dequantised weights).
+size_t moe_units_table_bytes(int64_t NK, int ne);
+int moe_units_forward(const float* x, const int32_t* grouped, const int32_t* offsets, const void* gates, const void* ups,
+                      const void* downs, float* act, float* y, void* units_scratch, int64_t N, int d, int E, int ne, int K,
+                      int kind);
 int moe_dispatch_perm(const int32_t* idx, int64_t N, int ne, int K, int32_t* grouped, int32_t* inv, int32_t* offsets);
 size_t moe_shared_scratch_bytes(int64_t N, int d, int SH);
 int moe_shared_expert(const float* x, const void* sh_g, const void* sh_u, const void* sh_d, float* out, int64_t N, int d,

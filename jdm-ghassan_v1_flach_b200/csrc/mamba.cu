@@ -117,6 +117,59 @@ mamba_step_scan_kernel(const float* __restrict__ bc, const float* __restrict__ d
     if (lane == 0) y[(int64_t)m * p.d_inner + row] = acc + Dv[h] * xv;
 }
 
+// The same update for many sequences (d_state 128, d_head a multiple of SCAN_ROWS): a warp owns
+// SCAN_ROWS consecutive rows of one head and issues all their 128-bit state loads before it
+// uses any, so that four times the bytes are in flight per warp - with one sequence the
+// kernel is a handful of rows per SM, with 64 it is a 200 MB stream that needs them.  Same
+// products in the same order per element as the kernel above.
+constexpr int SCAN_ROWS = 4;
+__global__ void __launch_bounds__(SCAN_WARPS * 32)
+mamba_step_scan_stream_kernel(const float* __restrict__ bc, const float* __restrict__ dt_raw,
+                              const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                              const float* __restrict__ Dv, float* __restrict__ ssm_state, float* __restrict__ y,
+                              int dt_stride, MambaDims p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rows = p.n_heads * p.d_head;
+    const int row0 = (blockIdx.x * SCAN_WARPS + warp) * SCAN_ROWS;
+    const int m = blockIdx.y;
+    if (row0 >= rows) return;
+    float* s = ssm_state + ((int64_t)m * rows + row0) * 128 + lane * 4;
+    float4 sv[SCAN_ROWS];
+#pragma unroll
+    for (int r = 0; r < SCAN_ROWS; ++r) sv[r] = __ldcs(reinterpret_cast<const float4*>(s + r * 128));
+    const int h = row0 / p.d_head;
+    const float u = dt_raw[(int64_t)m * dt_stride + h] + dt_bias[h];
+    const float dt = (u > 20.0f) ? u : log1pf(expf(u));
+    const float A = -expf(a_log[h]);
+    const float dA = expf(__fmul_rn(A, dt));
+    const float* bcm = bc + (int64_t)m * p.conv_dim;
+    const float* Bv = bcm + p.d_inner;
+    const float4 b4 = *reinterpret_cast<const float4*>(Bv + lane * 4);
+    const float4 c4 = *reinterpret_cast<const float4*>(Bv + 128 + lane * 4);
+    const float dskip = Dv[h];
+    float acc[SCAN_ROWS], xv[SCAN_ROWS];
+#pragma unroll
+    for (int r = 0; r < SCAN_ROWS; ++r) {
+        xv[r] = bcm[row0 + r];
+        float4 v = sv[r];
+        v.x = __fadd_rn(__fmul_rn(dA, v.x), __fmul_rn(__fmul_rn(dt, b4.x), xv[r]));
+        v.y = __fadd_rn(__fmul_rn(dA, v.y), __fmul_rn(__fmul_rn(dt, b4.y), xv[r]));
+        v.z = __fadd_rn(__fmul_rn(dA, v.z), __fmul_rn(__fmul_rn(dt, b4.z), xv[r]));
+        v.w = __fadd_rn(__fmul_rn(dA, v.w), __fmul_rn(__fmul_rn(dt, b4.w), xv[r]));
+        __stcs(reinterpret_cast<float4*>(s + r * 128), v);
+        acc[r] = c4.x * v.x + c4.y * v.y + c4.z * v.z + c4.w * v.w;
+    }
+#pragma unroll
+    for (int r = 0; r < SCAN_ROWS; ++r) acc[r] = warp_sum(acc[r]);
+    if (lane < SCAN_ROWS) {
+        float a = acc[0], x = xv[0];
+#pragma unroll
+        for (int r = 1; r < SCAN_ROWS; ++r)
+            if (lane == r) { a = acc[r]; x = xv[r]; }
+        y[(int64_t)m * p.d_inner + row0 + lane] = a + dskip * x;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Decode, many sequences: the convolution step on rows of an already computed
 // projection [M, proj] (gate | bc | dt).  One thread per (sequence, channel); same
@@ -457,8 +510,13 @@ int mamba2_step(const float* x, const void* w_in, const float* conv_w, const flo
         mamba_conv_step_kernel<<<(unsigned)ceil_div64(items, 256), 256, 0, stream()>>>(proj, conv_w, conv_b, conv_state,
                                                                                        bc, batch, p);
         B200_LAUNCH_CHECK("mamba_conv_step_kernel");
-        mamba_step_scan_kernel<<<dim3(ceil_div(rows, SCAN_WARPS), batch), SCAN_WARPS * 32, 0, stream()>>>(
-            bc, proj + p.d_inner + p.conv_dim, dt_bias, a_log, D, ssm_state, y, p.proj, p);
+        if (p.d_state == 128 && p.d_head % SCAN_ROWS == 0 && (reinterpret_cast<uintptr_t>(ssm_state) & 15) == 0 &&
+            (reinterpret_cast<uintptr_t>(bc) & 15) == 0 && p.conv_dim % 4 == 0 && p.d_inner % 4 == 0)
+            mamba_step_scan_stream_kernel<<<dim3(ceil_div(rows, SCAN_WARPS * SCAN_ROWS), batch), SCAN_WARPS * 32, 0, stream()>>>(
+                bc, proj + p.d_inner + p.conv_dim, dt_bias, a_log, D, ssm_state, y, p.proj, p);
+        else
+            mamba_step_scan_kernel<<<dim3(ceil_div(rows, SCAN_WARPS), batch), SCAN_WARPS * 32, 0, stream()>>>(
+                bc, proj + p.d_inner + p.conv_dim, dt_bias, a_log, D, ssm_state, y, p.proj, p);
         B200_LAUNCH_CHECK("mamba_step_scan_kernel");
         launch_gated_norm(y, proj, p.proj, norm_w, y, p.d_inner, p.eps, nullptr, batch);
         B200_LAUNCH_CHECK("mamba_gated_norm_kernel");

@@ -18,6 +18,11 @@
 namespace b200 {
 
 // moe_grouped.cu
+constexpr int MOE_UNITS_MAX_ROWS = 12;
+int moe_forward_units(const float* x, const float* router_w, const float* router_bias, const void* gates,
+                      const void* ups, const void* downs, const void* sh_g, const void* sh_u, const void* sh_d,
+                      float* out, float* probs_cache, int32_t* idx_cache, float* w_cache, int64_t N, int d, int E,
+                      int ne, int K, int SH, int kind);
 int moe_forward_grouped(const float* x, const float* router_w, const float* router_bias, const void* gates,
                         const void* ups, const void* downs, const void* sh_g, const void* sh_u, const void* sh_d,
                         float* out, float* probs_cache, int32_t* idx_cache, float* w_cache, int64_t N, int d, int E,
@@ -498,6 +503,17 @@ int moe_forward(const float* x, const float* router_w, const float* router_bias,
     // Many tokens over fp16 / packed experts: expert-grouped tensor-core GEMMs.  The
     // optional fp32 scratch outputs only exist on the token-major path.
     auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    // A decode batch: at most MOE_UNITS_MAX_ROWS rows per expert on average.  The experts'
+    // rows would leave the 128-row tensor-core tiles nearly empty; they run as weight streams
+    // shared by their tokens instead (moe_units.cu).
+    if (N > 8 && N * K <= (int64_t)MOE_UNITS_MAX_ROWS * ne && kind != KIND_F32 && !s_gate && !s_up && !s_act && aligned16(x) &&
+        aligned16(out) && aligned16(gates) && aligned16(ups) && aligned16(downs) && d % 8 == 0 &&
+        (kind != 3 || (d % 256 == 0 && E % 256 == 0)) && ne <= 256 &&
+        (!shared || (aligned16(sh_g) && aligned16(sh_u) && aligned16(sh_d) && (kind == KIND_F16 || SH % 256 == 0)))) {
+        const int rc = moe_forward_units(x, router_w, router_bias, gates, ups, downs, sh_g, sh_u, sh_d, out, probs_cache,
+                                         idx_cache, w_cache, N, d, E, ne, K, shared ? SH : 0, kind);
+        if (rc != B200_EUNSUPPORTED) return rc;
+    }
     if (N >= GEMM_MIN_ROWS && kind != KIND_F32 && !s_gate && !s_up && !s_act && aligned16(x) && aligned16(out) &&
         aligned16(gates) && aligned16(ups) && aligned16(downs) &&
         (!shared || (aligned16(sh_g) && aligned16(sh_u) && aligned16(sh_d))))

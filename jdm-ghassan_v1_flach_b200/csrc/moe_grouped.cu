@@ -160,6 +160,53 @@ int moe_forward_grouped(const float* x, const float* router_w, const float* rout
 }
 
 // ===========================================================================
+// A decode batch (more tokens than the token-major kernels take, fewer than fill the
+// tensor-core tiles of every expert): routing and permutation as above, the routed experts
+// through moe_units.cu, the shared expert as a GEMM on the side stream, the same k-ordered
+// combination.
+// ===========================================================================
+int moe_combine(const float* y, const int32_t* inv, const float* w, float* out, int64_t N, int d, int K, bool accumulate);
+int moe_forward_units(const float* x, const float* router_w, const float* router_bias, const void* gates,
+                      const void* ups, const void* downs, const void* sh_g, const void* sh_u, const void* sh_d,
+                      float* out, float* probs_cache, int32_t* idx_cache, float* w_cache, int64_t N, int d, int E,
+                      int ne, int K, int SH, int kind) {
+    const bool shared = sh_g && sh_u && sh_d && SH > 0;
+    const size_t NK = (size_t)N * K;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
+    const size_t o_idx = take(NK * 4), o_w = take(NK * 4), o_grp = take(NK * 4), o_inv = take(NK * 4),
+                 o_off = take((size_t)(ne + 1) * 4), o_units = take(moe_units_table_bytes((int64_t)NK, ne)),
+                 o_act = take(NK * E * 4), o_y = take(NK * d * 4),
+                 o_sh = shared ? take(moe_shared_scratch_bytes(N, d, SH)) : 0;
+    void* wsp;
+    int rc = workspace(WS_MOE).ensure(off + 256, &wsp);
+    if (rc) return rc;
+    char* base = static_cast<char*>(wsp);
+    int32_t* idx = idx_cache ? idx_cache : reinterpret_cast<int32_t*>(base + o_idx);
+    float* w = w_cache ? w_cache : reinterpret_cast<float*>(base + o_w);
+    int32_t* grouped = reinterpret_cast<int32_t*>(base + o_grp);
+    int32_t* inv = reinterpret_cast<int32_t*>(base + o_inv);
+    int32_t* offsets = reinterpret_cast<int32_t*>(base + o_off);
+    float* act = reinterpret_cast<float*>(base + o_act);
+    float* y = reinterpret_cast<float*>(base + o_y);
+    if (shared) {
+        if ((rc = side_begin())) return rc;
+        rc = moe_shared_expert(x, sh_g, sh_u, sh_d, out, N, d, SH, kind, base + o_sh);
+        const int rc2 = side_end();
+        if (rc) return rc;
+        if (rc2) return rc2;
+    }
+    rc = moe_route(x, router_w, router_bias, probs_cache, idx, w, N, d, ne, K);
+    if (rc) return rc;
+    rc = moe_dispatch_perm(idx, N, ne, K, grouped, inv, offsets);
+    if (rc) return rc;
+    rc = moe_units_forward(x, grouped, offsets, gates, ups, downs, act, y, base + o_units, N, d, E, ne, K, kind);
+    if (rc) return rc;
+    if (shared && (rc = side_wait())) return rc;
+    return moe_combine(y, inv, w, out, N, d, K, shared);
+}
+
+// ===========================================================================
 // The same layer cut at its exchange points, for expert parallelism: a rank routes
 // and packs its own tokens (rows come out sorted by expert, hence by owning rank),
 // the rows travel, the owner runs its experts on whatever rows arrived - one group

@@ -66,7 +66,7 @@ def main():
             assert torch.equal(idx, want_idx[lo:lo + n.value]), f"rank {rank} T {T}: routing differs"
         torch.cuda.synchronize()
         assert lib.raw("b200_stream_status") == 0, f"rank {rank} T {T}: a bounded wait ran out"
-        if T >= 32:
+        if T * K > 12 * ne:          # below that the single GPU runs its fp32 decode-batch kernels
             assert torch.equal(got, want), f"rank {rank} T {T}: max diff {(got - want).abs().max().item():.3e}"
         else:
             fp16_close(host(got), host(want))

@@ -35,7 +35,7 @@ def _single_gpu_layer(dc, T, d, E, ne, K, SH, wkind):
 @pytest.mark.parametrize("wkind,d,E,SH", [(3, 256, 256, 512), (-1, 128, 64, 64), (2, 256, 256, 256)])
 def test_world_size_one_equals_the_layer(oracle, wkind, d, E, SH):
     from gpu_util import host
-    T, ne, K = 96, 16, 2
+    T, ne, K = 200, 16, 2            # more than 12 rows per expert: the single GPU takes the tensor-core path too
     c, dc = _dev_case(oracle, 7, T, d, E, ne, K, SH, wkind)
     layer = ep.ExpertParallelMoE(d, E, ne, K, SH, wkind, dc["router_w"], dc["router_bias"], dc["gates"], dc["ups"],
                                  dc["downs"], (dc["sh_g"], dc["sh_u"], dc["sh_d"]))
@@ -165,7 +165,10 @@ def test_dispatch_free_form_few_rows_leaves_other_ranks_rows_alone(oracle):
         idx0 = idx
     want, want_idx = _single_gpu_layer(dc, T, d, E, ne, K, SH, wkind)
     assert np.array_equal(host(idx0), want_idx)
-    np.testing.assert_allclose(host(total), want, **SUM_ORDER)
+    # (at this size the single-GPU layer runs its fp32 decode-batch kernels, the ranks the
+    # tensor-core GEMM on fp16 operands: compared at the fp16 bound)
+    from gpu_util import fp16_close
+    fp16_close(host(total), want)
 
 
 def test_dispatch_free_form_replays_as_a_cuda_graph(oracle):
@@ -258,9 +261,9 @@ def test_peer_memory_host_with_ranks_in_one_process(oracle, G):
         want, want_idx = _single_gpu_layer(dict(dc, x=x), T, d, E, ne, K, SH, wkind)
         assert np.array_equal(host(idx), want_idx)
         for o in outs:                                   # every rank holds the whole output
-            if T >= 32:      # the same tensor-core kernels, the same order of additions: identical bits
+            if T * K > 12 * ne:   # the same tensor-core kernels, the same order of additions: identical bits
                 assert np.array_equal(host(o).view(np.uint32), want.view(np.uint32))
-            else:            # a few tokens take the single GPU's fp32 few-token kernels instead
+            else:            # a decode-sized batch takes the single GPU's fp32 few-token kernels instead
                 fp16_close(host(o), want)
                 assert np.array_equal(host(o), host(outs[0]))
     assert pkg.lib().raw("b200_stream_status") == 0

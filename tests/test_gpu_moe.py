@@ -83,6 +83,26 @@ def test_layer_config3_shape(oracle, N):
     _close(got["out"], out, N, 3)
 
 
+@pytest.mark.parametrize("wkind", [3, 2, 0, -1])
+@pytest.mark.parametrize("N", [9, 33, 128])
+def test_layer_decode_batch_without_shared_expert_is_fp32_tight(oracle, wkind, N):
+    """A decode batch (more than 8 tokens, at most ~12 rows per expert) runs the routed experts
+    as weight streams shared by their tokens, on the few-token dot engine: exact dequantised
+    weights, fp32 accumulation - the summation-order bound, not the fp16 one.  Without a
+    shared expert nothing in the layer touches the tensor-core GEMM.  Ragged loads: the router
+    bias sends up to a few dozen tokens to one expert (several units) and none to others."""
+    from gpu_util import SUM_ORDER
+    d, E, ne, K, SH = 512, 256, 64, 6, 0
+    c = moe_case(oracle, 900 + N + wkind, N, d, E, ne, K, 0, wkind, bias_sigma=0.05)
+    got = _run(c, N, d, E, ne, K, SH, wkind)
+    out, probs, idx, w = _oracle(oracle, c, d, E, ne, K, SH, wkind)
+    assert np.array_equal(got["idx"], idx)
+    _ulp_close(got["w"], w)
+    np.testing.assert_allclose(got["out"], out, **SUM_ORDER)
+    again = _run(c, N, d, E, ne, K, SH, wkind)
+    assert np.array_equal(got["out"].view(np.uint32), again["out"].view(np.uint32))      # run-to-run bit-stable
+
+
 def test_layer_config3_4096_tokens(oracle):
     """The prefill-sized case: routing checked on every token, outputs on a sample of
     tokens (a token's output depends on no other token), and run-to-run bit stability."""
