@@ -61,8 +61,10 @@ __global__ void moe_units_build_kernel(const int32_t* __restrict__ offsets, int 
     }
 }
 
-// grid (ctas per unit, unit slots).  A tile: R rows of the expert's gate matrix followed by
-// the same R rows of its up matrix.
+// grid (ctas per unit, unit slots).  An output tile is R rows of the activation; its two weight
+// tiles - R rows of the expert's gate matrix, the same R rows of its up matrix - travel as two
+// consecutive ring entries (2 i, 2 i + 1), which keeps a stage small enough that two CTAs fit
+// an SM next to eight tokens' staged activations.
 template <int KIND>
 __global__ void __launch_bounds__(SG_THREADS, 2) moe_units_gateup_kernel(MoeUnitArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -89,20 +91,18 @@ __global__ void __launch_bounds__(SG_THREADS, 2) moe_units_gateup_kernel(MoeUnit
     const int first = blockIdx.x, step = gridDim.x;
     const int n_my = first < num_tiles ? (num_tiles - first + step - 1) / step : 0;
     const int64_t rb = row_bytes_of(KIND, a.d);
-    const int sub = a.rows_per_tile * (int)rb;
 
     if (warp == SG_CONSUMERS) {
         if (lane == 0) {
             int issued = 0;
-            for (int i = 0; i < n_my; ++i) {
+            for (int i = 0; i < 2 * n_my; ++i) {
                 if (!ring.acquire(i)) break;
-                const int r0 = (first + i * step) * a.rows_per_tile;
+                const int r0 = (first + (i >> 1) * step) * a.rows_per_tile;
                 const int rows = min(a.rows_per_tile, a.E - r0);
                 const int64_t row0 = (int64_t)e * a.E + r0;
                 const uint32_t bytes = (uint32_t)(rows * rb);
-                ring.expect(i, 2 * bytes);
-                ring.copy(i, 0, a.gates + row0 * rb, bytes);
-                ring.copy(i, sub, a.ups + row0 * rb, bytes);
+                ring.expect(i, bytes);
+                ring.copy(i, 0, ((i & 1) ? a.ups : a.gates) + row0 * rb, bytes);
                 issued = i + 1;
             }
             ring.drain(issued);
@@ -114,14 +114,15 @@ __global__ void __launch_bounds__(SG_THREADS, 2) moe_units_gateup_kernel(MoeUnit
         stage_x<KIND, false, false>(a.x + (int64_t)(a.grouped[p0 + m] / a.K) * a.d, nullptr, xa, m, 0.0f, red_d, 0.0);
     const int e_row = threadIdx.x >> 3, e_m = threadIdx.x & 7;
     for (int i = 0; i < n_my; ++i) {
-        if (!ring.wait_full(i)) break;
         const int r0 = (first + i * step) * a.rows_per_tile;
         const int rows = min(a.rows_per_tile, a.E - r0);
-        const uint8_t* ts = ring.stage(i);
         float* red_buf = red + (size_t)(i & 1) * RED_BUF;
-        tile_compute<KIND, UNIT_SLOTS>(ts, rb, rows, a.d, xa, 0, M, red_buf, warp, lane);
-        tile_compute<KIND, UNIT_SLOTS>(ts + sub, rb, rows, a.d, xa, 0, M, red_buf + RED_PASS, warp, lane);
-        ring.release(i);
+        if (!ring.wait_full(2 * i)) break;
+        tile_compute<KIND, UNIT_SLOTS>(ring.stage(2 * i), rb, rows, a.d, xa, 0, M, red_buf, warp, lane);
+        ring.release(2 * i);
+        if (!ring.wait_full(2 * i + 1)) break;
+        tile_compute<KIND, UNIT_SLOTS>(ring.stage(2 * i + 1), rb, rows, a.d, xa, 0, M, red_buf + RED_PASS, warp, lane);
+        ring.release(2 * i + 1);
         consumer_sync();
         if (e_row < rows && e_m < M) {
             const float g = red_value<KIND>(red_buf, e_row, e_m);
@@ -199,12 +200,16 @@ static int moe_units_kind(MoeUnitArgs a, int max_units) {
     int rc;
     {
         MoeUnitArgs g = a;
-        const int R = pick_rows(KIND, 2 * rb_d, rb_d, rb_d, a.E);
+        const int R = pick_rows(KIND, rb_d, rb_d, rb_d, a.E);
         if (R < 1 || !tail_tile_ok(a.E, R, rb_d)) return fail(B200_EUNSUPPORTED, "moe_units: row size cannot be tiled to 16 bytes");
         g.rows_per_tile = R;
-        g.stage_bytes = (int)(((size_t)2 * R * rb_d + 127) / 128 * 128);
+        g.stage_bytes = (int)(((size_t)R * rb_d + 127) / 128 * 128);
         const size_t other = xact_bytes<KIND>(a.d, UNIT_SLOTS, false) + fixed;
-        g.n_stages = pick_stages(g.stage_bytes, other);
+        // two resident CTAs per SM matter more here than a deep ring (the tiles of a unit are
+        // consecutive rows: the stream has no gaps to hide): two stages in half an SM's shared
+        // memory are taken before more stages in all of it
+        g.n_stages = pick_stages_in(g.stage_bytes, other, SMEM_BUDGET);
+        if (g.n_stages < 2) g.n_stages = pick_stages_in(g.stage_bytes, other, SMEM_BUDGET_FULL);
         if (g.n_stages < 2) return fail(B200_EUNSUPPORTED, "moe_units: hidden size %d does not fit the shared-memory staging", a.d);
         auto kern = moe_units_gateup_kernel<KIND>;
         static bool cfgd = false;
