@@ -665,7 +665,8 @@ def moe_sweep_bench(lib, sizes=(1, 64, 512, 4096)):
         out.append({"tokens": T, "ms_per_layer": ms, "experts_touched": touched, "weight_bytes": wbytes,
                     "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / hbm_peak, "tflops": tfs,
                     "frac_of_dense_peak": tfs / tf_peak, "bound": bound,
-                    "operands": "fp32 (exact dequantised weights)" if T < 32 else "fp16 x in-kernel dequantised Q4_K, fp32 accumulation"})
+                    "operands": "fp32 (exact dequantised weights; the shared expert as an fp16 tensor-core GEMM from 9 tokens on)"
+                                if T * K <= 12 * ne else "fp16 x in-kernel dequantised Q4_K, fp32 accumulation"})
     return out
 
 
@@ -900,16 +901,26 @@ def main():
     ap.add_argument("--profile-step", action="store_true",
                     help="after the timed steps run ONE more step between cudaProfilerStart/Stop and exit "
                          "(for ncu --profile-from-start off: DRAM bytes of every launch of a step)")
-    ap.add_argument("--only", default="", choices=["", "gemm", "prefill", "config5"],
+    ap.add_argument("--only", default="", choices=["", "gemm", "prefill", "config5", "moe64", "quantize"],
                     help="gemm: time the tensor-core linears and the MoE layer alone (small; also the profiling case); "
                          "prefill: time the prompt path alone (with --small: the profiling case); "
-                         "config5: the H-Small-shaped model on the ragged 64-sequence workload (about 40 GB on the device)")
+                         "config5: the H-Small-shaped model on the ragged 64-sequence workload (about 40 GB on the device); "
+                         "moe64 / quantize: the MoE layer on 64 tokens / the load-time quantisers alone (profiling cases)")
     args = ap.parse_args()
     if args.only == "gemm":
         gemm_only_bench()
         return
     if args.only == "prefill":
         prefill_only_bench(args)
+        return
+    if args.only == "moe64":
+        # the MoE layer on a decode batch of 64 tokens (small profiling case)
+        lib = importlib.import_module(PKG).lib()
+        print(json.dumps({"moe_sweep": moe_sweep_bench(lib, sizes=(64,))}))
+        return
+    if args.only == "quantize":
+        lib = importlib.import_module(PKG).lib()
+        print(json.dumps({"quantizers": quantize_bench(lib)}))
         return
     if args.only == "config5":
         print(json.dumps({"config5": config5_bench(steps=args.steps if args.steps != 128 else 256)}))
