@@ -200,7 +200,12 @@ int b200_gguf_open(const char* path, b200_gguf** out) {
         if (!c.ok) return bail("truncated or malformed metadata");
         if (numeric) {
             g->numbers.push_back({key, num});
-            if (key == "general.alignment" && num >= 1.0) g->alignment = (uint64_t)num;
+            if (key == "general.alignment") {
+                // a power of two of at most 1 MiB, as every writer produces; anything else is a damaged file
+                const uint64_t a = num >= 1.0 && num <= 1048576.0 ? (uint64_t)num : 0;
+                if (a == 0 || (a & (a - 1)) != 0) return bail("implausible general.alignment");
+                g->alignment = a;
+            }
         }
     }
     g->tensors.resize((size_t)n_tensors);
@@ -210,8 +215,12 @@ int b200_gguf_open(const char* path, b200_gguf** out) {
         if (!c.ok || nd > 4) return bail("tensor with more than four dimensions");
         t.numel = 1;
         for (uint32_t k = 0; k < nd; ++k) {
-            t.dims.push_back(c.pod<uint64_t>());
-            t.numel *= t.dims.back();
+            const uint64_t dim = c.pod<uint64_t>();
+            // (a product beyond 2^40 elements cannot lie inside a file; refusing it here also keeps
+            // the multiplication from wrapping)
+            if (dim == 0 || dim > ((uint64_t)1 << 40) || t.numel > ((uint64_t)1 << 40) / dim) return bail("implausible tensor shape");
+            t.dims.push_back(dim);
+            t.numel *= dim;
         }
         t.type = c.pod<uint32_t>();
         t.offset = c.pod<uint64_t>();

@@ -94,6 +94,17 @@ def test_rejects_a_file_that_is_not_gguf(lib, tmp_path):
     raw = open(PATH, "rb").read()
     p.write_bytes(raw[:200])                       # cut inside the tensor table
     assert lib.raw("b200_gguf_open", str(p).encode(), C.byref(h)) != 0
+    # a tensor whose dimensions multiply past 2^64 (would wrap to a small element count)
+    import struct
+    name = b"tok_embeddings"
+    at = raw.index(struct.pack("<Q", len(name)) + name) + 8 + len(name)       # its table entry: n_dims, dims ...
+    nd = struct.unpack_from("<I", raw, at)[0]
+    assert nd == 2
+    bad = bytearray(raw)
+    struct.pack_into("<QQ", bad, at + 4, 1 << 62, 1 << 62)
+    p.write_bytes(bytes(bad))
+    assert lib.raw("b200_gguf_open", str(p).encode(), C.byref(h)) != 0
+    assert "shape" in lib.last_error()
 
 
 def test_storage_kind_policy(lib):
