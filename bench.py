@@ -756,6 +756,40 @@ def quantize_bench(lib):
     return out
 
 
+def config1_bench():
+    """Config 1 end to end: the 8-layer hybrid (hidden 768, vocabulary 32768, Q8_0), a 128-token prompt
+    through b200_decoder_prefill, then 128 greedy steps through b200_decoder_step_host (host token in,
+    host pick out, a synchronise per token) - wall clock around the whole generation."""
+    import torch
+    from model_util import CONFIG_1
+    cfg = dict(CONFIG_1)
+    model = DeviceModel(cfg, 1, 128 + 128 + 16, seed=0)
+    model.configure(1, 1)
+    prompt = torch.randint(0, cfg["vocab"], (1, 128), device="cuda", dtype=torch.int32,
+                           generator=torch.Generator(device="cuda").manual_seed(1))
+    tok = torch.empty(1, dtype=torch.int32, device="cuda")
+    tin, tout = np.zeros(1, np.int32), np.zeros(1, np.int32)
+
+    def generate():
+        model.reset()
+        model.prefill(prompt, tok)
+        tin[0] = int(tok.cpu()[0])
+        for _ in range(128):
+            model.step_host(tin, tout)
+            tin[0] = tout[0]
+
+    generate()                      # sizes workspaces, records the graph
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    generate()
+    torch.cuda.synchronize()
+    sec = time.perf_counter() - t0
+    model.close()
+    return {"workload": "8 layers (6 Mamba-2 + 2 GQA), hidden 768, vocabulary 32768, Q8_0, batch 1: 128-token prompt + 128 greedy steps",
+            "seconds": sec, "decode_tok_s_incl_prompt": 128 / sec, "ms_per_generated_token": sec / 128 * 1e3,
+            "mode": "prefill through the many-token kernels, steps through b200_decoder_step_host (fused mode, CUDA graph)"}
+
+
 def config5_bench(steps=256, n_seq=64, lo=256, hi=8192):
     """The ragged serving workload on one GPU: the H-Small-shaped model (hidden 4096, 36 Mamba-2 + 4 GQA
     layers, 72 experts / top-10, Q4_K, random-init), 64 sequences with prompt lengths uniform in
@@ -1058,13 +1092,14 @@ def main():
     if world > 1 and not args.quick:
         # where the exchange pays: more tokens per pass (the prompt side of the workload)
         ep_sweep = [moe_layer_bench(lib, rank, world, tokens=t, iters=5) for t in (16384, 65536)]
-    batch64 = moe_sweep = mamba_ops = quantizers = None
+    batch64 = moe_sweep = mamba_ops = quantizers = config1 = None
     if world == 1 and B == 1 and not args.small and not args.quick:
         model.close()
         model = None
         moe_sweep = moe_sweep_bench(lib)
         mamba_ops = mamba_ops_bench(lib)
         quantizers = quantize_bench(lib)
+        config1 = config1_bench()
         batch64 = batch_decode_bench(cfg, 64, 4096, 16, seed=rank)
 
     default_workload = (B == 1 and args.ctx == 4096 and args.fused == 1 and args.graph == 1 and not args.small)
@@ -1101,6 +1136,7 @@ def main():
             "moe_sweep": moe_sweep,
             "mamba_ops": mamba_ops,
             "quantizers": quantizers,
+            "config1": config1,
             "moe_layer_ep_sweep": ep_sweep,
             "batch64": batch64,
             "prefill": None if prefill_ms is None else {
