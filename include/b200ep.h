@@ -15,21 +15,24 @@
  * peers' blocks (CUDA IPC across processes; plain pointers for ranks of one process).
  * A forward pass is, per rank, stream-ordered and free of host synchronisation:
  *
- *   route + pack      this rank's token slice [rank T / world, (rank + 1) T / world): top-K,
- *                     one fp16 row per (token, k) slot sorted by expert - rows bound for one
- *                     rank are contiguous
- *   dispatch          a kernel stores each rank's rows and a header (rows per local expert,
- *                     where they sit in the sender's order) straight into that rank's block,
- *                     fences, and raises the sender's flag there (an epoch number)
- *   experts           waits (bounded) for every sender's flag, reads the headers into a group
- *                     list, runs the grouped tcgen05 GEMMs over (sender, local expert) blocks
- *                     in arrival order - while the shared expert of the rank's own tokens
- *                     runs on a second stream
- *   return            a kernel stores the result rows into the senders' blocks at the
- *                     positions the headers named, fence, flag
- *   combine + gather  waits for the returns, adds shared expert and the K weighted rows in k
- *                     order, stores the slice into every rank's output, fence, flag; the
- *                     layer is complete on a rank when it has every rank's slice flag
+ *   route + dispatch  this rank's token slice [rank T / world, (rank + 1) T / world): top-K and the
+ *                     expert-sorted order of its (token, k) slots; one kernel rounds each slot's
+ *                     row to fp16 and stores it straight into the block of the rank that owns its
+ *                     expert, with a header (rows per local expert, where they sit in the sender's
+ *                     order), fences, and raises the sender's flag there (the pass number); the
+ *                     shared expert of the slice runs meanwhile on a second stream
+ *   experts + return  waits (bounded) for every sender's flag, turns the headers into a group list
+ *                     (gaps between the senders' regions are skipped by the tile scheduler), runs
+ *                     the grouped tcgen05 GEMMs over (sender, local expert) blocks in arrival order;
+ *                     the down projection's epilogue stores each result row at its home in the
+ *                     sender's block; fence, flag
+ *   combine + gather  waits for the returns, adds shared expert and the K weighted rows in k order
+ *                     and stores the slice into every rank's output, fence, flag
+ *   wait              the pass is complete on a rank when it has every rank's slice flag
+ *
+ * The pass number lives in device memory and the pass reads nothing on the host, so
+ * b200_ep_forward records it into a CUDA graph on its third call with the same (x, T) and
+ * replays it afterwards.
  *
  * Every wait is bounded (spin limit); when one runs out the kernel sets the library's
  * status word and returns, and the next b200_stream_status() reports B200_ECUDA.  The
@@ -76,8 +79,8 @@ int b200_ep_connect_local(b200_ep* ep, b200_ep* const* peers);
  * the library's stream and returns; ranks must call it the same number of times with the
  * same T. */
 int b200_ep_forward(b200_ep* ep, const float* x, int T);
-/* The same in its four stream-ordered phases (0 route + pack + dispatch, 1 experts + return,
- * 2 combine + gather, 3 wait for all slices).  Ranks that share one GPU must run phase p for
+/* The same in its four stream-ordered phases (0 route + dispatch, 1 experts + return,
+ * 2 combine + gather, 3 wait for all slices), always eager.  Ranks that share one GPU must run phase p for
  * every rank before phase p + 1 of any (their waits then never spin). */
 int b200_ep_phase(b200_ep* ep, int phase, const float* x, int T);
 /* out_dev: [T, d] fp32 of the last pass (valid until the next pass begins on any rank). */
@@ -87,8 +90,9 @@ int b200_ep_output(b200_ep* ep, const float** out_dev);
 int b200_ep_routing(b200_ep* ep, const int32_t** idx_dev, const float** w_dev, int* n_slice);
 /* Test hook: iterations a flag wait may spin (0 restores the default). */
 int b200_ep_set_spin_limit(b200_ep* ep, int spin_limit);
-/* Bytes the last pass moved over the links from this rank (rows out, results out, slices
- * out), counted on the host from the header of the pass before (synchronises). */
+/* Bytes the last pass moved over the links from this rank: the fp16 rows of slots whose expert
+ * lives elsewhere, as many fp32 result rows, and the output slice to world - 1 peers; counted on
+ * the host from the pass's expert offsets (synchronises). */
 int b200_ep_link_bytes(b200_ep* ep, double* bytes);
 
 #ifdef __cplusplus
