@@ -259,8 +259,10 @@ int b200_softmax_cross_entropy(const float* logits, const int32_t* targets, floa
                                double* out_loss_sum, int64_t* out_count, float z_scale);
 int b200_argmax_token(const float* logits, int V, int32_t* token_host);                      /* :290; synchronous D2H */
 int b200_argmax_token_device(const float* logits, int V, int32_t* token_dev);                /* extension: no sync */
+/* :291.  hist: a host array as in the reference (staged to the device here), or a device pointer
+ * (used in place). */
 int b200_apply_rep_penalties(float* logits, int V, const int32_t* hist, int hist_n,
-                             float rep, float freq, float pres);                             /* :291 */
+                             float rep, float freq, float pres);
 int b200_free_sampling_workspace(void);                                                      /* :293 */
 
 /* ---- workspaces: cuda_ops.h:157,309-328 ----------------------------------------- */

@@ -315,6 +315,19 @@ int b200_apply_rep_penalties(float* logits, int V, const int32_t* hist, int hist
     const bool use_rep = rep > 0.0f && rep != 1.0f;
     if (!use_rep && freq == 0.0f && pres == 0.0f) return B200_OK;
     B200_REQUIRE(logits && hist, "apply_rep_penalties: null pointer");
+    // The reference hands over the history as a HOST array (it stages it itself,
+    // cuda/kernels.cu:1279-1308); a device pointer is accepted as well and used in place.
+    cudaPointerAttributes at;
+    const cudaError_t q = cudaPointerGetAttributes(&at, hist);
+    if (q != cudaSuccess) cudaGetLastError();
+    const bool on_device = q == cudaSuccess && (at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged);
+    if (!on_device) {
+        void* ws;
+        const int rc = workspace(WS_SAMPLE).ensure((size_t)hist_n * 4 + 256, &ws);
+        if (rc) return rc;
+        B200_CUDA(cudaMemcpyAsync(ws, hist, (size_t)hist_n * 4, cudaMemcpyHostToDevice, stream()));
+        hist = static_cast<const int32_t*>(ws);
+    }
     rep_penalty_kernel<<<flat_grid(hist_n), 256, 0, stream()>>>(logits, V, hist, hist_n, rep, freq, pres);
     B200_LAUNCH_CHECK("rep_penalty_kernel");
     return B200_OK;

@@ -444,3 +444,22 @@ REF_API int ref_score_tokens(void* h, const i32* tokens, int T, const unsigned c
         *mean_nll = s->gen->score_tokens(t, mask ? &m : nullptr, n_scored, nullptr);
     });
 }
+
+// Generator::prefill + Generator::generate (inference/generator.cpp:917-1098) with a sampling
+// configuration: on the CUDA device this is the engine's fast path (penalties and top-K on the
+// device, Sampler::sample_candidates on the host), on the CPU device Sampler::sample.
+REF_API int ref_generate(void* h, const i32* prompt, int n_prompt, int max_new, const float* f, const int* ic, u64 seed,
+                         i32* out, int* n_out) {
+    return guarded([&] {
+        RefSession* s = static_cast<RefSession*>(h);
+        s->gen->reset();
+        s->gen->prefill(std::vector<i32>(prompt, prompt + n_prompt));
+        GenerationConfig cfg;
+        cfg.max_new_tokens = max_new;
+        cfg.stop_tokens = {-1};
+        cfg.sampling = sampling_of(f, ic, seed);
+        const std::vector<i32> toks = s->gen->generate(cfg, nullptr);
+        *n_out = static_cast<int>(toks.size());
+        std::memcpy(out, toks.data(), sizeof(i32) * toks.size());
+    });
+}

@@ -437,6 +437,16 @@ class RefGenerator:
                  "score_tokens")
         return nll.value, n.value
 
+    def generate(self, prompt, max_new, sampling, seed):
+        """Generator::prefill + generate with an oracle_lib.Sampling configuration."""
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        out = np.empty(max_new, np.int32)
+        n = C.c_int()
+        self._ck(self.lib.ref_generate(self.h, prompt.ctypes.data_as(C.c_void_p), prompt.size, max_new,
+                                       sampling.f.ctypes.data_as(C.c_void_p), sampling.i.ctypes.data_as(C.c_void_p),
+                                       C.c_uint64(seed), out.ctypes.data_as(C.c_void_p), C.byref(n)), "generate")
+        return out[:n.value].copy()
+
     def close(self):
         if self.h:
             self.lib.ref_model_destroy(self.h)

@@ -124,6 +124,10 @@ def test_topk_and_penalties(oracle):
     hist[:50] = hist[50:100]
     dl = dev(logits)
     ops.apply_rep_penalties(dl, V, dev(hist), hist.size, 1.12, 0.05, 0.3)
+    # and with the history in host memory, as the reference's generator passes it
+    dl_host_hist = dev(logits)
+    ops.apply_rep_penalties(dl_host_hist, V, hist.ctypes.data, hist.size, 1.12, 0.05, 0.3)
+    assert np.array_equal(host(dl_host_hist).view(np.uint32), host(dl).view(np.uint32))
     np.testing.assert_allclose(host(dl), oracle.rep_penalties(logits, hist, 1.12, 0.05, 0.3), rtol=1e-6, atol=1e-6)
 
 
