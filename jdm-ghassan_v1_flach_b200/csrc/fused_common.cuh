@@ -71,27 +71,35 @@ struct Ring {
         }
         __syncthreads();
     }
-    __device__ __forceinline__ uint8_t* stage(int i) const { return stages + (size_t)(i % n_stages) * stage_bytes; }
+    // i / n_stages and i % n_stages without a division (n_stages <= SG_MAX_STAGES = 4: the high
+    // word of i * ceil(2^32 / n) is the exact quotient for every i below 2^31)
+    __device__ __forceinline__ int lap(int i) const {
+        const uint32_t inv = n_stages == 2 ? 0x80000000u : n_stages == 3 ? 0x55555556u : 0x40000000u;
+        return n_stages == 1 ? i : (int)__umulhi((uint32_t)i, inv);
+    }
+    __device__ __forceinline__ int slot(int i) const { return i - lap(i) * n_stages; }
+    __device__ __forceinline__ uint8_t* stage(int i) const { return stages + (size_t)slot(i) * stage_bytes; }
     // producer side
     __device__ __forceinline__ bool acquire(int i) {
-        return i < n_stages || mbar_wait(&empty[i % n_stages], ((i / n_stages) - 1) & 1, status);
+        return i < n_stages || mbar_wait(&empty[slot(i)], (lap(i) - 1) & 1, status);
     }
-    __device__ __forceinline__ void expect(int i, uint32_t bytes) { mbar_expect_tx(&full[i % n_stages], bytes); }
+    __device__ __forceinline__ void expect(int i, uint32_t bytes) { mbar_expect_tx(&full[slot(i)], bytes); }
     __device__ __forceinline__ void copy(int i, int offset, const void* src, uint32_t bytes) {
-        tma_load_1d(stage(i) + offset, src, bytes, &full[i % n_stages]);
+        tma_load_1d(stage(i) + offset, src, bytes, &full[slot(i)]);
     }
     // never leave with copies of this CTA still in flight
     __device__ __forceinline__ void drain(int issued) {
         for (int i = max(0, issued - n_stages); i < issued; ++i)
-            if (!mbar_wait(&full[i % n_stages], (i / n_stages) & 1, status)) break;
+            if (!mbar_wait(&full[slot(i)], lap(i) & 1, status)) break;
     }
     // consumer side
-    __device__ __forceinline__ bool wait_full(int i) { return mbar_wait(&full[i % n_stages], (i / n_stages) & 1, status); }
+    __device__ __forceinline__ bool wait_full(int i) { return mbar_wait(&full[slot(i)], lap(i) & 1, status); }
     __device__ __forceinline__ void release(int i) {
         __syncwarp();
-        if ((threadIdx.x & 31) == 0) mbar_arrive(&empty[i % n_stages]);
+        if ((threadIdx.x & 31) == 0) mbar_arrive(&empty[slot(i)]);
     }
 };
+static_assert(SG_MAX_STAGES <= 4, "Ring::lap covers up to four stages");
 
 // ---- activations in shared memory ----------------------------------------------
 // Scalar path: fp32, unit-major (stream.cuh).  Tensor-core path: fp16 hi/lo parts
@@ -104,9 +112,10 @@ struct XAct {
     float* sumx = nullptr;
     float* f32 = nullptr;      // [tokens][K] natural order, may be null
     int K = 0, tokens = 0;
+    int zrow = -1;             // row that stands in for absent tokens (-1: the zero row after the last token)
     __device__ __forceinline__ XHalf half() const {
         XHalf h;
-        h.hi = hi; h.lo = lo; h.sumx = sumx; h.stride = K + XH_PAD; h.nsub = K >> 5; h.zero_row = tokens;
+        h.hi = hi; h.lo = lo; h.sumx = sumx; h.stride = K + XH_PAD; h.nsub = K >> 5; h.zero_row = zrow >= 0 ? zrow : tokens;
         return h;
     }
 };
@@ -334,31 +343,45 @@ __device__ __forceinline__ double stage_x(const float* x, const float* nw_s, con
 // `cnt` vectors of K floats (src + r * src_stride) into token rows 0..cnt-1 of xa in
 // one pass: all loads in flight together, one barrier.  No normalisation.  Falls back
 // to one stage_x per vector when the runs do not fit the registers.
-template <int KIND, bool CG = false, int NC = SG_CONSUMERS>
+// row_index (optional): row r is read from src + (row_index[r] / div) * src_stride (a gather).
+// XQ: runs of four a thread may hold (cnt * K <= XQ * 4 * threads for the one-pass form).
+template <int KIND, bool CG = false, int NC = SG_CONSUMERS, int XQ = XQ_REG>
 __device__ __forceinline__ void stage_rows(const float* src, int64_t src_stride, const XAct& xa, int cnt,
-                                           double* red) {
+                                           double* red, const int32_t* row_index = nullptr, int div = 1) {
     constexpr int SG_CTHREADS = NC * 32;
     const int K = xa.K, nq = K >> 2, total = cnt * nq;
     const int nrun = (total + SG_CTHREADS - 1) / SG_CTHREADS;
-    if (nrun > XQ_REG || (reinterpret_cast<uintptr_t>(src) & 15) != 0 || (src_stride & 3) != 0) {
-        for (int r = 0; r < cnt; ++r) stage_x<KIND, false, false, CG, NC>(src + r * src_stride, nullptr, xa, r, 0.0f, red, 0.0);
+    auto row_of = [&](int r) -> int64_t { return row_index ? (int64_t)(row_index[r] / div) : (int64_t)r; };
+    if (nrun > XQ || (reinterpret_cast<uintptr_t>(src) & 15) != 0 || (src_stride & 3) != 0) {
+        for (int r = 0; r < cnt; ++r)
+            stage_x<KIND, false, false, CG, NC>(src + row_of(r) * src_stride, nullptr, xa, r, 0.0f, red, 0.0);
         return;
     }
     const int lane = threadIdx.x & 31;
     const size_t row = (size_t)(K + XH_PAD);
-    float4 v[XQ_REG];
+    // i / nq by one multiplication (exact for i < 2^16 * ... : i <= XQ * threads, nq <= 2^14); the
+    // gathered rows' numbers are worked out once, by cnt threads, into the reduction scratch
+    const uint32_t nq_inv = 0xFFFFFFFFu / (uint32_t)nq + 1u;
+    int* rix = reinterpret_cast<int*>(red);
+    if (row_index) {
+        if ((int)threadIdx.x < cnt) rix[threadIdx.x] = row_index[threadIdx.x] / div;
+        consumer_sync<NC>();
+    }
+    float4 v[XQ];
 #pragma unroll
-    for (int j = 0; j < XQ_REG; ++j) {
+    for (int j = 0; j < XQ; ++j) {
         const int i = j * SG_CTHREADS + threadIdx.x;
-        const int r = i / nq, q = i - r * nq;
-        v[j] = (j < nrun && i < total) ? ld_f4<CG>(src + r * src_stride + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const int r = (int)__umulhi((uint32_t)i, nq_inv), q = i - r * nq;
+        const int64_t sr = row_index ? (int64_t)rix[min(r, cnt - 1)] : (int64_t)r;
+        v[j] = (j < nrun && i < total) ? ld_f4<CG>(src + sr * src_stride + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
-    for (int j = 0; j < XQ_REG; ++j) {
+    for (int j = 0; j < XQ; ++j) {
         if (j < nrun) {
             const int i = j * SG_CTHREADS + threadIdx.x;
             const bool ok = i < total;
-            const int r = ok ? i / nq : 0, q = ok ? i - r * nq : 0, k = q << 2;
+            const int rr = (int)__umulhi((uint32_t)i, nq_inv);
+            const int r = ok ? rr : 0, q = ok ? i - rr * nq : 0, k = q << 2;
             if (UsesMma<KIND>::value) {
                 __half h[4], l[4];
                 split_half(v[j].x, h[0], l[0]);

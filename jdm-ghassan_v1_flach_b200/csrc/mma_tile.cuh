@@ -69,46 +69,76 @@ __device__ __forceinline__ uint32_t nib_hi(uint32_t w) {   // nibbles at bits 4-
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// Q4_K: partial sums over this warp's share of K (64-weight groups g = part,
-// part + nparts, ...) for the 16 rows at `tile` (row stride rb bytes).  acc: the m16n8
-// accumulator fragment (rows lane/4 and lane/4+8, columns = tokens 2*(lane%4), +1).
+// 32-bit shared-memory loads (tiles and staged activations live in shared memory; plain
+// pointers would carry 64-bit generic address arithmetic through the loop).
+__device__ __forceinline__ uint4 lds_u4(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_u2(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float2 lds_f2(uint32_t a) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+    return v;
+}
+
+// Q4_K: partial sums over this warp's share of K - the 64-weight groups
+// [part * per, (part + 1) * per), per = ceil(K / 64 / nparts) - for the 16 rows at `tile`
+// (row stride rb bytes; tile and xh in shared memory).  acc: the m16n8 accumulator fragment
+// (rows lane/4 and lane/4+8, columns = tokens 2*(lane%4), +1).  A super-block's header is
+// decoded once for the groups of the range that share it.
 __device__ __forceinline__ void tile_dot_q4k(const uint8_t* tile, int rb, int K, const XHalf& xh, int M, int part,
                                              int nparts, int lane, float (&acc)[4]) {
     const int gid = lane >> 2, tig = lane & 3;
     const int tok = gid < M ? gid : xh.zero_row;
-    const __half* xh_row = xh.hi + (size_t)tok * xh.stride;
-    const __half* xl_row = xh.lo + (size_t)tok * xh.stride;
-    const int c0 = 2 * tig, c1 = 2 * tig + 1;
-    const float* sx0 = xh.sumx + (size_t)(c0 < M ? c0 : xh.zero_row) * xh.nsub;
-    const float* sx1 = xh.sumx + (size_t)(c1 < M ? c1 : xh.zero_row) * xh.nsub;
+    const int c0 = 2 * tig, c1 = c0 + 1;
     const int groups = K >> 6;
-    for (int g = part; g < groups; g += nparts) {
+    const int per = (groups + nparts - 1) / nparts;
+    const int g0 = part * per, g1 = min(groups, g0 + per);
+    const int row = lane & 15, hi = lane >> 4;
+    const uint32_t tile_s = static_cast<uint32_t>(__cvta_generic_to_shared(tile));
+    const uint32_t hdr_a = tile_s + row * rb;
+    const uint32_t wa_a = tile_s + gid * rb + 16 + 8 * tig;
+    const uint32_t wb_a = wa_a + 8 * rb;
+    const uint32_t x_off = (uint32_t)(tok * xh.stride + 8 * tig) * 2 + g0 * 128;
+    uint32_t xh_a = static_cast<uint32_t>(__cvta_generic_to_shared(xh.hi)) + x_off;
+    uint32_t xl_a = static_cast<uint32_t>(__cvta_generic_to_shared(xh.lo)) + x_off;
+    const uint32_t sum_s = static_cast<uint32_t>(__cvta_generic_to_shared(xh.sumx));
+    uint32_t s0_a = sum_s + (uint32_t)((c0 < M ? c0 : xh.zero_row) * xh.nsub) * 4 + g0 * 8;
+    uint32_t s1_a = sum_s + (uint32_t)((c1 < M ? c1 : xh.zero_row) * xh.nsub) * 4 + g0 * 8;
+    uint32_t sc_lo = 0, sc_hi = 0, mn_lo = 0, mn_hi = 0;
+    float d = 0.0f, dmin = 0.0f;
+    int cur_sb = -1;
+    for (int g = g0; g < g1; ++g, xh_a += 128, xl_a += 128, s0_a += 8, s1_a += 8) {
         const int sb = g >> 2, j = g & 3;
-        // this lane's (row, sub-block) scale pair; shared with the warp by shuffles
-        float P, Q;
-        {
-            const int row = lane & 15, hi = lane >> 4;
-            const uint8_t* hdr = tile + (size_t)row * rb + sb * 144;
-            const uint4 h4 = *reinterpret_cast<const uint4*>(hdr);
-            int s, m;
-            q4k_scale_min_regs(2 * j + hi, h4.y, h4.z, h4.w, s, m);
-            const float d = half_bits_to_float((uint16_t)(h4.x & 0xFFFF));
-            const float dmin = half_bits_to_float((uint16_t)(h4.x >> 16));
-            P = d * (float)s * (hi ? 0.0625f : 1.0f);
-            Q = dmin * (float)m;
+        if (sb != cur_sb) {                       // uniform over the warp
+            cur_sb = sb;
+            // this lane's row: d, dmin and the eight 6-bit (scale, min) pairs as bytes of two words each
+            const uint4 h4 = lds_u4(hdr_a + sb * 144);
+            d = half_bits_to_float((uint16_t)(h4.x & 0xFFFF));
+            dmin = half_bits_to_float((uint16_t)(h4.x >> 16));
+            sc_lo = h4.y & 0x3F3F3F3Fu;
+            mn_lo = h4.z & 0x3F3F3F3Fu;
+            sc_hi = (h4.w & 0x0F0F0F0Fu) | ((h4.y >> 2) & 0x30303030u);
+            mn_hi = ((h4.w >> 4) & 0x0F0F0F0Fu) | ((h4.z >> 2) & 0x30303030u);
         }
+        // this lane's (row, sub-block 2 j + hi) scale pair; shared with the warp by shuffles
+        const uint32_t sel = 2 * j + hi;
+        const float P = d * (float)(__byte_perm(sc_lo, sc_hi, sel) & 0xFFu) * (hi ? 0.0625f : 1.0f);
+        const float Q = dmin * (float)(__byte_perm(mn_lo, mn_hi, sel) & 0xFFu);
         const float P_lo_a = __shfl_sync(0xffffffffu, P, gid), P_lo_b = __shfl_sync(0xffffffffu, P, gid + 8);
         const float P_hi_a = __shfl_sync(0xffffffffu, P, 16 + gid), P_hi_b = __shfl_sync(0xffffffffu, P, 24 + gid);
         const float Q_lo_a = __shfl_sync(0xffffffffu, Q, gid), Q_lo_b = __shfl_sync(0xffffffffu, Q, gid + 8);
         const float Q_hi_a = __shfl_sync(0xffffffffu, Q, 16 + gid), Q_hi_b = __shfl_sync(0xffffffffu, Q, 24 + gid);
-        const uint8_t* wbase = tile + sb * 144 + 16 + 32 * j + 8 * tig;
-        const uint2 wa = *reinterpret_cast<const uint2*>(wbase + (size_t)gid * rb);
-        const uint2 wb = *reinterpret_cast<const uint2*>(wbase + (size_t)(gid + 8) * rb);
-        const int k0 = sb * 256 + j * 64 + 8 * tig;
-        const uint4 bh_lo = *reinterpret_cast<const uint4*>(xh_row + k0);
-        const uint4 bl_lo = *reinterpret_cast<const uint4*>(xl_row + k0);
-        const uint4 bh_hi = *reinterpret_cast<const uint4*>(xh_row + k0 + 32);
-        const uint4 bl_hi = *reinterpret_cast<const uint4*>(xl_row + k0 + 32);
+        const uint32_t woff = sb * 144 + 32 * j;
+        const uint2 wa = lds_u2(wa_a + woff);
+        const uint2 wb = lds_u2(wb_a + woff);
+        const uint4 bh_lo = lds_u4(xh_a), bl_lo = lds_u4(xl_a), bh_hi = lds_u4(xh_a + 64), bl_hi = lds_u4(xl_a + 64);
         float cl[4] = {0.f, 0.f, 0.f, 0.f}, ch[4] = {0.f, 0.f, 0.f, 0.f};
         {
             const uint32_t a0 = nib_lo(wa.x), a1 = nib_lo(wb.x), a2 = nib_lo(wa.x >> 8), a3 = nib_lo(wb.x >> 8);
@@ -126,12 +156,11 @@ __device__ __forceinline__ void tile_dot_q4k(const uint8_t* tile, int rb, int K,
             mma_16816(ch, e0, e1, e2, e3, bh_hi.z, bh_hi.w);
             mma_16816(ch, e0, e1, e2, e3, bl_hi.z, bl_hi.w);
         }
-        const int sub = sb * 8 + 2 * j;
-        const float s0l = sx0[sub], s1l = sx1[sub], s0h = sx0[sub + 1], s1h = sx1[sub + 1];
-        acc[0] += P_lo_a * cl[0] - Q_lo_a * s0l + P_hi_a * ch[0] - Q_hi_a * s0h;
-        acc[1] += P_lo_a * cl[1] - Q_lo_a * s1l + P_hi_a * ch[1] - Q_hi_a * s1h;
-        acc[2] += P_lo_b * cl[2] - Q_lo_b * s0l + P_hi_b * ch[2] - Q_hi_b * s0h;
-        acc[3] += P_lo_b * cl[3] - Q_lo_b * s1l + P_hi_b * ch[3] - Q_hi_b * s1h;
+        const float2 s0 = lds_f2(s0_a), s1 = lds_f2(s1_a);
+        acc[0] += P_lo_a * cl[0] - Q_lo_a * s0.x + P_hi_a * ch[0] - Q_hi_a * s0.y;
+        acc[1] += P_lo_a * cl[1] - Q_lo_a * s1.x + P_hi_a * ch[1] - Q_hi_a * s1.y;
+        acc[2] += P_lo_b * cl[2] - Q_lo_b * s0.x + P_hi_b * ch[2] - Q_hi_b * s0.y;
+        acc[3] += P_lo_b * cl[3] - Q_lo_b * s1.x + P_hi_b * ch[3] - Q_hi_b * s1.y;
     }
 }
 

@@ -22,6 +22,14 @@
 namespace b200 {
 
 constexpr int UNIT_SLOTS = 8;        // token columns of the dot engine
+// Rows carved for a unit's activations.  Tensor-core kinds: the columns of absent tokens are never
+// read back, so they may multiply any staged row - token 0 stands in and no zero row is kept
+// (xact_carve adds one row to its count: UNIT_SLOTS rows in all), which leaves room for a third
+// ring stage next to eight tokens.
+template <int KIND>
+struct UnitRows {
+    static constexpr int value = UsesMma<KIND>::value ? UNIT_SLOTS - 1 : UNIT_SLOTS;
+};
 
 struct MoeUnitArgs {
     const float* x = nullptr;            // [T, d] layer input
@@ -33,6 +41,7 @@ struct MoeUnitArgs {
     float* y = nullptr;                  // [NK, d], sorted order
     int d = 0, E = 0, K = 0;
     int rows_per_tile = 0, stage_bytes = 0, n_stages = 0;
+    int row_tiles = 1;                   // down kernel, tensor-core kinds: 16-row tiles per ring entry
     int* status = nullptr;
     bool dry = false;
 };
@@ -74,7 +83,8 @@ __global__ void __launch_bounds__(SG_THREADS, 2) moe_units_gateup_kernel(MoeUnit
     ring.n_stages = a.n_stages;
     ring.status = a.status;
     XAct xa;
-    uint8_t* p = xact_carve<KIND>(xa, smem + (size_t)a.n_stages * a.stage_bytes, a.d, UNIT_SLOTS, false);
+    uint8_t* p = xact_carve<KIND>(xa, smem + (size_t)a.n_stages * a.stage_bytes, a.d, UnitRows<KIND>::value, false);
+    xa.zrow = 0;
     float* red = reinterpret_cast<float*>(p);
     p += (size_t)RED_FLOATS * 4;
     ring.full = reinterpret_cast<uint64_t*>(p);
@@ -109,9 +119,8 @@ __global__ void __launch_bounds__(SG_THREADS, 2) moe_units_gateup_kernel(MoeUnit
         }
         return;
     }
-    xact_zero_row<KIND>(xa);
-    for (int m = 0; m < M; ++m)
-        stage_x<KIND, false, false>(a.x + (int64_t)(a.grouped[p0 + m] / a.K) * a.d, nullptr, xa, m, 0.0f, red_d, 0.0);
+    // the unit's tokens in one pass: every load in flight before the first is used, one barrier
+    stage_rows<KIND, false, SG_CONSUMERS, 12>(a.x, a.d, xa, M, red_d, a.grouped + p0, a.K);
     const int e_row = threadIdx.x >> 3, e_m = threadIdx.x & 7;
     for (int i = 0; i < n_my; ++i) {
         const int r0 = (first + i * step) * a.rows_per_tile;
@@ -142,7 +151,8 @@ __global__ void __launch_bounds__(SG_THREADS, 2) moe_units_down_kernel(MoeUnitAr
     ring.n_stages = a.n_stages;
     ring.status = a.status;
     XAct xa;
-    uint8_t* p = xact_carve<KIND>(xa, smem + (size_t)a.n_stages * a.stage_bytes, a.E, UNIT_SLOTS, false);
+    uint8_t* p = xact_carve<KIND>(xa, smem + (size_t)a.n_stages * a.stage_bytes, a.E, UnitRows<KIND>::value, false);
+    xa.zrow = 0;
     float* red = reinterpret_cast<float*>(p);
     p += (size_t)RED_FLOATS * 4;
     ring.full = reinterpret_cast<uint64_t*>(p);
@@ -176,18 +186,54 @@ __global__ void __launch_bounds__(SG_THREADS, 2) moe_units_down_kernel(MoeUnitAr
         }
         return;
     }
-    xact_zero_row<KIND>(xa);
     stage_rows<KIND>(a.act + (int64_t)p0 * a.E, a.E, xa, M, red_d);
     const int e_row = threadIdx.x >> 3, e_m = threadIdx.x & 7;
-    for (int i = 0; i < n_my; ++i) {
-        if (!ring.wait_full(i)) break;
-        const int r0 = (first + i * step) * a.rows_per_tile;
-        const int rows = min(a.rows_per_tile, a.d - r0);
-        float* red_buf = red + (size_t)(i & 1) * RED_BUF;
-        tile_compute<KIND, UNIT_SLOTS>(ring.stage(i), rb, rows, a.E, xa, 0, M, red_buf, warp, lane);
-        ring.release(i);
-        consumer_sync();
-        if (e_row < rows && e_m < M) a.y[(int64_t)(p0 + e_m) * a.d + r0 + e_row] = red_value<KIND>(red_buf, e_row, e_m);
+    if constexpr (UsesMma<KIND>::value) {
+        // A ring entry holds RT 16-row tiles; warp = (tile rt, K part kp of KP = 8 / RT), so a warp
+        // runs RT times the groups of a one-tile entry between two hand-overs and the parts to add
+        // afterwards are KP, not eight.  red: [kp][rt][16 rows][8 tokens].
+        const int RT = a.row_tiles, KP = SG_CONSUMERS / RT;
+        const int rt = warp / KP, kp = warp - rt * KP;
+        const XHalf xh = xa.half();
+        for (int i = 0; i < n_my; ++i) {
+            if (!ring.wait_full(i)) break;
+            const int r0 = (first + i * step) * a.rows_per_tile;
+            const int rows = min(a.rows_per_tile, a.d - r0);
+            float* red_buf = red + (size_t)(i & 1) * RED_BUF;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint8_t* sub = ring.stage(i) + (size_t)rt * TILE_ROWS * rb;
+            if (rt * TILE_ROWS < rows) {
+                if (KIND == 3) tile_dot_q4k(sub, (int)rb, a.E, xh, M, kp, KP, lane, acc);
+                else tile_dot_f16(sub, (int)rb, a.E, xh, M, kp, KP, lane, acc);
+            }
+            float* o = red_buf + (size_t)(kp * RT + rt) * RED_PASS;
+            const int gid = lane >> 2, c = 2 * (lane & 3);
+            o[gid * RED_TOK + c] = acc[0];
+            o[gid * RED_TOK + c + 1] = acc[1];
+            o[(gid + 8) * RED_TOK + c] = acc[2];
+            o[(gid + 8) * RED_TOK + c + 1] = acc[3];
+            ring.release(i);
+            consumer_sync();
+            for (int row = e_row; row < rows; row += SG_CTHREADS / RED_TOK) {
+                if (e_m < M) {
+                    const float* src = red_buf + (size_t)(row >> 4) * RED_PASS + (row & 15) * RED_TOK + e_m;
+                    float v = 0.0f;
+                    for (int q = 0; q < KP; ++q) v += src[(size_t)q * RT * RED_PASS];
+                    a.y[(int64_t)(p0 + e_m) * a.d + r0 + row] = v;
+                }
+            }
+        }
+    } else {
+        for (int i = 0; i < n_my; ++i) {
+            if (!ring.wait_full(i)) break;
+            const int r0 = (first + i * step) * a.rows_per_tile;
+            const int rows = min(a.rows_per_tile, a.d - r0);
+            float* red_buf = red + (size_t)(i & 1) * RED_BUF;
+            tile_compute<KIND, UNIT_SLOTS>(ring.stage(i), rb, rows, a.E, xa, 0, M, red_buf, warp, lane);
+            ring.release(i);
+            consumer_sync();
+            if (e_row < rows && e_m < M) a.y[(int64_t)(p0 + e_m) * a.d + r0 + e_row] = red_value<KIND>(red_buf, e_row, e_m);
+        }
     }
 }
 
@@ -204,7 +250,7 @@ static int moe_units_kind(MoeUnitArgs a, int max_units) {
         if (R < 1 || !tail_tile_ok(a.E, R, rb_d)) return fail(B200_EUNSUPPORTED, "moe_units: row size cannot be tiled to 16 bytes");
         g.rows_per_tile = R;
         g.stage_bytes = (int)(((size_t)R * rb_d + 127) / 128 * 128);
-        const size_t other = xact_bytes<KIND>(a.d, UNIT_SLOTS, false) + fixed;
+        const size_t other = xact_bytes<KIND>(a.d, UnitRows<KIND>::value, false) + fixed;
         // two resident CTAs per SM matter more here than a deep ring (the tiles of a unit are
         // consecutive rows: the stream has no gaps to hide): two stages in half an SM's shared
         // memory are taken before more stages in all of it
@@ -220,11 +266,19 @@ static int moe_units_kind(MoeUnitArgs a, int max_units) {
     }
     {
         MoeUnitArgs g = a;
-        const int R = pick_rows(KIND, rb_e, rb_e, rb_e, a.d);
+        int R = pick_rows(KIND, rb_e, rb_e, rb_e, a.d);
+        if (UsesMma<KIND>::value) {
+            // short contractions: several 16-row tiles per ring entry, so that a warp has about four
+            // groups of 64 to run per entry (E = 512: four tiles, two K parts)
+            const int groups = std::max(1, a.E / 64);
+            g.row_tiles = groups <= 8 ? 4 : groups <= 16 ? 2 : 1;
+            while (g.row_tiles > 1 && (a.d < R * g.row_tiles || !tail_tile_ok(a.d, R * g.row_tiles, rb_e))) g.row_tiles /= 2;
+            R *= g.row_tiles;
+        }
         if (R < 1 || !tail_tile_ok(a.d, R, rb_e)) return fail(B200_EUNSUPPORTED, "moe_units: row size cannot be tiled to 16 bytes");
         g.rows_per_tile = R;
         g.stage_bytes = (int)(((size_t)R * rb_e + 127) / 128 * 128);
-        const size_t other = xact_bytes<KIND>(a.E, UNIT_SLOTS, false) + fixed;
+        const size_t other = xact_bytes<KIND>(a.E, UnitRows<KIND>::value, false) + fixed;
         g.n_stages = pick_stages(g.stage_bytes, other);
         if (g.n_stages < 2) return fail(B200_EUNSUPPORTED, "moe_units: expert width %d does not fit the shared-memory staging", a.E);
         auto kern = moe_units_down_kernel<KIND>;
