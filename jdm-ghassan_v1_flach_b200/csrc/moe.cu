@@ -424,6 +424,80 @@ route_logits_kernel(const float* __restrict__ x, const float* __restrict__ route
         }
 }
 
+// A decode batch (tens of tokens): the tiled kernel above would occupy N / 8 x ne / 32 blocks -
+// 16 SMs for 64 tokens - each crawling along 1536-long chains.  Here a block takes 8 tokens x 8
+// experts (64 chains), and the two parts of a chain are split over its threads: the group sums
+// ((a0 b0 + a1 b1) + a2 b2) + a3 b3 of a 1024-column piece are independent and go to shared
+// memory four threads per chain; one thread per chain then adds them in order (the only
+// sequential part: one dependent add per group).  Same values, same order as the chains above.
+constexpr int RC_TOK = 8, RC_EXP = 8, RC_COLS = 1024, RC_LD = RC_COLS + 4, RC_GLD = RC_COLS / 4 + 1;
+constexpr size_t RC_SMEM = ((size_t)(RC_TOK + RC_EXP) * RC_LD + (size_t)RC_TOK * RC_EXP * RC_GLD) * 4;
+__global__ void __launch_bounds__(256)
+route_logits_chains_kernel(const float* __restrict__ x, const float* __restrict__ router_w, float* __restrict__ logits,
+                           int64_t N, int d, int ne) {
+    extern __shared__ __align__(16) float rc_smem[];
+    float* xs = rc_smem;                                  // [RC_TOK][RC_LD]
+    float* ws = xs + RC_TOK * RC_LD;                      // [RC_EXP][RC_LD]
+    float* gs = ws + RC_EXP * RC_LD;                      // [64 chains][RC_GLD]
+    const int64_t t0 = (int64_t)blockIdx.x * RC_TOK;
+    const int e0 = blockIdx.y * RC_EXP;
+    const int c = threadIdx.x & 63, sub = threadIdx.x >> 6;          // chain, which quarter of its groups
+    const int tc = c & 7, ec = c >> 3;
+    float chain = 0.0f;
+    // A piece is at most 256 runs of four wide: one run per thread and row, all 16 loads in flight;
+    // the next piece is fetched into registers while the current one is worked on.
+    const int q = threadIdx.x, c4 = q * 4;
+    float4 v[RC_TOK + RC_EXP];
+    auto fetch = [&](int k0) {
+        const int q4 = min(RC_COLS, d - k0) >> 2;
+#pragma unroll
+        for (int row = 0; row < RC_TOK + RC_EXP; ++row) {
+            v[row] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (q < q4) {
+                if (row < RC_TOK) {
+                    if (t0 + row < N) v[row] = *reinterpret_cast<const float4*>(x + (t0 + row) * d + k0 + c4);
+                } else if (e0 + row - RC_TOK < ne) {
+                    v[row] = *reinterpret_cast<const float4*>(router_w + (int64_t)(e0 + row - RC_TOK) * d + k0 + c4);
+                }
+            }
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < d; k0 += RC_COLS) {
+        const int kc = min(RC_COLS, d - k0), q4 = kc >> 2;           // kc % 4 == 0
+        __syncthreads();                                             // the previous piece has been consumed
+        if (q < q4) {
+#pragma unroll
+            for (int row = 0; row < RC_TOK + RC_EXP; ++row)
+                *reinterpret_cast<float4*>((row < RC_TOK ? xs + row * RC_LD : ws + (row - RC_TOK) * RC_LD) + c4) = v[row];
+        }
+        __syncthreads();
+        if (k0 + RC_COLS < d) fetch(k0 + RC_COLS);
+        const float* xa = xs + tc * RC_LD;
+        const float* wb = ws + ec * RC_LD;
+        float* gc = gs + c * RC_GLD;
+#pragma unroll 4
+        for (int g = sub; g < q4; g += 4) {
+            const float4 a = *reinterpret_cast<const float4*>(xa + 4 * g);
+            const float4 b = *reinterpret_cast<const float4*>(wb + 4 * g);
+            float t = __fadd_rn(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y));
+            t = __fadd_rn(t, __fmul_rn(a.z, b.z));
+            t = __fadd_rn(t, __fmul_rn(a.w, b.w));
+            gc[g] = t;
+        }
+        __syncthreads();
+        if (threadIdx.x < 64) {
+#pragma unroll 8
+            for (int g = 0; g < q4; ++g) chain = __fadd_rn(chain, gc[g]);
+        }
+    }
+    if (threadIdx.x < 64) {
+        const int64_t t = t0 + tc;
+        const int e = e0 + ec;
+        if (t < N && e < ne) logits[t * ne + e] = chain;
+    }
+}
+
 constexpr int RF_WARPS = 8;
 __global__ void __launch_bounds__(RF_WARPS * 32)
 route_finish_kernel(const float* __restrict__ logits, const float* __restrict__ router_bias, float* __restrict__ probs_out,
@@ -448,7 +522,16 @@ int moe_route(const float* x, const float* router_w, const float* router_bias, f
         int rc = workspace(WS_ROUTE).ensure((size_t)N * ne * 4 + 256, &wsp);
         if (rc) return rc;
         float* logits = static_cast<float*>(wsp);
-        if (N <= 1024) {
+        if (N <= 256) {
+            static bool configured = false;
+            if (!configured) {
+                B200_CUDA(cudaFuncSetAttribute(route_logits_chains_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)RC_SMEM));
+                configured = true;
+            }
+            const dim3 grid((unsigned)ceil_div64(N, RC_TOK), ceil_div(ne, RC_EXP));
+            route_logits_chains_kernel<<<grid, 256, RC_SMEM, stream()>>>(x, router_w, logits, N, d, ne);
+        } else if (N <= 1024) {
             const dim3 grid((unsigned)ceil_div64(N, 8), ceil_div(ne, 32));
             route_logits_kernel<1, 1><<<grid, 256, 0, stream()>>>(x, router_w, logits, N, d, ne);
         } else {
