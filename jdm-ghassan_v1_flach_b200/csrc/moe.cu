@@ -237,6 +237,85 @@ perm_fill_kernel(const int32_t* __restrict__ idx, int64_t NK, int ne, const int3
     }
 }
 
+// Up to PERM_CHUNK slots (a decode batch): the three steps and the inverse in one block -
+// histogram, scan over the experts, the same ranked fill (cursor = the expert's offset).
+__global__ void __launch_bounds__(PERM_THREADS)
+perm_small_kernel(const int32_t* __restrict__ idx, int NK, int ne, int32_t* __restrict__ grouped,
+                  int32_t* __restrict__ inv, int32_t* __restrict__ offsets) {
+    constexpr int NW = PERM_THREADS / 32;
+    __shared__ int cursor[MOE_MAX_NE + 1];
+    __shared__ int wcnt[NW][MOE_MAX_NE];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = threadIdx.x; e <= ne; e += blockDim.x) cursor[e] = 0;
+    __syncthreads();
+    int mine[PERM_ITERS];
+#pragma unroll
+    for (int it = 0; it < PERM_ITERS; ++it) {
+        const int s = it * PERM_THREADS + threadIdx.x;
+        mine[it] = s < NK ? idx[s] : -1;
+        if (s < NK) atomicAdd(&cursor[mine[it]], 1);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // exclusive scan of the counts, 32 experts at a time
+        int run = 0;
+        for (int e0 = 0; e0 <= ne; e0 += 32) {
+            const int e = e0 + lane;
+            const int c = e < ne ? cursor[e] : 0;
+            int incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            if (e <= ne) {
+                cursor[e] = run + incl - c;
+                offsets[e] = run + incl - c;
+            }
+            run += __shfl_sync(0xffffffffu, incl, 31);
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < PERM_ITERS; ++it) {
+        if (it * PERM_THREADS >= NK) break;                   // uniform
+        for (int i = threadIdx.x; i < NW * MOE_MAX_NE; i += blockDim.x) (&wcnt[0][0])[i] = 0;
+        __syncthreads();
+        const int s = it * PERM_THREADS + threadIdx.x;
+        const bool live = s < NK;
+        const int e = live ? mine[it] : -1 - lane;            // dead lanes match nobody
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        if (live && rank == 0) wcnt[warp][e] = __popc(peers);
+        __syncthreads();
+        if (live) {
+            int pos = cursor[e] + rank;
+            for (int w = 0; w < warp; ++w) pos += wcnt[w][e];
+            grouped[pos] = (int32_t)s;
+            if (inv) inv[s] = pos;
+        }
+        __syncthreads();
+        for (int ee = threadIdx.x; ee < ne; ee += blockDim.x) {
+            int add = 0;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) add += wcnt[w][ee];
+            cursor[ee] += add;
+        }
+        __syncthreads();
+    }
+}
+
+// grouped, offsets and (optionally) the inverse permutation in one launch when the slots fit one block.
+int moe_permutation_inv(const int32_t* idx, int64_t NK, int ne, int32_t* grouped, int32_t* inv, int32_t* offsets) {
+    B200_REQUIRE(idx && grouped && offsets, "moe_permutation: null pointer");
+    B200_REQUIRE(ne > 0 && ne <= MOE_MAX_NE, "moe_permutation: ne out of range");
+    if (NK < 0 || NK > PERM_CHUNK) return fail(B200_EUNSUPPORTED, "moe_permutation_inv: more slots than one block takes");
+    perm_small_kernel<<<1, PERM_THREADS, 0, stream()>>>(idx, (int)NK, ne, grouped, inv, offsets);
+    B200_LAUNCH_CHECK("perm_small_kernel");
+    return B200_OK;
+}
+int moe_permutation_small_max() { return PERM_CHUNK; }
+
 int moe_permutation(const int32_t* idx, int64_t NK, int ne, int32_t* grouped, int32_t* offsets) {
     B200_REQUIRE(idx && grouped && offsets, "moe_permutation: null pointer");
     B200_REQUIRE(ne > 0 && ne <= MOE_MAX_NE, "moe_permutation: ne out of range");
@@ -434,7 +513,8 @@ constexpr int RC_TOK = 8, RC_EXP = 8, RC_COLS = 1024, RC_LD = RC_COLS + 4, RC_GL
 constexpr size_t RC_SMEM = ((size_t)(RC_TOK + RC_EXP) * RC_LD + (size_t)RC_TOK * RC_EXP * RC_GLD) * 4;
 __global__ void __launch_bounds__(256)
 route_logits_chains_kernel(const float* __restrict__ x, const float* __restrict__ router_w, float* __restrict__ logits,
-                           int64_t N, int d, int ne) {
+                           int64_t N, int d, int ne, const float* __restrict__ router_bias, float* __restrict__ probs_out,
+                           int32_t* __restrict__ idx_out, float* __restrict__ w_out, int K, int* __restrict__ counters) {
     extern __shared__ __align__(16) float rc_smem[];
     float* xs = rc_smem;                                  // [RC_TOK][RC_LD]
     float* ws = xs + RC_TOK * RC_LD;                      // [RC_EXP][RC_LD]
@@ -496,6 +576,51 @@ route_logits_chains_kernel(const float* __restrict__ x, const float* __restrict_
         const int e = e0 + ec;
         if (t < N && e < ne) logits[t * ne + e] = chain;
     }
+    // The block that completes a token group's last expert tile turns the group's logits into
+    // (idx, w), one warp per token: nobody waits - each block counts itself in after publishing
+    // its logits, and whoever counts last finds all of them (fence before the count and after it).
+    __shared__ int s_last;
+    if (!counters) return;                                   // the caller finishes with route_finish_kernel
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(&counters[blockIdx.x], 1) == (int)gridDim.y - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        float* s_p = rc_smem + (size_t)warp * (2 * MOE_MAX_NE + 2 * MOE_MAX_K);      // the tiles are dead
+        float* s_sel = s_p + MOE_MAX_NE;
+        float* s_w = s_sel + MOE_MAX_NE;
+        int* s_idx = reinterpret_cast<int*>(s_w + MOE_MAX_K);
+        const int64_t t = t0 + warp;
+        if (warp < RC_TOK && t < N) {
+            route_finish_warp(logits + t * ne, router_bias, ne, K, s_p, s_sel, s_idx, s_w,
+                              probs_out ? probs_out + t * ne : nullptr, lane);
+            if (lane < K) {
+                idx_out[t * K + lane] = s_idx[lane];
+                w_out[t * K + lane] = s_w[lane];
+            }
+        }
+        if (threadIdx.x == 0) counters[blockIdx.x] = 0;       // ready for the next call
+    }
+}
+
+// Arrival counters of the kernel above (one per token group), zeroed once; every call leaves them zero.
+// Not created while the stream is being captured into a graph (an allocation and a memset on the
+// default stream do not belong there): the caller then runs the separate finishing kernel.
+static int* route_counters() {
+    static int* p = nullptr;
+    if (!p) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream(), &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        if (cudaMalloc(&p, 4096) != cudaSuccess) { p = nullptr; cudaGetLastError(); return nullptr; }
+        if (cudaMemset(p, 0, 4096) != cudaSuccess) { cudaFree(p); p = nullptr; cudaGetLastError(); return nullptr; }
+    }
+    return p;
 }
 
 constexpr int RF_WARPS = 8;
@@ -529,8 +654,12 @@ int moe_route(const float* x, const float* router_w, const float* router_bias, f
                                                (int)RC_SMEM));
                 configured = true;
             }
+            int* counters = route_counters();
             const dim3 grid((unsigned)ceil_div64(N, RC_TOK), ceil_div(ne, RC_EXP));
-            route_logits_chains_kernel<<<grid, 256, RC_SMEM, stream()>>>(x, router_w, logits, N, d, ne);
+            route_logits_chains_kernel<<<grid, 256, RC_SMEM, stream()>>>(x, router_w, logits, N, d, ne, router_bias, probs, idx,
+                                                                         w, K, counters);
+            B200_LAUNCH_CHECK("route_logits_chains_kernel");
+            if (counters) return B200_OK;
         } else if (N <= 1024) {
             const dim3 grid((unsigned)ceil_div64(N, 8), ceil_div(ne, 32));
             route_logits_kernel<1, 1><<<grid, 256, 0, stream()>>>(x, router_w, logits, N, d, ne);

@@ -21,6 +21,8 @@ namespace b200 {
 int moe_route(const float* x, const float* router_w, const float* router_bias, float* probs, int32_t* idx, float* w,
               int64_t N, int d, int ne, int K);
 int moe_permutation(const int32_t* idx, int64_t NK, int ne, int32_t* grouped, int32_t* offsets);
+int moe_permutation_inv(const int32_t* idx, int64_t NK, int ne, int32_t* grouped, int32_t* inv, int32_t* offsets);
+int moe_permutation_small_max();
 
 constexpr int GROUPED_CHUNK_TOKENS = 8192;
 
@@ -228,6 +230,7 @@ int moe_dispatch_perm(const int32_t* idx, int64_t N, int ne, int K, int32_t* gro
     B200_REQUIRE(idx && grouped && inv && offsets, "moe_dispatch_perm: null pointer");
     const int64_t NK = N * K;
     if (NK <= 0) return B200_OK;
+    if (NK <= moe_permutation_small_max()) return moe_permutation_inv(idx, NK, ne, grouped, inv, offsets);
     const int rc = moe_permutation(idx, NK, ne, grouped, offsets);
     if (rc) return rc;
     perm_inverse_kernel<<<(unsigned)ceil_div64(NK, 256), 256, 0, stream()>>>(grouped, inv, NK);
