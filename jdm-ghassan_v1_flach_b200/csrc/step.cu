@@ -192,6 +192,11 @@ static int pick_next(b200_decoder* dec, float* logits, const int32_t* fed, int T
 }
 
 // The op sequence of one token, enqueued on the library's current stream.
+constexpr int RRN_PER = 16;      // row elements a thread keeps in registers: dim <= 4096
+__global__ void residual_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, float s,
+                                        const float* __restrict__ w, float* __restrict__ out, int dim, float eps,
+                                        __half* __restrict__ out16);
+
 static int enqueue_step(b200_decoder* dec, const int32_t* tokens, int32_t* next) {
     const int B = dec->batch, d = dec->d;
     cudaStream_t st = stream();
@@ -206,9 +211,22 @@ static int enqueue_step(b200_decoder* dec, const int32_t* tokens, int32_t* next)
     STEP(b200_embedding_forward_half(tokens, dec->embed, dec->x, B, d, dec->vocab));
     if (dec->emb_mult != 1.0f) STEP(b200_scale_inplace(dec->x, dec->emb_mult, (int64_t)B * d));
     const int res_grid = std::min(ceil_div(B * d, 256), num_sms() * 8);
+    // x += res_mult * proj followed by the next norm, one launch when the row fits the registers
+    auto residual_norm = [&](const float* norm_w) -> int {
+        if (d <= RRN_PER * 256) {
+            residual_rmsnorm_kernel<<<(unsigned)B, 256, 0, st>>>(dec->x, dec->proj, dec->res_mult, norm_w, dec->xb, d,
+                                                                dec->eps, nullptr);
+            B200_LAUNCH_CHECK("residual_rmsnorm_kernel");
+            return B200_OK;
+        }
+        residual_kernel<<<res_grid, 256, 0, st>>>(dec->x, dec->proj, dec->res_mult, (int64_t)B * d);
+        B200_LAUNCH_CHECK("residual_kernel");
+        return b200_rmsnorm_forward(dec->x, norm_w, dec->xb, nullptr, B, d, dec->eps);
+    };
+    if (dec->n_layers > 0) STEP(b200_rmsnorm_forward(dec->x, dec->L[0].attn_norm, dec->xb, nullptr, B, d, dec->eps));
+    else STEP(b200_rmsnorm_forward(dec->x, dec->final_norm, dec->xb, nullptr, B, d, dec->eps));
     for (int l = 0; l < dec->n_layers; ++l) {
         LayerW& w = dec->L[l];
-        STEP(b200_rmsnorm_forward(dec->x, w.attn_norm, dec->xb, nullptr, B, d, dec->eps));
         if (dec->types[l] == 0) {
             STEP(b200_mamba2_step_batched(dec->xb, static_cast<const uint16_t*>(w.mamba_in), w.conv_w, w.conv_b,
                                           w.dt_bias, w.a_log, w.D, w.mamba_norm,
@@ -241,18 +259,14 @@ static int enqueue_step(b200_decoder* dec, const int32_t* tokens, int32_t* next)
             else
                 STEP(b200_linear_forward_fp16(dec->attn, static_cast<const uint16_t*>(w.wo), dec->proj, B, qd, d));
         }
-        residual_kernel<<<res_grid, 256, 0, st>>>(dec->x, dec->proj, dec->res_mult, (int64_t)B * d);
-        B200_LAUNCH_CHECK("residual_kernel");
-        STEP(b200_rmsnorm_forward(dec->x, w.ffn_norm, dec->xb, nullptr, B, d, dec->eps));
+        STEP(residual_norm(w.ffn_norm));
         STEP(b200_moe_forward_bias_half(dec->xb, w.router, w.router_bias, static_cast<const uint16_t*>(w.gate),
                                         static_cast<const uint16_t*>(w.up), static_cast<const uint16_t*>(w.down),
                                         static_cast<const uint16_t*>(w.sh_gate), static_cast<const uint16_t*>(w.sh_up),
                                         static_cast<const uint16_t*>(w.sh_down), dec->proj, nullptr, nullptr, nullptr,
                                         nullptr, nullptr, nullptr, B, d, dec->E, dec->ne, dec->K, dec->SH, dec->qkind));
-        residual_kernel<<<res_grid, 256, 0, st>>>(dec->x, dec->proj, dec->res_mult, (int64_t)B * d);
-        B200_LAUNCH_CHECK("residual_kernel");
+        STEP(residual_norm(l + 1 < dec->n_layers ? dec->L[l + 1].attn_norm : dec->final_norm));
     }
-    STEP(b200_rmsnorm_forward(dec->x, dec->final_norm, dec->xb, nullptr, B, d, dec->eps));
     STEP(b200_linear_forward_fp16(dec->xb, dec->lm_head, dec->logits, B, d, dec->vocab));
     if (dec->logits_scaling != 1.0f)
         STEP(b200_scale_inplace(dec->logits, 1.0f / dec->logits_scaling, (int64_t)B * dec->vocab));
@@ -422,7 +436,6 @@ __global__ void last_rows_kernel(const float* __restrict__ src, float* __restric
 // x = x + s * y, then out = rmsnorm(x) * w: the residual update and the norm that follows it
 // in one pass over the row (the same operations in the same order as residual_kernel and
 // rmsnorm_kernel: double sum of squares, inv rounded to float).  One block per row.
-constexpr int RRN_PER = 16;      // row elements a thread keeps in registers: dim <= 4096
 // out16 (optional): the normalised row once more as fp16 (clamped), for the tensor-core GEMMs.
 __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, float s,
                                                                const float* __restrict__ w, float* __restrict__ out,
