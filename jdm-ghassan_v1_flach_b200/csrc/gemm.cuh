@@ -16,6 +16,10 @@ constexpr int GEMM_MIN_ROWS = 32;
 
 // dst[r, :] = fp16(src[(row_map ? row_map[r] / div : r), :]); K % 8 == 0.
 int pack_rows_f16(const float* src, const int32_t* row_map, int div, __half* dst, int64_t rows, int K);
+// The fp16 copy a producer registered for exactly these rows (f16_shadow_set), or null; see gemm_umma.cu.
+void f16_shadow_set(const float* src, const __half* rows16, int64_t rows, int K);
+void f16_shadow_clear();
+const __half* f16_shadow_find(const float* src, int64_t rows, int K);
 
 // C = A . B^T on tcgen05.  A [a_rows, K] fp16, B (and B2) [b_rows, K] fp16, fp32
 // accumulation.  Rows of A form `groups` consecutive ranges given by the device

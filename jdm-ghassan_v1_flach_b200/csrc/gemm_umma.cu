@@ -739,6 +739,17 @@ __global__ void __launch_bounds__(256) pack_rows_f16_kernel(const float* __restr
     }
 }
 
+// A producer that has already written a block of fp32 rows once more as fp16 (a fused norm)
+// registers the copy; the next un-gathered pack of exactly that block is then skipped and the
+// GEMM reads the copy.  One entry, owned by the thread that drives the library; the producer's
+// caller clears it as soon as the rows' consumers have been enqueued.
+static struct { const float* src; const __half* rows16; int64_t rows; int K; } g_f16_shadow = {nullptr, nullptr, 0, 0};
+void f16_shadow_set(const float* src, const __half* rows16, int64_t rows, int K) { g_f16_shadow = {src, rows16, rows, K}; }
+void f16_shadow_clear() { g_f16_shadow = {nullptr, nullptr, 0, 0}; }
+const __half* f16_shadow_find(const float* src, int64_t rows, int K) {
+    return (src && g_f16_shadow.src == src && g_f16_shadow.rows == rows && g_f16_shadow.K == K) ? g_f16_shadow.rows16 : nullptr;
+}
+
 int pack_rows_f16(const float* src, const int32_t* row_map, int div, __half* dst, int64_t rows, int K) {
     B200_REQUIRE(src && dst && rows >= 0 && K > 0 && K % 8 == 0, "pack_rows_f16: K must be a positive multiple of 8");
     B200_REQUIRE((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0,

@@ -150,9 +150,13 @@ int linear(const float* x, const void* w, int kind, float* y, int M, int K, int 
         void* ws;
         int rc = workspace(WS_LINEAR).ensure(a_bytes + b_bytes + 256, &ws);
         if (rc) return rc;
-        __half* a16 = static_cast<__half*>(ws);
-        rc = pack_rows_f16(x, nullptr, 1, a16, M, K);
-        if (rc) return rc;
+        const __half* a16 = f16_shadow_find(x, M, K);       // rows a fused norm has already written as fp16
+        if (!a16) {
+            __half* packed = static_cast<__half*>(ws);
+            rc = pack_rows_f16(x, nullptr, 1, packed, M, K);
+            if (rc) return rc;
+            a16 = packed;
+        }
         if (in_kernel)
             return umma_gemm_q(GEMM_EPI_STORE, kind, a16, M, w, nullptr, N, nullptr, 1, M, N, K, y, nullptr, N, 1.0f);
         const __half* b16 = static_cast<const __half*>(w);

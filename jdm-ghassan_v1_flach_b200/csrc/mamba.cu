@@ -497,13 +497,16 @@ int mamba2_step(const float* x, const void* w_in, const float* conv_w, const flo
     if (batch >= GEMM_MIN_ROWS && kind != KIND_F32) {
         // many sequences: both projections as tensor-core GEMMs, the conv step on its own
         void* wsp2;
-        rc = workspace(WS_MAMBA).ensure((per + p.proj) * batch * sizeof(float) + 512, &wsp2);
+        const bool out_gemm = p.d_inner % 8 == 0 && p.d_inner <= 4096 && linear_uses_gemm(w_out, kind, out, batch, p.d_inner, p.d);
+        const size_t f32_bytes = ((per + p.proj) * batch * sizeof(float) + 255) & ~(size_t)255;
+        rc = workspace(WS_MAMBA).ensure(f32_bytes + (out_gemm ? (size_t)batch * p.d_inner * 2 : 0) + 512, &wsp2);
         if (rc) return rc;
         gate = static_cast<float*>(wsp2);
         bc = gate + (size_t)batch * p.d_inner;
         dt_raw = bc + (size_t)batch * p.conv_dim;
         y = dt_raw + (((size_t)batch * p.n_heads + 3) & ~(size_t)3);
         float* proj = y + (size_t)batch * p.d_inner;
+        __half* y16 = reinterpret_cast<__half*>(static_cast<char*>(wsp2) + f32_bytes);   // the normed rows for out_proj
         rc = linear(x, w_in, kind, proj, batch, p.d, p.proj);
         if (rc) return rc;
         const int64_t items = (int64_t)batch * p.conv_dim;
@@ -518,8 +521,9 @@ int mamba2_step(const float* x, const void* w_in, const float* conv_w, const flo
             mamba_step_scan_kernel<<<dim3(ceil_div(rows, SCAN_WARPS), batch), SCAN_WARPS * 32, 0, stream()>>>(
                 bc, proj + p.d_inner + p.conv_dim, dt_bias, a_log, D, ssm_state, y, p.proj, p);
         B200_LAUNCH_CHECK("mamba_step_scan_kernel");
-        launch_gated_norm(y, proj, p.proj, norm_w, y, p.d_inner, p.eps, nullptr, batch);
+        launch_gated_norm(y, proj, p.proj, norm_w, y, p.d_inner, p.eps, out_gemm ? y16 : nullptr, batch);
         B200_LAUNCH_CHECK("mamba_gated_norm_kernel");
+        if (out_gemm) return linear_a16(y16, w_out, kind, out, batch, p.d_inner, p.d);
         return linear(y, w_out, kind, out, batch, p.d_inner, p.d);
     }
     for (int m0 = 0; m0 < batch; m0 += 8) {

@@ -299,10 +299,14 @@ int moe_shared_expert(const float* x, const void* sh_g, const void* sh_u, const 
         rc = workspace(WS_MOE).ensure(moe_shared_scratch_bytes(N, d, SH), &wsp);
         if (rc) return rc;
     }
-    __half* xs = static_cast<__half*>(wsp);
+    const __half* xs = f16_shadow_find(x, N, d);           // rows a fused norm has already written as fp16
     __half* sact = reinterpret_cast<__half*>(static_cast<char*>(wsp) + xs_bytes);
-    rc = pack_rows_f16(x, nullptr, 1, xs, N, d);
-    if (rc) return rc;
+    if (!xs) {
+        __half* packed = static_cast<__half*>(wsp);
+        rc = pack_rows_f16(x, nullptr, 1, packed, N, d);
+        if (rc) return rc;
+        xs = packed;
+    }
     if (kind == KIND_F16) {
         rc = umma_gemm(GEMM_EPI_SWIGLU, xs, N, static_cast<const __half*>(sh_g), static_cast<const __half*>(sh_u), SH,
                        nullptr, 1, (int)N, SH, d, nullptr, sact, SH, 1.0f);

@@ -111,6 +111,7 @@ struct b200_decoder {
     std::vector<LayerW> L;
     // buffers
     std::vector<void*> owned;
+    __half* xb16 = nullptr;      // xb once more as fp16 rows (per-op step with enough rows for the GEMMs)
     float *x = nullptr, *xb = nullptr, *proj = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *logits = nullptr;
     int32_t *tok = nullptr, *next = nullptr, *len = nullptr, *pos = nullptr, *page_table = nullptr;
     int position = 0;
@@ -212,11 +213,18 @@ static int enqueue_step(b200_decoder* dec, const int32_t* tokens, int32_t* next)
     if (dec->emb_mult != 1.0f) STEP(b200_scale_inplace(dec->x, dec->emb_mult, (int64_t)B * d));
     const int res_grid = std::min(ceil_div(B * d, 256), num_sms() * 8);
     // x += res_mult * proj followed by the next norm, one launch when the row fits the registers
+    // With enough rows for the tensor-core GEMMs the norm also leaves its rows as fp16 and registers
+    // them, so the projections that read xb next (in_proj; q, k, v; the shared expert) skip their
+    // conversion pass; the entry is dropped before xb is written again and when the step ends.
+    const bool rows16 = B >= GEMM_MIN_ROWS && d % 8 == 0;
+    f16_shadow_clear();
     auto residual_norm = [&](const float* norm_w) -> int {
+        f16_shadow_clear();
         if (d <= RRN_PER * 256) {
             residual_rmsnorm_kernel<<<(unsigned)B, 256, 0, st>>>(dec->x, dec->proj, dec->res_mult, norm_w, dec->xb, d,
-                                                                dec->eps, nullptr);
+                                                                dec->eps, rows16 ? dec->xb16 : nullptr);
             B200_LAUNCH_CHECK("residual_rmsnorm_kernel");
+            if (rows16) f16_shadow_set(dec->xb, dec->xb16, B, d);
             return B200_OK;
         }
         residual_kernel<<<res_grid, 256, 0, st>>>(dec->x, dec->proj, dec->res_mult, (int64_t)B * d);
@@ -267,7 +275,9 @@ static int enqueue_step(b200_decoder* dec, const int32_t* tokens, int32_t* next)
                                         nullptr, nullptr, nullptr, B, d, dec->E, dec->ne, dec->K, dec->SH, dec->qkind));
         STEP(residual_norm(l + 1 < dec->n_layers ? dec->L[l + 1].attn_norm : dec->final_norm));
     }
-    STEP(b200_linear_forward_fp16(dec->xb, dec->lm_head, dec->logits, B, d, dec->vocab));
+    rc = b200_linear_forward_fp16(dec->xb, dec->lm_head, dec->logits, B, d, dec->vocab);
+    f16_shadow_clear();
+    if (rc) return rc;
     if (dec->logits_scaling != 1.0f)
         STEP(b200_scale_inplace(dec->logits, 1.0f / dec->logits_scaling, (int64_t)B * dec->vocab));
     STEP(pick_next(dec, dec->logits, tokens, 1, next, 0, B));
@@ -834,6 +844,7 @@ int b200_decoder_create(b200_decoder** out, int batch, int vocab, int hidden, in
     auto A = [&](void** p, size_t bytes) { if (!rc) rc = dev_alloc(dec, p, bytes); };
     A((void**)&dec->x, (size_t)B * d * 4);
     A((void**)&dec->xb, (size_t)B * d * 4);
+    A((void**)&dec->xb16, (size_t)B * d * 2);
     A((void**)&dec->proj, (size_t)B * d * 4);
     A((void**)&dec->q, (size_t)B * std::max(qd, 1) * 4);
     A((void**)&dec->k, (size_t)B * std::max(kvd, 1) * 4);
