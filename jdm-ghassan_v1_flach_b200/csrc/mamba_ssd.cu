@@ -246,40 +246,39 @@ ssd_chunk_state_kernel(const float* __restrict__ proj, const float* __restrict__
 }
 
 // ---- carry over chunks: chunk_state[c] becomes the state BEFORE chunk c ------------
-// one thread per state element of (b, h); sequential over the chunks, eight chunks'
-// loads in flight at a time.
+// one thread per state element of (b, h): grid (d_head d_state / 256, heads, sequences), so no
+// index is divided; sequential over the chunks, eight chunks' loads in flight at a time.
 __global__ void __launch_bounds__(256)
 ssd_carry_kernel(float* __restrict__ chunk_state, const float* __restrict__ decay, float* __restrict__ state, int B,
                  int NC, MambaDims p, const int32_t* __restrict__ seq_chunk0) {
-    const int64_t per = (int64_t)p.d_head * p.d_state;
-    const int64_t total = (int64_t)B * p.n_heads * per;
+    const int per = p.d_head * p.d_state;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= per) return;
+    const int h = blockIdx.y, b = blockIdx.z;
     const int64_t cstride = (int64_t)p.n_heads * per;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t bh = i / per, e = i - bh * per;
-        const int b = (int)(bh / p.n_heads), h = (int)(bh - (int64_t)b * p.n_heads);
-        // the sequence's chunks are consecutive entries of the per-chunk arrays
-        const int64_t c_first = seq_chunk0 ? seq_chunk0[b] : (int64_t)b * NC;
-        const int nc = seq_chunk0 ? seq_chunk0[b + 1] - seq_chunk0[b] : NC;
-        float* cs = chunk_state + (c_first * p.n_heads + h) * per + e;
-        const float* dc = decay + c_first * p.n_heads + h;
-        float s = state[i];
-        for (int c0 = 0; c0 < nc; c0 += 8) {
-            float own[8], de[8];
+    const int64_t i = ((int64_t)b * p.n_heads + h) * per + e;
+    // the sequence's chunks are consecutive entries of the per-chunk arrays
+    const int64_t c_first = seq_chunk0 ? seq_chunk0[b] : (int64_t)b * NC;
+    const int nc = seq_chunk0 ? seq_chunk0[b + 1] - seq_chunk0[b] : NC;
+    float* cs = chunk_state + (c_first * p.n_heads + h) * per + e;
+    const float* dc = decay + c_first * p.n_heads + h;
+    float s = state[i];
+    for (int c0 = 0; c0 < nc; c0 += 8) {
+        float own[8], de[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (c0 + j < nc) {
-                    own[j] = __ldcs(cs + (c0 + j) * cstride);
-                    de[j] = dc[(int64_t)(c0 + j) * p.n_heads];
-                }
+        for (int j = 0; j < 8; ++j)
+            if (c0 + j < nc) {
+                own[j] = __ldcs(cs + (c0 + j) * cstride);
+                de[j] = dc[(int64_t)(c0 + j) * p.n_heads];
+            }
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (c0 + j < nc) {
-                    cs[(c0 + j) * cstride] = s;
-                    s = de[j] * s + own[j];
-                }
-        }
-        state[i] = s;
+        for (int j = 0; j < 8; ++j)
+            if (c0 + j < nc) {
+                cs[(c0 + j) * cstride] = s;
+                s = de[j] * s + own[j];
+            }
     }
+    state[i] = s;
 }
 
 // ---- per (chunk, head, sequence): outputs ------------------------------------------
@@ -751,8 +750,7 @@ int mamba_ssd_scan(const float* proj, const float* bc, const float* dt_bias, con
     else
         ssd_chunk_state_kernel<false><<<grid, SSD_THREADS, smem_st, stream()>>>(proj, bc, dt_bias, a_log, dtcum, cstate, decay, T, NC, p, tab, NT);
     B200_LAUNCH_CHECK("ssd_chunk_state_kernel");
-    const int64_t elems = (int64_t)B * p.n_heads * P * N;
-    ssd_carry_kernel<<<(unsigned)std::min<int64_t>(ceil_div64(elems, 256), (int64_t)num_sms() * 16), 256, 0, stream()>>>(
+    ssd_carry_kernel<<<dim3((unsigned)ceil_div(p.d_head * p.d_state, 256), (unsigned)p.n_heads, (unsigned)B), 256, 0, stream()>>>(
         cstate, decay, state, B, NC, p, lay ? lay->seq_chunk0 : nullptr);
     B200_LAUNCH_CHECK("ssd_carry_kernel");
     if (half_tiles)
