@@ -320,6 +320,7 @@ int moe_permutation(const int32_t* idx, int64_t NK, int ne, int32_t* grouped, in
     B200_REQUIRE(idx && grouped && offsets, "moe_permutation: null pointer");
     B200_REQUIRE(ne > 0 && ne <= MOE_MAX_NE, "moe_permutation: ne out of range");
     B200_REQUIRE(NK >= 0 && NK < ((int64_t)1 << 31), "moe_permutation: slot count out of range");
+    if (NK <= PERM_CHUNK) return moe_permutation_inv(idx, NK, ne, grouped, nullptr, offsets);     // one block does it all
     const int nblocks = (int)std::max<int64_t>(1, ceil_div64(NK, PERM_CHUNK));
     void* wsp;
     int rc = workspace(WS_PERM).ensure((size_t)nblocks * ne * sizeof(int32_t) + 256, &wsp);

@@ -162,6 +162,26 @@ def test_routing_bit_exact_many_tokens(oracle):
     assert not host(out).any()
 
 
+@pytest.mark.parametrize("d,ne,K", [(1536, 64, 6), (4096, 72, 10), (256, 10, 2)])
+def test_routing_bit_exact_decode_batches(oracle, d, ne, K):
+    """Token counts around the decode-batch router (8 x 8 chains per block, the finish folded into
+    the last block of a token group; 16 to 256 tokens) and its neighbours: indices identical,
+    probabilities and weights within a few ulp, expert counts that are no multiple of 8."""
+    from gpu_util import dev, empty, host, ops
+    r = np.random.default_rng(d + ne)
+    rw = (r.standard_normal((ne, d)) / np.sqrt(d)).astype(np.float32)
+    bias = (r.standard_normal(ne) * 0.5 / ne).astype(np.float32)
+    for N in (15, 16, 17, 100, 255, 256, 257):
+        x = r.standard_normal((N, d)).astype(np.float32)
+        probs, idx, w = oracle.moe_route(x, rw, bias, ne, K)
+        dp, di, dw = empty((N, ne)), empty((N, K), torch.int32), empty((N, K))
+        for _ in range(2):          # twice: the arrival counters must be back at zero
+            ops.moe_route(dev(x), dev(rw), dev(bias), dp, di, dw, N, d, ne, K)
+            assert np.array_equal(host(di), idx), N
+            _ulp_close(host(dp), probs)
+            _ulp_close(host(dw), w)
+
+
 def test_routing_ties_and_degenerate(oracle):
     """Identical router rows give exact ties (lowest index wins); huge negative bias and
     underflowing probabilities exercise the uniform-weight fallback."""
@@ -212,7 +232,8 @@ def test_no_shared_k1_and_scratch_outputs(oracle):
         np.testing.assert_allclose(got["sa"][t, 0], oracle.swiglu(g, u), rtol=1e-4, atol=1e-5)
 
 
-@pytest.mark.parametrize("NK,ne", [(1, 4), (6, 64), (4096 * 6, 64), (100003, 72), (64 * 4096 * 6, 64)])
+@pytest.mark.parametrize("NK,ne", [(1, 4), (6, 64), (384, 64), (1000, 72), (1024, 256), (1025, 64), (4096 * 6, 64), (100003, 72),
+                                   (64 * 4096 * 6, 64)])
 def test_permutation_bit_exact(oracle, NK, ne):
     """Stable counting sort by expert; the largest case is batch-64 x 4096-token prefill."""
     from gpu_util import dev, empty, host, ops
