@@ -55,9 +55,33 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(const float* __restri
     const float* row = logits + (int64_t)blockIdx.x * V;
     float bv = 0.0f;
     int bi = -1;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
+    auto visit = [&](float v, int i) {
         if (isfinite(v) && (bi < 0 || v > bv)) { bv = v; bi = i; }   // ascending i per thread
+    };
+    if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        // four runs of four per pass, all loads issued before the first compare
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const int n4 = V >> 2;
+        for (int q0 = threadIdx.x; q0 < n4; q0 += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int q = q0 + u * blockDim.x;
+                v[u] = q < n4 ? row4[q] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int q = q0 + u * blockDim.x;
+                if (q < n4) {
+                    visit(v[u].x, 4 * q);
+                    visit(v[u].y, 4 * q + 1);
+                    visit(v[u].z, 4 * q + 2);
+                    visit(v[u].w, 4 * q + 3);
+                }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < V; i += blockDim.x) visit(row[i], i);
     }
     auto take = [&](float ov, int oi) {
         if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
