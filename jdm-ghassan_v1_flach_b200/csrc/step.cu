@@ -814,7 +814,9 @@ static int enqueue(b200_decoder* dec, const int32_t* tokens, int32_t* next) {
     NvtxRange range(dec->fused == 2 ? "b200.step.persistent" : dec->fused ? "b200.step.fused" : "b200.step.per_op");
     if (dec->fused == 2) return enqueue_step_persistent(dec, tokens, next);
     if (dec->fused && dec->batch <= 8) return enqueue_step_fused(dec, tokens, next);
-    return enqueue_step(dec, tokens, next);
+    const int rc = enqueue_step(dec, tokens, next);
+    f16_shadow_clear();           // also when a call inside the step failed half-way
+    return rc;
 }
 
 static int check_ready(const b200_decoder* dec) {
